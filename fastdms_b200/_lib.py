@@ -1,0 +1,141 @@
+"""ctypes binding of libfastdms_b200.so (the C ABI declared in include/fastdms_b200.h).
+
+The library is the product: there is no CPU or PyTorch fallback.  `lib()` raises if the shared
+object is missing (build it with `python -m fastdms_b200.build` or `__graft_entry__.build()`).
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_char_p, c_double, c_float, c_int32, c_int64, c_void_p
+from pathlib import Path
+
+import torch
+
+LIB_PATH = Path(__file__).resolve().parent / "libfastdms_b200.so"
+
+FDMS_OK = 0
+FDMS_E_ARG, FDMS_E_DTYPE, FDMS_E_WORKSPACE, FDMS_E_CUDA, FDMS_E_CAPACITY = -1, -2, -3, -4, -5
+DEV_WAIT_TIMEOUT, DEV_BAD_INDEX = 1, 2
+
+F32, BF16, F16, E4M3 = 0, 1, 2, 3
+_DTYPES = {torch.float32: F32, torch.bfloat16: BF16, torch.float16: F16, torch.float8_e4m3fn: E4M3}
+
+P, I32, I64, F, DBL = c_void_p, c_int32, c_int64, c_float, c_double
+
+# name -> (restype, argtypes); the order is the order of the C declaration
+_SIGNATURES = {
+    "fdms_abi_version": (I32, []),
+    "fdms_last_error": (c_char_p, []),
+    "fdms_attn_decode_workspace_bytes": (I64, [I32, I32, I32]),
+    "fdms_attn_decode": (I32, [P, I32, I64, I64, P, P, I32, I64, P, P, I64, P, I64, I64, P, P,
+                               P, I32, I64, I64, I32, I32, I32, I32, F, P, P, I64, P, I64, P, P]),
+    "fdms_store_decode": (I32, [P, I64, I64, P, I64, I64, P, I64, I64, I32, P, I64, P, P, P, I32, I64,
+                                P, I64, P, I64, P, P, I32, I32, I32, I32, DBL, DBL, I32, I32, I32, I32, P, P]),
+    "fdms_extract_decisions": (I32, [P, I32, I64, I64, P, I64, I64, I32, I32, I32, DBL, DBL, P]),
+    "fdms_expire_compact": (I32, [P, I64, I64, I64, P, I64, I64, I64, P, P, I64, I64, P, P, I64, I32, I64,
+                                  P, I64, I64, I64, P, P, I64, P, P, I32, I32, I32, I32, I32, I32, P, P, P]),
+    "fdms_pack_count": (I32, [P, I64, P, P, P, I32, I32, I32, I32, P]),
+    "fdms_pack_scatter": (I32, [P, P, I32, I64, I64, P, I64, P, P, I32, P, P, P, I32, I64, P, I64,
+                                P, I64, I64, P, P, I64, I64, P, I64, I64, P, I64, I32, P, P,
+                                I32, I32, I32, I32, P, P]),
+    "fdms_alloc_pages": (I32, [P, P, I64, I64, I32, P, P, P, I32, I32, P, P]),
+    "fdms_free_pages": (I32, [P, I64, P, I64, I64, I32, P, P, P, I64, I32, I32, P, P]),
+    "fdms_build_decode_metadata": (I32, [P, P, I64, I64, P, I64, I64, I64, I32, P, P, I64, P,
+                                         P, P, P, P, I32, I32, I32, P, P]),
+    "fdms_record_decisions": (I32, [P, I64, I64, I64, P, I64, I64, I64, P, I64, I64, P, I64, I64, P, P,
+                                    I32, I32, I32, I32, P, P]),
+    "fdms_kv_quant": (I32, [P, I32, P, P, I64, I32, I32, P]),
+    "fdms_kv_dequant": (I32, [P, P, I32, P, I64, I32, I32, P]),
+}
+
+_lib = None
+
+
+def exported_symbols() -> list[str]:
+    return list(_SIGNATURES)
+
+
+def lib() -> ctypes.CDLL:
+    """The loaded library; raises RuntimeError when it has not been built."""
+    global _lib
+    if _lib is None:
+        if not LIB_PATH.exists():
+            raise RuntimeError(
+                f"{LIB_PATH} is missing: the fastdms_b200 CUDA library has not been built "
+                "(run `python -m fastdms_b200.build`); there is no fallback path")
+        handle = ctypes.CDLL(str(LIB_PATH))
+        for name, (res, args) in _SIGNATURES.items():
+            fn = getattr(handle, name)
+            fn.restype = res
+            fn.argtypes = args
+        _lib = handle
+    return _lib
+
+
+def dtype_code(dt: torch.dtype) -> int:
+    try:
+        return _DTYPES[dt]
+    except KeyError:
+        raise ValueError(f"unsupported dtype {dt}") from None
+
+
+def ptr(t: torch.Tensor | None) -> int | None:
+    return None if t is None else t.data_ptr()
+
+
+def stream_ptr(device) -> int:
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+def check(status: int) -> None:
+    """Maps a C status to the reference's exception classes (ValueError for argument/shape/dtype
+    problems, RuntimeError for state/capacity/CUDA problems)."""
+    if status == FDMS_OK:
+        return
+    msg = lib().fdms_last_error().decode("utf-8", "replace")
+    if status in (FDMS_E_ARG, FDMS_E_DTYPE, FDMS_E_WORKSPACE):
+        raise ValueError(msg)
+    raise RuntimeError(msg)
+
+
+def require_cuda(*tensors: torch.Tensor) -> None:
+    for t in tensors:
+        if t is not None and not t.is_cuda:
+            raise RuntimeError("fastdms_b200 kernels require CUDA tensors (there is no CPU fallback)")
+
+
+# ---- per-device scratch owned by the Python layer (the C library allocates nothing) ------------
+_status_words: dict[int, torch.Tensor] = {}
+_workspaces: dict[tuple[int, int], torch.Tensor] = {}
+
+
+def status_word(device: torch.device) -> torch.Tensor:
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    w = _status_words.get(idx)
+    if w is None:
+        w = torch.zeros(1, dtype=torch.int32, device=device)
+        _status_words[idx] = w
+    return w
+
+
+def read_device_status(device: torch.device | str = "cuda", clear: bool = True) -> int:
+    """Synchronising read of the device status word (OR of FDMS_DEV_* bits raised by kernels)."""
+    device = torch.device(device)
+    w = status_word(device)
+    v = int(w.item())
+    if clear and v:
+        w.zero_()
+    return v
+
+
+def attn_workspace(device: torch.device, batch: int, num_kv_heads: int, head_dim: int) -> torch.Tensor:
+    """Zero-initialised split-K workspace, one per (device, stream); grown on demand and reused
+    (the kernel leaves its counters at zero)."""
+    need = lib().fdms_attn_decode_workspace_bytes(batch, num_kv_heads, head_dim)
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    key = (idx, torch.cuda.current_stream(device).cuda_stream)
+    ws = _workspaces.get(key)
+    if ws is None or ws.numel() < need:
+        ws = torch.zeros(need, dtype=torch.uint8, device=device)
+        _workspaces[key] = ws
+    return ws

@@ -1,0 +1,733 @@
+// Compact decode attention over ragged per-(sequence, KV head) spans of the compact KV pool.
+//
+// Fast path (FP8 e4m3 pools, head_dim 64 or 128, group size <= 8)
+// ----------------------------------------------------------------
+// The kernel is a single-wave, work-balanced scan of the pool:
+//   * Work unit = one 16-row page of one span.  Every CTA computes the exclusive prefix sum of the
+//     spans' page counts in shared memory (one coalesced read of live_counts) and takes an equal
+//     contiguous slice of the flattened page list, so ragged lengths cost no idle CTAs and no host
+//     round trip ("split-K across the compact length" with a stream-K style partition).
+//   * A producer warp resolves each page's address (span base or block table) and stages K and V
+//     pages into a shared-memory ring with bulk asynchronous copies (cp.async.bulk, the TMA unit's
+//     untiled form) that complete on per-stage mbarriers.  A CTA's whole slice is normally in
+//     flight at once: the working set of one layer is only a few times the bandwidth-delay
+//     product of HBM, so latency is hidden by issuing everything up front, not by occupancy.
+//   * Eight consumer warps each own every 8th page.  Per page a warp computes the GQA-packed
+//     S = q K^T and O += P V tiles with mma.sync.m16n8k16 (f16 operands, f32 accumulate): q heads
+//     sit on the M axis, FP8 K/V bytes are converted exactly to f16 in registers, the softmax
+//     is the usual online form with warp-shuffle row reductions in the log2 domain.
+//   * Partial (m, l, O) of a CTA's slice are merged across warps in shared memory.  A span cut
+//     by a slice boundary is finished by the last CTA to arrive at a per-span counter
+//     (threadfence + atomic, no spinning): it folds the partials left in the workspace and writes
+//     the output.  No second launch.
+// Every wait on an mbarrier is bounded; on expiry the kernel raises FDMS_DEV_WAIT_TIMEOUT in the
+// status word, stops issuing copies, drains with short waits and returns.
+//
+// Algorithmic HBM bytes per launch: sum over spans of live * 2 * head_dim (FP8 K + V), plus
+// batch*q_heads*head_dim*(q + out) and 8-12 bytes of metadata per span.
+//
+// Generic path: any pool dtype (f32/bf16/f16/e4m3), any head_dim <= 256, any group size.  One CTA per
+// (sequence, q head); used for the reference's small float32 fixtures, not for speed.
+#include <cuda.h>
+#include <stdlib.h>
+
+#include "common.cuh"
+
+namespace fdms {
+
+constexpr int kPage = 16;
+constexpr int kConsumerWarps = 8;
+constexpr int kConsumerThreads = kConsumerWarps * 32;
+constexpr int kFastThreads = kConsumerThreads + 32;   // + one producer warp
+constexpr int kMaxGroup = 8;
+constexpr int kMaxGrid = 1024;
+constexpr int kWaitLimit = 400000;       // polls of mbarrier.try_wait before giving up
+constexpr int kWaitLimitDrain = 2000;
+constexpr float kLog2e = 1.4426950408889634f;
+
+// ------------------------------------------------------------------------------------------------
+// PTX wrappers
+// ------------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, int count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+    return ok != 0;
+}
+// Bounded wait: false when the limit ran out.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int limit) {
+    for (int i = 0; i < limit; ++i)
+        if (mbar_try_wait(bar, parity)) return true;
+    return false;
+}
+// 1-D bulk copy global -> shared, completing `bytes` on the mbarrier.  Addresses and size are
+// multiples of 16 bytes.
+__device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
+    asm volatile(
+        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+        ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void consumer_bar() {
+    asm volatile("bar.sync 1, %0;" ::"n"(kConsumerThreads) : "memory");
+}
+__device__ __forceinline__ float ex2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+__device__ __forceinline__ uint32_t e4m3x2_to_f16x2(uint32_t two_bytes) {
+    uint32_t r;
+    asm("{\n\t.reg .b16 t;\n\tcvt.u16.u32 t, %1;\n\tcvt.rn.f16x2.e4m3x2 %0, t;\n\t}" : "=r"(r) : "r"(two_bytes));
+    return r;
+}
+__device__ __forceinline__ uint32_t pack_f16x2(float lo, float hi) {
+    __half2 h = __floats2half2_rn(lo, hi);
+    return *(uint32_t*)&h;
+}
+// D(16x8, f32) += A(16x16, f16) * B(16x8, f16) with A rows 8..15 identically zero (a1 = a3 = 0):
+// only c0, c1 (row g) carry data.
+__device__ __forceinline__ void mma_top(float& c0, float& c1, uint32_t a0, uint32_t a2, uint32_t b0, uint32_t b1) {
+    float d2, d3;
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%10,%10};"
+        : "+f"(c0), "+f"(c1), "=f"(d2), "=f"(d3)
+        : "r"(a0), "r"(0u), "r"(a2), "r"(0u), "r"(b0), "r"(b1), "f"(0.0f));
+}
+
+// Physical row inside a page for MMA column n of n-tile u.  The permutation keeps the K reads
+// (rows tokrow(u, g), 16 bytes per lane) free of bank conflicts and the V reads (rows
+// tokrow(u, 2t), tokrow(u, 2t+1), 8 bytes per lane) at the 2-way minimum that 64-byte rows allow.
+__device__ __forceinline__ int tokrow(int u, int n) {
+    const int tp = n >> 1;
+    return 8 * u + 2 * tp + ((n & 1) ^ (tp & 1));
+}
+
+struct AttnParams {
+    const void* q; int q_dtype; int64_t q_sb, q_sh;
+    const uint8_t* k_pool; const uint8_t* v_pool; int64_t pool_rows;
+    const int32_t* base; const int32_t* live; int64_t meta_sb;
+    const int32_t* bt; int64_t bt_sb, bt_sh;
+    const float* k_scale; const float* v_scale;
+    void* out; int out_dtype; int64_t out_sb, out_sh;
+    int batch, hq, hk, group;
+    float scale;
+    const int64_t* rope_pos; const float* rope_cs; int64_t rope_stride;
+    int32_t* counters; float* part_ml; float* part_o;
+    int32_t* dev_status;
+    int stages;
+};
+
+// ------------------------------------------------------------------------------------------------
+// Fast kernel
+// ------------------------------------------------------------------------------------------------
+template <int D>
+struct FastCfg {
+    static constexpr int kCh = D / 64;          // 64-element chunks of a row
+    static constexpr int kKSteps = D / 16;      // MMA k-steps of S = q K^T
+    static constexpr int kNT = D / 8;           // MMA n-tiles of O = P V
+    static constexpr int kPageBytes = kPage * D;
+    static constexpr int kStageBytes = 2 * kPageBytes;
+};
+
+// q element (with optional inline neox RoPE and decision-lane zeroing), float32.
+__device__ __forceinline__ float load_q_elem(const AttnParams& p, int b, int head, int g, int d, int dim) {
+    const int64_t off = (int64_t)b * p.q_sb + (int64_t)head * p.q_sh;
+    float x = load_as_float(p.q, off + d, p.q_dtype);
+    if (p.rope_pos == nullptr) return x;
+    const int half = dim >> 1;
+    const bool lower = d < half;
+    const int i = lower ? d : d - half;
+    float x1 = lower ? x : load_as_float(p.q, off + i, p.q_dtype);
+    float x2 = lower ? load_as_float(p.q, off + half + i, p.q_dtype) : x;
+    if (g == 0 && i == half - 1) x2 = 0.0f;      // the borrowed decision channel (head_dim - 1)
+    const float* cs = p.rope_cs + p.rope_pos[b] * p.rope_stride;
+    const float c = cs[i], s = cs[half + i];
+    return lower ? __fsub_rn(__fmul_rn(x1, c), __fmul_rn(x2, s)) : __fadd_rn(__fmul_rn(x2, c), __fmul_rn(x1, s));
+}
+
+template <int D>
+__global__ void __launch_bounds__(kFastThreads, (D == 64 ? 2 : 1)) attn_decode_fast_kernel(AttnParams p) {
+    using C = FastCfg<D>;
+    extern __shared__ __align__(128) uint8_t smem[];
+    const int items = p.batch * p.hk;
+    const int NS = p.stages;
+    // shared memory carve-up
+    uint8_t* s_stage = smem;
+    uint64_t* s_full = (uint64_t*)(s_stage + (size_t)NS * C::kStageBytes);
+    uint64_t* s_empty = s_full + NS;
+    float* s_m = (float*)(s_empty + NS);                      // [warps][8]
+    float* s_l = s_m + kConsumerWarps * kMaxGroup;            // [warps][8]
+    float* s_o = s_l + kConsumerWarps * kMaxGroup;            // [warps][8][D]
+    int* s_cu = (int*)(s_o + kConsumerWarps * kMaxGroup * D); // [items + 1] page prefix
+    int* s_live = s_cu + items + 1;                           // [items]
+    volatile int* s_flags = s_live + items;                   // [0] abort, [1] last-arriver flag
+    __shared__ int s_scan[kFastThreads / 32];
+    __shared__ int s_carry;
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+
+    // ---- page prefix over spans (every CTA, redundantly) -------------------------------------
+    if (tid == 0) { s_carry = 0; s_flags[0] = 0; s_flags[1] = 0; s_cu[0] = 0; }
+    __syncthreads();
+    for (int i0 = 0; i0 < items; i0 += kFastThreads) {
+        const int i = i0 + tid;
+        int n = 0;
+        if (i < items) {
+            const int b = i / p.hk, h = i - b * p.hk;
+            n = p.live[(int64_t)b * p.meta_sb + h];
+            if (n < 0) n = 0;
+            s_live[i] = n;
+        }
+        int x = (n + kPage - 1) / kPage;
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+            const int y = __shfl_up_sync(0xffffffffu, x, d);
+            if (lane >= d) x += y;
+        }
+        if (lane == 31) s_scan[warp] = x;
+        __syncthreads();
+        int before = s_carry;
+        for (int w = 0; w < warp; ++w) before += s_scan[w];
+        if (i < items) s_cu[i + 1] = before + x;
+        __syncthreads();
+        if (tid == kFastThreads - 1) s_carry = before + x;
+        __syncthreads();
+    }
+    const int NP = s_cu[items];
+    const int ncta = min((int)gridDim.x, NP);
+    const int cta = blockIdx.x;
+
+    // spans without any live row produce zeros (CTA 0)
+    if (cta == 0) {
+        for (int i = 0; i < items; ++i) {
+            if (s_live[i] > 0) continue;
+            const int b = i / p.hk, h = i - b * p.hk;
+            for (int e = tid; e < p.group * D; e += kFastThreads) {
+                const int g = e / D, d = e - g * D;
+                store_from_float(p.out, (int64_t)b * p.out_sb + (int64_t)(h * p.group + g) * p.out_sh + d, p.out_dtype, 0.0f);
+            }
+        }
+    }
+    if (cta >= ncta) return;
+
+    const int pg_begin = (int)(((long long)cta * NP) / ncta);
+    const int pg_end = (int)(((long long)(cta + 1) * NP) / ncta);
+    const int npages = pg_end - pg_begin;
+
+    if (tid == 0) {
+        for (int s = 0; s < NS; ++s) { mbar_init(&s_full[s], 1); mbar_init(&s_empty[s], 1); }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+
+    // first span overlapping this slice: largest item with s_cu[item] <= pg_begin
+    int item0;
+    {
+        int lo = 0, hi = items;               // invariant: s_cu[lo] <= pg_begin < s_cu[hi]
+        while (hi - lo > 1) {
+            const int mid = (lo + hi) >> 1;
+            if (s_cu[mid] <= pg_begin) lo = mid; else hi = mid;
+        }
+        item0 = lo;
+    }
+
+    if (warp == kConsumerWarps) {
+        // =============================== producer warp =========================================
+        for (int j0 = 0; j0 < npages; j0 += 32) {
+            const int j = j0 + lane;
+            if (j < npages && s_flags[0] == 0) {
+                const int gp = pg_begin + j;
+                int lo = item0, hi = items;
+                while (hi - lo > 1) {
+                    const int mid = (lo + hi) >> 1;
+                    if (s_cu[mid] <= gp) lo = mid; else hi = mid;
+                }
+                const int item = lo;
+                const int pi = gp - s_cu[item];
+                const int rows = min(kPage, s_live[item] - pi * kPage);
+                const int b = item / p.hk, h = item - b * p.hk;
+                int64_t row0;
+                if (p.bt) row0 = (int64_t)p.bt[(int64_t)b * p.bt_sb + (int64_t)h * p.bt_sh + pi] * kPage;
+                else row0 = (int64_t)p.base[(int64_t)b * p.meta_sb + h] + (int64_t)pi * kPage;
+                const int slot = j % NS;
+                bool ok = true;
+                if (j >= NS) ok = mbar_wait(&s_empty[slot], ((j / NS) - 1) & 1, kWaitLimit);
+                if (!ok) {
+                    s_flags[0] = 1;
+                    if (p.dev_status) atomicOr(p.dev_status, FDMS_DEV_WAIT_TIMEOUT);
+                } else if (row0 < 0 || row0 + rows > p.pool_rows) {
+                    // bad address: flag it and complete the stage without copying (zero rows valid)
+                    if (p.dev_status) atomicOr(p.dev_status, FDMS_DEV_BAD_INDEX);
+                    mbar_arrive(&s_full[slot]);
+                } else {
+                    const uint32_t bytes = (uint32_t)rows * D;
+                    uint8_t* dst = s_stage + (size_t)slot * C::kStageBytes;
+                    mbar_expect_tx(&s_full[slot], 2 * bytes);
+                    bulk_g2s(dst, p.k_pool + row0 * D, bytes, &s_full[slot]);
+                    bulk_g2s(dst + C::kPageBytes, p.v_pool + row0 * D, bytes, &s_full[slot]);
+                }
+            }
+            __syncwarp();
+        }
+        return;
+    }
+
+    // ================================= consumer warps ===========================================
+    const int g = lane >> 2, t = lane & 3;
+    for (int item = item0; item < items && s_cu[item] < pg_end; ++item) {
+        const int it_begin = s_cu[item], it_end = s_cu[item + 1];
+        if (it_begin == it_end) continue;
+        const int seg_begin = max(it_begin, pg_begin), seg_end = min(it_end, pg_end);
+        const int b = item / p.hk, h = item - b * p.hk;
+        const int live = s_live[item];
+        const float sl2 = p.scale * (p.k_scale ? p.k_scale[h] : 1.0f) * kLog2e;
+
+        // q fragments of head g (rows >= group are zero)
+        uint32_t qa[C::kKSteps][2];
+#pragma unroll
+        for (int ch = 0; ch < C::kCh; ++ch) {
+#pragma unroll
+            for (int s = 0; s < 4; ++s) {
+                float x[4] = {0.f, 0.f, 0.f, 0.f};
+                if (g < p.group) {
+                    const int d0 = 64 * ch + 16 * t + 4 * s;
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) x[e] = load_q_elem(p, b, h * p.group + g, g, d0 + e, D);
+                }
+                qa[4 * ch + s][0] = pack_f16x2(x[0], x[1]);
+                qa[4 * ch + s][1] = pack_f16x2(x[2], x[3]);
+            }
+        }
+
+        float m_run = -INFINITY, l_run = 0.0f;
+        float o[C::kNT][2];
+#pragma unroll
+        for (int j = 0; j < C::kNT; ++j) { o[j][0] = 0.0f; o[j][1] = 0.0f; }
+
+        // pages of this segment owned by this warp: local index j = gp - pg_begin, j % 8 == warp
+        int j = seg_begin - pg_begin;
+        j += (warp - (j % kConsumerWarps) + kConsumerWarps) % kConsumerWarps;
+        for (; j < seg_end - pg_begin; j += kConsumerWarps) {
+            const int slot = j % NS;
+            const bool aborted = s_flags[0] != 0;
+            const bool ok = mbar_wait(&s_full[slot], (j / NS) & 1, aborted ? kWaitLimitDrain : kWaitLimit);
+            if (!ok && !aborted) {
+                s_flags[0] = 1;
+                if (lane == 0 && p.dev_status) atomicOr(p.dev_status, FDMS_DEV_WAIT_TIMEOUT);
+            }
+            if (ok && !aborted) {
+                const uint8_t* Ks = s_stage + (size_t)slot * C::kStageBytes;
+                const uint8_t* Vs = Ks + C::kPageBytes;
+                const int pi = pg_begin + j - it_begin;
+                const int rows = min(kPage, live - pi * kPage);
+
+                // ---- S = q K^T for the two 8-token n-tiles ----
+                float sc[2][2];
+#pragma unroll
+                for (int u = 0; u < 2; ++u) {
+                    const int r = tokrow(u, g);
+                    float c0 = 0.0f, c1 = 0.0f;
+                    uint4 kw[C::kCh];
+                    if (C::kCh == 1) {
+                        kw[0] = *(const uint4*)(Ks + r * D + 16 * t);
+                    } else {
+                        // 128-byte rows: odd rows read the upper half first so that the two rows of
+                        // a quarter-warp hit different banks
+                        const int sw = r & 1;
+                        const uint4 a = *(const uint4*)(Ks + r * D + 64 * sw + 16 * t);
+                        const uint4 c = *(const uint4*)(Ks + r * D + 64 * (sw ^ 1) + 16 * t);
+                        kw[0] = sw ? c : a;
+                        kw[C::kCh - 1] = sw ? a : c;
+                    }
+#pragma unroll
+                    for (int ch = 0; ch < C::kCh; ++ch) {
+                        const uint32_t w4[4] = {kw[ch].x, kw[ch].y, kw[ch].z, kw[ch].w};
+#pragma unroll
+                        for (int s = 0; s < 4; ++s) {
+                            const uint32_t b0 = e4m3x2_to_f16x2(w4[s] & 0xffffu);
+                            const uint32_t b1 = e4m3x2_to_f16x2(w4[s] >> 16);
+                            mma_top(c0, c1, qa[4 * ch + s][0], qa[4 * ch + s][1], b0, b1);
+                        }
+                    }
+                    sc[u][0] = c0 * sl2;
+                    sc[u][1] = c1 * sl2;
+                }
+                int rA[2], rB[2];
+#pragma unroll
+                for (int u = 0; u < 2; ++u) { rA[u] = tokrow(u, 2 * t); rB[u] = tokrow(u, 2 * t + 1); }
+                if (rows < kPage) {
+#pragma unroll
+                    for (int u = 0; u < 2; ++u) {
+                        if (rA[u] >= rows) sc[u][0] = -INFINITY;
+                        if (rB[u] >= rows) sc[u][1] = -INFINITY;
+                    }
+                }
+                // ---- online softmax (row = head g, reduce over the 4 lanes of the quad) ----
+                float mx = fmaxf(fmaxf(sc[0][0], sc[0][1]), fmaxf(sc[1][0], sc[1][1]));
+                mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+                mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+                const float m_new = fmaxf(m_run, mx);
+                const float alpha = ex2(m_run - m_new);
+                float pr[2][2];
+#pragma unroll
+                for (int u = 0; u < 2; ++u) { pr[u][0] = ex2(sc[u][0] - m_new); pr[u][1] = ex2(sc[u][1] - m_new); }
+                l_run = l_run * alpha + (pr[0][0] + pr[0][1]) + (pr[1][0] + pr[1][1]);
+                m_run = m_new;
+                const uint32_t pa0 = pack_f16x2(pr[0][0], pr[0][1]);
+                const uint32_t pa2 = pack_f16x2(pr[1][0], pr[1][1]);
+#pragma unroll
+                for (int jn = 0; jn < C::kNT; ++jn) { o[jn][0] *= alpha; o[jn][1] *= alpha; }
+
+                // ---- O += P V ----
+#pragma unroll
+                for (int ch = 0; ch < C::kCh; ++ch) {
+                    uint2 va[2], vb[2];
+#pragma unroll
+                    for (int u = 0; u < 2; ++u) {
+                        if (C::kCh == 1) {
+                            va[u] = *(const uint2*)(Vs + rA[u] * D + 8 * g);
+                            vb[u] = *(const uint2*)(Vs + rB[u] * D + 8 * g);
+                        } else {
+                            va[u] = *(const uint2*)(Vs + rA[u] * D + 64 * ch + 8 * g);
+                            vb[u] = *(const uint2*)(Vs + rB[u] * D + 64 * ch + 8 * g);
+                        }
+                        if (rows < kPage) {                   // stale bytes must not reach the MMA
+                            if (rA[u] >= rows) va[u] = make_uint2(0u, 0u);
+                            if (rB[u] >= rows) vb[u] = make_uint2(0u, 0u);
+                        }
+                    }
+                    uint32_t bf[2][8];
+#pragma unroll
+                    for (int u = 0; u < 2; ++u) {
+                        const uint32_t x0 = __byte_perm(va[u].x, vb[u].x, 0x5140);
+                        const uint32_t x1 = __byte_perm(va[u].x, vb[u].x, 0x7362);
+                        const uint32_t y0 = __byte_perm(va[u].y, vb[u].y, 0x5140);
+                        const uint32_t y1 = __byte_perm(va[u].y, vb[u].y, 0x7362);
+                        bf[u][0] = e4m3x2_to_f16x2(x0 & 0xffffu); bf[u][1] = e4m3x2_to_f16x2(x0 >> 16);
+                        bf[u][2] = e4m3x2_to_f16x2(x1 & 0xffffu); bf[u][3] = e4m3x2_to_f16x2(x1 >> 16);
+                        bf[u][4] = e4m3x2_to_f16x2(y0 & 0xffffu); bf[u][5] = e4m3x2_to_f16x2(y0 >> 16);
+                        bf[u][6] = e4m3x2_to_f16x2(y1 & 0xffffu); bf[u][7] = e4m3x2_to_f16x2(y1 >> 16);
+                    }
+#pragma unroll
+                    for (int jj = 0; jj < 8; ++jj)
+                        mma_top(o[8 * ch + jj][0], o[8 * ch + jj][1], pa0, pa2, bf[0][jj], bf[1][jj]);
+                }
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&s_empty[slot]);
+        }
+
+        // ---- merge the warps' partial (m, l, O) of this segment ----
+        l_run += __shfl_xor_sync(0xffffffffu, l_run, 1);
+        l_run += __shfl_xor_sync(0xffffffffu, l_run, 2);
+        if (t == 0) { s_m[warp * kMaxGroup + g] = m_run; s_l[warp * kMaxGroup + g] = l_run; }
+        {
+            float* so = s_o + ((size_t)warp * kMaxGroup + g) * D;
+#pragma unroll
+            for (int jn = 0; jn < C::kNT; ++jn) {
+                const int ch = jn >> 3, jj = jn & 7;
+                so[64 * ch + 16 * t + jj] = o[jn][0];
+                so[64 * ch + 16 * t + 8 + jj] = o[jn][1];
+            }
+        }
+        consumer_bar();
+        const bool whole = seg_begin == it_begin && seg_end == it_end;
+        const float vs = p.v_scale ? p.v_scale[h] : 1.0f;
+        const int pslot = 2 * cta + (seg_begin == pg_begin ? 0 : 1);
+        for (int e = tid; e < p.group * D; e += kConsumerThreads) {
+            const int gg = e / D, d = e - gg * D;
+            float M = -INFINITY;
+#pragma unroll
+            for (int w = 0; w < kConsumerWarps; ++w) M = fmaxf(M, s_m[w * kMaxGroup + gg]);
+            float acc = 0.0f, L = 0.0f;
+#pragma unroll
+            for (int w = 0; w < kConsumerWarps; ++w) {
+                const float f = ex2(s_m[w * kMaxGroup + gg] - M);
+                acc += f * s_o[((size_t)w * kMaxGroup + gg) * D + d];
+                L += f * s_l[w * kMaxGroup + gg];
+            }
+            if (whole) {
+                store_from_float(p.out, (int64_t)b * p.out_sb + (int64_t)(h * p.group + gg) * p.out_sh + d,
+                                 p.out_dtype, acc / L * vs);
+            } else {
+                p.part_o[((size_t)pslot * kMaxGroup + gg) * D + d] = acc;
+                if (d == 0) {
+                    p.part_ml[((size_t)pslot * kMaxGroup + gg) * 2] = M;
+                    p.part_ml[((size_t)pslot * kMaxGroup + gg) * 2 + 1] = L;
+                }
+            }
+        }
+        if (!whole) {
+            // publish the partial, count arrivals; the last CTA of the span folds all of them
+            __threadfence();
+            consumer_bar();
+            const int c_first = (int)((((long long)it_begin + 1) * ncta - 1) / NP);
+            const int c_last = (int)(((long long)it_end * ncta - 1) / NP);
+            if (tid == 0) {
+                const int prev = atomicAdd(&p.counters[item], 1);
+                const int last = prev == (c_last - c_first);
+                if (last) p.counters[item] = 0;          // leave the workspace ready for the next call
+                s_flags[1] = last;
+            }
+            consumer_bar();
+            if (s_flags[1]) {
+                __threadfence();
+                for (int e = tid; e < p.group * D; e += kConsumerThreads) {
+                    const int gg = e / D, d = e - gg * D;
+                    float M = -INFINITY;
+                    for (int c = c_first; c <= c_last; ++c) {
+                        const int cb = (int)(((long long)c * NP) / ncta);
+                        const int ps = 2 * c + (max(it_begin, cb) == cb ? 0 : 1);
+                        M = fmaxf(M, __ldcg(&p.part_ml[((size_t)ps * kMaxGroup + gg) * 2]));
+                    }
+                    float acc = 0.0f, L = 0.0f;
+                    for (int c = c_first; c <= c_last; ++c) {
+                        const int cb = (int)(((long long)c * NP) / ncta);
+                        const int ps = 2 * c + (max(it_begin, cb) == cb ? 0 : 1);
+                        const float f = ex2(__ldcg(&p.part_ml[((size_t)ps * kMaxGroup + gg) * 2]) - M);
+                        acc += f * __ldcg(&p.part_o[((size_t)ps * kMaxGroup + gg) * D + d]);
+                        L += f * __ldcg(&p.part_ml[((size_t)ps * kMaxGroup + gg) * 2 + 1]);
+                    }
+                    store_from_float(p.out, (int64_t)b * p.out_sb + (int64_t)(h * p.group + gg) * p.out_sh + d,
+                                     p.out_dtype, acc / L * vs);
+                }
+            }
+        }
+        consumer_bar();     // merge buffers are reused by the next segment
+    }
+}
+
+// ------------------------------------------------------------------------------------------------
+// Generic kernel: one CTA (4 warps) per (sequence, q head); warps stride over the span's rows,
+// lanes over head_dim.
+// ------------------------------------------------------------------------------------------------
+constexpr int kGenWarps = 4;
+constexpr int kGenMaxPerLane = 8;      // head_dim <= 256
+
+struct GenParams {
+    AttnParams a;
+    const void* k_pool; const void* v_pool; int kv_dtype; int dim;
+};
+
+__global__ void __launch_bounds__(kGenWarps * 32) attn_decode_generic_kernel(GenParams gp) {
+    const AttnParams& p = gp.a;
+    const int D = gp.dim;
+    __shared__ float s_m[kGenWarps], s_l[kGenWarps];
+    __shared__ float s_o[kGenWarps][kGenMaxPerLane * 32];
+    const int b = blockIdx.x / p.hq, hq = blockIdx.x % p.hq;
+    const int h = hq / p.group, g = hq % p.group;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int live = max(0, p.live[(int64_t)b * p.meta_sb + h]);
+    const int base = p.base ? p.base[(int64_t)b * p.meta_sb + h] : 0;
+    const int32_t* bt = p.bt ? p.bt + (int64_t)b * p.bt_sb + (int64_t)h * p.bt_sh : nullptr;
+    const float ksc = p.scale * (p.k_scale ? p.k_scale[h] : 1.0f);
+    float q[kGenMaxPerLane], acc[kGenMaxPerLane];
+#pragma unroll
+    for (int e = 0; e < kGenMaxPerLane; ++e) {
+        const int d = lane + 32 * e;
+        q[e] = d < D ? load_q_elem(p, b, hq, g, d, D) : 0.0f;
+        acc[e] = 0.0f;
+    }
+    float m = -INFINITY, l = 0.0f;
+    for (int i = warp; i < live; i += kGenWarps) {
+        const int64_t row = span_row(base, bt, i);
+        if (row < 0 || row >= p.pool_rows) {
+            if (lane == 0 && p.dev_status) atomicOr(p.dev_status, FDMS_DEV_BAD_INDEX);
+            continue;
+        }
+        float dot = 0.0f;
+#pragma unroll
+        for (int e = 0; e < kGenMaxPerLane; ++e) {
+            const int d = lane + 32 * e;
+            if (d < D) dot += q[e] * load_as_float(gp.k_pool, row * D + d, gp.kv_dtype);
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+        const float s = dot * ksc;
+        const float m_new = fmaxf(m, s);
+        const float alpha = __expf(m - m_new), pr = __expf(s - m_new);
+        l = l * alpha + pr;
+        m = m_new;
+#pragma unroll
+        for (int e = 0; e < kGenMaxPerLane; ++e) {
+            const int d = lane + 32 * e;
+            if (d < D) acc[e] = acc[e] * alpha + pr * load_as_float(gp.v_pool, row * D + d, gp.kv_dtype);
+        }
+    }
+    if (lane == 0) { s_m[warp] = m; s_l[warp] = l; }
+#pragma unroll
+    for (int e = 0; e < kGenMaxPerLane; ++e) s_o[warp][lane + 32 * e] = acc[e];
+    __syncthreads();
+    const float vs = p.v_scale ? p.v_scale[h] : 1.0f;
+    for (int d = threadIdx.x; d < D; d += kGenWarps * 32) {
+        float M = -INFINITY;
+        for (int w = 0; w < kGenWarps; ++w) M = fmaxf(M, s_m[w]);
+        float a = 0.0f, L = 0.0f;
+        for (int w = 0; w < kGenWarps; ++w) {
+            const float f = (s_m[w] == -INFINITY) ? 0.0f : __expf(s_m[w] - M);
+            a += f * s_o[w][d];
+            L += f * s_l[w];
+        }
+        const float r = live > 0 ? a / L * vs : 0.0f;
+        store_from_float(p.out, (int64_t)b * p.out_sb + (int64_t)hq * p.out_sh + d, p.out_dtype, r);
+    }
+}
+
+// ------------------------------------------------------------------------------------------------
+// Host side
+// ------------------------------------------------------------------------------------------------
+struct DeviceInfo { int sms; int smem_optin; bool ok; };
+
+static DeviceInfo device_info() {
+    // One entry per device ordinal, filled on first use (the values never change).
+    static DeviceInfo cache[64];
+    static bool have[64] = {false};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return DeviceInfo{0, 0, false};
+    if (!have[dev]) {
+        DeviceInfo d{0, 0, true};
+        if (cudaDeviceGetAttribute(&d.sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) d.ok = false;
+        if (cudaDeviceGetAttribute(&d.smem_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev) != cudaSuccess) d.ok = false;
+        cache[dev] = d;
+        have[dev] = true;
+    }
+    return cache[dev];
+}
+
+static int env_int(const char* name, int dflt) {
+    const char* v = getenv(name);
+    if (!v || !*v) return dflt;
+    return atoi(v);
+}
+
+static size_t fast_smem_bytes(int D, int stages, int items) {
+    size_t s = (size_t)stages * 2 * kPage * D;          // ring
+    s += (size_t)stages * 2 * sizeof(uint64_t);         // barriers
+    s += (size_t)kConsumerWarps * kMaxGroup * (2 + D) * sizeof(float);
+    s += ((size_t)items * 2 + 1 + 2) * sizeof(int);
+    return s + 128;
+}
+
+}  // namespace fdms
+
+using namespace fdms;
+
+extern "C" int64_t fdms_attn_decode_workspace_bytes(int32_t batch, int32_t num_kv_heads, int32_t head_dim) {
+    if (batch < 0 || num_kv_heads <= 0 || head_dim <= 0) return -1;
+    const int64_t counters = (((int64_t)batch * num_kv_heads * 4 + 255) / 256) * 256;
+    const int64_t ml = (int64_t)2 * kMaxGrid * kMaxGroup * 2 * 4;
+    const int64_t po = (int64_t)2 * kMaxGrid * kMaxGroup * head_dim * 4;
+    return counters + ml + po;
+}
+
+extern "C" int32_t fdms_attn_decode(
+    const void* q, int32_t q_dtype, int64_t q_stride_b, int64_t q_stride_h,
+    const void* k_pool, const void* v_pool, int32_t kv_dtype, int64_t pool_rows,
+    const int32_t* base_offsets, const int32_t* live_counts, int64_t meta_stride_b,
+    const int32_t* block_tables, int64_t bt_stride_b, int64_t bt_stride_h,
+    const float* k_scale, const float* v_scale,
+    void* out, int32_t out_dtype, int64_t out_stride_b, int64_t out_stride_h,
+    int32_t batch, int32_t num_q_heads, int32_t num_kv_heads, int32_t head_dim, float scale,
+    const int64_t* q_rope_positions, const float* q_rope_cos_sin, int64_t cos_sin_stride,
+    void* workspace, int64_t workspace_bytes, int32_t* dev_status, void* stream) {
+    clear_error();
+    FDMS_REQUIRE(q && k_pool && v_pool && live_counts && out, FDMS_E_ARG, "fdms_attn_decode: null pointer");
+    FDMS_REQUIRE(base_offsets || block_tables, FDMS_E_ARG, "fdms_attn_decode: base_offsets or block_tables required");
+    FDMS_REQUIRE(batch >= 0 && num_q_heads > 0 && num_kv_heads > 0 && head_dim > 0, FDMS_E_ARG,
+                 "fdms_attn_decode: bad sizes");
+    FDMS_REQUIRE(num_q_heads % num_kv_heads == 0, FDMS_E_ARG, "q_heads=%d must be divisible by kv_heads=%d",
+                 num_q_heads, num_kv_heads);
+    FDMS_REQUIRE(head_dim <= 256, FDMS_E_CAPACITY, "head_dim=%d is above the kernel limit of 256", head_dim);
+    FDMS_REQUIRE(q_dtype == FDMS_F32 || q_dtype == FDMS_BF16 || q_dtype == FDMS_F16, FDMS_E_DTYPE,
+                 "fdms_attn_decode: q dtype %d not supported", q_dtype);
+    FDMS_REQUIRE(out_dtype == FDMS_F32 || out_dtype == FDMS_BF16 || out_dtype == FDMS_F16, FDMS_E_DTYPE,
+                 "fdms_attn_decode: out dtype %d not supported", out_dtype);
+    FDMS_REQUIRE(kv_dtype >= FDMS_F32 && kv_dtype <= FDMS_E4M3, FDMS_E_DTYPE,
+                 "fdms_attn_decode: pool dtype %d not supported", kv_dtype);
+    FDMS_REQUIRE((q_rope_positions == nullptr) == (q_rope_cos_sin == nullptr), FDMS_E_ARG,
+                 "inline q RoPE requires both positions and cos_sin_cache");
+    FDMS_REQUIRE(!q_rope_positions || head_dim % 2 == 0, FDMS_E_ARG, "inline q RoPE requires even head_dim, got %d", head_dim);
+    if (batch == 0) return FDMS_OK;
+    const int group = num_q_heads / num_kv_heads;
+    const int items = batch * num_kv_heads;
+
+    AttnParams p;
+    p.q = q; p.q_dtype = q_dtype; p.q_sb = q_stride_b; p.q_sh = q_stride_h;
+    p.k_pool = (const uint8_t*)k_pool; p.v_pool = (const uint8_t*)v_pool; p.pool_rows = pool_rows;
+    p.base = base_offsets; p.live = live_counts; p.meta_sb = meta_stride_b;
+    p.bt = block_tables; p.bt_sb = bt_stride_b; p.bt_sh = bt_stride_h;
+    p.k_scale = k_scale; p.v_scale = v_scale;
+    p.out = out; p.out_dtype = out_dtype; p.out_sb = out_stride_b; p.out_sh = out_stride_h;
+    p.batch = batch; p.hq = num_q_heads; p.hk = num_kv_heads; p.group = group;
+    p.scale = scale;
+    p.rope_pos = q_rope_positions; p.rope_cs = q_rope_cos_sin; p.rope_stride = cos_sin_stride;
+    p.counters = nullptr; p.part_ml = nullptr; p.part_o = nullptr;
+    p.dev_status = dev_status;
+    p.stages = 0;
+
+    const bool fast = kv_dtype == FDMS_E4M3 && (head_dim == 64 || head_dim == 128) && group <= kMaxGroup &&
+                      ((uintptr_t)k_pool % 16 == 0) && ((uintptr_t)v_pool % 16 == 0) &&
+                      env_int("FDMS_ATTN_FORCE_GENERIC", 0) == 0;
+    if (fast) {
+        const DeviceInfo di = device_info();
+        FDMS_REQUIRE(di.ok && di.sms > 0, FDMS_E_CUDA, "fdms_attn_decode: cannot query the device");
+        FDMS_REQUIRE(workspace != nullptr, FDMS_E_WORKSPACE, "fdms_attn_decode: workspace is required");
+        FDMS_REQUIRE((uintptr_t)workspace % 256 == 0, FDMS_E_WORKSPACE, "fdms_attn_decode: workspace must be 256-byte aligned");
+        const int64_t need = fdms_attn_decode_workspace_bytes(batch, num_kv_heads, head_dim);
+        FDMS_REQUIRE(workspace_bytes >= need, FDMS_E_WORKSPACE,
+                     "fdms_attn_decode: workspace of %lld bytes is smaller than the %lld required",
+                     (long long)workspace_bytes, (long long)need);
+        const int64_t counters = (((int64_t)items * 4 + 255) / 256) * 256;
+        p.counters = (int32_t*)workspace;
+        p.part_ml = (float*)((uint8_t*)workspace + counters);
+        p.part_o = p.part_ml + (size_t)2 * kMaxGrid * kMaxGroup * 2;
+
+        int ctas_per_sm = env_int("FDMS_ATTN_CTAS_PER_SM", head_dim == 64 ? 2 : 1);
+        if (ctas_per_sm < 1) ctas_per_sm = 1;
+        int stages = env_int("FDMS_ATTN_STAGES", 32);
+        if (stages < 32) stages = 32;
+        // shrink the ring until the requested residency fits
+        const size_t per_sm = (size_t)di.smem_optin;
+        while (ctas_per_sm > 1 && (fast_smem_bytes(head_dim, stages, items) + 1024) * ctas_per_sm > per_sm + 0)
+            --ctas_per_sm;
+        size_t smem = fast_smem_bytes(head_dim, stages, items);
+        FDMS_REQUIRE(smem <= (size_t)di.smem_optin, FDMS_E_CAPACITY,
+                     "fdms_attn_decode: batch*kv_heads=%d needs %zu bytes of shared memory (limit %d)", items, smem,
+                     di.smem_optin);
+        int grid = di.sms * ctas_per_sm;
+        if (grid > kMaxGrid) grid = kMaxGrid;
+        p.stages = stages;
+        cudaError_t e;
+        if (head_dim == 64) {
+            e = cudaFuncSetAttribute(attn_decode_fast_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            if (e != cudaSuccess) return fail(FDMS_E_CUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
+            attn_decode_fast_kernel<64><<<grid, kFastThreads, smem, (cudaStream_t)stream>>>(p);
+        } else {
+            e = cudaFuncSetAttribute(attn_decode_fast_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            if (e != cudaSuccess) return fail(FDMS_E_CUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
+            attn_decode_fast_kernel<128><<<grid, kFastThreads, smem, (cudaStream_t)stream>>>(p);
+        }
+        FDMS_CHECK_LAUNCH("attn_decode_fast_kernel");
+        return FDMS_OK;
+    }
+
+    GenParams gp;
+    gp.a = p; gp.k_pool = k_pool; gp.v_pool = v_pool; gp.kv_dtype = kv_dtype; gp.dim = head_dim;
+    attn_decode_generic_kernel<<<batch * num_q_heads, kGenWarps * 32, 0, (cudaStream_t)stream>>>(gp);
+    FDMS_CHECK_LAUNCH("attn_decode_generic_kernel");
+    return FDMS_OK;
+}

@@ -1,0 +1,632 @@
+"""CompactKVManager: owner of the compact FP8 KV pools and of the per-(layer, sequence, KV head)
+DMS metadata.  Public names follow the reference's `fastdms/engine/compact_kv.py`.
+
+B200-first layout (differences from the reference are storage only, results are identical):
+  * One pool allocation per manager, `[layers, capacity_tokens, head_dim]` for K and for V, made
+    up front (180 GB of HBM makes the reference's lazy 256-slot growth, and the CUDA-graph
+    re-capture it forces, unnecessary).  `compact_k_per_layer[l]` are views into it.
+  * Metadata is always layer-major on the device: `[layers, active_slots, kv_heads(, capacity)]`.
+    A sequence's state object holds views of its slot, like the reference's layer-major mode.
+  * Two span layouts: contiguous ranges handed out by a host first-fit list (the reference's
+    scheme, so base offsets and slot indices are bit-identical), or 16-row pages with block tables
+    and a per-layer free stack that lives on the GPU (`paged=True`; no host round trip at all).
+  * Expiry, decode metadata and decision recording each take ONE launch for all layers.
+"""
+from __future__ import annotations
+
+import os
+from dataclasses import dataclass
+
+import torch
+
+from fastdms_b200 import _lib
+from fastdms_b200.engine.sequence import Sequence
+
+PAGE = 16
+PACK_CHUNK = 256
+_I64_MAX = (1 << 63) - 1
+
+
+@dataclass(slots=True)
+class CompactKVMetadata:
+    base_offsets: torch.Tensor
+    live_counts: torch.Tensor
+    token_positions: torch.Tensor | None = None
+
+    @property
+    def max_live_count(self) -> int:
+        if self.live_counts.numel() == 0:
+            return 0
+        return int(self.live_counts.max().item())
+
+
+@dataclass(slots=True)
+class CompactKVSequenceState:
+    """Views of one sequence's rows in the manager's layer-major arrays (reference:
+    compact_kv.py:500-520)."""
+    seq_id: int
+    base_offsets: torch.Tensor      # [layers, kv_heads] int32, -1 = not allocated
+    range_capacity: torch.Tensor    # [layers, kv_heads] int32 reserved rows
+    live_counts: torch.Tensor       # [layers, kv_heads] int32
+    token_positions: torch.Tensor   # [layers, kv_heads, capacity] int32, -1 padded
+    evict_mask: torch.Tensor        # [layers, kv_heads, capacity] bool
+    max_capacity_per_lh: int
+    decode_headroom: int
+    active_slot: int | None = None
+    dms_initial_expiry_done: bool = False
+    last_dms_expiry_position: int = -1
+    # host mirror of the reserved ranges: (base, size) per [layer][head]; avoids device reads on free
+    host_ranges: list | None = None
+
+
+def build_emulated_dms_live_mask(*, num_layers: int, num_kv_heads: int, num_tokens: int, mode: str,
+                                 stride: int, recent_tokens: int, device) -> torch.Tensor:
+    """Synthetic retention masks used by the reference's non-DMS modes (compact_kv.py:523-551)."""
+    if mode == "all":
+        return torch.ones((num_layers, num_kv_heads, num_tokens), device=device, dtype=torch.bool)
+    if mode != "dms_stride":
+        raise ValueError(f"unknown compact KV retention mode: {mode}")
+    if stride <= 0:
+        raise ValueError(f"stride must be positive, got {stride}")
+    if recent_tokens < 0:
+        raise ValueError(f"recent_tokens must be non-negative, got {recent_tokens}")
+    pos = torch.arange(num_tokens, device=device)
+    l = torch.arange(num_layers, device=device).view(-1, 1, 1)
+    h = torch.arange(num_kv_heads, device=device).view(1, -1, 1)
+    mask = (pos.view(1, 1, -1) + l + h) % stride == 0
+    if recent_tokens:
+        mask[..., max(0, num_tokens - recent_tokens):] = True
+    if num_tokens:
+        mask[..., -1] = True
+    return mask
+
+
+def expiry_interval_from_env(default: int) -> int:
+    """FASTDMS_DMS_EXPIRY_INTERVAL: 1 = expire every step (exact), N = only when position % N == 0."""
+    raw = os.environ.get("FASTDMS_DMS_EXPIRY_INTERVAL")
+    return max(1, int(raw)) if raw not in (None, "") else max(1, int(default))
+
+
+class CompactKVManager:
+    def __init__(
+        self,
+        *,
+        num_layers: int,
+        num_kv_heads: int,
+        capacity_tokens: int,
+        max_model_len: int,
+        device: torch.device | str,
+        target_live_tokens_per_seq: int | None = None,
+        head_dim: int | None = None,
+        compact_dtype: torch.dtype | None = None,
+        per_layer_storage: bool = True,
+        layer_major_metadata: bool = True,
+        max_active_seqs: int | None = None,
+        paged: bool = False,
+        k_scale: torch.Tensor | None = None,
+        v_scale: torch.Tensor | None = None,
+        dms_expiry_interval: int = 1,
+    ):
+        if capacity_tokens <= 0:
+            raise ValueError(f"capacity_tokens must be positive, got {capacity_tokens}")
+        self.num_layers = int(num_layers)
+        self.num_kv_heads = int(num_kv_heads)
+        self.capacity_tokens = int(capacity_tokens)
+        self.max_model_len = int(max_model_len)
+        self.device = torch.device(device)
+        if self.device.type != "cuda":
+            raise RuntimeError("CompactKVManager requires a CUDA device (there is no CPU fallback)")
+        if head_dim is None or compact_dtype is None:
+            raise RuntimeError("CompactKVManager requires head_dim and compact_dtype")
+        self.head_dim = int(head_dim)
+        self.compact_dtype = compact_dtype
+        self.per_layer_storage = True
+        self.layer_major_metadata = True
+        self.max_active_seqs = int(max_active_seqs or 64)
+        self.target_live_tokens_per_seq = target_live_tokens_per_seq
+        self.paged = bool(paged)
+        self.dms_expiry_interval = int(dms_expiry_interval)
+        self.debug_checks = os.environ.get("FASTDMS_COMPACT_DEBUG_CHECKS") == "1"
+        self.admission_denied_count = 0
+        L, S, Hk, C = self.num_layers, self.max_active_seqs, self.num_kv_heads, self.max_model_len
+        dev = self.device
+        if self.paged:
+            self.capacity_tokens = ((self.capacity_tokens + PAGE - 1) // PAGE) * PAGE
+        # pools: one allocation each, [layers, rows, head_dim]
+        self.compact_k = torch.zeros((L, self.capacity_tokens, self.head_dim), device=dev, dtype=compact_dtype)
+        self.compact_v = torch.zeros_like(self.compact_k)
+        self.compact_k_per_layer = [self.compact_k[l] for l in range(L)]
+        self.compact_v_per_layer = [self.compact_v[l] for l in range(L)]
+        # layer-major metadata
+        self.layer_major_base_offsets = torch.full((L, S, Hk), -1, device=dev, dtype=torch.int32)
+        self.layer_major_range_capacity = torch.zeros((L, S, Hk), device=dev, dtype=torch.int32)
+        self.layer_major_live_counts = torch.zeros((L, S, Hk), device=dev, dtype=torch.int32)
+        self.layer_major_token_positions = torch.full((L, S, Hk, C), -1, device=dev, dtype=torch.int32)
+        self.layer_major_evict_mask = torch.zeros((L, S, Hk, C), device=dev, dtype=torch.bool)
+        self.free_active_slots: list[int] = list(range(S))
+        self.active_slot_by_seq: dict[int, int] = {}
+        self.seq_states: dict[int, CompactKVSequenceState] = {}
+        # span allocator (host) or page allocator (device)
+        self.free_ranges_per_layer: list[list[tuple[int, int]]] = [[(0, self.capacity_tokens)] for _ in range(L)]
+        self.block_tables = None
+        self.free_pages = None
+        self.free_page_counts = None
+        self.max_pages = 0
+        self.pages_per_layer = 0
+        if self.paged:
+            self.pages_per_layer = self.capacity_tokens // PAGE
+            self.max_pages = (C + PAGE - 1) // PAGE
+            self.block_tables = torch.full((L, S, Hk, self.max_pages), -1, device=dev, dtype=torch.int32)
+            # stack of free page ids; popped from the top, so page 0 is handed out first
+            ids = torch.arange(self.pages_per_layer - 1, -1, -1, device=dev, dtype=torch.int32)
+            self.free_pages = ids.unsqueeze(0).repeat(L, 1).contiguous()
+            self.free_page_counts = torch.full((L,), self.pages_per_layer, device=dev, dtype=torch.int32)
+        self.k_scale = self._check_scale(k_scale)
+        self.v_scale = self._check_scale(v_scale)
+        self._attn_modules: list = []
+        self._slot_cache: dict[tuple, torch.Tensor] = {}
+        self._decode_buffers: dict[int, tuple] = {}
+        self._stats_init = torch.tensor([0, _I64_MAX, 0, _I64_MAX, 0], device=dev, dtype=torch.int64)
+
+    # ------------------------------------------------------------------ helpers
+    def _check_scale(self, s):
+        if s is None:
+            return None
+        if tuple(s.shape) != (self.num_layers, self.num_kv_heads):
+            raise ValueError(f"expected per-(layer, kv head) scale {(self.num_layers, self.num_kv_heads)}, got {tuple(s.shape)}")
+        return s.to(device=self.device, dtype=torch.float32).contiguous()
+
+    def layer_scales(self, layer_id: int):
+        ks = None if self.k_scale is None else self.k_scale[layer_id]
+        vs = None if self.v_scale is None else self.v_scale[layer_id]
+        return ks, vs
+
+    def attach_attention_modules(self, attn_modules: list) -> None:
+        """Binds every attention module (ordered by layer) to its layer's pool views."""
+        self._attn_modules = attn_modules
+        for l, module in enumerate(attn_modules[: self.num_layers]):
+            module.compact_k_cache = self.compact_k_per_layer[l]
+            module.compact_v_cache = self.compact_v_per_layer[l]
+            module.compact_k_scale, module.compact_v_scale = self.layer_scales(l)
+
+    def _ensure_layer_storage(self, layer_id: int, min_tokens: int):
+        """Pools are allocated up front; only checks the request against the layer capacity."""
+        if min_tokens > self.capacity_tokens:
+            raise RuntimeError(
+                f"compact KV capacity exhausted in layer {layer_id}: requested {min_tokens}, capacity {self.capacity_tokens}")
+        return self.compact_k_per_layer[layer_id], self.compact_v_per_layer[layer_id]
+
+    def _slots_tensor(self, states) -> torch.Tensor:
+        key = tuple(int(s.active_slot) for s in states)
+        t = self._slot_cache.get(key)
+        if t is None:
+            if len(self._slot_cache) > 256:
+                self._slot_cache.clear()
+            t = torch.tensor(key, device=self.device, dtype=torch.int32)
+            self._slot_cache[key] = t
+        return t
+
+    def _states(self, seqs) -> list[CompactKVSequenceState]:
+        states = [self.seq_states.get(seq.seq_id) for seq in seqs]
+        if any(s is None for s in states):
+            missing = [seq.seq_id for seq, s in zip(seqs, states) if s is None]
+            raise RuntimeError(f"sequence(s) {missing} have no compact KV allocation")
+        return states
+
+    def _contiguous_active_slot_start(self, states) -> int | None:
+        if not states:
+            return None
+        slots = [s.active_slot for s in states]
+        if any(s is None for s in slots):
+            return None
+        start = int(slots[0])
+        return start if [int(s) for s in slots] == list(range(start, start + len(slots))) else None
+
+    # ------------------------------------------------------------------ span allocator (host)
+    def free_tokens_in_layer(self, layer_id: int) -> int:
+        if self.paged:
+            return int(self.free_page_counts[layer_id].item()) * PAGE
+        return sum(n for _, n in self.free_ranges_per_layer[layer_id])
+
+    @property
+    def free_tokens(self) -> int:
+        if self.paged:
+            return int(self.free_page_counts.sum().item()) * PAGE
+        return sum(self.free_tokens_in_layer(l) for l in range(self.num_layers))
+
+    def _alloc_range(self, layer_id: int, length: int) -> int:
+        """First fit over the layer's sorted free list (reference: compact_kv.py:705-718)."""
+        free = self.free_ranges_per_layer[layer_id]
+        for idx, (start, available) in enumerate(free):
+            if available < length:
+                continue
+            if available == length:
+                free.pop(idx)
+            else:
+                free[idx] = (start + length, available - length)
+            return start
+        raise RuntimeError(
+            f"compact KV capacity exhausted in layer {layer_id}: requested {length}, "
+            f"free {self.free_tokens_in_layer(layer_id)}")
+
+    def _free_range(self, layer_id: int, start: int, length: int) -> None:
+        if length <= 0:
+            return
+        free = self.free_ranges_per_layer[layer_id]
+        free.append((start, length))
+        free.sort()
+        merged: list[tuple[int, int]] = []
+        for s, n in free:
+            if merged and s <= merged[-1][0] + merged[-1][1]:
+                ps, pn = merged[-1]
+                merged[-1] = (ps, max(ps + pn, s + n) - ps)
+            else:
+                merged.append((s, n))
+        self.free_ranges_per_layer[layer_id] = merged
+
+    def _reservation_tokens(self, seq: Sequence) -> int:
+        worst = min(self.max_model_len, seq.num_prompt_tokens + seq.max_tokens)
+        if self.target_live_tokens_per_seq is not None:
+            return min(worst, max(1, int(self.target_live_tokens_per_seq)))
+        return worst
+
+    def can_allocate(self, seq: Sequence) -> bool:
+        """Conservative admission: the worst-case reservation must fit in every layer."""
+        if not self.free_active_slots and seq.seq_id not in self.seq_states:
+            return False
+        needed = self._reservation_tokens(seq) * self.num_kv_heads
+        if self.paged:
+            needed = ((self._reservation_tokens(seq) + PAGE - 1) // PAGE) * PAGE * self.num_kv_heads
+            return bool((self.free_page_counts.to(torch.int64) * PAGE >= needed).all().item())
+        return all(self.free_tokens_in_layer(l) >= needed for l in range(self.num_layers))
+
+    # ------------------------------------------------------------------ registration
+    def allocate(self, seq: Sequence) -> CompactKVSequenceState:
+        """Registers a sequence: takes an active slot and resets its metadata rows; the spans are
+        reserved later, per layer, from the observed live counts (reference: compact_kv.py:753-828)."""
+        existing = self.seq_states.get(seq.seq_id)
+        if existing is not None:
+            return existing
+        cap = self._reservation_tokens(seq)
+        if cap <= 0:
+            raise ValueError(f"invalid reservation {cap} for seq {seq.seq_id}")
+        if not self.free_active_slots:
+            raise RuntimeError(f"compact KV active-slot capacity exhausted: max_active_seqs={self.max_active_seqs}")
+        slot = self.free_active_slots.pop(0)
+        self.active_slot_by_seq[seq.seq_id] = slot
+        base = self.layer_major_base_offsets[:, slot, :]
+        rcap = self.layer_major_range_capacity[:, slot, :]
+        live = self.layer_major_live_counts[:, slot, :]
+        pos = self.layer_major_token_positions[:, slot, :, :cap]
+        ev = self.layer_major_evict_mask[:, slot, :, :cap]
+        base.fill_(-1)
+        rcap.zero_()
+        live.zero_()
+        pos.fill_(-1)
+        ev.zero_()
+        state = CompactKVSequenceState(
+            seq_id=seq.seq_id, base_offsets=base, range_capacity=rcap, live_counts=live,
+            token_positions=pos, evict_mask=ev, max_capacity_per_lh=cap,
+            decode_headroom=int(seq.max_tokens), active_slot=slot,
+            host_ranges=[[None] * self.num_kv_heads for _ in range(self.num_layers)])
+        self.seq_states[seq.seq_id] = state
+        return state
+
+    def _reserve_layer(self, state: CompactKVSequenceState, layer_id: int, live_per_head: list[int]):
+        """Host part of the per-layer reservation: first-fit ranges of min(live + headroom, C) rows
+        per head (reference: compact_kv.py:830-857).  Returns (bases, sizes)."""
+        sizes = [max(min(int(n) + int(state.decode_headroom), state.max_capacity_per_lh), 1) for n in live_per_head]
+        bases: list[int] = []
+        try:
+            for size in sizes:
+                bases.append(self._alloc_range(layer_id, size))
+        except Exception:
+            for b, sz in zip(bases, sizes):
+                self._free_range(layer_id, b, sz)
+            raise
+        for h, (b, sz) in enumerate(zip(bases, sizes)):
+            state.host_ranges[layer_id][h] = (b, sz)
+        return bases, sizes
+
+    def _allocate_layer_ranges_for_seq(self, state, layer_id: int, live_count_per_head: torch.Tensor) -> torch.Tensor:
+        bases, sizes = self._reserve_layer(state, layer_id, live_count_per_head.tolist())
+        bases_t = torch.tensor(bases, device=self.device, dtype=torch.int32)
+        state.base_offsets[layer_id].copy_(bases_t)
+        state.range_capacity[layer_id].copy_(torch.tensor(sizes, device=self.device, dtype=torch.int32))
+        return bases_t
+
+    def mark_all_heads_live(self, seq_id: int, live_count: int) -> None:
+        self.mark_live_counts(seq_id, torch.full((self.num_layers, self.num_kv_heads), live_count,
+                                                 device=self.device, dtype=torch.int32))
+
+    def mark_live_counts(self, seq_id: int, live_counts: torch.Tensor) -> None:
+        state = self.seq_states[seq_id]
+        if live_counts.shape != (self.num_layers, self.num_kv_heads):
+            raise ValueError(f"expected live_counts {(self.num_layers, self.num_kv_heads)}, got {tuple(live_counts.shape)}")
+        live_counts = live_counts.to(device=self.device, dtype=torch.int32)
+        if not self.paged and bool(torch.any(live_counts > state.range_capacity).item()):
+            raise RuntimeError(
+                f"compact KV live count {int(live_counts.max().item())} exceeds per-(layer,head) range capacity")
+        state.live_counts.copy_(live_counts)
+
+    # ------------------------------------------------------------------ prefill pack
+    def streaming_pack_layer(self, *, layer_id: int, k: torch.Tensor, v: torch.Tensor, evict_mask: torch.Tensor,
+                             cu_seqlens_q: torch.Tensor, seq_ids: list[int], window_size: int) -> None:
+        """Packs one layer's post-RoPE K / raw V of a prefill batch into compact spans
+        (reference: compact_kv.py:915-1099).  k, v [total_tokens, kv_heads, head_dim];
+        evict_mask bool [total_tokens, kv_heads]; cu_seqlens_q int32 [num_seqs + 1]."""
+        _lib.require_cuda(k, v, evict_mask)
+        states = []
+        for sid in seq_ids:
+            st = self.seq_states.get(sid)
+            if st is None:
+                raise RuntimeError(f"sequence {sid} has no compact KV allocation")
+            states.append(st)
+        n = len(states)
+        if n == 0:
+            return
+        dev = self.device
+        Hk, D = self.num_kv_heads, self.head_dim
+        if k.shape != v.shape or k.ndim != 3 or k.shape[1] != Hk or k.shape[2] != D:
+            raise ValueError(f"expected k/v as [tokens, {Hk}, {D}], got {tuple(k.shape)} / {tuple(v.shape)}")
+        if k.stride(2) != 1 or v.stride() != k.stride():
+            k, v = k.contiguous(), v.contiguous()
+        if evict_mask.dtype != torch.bool or evict_mask.shape != (k.shape[0], Hk):
+            raise ValueError(f"expected bool evict_mask {(k.shape[0], Hk)}, got {tuple(evict_mask.shape)} {evict_mask.dtype}")
+        evict_mask = evict_mask.contiguous()
+        cu = cu_seqlens_q.to(device=dev, dtype=torch.int32).contiguous()
+        cu_host = cu_seqlens_q.tolist() if not cu_seqlens_q.is_cuda else None
+        if cu_host is None:
+            cu_host = cu.tolist()                                   # one small device read per layer
+        max_len = max(cu_host[i + 1] - cu_host[i] for i in range(n))
+        max_chunks = max(1, (max_len + PACK_CHUNK - 1) // PACK_CHUNK)
+        live = torch.empty((n, Hk), device=dev, dtype=torch.int32)
+        chunk_offsets = torch.empty((n, Hk, max_chunks), device=dev, dtype=torch.int32)
+        ev_u8 = evict_mask.view(torch.uint8)
+        stream = _lib.stream_ptr(dev)
+        status = _lib.status_word(dev)
+        lib = _lib.lib()
+        slots_t = self._slots_tensor(states)
+        with torch.cuda.device(dev):
+            _lib.check(lib.fdms_pack_count(ev_u8.data_ptr(), ev_u8.stride(0), cu.data_ptr(), live.data_ptr(),
+                                           chunk_offsets.data_ptr(), max_chunks, n, Hk, int(window_size), stream))
+            capacity = self.max_model_len
+            if self.paged:
+                bt = self.block_tables[layer_id]
+                _lib.check(lib.fdms_alloc_pages(
+                    live.data_ptr(), bt.data_ptr(), bt.stride(0), bt.stride(1), self.max_pages,
+                    slots_t.data_ptr(), self.free_pages[layer_id].data_ptr(),
+                    self.free_page_counts[layer_id:].data_ptr(), n, Hk, status.data_ptr(), stream))
+                base_ptr, base_ss = None, 0
+                bt_args = (bt.data_ptr(), bt.stride(0), bt.stride(1))
+            else:
+                live_host = live.tolist()        # the host first-fit allocator needs the counts
+                all_bases, all_sizes = [], []
+                for st, row in zip(states, live_host):
+                    if max(row) > st.max_capacity_per_lh:
+                        raise RuntimeError(
+                            f"streaming pack live count {max(row)} exceeds metadata capacity "
+                            f"{st.max_capacity_per_lh} (layer {layer_id}, seq {st.seq_id})")
+                    b, s = self._reserve_layer(st, layer_id, row)
+                    all_bases.append(b)
+                    all_sizes.append(s)
+                hi = max(b + s for bs, ss in zip(all_bases, all_sizes) for b, s in zip(bs, ss))
+                self._ensure_layer_storage(layer_id, hi)
+                both = torch.tensor([all_bases, all_sizes], dtype=torch.int32).to(dev, non_blocking=True)
+                idx = slots_t.long()
+                self.layer_major_base_offsets[layer_id].index_copy_(0, idx, both[0])
+                self.layer_major_range_capacity[layer_id].index_copy_(0, idx, both[1])
+                base_l = self.layer_major_base_offsets[layer_id]
+                base_ptr, base_ss = base_l.data_ptr(), base_l.stride(0)
+                bt_args = (None, 0, 0)
+            pos = self.layer_major_token_positions[layer_id]
+            evm = self.layer_major_evict_mask[layer_id].view(torch.uint8)
+            lc = self.layer_major_live_counts[layer_id]
+            ks, vs = self.layer_scales(layer_id)
+            ck, cv = self.compact_k_per_layer[layer_id], self.compact_v_per_layer[layer_id]
+            _lib.check(lib.fdms_pack_scatter(
+                k.data_ptr(), v.data_ptr(), _lib.dtype_code(k.dtype), k.stride(0), k.stride(1),
+                ev_u8.data_ptr(), ev_u8.stride(0), cu.data_ptr(),
+                chunk_offsets.data_ptr(), max_chunks, live.data_ptr(),
+                ck.data_ptr(), cv.data_ptr(), _lib.dtype_code(ck.dtype), ck.shape[0],
+                base_ptr, base_ss, *bt_args,
+                slots_t.data_ptr(),
+                pos.data_ptr(), pos.stride(0), pos.stride(1),
+                evm.data_ptr(), evm.stride(0), evm.stride(1),
+                lc.data_ptr(), lc.stride(0), capacity,
+                _lib.ptr(ks), _lib.ptr(vs),
+                n, Hk, D, int(window_size), status.data_ptr(), stream))
+
+    # ------------------------------------------------------------------ expiry
+    def apply_dms_evictions(self, seqs: list[Sequence], current_positions: list[int], *, window_size: int,
+                            compact_k=None, compact_v=None, sync_stats: bool = True,
+                            expiry_interval: int | None = None, incremental: bool = False) -> dict:
+        """Drops evict-marked tokens that left the window and compacts every span in place, all
+        layers in one launch (reference: compact_kv.py:1174-1361).  `expiry_interval` > 1 skips
+        the launch unless some position is a multiple of it (the reference's windowed cadence,
+        :1214-1235); the default comes from the constructor / FASTDMS_DMS_EXPIRY_INTERVAL."""
+        if len(seqs) != len(current_positions):
+            raise ValueError("seq/current_positions length mismatch")
+        zero_stats = {"evicted_tokens": 0, "live_tokens_before_min": 0, "live_tokens_before_max": 0,
+                      "live_tokens_after_min": 0, "live_tokens_after_max": 0}
+        if not seqs:
+            return zero_stats
+        states = self._states(seqs)
+        interval = expiry_interval if expiry_interval is not None else expiry_interval_from_env(self.dms_expiry_interval)
+        sequential = all(st.dms_initial_expiry_done and int(p) == st.last_dms_expiry_position + 1
+                         for st, p in zip(states, current_positions))
+        for st, p in zip(states, current_positions):
+            st.last_dms_expiry_position = int(p)
+        if interval > 1 and sequential and not any(int(p) % interval == 0 for p in current_positions):
+            if not sync_stats:
+                return zero_stats
+            lc = self.layer_major_live_counts[:, self._slots_tensor(states).long(), :].to(torch.int64)
+            lo, hi = int(lc.min().item()), int(lc.max().item())
+            return {"evicted_tokens": 0, "live_tokens_before_min": lo, "live_tokens_before_max": hi,
+                    "live_tokens_after_min": lo, "live_tokens_after_max": hi}
+        dev = self.device
+        cur = torch.tensor([int(p) for p in current_positions], dtype=torch.int64).to(dev, non_blocking=True)
+        slots_t = self._slots_tensor(states)
+        stats = self._stats_init.clone()
+        pos, ev = self.layer_major_token_positions, self.layer_major_evict_mask.view(torch.uint8)
+        lc, base = self.layer_major_live_counts, self.layer_major_base_offsets
+        row_bytes = self.head_dim * self.compact_k.element_size()
+        if self.paged:
+            bt = self.block_tables
+            bt_args = (bt.data_ptr(), bt.stride(0), bt.stride(1), bt.stride(2),
+                       self.free_pages.data_ptr(), self.free_page_counts.data_ptr(), self.pages_per_layer)
+            base_ptr = None
+        else:
+            bt_args = (None, 0, 0, 0, None, None, 0)
+            base_ptr = base.data_ptr()
+        with torch.cuda.device(dev):
+            rc = _lib.lib().fdms_expire_compact(
+                pos.data_ptr(), pos.stride(0), pos.stride(1), pos.stride(2),
+                ev.data_ptr(), ev.stride(0), ev.stride(1), ev.stride(2),
+                lc.data_ptr(), base_ptr, lc.stride(0), lc.stride(1),
+                self.compact_k.data_ptr(), self.compact_v.data_ptr(),
+                self.compact_k.stride(0) * self.compact_k.element_size(), row_bytes, self.capacity_tokens,
+                *bt_args,
+                slots_t.data_ptr(), cur.data_ptr(),
+                self.num_layers, len(states), self.num_kv_heads, self.max_model_len,
+                int(window_size), 1 if incremental else 0, stats.data_ptr(),
+                _lib.status_word(dev).data_ptr(), _lib.stream_ptr(dev))
+        _lib.check(rc)
+        for st in states:
+            st.dms_initial_expiry_done = True
+        keys = ("evicted_tokens", "live_tokens_before_min", "live_tokens_before_max",
+                "live_tokens_after_min", "live_tokens_after_max")
+        if sync_stats:
+            return dict(zip(keys, stats.tolist()))
+        return {k: stats[i] for i, k in enumerate(keys)}
+
+    # ------------------------------------------------------------------ decode metadata
+    def prepare_decode_metadata(self, seqs: list[Sequence]):
+        """slot = row of logical index `live` of every (layer, seq, head); live += 1 in place, so
+        the forward sees the count that includes the token being appended.  Returns
+        (base_offsets, live_counts, slot_mapping, max_capacity), each [layers, batch, kv_heads]
+        int32 (reference: compact_kv.py:1727-1770).  No host synchronisation."""
+        states = self._states(seqs)
+        B = len(states)
+        dev = self.device
+        L, Hk = self.num_layers, self.num_kv_heads
+        bufs = self._decode_buffers.get(B)
+        if bufs is None:
+            bufs = tuple(torch.empty((L, B, Hk), device=dev, dtype=torch.int32) for _ in range(3)) + (
+                torch.empty((L, B * Hk + 1), device=dev, dtype=torch.int32),)
+            self._decode_buffers[B] = bufs
+        base_out, live_out, slot_out, cu_out = bufs
+        slots_t = self._slots_tensor(states)
+        lc, base = self.layer_major_live_counts, self.layer_major_base_offsets
+        if self.paged:
+            bt = self.block_tables
+            bt_args = (bt.data_ptr(), bt.stride(0), bt.stride(1), bt.stride(2), self.max_pages,
+                       self.free_pages.data_ptr(), self.free_page_counts.data_ptr(), self.pages_per_layer)
+            base_ptr = None
+        else:
+            bt_args = (None, 0, 0, 0, 0, None, None, 0)
+            base_ptr = base.data_ptr()
+        with torch.cuda.device(dev):
+            rc = _lib.lib().fdms_build_decode_metadata(
+                lc.data_ptr(), base_ptr, lc.stride(0), lc.stride(1), *bt_args,
+                slots_t.data_ptr(), base_out.data_ptr(), live_out.data_ptr(), slot_out.data_ptr(), cu_out.data_ptr(),
+                L, B, Hk, _lib.status_word(dev).data_ptr(), _lib.stream_ptr(dev))
+        _lib.check(rc)
+        self.last_cu_live = cu_out
+        return base_out, live_out, slot_out, max(st.max_capacity_per_lh for st in states)
+
+    def decode_block_tables(self, seqs: list[Sequence]) -> torch.Tensor | None:
+        """[layers, batch, kv_heads, max_pages] block tables of the batch (paged layout only)."""
+        if not self.paged:
+            return None
+        states = self._states(seqs)
+        start = self._contiguous_active_slot_start(states)
+        if start is not None:
+            return self.block_tables[:, start:start + len(states)]
+        return self.block_tables.index_select(1, self._slots_tensor(states).long())
+
+    def record_appended_dms_decisions(self, seqs: list[Sequence], current_positions, layer_evictions,
+                                      *, sync_stats: bool = True) -> dict:
+        """After the forward: token_positions[l, seq, h, live-1] = position, evict_mask[...] = the
+        decision the layer made for the appended token (reference: compact_kv.py:1562-1725)."""
+        if len(seqs) != len(current_positions):
+            raise ValueError("seq/current_positions length mismatch")
+        B = len(seqs)
+        if B == 0:
+            return {"eviction_decisions_true": 0, "eviction_decisions_total": 0}
+        dev = self.device
+        L, Hk = self.num_layers, self.num_kv_heads
+        if isinstance(layer_evictions, torch.Tensor):
+            if tuple(layer_evictions.shape) != (L, B, Hk):
+                raise RuntimeError(f"expected DMS decode decisions {(L, B, Hk)}, got {tuple(layer_evictions.shape)}")
+            evict_all = layer_evictions
+        else:
+            rows = []
+            for l in range(L):
+                e = layer_evictions.get(l)
+                if e is None:
+                    raise RuntimeError(f"missing DMS decode eviction decisions for layer {l}")
+                if tuple(e.shape) != (B, Hk):
+                    raise RuntimeError(f"expected DMS decode decisions {(B, Hk)}, got {tuple(e.shape)}")
+                rows.append(e)
+            evict_all = torch.stack(rows, dim=0)
+        evict_all = evict_all.to(device=dev, dtype=torch.bool)
+        if evict_all.stride(2) != 1:
+            evict_all = evict_all.contiguous()
+        if isinstance(current_positions, torch.Tensor):
+            if current_positions.numel() != B:
+                raise ValueError("current_positions tensor length mismatch")
+            pos_t = current_positions.to(device=dev, dtype=torch.int64).contiguous()
+        else:
+            pos_t = torch.tensor([int(p) for p in current_positions], dtype=torch.int64).to(dev, non_blocking=True)
+        states = self._states(seqs)
+        slots_t = self._slots_tensor(states)
+        pos, ev = self.layer_major_token_positions, self.layer_major_evict_mask.view(torch.uint8)
+        lc = self.layer_major_live_counts
+        ea = evict_all.view(torch.uint8)
+        true_count = torch.zeros(1, device=dev, dtype=torch.int64)
+        with torch.cuda.device(dev):
+            rc = _lib.lib().fdms_record_decisions(
+                pos.data_ptr(), pos.stride(0), pos.stride(1), pos.stride(2),
+                ev.data_ptr(), ev.stride(0), ev.stride(1), ev.stride(2),
+                lc.data_ptr(), lc.stride(0), lc.stride(1),
+                ea.data_ptr(), ea.stride(0), ea.stride(1),
+                pos_t.data_ptr(), slots_t.data_ptr(), L, B, Hk, self.max_model_len,
+                true_count.data_ptr(), _lib.stream_ptr(dev))
+        _lib.check(rc)
+        total_true = true_count[0]
+        return {"eviction_decisions_true": int(total_true.item()) if sync_stats else total_true,
+                "eviction_decisions_total": L * B * Hk}
+
+    # ------------------------------------------------------------------ release
+    def free(self, seq_id: int) -> None:
+        """Returns a sequence's spans / pages and its active slot (reference: compact_kv.py:1772-1795)."""
+        state = self.seq_states.pop(seq_id, None)
+        if state is None:
+            return
+        slot = int(state.active_slot)
+        if self.paged:
+            slot_t = torch.tensor([slot], device=self.device, dtype=torch.int32)
+            status = _lib.status_word(self.device)
+            with torch.cuda.device(self.device):
+                for l in range(self.num_layers):
+                    bt = self.block_tables[l]
+                    lc = self.layer_major_live_counts[l]
+                    _lib.check(_lib.lib().fdms_free_pages(
+                        lc.data_ptr(), lc.stride(0), bt.data_ptr(), bt.stride(0), bt.stride(1), self.max_pages,
+                        slot_t.data_ptr(), self.free_pages[l].data_ptr(), self.free_page_counts[l:].data_ptr(),
+                        self.pages_per_layer, 1, self.num_kv_heads, status.data_ptr(), _lib.stream_ptr(self.device)))
+        else:
+            for l in range(self.num_layers):
+                for h in range(self.num_kv_heads):
+                    r = state.host_ranges[l][h]
+                    if r is not None and r[0] >= 0 and r[1] > 0:
+                        self._free_range(l, r[0], r[1])
+        self.active_slot_by_seq.pop(seq_id, None)
+        self.layer_major_base_offsets[:, slot, :].fill_(-1)
+        self.layer_major_range_capacity[:, slot, :].zero_()
+        self.layer_major_live_counts[:, slot, :].zero_()
+        self.layer_major_token_positions[:, slot, :, :state.max_capacity_per_lh].fill_(-1)
+        self.layer_major_evict_mask[:, slot, :, :state.max_capacity_per_lh].zero_()
+        self.free_active_slots.append(slot)
+        self.free_active_slots.sort()

@@ -1,0 +1,239 @@
+/*
+ * fastdms_b200 -- C ABI of the B200-native compact-DMS decode path.
+ *
+ * One shared library (libfastdms_b200.so) exports every entry point below.  All functions are
+ * `extern "C"`, take raw device pointers plus explicit sizes/strides, return an int32 status
+ * (0 = ok, < 0 = FDMS_E_*), never throw, never exit and never trap on the device.  The library
+ * owns no memory: every buffer (pools, metadata, outputs, workspaces) belongs to the caller.
+ * Kernels are enqueued on the CUDA stream passed as `stream` (a cudaStream_t; NULL = default
+ * stream) and do not synchronise, allocate or copy to the host, so a sequence of calls can be
+ * captured into a CUDA graph as long as the pointers stay stable.
+ *
+ * The reference project (shisa-ai/FastDMS) has no FFI; the interface each entry point replaces is
+ * the Python function / Triton kernel named in its comment (paths inside the reference project).
+ *
+ * Layouts
+ *   pools        K and V pools are row arrays [slots, head_dim] with contiguous rows.  A span of a
+ *                (sequence, KV head) is either `live` consecutive rows starting at `base`
+ *                (block_tables == NULL, the reference layout) or 16-row pages listed in a block
+ *                table: logical row i lives at block_table[i / 16] * 16 + i % 16.
+ *   metadata     int32 [batch, kv_heads] (one layer) or [layers, batch, kv_heads]; strides are in
+ *                elements.
+ *   FP8          e4m3 ("fn": no infinities, max 448) with an optional per-KV-head float scale:
+ *                stored = value / scale, value = stored * scale.  scale == NULL means 1.0, which
+ *                is the reference's bare cast.
+ */
+#ifndef FASTDMS_B200_H
+#define FASTDMS_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define FDMS_ABI_VERSION 1
+
+/* status codes */
+#define FDMS_OK 0
+#define FDMS_E_ARG (-1)         /* bad shape / stride / null pointer: the reference raises ValueError */
+#define FDMS_E_DTYPE (-2)       /* unsupported dtype combination: ValueError */
+#define FDMS_E_WORKSPACE (-3)   /* workspace missing or too small: ValueError */
+#define FDMS_E_CUDA (-4)        /* a CUDA runtime call failed: RuntimeError */
+#define FDMS_E_CAPACITY (-5)    /* a size exceeds a documented limit: RuntimeError */
+
+/* dtype codes */
+#define FDMS_F32 0
+#define FDMS_BF16 1
+#define FDMS_F16 2
+#define FDMS_E4M3 3
+
+/* bits of the optional device status word (int32, OR-ed by kernels, never cleared by them) */
+#define FDMS_DEV_WAIT_TIMEOUT 1   /* a bounded wait on an async copy ran out; results are invalid */
+#define FDMS_DEV_BAD_INDEX 2      /* a slot / page index was out of range and the access was skipped */
+
+int32_t fdms_abi_version(void);
+/* Message of the last failing call on this host thread (empty string if none). */
+const char* fdms_last_error(void);
+
+/* ---------------------------------------------------------------------------------------------
+ * (a) compact decode attention.
+ * Replaces fastdms/layers/compact_attention.py:1116-1336 compact_decode_attention (split-K partial
+ * + reduce kernels :334-603, inline-RoPE variant :418-534).
+ *   out[b, hq, :] = softmax(scale * K_span q[b, hq]) V_span   over the span of KV head hq / group.
+ * q/out [batch, q_heads, head_dim] with the given element strides (inner stride 1).
+ * Optional inline neox RoPE of q at q_rope_positions[b] (int64) with the decision lane
+ * (first head of each group, channel head_dim-1) zeroed first; cos_sin rows are
+ * [cos(head_dim/2) | sin(head_dim/2)] float32 with row stride cos_sin_stride.
+ * workspace: fdms_attn_decode_workspace_bytes(...) bytes, 256-byte aligned.  Its first
+ * `batch*kv_heads` int32 must be zero before the FIRST call; every call leaves them zero again.
+ * Calls that share a workspace must not overlap on the GPU.
+ * --------------------------------------------------------------------------------------------- */
+int64_t fdms_attn_decode_workspace_bytes(int32_t batch, int32_t num_kv_heads, int32_t head_dim);
+
+int32_t fdms_attn_decode(
+    const void* q, int32_t q_dtype, int64_t q_stride_b, int64_t q_stride_h,
+    const void* k_pool, const void* v_pool, int32_t kv_dtype, int64_t pool_rows,
+    const int32_t* base_offsets, const int32_t* live_counts, int64_t meta_stride_b,
+    const int32_t* block_tables, int64_t bt_stride_b, int64_t bt_stride_h,
+    const float* k_scale, const float* v_scale,
+    void* out, int32_t out_dtype, int64_t out_stride_b, int64_t out_stride_h,
+    int32_t batch, int32_t num_q_heads, int32_t num_kv_heads, int32_t head_dim, float scale,
+    const int64_t* q_rope_positions, const float* q_rope_cos_sin, int64_t cos_sin_stride,
+    void* workspace, int64_t workspace_bytes, int32_t* dev_status, void* stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * (b)+(d) fused decode preprocess: DMS decision + RoPE + FP8 quantise + append store.
+ * Replaces fastdms/layers/compact_attention.py:1010-1113 fused_dms_rope_store_compact_decode
+ * (kernel :67-209); with rope == 0 and evict_out == NULL it is store_compact_kvcache (:968-1007).
+ * Per (b, kv head h): v = q[b, h*group, D-1]; evict_out[b,h] = v > offset/scale (scale > 0) else
+ * (v*scale - offset) > 0; that lane is zeroed; neox RoPE (float32, no fused multiply-add, result
+ * rounded to the activation dtype) of the group's q heads (store_q) and of k (written back when
+ * store_k); k (post-RoPE) and v are divided by the head's scale, cast to the pool dtype and
+ * written to row slot_mapping[b,h] (negative = skip).  positions: int64 [batch].
+ * --------------------------------------------------------------------------------------------- */
+int32_t fdms_store_decode(
+    void* q, int64_t q_stride_b, int64_t q_stride_h,
+    void* k, int64_t k_stride_b, int64_t k_stride_h,
+    const void* v, int64_t v_stride_b, int64_t v_stride_h, int32_t act_dtype,
+    const float* cos_sin, int64_t cos_sin_stride, const int64_t* positions,
+    void* k_pool, void* v_pool, int32_t kv_dtype, int64_t pool_rows,
+    const int32_t* slot_mapping, int64_t slot_stride_b,
+    uint8_t* evict_out, int64_t evict_stride_b,
+    const float* k_scale, const float* v_scale,
+    int32_t batch, int32_t num_q_heads, int32_t num_kv_heads, int32_t head_dim,
+    double alpha_scale, double alpha_offset,
+    int32_t do_decision, int32_t do_rope, int32_t store_q, int32_t store_k,
+    int32_t* dev_status, void* stream);
+
+/* Prefill-side decision extraction.  Replaces fastdms/engine/dms.py:152-232
+ * extract_dms_eviction_decisions (kernel :12-42): evict[t,h] from q[t, h*group, D-1], lane zeroed. */
+int32_t fdms_extract_decisions(
+    void* q, int32_t q_dtype, int64_t q_stride_t, int64_t q_stride_h,
+    uint8_t* evict_out, int64_t evict_stride_t,
+    int64_t tokens, int32_t num_q_heads, int32_t num_kv_heads, int32_t head_dim,
+    double alpha_scale, double alpha_offset, void* stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * (b) expiry: DMS eviction + in-place stable compaction of every (layer, seq, head) span.
+ * Replaces fastdms/engine/compact_kv.py:1174-1361 apply_dms_evictions (python path) and
+ * fastdms/layers/compact_attention.py:861-965 dms_expiry_one_layer / _incremental_one_layer
+ * (kernels :690-858), for all layers in one launch and without the 32768-slot span limit.
+ * A slot i < live is kept iff !evict[i] || cur - pos[i] <= window; kept K/V rows, positions and
+ * evict bits move to the front in order; [new_live, old_live) of the metadata rows becomes -1 / 0;
+ * live_counts is updated.  mode 1 (incremental): only the first slot with evict && pos < cur-window
+ * is dropped.  Layer l uses pools k_pool + l*pool_layer_stride_bytes (rows of row_bytes bytes, a
+ * multiple of 4) and metadata [layers, seqs, kv_heads(, capacity)] arrays with the given element
+ * strides.  With block tables, pages that end up beyond the live prefix are pushed onto the
+ * layer's free stack (free_pages int32 [layers, pages_per_layer], free_counts int32 [layers]).
+ * seq_slots: optional int32 [num_seqs] rows of the metadata arrays to process (NULL = 0..num_seqs-1);
+ * current_positions: int64 [num_seqs].  stats: optional int64[5] {evicted, live_before_min,
+ * live_before_max, live_after_min, live_after_max}; the caller initialises it to
+ * {0, INT64_MAX, 0, INT64_MAX, 0}.
+ * --------------------------------------------------------------------------------------------- */
+int32_t fdms_expire_compact(
+    int32_t* token_positions, int64_t pos_stride_l, int64_t pos_stride_s, int64_t pos_stride_h,
+    uint8_t* evict_mask, int64_t ev_stride_l, int64_t ev_stride_s, int64_t ev_stride_h,
+    int32_t* live_counts, const int32_t* base_offsets,
+    int64_t meta_stride_l, int64_t meta_stride_s,
+    void* k_pool, void* v_pool, int64_t pool_layer_stride_bytes, int32_t row_bytes, int64_t pool_rows,
+    int32_t* block_tables, int64_t bt_stride_l, int64_t bt_stride_s, int64_t bt_stride_h,
+    int32_t* free_pages, int32_t* free_counts, int64_t pages_per_layer,
+    const int32_t* seq_slots, const int64_t* current_positions,
+    int32_t num_layers, int32_t num_seqs, int32_t num_kv_heads, int32_t capacity,
+    int32_t window, int32_t mode, int64_t* stats, int32_t* dev_status, void* stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * (b) prefill pack of one layer, two launches around the span / page allocation.
+ * Replaces fastdms/engine/compact_kv.py:915-1099 streaming_pack_layer (kernels :140-262).
+ * keep[t,h] = !evict[t,h] || t_in_seq >= max(0, T-1-window).
+ * fdms_pack_count : live_out[s,h] = number of kept tokens; chunk_offsets[s,h,c] = exclusive prefix
+ *                   of kept tokens before 256-token chunk c (int32 [num_seqs, kv_heads, max_chunks],
+ *                   max_chunks >= ceil(longest prompt / 256)).
+ * fdms_pack_scatter: kept tokens go to logical row `rank` of their span (row base[s,h]+rank or the
+ *                   paged address), divided by the head's scale and cast to the pool dtype;
+ *                   positions (index within the prompt) and evict bits are written at [s,h,rank];
+ *                   the metadata rows are reset to -1 / 0 beyond live; live_counts[s,h] = live_in.
+ * cu_seqlens int32 [num_seqs+1]; k/v [total_tokens, kv_heads, head_dim] activation dtype; metadata
+ * arrays are the layer's [seqs, kv_heads(, capacity)] slices; seq_slots maps batch rows to them.
+ * --------------------------------------------------------------------------------------------- */
+int32_t fdms_pack_count(
+    const uint8_t* evict, int64_t evict_stride_t, const int32_t* cu_seqlens,
+    int32_t* live_out, int32_t* chunk_offsets, int32_t max_chunks,
+    int32_t num_seqs, int32_t num_kv_heads, int32_t window, void* stream);
+
+int32_t fdms_pack_scatter(
+    const void* k, const void* v, int32_t act_dtype, int64_t kv_stride_t, int64_t kv_stride_h,
+    const uint8_t* evict, int64_t evict_stride_t, const int32_t* cu_seqlens,
+    const int32_t* chunk_offsets, int32_t max_chunks, const int32_t* live_in,
+    void* k_pool, void* v_pool, int32_t kv_dtype, int64_t pool_rows,
+    const int32_t* base_offsets, int64_t base_stride_s,
+    const int32_t* block_tables, int64_t bt_stride_s, int64_t bt_stride_h,
+    const int32_t* seq_slots,
+    int32_t* token_positions, int64_t pos_stride_s, int64_t pos_stride_h,
+    uint8_t* evict_mask, int64_t ev_stride_s, int64_t ev_stride_h,
+    int32_t* live_counts, int64_t meta_stride_s, int32_t capacity,
+    const float* k_scale, const float* v_scale,
+    int32_t num_seqs, int32_t num_kv_heads, int32_t head_dim, int32_t window,
+    int32_t* dev_status, void* stream);
+
+/* Page allocator of the paged layout (no counterpart in the reference, whose spans are contiguous
+ * ranges handed out by a host first-fit list, fastdms/engine/compact_kv.py:705-737).
+ * fdms_alloc_pages pops ceil(rows_needed[s,h] / 16) pages per span from one layer's free stack into
+ * its block-table row; fdms_free_pages pushes every page of the listed spans back and clears the
+ * rows.  block_tables is the layer's [seqs, kv_heads, max_pages] slice. */
+int32_t fdms_alloc_pages(
+    const int32_t* rows_needed, int32_t* block_tables, int64_t bt_stride_s, int64_t bt_stride_h,
+    int32_t max_pages, const int32_t* seq_slots, int32_t* free_pages, int32_t* free_count,
+    int32_t num_seqs, int32_t num_kv_heads, int32_t* dev_status, void* stream);
+int32_t fdms_free_pages(
+    const int32_t* live_counts, int64_t meta_stride_s, int32_t* block_tables, int64_t bt_stride_s,
+    int64_t bt_stride_h, int32_t max_pages, const int32_t* seq_slots, int32_t* free_pages,
+    int32_t* free_count, int64_t pages_per_layer, int32_t num_seqs, int32_t num_kv_heads,
+    int32_t* dev_status, void* stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * (c) ragged-batch decode metadata for all layers in one launch.
+ * Replaces fastdms/engine/compact_kv.py:1727-1770 prepare_decode_metadata.  For every
+ * (layer, batch row b -> metadata row seq_slots[b], head): base_out = base; slot_out = physical
+ * row of logical index `live` (base+live, or through the block table; when live is a multiple of
+ * 16 and block tables are used a page is popped from the layer's free stack first);
+ * live += 1 in the manager's array and live_out = the incremented value.  cu_live_out (optional,
+ * int32 [layers, batch*kv_heads + 1]) receives the exclusive prefix sum of live_out per layer.
+ * free_pages int32 [layers, pages_per_layer], free_counts int32 [layers]: per-layer stacks of
+ * free page ids (only with block tables).
+ * --------------------------------------------------------------------------------------------- */
+int32_t fdms_build_decode_metadata(
+    int32_t* live_counts, const int32_t* base_offsets, int64_t meta_stride_l, int64_t meta_stride_s,
+    int32_t* block_tables, int64_t bt_stride_l, int64_t bt_stride_s, int64_t bt_stride_h, int32_t max_pages,
+    int32_t* free_pages, int32_t* free_counts, int64_t pages_per_layer,
+    const int32_t* seq_slots,
+    int32_t* base_out, int32_t* live_out, int32_t* slot_out, int32_t* cu_live_out,
+    int32_t num_layers, int32_t batch, int32_t num_kv_heads, int32_t* dev_status, void* stream);
+
+/* Replaces fastdms/engine/compact_kv.py:1562-1725 record_appended_dms_decisions (kernel :426-484):
+ * token_positions[l, slot, h, live-1] = positions[b]; evict_mask[...] = evict_all[l,b,h];
+ * true_count (optional int64, caller-zeroed) accumulates the number of true decisions. */
+int32_t fdms_record_decisions(
+    int32_t* token_positions, int64_t pos_stride_l, int64_t pos_stride_s, int64_t pos_stride_h,
+    uint8_t* evict_mask, int64_t ev_stride_l, int64_t ev_stride_s, int64_t ev_stride_h,
+    const int32_t* live_counts, int64_t meta_stride_l, int64_t meta_stride_s,
+    const uint8_t* evict_all, int64_t ea_stride_l, int64_t ea_stride_b,
+    const int64_t* positions, const int32_t* seq_slots,
+    int32_t num_layers, int32_t batch, int32_t num_kv_heads, int32_t capacity,
+    int64_t* true_count, void* stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * (d) FP8 e4m3 KV quantise / dequantise with a per-KV-head scale, x [n, kv_heads, head_dim].
+ * The reference's equivalent is the bare cast `.to(float8_e4m3fn)` (fastdms/engine/compact_kv.py:
+ * 1085-1087), i.e. scale == NULL.  Round to nearest even, saturating at +-448.
+ * --------------------------------------------------------------------------------------------- */
+int32_t fdms_kv_quant(const void* x, int32_t x_dtype, uint8_t* out, const float* scale,
+                      int64_t n, int32_t num_kv_heads, int32_t head_dim, void* stream);
+int32_t fdms_kv_dequant(const uint8_t* x, void* out, int32_t out_dtype, const float* scale,
+                        int64_t n, int32_t num_kv_heads, int32_t head_dim, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FASTDMS_B200_H */

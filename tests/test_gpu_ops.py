@@ -1,0 +1,342 @@
+"""GPU parity tests: every CUDA entry point (called through the C ABI) against the numpy oracle and
+the vectors produced by the reference's CPU code.  Integer / byte results must be bit-exact;
+attention outputs must be within 2e-2 max-abs of the float32 oracle (FP8 K/V, bf16 q)."""
+from __future__ import annotations
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import compact_dms as O
+from oracle.dtypes import bf16_bits_to_f32, decode_e4m3, encode_e4m3
+
+pytestmark = pytest.mark.gpu
+
+ATTN_TOL = 2e-2      # max-abs, FP8 pools / bf16 activations vs float32 oracle
+F32_TOL = 1e-4       # the reference's own tolerance for its float32 fixtures
+
+
+@pytest.fixture(scope="module")
+def dev():
+    assert torch.cuda.is_available(), "GPU tests need a CUDA device"
+    from fastdms_b200 import _lib
+    _lib.lib()
+    return torch.device("cuda:0")
+
+
+@pytest.fixture(autouse=True)
+def _status_clean(dev):
+    from fastdms_b200 import _lib
+    _lib.read_device_status(dev)
+    yield
+    assert _lib.read_device_status(dev) == 0, "a kernel raised a device status bit"
+
+
+def t_bf16(a, dev):
+    return torch.from_numpy(a.view(np.int16).copy()).view(torch.bfloat16).to(dev)
+
+
+def t_fp8(a, dev):
+    return torch.from_numpy(a.copy()).view(torch.float8_e4m3fn).to(dev)
+
+
+def n_bf16(t):
+    return bf16_bits_to_f32(t.detach().cpu().contiguous().view(torch.int16).numpy().view(np.uint16))
+
+
+def n_u8(t):
+    return t.detach().cpu().contiguous().view(torch.uint8).numpy()
+
+
+# ------------------------------------------------------------------------------------------------
+def test_extract_decisions(ops_golden, dev):
+    from fastdms_b200.engine.dms import extract_dms_eviction_decisions
+    z = ops_golden
+    q = torch.from_numpy(z["extract_f32_q"]).to(dev)
+    qc, ev = extract_dms_eviction_decisions(q, num_kv_heads=8, num_qo_heads=32, head_dim=64,
+                                            alpha_scale=100.0, alpha_offset=5.0)
+    assert torch.equal(q.cpu(), torch.from_numpy(z["extract_f32_q"]))          # not in place
+    assert np.array_equal(ev.cpu().numpy(), z["extract_f32_evict"])
+    assert np.array_equal(qc.cpu().numpy(), z["extract_f32_q_out"])
+    out = torch.empty((11, 8), dtype=torch.bool, device=dev)
+    q2, ev2 = extract_dms_eviction_decisions(q.clone(), num_kv_heads=8, num_qo_heads=32, head_dim=64,
+                                             alpha_scale=100.0, alpha_offset=5.0, inplace=True, out=out)
+    assert ev2.data_ptr() == out.data_ptr() and np.array_equal(out.cpu().numpy(), z["extract_f32_evict"])
+    qb = t_bf16(z["extract_bf16_q"], dev)
+    qc, ev = extract_dms_eviction_decisions(qb, num_kv_heads=2, num_qo_heads=4, head_dim=64,
+                                            alpha_scale=100.0, alpha_offset=5.0)
+    assert np.array_equal(ev.cpu().numpy(), z["extract_bf16_evict"])
+    assert np.array_equal(n_u8(qc), z["extract_bf16_q_out"].view(np.uint8))
+    qn = torch.from_numpy(z["extract_neg_q"]).to(dev).view(9, 8 * 32)          # flat [T, H*D] form
+    qc, ev = extract_dms_eviction_decisions(qn, num_kv_heads=4, num_qo_heads=8, head_dim=32,
+                                            alpha_scale=-50.0, alpha_offset=1.0)
+    assert np.array_equal(ev.cpu().numpy(), z["extract_neg_evict"])
+    assert np.array_equal(qc.view(9, 8, 32).cpu().numpy(), z["extract_neg_q_out"])
+    with pytest.raises(ValueError):
+        extract_dms_eviction_decisions(q, num_kv_heads=5, num_qo_heads=32, head_dim=64, alpha_scale=100.0, alpha_offset=5.0)
+
+
+@pytest.mark.parametrize("tag,act,pool", [("f32d32", "f32", "f32"), ("bf16d64", "bf16", "e4m3"), ("bf16d128", "bf16", "e4m3")])
+def test_fused_rope_store_decode(ops_golden, dev, tag, act, pool):
+    from fastdms_b200.layers.compact_attention import fused_dms_rope_store_compact_decode, store_compact_kvcache
+    z = ops_golden
+    g = lambda n: z[f"ropestore_{tag}_{n}"]
+    up = (lambda a: torch.from_numpy(a.copy()).to(dev)) if act == "f32" else (lambda a: t_bf16(a, dev))
+    raw = lambda t: n_u8(t)
+    q, k, v = up(g("q")), up(g("k")), up(g("v"))
+    B, Hk, D = k.shape
+    positions = torch.from_numpy(g("positions")).to(dev)
+    cache = torch.zeros((int(positions.max()) + 1, 1, D), dtype=torch.float32, device=dev)
+    cache[positions, 0] = torch.from_numpy(g("cos_sin_rows")).to(dev)
+    pool_dt = torch.float32 if pool == "f32" else torch.float8_e4m3fn
+    slots = torch.from_numpy(g("slots")).to(dev)
+    ref_ck, ref_cv = g("compact_k"), g("compact_v")
+
+    def run(**kw):
+        qq, kk = q.clone(), k.clone()
+        ck = torch.zeros(ref_ck.shape, dtype=torch.float32, device=dev).to(pool_dt)
+        cv = torch.zeros_like(ck)
+        ev = torch.empty((B, Hk), dtype=torch.bool, device=dev)
+        fused_dms_rope_store_compact_decode(qq, kk, v, cache, ck, cv, slots, ev, positions, num_kv_heads=Hk,
+                                            alpha_scale=100.0, alpha_offset=5.0, **kw)
+        return qq, kk, ck, cv, ev
+
+    qq, kk, ck, cv, ev = run()
+    assert np.array_equal(ev.cpu().numpy(), g("evict"))
+    assert np.array_equal(raw(qq), g("q_out").view(np.uint8).reshape(raw(qq).shape))
+    assert np.array_equal(raw(kk), g("k_out").view(np.uint8).reshape(raw(kk).shape))
+    assert np.array_equal(raw(ck), ref_ck.view(np.uint8).reshape(raw(ck).shape))
+    assert np.array_equal(raw(cv), ref_cv.view(np.uint8).reshape(raw(cv).shape))
+    # transient k left alone, pool identical
+    qq, kk, ck, cv, ev = run(store_transient_k=False)
+    assert torch.equal(kk, k) and np.array_equal(raw(ck), ref_ck.view(np.uint8).reshape(raw(ck).shape))
+    assert np.array_equal(raw(qq), g("q_out").view(np.uint8).reshape(raw(qq).shape))
+    # q left alone (rotated later inside attention), decisions identical
+    qq, kk, ck, cv, ev = run(store_q=False)
+    assert torch.equal(qq, q) and np.array_equal(ev.cpu().numpy(), g("evict"))
+    assert np.array_equal(raw(ck), ref_ck.view(np.uint8).reshape(raw(ck).shape))
+    # plain store of already-rotated k
+    ck2 = torch.zeros_like(ck)
+    cv2 = torch.zeros_like(cv)
+    store_compact_kvcache(up(g("k_out")), v, ck2, cv2, slots)
+    assert torch.equal(ck2.view(torch.uint8), ck.view(torch.uint8)) and torch.equal(cv2.view(torch.uint8), cv.view(torch.uint8))
+    with pytest.raises(ValueError):
+        fused_dms_rope_store_compact_decode(q, k, v, cache, ck, cv, slots[:, :1], ev, positions, num_kv_heads=Hk,
+                                            alpha_scale=100.0, alpha_offset=5.0)
+
+
+def test_store_with_per_head_scale(dev):
+    from fastdms_b200.layers.compact_attention import store_compact_kvcache
+    rng = np.random.default_rng(11)
+    B, Hk, D = 4, 2, 64
+    k = rng.standard_normal((B, Hk, D)).astype(np.float32) * 30
+    v = rng.standard_normal((B, Hk, D)).astype(np.float32) * 0.01
+    ks, vs = O.absmax_scale(k), O.absmax_scale(v)
+    kb = torch.from_numpy(k).to(dev).to(torch.bfloat16)
+    vb = torch.from_numpy(v).to(dev).to(torch.bfloat16)
+    slots = torch.arange(B * Hk, dtype=torch.int32, device=dev).view(B, Hk)
+    ck = torch.zeros((B * Hk, D), dtype=torch.float8_e4m3fn, device=dev)
+    cv = torch.zeros_like(ck)
+    store_compact_kvcache(kb, vb, ck, cv, slots, k_scale=torch.from_numpy(ks).to(dev), v_scale=torch.from_numpy(vs).to(dev))
+    exp_k = O.kv_quant(n_bf16(kb), ks).reshape(B * Hk, D)
+    exp_v = O.kv_quant(n_bf16(vb), vs).reshape(B * Hk, D)
+    assert np.array_equal(n_u8(ck), exp_k) and np.array_equal(n_u8(cv), exp_v)
+
+
+# ------------------------------------------------------------------------------------------------
+def _attn(dev, q, k, v, base, live, **kw):
+    from fastdms_b200.layers.compact_attention import compact_decode_attention
+    return compact_decode_attention(q, k, v, torch.from_numpy(base).to(dev), torch.from_numpy(live).to(dev), **kw)
+
+
+def test_attention_reference_f32_fixture(ops_golden, dev):
+    """The reference's own split-K test shape (float32, head_dim 16): generic kernel."""
+    z = ops_golden
+    q, k, v = (torch.from_numpy(z[f"attn_f32d16_{n}"]).to(dev) for n in ("q", "k", "v"))
+    out = _attn(dev, q, k, v, z["attn_f32d16_base"], z["attn_f32d16_live"], max_live_count=20, block_n=16)
+    assert np.abs(out.cpu().numpy() - z["attn_f32d16_out"]).max() < F32_TOL
+    o2 = _attn(dev, torch.ones((1, 4, 4), device=dev), torch.from_numpy(z["packka_compact_k"]).to(dev),
+               torch.from_numpy(z["packka_compact_v"]).to(dev), z["packka_base"], z["packka_live"], scale=1.0)
+    assert np.abs(o2.cpu().numpy() - z["packka_attn_out"]).max() < F32_TOL
+
+
+@pytest.mark.parametrize("tag,scale", [("fp8d64", None), ("fp8d128", 0.11)])
+@pytest.mark.parametrize("generic", [False, True])
+def test_attention_fp8_golden(ops_golden, dev, tag, scale, generic, monkeypatch):
+    z = ops_golden
+    if generic:
+        monkeypatch.setenv("FDMS_ATTN_FORCE_GENERIC", "1")
+    q = t_bf16(z[f"attn_{tag}_q"], dev)
+    k, v = t_fp8(z[f"attn_{tag}_k"], dev), t_fp8(z[f"attn_{tag}_v"], dev)
+    base, live = z[f"attn_{tag}_base"], z[f"attn_{tag}_live"]
+    out = _attn(dev, q, k, v, base, live, scale=scale)
+    want = O.decode_attention(bf16_bits_to_f32(z[f"attn_{tag}_q"].view(np.uint16)), z[f"attn_{tag}_k"],
+                              z[f"attn_{tag}_v"], base, live, scale, pool_dtype="e4m3")
+    assert np.abs(n_bf16(out) - want).max() < ATTN_TOL
+    # and against the reference's own output (bf16), same tolerance
+    assert np.abs(n_bf16(out) - bf16_bits_to_f32(z[f"attn_{tag}_out"].view(np.uint16))).max() < ATTN_TOL
+
+
+def _config2_case(rng, B, Hk, G, D, mean, jitter, recent, paged, pool_pages_extra=9):
+    """Config-2 style inputs: ragged spans, N(0,1) K/V quantised with per-head absmax scales."""
+    live = (mean + rng.integers(-jitter, jitter + 1, size=(B, Hk)) + recent).astype(np.int32)
+    pages = -(-live // 16)
+    total_pages = int(pages.sum()) + pool_pages_extra
+    rows = total_pages * 16
+    kf = rng.standard_normal((rows, D)).astype(np.float32)
+    vf = rng.standard_normal((rows, D)).astype(np.float32)
+    q = rng.standard_normal((B, Hk * G, D)).astype(np.float32)
+    ks = np.full(Hk, np.abs(kf).max() / 448.0, np.float32) * (1 + 0.1 * np.arange(Hk, dtype=np.float32))
+    vs = np.full(Hk, np.abs(vf).max() / 448.0, np.float32) * (1 + 0.05 * np.arange(Hk, dtype=np.float32))
+    maxp = int(pages.max())
+    bt = np.full((B, Hk, maxp), -1, np.int32)
+    base = np.zeros((B, Hk), np.int32)
+    kq = np.zeros((rows, D), np.uint8)
+    vq = np.zeros((rows, D), np.uint8)
+    if paged:
+        perm = rng.permutation(total_pages)
+        nxt = 0
+        for b in range(B):
+            for h in range(Hk):
+                for p in range(int(pages[b, h])):
+                    bt[b, h, p] = perm[nxt]; nxt += 1
+                rws = O.gather_span(np.arange(rows), 0, int(live[b, h]), bt[b, h])
+                kq[rws] = encode_e4m3(kf[rws] / ks[h]); vq[rws] = encode_e4m3(vf[rws] / vs[h])
+    else:
+        cur = 0
+        for b in range(B):
+            for h in range(Hk):
+                base[b, h] = cur
+                n = int(live[b, h])
+                kq[cur:cur + n] = encode_e4m3(kf[cur:cur + n] / ks[h]); vq[cur:cur + n] = encode_e4m3(vf[cur:cur + n] / vs[h])
+                cur += n + int(rng.integers(0, 5))
+    return q, kq, vq, base, live, (bt if paged else None), ks, vs
+
+
+@pytest.mark.parametrize("D,G", [(64, 4), (128, 4), (64, 8), (64, 1)])
+@pytest.mark.parametrize("paged", [False, True])
+def test_attention_ragged_scaled(dev, D, G, paged):
+    from fastdms_b200.layers.compact_attention import compact_decode_attention
+    rng = np.random.default_rng(100 + D + G + int(paged))
+    B, Hk = 3, 2
+    q, kq, vq, base, live, bt, ks, vs = _config2_case(rng, B, Hk, G, D, 300, 100, 40, paged)
+    qb = torch.from_numpy(q).to(dev).to(torch.bfloat16)
+    out = compact_decode_attention(
+        qb, t_fp8(kq, dev), t_fp8(vq, dev), torch.from_numpy(base).to(dev), torch.from_numpy(live).to(dev),
+        block_tables=None if bt is None else torch.from_numpy(bt).to(dev),
+        k_scale=torch.from_numpy(ks).to(dev), v_scale=torch.from_numpy(vs).to(dev))
+    want = O.decode_attention(n_bf16(qb), kq, vq, base, live, pool_dtype="e4m3", k_scale=ks, v_scale=vs, block_tables=bt)
+    assert np.abs(n_bf16(out) - want).max() < ATTN_TOL
+
+
+def test_attention_config2_shape(dev):
+    """BASELINE config 2: 8 sequences, 32 q / 8 KV heads, head_dim 64, live = 1024 +- 128 + 256,
+    16-row pages with randomly permuted block tables, per-head absmax scales."""
+    from fastdms_b200.layers.compact_attention import compact_decode_attention
+    rng = np.random.default_rng(0)
+    q, kq, vq, base, live, bt, ks, vs = _config2_case(rng, 8, 8, 4, 64, 1024, 128, 256, True)
+    qb = torch.from_numpy(q).to(dev).to(torch.bfloat16)
+    args = (qb, t_fp8(kq, dev), t_fp8(vq, dev), torch.from_numpy(base).to(dev), torch.from_numpy(live).to(dev))
+    kw = dict(block_tables=torch.from_numpy(bt).to(dev), k_scale=torch.from_numpy(ks).to(dev), v_scale=torch.from_numpy(vs).to(dev))
+    out = compact_decode_attention(*args, **kw)
+    want = O.decode_attention(n_bf16(qb), kq, vq, base, live, pool_dtype="e4m3", k_scale=ks, v_scale=vs, block_tables=bt)
+    assert np.abs(n_bf16(out) - want).max() < ATTN_TOL
+    # repeated calls reuse the split-K workspace (counters must come back to zero) and are deterministic
+    for _ in range(3):
+        again = compact_decode_attention(*args, **kw)
+        assert torch.equal(again, out)
+
+
+def test_attention_edge_lengths(dev):
+    """live = 1, exact page multiples, one long span next to tiny ones, and an empty span."""
+    from fastdms_b200.layers.compact_attention import compact_decode_attention
+    rng = np.random.default_rng(5)
+    D, G, Hk = 64, 4, 2
+    live = np.array([[1, 16], [17, 5000], [32, 0]], np.int32)
+    B = live.shape[0]
+    base = np.zeros_like(live)
+    cur = 0
+    for b in range(B):
+        for h in range(Hk):
+            base[b, h] = cur; cur += int(live[b, h]) + 3
+    kq = encode_e4m3(rng.standard_normal((cur, D)).astype(np.float32))
+    vq = encode_e4m3(rng.standard_normal((cur, D)).astype(np.float32))
+    q = rng.standard_normal((B, Hk * G, D)).astype(np.float32)
+    qb = torch.from_numpy(q).to(dev).to(torch.bfloat16)
+    out = compact_decode_attention(qb, t_fp8(kq, dev), t_fp8(vq, dev), torch.from_numpy(base).to(dev), torch.from_numpy(live).to(dev))
+    got = n_bf16(out)
+    live2 = live.copy(); live2[2, 1] = 1     # the oracle divides by zero on an empty span: compare the rest
+    want = O.decode_attention(n_bf16(qb), kq, vq, base, live2, pool_dtype="e4m3")
+    mask = np.ones_like(got, bool); mask[2, G:] = False
+    assert np.abs(got - want)[mask].max() < ATTN_TOL
+    assert np.all(got[2, G:] == 0)            # an empty span yields zeros, not NaN
+
+
+def test_attention_inline_q_rope(ops_golden, dev):
+    """q rotated inside the attention kernel == q rotated by the store kernel first."""
+    from fastdms_b200.layers.compact_attention import compact_decode_attention
+    z = ops_golden
+    g = lambda n: z[f"ropestore_bf16d64_{n}"]
+    q = t_bf16(g("q"), dev)
+    B, Hq, D = q.shape
+    Hk = g("k").shape[1]
+    positions = torch.from_numpy(g("positions")).to(dev)
+    cache = torch.zeros((int(positions.max()) + 1, 1, D), dtype=torch.float32, device=dev)
+    cache[positions, 0] = torch.from_numpy(g("cos_sin_rows")).to(dev)
+    rng = np.random.default_rng(2)
+    live = rng.integers(20, 90, size=(B, Hk)).astype(np.int32)
+    base = (np.arange(B * Hk, dtype=np.int32) * 100).reshape(B, Hk)
+    kq = encode_e4m3(rng.standard_normal((B * Hk * 100, D)).astype(np.float32))
+    vq = encode_e4m3(rng.standard_normal((B * Hk * 100, D)).astype(np.float32))
+    out = compact_decode_attention(q, t_fp8(kq, dev), t_fp8(vq, dev), torch.from_numpy(base).to(dev),
+                                   torch.from_numpy(live).to(dev), q_rope_positions=positions, q_rope_cos_sin_cache=cache)
+    qf, _ = O.extract_decisions(bf16_bits_to_f32(g("q").view(np.uint16)), Hk, 100.0, 5.0)
+    cs = cache[:, 0].cpu().numpy()
+    pos = g("positions")
+    q_rot = O.rope_neox(qf, cs[pos, : D // 2][:, None, :], cs[pos, D // 2:][:, None, :])
+    want = O.decode_attention(q_rot, kq, vq, base, live, pool_dtype="e4m3")
+    assert np.abs(n_bf16(out) - want).max() < ATTN_TOL
+    with pytest.raises(ValueError):
+        compact_decode_attention(q, t_fp8(kq, dev), t_fp8(vq, dev), torch.from_numpy(base).to(dev),
+                                 torch.from_numpy(live).to(dev), q_rope_positions=positions)
+
+
+def test_attention_argument_errors(dev):
+    from fastdms_b200.layers.compact_attention import compact_decode_attention
+    q = torch.zeros((2, 8, 64), dtype=torch.bfloat16, device=dev)
+    k = torch.zeros((64, 64), dtype=torch.float8_e4m3fn, device=dev)
+    meta = torch.ones((2, 2), dtype=torch.int32, device=dev)
+    with pytest.raises(ValueError):
+        compact_decode_attention(q[0], k, k, meta, meta)
+    with pytest.raises(ValueError):
+        compact_decode_attention(q, k, k[:, :32], meta, meta)
+    with pytest.raises(ValueError):
+        compact_decode_attention(q, k, k, meta[:1], meta[:1])
+    with pytest.raises(ValueError):
+        compact_decode_attention(q, k, k, torch.ones((2, 3), dtype=torch.int32, device=dev), torch.ones((2, 3), dtype=torch.int32, device=dev))
+    with pytest.raises(RuntimeError):
+        compact_decode_attention(q.cpu(), k.cpu(), k.cpu(), meta.cpu(), meta.cpu())
+
+
+# ------------------------------------------------------------------------------------------------
+def test_kv_quant_dequant(dev):
+    from fastdms_b200.layers.compact_attention import kv_dequantize_fp8, kv_quantize_fp8
+    rng = np.random.default_rng(7)
+    x = rng.standard_normal((300, 8, 64)).astype(np.float32) * np.logspace(-2, 2, 8, dtype=np.float32)[None, :, None]
+    s = O.absmax_scale(x)
+    xt, st = torch.from_numpy(x).to(dev), torch.from_numpy(s).to(dev)
+    qd = kv_quantize_fp8(xt, st)
+    assert np.array_equal(n_u8(qd), O.kv_quant(x, s))
+    assert np.array_equal(kv_dequantize_fp8(qd, st).cpu().numpy(), O.kv_dequant(O.kv_quant(x, s), s))
+    xb = xt.to(torch.bfloat16)
+    assert np.array_equal(n_u8(kv_quantize_fp8(xb, st)), O.kv_quant(n_bf16(xb), s))
+    assert np.array_equal(n_bf16(kv_dequantize_fp8(qd, st, torch.bfloat16)), O.kv_dequant(O.kv_quant(x, s), s, "bf16"))
+    # scale None is the reference's bare cast; out-of-range saturates to +-448
+    big = torch.tensor([[[1000.0, -1000.0] + [0.5] * 14]], device=dev)
+    assert decode_e4m3(n_u8(kv_quantize_fp8(big)))[0, 0, :3].tolist() == [448.0, -448.0, 0.5]
+    # idempotence at full config-2 volume (round trip is a fixed point)
+    y = torch.randn((81920, 8, 64), device=dev, dtype=torch.bfloat16)
+    sc = (y.float().abs().amax(dim=(0, 2)) / 448.0).contiguous()
+    q1 = kv_quantize_fp8(y, sc)
+    q2 = kv_quantize_fp8(kv_dequantize_fp8(q1, sc), sc)
+    assert torch.equal(q1.view(torch.uint8), q2.view(torch.uint8))
