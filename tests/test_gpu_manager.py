@@ -166,9 +166,9 @@ def _load_expiry_state(m, seq, z, prefix, pool, dev):
         v = torch.from_numpy(z[f"{prefix}_v_l{l}"].copy())
         if pool == torch.float8_e4m3fn:
             k, v = k.view(torch.float8_e4m3fn), v.view(torch.float8_e4m3fn)
-        n = k.shape[0]
-        m.compact_k_per_layer[l][:n].copy_(k)
-        m.compact_v_per_layer[l][:n].copy_(v)
+        n = min(k.shape[0], m.capacity_tokens)   # the reference grows its pools in 256-row steps
+        m.compact_k_per_layer[l][:n].copy_(k[:n])
+        m.compact_v_per_layer[l][:n].copy_(v[:n])
     return st
 
 
