@@ -106,7 +106,7 @@ def require_cuda(*tensors: torch.Tensor) -> None:
 
 # ---- per-device scratch owned by the Python layer (the C library allocates nothing) ------------
 _status_words: dict[int, torch.Tensor] = {}
-_workspaces: dict[tuple[int, int], torch.Tensor] = {}
+_workspaces: dict[int, torch.Tensor] = {}
 
 
 def status_word(device: torch.device) -> torch.Tensor:
@@ -129,13 +129,13 @@ def read_device_status(device: torch.device | str = "cuda", clear: bool = True) 
 
 
 def attn_workspace(device: torch.device, batch: int, num_kv_heads: int, head_dim: int) -> torch.Tensor:
-    """Zero-initialised split-K workspace, one per (device, stream); grown on demand and reused
-    (the kernel leaves its counters at zero)."""
+    """Zero-initialised split-K workspace, one per device, grown on demand and reused (the kernel
+    leaves its counters at zero).  Launches that use it are ordered by the stream they run on;
+    callers that drive several streams at once must pass their own workspace instead."""
     need = lib().fdms_attn_decode_workspace_bytes(batch, num_kv_heads, head_dim)
     idx = device.index if device.index is not None else torch.cuda.current_device()
-    key = (idx, torch.cuda.current_stream(device).cuda_stream)
-    ws = _workspaces.get(key)
+    ws = _workspaces.get(idx)
     if ws is None or ws.numel() < need:
         ws = torch.zeros(need, dtype=torch.uint8, device=device)
-        _workspaces[key] = ws
+        _workspaces[idx] = ws
     return ws

@@ -468,6 +468,21 @@ class CompactKVManager:
         cur = torch.tensor([int(p) for p in current_positions], dtype=torch.int64).to(dev, non_blocking=True)
         slots_t = self._slots_tensor(states)
         stats = self._stats_init.clone()
+        self.expire_device(slots_t, cur, window_size=window_size, incremental=incremental, stats=stats)
+        for st in states:
+            st.dms_initial_expiry_done = True
+        keys = ("evicted_tokens", "live_tokens_before_min", "live_tokens_before_max",
+                "live_tokens_after_min", "live_tokens_after_max")
+        if sync_stats:
+            return dict(zip(keys, stats.tolist()))
+        return {k: stats[i] for i, k in enumerate(keys)}
+
+    def expire_device(self, slots_t: torch.Tensor, cur_positions_t: torch.Tensor, *, window_size: int,
+                      incremental: bool = False, stats: torch.Tensor | None = None) -> None:
+        """The expiry launch itself, on device-resident arguments only (no allocation, no host
+        synchronisation; safe inside CUDA-graph capture).  slots_t int32 [n] active slots,
+        cur_positions_t int64 [n]; stats optional int64[5] initialised by the caller."""
+        dev = self.device
         pos, ev = self.layer_major_token_positions, self.layer_major_evict_mask.view(torch.uint8)
         lc, base = self.layer_major_live_counts, self.layer_major_base_offsets
         row_bytes = self.head_dim * self.compact_k.element_size()
@@ -487,18 +502,51 @@ class CompactKVManager:
                 self.compact_k.data_ptr(), self.compact_v.data_ptr(),
                 self.compact_k.stride(0) * self.compact_k.element_size(), row_bytes, self.capacity_tokens,
                 *bt_args,
-                slots_t.data_ptr(), cur.data_ptr(),
-                self.num_layers, len(states), self.num_kv_heads, self.max_model_len,
-                int(window_size), 1 if incremental else 0, stats.data_ptr(),
+                slots_t.data_ptr(), cur_positions_t.data_ptr(),
+                self.num_layers, slots_t.numel(), self.num_kv_heads, self.max_model_len,
+                int(window_size), 1 if incremental else 0, _lib.ptr(stats),
                 _lib.status_word(dev).data_ptr(), _lib.stream_ptr(dev))
         _lib.check(rc)
-        for st in states:
-            st.dms_initial_expiry_done = True
-        keys = ("evicted_tokens", "live_tokens_before_min", "live_tokens_before_max",
-                "live_tokens_after_min", "live_tokens_after_max")
-        if sync_stats:
-            return dict(zip(keys, stats.tolist()))
-        return {k: stats[i] for i, k in enumerate(keys)}
+
+    def decode_metadata_device(self, slots_t: torch.Tensor, base_out: torch.Tensor, live_out: torch.Tensor,
+                               slot_out: torch.Tensor, cu_out: torch.Tensor | None = None) -> None:
+        """The decode-metadata launch on device-resident arguments (capture-safe).  Outputs are
+        int32 [layers, batch, kv_heads]; cu_out int32 [layers, batch*kv_heads + 1]."""
+        dev = self.device
+        lc, base = self.layer_major_live_counts, self.layer_major_base_offsets
+        if self.paged:
+            bt = self.block_tables
+            bt_args = (bt.data_ptr(), bt.stride(0), bt.stride(1), bt.stride(2), self.max_pages,
+                       self.free_pages.data_ptr(), self.free_page_counts.data_ptr(), self.pages_per_layer)
+            base_ptr = None
+        else:
+            bt_args = (None, 0, 0, 0, 0, None, None, 0)
+            base_ptr = base.data_ptr()
+        with torch.cuda.device(dev):
+            rc = _lib.lib().fdms_build_decode_metadata(
+                lc.data_ptr(), base_ptr, lc.stride(0), lc.stride(1), *bt_args,
+                slots_t.data_ptr(), base_out.data_ptr(), live_out.data_ptr(), slot_out.data_ptr(), _lib.ptr(cu_out),
+                self.num_layers, slots_t.numel(), self.num_kv_heads,
+                _lib.status_word(dev).data_ptr(), _lib.stream_ptr(dev))
+        _lib.check(rc)
+
+    def record_device(self, slots_t: torch.Tensor, positions_t: torch.Tensor, evict_all: torch.Tensor,
+                      true_count: torch.Tensor | None = None) -> None:
+        """The decision-recording launch on device-resident arguments (capture-safe).
+        positions_t int64 [batch]; evict_all bool [layers, batch, kv_heads], head-contiguous."""
+        dev = self.device
+        pos, ev = self.layer_major_token_positions, self.layer_major_evict_mask.view(torch.uint8)
+        lc = self.layer_major_live_counts
+        ea = evict_all.view(torch.uint8)
+        with torch.cuda.device(dev):
+            rc = _lib.lib().fdms_record_decisions(
+                pos.data_ptr(), pos.stride(0), pos.stride(1), pos.stride(2),
+                ev.data_ptr(), ev.stride(0), ev.stride(1), ev.stride(2),
+                lc.data_ptr(), lc.stride(0), lc.stride(1),
+                ea.data_ptr(), ea.stride(0), ea.stride(1),
+                positions_t.data_ptr(), slots_t.data_ptr(), self.num_layers, slots_t.numel(), self.num_kv_heads,
+                self.max_model_len, _lib.ptr(true_count), _lib.stream_ptr(dev))
+        _lib.check(rc)
 
     # ------------------------------------------------------------------ decode metadata
     def prepare_decode_metadata(self, seqs: list[Sequence]):
@@ -516,22 +564,7 @@ class CompactKVManager:
                 torch.empty((L, B * Hk + 1), device=dev, dtype=torch.int32),)
             self._decode_buffers[B] = bufs
         base_out, live_out, slot_out, cu_out = bufs
-        slots_t = self._slots_tensor(states)
-        lc, base = self.layer_major_live_counts, self.layer_major_base_offsets
-        if self.paged:
-            bt = self.block_tables
-            bt_args = (bt.data_ptr(), bt.stride(0), bt.stride(1), bt.stride(2), self.max_pages,
-                       self.free_pages.data_ptr(), self.free_page_counts.data_ptr(), self.pages_per_layer)
-            base_ptr = None
-        else:
-            bt_args = (None, 0, 0, 0, 0, None, None, 0)
-            base_ptr = base.data_ptr()
-        with torch.cuda.device(dev):
-            rc = _lib.lib().fdms_build_decode_metadata(
-                lc.data_ptr(), base_ptr, lc.stride(0), lc.stride(1), *bt_args,
-                slots_t.data_ptr(), base_out.data_ptr(), live_out.data_ptr(), slot_out.data_ptr(), cu_out.data_ptr(),
-                L, B, Hk, _lib.status_word(dev).data_ptr(), _lib.stream_ptr(dev))
-        _lib.check(rc)
+        self.decode_metadata_device(self._slots_tensor(states), base_out, live_out, slot_out, cu_out)
         self.last_cu_live = cu_out
         return base_out, live_out, slot_out, max(st.max_capacity_per_lh for st in states)
 
@@ -581,19 +614,8 @@ class CompactKVManager:
             pos_t = torch.tensor([int(p) for p in current_positions], dtype=torch.int64).to(dev, non_blocking=True)
         states = self._states(seqs)
         slots_t = self._slots_tensor(states)
-        pos, ev = self.layer_major_token_positions, self.layer_major_evict_mask.view(torch.uint8)
-        lc = self.layer_major_live_counts
-        ea = evict_all.view(torch.uint8)
         true_count = torch.zeros(1, device=dev, dtype=torch.int64)
-        with torch.cuda.device(dev):
-            rc = _lib.lib().fdms_record_decisions(
-                pos.data_ptr(), pos.stride(0), pos.stride(1), pos.stride(2),
-                ev.data_ptr(), ev.stride(0), ev.stride(1), ev.stride(2),
-                lc.data_ptr(), lc.stride(0), lc.stride(1),
-                ea.data_ptr(), ea.stride(0), ea.stride(1),
-                pos_t.data_ptr(), slots_t.data_ptr(), L, B, Hk, self.max_model_len,
-                true_count.data_ptr(), _lib.stream_ptr(dev))
-        _lib.check(rc)
+        self.record_device(slots_t, pos_t, evict_all, true_count)
         total_true = true_count[0]
         return {"eviction_decisions_true": int(total_true.item()) if sync_stats else total_true,
                 "eviction_decisions_total": L * B * Hk}

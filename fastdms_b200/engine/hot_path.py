@@ -1,0 +1,141 @@
+"""One decode step of the compact-DMS path for a fixed batch, captured as a CUDA graph.
+
+Order of work inside a step (the reference's order: engine/model_runner.py:713-772 prepare_decode,
+models/llama.py:138-201 per layer, model_runner.py:681-711 record):
+
+    expiry (all layers)  ->  decode metadata (all layers, live += 1)
+    ->  per layer: fused decision + RoPE + FP8 store, then compact attention
+    ->  decision recording (all layers)  ->  positions += 1
+
+Everything is a launch on device-resident state, so the whole step is ONE graph replay:
+2 + 2 * layers + 1 kernels of this library plus one position increment.
+
+`DecodeHotPath` is driven either with activations that already sit in its device buffers
+(`step_device`) or with host buffers (`step_host`: pinned host -> device copies of the step's
+q/k/v and positions, graph replay, device -> host copy of the attention output).
+"""
+from __future__ import annotations
+
+import torch
+
+from fastdms_b200 import _lib
+from fastdms_b200.engine.compact_kv import CompactKVManager
+from fastdms_b200.layers.compact_attention import (compact_decode_attention,
+                                                   fused_dms_rope_store_compact_decode)
+
+
+class DecodeHotPath:
+    def __init__(self, manager: CompactKVManager, seqs: list, *, num_q_heads: int, window_size: int,
+                 alpha_scale: float, alpha_offset: float, cos_sin_cache: torch.Tensor,
+                 act_dtype: torch.dtype = torch.bfloat16, scale: float | None = None,
+                 expire_every_step: bool = True, use_cuda_graph: bool = True):
+        self.m = manager
+        self.seqs = list(seqs)
+        self.states = manager._states(self.seqs)
+        dev = manager.device
+        L, Hk, D = manager.num_layers, manager.num_kv_heads, manager.head_dim
+        B = len(self.seqs)
+        self.L, self.B, self.Hq, self.Hk, self.D = L, B, int(num_q_heads), Hk, D
+        self.window_size = int(window_size)
+        self.alpha_scale, self.alpha_offset = float(alpha_scale), float(alpha_offset)
+        self.scale = scale
+        self.expire_every_step = expire_every_step
+        self.cos_sin_cache = cos_sin_cache.to(device=dev, dtype=torch.float32).contiguous()
+        self.slots_t = manager._slots_tensor(self.states)
+        # device-resident step state
+        self.q = torch.zeros((L, B, self.Hq, D), device=dev, dtype=act_dtype)
+        self.k = torch.zeros((L, B, Hk, D), device=dev, dtype=act_dtype)
+        self.v = torch.zeros((L, B, Hk, D), device=dev, dtype=act_dtype)
+        self.out = torch.zeros((L, B, self.Hq, D), device=dev, dtype=act_dtype)
+        self.positions = torch.zeros((B,), device=dev, dtype=torch.int64)
+        self.evict_all = torch.zeros((L, B, Hk), device=dev, dtype=torch.bool)
+        self.base = torch.zeros((L, B, Hk), device=dev, dtype=torch.int32)
+        self.live = torch.zeros_like(self.base)
+        self.slot = torch.zeros_like(self.base)
+        self.cu_live = torch.zeros((L, B * Hk + 1), device=dev, dtype=torch.int32)
+        self.block_tables = manager.decode_block_tables(self.seqs)
+        # pinned staging for the host-driven step
+        self._h_q = self._h_k = self._h_v = self._h_out = self._h_pos = None
+        self.graph = None
+        self.use_cuda_graph = use_cuda_graph
+        self.launches_per_step = 2 + 2 * L + 1
+        _lib.attn_workspace(dev, B, Hk, D)          # allocate outside any capture
+
+    # ---------------------------------------------------------------- the step itself
+    def _enqueue(self) -> None:
+        m = self.m
+        if self.expire_every_step:
+            m.expire_device(self.slots_t, self.positions, window_size=self.window_size)
+        m.decode_metadata_device(self.slots_t, self.base, self.live, self.slot, self.cu_live)
+        for l in range(self.L):
+            ks, vs = m.layer_scales(l)
+            ck, cv = m.compact_k_per_layer[l], m.compact_v_per_layer[l]
+            fused_dms_rope_store_compact_decode(
+                self.q[l], self.k[l], self.v[l], self.cos_sin_cache, ck, cv, self.slot[l], self.evict_all[l],
+                self.positions, num_kv_heads=self.Hk, alpha_scale=self.alpha_scale, alpha_offset=self.alpha_offset,
+                store_q=True, store_transient_k=False, k_scale=ks, v_scale=vs)
+            compact_decode_attention(
+                self.q[l], ck, cv, self.base[l], self.live[l], scale=self.scale,
+                block_tables=None if self.block_tables is None else self.block_tables[l],
+                k_scale=ks, v_scale=vs, out=self.out[l])
+        m.record_device(self.slots_t, self.positions, self.evict_all)
+        self.positions.add_(1)
+
+    def capture(self) -> None:
+        """Runs one eager step (warm-up; it advances the state like any step) and records the graph."""
+        if not self.use_cuda_graph or self.graph is not None:
+            return
+        self._enqueue()
+        torch.cuda.synchronize(self.m.device)
+        g = torch.cuda.CUDAGraph()
+        # Capturing enqueues nothing on the device, but the Python-side calls are the same; the
+        # captured launches read the state at replay time.
+        with torch.cuda.graph(g):
+            self._enqueue()
+        self.graph = g
+
+    def step_device(self) -> None:
+        """One step on the activations currently in self.q / self.k / self.v at self.positions."""
+        if self.use_cuda_graph:
+            if self.graph is None:
+                raise RuntimeError("call capture() before step_device()")
+            self.graph.replay()
+        else:
+            self._enqueue()
+
+    def set_positions(self, positions) -> None:
+        self.positions.copy_(torch.as_tensor(positions, dtype=torch.int64), non_blocking=True)
+
+    # ---------------------------------------------------------------- host-driven step
+    def _ensure_pinned(self) -> None:
+        if self._h_q is None:
+            pin = lambda t: torch.empty(t.shape, dtype=t.dtype, pin_memory=True)
+            self._h_q, self._h_k, self._h_v, self._h_out = pin(self.q), pin(self.k), pin(self.v), pin(self.out)
+            self._h_pos = torch.empty((self.B,), dtype=torch.int64, pin_memory=True)
+
+    def step_host(self, q_host: torch.Tensor, k_host: torch.Tensor, v_host: torch.Tensor,
+                  positions_host: torch.Tensor) -> torch.Tensor:
+        """Host buffers in, host buffer out.  Inputs are staged through pinned memory, copied to
+        the device, the step runs, and the attention output [layers, batch, q_heads, head_dim] is
+        copied back.  Returns the pinned result tensor (overwritten by the next call)."""
+        self._ensure_pinned()
+        self._h_q.copy_(q_host)
+        self._h_k.copy_(k_host)
+        self._h_v.copy_(v_host)
+        self._h_pos.copy_(positions_host)
+        self.q.copy_(self._h_q, non_blocking=True)
+        self.k.copy_(self._h_k, non_blocking=True)
+        self.v.copy_(self._h_v, non_blocking=True)
+        self.positions.copy_(self._h_pos, non_blocking=True)
+        self.step_device()
+        self._h_out.copy_(self.out, non_blocking=True)
+        torch.cuda.current_stream(self.m.device).synchronize()
+        return self._h_out
+
+    @property
+    def h2d_bytes_per_step(self) -> int:
+        return sum(t.numel() * t.element_size() for t in (self.q, self.k, self.v, self.positions))
+
+    @property
+    def d2h_bytes_per_step(self) -> int:
+        return self.out.numel() * self.out.element_size()
