@@ -2,26 +2,26 @@
 //
 // Fast path (FP8 e4m3 pools, head_dim 64 or 128, group size <= 8)
 // ----------------------------------------------------------------
-// The kernel is a single-wave, work-balanced scan of the pool:
-//   * Work unit = one 16-row page of one span.  Every CTA computes the exclusive prefix sum of the
-//     spans' page counts in shared memory (one coalesced read of live_counts) and takes an equal
-//     contiguous slice of the flattened page list, so ragged lengths cost no idle CTAs and no host
-//     round trip ("split-K across the compact length" with a stream-K style partition).
+//   * Split-K across the compact length on thread-block clusters.  A span (one sequence, one KV
+//     head) is cut into `splits` equal page ranges; the CTAs of one cluster take one range each.
+//     Partial (m, l, O) results travel to the cluster's first CTA through distributed shared memory
+//     (remote stores + one cluster barrier), which folds them and writes the output: no global
+//     round trip, no second launch.  The host picks splits (1..16) so that the grid is about one
+//     wave of 2 CTAs per SM.  Very long spans at tiny batch use several clusters per span
+//     (`chunks` > 1); only then do cluster leaders meet in the global workspace, where the last one
+//     to arrive at a per-span counter folds the chunk partials (threadfence + atomic, no spinning).
 //   * A producer warp resolves each page's address (span base or block table) and stages K and V
 //     pages into a shared-memory ring with bulk asynchronous copies (cp.async.bulk, the TMA unit's
-//     untiled form) that complete on per-stage mbarriers.  A CTA's whole slice is normally in
-//     flight at once: the working set of one layer is only a few times the bandwidth-delay
-//     product of HBM, so latency is hidden by issuing everything up front, not by occupancy.
+//     untiled form) that complete on per-stage mbarriers.  A CTA's whole range is normally in
+//     flight at once: one layer's working set is only a few times the bandwidth-delay product of
+//     HBM, so latency is hidden by issuing everything up front, not by occupancy.
 //   * Eight consumer warps each own every 8th page.  Per page a warp computes the GQA-packed
 //     S = q K^T and O += P V tiles with mma.sync.m16n8k16 (f16 operands, f32 accumulate): q heads
-//     sit on the M axis, FP8 K/V bytes are converted exactly to f16 in registers, the softmax
-//     is the usual online form with warp-shuffle row reductions in the log2 domain.
-//   * Partial (m, l, O) of a CTA's slice are merged across warps in shared memory.  A span cut
-//     by a slice boundary is finished by the last CTA to arrive at a per-span counter
-//     (threadfence + atomic, no spinning): it folds the partials left in the workspace and writes
-//     the output.  No second launch.
+//     sit on the M axis, FP8 K/V bytes are converted exactly to f16 in registers, the softmax is
+//     the online form with warp-shuffle row reductions in the log2 domain.
 // Every wait on an mbarrier is bounded; on expiry the kernel raises FDMS_DEV_WAIT_TIMEOUT in the
-// status word, stops issuing copies, drains with short waits and returns.
+// status word, stops issuing copies, drains with short waits and still takes part in every
+// cluster barrier before it returns.
 //
 // Algorithmic HBM bytes per launch: sum over spans of live * 2 * head_dim (FP8 K + V), plus
 // batch*q_heads*head_dim*(q + out) and 8-12 bytes of metadata per span.
@@ -40,7 +40,8 @@ constexpr int kConsumerWarps = 8;
 constexpr int kConsumerThreads = kConsumerWarps * 32;
 constexpr int kFastThreads = kConsumerThreads + 32;   // + one producer warp
 constexpr int kMaxGroup = 8;
-constexpr int kMaxGrid = 1024;
+constexpr int kMaxSplits = 16;           // cluster size limit (8 portable, 16 with the opt-in attribute)
+constexpr int kMaxChunks = 64;           // clusters per span
 constexpr int kWaitLimit = 400000;       // polls of mbarrier.try_wait before giving up
 constexpr int kWaitLimitDrain = 2000;
 constexpr float kLog2e = 1.4426950408889634f;
@@ -84,6 +85,19 @@ __device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t by
 __device__ __forceinline__ void consumer_bar() {
     asm volatile("bar.sync 1, %0;" ::"n"(kConsumerThreads) : "memory");
 }
+// Cluster barrier, split phase.  Every thread of every CTA of the cluster executes each call once.
+__device__ __forceinline__ void cluster_arrive_relaxed() { asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory"); }
+__device__ __forceinline__ void cluster_arrive_release() { asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory"); }
+__device__ __forceinline__ void cluster_wait_acquire() { asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory"); }
+// Address of `local` (this CTA's shared memory) in CTA `rank` of the cluster.
+__device__ __forceinline__ uint32_t map_to_rank(const void* local, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_u32(local)), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ void st_cluster_f32(uint32_t addr, float v) {
+    asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory");
+}
 __device__ __forceinline__ float ex2(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -106,6 +120,7 @@ __device__ __forceinline__ void mma_top(float& c0, float& c1, uint32_t a0, uint3
         "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%10,%10};"
         : "+f"(c0), "+f"(c1), "=f"(d2), "=f"(d3)
         : "r"(a0), "r"(0u), "r"(a2), "r"(0u), "r"(b0), "r"(b1), "f"(0.0f));
+    (void)d2; (void)d3;
 }
 
 // Physical row inside a page for MMA column n of n-tile u.  The permutation keeps the K reads
@@ -126,9 +141,9 @@ struct AttnParams {
     int batch, hq, hk, group;
     float scale;
     const int64_t* rope_pos; const float* rope_cs; int64_t rope_stride;
-    int32_t* counters; float* part_ml; float* part_o;
+    int32_t* counters; float* part_ml; float* part_o;     // only used when chunks > 1
     int32_t* dev_status;
-    int stages;
+    int stages, splits, chunks;
 };
 
 // ------------------------------------------------------------------------------------------------
@@ -159,12 +174,152 @@ __device__ __forceinline__ float load_q_elem(const AttnParams& p, int b, int hea
     return lower ? __fsub_rn(__fmul_rn(x1, c), __fmul_rn(x2, s)) : __fadd_rn(__fmul_rn(x2, c), __fmul_rn(x1, s));
 }
 
+// A-fragments of q for head g of the group: qa[4*ch + s] = {q[d0], q[d0+1]} , {q[d0+2], q[d0+3]} with
+// d0 = 64*ch + 16*t + 4*s, i.e. lane t reads 16 consecutive elements per 64-element chunk.
+template <int D>
+__device__ __forceinline__ void load_q_frags(const AttnParams& p, int b, int h, int g, int t,
+                                             uint32_t (&qa)[FastCfg<D>::kKSteps][2]) {
+    using C = FastCfg<D>;
+    const bool active = g < p.group;
+    const int head = h * p.group + g;
+    const bool vec = p.rope_pos == nullptr && p.q_dtype != FDMS_F32 &&
+                     (((uintptr_t)p.q | (uintptr_t)(p.q_sb * 2) | (uintptr_t)(p.q_sh * 2)) & 15) == 0;
+#pragma unroll
+    for (int ch = 0; ch < C::kCh; ++ch) {
+        const int d0 = 64 * ch + 16 * t;
+        if (!active) {
+#pragma unroll
+            for (int s = 0; s < 4; ++s) { qa[4 * ch + s][0] = 0u; qa[4 * ch + s][1] = 0u; }
+        } else if (vec) {
+            const uint16_t* src = (const uint16_t*)p.q + (int64_t)b * p.q_sb + (int64_t)head * p.q_sh + d0;
+            const uint4 w0 = *(const uint4*)src, w1 = *(const uint4*)(src + 8);
+            const uint32_t w[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+#pragma unroll
+            for (int s = 0; s < 4; ++s) {
+#pragma unroll
+                for (int e = 0; e < 2; ++e) {
+                    uint32_t x = w[2 * s + e];
+                    if (p.q_dtype == FDMS_BF16) {     // bf16 pair -> f16 pair through float32
+                        const float lo = __uint_as_float(x << 16), hi = __uint_as_float(x & 0xffff0000u);
+                        x = pack_f16x2(lo, hi);
+                    }
+                    qa[4 * ch + s][e] = x;
+                }
+            }
+        } else {
+#pragma unroll
+            for (int s = 0; s < 4; ++s) {
+                float x[4];
+#pragma unroll
+                for (int e = 0; e < 4; ++e) x[e] = load_q_elem(p, b, head, g, d0 + 4 * s + e, D);
+                qa[4 * ch + s][0] = pack_f16x2(x[0], x[1]);
+                qa[4 * ch + s][1] = pack_f16x2(x[2], x[3]);
+            }
+        }
+    }
+}
+
+// One staged page (K rows at Ks, V rows at Vs, `rows` of them valid): online-softmax update of the
+// warp's running (m, l, O) for head g.
+template <int D>
+__device__ __forceinline__ void process_page(const uint8_t* Ks, const uint8_t* Vs, int rows, int g, int t, float sl2,
+                                             const uint32_t (&qa)[FastCfg<D>::kKSteps][2], float& m_run, float& l_run,
+                                             float (&o)[FastCfg<D>::kNT][2]) {
+    using C = FastCfg<D>;
+    // ---- S = q K^T for the two 8-token n-tiles ----
+    float sc[2][2];
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+        const int r = tokrow(u, g);
+        float c0 = 0.0f, c1 = 0.0f;
+        uint4 kw[C::kCh];
+        if (C::kCh == 1) {
+            kw[0] = *(const uint4*)(Ks + r * D + 16 * t);
+        } else {
+            // 128-byte rows: odd rows read the upper half first so that the two rows of a
+            // quarter-warp hit different banks
+            const int sw = r & 1;
+            const uint4 a = *(const uint4*)(Ks + r * D + 64 * sw + 16 * t);
+            const uint4 c = *(const uint4*)(Ks + r * D + 64 * (sw ^ 1) + 16 * t);
+            kw[0] = sw ? c : a;
+            kw[C::kCh - 1] = sw ? a : c;
+        }
+#pragma unroll
+        for (int ch = 0; ch < C::kCh; ++ch) {
+            const uint32_t w4[4] = {kw[ch].x, kw[ch].y, kw[ch].z, kw[ch].w};
+#pragma unroll
+            for (int s = 0; s < 4; ++s) {
+                const uint32_t b0 = e4m3x2_to_f16x2(w4[s] & 0xffffu);
+                const uint32_t b1 = e4m3x2_to_f16x2(w4[s] >> 16);
+                mma_top(c0, c1, qa[4 * ch + s][0], qa[4 * ch + s][1], b0, b1);
+            }
+        }
+        sc[u][0] = c0 * sl2;
+        sc[u][1] = c1 * sl2;
+    }
+    int rA[2], rB[2];
+#pragma unroll
+    for (int u = 0; u < 2; ++u) { rA[u] = tokrow(u, 2 * t); rB[u] = tokrow(u, 2 * t + 1); }
+    if (rows < kPage) {
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+            if (rA[u] >= rows) sc[u][0] = -INFINITY;
+            if (rB[u] >= rows) sc[u][1] = -INFINITY;
+        }
+    }
+    // ---- online softmax (row = head g, reduce over the 4 lanes of the quad) ----
+    float mx = fmaxf(fmaxf(sc[0][0], sc[0][1]), fmaxf(sc[1][0], sc[1][1]));
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+    const float m_new = fmaxf(m_run, mx);
+    const float alpha = ex2(m_run - m_new);
+    float pr[2][2];
+#pragma unroll
+    for (int u = 0; u < 2; ++u) { pr[u][0] = ex2(sc[u][0] - m_new); pr[u][1] = ex2(sc[u][1] - m_new); }
+    l_run = l_run * alpha + (pr[0][0] + pr[0][1]) + (pr[1][0] + pr[1][1]);
+    m_run = m_new;
+    const uint32_t pa0 = pack_f16x2(pr[0][0], pr[0][1]);
+    const uint32_t pa2 = pack_f16x2(pr[1][0], pr[1][1]);
+#pragma unroll
+    for (int jn = 0; jn < C::kNT; ++jn) { o[jn][0] *= alpha; o[jn][1] *= alpha; }
+
+    // ---- O += P V ----
+#pragma unroll
+    for (int ch = 0; ch < C::kCh; ++ch) {
+        uint2 va[2], vb[2];
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+            va[u] = *(const uint2*)(Vs + rA[u] * D + 64 * ch + 8 * g);
+            vb[u] = *(const uint2*)(Vs + rB[u] * D + 64 * ch + 8 * g);
+            if (rows < kPage) {                   // stale bytes must not reach the MMA
+                if (rA[u] >= rows) va[u] = make_uint2(0u, 0u);
+                if (rB[u] >= rows) vb[u] = make_uint2(0u, 0u);
+            }
+        }
+        uint32_t bf[2][8];
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+            const uint32_t x0 = __byte_perm(va[u].x, vb[u].x, 0x5140);
+            const uint32_t x1 = __byte_perm(va[u].x, vb[u].x, 0x7362);
+            const uint32_t y0 = __byte_perm(va[u].y, vb[u].y, 0x5140);
+            const uint32_t y1 = __byte_perm(va[u].y, vb[u].y, 0x7362);
+            bf[u][0] = e4m3x2_to_f16x2(x0 & 0xffffu); bf[u][1] = e4m3x2_to_f16x2(x0 >> 16);
+            bf[u][2] = e4m3x2_to_f16x2(x1 & 0xffffu); bf[u][3] = e4m3x2_to_f16x2(x1 >> 16);
+            bf[u][4] = e4m3x2_to_f16x2(y0 & 0xffffu); bf[u][5] = e4m3x2_to_f16x2(y0 >> 16);
+            bf[u][6] = e4m3x2_to_f16x2(y1 & 0xffffu); bf[u][7] = e4m3x2_to_f16x2(y1 >> 16);
+        }
+#pragma unroll
+        for (int jj = 0; jj < 8; ++jj)
+            mma_top(o[8 * ch + jj][0], o[8 * ch + jj][1], pa0, pa2, bf[0][jj], bf[1][jj]);
+    }
+}
+
 template <int D>
 __global__ void __launch_bounds__(kFastThreads, (D == 64 ? 2 : 1)) attn_decode_fast_kernel(AttnParams p) {
     using C = FastCfg<D>;
     extern __shared__ __align__(128) uint8_t smem[];
-    const int items = p.batch * p.hk;
     const int NS = p.stages;
+    const int S = p.splits, CH = p.chunks, G = p.group;
     // shared memory carve-up
     uint8_t* s_stage = smem;
     uint64_t* s_full = (uint64_t*)(s_stage + (size_t)NS * C::kStageBytes);
@@ -172,105 +327,49 @@ __global__ void __launch_bounds__(kFastThreads, (D == 64 ? 2 : 1)) attn_decode_f
     float* s_m = (float*)(s_empty + NS);                      // [warps][8]
     float* s_l = s_m + kConsumerWarps * kMaxGroup;            // [warps][8]
     float* s_o = s_l + kConsumerWarps * kMaxGroup;            // [warps][8][D]
-    int* s_cu = (int*)(s_o + kConsumerWarps * kMaxGroup * D); // [items + 1] page prefix
-    int* s_live = s_cu + items + 1;                           // [items]
-    volatile int* s_flags = s_live + items;                   // [0] abort, [1] last-arriver flag
-    __shared__ int s_scan[kFastThreads / 32];
-    __shared__ int s_carry;
+    float* r_ml = s_o + kConsumerWarps * kMaxGroup * D;       // [S][G][2]   partials received from the cluster
+    float* r_o = r_ml + S * G * 2;                            // [S][G][D]
+    __shared__ int s_abort, s_last;
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int item = blockIdx.y;
+    const int rank = blockIdx.x % S;            // == rank of this CTA in its cluster
+    const int chunk = blockIdx.x / S;
+    const int part = chunk * S + rank, nparts = S * CH;
+    const int b = item / p.hk, h = item - b * p.hk;
 
-    // ---- page prefix over spans (every CTA, redundantly) -------------------------------------
-    if (tid == 0) { s_carry = 0; s_flags[0] = 0; s_flags[1] = 0; s_cu[0] = 0; }
+    if (S > 1) cluster_arrive_relaxed();        // phase 1: "every CTA of the cluster has started"
+
+    const int live = max(0, p.live[(int64_t)b * p.meta_sb + h]);
+    const int npg = (live + kPage - 1) / kPage;
+    const int pq = npg / nparts, prem = npg - pq * nparts;
+    const int pg_begin = part * pq + min(part, prem);
+    const int npages = pq + (part < prem ? 1 : 0);
+
+    if (tid == 0) { s_abort = 0; s_last = 0; }
+    for (int s = tid; s < NS; s += kFastThreads) { mbar_init(&s_full[s], 1); mbar_init(&s_empty[s], 1); }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     __syncthreads();
-    for (int i0 = 0; i0 < items; i0 += kFastThreads) {
-        const int i = i0 + tid;
-        int n = 0;
-        if (i < items) {
-            const int b = i / p.hk, h = i - b * p.hk;
-            n = p.live[(int64_t)b * p.meta_sb + h];
-            if (n < 0) n = 0;
-            s_live[i] = n;
-        }
-        int x = (n + kPage - 1) / kPage;
-#pragma unroll
-        for (int d = 1; d < 32; d <<= 1) {
-            const int y = __shfl_up_sync(0xffffffffu, x, d);
-            if (lane >= d) x += y;
-        }
-        if (lane == 31) s_scan[warp] = x;
-        __syncthreads();
-        int before = s_carry;
-        for (int w = 0; w < warp; ++w) before += s_scan[w];
-        if (i < items) s_cu[i + 1] = before + x;
-        __syncthreads();
-        if (tid == kFastThreads - 1) s_carry = before + x;
-        __syncthreads();
-    }
-    const int NP = s_cu[items];
-    const int ncta = min((int)gridDim.x, NP);
-    const int cta = blockIdx.x;
-
-    // spans without any live row produce zeros (CTA 0)
-    if (cta == 0) {
-        for (int i = 0; i < items; ++i) {
-            if (s_live[i] > 0) continue;
-            const int b = i / p.hk, h = i - b * p.hk;
-            for (int e = tid; e < p.group * D; e += kFastThreads) {
-                const int g = e / D, d = e - g * D;
-                store_from_float(p.out, (int64_t)b * p.out_sb + (int64_t)(h * p.group + g) * p.out_sh + d, p.out_dtype, 0.0f);
-            }
-        }
-    }
-    if (cta >= ncta) return;
-
-    const int pg_begin = (int)(((long long)cta * NP) / ncta);
-    const int pg_end = (int)(((long long)(cta + 1) * NP) / ncta);
-    const int npages = pg_end - pg_begin;
-
-    if (tid == 0) {
-        for (int s = 0; s < NS; ++s) { mbar_init(&s_full[s], 1); mbar_init(&s_empty[s], 1); }
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    }
-    __syncthreads();
-
-    // first span overlapping this slice: largest item with s_cu[item] <= pg_begin
-    int item0;
-    {
-        int lo = 0, hi = items;               // invariant: s_cu[lo] <= pg_begin < s_cu[hi]
-        while (hi - lo > 1) {
-            const int mid = (lo + hi) >> 1;
-            if (s_cu[mid] <= pg_begin) lo = mid; else hi = mid;
-        }
-        item0 = lo;
-    }
+    volatile int* v_abort = &s_abort;
 
     if (warp == kConsumerWarps) {
         // =============================== producer warp =========================================
+        const int32_t* btrow = p.bt ? p.bt + (int64_t)b * p.bt_sb + (int64_t)h * p.bt_sh : nullptr;
+        const int64_t base = p.bt ? 0 : (int64_t)p.base[(int64_t)b * p.meta_sb + h];
         for (int j0 = 0; j0 < npages; j0 += 32) {
             const int j = j0 + lane;
-            if (j < npages && s_flags[0] == 0) {
-                const int gp = pg_begin + j;
-                int lo = item0, hi = items;
-                while (hi - lo > 1) {
-                    const int mid = (lo + hi) >> 1;
-                    if (s_cu[mid] <= gp) lo = mid; else hi = mid;
-                }
-                const int item = lo;
-                const int pi = gp - s_cu[item];
-                const int rows = min(kPage, s_live[item] - pi * kPage);
-                const int b = item / p.hk, h = item - b * p.hk;
-                int64_t row0;
-                if (p.bt) row0 = (int64_t)p.bt[(int64_t)b * p.bt_sb + (int64_t)h * p.bt_sh + pi] * kPage;
-                else row0 = (int64_t)p.base[(int64_t)b * p.meta_sb + h] + (int64_t)pi * kPage;
+            if (j < npages && *v_abort == 0) {
+                const int pi = pg_begin + j;
+                const int rows = min(kPage, live - pi * kPage);
+                const int64_t row0 = btrow ? (int64_t)btrow[pi] * kPage : base + (int64_t)pi * kPage;
                 const int slot = j % NS;
                 bool ok = true;
                 if (j >= NS) ok = mbar_wait(&s_empty[slot], ((j / NS) - 1) & 1, kWaitLimit);
                 if (!ok) {
-                    s_flags[0] = 1;
+                    *v_abort = 1;
                     if (p.dev_status) atomicOr(p.dev_status, FDMS_DEV_WAIT_TIMEOUT);
                 } else if (row0 < 0 || row0 + rows > p.pool_rows) {
-                    // bad address: flag it and complete the stage without copying (zero rows valid)
+                    // bad address: flag it and complete the stage without copying
                     if (p.dev_status) atomicOr(p.dev_status, FDMS_DEV_BAD_INDEX);
                     mbar_arrive(&s_full[slot]);
                 } else {
@@ -283,231 +382,153 @@ __global__ void __launch_bounds__(kFastThreads, (D == 64 ? 2 : 1)) attn_decode_f
             }
             __syncwarp();
         }
+        if (S > 1) {                             // the producer takes part in both cluster phases
+            cluster_wait_acquire();
+            cluster_arrive_release();
+            cluster_wait_acquire();
+        }
         return;
     }
 
     // ================================= consumer warps ===========================================
     const int g = lane >> 2, t = lane & 3;
-    for (int item = item0; item < items && s_cu[item] < pg_end; ++item) {
-        const int it_begin = s_cu[item], it_end = s_cu[item + 1];
-        if (it_begin == it_end) continue;
-        const int seg_begin = max(it_begin, pg_begin), seg_end = min(it_end, pg_end);
-        const int b = item / p.hk, h = item - b * p.hk;
-        const int live = s_live[item];
-        const float sl2 = p.scale * (p.k_scale ? p.k_scale[h] : 1.0f) * kLog2e;
+    const float sl2 = p.scale * (p.k_scale ? p.k_scale[h] : 1.0f) * kLog2e;
+    uint32_t qa[C::kKSteps][2];
+    load_q_frags<D>(p, b, h, g, t, qa);
 
-        // q fragments of head g (rows >= group are zero)
-        uint32_t qa[C::kKSteps][2];
+    float m_run = -INFINITY, l_run = 0.0f;
+    float o[C::kNT][2];
 #pragma unroll
-        for (int ch = 0; ch < C::kCh; ++ch) {
-#pragma unroll
-            for (int s = 0; s < 4; ++s) {
-                float x[4] = {0.f, 0.f, 0.f, 0.f};
-                if (g < p.group) {
-                    const int d0 = 64 * ch + 16 * t + 4 * s;
-#pragma unroll
-                    for (int e = 0; e < 4; ++e) x[e] = load_q_elem(p, b, h * p.group + g, g, d0 + e, D);
-                }
-                qa[4 * ch + s][0] = pack_f16x2(x[0], x[1]);
-                qa[4 * ch + s][1] = pack_f16x2(x[2], x[3]);
-            }
+    for (int j = 0; j < C::kNT; ++j) { o[j][0] = 0.0f; o[j][1] = 0.0f; }
+
+    for (int j = warp; j < npages; j += kConsumerWarps) {
+        const int slot = j % NS;
+        const bool aborted = *v_abort != 0;
+        const bool ok = mbar_wait(&s_full[slot], (j / NS) & 1, aborted ? kWaitLimitDrain : kWaitLimit);
+        if (!ok && !aborted) {
+            *v_abort = 1;
+            if (lane == 0 && p.dev_status) atomicOr(p.dev_status, FDMS_DEV_WAIT_TIMEOUT);
         }
-
-        float m_run = -INFINITY, l_run = 0.0f;
-        float o[C::kNT][2];
-#pragma unroll
-        for (int j = 0; j < C::kNT; ++j) { o[j][0] = 0.0f; o[j][1] = 0.0f; }
-
-        // pages of this segment owned by this warp: local index j = gp - pg_begin, j % 8 == warp
-        int j = seg_begin - pg_begin;
-        j += (warp - (j % kConsumerWarps) + kConsumerWarps) % kConsumerWarps;
-        for (; j < seg_end - pg_begin; j += kConsumerWarps) {
-            const int slot = j % NS;
-            const bool aborted = s_flags[0] != 0;
-            const bool ok = mbar_wait(&s_full[slot], (j / NS) & 1, aborted ? kWaitLimitDrain : kWaitLimit);
-            if (!ok && !aborted) {
-                s_flags[0] = 1;
-                if (lane == 0 && p.dev_status) atomicOr(p.dev_status, FDMS_DEV_WAIT_TIMEOUT);
-            }
-            if (ok && !aborted) {
-                const uint8_t* Ks = s_stage + (size_t)slot * C::kStageBytes;
-                const uint8_t* Vs = Ks + C::kPageBytes;
-                const int pi = pg_begin + j - it_begin;
-                const int rows = min(kPage, live - pi * kPage);
-
-                // ---- S = q K^T for the two 8-token n-tiles ----
-                float sc[2][2];
-#pragma unroll
-                for (int u = 0; u < 2; ++u) {
-                    const int r = tokrow(u, g);
-                    float c0 = 0.0f, c1 = 0.0f;
-                    uint4 kw[C::kCh];
-                    if (C::kCh == 1) {
-                        kw[0] = *(const uint4*)(Ks + r * D + 16 * t);
-                    } else {
-                        // 128-byte rows: odd rows read the upper half first so that the two rows of
-                        // a quarter-warp hit different banks
-                        const int sw = r & 1;
-                        const uint4 a = *(const uint4*)(Ks + r * D + 64 * sw + 16 * t);
-                        const uint4 c = *(const uint4*)(Ks + r * D + 64 * (sw ^ 1) + 16 * t);
-                        kw[0] = sw ? c : a;
-                        kw[C::kCh - 1] = sw ? a : c;
-                    }
-#pragma unroll
-                    for (int ch = 0; ch < C::kCh; ++ch) {
-                        const uint32_t w4[4] = {kw[ch].x, kw[ch].y, kw[ch].z, kw[ch].w};
-#pragma unroll
-                        for (int s = 0; s < 4; ++s) {
-                            const uint32_t b0 = e4m3x2_to_f16x2(w4[s] & 0xffffu);
-                            const uint32_t b1 = e4m3x2_to_f16x2(w4[s] >> 16);
-                            mma_top(c0, c1, qa[4 * ch + s][0], qa[4 * ch + s][1], b0, b1);
-                        }
-                    }
-                    sc[u][0] = c0 * sl2;
-                    sc[u][1] = c1 * sl2;
-                }
-                int rA[2], rB[2];
-#pragma unroll
-                for (int u = 0; u < 2; ++u) { rA[u] = tokrow(u, 2 * t); rB[u] = tokrow(u, 2 * t + 1); }
-                if (rows < kPage) {
-#pragma unroll
-                    for (int u = 0; u < 2; ++u) {
-                        if (rA[u] >= rows) sc[u][0] = -INFINITY;
-                        if (rB[u] >= rows) sc[u][1] = -INFINITY;
-                    }
-                }
-                // ---- online softmax (row = head g, reduce over the 4 lanes of the quad) ----
-                float mx = fmaxf(fmaxf(sc[0][0], sc[0][1]), fmaxf(sc[1][0], sc[1][1]));
-                mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
-                mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
-                const float m_new = fmaxf(m_run, mx);
-                const float alpha = ex2(m_run - m_new);
-                float pr[2][2];
-#pragma unroll
-                for (int u = 0; u < 2; ++u) { pr[u][0] = ex2(sc[u][0] - m_new); pr[u][1] = ex2(sc[u][1] - m_new); }
-                l_run = l_run * alpha + (pr[0][0] + pr[0][1]) + (pr[1][0] + pr[1][1]);
-                m_run = m_new;
-                const uint32_t pa0 = pack_f16x2(pr[0][0], pr[0][1]);
-                const uint32_t pa2 = pack_f16x2(pr[1][0], pr[1][1]);
-#pragma unroll
-                for (int jn = 0; jn < C::kNT; ++jn) { o[jn][0] *= alpha; o[jn][1] *= alpha; }
-
-                // ---- O += P V ----
-#pragma unroll
-                for (int ch = 0; ch < C::kCh; ++ch) {
-                    uint2 va[2], vb[2];
-#pragma unroll
-                    for (int u = 0; u < 2; ++u) {
-                        if (C::kCh == 1) {
-                            va[u] = *(const uint2*)(Vs + rA[u] * D + 8 * g);
-                            vb[u] = *(const uint2*)(Vs + rB[u] * D + 8 * g);
-                        } else {
-                            va[u] = *(const uint2*)(Vs + rA[u] * D + 64 * ch + 8 * g);
-                            vb[u] = *(const uint2*)(Vs + rB[u] * D + 64 * ch + 8 * g);
-                        }
-                        if (rows < kPage) {                   // stale bytes must not reach the MMA
-                            if (rA[u] >= rows) va[u] = make_uint2(0u, 0u);
-                            if (rB[u] >= rows) vb[u] = make_uint2(0u, 0u);
-                        }
-                    }
-                    uint32_t bf[2][8];
-#pragma unroll
-                    for (int u = 0; u < 2; ++u) {
-                        const uint32_t x0 = __byte_perm(va[u].x, vb[u].x, 0x5140);
-                        const uint32_t x1 = __byte_perm(va[u].x, vb[u].x, 0x7362);
-                        const uint32_t y0 = __byte_perm(va[u].y, vb[u].y, 0x5140);
-                        const uint32_t y1 = __byte_perm(va[u].y, vb[u].y, 0x7362);
-                        bf[u][0] = e4m3x2_to_f16x2(x0 & 0xffffu); bf[u][1] = e4m3x2_to_f16x2(x0 >> 16);
-                        bf[u][2] = e4m3x2_to_f16x2(x1 & 0xffffu); bf[u][3] = e4m3x2_to_f16x2(x1 >> 16);
-                        bf[u][4] = e4m3x2_to_f16x2(y0 & 0xffffu); bf[u][5] = e4m3x2_to_f16x2(y0 >> 16);
-                        bf[u][6] = e4m3x2_to_f16x2(y1 & 0xffffu); bf[u][7] = e4m3x2_to_f16x2(y1 >> 16);
-                    }
-#pragma unroll
-                    for (int jj = 0; jj < 8; ++jj)
-                        mma_top(o[8 * ch + jj][0], o[8 * ch + jj][1], pa0, pa2, bf[0][jj], bf[1][jj]);
-                }
-            }
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&s_empty[slot]);
+        if (ok && !aborted) {
+            const uint8_t* Ks = s_stage + (size_t)slot * C::kStageBytes;
+            const int rows = min(kPage, live - (pg_begin + j) * kPage);
+            process_page<D>(Ks, Ks + C::kPageBytes, rows, g, t, sl2, qa, m_run, l_run, o);
         }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&s_empty[slot]);
+    }
 
-        // ---- merge the warps' partial (m, l, O) of this segment ----
-        l_run += __shfl_xor_sync(0xffffffffu, l_run, 1);
-        l_run += __shfl_xor_sync(0xffffffffu, l_run, 2);
-        if (t == 0) { s_m[warp * kMaxGroup + g] = m_run; s_l[warp * kMaxGroup + g] = l_run; }
-        {
-            float* so = s_o + ((size_t)warp * kMaxGroup + g) * D;
+    // ---- merge the warps' partial (m, l, O) ----
+    l_run += __shfl_xor_sync(0xffffffffu, l_run, 1);
+    l_run += __shfl_xor_sync(0xffffffffu, l_run, 2);
+    if (t == 0) { s_m[warp * kMaxGroup + g] = m_run; s_l[warp * kMaxGroup + g] = l_run; }
+    if (g < G) {
+        float* so = s_o + ((size_t)warp * kMaxGroup + g) * D;
 #pragma unroll
-            for (int jn = 0; jn < C::kNT; ++jn) {
-                const int ch = jn >> 3, jj = jn & 7;
-                so[64 * ch + 16 * t + jj] = o[jn][0];
-                so[64 * ch + 16 * t + 8 + jj] = o[jn][1];
-            }
+        for (int jn = 0; jn < C::kNT; ++jn) {
+            const int ch = jn >> 3, jj = jn & 7;
+            so[64 * ch + 16 * t + jj] = o[jn][0];
+            so[64 * ch + 16 * t + 8 + jj] = o[jn][1];
         }
-        consumer_bar();
-        const bool whole = seg_begin == it_begin && seg_end == it_end;
-        const float vs = p.v_scale ? p.v_scale[h] : 1.0f;
-        const int pslot = 2 * cta + (seg_begin == pg_begin ? 0 : 1);
-        for (int e = tid; e < p.group * D; e += kConsumerThreads) {
-            const int gg = e / D, d = e - gg * D;
-            float M = -INFINITY;
+    }
+    consumer_bar();
+    if (S > 1) cluster_wait_acquire();          // phase 1 complete: the leader's shared memory exists
+    const float vs = p.v_scale ? p.v_scale[h] : 1.0f;
+    const uint32_t r_ml0 = S > 1 ? map_to_rank(r_ml, 0) : 0u;
+    const uint32_t r_o0 = S > 1 ? map_to_rank(r_o, 0) : 0u;
+    for (int e = tid; e < G * D; e += kConsumerThreads) {
+        const int gg = e / D, d = e - gg * D;
+        float M = -INFINITY;
 #pragma unroll
-            for (int w = 0; w < kConsumerWarps; ++w) M = fmaxf(M, s_m[w * kMaxGroup + gg]);
-            float acc = 0.0f, L = 0.0f;
+        for (int w = 0; w < kConsumerWarps; ++w) M = fmaxf(M, s_m[w * kMaxGroup + gg]);
+        float acc = 0.0f, Lsum = 0.0f;
+        if (M != -INFINITY) {
 #pragma unroll
             for (int w = 0; w < kConsumerWarps; ++w) {
                 const float f = ex2(s_m[w * kMaxGroup + gg] - M);
                 acc += f * s_o[((size_t)w * kMaxGroup + gg) * D + d];
-                L += f * s_l[w * kMaxGroup + gg];
-            }
-            if (whole) {
-                store_from_float(p.out, (int64_t)b * p.out_sb + (int64_t)(h * p.group + gg) * p.out_sh + d,
-                                 p.out_dtype, acc / L * vs);
-            } else {
-                p.part_o[((size_t)pslot * kMaxGroup + gg) * D + d] = acc;
-                if (d == 0) {
-                    p.part_ml[((size_t)pslot * kMaxGroup + gg) * 2] = M;
-                    p.part_ml[((size_t)pslot * kMaxGroup + gg) * 2 + 1] = L;
-                }
+                Lsum += f * s_l[w * kMaxGroup + gg];
             }
         }
-        if (!whole) {
-            // publish the partial, count arrivals; the last CTA of the span folds all of them
-            __threadfence();
-            consumer_bar();
-            const int c_first = (int)((((long long)it_begin + 1) * ncta - 1) / NP);
-            const int c_last = (int)(((long long)it_end * ncta - 1) / NP);
-            if (tid == 0) {
-                const int prev = atomicAdd(&p.counters[item], 1);
-                const int last = prev == (c_last - c_first);
-                if (last) p.counters[item] = 0;          // leave the workspace ready for the next call
-                s_flags[1] = last;
-            }
-            consumer_bar();
-            if (s_flags[1]) {
-                __threadfence();
-                for (int e = tid; e < p.group * D; e += kConsumerThreads) {
-                    const int gg = e / D, d = e - gg * D;
-                    float M = -INFINITY;
-                    for (int c = c_first; c <= c_last; ++c) {
-                        const int cb = (int)(((long long)c * NP) / ncta);
-                        const int ps = 2 * c + (max(it_begin, cb) == cb ? 0 : 1);
-                        M = fmaxf(M, __ldcg(&p.part_ml[((size_t)ps * kMaxGroup + gg) * 2]));
-                    }
-                    float acc = 0.0f, L = 0.0f;
-                    for (int c = c_first; c <= c_last; ++c) {
-                        const int cb = (int)(((long long)c * NP) / ncta);
-                        const int ps = 2 * c + (max(it_begin, cb) == cb ? 0 : 1);
-                        const float f = ex2(__ldcg(&p.part_ml[((size_t)ps * kMaxGroup + gg) * 2]) - M);
-                        acc += f * __ldcg(&p.part_o[((size_t)ps * kMaxGroup + gg) * D + d]);
-                        L += f * __ldcg(&p.part_ml[((size_t)ps * kMaxGroup + gg) * 2 + 1]);
-                    }
-                    store_from_float(p.out, (int64_t)b * p.out_sb + (int64_t)(h * p.group + gg) * p.out_sh + d,
-                                     p.out_dtype, acc / L * vs);
-                }
+        if (S == 1 && CH == 1) {
+            store_from_float(p.out, (int64_t)b * p.out_sb + (int64_t)(h * G + gg) * p.out_sh + d, p.out_dtype,
+                             Lsum > 0.0f ? acc / Lsum * vs : 0.0f);
+        } else if (S == 1) {
+            r_o[gg * D + d] = acc;
+            if (d == 0) { r_ml[gg * 2] = M; r_ml[gg * 2 + 1] = Lsum; }
+        } else {
+            st_cluster_f32(r_o0 + (uint32_t)(((rank * G + gg) * D + d) * 4), acc);
+            if (d == 0) {
+                st_cluster_f32(r_ml0 + (uint32_t)(((rank * G + gg) * 2) * 4), M);
+                st_cluster_f32(r_ml0 + (uint32_t)(((rank * G + gg) * 2 + 1) * 4), Lsum);
             }
         }
-        consumer_bar();     // merge buffers are reused by the next segment
+    }
+    if (S == 1 && CH == 1) return;
+    if (S > 1) {
+        cluster_arrive_release();               // phase 2: partials are in the leader's shared memory
+        cluster_wait_acquire();
+        if (rank != 0) return;
+    } else {
+        consumer_bar();
+    }
+
+    // ---- cluster leader: fold the S partials ----
+    const int pslot = item * CH + chunk;
+    for (int e = tid; e < G * D; e += kConsumerThreads) {
+        const int gg = e / D, d = e - gg * D;
+        float M = -INFINITY;
+        for (int r = 0; r < S; ++r) M = fmaxf(M, r_ml[(r * G + gg) * 2]);
+        float acc = 0.0f, Lsum = 0.0f;
+        if (M != -INFINITY) {
+            for (int r = 0; r < S; ++r) {
+                const float f = ex2(r_ml[(r * G + gg) * 2] - M);
+                acc += f * r_o[(r * G + gg) * D + d];
+                Lsum += f * r_ml[(r * G + gg) * 2 + 1];
+            }
+        }
+        if (CH == 1) {
+            store_from_float(p.out, (int64_t)b * p.out_sb + (int64_t)(h * G + gg) * p.out_sh + d, p.out_dtype,
+                             Lsum > 0.0f ? acc / Lsum * vs : 0.0f);
+        } else {
+            p.part_o[((size_t)pslot * kMaxGroup + gg) * D + d] = acc;
+            if (d == 0) {
+                p.part_ml[((size_t)pslot * kMaxGroup + gg) * 2] = M;
+                p.part_ml[((size_t)pslot * kMaxGroup + gg) * 2 + 1] = Lsum;
+            }
+        }
+    }
+    if (CH == 1) return;
+
+    // ---- several clusters per span: the last leader to arrive folds the chunk partials ----
+    __threadfence();
+    consumer_bar();
+    if (tid == 0) {
+        const int prev = atomicAdd(&p.counters[item], 1);
+        const int last = prev == CH - 1;
+        if (last) p.counters[item] = 0;          // leave the workspace ready for the next call
+        s_last = last;
+    }
+    consumer_bar();
+    if (*(volatile int*)&s_last) {
+        __threadfence();
+        for (int e = tid; e < G * D; e += kConsumerThreads) {
+            const int gg = e / D, d = e - gg * D;
+            float M = -INFINITY;
+            for (int c = 0; c < CH; ++c)
+                M = fmaxf(M, __ldcg(&p.part_ml[((size_t)(item * CH + c) * kMaxGroup + gg) * 2]));
+            float acc = 0.0f, Lsum = 0.0f;
+            if (M != -INFINITY) {
+                for (int c = 0; c < CH; ++c) {
+                    const size_t ps = (size_t)(item * CH + c) * kMaxGroup + gg;
+                    const float f = ex2(__ldcg(&p.part_ml[ps * 2]) - M);
+                    acc += f * __ldcg(&p.part_o[ps * D + d]);
+                    Lsum += f * __ldcg(&p.part_ml[ps * 2 + 1]);
+                }
+            }
+            store_from_float(p.out, (int64_t)b * p.out_sb + (int64_t)(h * G + gg) * p.out_sh + d, p.out_dtype,
+                             Lsum > 0.0f ? acc / Lsum * vs : 0.0f);
+        }
     }
 }
 
@@ -590,6 +611,8 @@ __global__ void __launch_bounds__(kGenWarps * 32) attn_decode_generic_kernel(Gen
 // ------------------------------------------------------------------------------------------------
 // Host side
 // ------------------------------------------------------------------------------------------------
+constexpr int kMaxPartialSlots = 1024;     // spans * chunks when chunks > 1
+
 struct DeviceInfo { int sms; int smem_optin; bool ok; };
 
 static DeviceInfo device_info() {
@@ -614,12 +637,67 @@ static int env_int(const char* name, int dflt) {
     return atoi(v);
 }
 
-static size_t fast_smem_bytes(int D, int stages, int items) {
+static size_t fast_smem_bytes(int D, int stages, int splits, int group) {
     size_t s = (size_t)stages * 2 * kPage * D;          // ring
     s += (size_t)stages * 2 * sizeof(uint64_t);         // barriers
     s += (size_t)kConsumerWarps * kMaxGroup * (2 + D) * sizeof(float);
-    s += ((size_t)items * 2 + 1 + 2) * sizeof(int);
+    s += (size_t)splits * group * (2 + D) * sizeof(float);
     return s + 128;
+}
+
+template <int D>
+static void fill_launch_config(cudaLaunchConfig_t& cfg, cudaLaunchAttribute* attr, int splits, int chunks, int items,
+                               size_t smem, cudaStream_t stream) {
+    cfg = cudaLaunchConfig_t{};
+    cfg.gridDim = dim3((unsigned)(splits * chunks), (unsigned)items, 1);
+    cfg.blockDim = dim3(kFastThreads, 1, 1);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = (unsigned)splits;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+}
+
+// Whether a cluster of `splits` CTAs with `smem` bytes each can be resident on this device.
+// Asked once per (head_dim, splits, smem) and remembered.
+template <int D>
+static bool cluster_fits(int splits, size_t smem) {
+    static size_t known_smem[kMaxSplits + 1] = {0};
+    static int known[kMaxSplits + 1] = {0};          // 0 unknown, 1 fits, -1 does not
+    if (splits == 1) return true;
+    if (known[splits] != 0 && known_smem[splits] == smem) return known[splits] > 0;
+    auto kern = attn_decode_fast_kernel<D>;
+    bool ok = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) == cudaSuccess;
+    if (ok && splits > 8) ok = cudaFuncSetAttribute(kern, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) == cudaSuccess;
+    if (ok) {
+        cudaLaunchConfig_t cfg;
+        cudaLaunchAttribute attr[1];
+        fill_launch_config<D>(cfg, attr, splits, 1, 1, smem, nullptr);
+        int n = 0;
+        ok = cudaOccupancyMaxActiveClusters(&n, kern, &cfg) == cudaSuccess && n > 0;
+    }
+    cudaGetLastError();                               // a failed query must not poison the next launch check
+    known[splits] = ok ? 1 : -1;
+    known_smem[splits] = smem;
+    return ok;
+}
+
+template <int D>
+static cudaError_t launch_fast(const AttnParams& p, int items, size_t smem, cudaStream_t stream) {
+    auto kern = attn_decode_fast_kernel<D>;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return e;
+    if (p.splits > 8) {
+        e = cudaFuncSetAttribute(kern, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+        if (e != cudaSuccess) return e;
+    }
+    cudaLaunchConfig_t cfg;
+    cudaLaunchAttribute attr[1];
+    fill_launch_config<D>(cfg, attr, p.splits, p.chunks, items, smem, stream);
+    return cudaLaunchKernelEx(&cfg, kern, p);
 }
 
 }  // namespace fdms
@@ -629,8 +707,8 @@ using namespace fdms;
 extern "C" int64_t fdms_attn_decode_workspace_bytes(int32_t batch, int32_t num_kv_heads, int32_t head_dim) {
     if (batch < 0 || num_kv_heads <= 0 || head_dim <= 0) return -1;
     const int64_t counters = (((int64_t)batch * num_kv_heads * 4 + 255) / 256) * 256;
-    const int64_t ml = (int64_t)2 * kMaxGrid * kMaxGroup * 2 * 4;
-    const int64_t po = (int64_t)2 * kMaxGrid * kMaxGroup * head_dim * 4;
+    const int64_t ml = (int64_t)kMaxPartialSlots * kMaxGroup * 2 * 4;
+    const int64_t po = (int64_t)kMaxPartialSlots * kMaxGroup * head_dim * 4;
     return counters + ml + po;
 }
 
@@ -677,50 +755,58 @@ extern "C" int32_t fdms_attn_decode(
     p.rope_pos = q_rope_positions; p.rope_cs = q_rope_cos_sin; p.rope_stride = cos_sin_stride;
     p.counters = nullptr; p.part_ml = nullptr; p.part_o = nullptr;
     p.dev_status = dev_status;
-    p.stages = 0;
+    p.stages = 0; p.splits = 1; p.chunks = 1;
 
     const bool fast = kv_dtype == FDMS_E4M3 && (head_dim == 64 || head_dim == 128) && group <= kMaxGroup &&
-                      ((uintptr_t)k_pool % 16 == 0) && ((uintptr_t)v_pool % 16 == 0) &&
+                      items <= 65535 && ((uintptr_t)k_pool % 16 == 0) && ((uintptr_t)v_pool % 16 == 0) &&
                       env_int("FDMS_ATTN_FORCE_GENERIC", 0) == 0;
     if (fast) {
         const DeviceInfo di = device_info();
         FDMS_REQUIRE(di.ok && di.sms > 0, FDMS_E_CUDA, "fdms_attn_decode: cannot query the device");
-        FDMS_REQUIRE(workspace != nullptr, FDMS_E_WORKSPACE, "fdms_attn_decode: workspace is required");
-        FDMS_REQUIRE((uintptr_t)workspace % 256 == 0, FDMS_E_WORKSPACE, "fdms_attn_decode: workspace must be 256-byte aligned");
-        const int64_t need = fdms_attn_decode_workspace_bytes(batch, num_kv_heads, head_dim);
-        FDMS_REQUIRE(workspace_bytes >= need, FDMS_E_WORKSPACE,
-                     "fdms_attn_decode: workspace of %lld bytes is smaller than the %lld required",
-                     (long long)workspace_bytes, (long long)need);
-        const int64_t counters = (((int64_t)items * 4 + 255) / 256) * 256;
-        p.counters = (int32_t*)workspace;
-        p.part_ml = (float*)((uint8_t*)workspace + counters);
-        p.part_o = p.part_ml + (size_t)2 * kMaxGrid * kMaxGroup * 2;
-
-        int ctas_per_sm = env_int("FDMS_ATTN_CTAS_PER_SM", head_dim == 64 ? 2 : 1);
-        if (ctas_per_sm < 1) ctas_per_sm = 1;
+        const int ctas_per_sm = head_dim == 64 ? 2 : 1;
+        const int target = di.sms * ctas_per_sm;
         int stages = env_int("FDMS_ATTN_STAGES", 32);
         if (stages < 32) stages = 32;
-        // shrink the ring until the requested residency fits
-        const size_t per_sm = (size_t)di.smem_optin;
-        while (ctas_per_sm > 1 && (fast_smem_bytes(head_dim, stages, items) + 1024) * ctas_per_sm > per_sm + 0)
-            --ctas_per_sm;
-        size_t smem = fast_smem_bytes(head_dim, stages, items);
-        FDMS_REQUIRE(smem <= (size_t)di.smem_optin, FDMS_E_CAPACITY,
-                     "fdms_attn_decode: batch*kv_heads=%d needs %zu bytes of shared memory (limit %d)", items, smem,
-                     di.smem_optin);
-        int grid = di.sms * ctas_per_sm;
-        if (grid > kMaxGrid) grid = kMaxGrid;
-        p.stages = stages;
-        cudaError_t e;
-        if (head_dim == 64) {
-            e = cudaFuncSetAttribute(attn_decode_fast_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-            if (e != cudaSuccess) return fail(FDMS_E_CUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
-            attn_decode_fast_kernel<64><<<grid, kFastThreads, smem, (cudaStream_t)stream>>>(p);
-        } else {
-            e = cudaFuncSetAttribute(attn_decode_fast_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-            if (e != cudaSuccess) return fail(FDMS_E_CUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
-            attn_decode_fast_kernel<128><<<grid, kFastThreads, smem, (cudaStream_t)stream>>>(p);
+        // splits: largest power of two that keeps the grid within about one wave
+        int max_splits = env_int("FDMS_ATTN_MAX_SPLITS", 8);
+        if (max_splits > kMaxSplits) max_splits = kMaxSplits;
+        int splits = 1;
+        while (splits * 2 <= max_splits && (int64_t)items * splits * 2 <= target) splits *= 2;
+        const int forced = env_int("FDMS_ATTN_SPLITS", 0);
+        if (forced >= 1 && forced <= kMaxSplits && (forced & (forced - 1)) == 0) splits = forced;
+        while (splits > 1 && (fast_smem_bytes(head_dim, stages, splits, group) > (size_t)di.smem_optin ||
+                              !(head_dim == 64 ? cluster_fits<64>(splits, fast_smem_bytes(head_dim, stages, splits, group))
+                                               : cluster_fits<128>(splits, fast_smem_bytes(head_dim, stages, splits, group)))))
+            splits /= 2;
+        // chunks: more clusters per span when even the largest cluster leaves most SMs idle
+        int chunks = 1;
+        if ((int64_t)items * splits * 2 <= target) {
+            chunks = target / (items * splits);
+            if (chunks > kMaxChunks) chunks = kMaxChunks;
+            while (chunks > 1 && (int64_t)items * chunks > kMaxPartialSlots) --chunks;
         }
+        const int forced_chunks = env_int("FDMS_ATTN_CHUNKS", 0);
+        if (forced_chunks >= 1 && forced_chunks <= kMaxChunks && (int64_t)items * forced_chunks <= kMaxPartialSlots)
+            chunks = forced_chunks;
+        if (chunks > 1) {
+            FDMS_REQUIRE(workspace != nullptr, FDMS_E_WORKSPACE, "fdms_attn_decode: workspace is required");
+            FDMS_REQUIRE((uintptr_t)workspace % 256 == 0, FDMS_E_WORKSPACE, "fdms_attn_decode: workspace must be 256-byte aligned");
+            const int64_t need = fdms_attn_decode_workspace_bytes(batch, num_kv_heads, head_dim);
+            FDMS_REQUIRE(workspace_bytes >= need, FDMS_E_WORKSPACE,
+                         "fdms_attn_decode: workspace of %lld bytes is smaller than the %lld required",
+                         (long long)workspace_bytes, (long long)need);
+            const int64_t counters = (((int64_t)items * 4 + 255) / 256) * 256;
+            p.counters = (int32_t*)workspace;
+            p.part_ml = (float*)((uint8_t*)workspace + counters);
+            p.part_o = p.part_ml + (size_t)kMaxPartialSlots * kMaxGroup * 2;
+        }
+        const size_t smem = fast_smem_bytes(head_dim, stages, splits, group);
+        FDMS_REQUIRE(smem <= (size_t)di.smem_optin, FDMS_E_CAPACITY,
+                     "fdms_attn_decode: %zu bytes of shared memory needed (limit %d)", smem, di.smem_optin);
+        p.stages = stages; p.splits = splits; p.chunks = chunks;
+        const cudaError_t e = head_dim == 64 ? launch_fast<64>(p, items, smem, (cudaStream_t)stream)
+                                             : launch_fast<128>(p, items, smem, (cudaStream_t)stream);
+        if (e != cudaSuccess) return fail(FDMS_E_CUDA, "attn_decode_fast_kernel launch failed: %s", cudaGetErrorString(e));
         FDMS_CHECK_LAUNCH("attn_decode_fast_kernel");
         return FDMS_OK;
     }

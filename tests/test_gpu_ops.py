@@ -247,6 +247,26 @@ def test_attention_config2_shape(dev):
         assert torch.equal(again, out)
 
 
+@pytest.mark.parametrize("splits,chunks", [(1, 1), (2, 1), (8, 1), (16, 1), (1, 3), (4, 5), (8, 64)])
+def test_attention_split_shapes(dev, splits, chunks, monkeypatch):
+    """Every split-K shape (cluster size x clusters per span) gives the same answer, including
+    shapes with more CTAs than pages; repeated calls leave the workspace counters at zero."""
+    from fastdms_b200.layers.compact_attention import compact_decode_attention
+    monkeypatch.setenv("FDMS_ATTN_SPLITS", str(splits))
+    monkeypatch.setenv("FDMS_ATTN_CHUNKS", str(chunks))
+    monkeypatch.setenv("FDMS_ATTN_MAX_SPLITS", "16")
+    rng = np.random.default_rng(40 + splits + chunks)
+    q, kq, vq, base, live, bt, ks, vs = _config2_case(rng, 2, 2, 4, 64, 500, 300, 3, True)
+    live[0, 0] = 5            # fewer pages than CTAs
+    qb = torch.from_numpy(q).to(dev).to(torch.bfloat16)
+    args = (qb, t_fp8(kq, dev), t_fp8(vq, dev), torch.from_numpy(base).to(dev), torch.from_numpy(live).to(dev))
+    kw = dict(block_tables=torch.from_numpy(bt).to(dev), k_scale=torch.from_numpy(ks).to(dev), v_scale=torch.from_numpy(vs).to(dev))
+    want = O.decode_attention(n_bf16(qb), kq, vq, base, live, pool_dtype="e4m3", k_scale=ks, v_scale=vs, block_tables=bt)
+    for _ in range(3):
+        out = compact_decode_attention(*args, **kw)
+        assert np.abs(n_bf16(out) - want).max() < ATTN_TOL
+
+
 def test_attention_edge_lengths(dev):
     """live = 1, exact page multiples, one long span next to tiny ones, and an empty span."""
     from fastdms_b200.layers.compact_attention import compact_decode_attention
