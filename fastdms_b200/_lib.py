@@ -16,6 +16,7 @@ LIB_PATH = Path(__file__).resolve().parent / "libfastdms_b200.so"
 FDMS_OK = 0
 FDMS_E_ARG, FDMS_E_DTYPE, FDMS_E_WORKSPACE, FDMS_E_CUDA, FDMS_E_CAPACITY = -1, -2, -3, -4, -5
 DEV_WAIT_TIMEOUT, DEV_BAD_INDEX = 1, 2
+ATTN_OVERLAP_PREVIOUS = 1
 
 F32, BF16, F16, E4M3 = 0, 1, 2, 3
 _DTYPES = {torch.float32: F32, torch.bfloat16: BF16, torch.float16: F16, torch.float8_e4m3fn: E4M3}
@@ -27,8 +28,8 @@ _SIGNATURES = {
     "fdms_abi_version": (I32, []),
     "fdms_last_error": (c_char_p, []),
     "fdms_attn_decode_workspace_bytes": (I64, [I32, I32, I32]),
-    "fdms_attn_decode": (I32, [P, I32, I64, I64, P, P, I32, I64, P, P, I64, P, I64, I64, P, P,
-                               P, I32, I64, I64, I32, I32, I32, I32, F, P, P, I64, P, I64, P, P]),
+    "fdms_attn_decode": (I32, [P, I32, I64, I64, P, P, I32, I64, P, P, I64, P, I64, I64, I32, P, P,
+                               P, I32, I64, I64, I32, I32, I32, I32, F, P, P, I64, P, I64, I32, P, P]),
     "fdms_store_decode": (I32, [P, I64, I64, P, I64, I64, P, I64, I64, I32, P, I64, P, P, P, I32, I64,
                                 P, I64, P, I64, P, P, I32, I32, I32, I32, DBL, DBL, I32, I32, I32, I32, P, P]),
     "fdms_extract_decisions": (I32, [P, I32, I64, I64, P, I64, I64, I32, I32, I32, DBL, DBL, P]),

@@ -42,8 +42,9 @@ constexpr int kFastThreads = kConsumerThreads + 32;   // + one producer warp
 constexpr int kMaxGroup = 8;
 constexpr int kMaxSplits = 16;           // cluster size limit (8 portable, 16 with the opt-in attribute)
 constexpr int kMaxChunks = 64;           // clusters per span
-constexpr int kWaitLimit = 400000;       // polls of mbarrier.try_wait before giving up
-constexpr int kWaitLimitDrain = 2000;
+constexpr int kWaitHintNs = 20000;       // each mbarrier.try_wait may sleep this long before it reports "not yet"
+constexpr int kWaitLimit = 50000;        // polls before giving up (about a second)
+constexpr int kWaitLimitDrain = 100;
 constexpr float kLog2e = 1.4426950408889634f;
 
 // ------------------------------------------------------------------------------------------------
@@ -64,9 +65,9 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
     uint32_t ok;
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
         "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+        : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity), "r"(kWaitHintNs) : "memory");
     return ok != 0;
 }
 // Bounded wait: false when the limit ran out.
@@ -98,6 +99,11 @@ __device__ __forceinline__ uint32_t map_to_rank(const void* local, uint32_t rank
 __device__ __forceinline__ void st_cluster_f32(uint32_t addr, float v) {
     asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory");
 }
+// Programmatic dependent launch.  `grid_dependency_wait` returns once the preceding kernel of the
+// stream has completed and its writes are visible (immediately when the launch was an ordinary one);
+// `grid_launch_dependents` lets a dependent launch that opted in start its own preamble early.
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ float ex2(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -135,7 +141,7 @@ struct AttnParams {
     const void* q; int q_dtype; int64_t q_sb, q_sh;
     const uint8_t* k_pool; const uint8_t* v_pool; int64_t pool_rows;
     const int32_t* base; const int32_t* live; int64_t meta_sb;
-    const int32_t* bt; int64_t bt_sb, bt_sh;
+    const int32_t* bt; int64_t bt_sb, bt_sh; int bt_pages;
     const float* k_scale; const float* v_scale;
     void* out; int out_dtype; int64_t out_sb, out_sh;
     int batch, hq, hk, group;
@@ -143,7 +149,7 @@ struct AttnParams {
     const int64_t* rope_pos; const float* rope_cs; int64_t rope_stride;
     int32_t* counters; float* part_ml; float* part_o;     // only used when chunks > 1
     int32_t* dev_status;
-    int stages, splits, chunks;
+    int stages, splits, chunks, overlap;
 };
 
 // ------------------------------------------------------------------------------------------------
@@ -339,12 +345,20 @@ __global__ void __launch_bounds__(kFastThreads, (D == 64 ? 2 : 1)) attn_decode_f
     const int b = item / p.hk, h = item - b * p.hk;
 
     if (S > 1) cluster_arrive_relaxed();        // phase 1: "every CTA of the cluster has started"
+    grid_launch_dependents();
 
+    // Pages are dealt round-robin: this CTA owns pages part, part + nparts, ... of the span, so the
+    // producer can fetch its block-table entries before the span length is known.
+    const bool producer = warp == kConsumerWarps;
+    const int32_t* btrow = p.bt ? p.bt + (int64_t)b * p.bt_sb + (int64_t)h * p.bt_sh : nullptr;
+    int32_t bt_first = -1;
+    if (producer && btrow) {
+        const int pi = part + lane * nparts;
+        if (pi < p.bt_pages) bt_first = btrow[pi];
+    }
     const int live = max(0, p.live[(int64_t)b * p.meta_sb + h]);
     const int npg = (live + kPage - 1) / kPage;
-    const int pq = npg / nparts, prem = npg - pq * nparts;
-    const int pg_begin = part * pq + min(part, prem);
-    const int npages = pq + (part < prem ? 1 : 0);
+    const int npages = part < npg ? (npg - part + nparts - 1) / nparts : 0;
 
     if (tid == 0) { s_abort = 0; s_last = 0; }
     for (int s = tid; s < NS; s += kFastThreads) { mbar_init(&s_full[s], 1); mbar_init(&s_empty[s], 1); }
@@ -352,36 +366,47 @@ __global__ void __launch_bounds__(kFastThreads, (D == 64 ? 2 : 1)) attn_decode_f
     __syncthreads();
     volatile int* v_abort = &s_abort;
 
-    if (warp == kConsumerWarps) {
+    if (producer) {
         // =============================== producer warp =========================================
-        const int32_t* btrow = p.bt ? p.bt + (int64_t)b * p.bt_sb + (int64_t)h * p.bt_sh : nullptr;
+        // The span's last page holds the row that the store kernel of this step has just written;
+        // it is fetched only after the dependency on the preceding kernel has been resolved.
         const int64_t base = p.bt ? 0 : (int64_t)p.base[(int64_t)b * p.meta_sb + h];
+        auto issue = [&](int j, int pi, int32_t page_id) {
+            const int rows = min(kPage, live - pi * kPage);
+            const int64_t row0 = btrow ? (int64_t)page_id * kPage : base + (int64_t)pi * kPage;
+            const int slot = j % NS;
+            bool ok = true;
+            if (j >= NS) ok = mbar_wait(&s_empty[slot], ((j / NS) - 1) & 1, kWaitLimit);
+            if (!ok) {
+                *v_abort = 1;
+                if (p.dev_status) atomicOr(p.dev_status, FDMS_DEV_WAIT_TIMEOUT);
+            } else if (row0 < 0 || row0 + rows > p.pool_rows) {
+                // bad address: flag it and complete the stage without copying
+                if (p.dev_status) atomicOr(p.dev_status, FDMS_DEV_BAD_INDEX);
+                mbar_arrive(&s_full[slot]);
+            } else {
+                const uint32_t bytes = (uint32_t)rows * D;
+                uint8_t* dst = s_stage + (size_t)slot * C::kStageBytes;
+                mbar_expect_tx(&s_full[slot], 2 * bytes);
+                bulk_g2s(dst, p.k_pool + row0 * D, bytes, &s_full[slot]);
+                bulk_g2s(dst + C::kPageBytes, p.v_pool + row0 * D, bytes, &s_full[slot]);
+            }
+        };
+        int tail_j = -1;
+        int32_t tail_id = -1;
         for (int j0 = 0; j0 < npages; j0 += 32) {
             const int j = j0 + lane;
+            const int pi = part + j * nparts;
             if (j < npages && *v_abort == 0) {
-                const int pi = pg_begin + j;
-                const int rows = min(kPage, live - pi * kPage);
-                const int64_t row0 = btrow ? (int64_t)btrow[pi] * kPage : base + (int64_t)pi * kPage;
-                const int slot = j % NS;
-                bool ok = true;
-                if (j >= NS) ok = mbar_wait(&s_empty[slot], ((j / NS) - 1) & 1, kWaitLimit);
-                if (!ok) {
-                    *v_abort = 1;
-                    if (p.dev_status) atomicOr(p.dev_status, FDMS_DEV_WAIT_TIMEOUT);
-                } else if (row0 < 0 || row0 + rows > p.pool_rows) {
-                    // bad address: flag it and complete the stage without copying
-                    if (p.dev_status) atomicOr(p.dev_status, FDMS_DEV_BAD_INDEX);
-                    mbar_arrive(&s_full[slot]);
-                } else {
-                    const uint32_t bytes = (uint32_t)rows * D;
-                    uint8_t* dst = s_stage + (size_t)slot * C::kStageBytes;
-                    mbar_expect_tx(&s_full[slot], 2 * bytes);
-                    bulk_g2s(dst, p.k_pool + row0 * D, bytes, &s_full[slot]);
-                    bulk_g2s(dst + C::kPageBytes, p.v_pool + row0 * D, bytes, &s_full[slot]);
-                }
+                const int32_t id = btrow ? (j0 == 0 ? bt_first : btrow[pi]) : 0;
+                if (pi == npg - 1) { tail_j = j; tail_id = id; }       // fetched after the dependency wait
+                else issue(j, pi, id);
             }
             __syncwarp();
         }
+        grid_dependency_wait();
+        if (tail_j >= 0 && *v_abort == 0) issue(tail_j, part + tail_j * nparts, tail_id);
+        __syncwarp();
         if (S > 1) {                             // the producer takes part in both cluster phases
             cluster_wait_acquire();
             cluster_arrive_release();
@@ -393,6 +418,7 @@ __global__ void __launch_bounds__(kFastThreads, (D == 64 ? 2 : 1)) attn_decode_f
     // ================================= consumer warps ===========================================
     const int g = lane >> 2, t = lane & 3;
     const float sl2 = p.scale * (p.k_scale ? p.k_scale[h] : 1.0f) * kLog2e;
+    grid_dependency_wait();                      // q is written by the preceding kernel (RoPE in place)
     uint32_t qa[C::kKSteps][2];
     load_q_frags<D>(p, b, h, g, t, qa);
 
@@ -411,7 +437,7 @@ __global__ void __launch_bounds__(kFastThreads, (D == 64 ? 2 : 1)) attn_decode_f
         }
         if (ok && !aborted) {
             const uint8_t* Ks = s_stage + (size_t)slot * C::kStageBytes;
-            const int rows = min(kPage, live - (pg_begin + j) * kPage);
+            const int rows = min(kPage, live - (part + j * nparts) * kPage);
             process_page<D>(Ks, Ks + C::kPageBytes, rows, g, t, sl2, qa, m_run, l_run, o);
         }
         __syncwarp();
@@ -647,7 +673,7 @@ static size_t fast_smem_bytes(int D, int stages, int splits, int group) {
 
 template <int D>
 static void fill_launch_config(cudaLaunchConfig_t& cfg, cudaLaunchAttribute* attr, int splits, int chunks, int items,
-                               size_t smem, cudaStream_t stream) {
+                               size_t smem, cudaStream_t stream, bool overlap = false) {
     cfg = cudaLaunchConfig_t{};
     cfg.gridDim = dim3((unsigned)(splits * chunks), (unsigned)items, 1);
     cfg.blockDim = dim3(kFastThreads, 1, 1);
@@ -659,6 +685,11 @@ static void fill_launch_config(cudaLaunchConfig_t& cfg, cudaLaunchAttribute* att
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
+    if (overlap) {
+        attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[1].val.programmaticStreamSerializationAllowed = 1;
+        cfg.numAttrs = 2;
+    }
 }
 
 // Whether a cluster of `splits` CTAs with `smem` bytes each can be resident on this device.
@@ -674,7 +705,7 @@ static bool cluster_fits(int splits, size_t smem) {
     if (ok && splits > 8) ok = cudaFuncSetAttribute(kern, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) == cudaSuccess;
     if (ok) {
         cudaLaunchConfig_t cfg;
-        cudaLaunchAttribute attr[1];
+        cudaLaunchAttribute attr[2];
         fill_launch_config<D>(cfg, attr, splits, 1, 1, smem, nullptr);
         int n = 0;
         ok = cudaOccupancyMaxActiveClusters(&n, kern, &cfg) == cudaSuccess && n > 0;
@@ -695,8 +726,8 @@ static cudaError_t launch_fast(const AttnParams& p, int items, size_t smem, cuda
         if (e != cudaSuccess) return e;
     }
     cudaLaunchConfig_t cfg;
-    cudaLaunchAttribute attr[1];
-    fill_launch_config<D>(cfg, attr, p.splits, p.chunks, items, smem, stream);
+    cudaLaunchAttribute attr[2];
+    fill_launch_config<D>(cfg, attr, p.splits, p.chunks, items, smem, stream, p.overlap != 0);
     return cudaLaunchKernelEx(&cfg, kern, p);
 }
 
@@ -716,15 +747,16 @@ extern "C" int32_t fdms_attn_decode(
     const void* q, int32_t q_dtype, int64_t q_stride_b, int64_t q_stride_h,
     const void* k_pool, const void* v_pool, int32_t kv_dtype, int64_t pool_rows,
     const int32_t* base_offsets, const int32_t* live_counts, int64_t meta_stride_b,
-    const int32_t* block_tables, int64_t bt_stride_b, int64_t bt_stride_h,
+    const int32_t* block_tables, int64_t bt_stride_b, int64_t bt_stride_h, int32_t bt_max_pages,
     const float* k_scale, const float* v_scale,
     void* out, int32_t out_dtype, int64_t out_stride_b, int64_t out_stride_h,
     int32_t batch, int32_t num_q_heads, int32_t num_kv_heads, int32_t head_dim, float scale,
     const int64_t* q_rope_positions, const float* q_rope_cos_sin, int64_t cos_sin_stride,
-    void* workspace, int64_t workspace_bytes, int32_t* dev_status, void* stream) {
+    void* workspace, int64_t workspace_bytes, int32_t flags, int32_t* dev_status, void* stream) {
     clear_error();
     FDMS_REQUIRE(q && k_pool && v_pool && live_counts && out, FDMS_E_ARG, "fdms_attn_decode: null pointer");
     FDMS_REQUIRE(base_offsets || block_tables, FDMS_E_ARG, "fdms_attn_decode: base_offsets or block_tables required");
+    FDMS_REQUIRE(!block_tables || bt_max_pages > 0, FDMS_E_ARG, "fdms_attn_decode: bt_max_pages must be positive");
     FDMS_REQUIRE(batch >= 0 && num_q_heads > 0 && num_kv_heads > 0 && head_dim > 0, FDMS_E_ARG,
                  "fdms_attn_decode: bad sizes");
     FDMS_REQUIRE(num_q_heads % num_kv_heads == 0, FDMS_E_ARG, "q_heads=%d must be divisible by kv_heads=%d",
@@ -747,7 +779,7 @@ extern "C" int32_t fdms_attn_decode(
     p.q = q; p.q_dtype = q_dtype; p.q_sb = q_stride_b; p.q_sh = q_stride_h;
     p.k_pool = (const uint8_t*)k_pool; p.v_pool = (const uint8_t*)v_pool; p.pool_rows = pool_rows;
     p.base = base_offsets; p.live = live_counts; p.meta_sb = meta_stride_b;
-    p.bt = block_tables; p.bt_sb = bt_stride_b; p.bt_sh = bt_stride_h;
+    p.bt = block_tables; p.bt_sb = bt_stride_b; p.bt_sh = bt_stride_h; p.bt_pages = bt_max_pages;
     p.k_scale = k_scale; p.v_scale = v_scale;
     p.out = out; p.out_dtype = out_dtype; p.out_sb = out_stride_b; p.out_sh = out_stride_h;
     p.batch = batch; p.hq = num_q_heads; p.hk = num_kv_heads; p.group = group;
@@ -755,7 +787,7 @@ extern "C" int32_t fdms_attn_decode(
     p.rope_pos = q_rope_positions; p.rope_cs = q_rope_cos_sin; p.rope_stride = cos_sin_stride;
     p.counters = nullptr; p.part_ml = nullptr; p.part_o = nullptr;
     p.dev_status = dev_status;
-    p.stages = 0; p.splits = 1; p.chunks = 1;
+    p.stages = 0; p.splits = 1; p.chunks = 1; p.overlap = (flags & FDMS_ATTN_OVERLAP_PREVIOUS) ? 1 : 0;
 
     const bool fast = kv_dtype == FDMS_E4M3 && (head_dim == 64 || head_dim == 128) && group <= kMaxGroup &&
                       items <= 65535 && ((uintptr_t)k_pool % 16 == 0) && ((uintptr_t)v_pool % 16 == 0) &&

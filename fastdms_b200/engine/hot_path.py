@@ -28,7 +28,7 @@ class DecodeHotPath:
     def __init__(self, manager: CompactKVManager, seqs: list, *, num_q_heads: int, window_size: int,
                  alpha_scale: float, alpha_offset: float, cos_sin_cache: torch.Tensor,
                  act_dtype: torch.dtype = torch.bfloat16, scale: float | None = None,
-                 expire_every_step: bool = True, use_cuda_graph: bool = True):
+                 expire_every_step: bool = True, use_cuda_graph: bool = True, overlap: bool = True):
         self.m = manager
         self.seqs = list(seqs)
         self.states = manager._states(self.seqs)
@@ -40,6 +40,7 @@ class DecodeHotPath:
         self.alpha_scale, self.alpha_offset = float(alpha_scale), float(alpha_offset)
         self.scale = scale
         self.expire_every_step = expire_every_step
+        self.overlap = overlap      # attention may start while the layer's store kernel still runs
         self.cos_sin_cache = cos_sin_cache.to(device=dev, dtype=torch.float32).contiguous()
         self.slots_t = manager._slots_tensor(self.states)
         # device-resident step state
@@ -77,7 +78,7 @@ class DecodeHotPath:
             compact_decode_attention(
                 self.q[l], ck, cv, self.base[l], self.live[l], scale=self.scale,
                 block_tables=None if self.block_tables is None else self.block_tables[l],
-                k_scale=ks, v_scale=vs, out=self.out[l])
+                k_scale=ks, v_scale=vs, out=self.out[l], overlap_previous_kernel=self.overlap)
         m.record_device(self.slots_t, self.positions, self.evict_all)
         self.positions.add_(1)
 

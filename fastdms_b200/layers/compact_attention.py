@@ -74,12 +74,16 @@ def compact_decode_attention(
     k_scale: torch.Tensor | None = None,
     v_scale: torch.Tensor | None = None,
     out: torch.Tensor | None = None,
+    overlap_previous_kernel: bool = False,
 ) -> torch.Tensor:
     """Decode attention over compact K/V spans (reference: compact_attention.py:1116-1336).
 
     q [batch, q_heads, head_dim]; compact_k/compact_v [slots, head_dim]; base_offsets/live_counts
     [batch, kv_heads]; q head hq reads the span of KV head hq // group.  `max_live_count`,
     `block_n` and `grouped` are accepted for signature compatibility and do not change the result.
+    `overlap_previous_kernel=True` lets the launch start while the preceding kernel of the stream
+    still runs; only valid when that kernel writes nothing this call reads except q and the last
+    live row of each span (the decode step's store kernel), see FDMS_ATTN_OVERLAP_PREVIOUS.
     """
     if q.ndim != 3:
         raise ValueError(f"expected q as [batch, q_heads, head_dim], got {q.shape}")
@@ -122,14 +126,14 @@ def compact_decode_attention(
     if base_offsets.stride(1) != 1 or live_counts.stride(1) != 1 or base_offsets.stride(0) != live_counts.stride(0):
         base_offsets = base_offsets.contiguous()
         live_counts = live_counts.contiguous()
-    bt_sb = bt_sh = 0
+    bt_sb = bt_sh = bt_pages = 0
     if block_tables is not None:
         if block_tables.ndim != 3 or block_tables.shape[:2] != (batch, num_kv_heads):
             raise ValueError(f"expected block_tables [batch, kv_heads, pages], got {tuple(block_tables.shape)}")
         block_tables = block_tables.to(device=dev, dtype=torch.int32)
         if block_tables.stride(2) != 1:
             block_tables = block_tables.contiguous()
-        bt_sb, bt_sh = block_tables.stride(0), block_tables.stride(1)
+        bt_sb, bt_sh, bt_pages = block_tables.stride(0), block_tables.stride(1), block_tables.shape[2]
     k_scale, v_scale = _scales(k_scale, v_scale, num_kv_heads, dev)
     if out is None:
         out = torch.empty_like(q)
@@ -152,12 +156,13 @@ def compact_decode_attention(
             q.data_ptr(), _lib.dtype_code(q.dtype), q.stride(0), q.stride(1),
             compact_k.data_ptr(), compact_v.data_ptr(), _lib.dtype_code(compact_k.dtype), compact_k.shape[0],
             base_offsets.data_ptr(), live_counts.data_ptr(), live_counts.stride(0),
-            _lib.ptr(block_tables), bt_sb, bt_sh,
+            _lib.ptr(block_tables), bt_sb, bt_sh, bt_pages,
             _lib.ptr(k_scale), _lib.ptr(v_scale),
             out.data_ptr(), _lib.dtype_code(out.dtype), out.stride(0), out.stride(1),
             batch, num_q_heads, num_kv_heads, head_dim, float(scale),
             _lib.ptr(rope_pos), _lib.ptr(rope_cs), cs_stride,
-            ws.data_ptr(), ws.numel(), status.data_ptr(), _lib.stream_ptr(dev))
+            ws.data_ptr(), ws.numel(), _lib.ATTN_OVERLAP_PREVIOUS if overlap_previous_kernel else 0,
+            status.data_ptr(), _lib.stream_ptr(dev))
     _lib.check(rc)
     return out
 

@@ -65,22 +65,30 @@ const char* fdms_last_error(void);
  * Optional inline neox RoPE of q at q_rope_positions[b] (int64) with the decision lane
  * (first head of each group, channel head_dim-1) zeroed first; cos_sin rows are
  * [cos(head_dim/2) | sin(head_dim/2)] float32 with row stride cos_sin_stride.
+ * block_tables: optional int32 [batch, kv_heads, bt_max_pages] (element strides given).
  * workspace: fdms_attn_decode_workspace_bytes(...) bytes, 256-byte aligned.  Its first
  * `batch*kv_heads` int32 must be zero before the FIRST call; every call leaves them zero again.
  * Calls that share a workspace must not overlap on the GPU.
+ * flags: FDMS_ATTN_OVERLAP_PREVIOUS lets the launch begin while the preceding kernel of the stream
+ * is still running (programmatic dependent launch).  The caller then promises that the preceding
+ * kernel writes none of: live_counts, base_offsets, block_tables, scales, and pool rows other than
+ * the LAST live row of each span.  q, that last row and every output are only touched after the
+ * preceding kernel has completed.  This is the situation of a decode step, where the preceding
+ * kernel is fdms_store_decode of the same layer.
  * --------------------------------------------------------------------------------------------- */
+#define FDMS_ATTN_OVERLAP_PREVIOUS 1
 int64_t fdms_attn_decode_workspace_bytes(int32_t batch, int32_t num_kv_heads, int32_t head_dim);
 
 int32_t fdms_attn_decode(
     const void* q, int32_t q_dtype, int64_t q_stride_b, int64_t q_stride_h,
     const void* k_pool, const void* v_pool, int32_t kv_dtype, int64_t pool_rows,
     const int32_t* base_offsets, const int32_t* live_counts, int64_t meta_stride_b,
-    const int32_t* block_tables, int64_t bt_stride_b, int64_t bt_stride_h,
+    const int32_t* block_tables, int64_t bt_stride_b, int64_t bt_stride_h, int32_t bt_max_pages,
     const float* k_scale, const float* v_scale,
     void* out, int32_t out_dtype, int64_t out_stride_b, int64_t out_stride_h,
     int32_t batch, int32_t num_q_heads, int32_t num_kv_heads, int32_t head_dim, float scale,
     const int64_t* q_rope_positions, const float* q_rope_cos_sin, int64_t cos_sin_stride,
-    void* workspace, int64_t workspace_bytes, int32_t* dev_status, void* stream);
+    void* workspace, int64_t workspace_bytes, int32_t flags, int32_t* dev_status, void* stream);
 
 /* ---------------------------------------------------------------------------------------------
  * (b)+(d) fused decode preprocess: DMS decision + RoPE + FP8 quantise + append store.
