@@ -75,28 +75,28 @@ __global__ void __launch_bounds__(kExpiryThreads) expire_compact_kernel(ExpiryPa
 
     int new_live = active ? 0 : old_live;
     if (active) {
-        // mode 1: only the first expired slot is dropped; find it first.
-        int first = INT_MAX;
-        if (p.mode == 1) {
-            if (tid == 0) s_first = INT_MAX;
-            __syncthreads();
-            for (int t0 = 0; t0 < live; t0 += kExpiryThreads) {
-                const int i = t0 + tid;
-                bool expired = false;
-                if (i < live) expired = ev[i] != 0 && (long long)pos[i] < cur - p.window;
-                const unsigned any = __ballot_sync(0xffffffffu, expired);
-                if (any && (tid & 31) == 0) atomicMin(&s_first, t0 + (tid & ~31) + __ffs(any) - 1);
-                __syncthreads();
-                if (s_first != INT_MAX) break;
-            }
-            first = s_first;
+        // Pre-pass without block-wide scans: index of the first slot that gets dropped
+        // (evict-marked and out of the window).  Everything before it stays where it is, so the
+        // compaction sweep can start at that slot's tile; in steady-state decode that is the last
+        // tile or two of the span, and a span with nothing to drop costs only this pass.
+        if (tid == 0) s_first = INT_MAX;
+        __syncthreads();
+        for (int t0 = 0; t0 < live; t0 += kExpiryThreads) {
+            const int i = t0 + tid;
+            bool expired = false;
+            if (i < live) expired = ev[i] != 0 && (long long)pos[i] < cur - p.window;
+            const unsigned any = __ballot_sync(0xffffffffu, expired);
+            if (any && (tid & 31) == 0) atomicMin(&s_first, t0 + (tid & ~31) + __ffs(any) - 1);
         }
+        __syncthreads();
+        const int first = s_first;
+        const int t_start = first == INT_MAX ? live : (first / kExpiryThreads) * kExpiryThreads;
 
         uint8_t* kp = p.k_pool + (int64_t)l * p.pool_layer_bytes;
         uint8_t* vp = p.v_pool + (int64_t)l * p.pool_layer_bytes;
         const int chunks = p.row_bytes / (int)sizeof(VecT);
-        int run = 0;
-        for (int t0 = 0; t0 < live; t0 += kExpiryThreads) {
+        int run = min(t_start, live);
+        for (int t0 = t_start; t0 < live; t0 += kExpiryThreads) {
             const int i = t0 + tid;
             const bool valid = i < live;
             int my_pos = -1;

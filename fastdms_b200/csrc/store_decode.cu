@@ -43,6 +43,11 @@ struct StoreParams {
     int32_t* dev_status;
 };
 
+// Latency matters more than bandwidth here (a few KB per launch), so the kernel is written as two
+// dependent rounds of global loads: [positions, slot, every q/k/v element this lane owns] and then
+// [cos/sin of the position]; everything is in registers before the first store.
+// NP = pairs (i, i + half) per lane, i.e. head_dim <= 64 * NP; MAXG = q heads per KV head.
+template <int NP, int MAXG>
 __global__ void store_decode_kernel(StoreParams p) {
     const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     const int lane = threadIdx.x & 31;
@@ -54,68 +59,85 @@ __global__ void store_decode_kernel(StoreParams p) {
     const int adt = p.act_dtype;
 
     const int64_t q0 = (int64_t)b * p.q_sb + (int64_t)(h * group) * p.q_sh;
-    if (p.do_decision) {
-        const float dv = load_as_float(p.q, q0 + p.dim - 1, adt);
-        __syncwarp();
-        if (lane == 0) {
-            if (p.evict) p.evict[(int64_t)b * p.evict_sb + h] = p.rule.evict(dv) ? 1 : 0;
-            // Without RoPE write-back the lane is cleared in place (plain extraction); with
-            // store_q the cleared value flows through the rotation below.
-            if (!p.do_rope) store_from_float(p.q, q0 + p.dim - 1, adt, 0.0f);
-        }
-    }
+    const int64_t k0 = (int64_t)b * p.k_sb + (int64_t)h * p.k_sh;
+    const int64_t v0 = (int64_t)b * p.v_sb + (int64_t)h * p.v_sh;
+    const bool rot_q = p.do_rope && p.store_q;
 
-    const float* cs = nullptr;
-    if (p.do_rope) cs = p.cos_sin + p.positions[b] * p.cs_stride;
-
-    if (p.do_rope && p.store_q) {
-        for (int g = 0; g < group; ++g) {
-            const int64_t qo = q0 + (int64_t)g * p.q_sh;
-            for (int i = lane; i < half; i += 32) {
-                const float c = cs[i], s = cs[half + i];
-                const float x1 = load_as_float(p.q, qo + i, adt);
-                float x2 = load_as_float(p.q, qo + half + i, adt);
-                if (p.do_decision && g == 0 && i == half - 1) x2 = 0.0f;
-                const float y1 = __fsub_rn(__fmul_rn(x1, c), __fmul_rn(x2, s));
-                const float y2 = __fadd_rn(__fmul_rn(x2, c), __fmul_rn(x1, s));
-                store_from_float(p.q, qo + i, adt, y1);
-                store_from_float(p.q, qo + half + i, adt, y2);
-            }
-        }
-    }
-
+    // ---- round 1: independent loads ----
+    const int64_t pos = p.do_rope ? p.positions[b] : 0;
     const int32_t slot = p.slot ? p.slot[(int64_t)b * p.slot_sb + h] : -1;
+    const float dv = p.do_decision ? load_as_float(p.q, q0 + p.dim - 1, adt) : 0.0f;
+    const float ks = p.k_scale ? p.k_scale[h] : 1.0f;
+    const float vs = p.v_scale ? p.v_scale[h] : 1.0f;
+    float kx[NP][2], vx[NP][2], qx[MAXG][NP][2];
+#pragma unroll
+    for (int n = 0; n < NP; ++n) {
+        const int i = lane + 32 * n;
+        const bool in = i < half;
+        kx[n][0] = in ? load_as_float(p.k, k0 + i, adt) : 0.0f;
+        kx[n][1] = in ? load_as_float(p.k, k0 + half + i, adt) : 0.0f;
+        vx[n][0] = in ? load_as_float(p.v, v0 + i, adt) : 0.0f;
+        vx[n][1] = in ? load_as_float(p.v, v0 + half + i, adt) : 0.0f;
+#pragma unroll
+        for (int g = 0; g < MAXG; ++g) {
+            const bool qin = in && rot_q && g < group;
+            qx[g][n][0] = qin ? load_as_float(p.q, q0 + (int64_t)g * p.q_sh + i, adt) : 0.0f;
+            qx[g][n][1] = qin ? load_as_float(p.q, q0 + (int64_t)g * p.q_sh + half + i, adt) : 0.0f;
+        }
+    }
+    // ---- round 2: cos / sin of this sequence's position ----
+    float cs[NP][2];
+#pragma unroll
+    for (int n = 0; n < NP; ++n) {
+        const int i = lane + 32 * n;
+        const bool in = p.do_rope && i < half;
+        cs[n][0] = in ? p.cos_sin[pos * p.cs_stride + i] : 1.0f;
+        cs[n][1] = in ? p.cos_sin[pos * p.cs_stride + half + i] : 0.0f;
+    }
+
+    if (p.do_decision && lane == 0) {
+        if (p.evict) p.evict[(int64_t)b * p.evict_sb + h] = p.rule.evict(dv) ? 1 : 0;
+        // Without RoPE write-back of q the lane is cleared in place only for plain extraction.
+        if (!p.do_rope) store_from_float(p.q, q0 + p.dim - 1, adt, 0.0f);
+    }
     bool do_store = slot >= 0;
     if (do_store && (int64_t)slot >= p.pool_rows) {
         if (lane == 0 && p.dev_status) atomicOr(p.dev_status, FDMS_DEV_BAD_INDEX);
         do_store = false;
     }
-    const float ks = p.k_scale ? p.k_scale[h] : 1.0f;
-    const float vs = p.v_scale ? p.v_scale[h] : 1.0f;
-    const int64_t k0 = (int64_t)b * p.k_sb + (int64_t)h * p.k_sh;
-    const int64_t v0 = (int64_t)b * p.v_sb + (int64_t)h * p.v_sh;
     const int64_t row = (int64_t)slot * p.dim;
-    for (int i = lane; i < half; i += 32) {
-        const float x1 = load_as_float(p.k, k0 + i, adt);
-        const float x2 = load_as_float(p.k, k0 + half + i, adt);
-        float y1 = x1, y2 = x2;
+#pragma unroll
+    for (int n = 0; n < NP; ++n) {
+        const int i = lane + 32 * n;
+        if (i >= half) continue;
+        const float c = cs[n][0], sn = cs[n][1];
+        if (rot_q) {
+#pragma unroll
+            for (int g = 0; g < MAXG; ++g) {
+                if (g >= group) break;
+                const float x1 = qx[g][n][0];
+                float x2 = qx[g][n][1];
+                if (p.do_decision && g == 0 && i == half - 1) x2 = 0.0f;     // the borrowed decision channel
+                const int64_t qo = q0 + (int64_t)g * p.q_sh;
+                store_from_float(p.q, qo + i, adt, __fsub_rn(__fmul_rn(x1, c), __fmul_rn(x2, sn)));
+                store_from_float(p.q, qo + half + i, adt, __fadd_rn(__fmul_rn(x2, c), __fmul_rn(x1, sn)));
+            }
+        }
+        float y1 = kx[n][0], y2 = kx[n][1];
         if (p.do_rope) {
-            const float c = cs[i], s = cs[half + i];
-            y1 = round_to_dtype(__fsub_rn(__fmul_rn(x1, c), __fmul_rn(x2, s)), adt);
-            y2 = round_to_dtype(__fadd_rn(__fmul_rn(x2, c), __fmul_rn(x1, s)), adt);
+            y1 = round_to_dtype(__fsub_rn(__fmul_rn(kx[n][0], c), __fmul_rn(kx[n][1], sn)), adt);
+            y2 = round_to_dtype(__fadd_rn(__fmul_rn(kx[n][1], c), __fmul_rn(kx[n][0], sn)), adt);
             if (p.store_k) {
                 store_from_float(p.k, k0 + i, adt, y1);
                 store_from_float(p.k, k0 + half + i, adt, y2);
             }
         }
         if (do_store) {
-            const float w1 = load_as_float(p.v, v0 + i, adt);
-            const float w2 = load_as_float(p.v, v0 + half + i, adt);
             if (p.k_scale) { y1 = __fdiv_rn(y1, ks); y2 = __fdiv_rn(y2, ks); }
             store_from_float(p.k_pool, row + i, p.kv_dtype, y1);
             store_from_float(p.k_pool, row + half + i, p.kv_dtype, y2);
-            store_from_float(p.v_pool, row + i, p.kv_dtype, p.v_scale ? __fdiv_rn(w1, vs) : w1);
-            store_from_float(p.v_pool, row + half + i, p.kv_dtype, p.v_scale ? __fdiv_rn(w2, vs) : w2);
+            store_from_float(p.v_pool, row + i, p.kv_dtype, p.v_scale ? __fdiv_rn(vx[n][0], vs) : vx[n][0]);
+            store_from_float(p.v_pool, row + half + i, p.kv_dtype, p.v_scale ? __fdiv_rn(vx[n][1], vs) : vx[n][1]);
         }
     }
 }
@@ -188,7 +210,16 @@ extern "C" int32_t fdms_store_decode(
     const int warps = batch * num_kv_heads;
     const int threads = 128;
     const int blocks = (warps * 32 + threads - 1) / threads;
-    store_decode_kernel<<<blocks, threads, 0, (cudaStream_t)stream>>>(p);
+    const int group = num_q_heads / num_kv_heads;
+    FDMS_REQUIRE(head_dim <= 256, FDMS_E_CAPACITY, "head_dim=%d is above the fused decode preprocess kernel limit", head_dim);
+    FDMS_REQUIRE(group <= 16 || !(do_rope && store_q), FDMS_E_CAPACITY,
+                 "group_size=%d is above the fused decode preprocess limit of 16", group);
+    if (head_dim <= 128 && group <= 4)
+        store_decode_kernel<2, 4><<<blocks, threads, 0, (cudaStream_t)stream>>>(p);
+    else if (head_dim <= 128 && group <= 8)
+        store_decode_kernel<2, 8><<<blocks, threads, 0, (cudaStream_t)stream>>>(p);
+    else
+        store_decode_kernel<4, 16><<<blocks, threads, 0, (cudaStream_t)stream>>>(p);
     FDMS_CHECK_LAUNCH("store_decode_kernel");
     return FDMS_OK;
 }
