@@ -1,0 +1,104 @@
+"""Tensor-parallel linear layers (bf16/fp32 weights, torch GEMMs).
+
+Same class names, parameter layout and `weight_loader` protocol as the reference's
+`fastdms/layers/linear.py` (:946-1048), so checkpoints load the same way: QKV and gate/up are
+packed column-parallel weights, o_proj/down_proj are row-parallel and all-reduce their output over
+the tensor-parallel group (NCCL).  The reference's opt-in FP8/int4 weight paths are not part of the
+compact-DMS decode path and are not provided.
+"""
+from __future__ import annotations
+
+import torch
+import torch.distributed as dist
+import torch.nn.functional as F
+from torch import nn
+
+
+def tp_world() -> tuple[int, int]:
+    if dist.is_available() and dist.is_initialized():
+        return dist.get_world_size(), dist.get_rank()
+    return 1, 0
+
+
+def divide(a: int, b: int) -> int:
+    assert a % b == 0, f"{a} is not divisible by {b}"
+    return a // b
+
+
+class LinearBase(nn.Module):
+    def __init__(self, input_size: int, output_size: int, bias: bool = False, tp_dim: int | None = None):
+        super().__init__()
+        self.tp_dim = tp_dim
+        self.tp_size, self.tp_rank = tp_world()
+        self.weight = nn.Parameter(torch.empty(output_size, input_size))
+        self.weight.weight_loader = self.weight_loader
+        if bias:
+            self.bias = nn.Parameter(torch.empty(output_size))
+            self.bias.weight_loader = self.weight_loader
+        else:
+            self.register_parameter("bias", None)
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        return F.linear(x, self.weight, self.bias)
+
+
+class ReplicatedLinear(LinearBase):
+    def weight_loader(self, param: nn.Parameter, loaded_weight: torch.Tensor):
+        param.data.copy_(loaded_weight)
+
+
+class ColumnParallelLinear(LinearBase):
+    def __init__(self, input_size: int, output_size: int, bias: bool = False):
+        tp_size, _ = tp_world()
+        super().__init__(input_size, divide(output_size, tp_size), bias, 0)
+
+    def weight_loader(self, param: nn.Parameter, loaded_weight: torch.Tensor):
+        shard = param.data.size(0)
+        param.data.copy_(loaded_weight.narrow(0, self.tp_rank * shard, shard))
+
+
+class MergedColumnParallelLinear(ColumnParallelLinear):
+    def __init__(self, input_size: int, output_sizes: list[int], bias: bool = False):
+        self.output_sizes = output_sizes
+        super().__init__(input_size, sum(output_sizes), bias)
+
+    def weight_loader(self, param: nn.Parameter, loaded_weight: torch.Tensor, loaded_shard_id: int):
+        offset = sum(self.output_sizes[:loaded_shard_id]) // self.tp_size
+        size = self.output_sizes[loaded_shard_id] // self.tp_size
+        param.data.narrow(0, offset, size).copy_(loaded_weight.chunk(self.tp_size, 0)[self.tp_rank])
+
+
+class QKVParallelLinear(ColumnParallelLinear):
+    def __init__(self, hidden_size: int, head_size: int, total_num_heads: int,
+                 total_num_kv_heads: int | None = None, bias: bool = False):
+        tp_size, _ = tp_world()
+        total_num_kv_heads = total_num_kv_heads or total_num_heads
+        self.head_size = head_size
+        self.num_heads = divide(total_num_heads, tp_size)
+        self.num_kv_heads = divide(total_num_kv_heads, tp_size)
+        super().__init__(hidden_size, (total_num_heads + 2 * total_num_kv_heads) * head_size, bias)
+
+    def weight_loader(self, param: nn.Parameter, loaded_weight: torch.Tensor, loaded_shard_id: str):
+        assert loaded_shard_id in ("q", "k", "v")
+        qs, ks = self.num_heads * self.head_size, self.num_kv_heads * self.head_size
+        offset, size = {"q": (0, qs), "k": (qs, ks), "v": (qs + ks, ks)}[loaded_shard_id]
+        param.data.narrow(0, offset, size).copy_(loaded_weight.chunk(self.tp_size, 0)[self.tp_rank])
+
+
+class RowParallelLinear(LinearBase):
+    def __init__(self, input_size: int, output_size: int, bias: bool = False):
+        tp_size, _ = tp_world()
+        super().__init__(divide(input_size, tp_size), output_size, bias, 1)
+
+    def weight_loader(self, param: nn.Parameter, loaded_weight: torch.Tensor):
+        if param.data.ndim == 1:
+            param.data.copy_(loaded_weight)
+            return
+        shard = param.data.size(1)
+        param.data.copy_(loaded_weight.narrow(1, self.tp_rank * shard, shard))
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        y = F.linear(x, self.weight, self.bias if self.tp_rank == 0 else None)
+        if self.tp_size > 1:
+            dist.all_reduce(y)
+        return y

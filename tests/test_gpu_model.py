@@ -1,0 +1,119 @@
+"""End-to-end parity on BASELINE config 0: the tiny Llama-style DMS model, four ragged prompts,
+32 greedy decode steps, against the trace of the reference's own model + CompactKVManager run on
+CPU (tests/golden/make_golden_model.py).  Eviction decisions, compact lengths and logical slot
+indices must be bit-exact, greedy tokens identical, logits within 2e-2."""
+from __future__ import annotations
+
+import sys
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+
+ROOT = Path(__file__).resolve().parent.parent
+sys.path.insert(0, str(ROOT / "tests" / "golden"))
+
+pytestmark = pytest.mark.gpu
+LOGIT_TOL = 2e-2
+
+
+@pytest.fixture(scope="module")
+def golden():
+    with np.load(ROOT / "tests" / "golden" / "model_golden.npz") as z:
+        return {k: z[k] for k in z.files}
+
+
+def _engine(golden, kv_dtype, paged, eager=False):
+    import make_golden_model as G
+    from fastdms_b200 import LLM
+    from fastdms_b200.layers import rotary_embedding
+    rotary_embedding._ROPE_CACHE.clear()
+    llm = LLM("config0-tiny-llama", hf_config=dict(G.MODEL_CFG), random_init_seed=G.SEED, dtype="float32",
+              kv_cache_dtype=kv_dtype, max_model_len=1024, max_num_seqs=4, max_num_batched_tokens=4096,
+              compact_kv_capacity_tokens=8192, dms_window_size=G.WINDOW, dms_alpha_scale=G.ALPHA_SCALE,
+              dms_alpha_offset=G.ALPHA_OFFSET, compact_kv_paged=paged, enforce_eager=eager, device="cuda:0")
+    # the rotary table the reference used (cos/sin of the same float32 angles can differ by an ulp
+    # between math libraries; the table is an input of the path, not part of it)
+    cache = llm.model_runner.model.model.layers[0].self_attn.rotary_emb.cos_sin_cache
+    ref = torch.from_numpy(golden["cos_sin_cache"]).to(cache.device)
+    cache[: ref.shape[0], 0].copy_(ref)
+    return llm, G
+
+
+@pytest.mark.parametrize("tag,kv_dtype,paged,eager", [
+    ("f32", "float32", False, False), ("fp8", "float8_e4m3fn", False, False),
+    ("fp8", "float8_e4m3fn", True, False), ("fp8", "float8_e4m3fn", False, True)])
+def test_config0_matches_reference_trace(golden, tag, kv_dtype, paged, eager):
+    from fastdms_b200 import SamplingParams, _lib
+    llm, G = _engine(golden, kv_dtype, paged, eager)
+    prompts = G.make_prompts()
+    sp = SamplingParams(temperature=0.0, max_tokens=G.DECODE_STEPS + 1, ignore_eos=True)
+    seqs = [llm.add_request(p, sp) for p in prompts]
+    runner, mgr = llm.model_runner, llm.model_runner.compact_kv_manager
+    want_tokens = golden[f"{tag}_tokens"]
+
+    # prefill: one step for all four prompts
+    llm.step()
+    got = [s.completion_token_ids[-1] for s in seqs]
+    assert got == want_tokens[0].tolist()
+    live = torch.stack([mgr.seq_states[s.seq_id].live_counts for s in seqs], dim=1).cpu().numpy()
+    assert np.array_equal(live, golden[f"{tag}_prefill_live"])
+    for step in range(G.DECODE_STEPS):
+        llm.step()
+        g = runner.graphs[len(seqs)]
+        assert np.array_equal(g.evict_all.cpu().numpy(), golden[f"{tag}_evict"][step]), f"decisions differ at step {step}"
+        assert np.array_equal(g.live.cpu().numpy(), golden[f"{tag}_live"][step]), f"compact lengths differ at step {step}"
+        logical = (g.live - 1).cpu().numpy() if paged else (g.slot - g.base).cpu().numpy()
+        assert np.array_equal(logical, golden[f"{tag}_slot"][step]), f"slot indices differ at step {step}"
+        err = np.abs(g.logits.float().cpu().numpy() - golden[f"{tag}_logits"][step]).max()
+        assert err < LOGIT_TOL, f"logits differ by {err} at step {step}"
+        got = [s.completion_token_ids[-1] for s in seqs]
+        assert got == want_tokens[step + 1].tolist(), f"greedy tokens differ at step {step}"
+    assert all(s.is_finished for s in seqs) and llm.is_finished()
+    # everything went back to the pool
+    if paged:
+        assert mgr.free_page_counts.tolist() == [mgr.pages_per_layer] * mgr.num_layers
+    else:
+        assert mgr.free_ranges_per_layer == [[(0, mgr.capacity_tokens)]] * mgr.num_layers
+    assert sorted(mgr.free_active_slots) == list(range(mgr.max_active_seqs))
+    assert _lib.read_device_status("cuda:0") == 0
+
+
+def test_config0_final_metadata_and_generate_api(golden):
+    """Same run through LLM.generate; positions / evict bits of the finished spans are read just
+    before the sequences are released (the scheduler frees them at the last step)."""
+    from fastdms_b200 import SamplingParams
+    llm, G = _engine(golden, "float8_e4m3fn", False)
+    sp = SamplingParams(temperature=0.0, max_tokens=G.DECODE_STEPS, ignore_eos=True)    # one step short of the trace
+    seqs = [llm.add_request(p, sp) for p in G.make_prompts()]
+    mgr = llm.model_runner.compact_kv_manager
+    for _ in range(G.DECODE_STEPS - 1):
+        llm.step()
+    # state after 30 decode steps == reference state after 30 steps is not stored; run the last step
+    # by hand so that the spans are still allocated afterwards
+    batch, is_prefill = llm.scheduler.schedule()
+    assert not is_prefill
+    tokens = llm.model_runner.run(batch, False)
+    want = golden["fp8_tokens"]
+    assert tokens == want[G.DECODE_STEPS - 1].tolist()
+    llm.scheduler.postprocess(batch, tokens, False)
+    llm.model_runner.free_compact(llm.scheduler.consume_freed_seq_ids())
+    out = [s.completion_token_ids for s in seqs]
+    assert np.array_equal(np.array(out).T, want[: G.DECODE_STEPS])
+    # a fresh engine through the one-call API gives the same tokens
+    llm2, _ = _engine(golden, "float8_e4m3fn", True)
+    res = llm2.generate(G.make_prompts(), SamplingParams(temperature=0.0, max_tokens=G.DECODE_STEPS, ignore_eos=True))
+    assert [r["token_ids"] for r in res] == out
+
+
+def test_sampling_and_argument_errors(golden):
+    from fastdms_b200 import SamplingParams
+    llm, G = _engine(golden, "float8_e4m3fn", False)
+    torch.manual_seed(0)
+    res = llm.generate(G.make_prompts()[:2], [SamplingParams(temperature=0.8, max_tokens=5, ignore_eos=True),
+                                              SamplingParams(temperature=0.0, max_tokens=7, ignore_eos=True)])
+    assert [len(r["token_ids"]) for r in res] == [5, 7]
+    assert res[1]["token_ids"] == golden["fp8_tokens"][:7, 1].tolist()     # the greedy request is unaffected
+    with pytest.raises(ValueError):
+        llm.add_request(list(range(1000)), SamplingParams(max_tokens=100))
