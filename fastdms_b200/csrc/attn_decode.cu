@@ -849,3 +849,88 @@ extern "C" int32_t fdms_attn_decode(
     FDMS_CHECK_LAUNCH("attn_decode_generic_kernel");
     return FDMS_OK;
 }
+
+// ------------------------------------------------------------------------------------------------
+// Decode attention for callers that cannot allocate device memory.
+//
+// fdms_attn_decode needs a caller-provided split-K workspace.  Some hosts have nowhere to get one
+// from: a serving process that hands its whole device-memory budget to the KV pool at start-up and
+// forbids later cudaMalloc calls (they synchronise the device and can fail late), or a plugin loaded
+// through a foreign-function interface into a runtime written in another language, which has
+// pointers to the tensors it was given but no device allocator of its own to call.  For them the
+// workspace lives in this library's image: a fixed array in device memory that every GPU loading the
+// library holds until the process exits.
+//
+// Size and limits: counters for 4096 spans + 1024 partial slots of 8 heads x (128 + 2) floats
+// = 4,276,224 bytes.  Hence batch * kv_heads <= 4096 and head_dim <= 128 (larger sizes are rejected;
+// use fdms_attn_decode with your own workspace).
+//
+// The array's name is a host-side stand-in in host code, not a device address; the real address is
+// resolved once per device with cudaGetSymbolAddress while that device is current, and that pointer
+// is what the kernel receives.  The FIRST call on each device does this resolution, so make that
+// first call outside any stream capture.
+//
+// All calls share the one array and it keeps whatever the previous call left in it.  The span
+// counters at its start must be zero when a launch begins, so every call clears them on its stream
+// first.  Two calls whose kernels overlap on the GPU (different streams, or the same stream with
+// launch overlap) race on the array and give wrong results: serialise them.
+// ------------------------------------------------------------------------------------------------
+namespace fdms {
+constexpr int kStaticMaxSpans = 4096;
+constexpr int kStaticMaxHeadDim = 128;
+constexpr size_t kStaticCounterBytes = (size_t)kStaticMaxSpans * sizeof(int32_t);
+constexpr size_t kStaticScratchBytes = kStaticCounterBytes + (size_t)kMaxPartialSlots * kMaxGroup * 2 * sizeof(float) +
+                                       (size_t)kMaxPartialSlots * kMaxGroup * kStaticMaxHeadDim * sizeof(float);
+static __device__ __align__(256) unsigned char g_attn_static_scratch[kStaticScratchBytes];
+
+// Device address of the scratch array on the current device (nullptr + error code on failure).
+static void* static_scratch_address(cudaError_t* err) {
+    static void* cached[64] = {nullptr};
+    int dev = 0;
+    *err = cudaGetDevice(&dev);
+    if (*err != cudaSuccess) return nullptr;
+    if (dev < 0 || dev >= 64) { *err = cudaErrorInvalidDevice; return nullptr; }
+    if (cached[dev] == nullptr) {
+        void* ptr = nullptr;
+        *err = cudaGetSymbolAddress(&ptr, g_attn_static_scratch);
+        if (*err != cudaSuccess) return nullptr;
+        cached[dev] = ptr;
+    }
+    return cached[dev];
+}
+}  // namespace fdms
+
+extern "C" int32_t fdms_attn_decode_noalloc(
+    const void* q, int32_t q_dtype, int64_t q_stride_b, int64_t q_stride_h,
+    const void* k_pool, const void* v_pool, int32_t kv_dtype, int64_t pool_rows,
+    const int32_t* base_offsets, const int32_t* live_counts, int64_t meta_stride_b,
+    const int32_t* block_tables, int64_t bt_stride_b, int64_t bt_stride_h, int32_t bt_max_pages,
+    const float* k_scale, const float* v_scale,
+    void* out, int32_t out_dtype, int64_t out_stride_b, int64_t out_stride_h,
+    int32_t batch, int32_t num_q_heads, int32_t num_kv_heads, int32_t head_dim, float scale,
+    const int64_t* q_rope_positions, const float* q_rope_cos_sin, int64_t cos_sin_stride,
+    int32_t* dev_status, void* stream) {
+    clear_error();
+    FDMS_REQUIRE(batch >= 0 && num_kv_heads > 0 && head_dim > 0, FDMS_E_ARG, "fdms_attn_decode_noalloc: bad sizes");
+    FDMS_REQUIRE((int64_t)batch * num_kv_heads <= kStaticMaxSpans, FDMS_E_CAPACITY,
+                 "fdms_attn_decode_noalloc: batch*kv_heads=%lld exceeds the built-in scratch limit of %d spans; "
+                 "use fdms_attn_decode with a caller workspace",
+                 (long long)batch * num_kv_heads, kStaticMaxSpans);
+    FDMS_REQUIRE(head_dim <= kStaticMaxHeadDim, FDMS_E_CAPACITY,
+                 "fdms_attn_decode_noalloc: head_dim=%d exceeds the built-in scratch limit of %d; "
+                 "use fdms_attn_decode with a caller workspace", head_dim, kStaticMaxHeadDim);
+    if (batch == 0) return FDMS_OK;
+    cudaError_t e = cudaSuccess;
+    void* scratch = static_scratch_address(&e);
+    if (scratch == nullptr || e != cudaSuccess)
+        return fail(FDMS_E_CUDA, "fdms_attn_decode_noalloc: cudaGetSymbolAddress failed: %s", cudaGetErrorString(e));
+    // the span counters must start at zero; the rest of the array is fully rewritten before it is read
+    e = cudaMemsetAsync(scratch, 0, (size_t)batch * num_kv_heads * sizeof(int32_t), (cudaStream_t)stream);
+    if (e != cudaSuccess)
+        return fail(FDMS_E_CUDA, "fdms_attn_decode_noalloc: clearing the counters failed: %s", cudaGetErrorString(e));
+    return fdms_attn_decode(q, q_dtype, q_stride_b, q_stride_h, k_pool, v_pool, kv_dtype, pool_rows, base_offsets,
+                            live_counts, meta_stride_b, block_tables, bt_stride_b, bt_stride_h, bt_max_pages, k_scale,
+                            v_scale, out, out_dtype, out_stride_b, out_stride_h, batch, num_q_heads, num_kv_heads,
+                            head_dim, scale, q_rope_positions, q_rope_cos_sin, cos_sin_stride, scratch,
+                            (int64_t)kStaticScratchBytes, 0, dev_status, stream);
+}

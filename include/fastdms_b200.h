@@ -90,6 +90,29 @@ int32_t fdms_attn_decode(
     const int64_t* q_rope_positions, const float* q_rope_cos_sin, int64_t cos_sin_stride,
     void* workspace, int64_t workspace_bytes, int32_t flags, int32_t* dev_status, void* stream);
 
+/* Decode attention with the split-K scratch built into the library, for callers that cannot
+ * allocate device memory (no counterpart in the reference, which allocates its partial buffers with
+ * torch.empty on every call).  Same arguments and results as fdms_attn_decode without workspace and
+ * flags.  Meant for hosts whose device memory was fully handed out at start-up and that forbid later
+ * cudaMalloc calls, and for foreign-language runtimes that load this library as a plugin and own no
+ * device allocator.  The scratch is a fixed 4,276,224-byte array in the library image, held by every
+ * GPU that loads the library until the process exits; limits: batch * kv_heads <= 4096 and
+ * head_dim <= 128, beyond which the call fails with FDMS_E_CAPACITY.  Nothing is allocated or freed.
+ * The first call on a device resolves the array's device address (cudaGetSymbolAddress): make it
+ * outside any stream capture.  All calls share the array and it keeps the previous call's contents;
+ * each call clears the counters it needs on its stream, but calls whose kernels overlap on the GPU
+ * race on it and must be serialised by the caller. */
+int32_t fdms_attn_decode_noalloc(
+    const void* q, int32_t q_dtype, int64_t q_stride_b, int64_t q_stride_h,
+    const void* k_pool, const void* v_pool, int32_t kv_dtype, int64_t pool_rows,
+    const int32_t* base_offsets, const int32_t* live_counts, int64_t meta_stride_b,
+    const int32_t* block_tables, int64_t bt_stride_b, int64_t bt_stride_h, int32_t bt_max_pages,
+    const float* k_scale, const float* v_scale,
+    void* out, int32_t out_dtype, int64_t out_stride_b, int64_t out_stride_h,
+    int32_t batch, int32_t num_q_heads, int32_t num_kv_heads, int32_t head_dim, float scale,
+    const int64_t* q_rope_positions, const float* q_rope_cos_sin, int64_t cos_sin_stride,
+    int32_t* dev_status, void* stream);
+
 /* ---------------------------------------------------------------------------------------------
  * (b)+(d) fused decode preprocess: DMS decision + RoPE + FP8 quantise + append store.
  * Replaces fastdms/layers/compact_attention.py:1010-1113 fused_dms_rope_store_compact_decode
