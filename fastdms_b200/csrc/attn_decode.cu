@@ -114,6 +114,11 @@ __device__ __forceinline__ uint32_t e4m3x2_to_f16x2(uint32_t two_bytes) {
     asm("{\n\t.reg .b16 t;\n\tcvt.u16.u32 t, %1;\n\tcvt.rn.f16x2.e4m3x2 %0, t;\n\t}" : "=r"(r) : "r"(two_bytes));
     return r;
 }
+// Both halves of a 32-bit word (4 e4m3 bytes) at once: lo = bytes 0,1 and hi = bytes 2,3 as f16x2.
+__device__ __forceinline__ void e4m3x4_to_f16x2x2(uint32_t w, uint32_t& lo, uint32_t& hi) {
+    asm("{\n\t.reg .b16 a, b;\n\tmov.b32 {a, b}, %2;\n\tcvt.rn.f16x2.e4m3x2 %0, a;\n\tcvt.rn.f16x2.e4m3x2 %1, b;\n\t}"
+        : "=r"(lo), "=r"(hi) : "r"(w));
+}
 __device__ __forceinline__ uint32_t pack_f16x2(float lo, float hi) {
     __half2 h = __floats2half2_rn(lo, hi);
     return *(uint32_t*)&h;
@@ -225,10 +230,94 @@ __device__ __forceinline__ void load_q_frags(const AttnParams& p, int b, int h, 
     }
 }
 
-// One staged page (K rows at Ks, V rows at Vs, `rows` of them valid): online-softmax update of the
-// warp's running (m, l, O) for head g.
+// Register image of one 16-row page in the MMA fragment layout of lane (g, t):
+//   k[u][ch]  : 16 bytes of K row tokrow(u, g), elements 64*ch + 16*t .. +15
+//   va/vb[u][ch]: 8 bytes of V rows tokrow(u, 2t) / tokrow(u, 2t+1), elements 64*ch + 8*g .. +7
 template <int D>
-__device__ __forceinline__ void process_page(const uint8_t* Ks, const uint8_t* Vs, int rows, int g, int t, float sl2,
+struct PageFrags {
+    uint4 k[2][FastCfg<D>::kCh];
+    uint2 va[2][FastCfg<D>::kCh];
+    uint2 vb[2][FastCfg<D>::kCh];
+};
+
+// Fragment loads from a page staged in shared memory.
+template <int D>
+__device__ __forceinline__ void load_frags_smem(const uint8_t* Ks, const uint8_t* Vs, int g, int t, PageFrags<D>& f) {
+    using C = FastCfg<D>;
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+        const int r = tokrow(u, g);
+        if (C::kCh == 1) {
+            f.k[u][0] = *(const uint4*)(Ks + r * D + 16 * t);
+        } else {
+            // 128-byte rows: odd rows read the upper half first so that the two rows of a
+            // quarter-warp hit different banks
+            const int sw = r & 1;
+            const uint4 a = *(const uint4*)(Ks + r * D + 64 * sw + 16 * t);
+            const uint4 c = *(const uint4*)(Ks + r * D + 64 * (sw ^ 1) + 16 * t);
+            f.k[u][0] = sw ? c : a;
+            f.k[u][C::kCh - 1] = sw ? a : c;
+        }
+        const int rA = tokrow(u, 2 * t), rB = tokrow(u, 2 * t + 1);
+#pragma unroll
+        for (int ch = 0; ch < C::kCh; ++ch) {
+            f.va[u][ch] = *(const uint2*)(Vs + rA * D + 64 * ch + 8 * g);
+            f.vb[u][ch] = *(const uint2*)(Vs + rB * D + 64 * ch + 8 * g);
+        }
+    }
+}
+
+// Byte offsets inside a page of the fragments of lane (g, t); computed once per thread.
+template <int D>
+struct LaneOffsets {
+    int k[2], va[2], vb[2];
+    __device__ __forceinline__ LaneOffsets(int g, int t) {
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+            k[u] = tokrow(u, g) * D + 16 * t;
+            va[u] = tokrow(u, 2 * t) * D + 8 * g;
+            vb[u] = tokrow(u, 2 * t + 1) * D + 8 * g;
+        }
+    }
+};
+
+// Fragment loads straight from the pool in global memory (page = 16 consecutive rows at Kg / Vg).
+// Per instruction a warp reads whole 32-byte sectors: K 8 rows x 64 bytes, V 4 rows x 64 bytes.
+// In a partial page, rows at or beyond `rows` are not read (they may lie outside the pool) and come
+// back as zeros.
+template <int D>
+__device__ __forceinline__ void load_frags_global(const uint8_t* Kg, const uint8_t* Vg, int rows, int g, int t,
+                                                  const LaneOffsets<D>& lo, PageFrags<D>& f) {
+    using C = FastCfg<D>;
+    if (rows == kPage) {
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+#pragma unroll
+            for (int ch = 0; ch < C::kCh; ++ch) {
+                f.k[u][ch] = __ldcs((const uint4*)(Kg + lo.k[u] + 64 * ch));
+                f.va[u][ch] = __ldcs((const uint2*)(Vg + lo.va[u] + 64 * ch));
+                f.vb[u][ch] = __ldcs((const uint2*)(Vg + lo.vb[u] + 64 * ch));
+            }
+        }
+        return;
+    }
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+        const int r = tokrow(u, g);
+        const int rA = tokrow(u, 2 * t), rB = tokrow(u, 2 * t + 1);
+#pragma unroll
+        for (int ch = 0; ch < C::kCh; ++ch) {
+            f.k[u][ch] = r < rows ? __ldcs((const uint4*)(Kg + lo.k[u] + 64 * ch)) : make_uint4(0u, 0u, 0u, 0u);
+            f.va[u][ch] = rA < rows ? __ldcs((const uint2*)(Vg + lo.va[u] + 64 * ch)) : make_uint2(0u, 0u);
+            f.vb[u][ch] = rB < rows ? __ldcs((const uint2*)(Vg + lo.vb[u] + 64 * ch)) : make_uint2(0u, 0u);
+        }
+    }
+}
+
+// One page (`rows` of its 16 rows valid): online-softmax update of the warp's running (m, l, O) for
+// head g.  Fragments of invalid rows must hold finite values (they are masked, not trusted).
+template <int D>
+__device__ __forceinline__ void process_page(const PageFrags<D>& f, int rows, int t, float sl2,
                                              const uint32_t (&qa)[FastCfg<D>::kKSteps][2], float& m_run, float& l_run,
                                              float (&o)[FastCfg<D>::kNT][2]) {
     using C = FastCfg<D>;
@@ -236,41 +325,25 @@ __device__ __forceinline__ void process_page(const uint8_t* Ks, const uint8_t* V
     float sc[2][2];
 #pragma unroll
     for (int u = 0; u < 2; ++u) {
-        const int r = tokrow(u, g);
         float c0 = 0.0f, c1 = 0.0f;
-        uint4 kw[C::kCh];
-        if (C::kCh == 1) {
-            kw[0] = *(const uint4*)(Ks + r * D + 16 * t);
-        } else {
-            // 128-byte rows: odd rows read the upper half first so that the two rows of a
-            // quarter-warp hit different banks
-            const int sw = r & 1;
-            const uint4 a = *(const uint4*)(Ks + r * D + 64 * sw + 16 * t);
-            const uint4 c = *(const uint4*)(Ks + r * D + 64 * (sw ^ 1) + 16 * t);
-            kw[0] = sw ? c : a;
-            kw[C::kCh - 1] = sw ? a : c;
-        }
 #pragma unroll
         for (int ch = 0; ch < C::kCh; ++ch) {
-            const uint32_t w4[4] = {kw[ch].x, kw[ch].y, kw[ch].z, kw[ch].w};
+            const uint32_t w4[4] = {f.k[u][ch].x, f.k[u][ch].y, f.k[u][ch].z, f.k[u][ch].w};
 #pragma unroll
             for (int s = 0; s < 4; ++s) {
-                const uint32_t b0 = e4m3x2_to_f16x2(w4[s] & 0xffffu);
-                const uint32_t b1 = e4m3x2_to_f16x2(w4[s] >> 16);
+                uint32_t b0, b1;
+                e4m3x4_to_f16x2x2(w4[s], b0, b1);
                 mma_top(c0, c1, qa[4 * ch + s][0], qa[4 * ch + s][1], b0, b1);
             }
         }
         sc[u][0] = c0 * sl2;
         sc[u][1] = c1 * sl2;
     }
-    int rA[2], rB[2];
-#pragma unroll
-    for (int u = 0; u < 2; ++u) { rA[u] = tokrow(u, 2 * t); rB[u] = tokrow(u, 2 * t + 1); }
     if (rows < kPage) {
 #pragma unroll
         for (int u = 0; u < 2; ++u) {
-            if (rA[u] >= rows) sc[u][0] = -INFINITY;
-            if (rB[u] >= rows) sc[u][1] = -INFINITY;
+            if (tokrow(u, 2 * t) >= rows) sc[u][0] = -INFINITY;
+            if (tokrow(u, 2 * t + 1) >= rows) sc[u][1] = -INFINITY;
         }
     }
     // ---- online softmax (row = head g, reduce over the 4 lanes of the quad) ----
@@ -286,37 +359,159 @@ __device__ __forceinline__ void process_page(const uint8_t* Ks, const uint8_t* V
     m_run = m_new;
     const uint32_t pa0 = pack_f16x2(pr[0][0], pr[0][1]);
     const uint32_t pa2 = pack_f16x2(pr[1][0], pr[1][1]);
+    if (__any_sync(0xffffffffu, alpha != 1.0f)) {          // the running maxima rarely move after the first pages
 #pragma unroll
-    for (int jn = 0; jn < C::kNT; ++jn) { o[jn][0] *= alpha; o[jn][1] *= alpha; }
+        for (int jn = 0; jn < C::kNT; ++jn) { o[jn][0] *= alpha; o[jn][1] *= alpha; }
+    }
 
     // ---- O += P V ----
 #pragma unroll
     for (int ch = 0; ch < C::kCh; ++ch) {
-        uint2 va[2], vb[2];
-#pragma unroll
-        for (int u = 0; u < 2; ++u) {
-            va[u] = *(const uint2*)(Vs + rA[u] * D + 64 * ch + 8 * g);
-            vb[u] = *(const uint2*)(Vs + rB[u] * D + 64 * ch + 8 * g);
-            if (rows < kPage) {                   // stale bytes must not reach the MMA
-                if (rA[u] >= rows) va[u] = make_uint2(0u, 0u);
-                if (rB[u] >= rows) vb[u] = make_uint2(0u, 0u);
-            }
-        }
         uint32_t bf[2][8];
 #pragma unroll
         for (int u = 0; u < 2; ++u) {
-            const uint32_t x0 = __byte_perm(va[u].x, vb[u].x, 0x5140);
-            const uint32_t x1 = __byte_perm(va[u].x, vb[u].x, 0x7362);
-            const uint32_t y0 = __byte_perm(va[u].y, vb[u].y, 0x5140);
-            const uint32_t y1 = __byte_perm(va[u].y, vb[u].y, 0x7362);
-            bf[u][0] = e4m3x2_to_f16x2(x0 & 0xffffu); bf[u][1] = e4m3x2_to_f16x2(x0 >> 16);
-            bf[u][2] = e4m3x2_to_f16x2(x1 & 0xffffu); bf[u][3] = e4m3x2_to_f16x2(x1 >> 16);
-            bf[u][4] = e4m3x2_to_f16x2(y0 & 0xffffu); bf[u][5] = e4m3x2_to_f16x2(y0 >> 16);
-            bf[u][6] = e4m3x2_to_f16x2(y1 & 0xffffu); bf[u][7] = e4m3x2_to_f16x2(y1 >> 16);
+            uint2 va = f.va[u][ch], vb = f.vb[u][ch];
+            if (rows < kPage) {                   // stale bytes must not reach the MMA
+                if (tokrow(u, 2 * t) >= rows) va = make_uint2(0u, 0u);
+                if (tokrow(u, 2 * t + 1) >= rows) vb = make_uint2(0u, 0u);
+            }
+            const uint32_t x0 = __byte_perm(va.x, vb.x, 0x5140);
+            const uint32_t x1 = __byte_perm(va.x, vb.x, 0x7362);
+            const uint32_t y0 = __byte_perm(va.y, vb.y, 0x5140);
+            const uint32_t y1 = __byte_perm(va.y, vb.y, 0x7362);
+            e4m3x4_to_f16x2x2(x0, bf[u][0], bf[u][1]);
+            e4m3x4_to_f16x2x2(x1, bf[u][2], bf[u][3]);
+            e4m3x4_to_f16x2x2(y0, bf[u][4], bf[u][5]);
+            e4m3x4_to_f16x2x2(y1, bf[u][6], bf[u][7]);
         }
 #pragma unroll
         for (int jj = 0; jj < 8; ++jj)
             mma_top(o[8 * ch + jj][0], o[8 * ch + jj][1], pa0, pa2, bf[0][jj], bf[1][jj]);
+    }
+}
+
+// Shared tail of the fast kernels (called by the 256 consumer threads of a CTA): folds the warps'
+// partial (m, l, O) in shared memory, sends the CTA's partial to the cluster leader through
+// distributed shared memory, and lets the leader (or, with several clusters per span, the last
+// leader to arrive) write the output.
+template <int D>
+__device__ __forceinline__ void fold_and_write(const AttnParams& p, float* s_m, float* s_l, float* s_o, float* r_ml,
+                                               float* r_o, int* s_last_ptr, int tid, int warp, int g, int t, int b,
+                                               int h, int item, int rank, int chunk, float m_run, float l_run,
+                                               float (&o)[FastCfg<D>::kNT][2]) {
+    using C = FastCfg<D>;
+    const int S = p.splits, CH = p.chunks, G = p.group;
+    // ---- merge the warps' partial (m, l, O) ----
+    l_run += __shfl_xor_sync(0xffffffffu, l_run, 1);
+    l_run += __shfl_xor_sync(0xffffffffu, l_run, 2);
+    if (t == 0) { s_m[warp * kMaxGroup + g] = m_run; s_l[warp * kMaxGroup + g] = l_run; }
+    if (g < G) {
+        float* so = s_o + ((size_t)warp * kMaxGroup + g) * D;
+#pragma unroll
+        for (int jn = 0; jn < C::kNT; ++jn) {
+            const int ch = jn >> 3, jj = jn & 7;
+            so[64 * ch + 16 * t + jj] = o[jn][0];
+            so[64 * ch + 16 * t + 8 + jj] = o[jn][1];
+        }
+    }
+    consumer_bar();
+    if (S > 1) cluster_wait_acquire();          // phase 1 complete: the leader's shared memory exists
+    const float vs = p.v_scale ? p.v_scale[h] : 1.0f;
+    const uint32_t r_ml0 = S > 1 ? map_to_rank(r_ml, 0) : 0u;
+    const uint32_t r_o0 = S > 1 ? map_to_rank(r_o, 0) : 0u;
+    for (int e = tid; e < G * D; e += kConsumerThreads) {
+        const int gg = e / D, d = e - gg * D;
+        float M = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < kConsumerWarps; ++w) M = fmaxf(M, s_m[w * kMaxGroup + gg]);
+        float acc = 0.0f, Lsum = 0.0f;
+        if (M != -INFINITY) {
+#pragma unroll
+            for (int w = 0; w < kConsumerWarps; ++w) {
+                const float f = ex2(s_m[w * kMaxGroup + gg] - M);
+                acc += f * s_o[((size_t)w * kMaxGroup + gg) * D + d];
+                Lsum += f * s_l[w * kMaxGroup + gg];
+            }
+        }
+        if (S == 1 && CH == 1) {
+            store_from_float(p.out, (int64_t)b * p.out_sb + (int64_t)(h * G + gg) * p.out_sh + d, p.out_dtype,
+                             Lsum > 0.0f ? acc / Lsum * vs : 0.0f);
+        } else if (S == 1) {
+            r_o[gg * D + d] = acc;
+            if (d == 0) { r_ml[gg * 2] = M; r_ml[gg * 2 + 1] = Lsum; }
+        } else {
+            st_cluster_f32(r_o0 + (uint32_t)(((rank * G + gg) * D + d) * 4), acc);
+            if (d == 0) {
+                st_cluster_f32(r_ml0 + (uint32_t)(((rank * G + gg) * 2) * 4), M);
+                st_cluster_f32(r_ml0 + (uint32_t)(((rank * G + gg) * 2 + 1) * 4), Lsum);
+            }
+        }
+    }
+    if (S == 1 && CH == 1) return;
+    if (S > 1) {
+        cluster_arrive_release();               // phase 2: partials are in the leader's shared memory
+        cluster_wait_acquire();
+        if (rank != 0) return;
+    } else {
+        consumer_bar();
+    }
+
+    // ---- cluster leader: fold the S partials ----
+    const int pslot = item * CH + chunk;
+    for (int e = tid; e < G * D; e += kConsumerThreads) {
+        const int gg = e / D, d = e - gg * D;
+        float M = -INFINITY;
+        for (int r = 0; r < S; ++r) M = fmaxf(M, r_ml[(r * G + gg) * 2]);
+        float acc = 0.0f, Lsum = 0.0f;
+        if (M != -INFINITY) {
+            for (int r = 0; r < S; ++r) {
+                const float f = ex2(r_ml[(r * G + gg) * 2] - M);
+                acc += f * r_o[(r * G + gg) * D + d];
+                Lsum += f * r_ml[(r * G + gg) * 2 + 1];
+            }
+        }
+        if (CH == 1) {
+            store_from_float(p.out, (int64_t)b * p.out_sb + (int64_t)(h * G + gg) * p.out_sh + d, p.out_dtype,
+                             Lsum > 0.0f ? acc / Lsum * vs : 0.0f);
+        } else {
+            p.part_o[((size_t)pslot * kMaxGroup + gg) * D + d] = acc;
+            if (d == 0) {
+                p.part_ml[((size_t)pslot * kMaxGroup + gg) * 2] = M;
+                p.part_ml[((size_t)pslot * kMaxGroup + gg) * 2 + 1] = Lsum;
+            }
+        }
+    }
+    if (CH == 1) return;
+
+    // ---- several clusters per span: the last leader to arrive folds the chunk partials ----
+    __threadfence();
+    consumer_bar();
+    if (tid == 0) {
+        const int prev = atomicAdd(&p.counters[item], 1);
+        const int last = prev == CH - 1;
+        if (last) p.counters[item] = 0;          // leave the workspace ready for the next call
+        *s_last_ptr = last;
+    }
+    consumer_bar();
+    if (*(volatile int*)s_last_ptr) {
+        __threadfence();
+        for (int e = tid; e < G * D; e += kConsumerThreads) {
+            const int gg = e / D, d = e - gg * D;
+            float M = -INFINITY;
+            for (int c = 0; c < CH; ++c)
+                M = fmaxf(M, __ldcg(&p.part_ml[((size_t)(item * CH + c) * kMaxGroup + gg) * 2]));
+            float acc = 0.0f, Lsum = 0.0f;
+            if (M != -INFINITY) {
+                for (int c = 0; c < CH; ++c) {
+                    const size_t ps = (size_t)(item * CH + c) * kMaxGroup + gg;
+                    const float f = ex2(__ldcg(&p.part_ml[ps * 2]) - M);
+                    acc += f * __ldcg(&p.part_o[ps * D + d]);
+                    Lsum += f * __ldcg(&p.part_ml[ps * 2 + 1]);
+                }
+            }
+            store_from_float(p.out, (int64_t)b * p.out_sb + (int64_t)(h * G + gg) * p.out_sh + d, p.out_dtype,
+                             Lsum > 0.0f ? acc / Lsum * vs : 0.0f);
+        }
     }
 }
 
@@ -438,124 +633,119 @@ __global__ void __launch_bounds__(kFastThreads, (D == 64 ? 2 : 1)) attn_decode_f
         if (ok && !aborted) {
             const uint8_t* Ks = s_stage + (size_t)slot * C::kStageBytes;
             const int rows = min(kPage, live - (part + j * nparts) * kPage);
-            process_page<D>(Ks, Ks + C::kPageBytes, rows, g, t, sl2, qa, m_run, l_run, o);
+            PageFrags<D> f;
+            load_frags_smem<D>(Ks, Ks + C::kPageBytes, g, t, f);
+            process_page<D>(f, rows, t, sl2, qa, m_run, l_run, o);
         }
         __syncwarp();
         if (lane == 0) mbar_arrive(&s_empty[slot]);
     }
 
-    // ---- merge the warps' partial (m, l, O) ----
-    l_run += __shfl_xor_sync(0xffffffffu, l_run, 1);
-    l_run += __shfl_xor_sync(0xffffffffu, l_run, 2);
-    if (t == 0) { s_m[warp * kMaxGroup + g] = m_run; s_l[warp * kMaxGroup + g] = l_run; }
-    if (g < G) {
-        float* so = s_o + ((size_t)warp * kMaxGroup + g) * D;
-#pragma unroll
-        for (int jn = 0; jn < C::kNT; ++jn) {
-            const int ch = jn >> 3, jj = jn & 7;
-            so[64 * ch + 16 * t + jj] = o[jn][0];
-            so[64 * ch + 16 * t + 8 + jj] = o[jn][1];
-        }
-    }
-    consumer_bar();
-    if (S > 1) cluster_wait_acquire();          // phase 1 complete: the leader's shared memory exists
-    const float vs = p.v_scale ? p.v_scale[h] : 1.0f;
-    const uint32_t r_ml0 = S > 1 ? map_to_rank(r_ml, 0) : 0u;
-    const uint32_t r_o0 = S > 1 ? map_to_rank(r_o, 0) : 0u;
-    for (int e = tid; e < G * D; e += kConsumerThreads) {
-        const int gg = e / D, d = e - gg * D;
-        float M = -INFINITY;
-#pragma unroll
-        for (int w = 0; w < kConsumerWarps; ++w) M = fmaxf(M, s_m[w * kMaxGroup + gg]);
-        float acc = 0.0f, Lsum = 0.0f;
-        if (M != -INFINITY) {
-#pragma unroll
-            for (int w = 0; w < kConsumerWarps; ++w) {
-                const float f = ex2(s_m[w * kMaxGroup + gg] - M);
-                acc += f * s_o[((size_t)w * kMaxGroup + gg) * D + d];
-                Lsum += f * s_l[w * kMaxGroup + gg];
-            }
-        }
-        if (S == 1 && CH == 1) {
-            store_from_float(p.out, (int64_t)b * p.out_sb + (int64_t)(h * G + gg) * p.out_sh + d, p.out_dtype,
-                             Lsum > 0.0f ? acc / Lsum * vs : 0.0f);
-        } else if (S == 1) {
-            r_o[gg * D + d] = acc;
-            if (d == 0) { r_ml[gg * 2] = M; r_ml[gg * 2 + 1] = Lsum; }
-        } else {
-            st_cluster_f32(r_o0 + (uint32_t)(((rank * G + gg) * D + d) * 4), acc);
-            if (d == 0) {
-                st_cluster_f32(r_ml0 + (uint32_t)(((rank * G + gg) * 2) * 4), M);
-                st_cluster_f32(r_ml0 + (uint32_t)(((rank * G + gg) * 2 + 1) * 4), Lsum);
-            }
-        }
-    }
-    if (S == 1 && CH == 1) return;
-    if (S > 1) {
-        cluster_arrive_release();               // phase 2: partials are in the leader's shared memory
-        cluster_wait_acquire();
-        if (rank != 0) return;
-    } else {
-        consumer_bar();
-    }
+    fold_and_write<D>(p, s_m, s_l, s_o, r_ml, r_o, &s_last, tid, warp, g, t, b, h, item, rank, chunk, m_run, l_run, o);
+}
 
-    // ---- cluster leader: fold the S partials ----
-    const int pslot = item * CH + chunk;
-    for (int e = tid; e < G * D; e += kConsumerThreads) {
-        const int gg = e / D, d = e - gg * D;
-        float M = -INFINITY;
-        for (int r = 0; r < S; ++r) M = fmaxf(M, r_ml[(r * G + gg) * 2]);
-        float acc = 0.0f, Lsum = 0.0f;
-        if (M != -INFINITY) {
-            for (int r = 0; r < S; ++r) {
-                const float f = ex2(r_ml[(r * G + gg) * 2] - M);
-                acc += f * r_o[(r * G + gg) * D + d];
-                Lsum += f * r_ml[(r * G + gg) * 2 + 1];
-            }
-        }
-        if (CH == 1) {
-            store_from_float(p.out, (int64_t)b * p.out_sb + (int64_t)(h * G + gg) * p.out_sh + d, p.out_dtype,
-                             Lsum > 0.0f ? acc / Lsum * vs : 0.0f);
-        } else {
-            p.part_o[((size_t)pslot * kMaxGroup + gg) * D + d] = acc;
-            if (d == 0) {
-                p.part_ml[((size_t)pslot * kMaxGroup + gg) * 2] = M;
-                p.part_ml[((size_t)pslot * kMaxGroup + gg) * 2 + 1] = Lsum;
-            }
-        }
-    }
-    if (CH == 1) return;
+// ------------------------------------------------------------------------------------------------
+// Direct-load variant of the fast kernel: no staging in shared memory.  Every warp reads the pages it
+// owns straight from the pool into registers, already in MMA fragment layout, with 128-bit (K) and
+// 64-bit (V) loads that cover whole 32-byte sectors, and keeps DEPTH pages in flight ahead of the
+// one it is computing on.  Measured on B200 the 1 KiB bulk copies of the staged variant are limited
+// by the per-SM request rate of the copy engine (about one request per 50 ns, i.e. < 3 TB/s chip
+// wide for 16-row pages); per-lane vector loads are not.
+// ------------------------------------------------------------------------------------------------
+constexpr int kDirectThreads = kConsumerThreads;
 
-    // ---- several clusters per span: the last leader to arrive folds the chunk partials ----
-    __threadfence();
-    consumer_bar();
-    if (tid == 0) {
-        const int prev = atomicAdd(&p.counters[item], 1);
-        const int last = prev == CH - 1;
-        if (last) p.counters[item] = 0;          // leave the workspace ready for the next call
-        s_last = last;
+template <int D, int DEPTH>
+__global__ void __launch_bounds__(kDirectThreads, (D == 64 ? 2 : 1)) attn_decode_direct_kernel(AttnParams p) {
+    using C = FastCfg<D>;
+    extern __shared__ __align__(128) uint8_t smem[];
+    const int S = p.splits, CH = p.chunks, G = p.group;
+    float* s_m = (float*)smem;                                // [warps][8]
+    float* s_l = s_m + kConsumerWarps * kMaxGroup;            // [warps][8]
+    float* s_o = s_l + kConsumerWarps * kMaxGroup;            // [warps][8][D]
+    float* r_ml = s_o + kConsumerWarps * kMaxGroup * D;       // [S][G][2]
+    float* r_o = r_ml + S * G * 2;                            // [S][G][D]
+    __shared__ int s_last;
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int g = lane >> 2, t = lane & 3;
+    const int item = blockIdx.y;
+    const int rank = blockIdx.x % S;
+    const int chunk = blockIdx.x / S;
+    const int part = chunk * S + rank, nparts = S * CH;
+    const int b = item / p.hk, h = item - b * p.hk;
+
+    if (S > 1) cluster_arrive_relaxed();        // phase 1: "every CTA of the cluster has started"
+    grid_launch_dependents();
+    if (tid == 0) s_last = 0;
+
+    // Pages are dealt round-robin twice: page pi of the span belongs to CTA pi % nparts, and inside a
+    // CTA its local pages go to warps round-robin.  Warp-local page i is span page
+    // part + (warp + 8 i) * nparts, which is known before the span length is.
+    const int32_t* btrow = p.bt ? p.bt + (int64_t)b * p.bt_sb + (int64_t)h * p.bt_sh : nullptr;
+    const int stride_pg = kConsumerWarps * nparts;
+    const int pg0 = part + warp * nparts;
+    int32_t idreg[DEPTH];
+#pragma unroll
+    for (int s = 0; s < DEPTH; ++s) {
+        const int pi = pg0 + s * stride_pg;
+        idreg[s] = (btrow && pi < p.bt_pages) ? btrow[pi] : 0;
     }
-    consumer_bar();
-    if (*(volatile int*)&s_last) {
-        __threadfence();
-        for (int e = tid; e < G * D; e += kConsumerThreads) {
-            const int gg = e / D, d = e - gg * D;
-            float M = -INFINITY;
-            for (int c = 0; c < CH; ++c)
-                M = fmaxf(M, __ldcg(&p.part_ml[((size_t)(item * CH + c) * kMaxGroup + gg) * 2]));
-            float acc = 0.0f, Lsum = 0.0f;
-            if (M != -INFINITY) {
-                for (int c = 0; c < CH; ++c) {
-                    const size_t ps = (size_t)(item * CH + c) * kMaxGroup + gg;
-                    const float f = ex2(__ldcg(&p.part_ml[ps * 2]) - M);
-                    acc += f * __ldcg(&p.part_o[ps * D + d]);
-                    Lsum += f * __ldcg(&p.part_ml[ps * 2 + 1]);
-                }
+    const int live = max(0, p.live[(int64_t)b * p.meta_sb + h]);
+    const int64_t base = p.bt ? 0 : (int64_t)p.base[(int64_t)b * p.meta_sb + h];
+    const int npg = (live + kPage - 1) / kPage;
+    const int nw = pg0 < npg ? (npg - pg0 + stride_pg - 1) / stride_pg : 0;     // pages of this warp
+
+    const LaneOffsets<D> lofs(g, t);
+    PageFrags<D> buf[DEPTH];
+    int brow[DEPTH];
+    // Issues the loads of warp-local page i into buffer slot s (page id taken from idreg[s]), then
+    // starts fetching the page id that slot s will need next.
+    auto issue = [&](int s, int i) {
+        const int pi = pg0 + i * stride_pg;
+        const int rows = min(kPage, live - pi * kPage);
+        const int64_t row0 = btrow ? (int64_t)idreg[s] * kPage : base + (int64_t)pi * kPage;
+        if (row0 < 0 || row0 + rows > p.pool_rows) {
+            if (lane == 0 && p.dev_status) atomicOr(p.dev_status, FDMS_DEV_BAD_INDEX);
+            brow[s] = 0;
+        } else {
+            brow[s] = rows;
+            load_frags_global<D>(p.k_pool + row0 * D, p.v_pool + row0 * D, rows, g, t, lofs, buf[s]);
+        }
+        const int nxt = pi + DEPTH * stride_pg;
+        if (btrow && nxt < npg && nxt < p.bt_pages) idreg[s] = btrow[nxt];
+    };
+#pragma unroll
+    for (int s = 0; s < DEPTH; ++s) {
+        brow[s] = 0;
+        if (s < nw && pg0 + s * stride_pg != npg - 1) issue(s, s);
+    }
+    // The span's last page holds the row written by the preceding kernel of the stream, and q was
+    // rotated in place by it: both are read only after the dependency has been resolved.
+    grid_dependency_wait();
+#pragma unroll
+    for (int s = 0; s < DEPTH; ++s)
+        if (s < nw && pg0 + s * stride_pg == npg - 1) issue(s, s);
+
+    const float sl2 = p.scale * (p.k_scale ? p.k_scale[h] : 1.0f) * kLog2e;
+    uint32_t qa[C::kKSteps][2];
+    load_q_frags<D>(p, b, h, g, t, qa);
+    float m_run = -INFINITY, l_run = 0.0f;
+    float o[C::kNT][2];
+#pragma unroll
+    for (int j = 0; j < C::kNT; ++j) { o[j][0] = 0.0f; o[j][1] = 0.0f; }
+
+    for (int i0 = 0; i0 < nw; i0 += DEPTH) {
+#pragma unroll
+        for (int s = 0; s < DEPTH; ++s) {
+            const int i = i0 + s;
+            if (i < nw) {
+                if (brow[s] > 0) process_page<D>(buf[s], brow[s], t, sl2, qa, m_run, l_run, o);
+                if (i + DEPTH < nw) issue(s, i + DEPTH);
             }
-            store_from_float(p.out, (int64_t)b * p.out_sb + (int64_t)(h * G + gg) * p.out_sh + d, p.out_dtype,
-                             Lsum > 0.0f ? acc / Lsum * vs : 0.0f);
         }
     }
+    __syncthreads();                              // s_last initialised, all warps done with their pages
+    fold_and_write<D>(p, s_m, s_l, s_o, r_ml, r_o, &s_last, tid, warp, g, t, b, h, item, rank, chunk, m_run, l_run, o);
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -671,12 +861,17 @@ static size_t fast_smem_bytes(int D, int stages, int splits, int group) {
     return s + 128;
 }
 
-template <int D>
-static void fill_launch_config(cudaLaunchConfig_t& cfg, cudaLaunchAttribute* attr, int splits, int chunks, int items,
-                               size_t smem, cudaStream_t stream, bool overlap = false) {
+static size_t direct_smem_bytes(int D, int splits, int group) {
+    return (size_t)kConsumerWarps * kMaxGroup * (2 + D) * sizeof(float) + (size_t)splits * group * (2 + D) * sizeof(float) + 128;
+}
+
+typedef void (*AttnKernel)(AttnParams);
+
+static void fill_launch_config(cudaLaunchConfig_t& cfg, cudaLaunchAttribute* attr, int threads, int splits, int chunks,
+                               int items, size_t smem, cudaStream_t stream, bool overlap = false) {
     cfg = cudaLaunchConfig_t{};
     cfg.gridDim = dim3((unsigned)(splits * chunks), (unsigned)items, 1);
-    cfg.blockDim = dim3(kFastThreads, 1, 1);
+    cfg.blockDim = dim3((unsigned)threads, 1, 1);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = stream;
     attr[0].id = cudaLaunchAttributeClusterDimension;
@@ -693,32 +888,28 @@ static void fill_launch_config(cudaLaunchConfig_t& cfg, cudaLaunchAttribute* att
 }
 
 // Whether a cluster of `splits` CTAs with `smem` bytes each can be resident on this device.
-// Asked once per (head_dim, splits, smem) and remembered.
-template <int D>
-static bool cluster_fits(int splits, size_t smem) {
-    static size_t known_smem[kMaxSplits + 1] = {0};
-    static int known[kMaxSplits + 1] = {0};          // 0 unknown, 1 fits, -1 does not
+// Asked once per (kernel variant, splits, smem) and remembered.
+static bool cluster_fits(AttnKernel kern, int variant, int threads, int splits, size_t smem) {
+    static size_t known_smem[4][kMaxSplits + 1] = {{0}};
+    static int known[4][kMaxSplits + 1] = {{0}};     // 0 unknown, 1 fits, -1 does not
     if (splits == 1) return true;
-    if (known[splits] != 0 && known_smem[splits] == smem) return known[splits] > 0;
-    auto kern = attn_decode_fast_kernel<D>;
+    if (known[variant][splits] != 0 && known_smem[variant][splits] == smem) return known[variant][splits] > 0;
     bool ok = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) == cudaSuccess;
     if (ok && splits > 8) ok = cudaFuncSetAttribute(kern, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) == cudaSuccess;
     if (ok) {
         cudaLaunchConfig_t cfg;
         cudaLaunchAttribute attr[2];
-        fill_launch_config<D>(cfg, attr, splits, 1, 1, smem, nullptr);
+        fill_launch_config(cfg, attr, threads, splits, 1, 1, smem, nullptr);
         int n = 0;
         ok = cudaOccupancyMaxActiveClusters(&n, kern, &cfg) == cudaSuccess && n > 0;
     }
     cudaGetLastError();                               // a failed query must not poison the next launch check
-    known[splits] = ok ? 1 : -1;
-    known_smem[splits] = smem;
+    known[variant][splits] = ok ? 1 : -1;
+    known_smem[variant][splits] = smem;
     return ok;
 }
 
-template <int D>
-static cudaError_t launch_fast(const AttnParams& p, int items, size_t smem, cudaStream_t stream) {
-    auto kern = attn_decode_fast_kernel<D>;
+static cudaError_t launch_attn(AttnKernel kern, int threads, const AttnParams& p, int items, size_t smem, cudaStream_t stream) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
     if (p.splits > 8) {
@@ -727,7 +918,7 @@ static cudaError_t launch_fast(const AttnParams& p, int items, size_t smem, cuda
     }
     cudaLaunchConfig_t cfg;
     cudaLaunchAttribute attr[2];
-    fill_launch_config<D>(cfg, attr, p.splits, p.chunks, items, smem, stream, p.overlap != 0);
+    fill_launch_config(cfg, attr, threads, p.splits, p.chunks, items, smem, stream, p.overlap != 0);
     return cudaLaunchKernelEx(&cfg, kern, p);
 }
 
@@ -799,6 +990,19 @@ extern "C" int32_t fdms_attn_decode(
         const int target = di.sms * ctas_per_sm;
         int stages = env_int("FDMS_ATTN_STAGES", 32);
         if (stages < 32) stages = 32;
+        // Loader: "direct" (default) reads pages straight into registers; "tma" stages them in shared
+        // memory with bulk copies.
+        const char* loader = getenv("FDMS_ATTN_LOADER");
+        const bool direct = !(loader && loader[0] == 't');
+        const int variant = (direct ? 0 : 2) + (head_dim == 64 ? 0 : 1);
+        AttnKernel kern = direct ? (head_dim == 64 ? (AttnKernel)attn_decode_direct_kernel<64, 3>
+                                                   : (AttnKernel)attn_decode_direct_kernel<128, 2>)
+                                 : (head_dim == 64 ? (AttnKernel)attn_decode_fast_kernel<64>
+                                                   : (AttnKernel)attn_decode_fast_kernel<128>);
+        const int threads = direct ? kDirectThreads : kFastThreads;
+        auto smem_for = [&](int sp) {
+            return direct ? direct_smem_bytes(head_dim, sp, group) : fast_smem_bytes(head_dim, stages, sp, group);
+        };
         // splits: largest power of two that keeps the grid within about one wave
         int max_splits = env_int("FDMS_ATTN_MAX_SPLITS", 8);
         if (max_splits > kMaxSplits) max_splits = kMaxSplits;
@@ -806,9 +1010,8 @@ extern "C" int32_t fdms_attn_decode(
         while (splits * 2 <= max_splits && (int64_t)items * splits * 2 <= target) splits *= 2;
         const int forced = env_int("FDMS_ATTN_SPLITS", 0);
         if (forced >= 1 && forced <= kMaxSplits && (forced & (forced - 1)) == 0) splits = forced;
-        while (splits > 1 && (fast_smem_bytes(head_dim, stages, splits, group) > (size_t)di.smem_optin ||
-                              !(head_dim == 64 ? cluster_fits<64>(splits, fast_smem_bytes(head_dim, stages, splits, group))
-                                               : cluster_fits<128>(splits, fast_smem_bytes(head_dim, stages, splits, group)))))
+        while (splits > 1 && (smem_for(splits) > (size_t)di.smem_optin ||
+                              !cluster_fits(kern, variant, threads, splits, smem_for(splits))))
             splits /= 2;
         // chunks: more clusters per span when even the largest cluster leaves most SMs idle
         int chunks = 1;
@@ -832,12 +1035,11 @@ extern "C" int32_t fdms_attn_decode(
             p.part_ml = (float*)((uint8_t*)workspace + counters);
             p.part_o = p.part_ml + (size_t)kMaxPartialSlots * kMaxGroup * 2;
         }
-        const size_t smem = fast_smem_bytes(head_dim, stages, splits, group);
+        const size_t smem = smem_for(splits);
         FDMS_REQUIRE(smem <= (size_t)di.smem_optin, FDMS_E_CAPACITY,
                      "fdms_attn_decode: %zu bytes of shared memory needed (limit %d)", smem, di.smem_optin);
         p.stages = stages; p.splits = splits; p.chunks = chunks;
-        const cudaError_t e = head_dim == 64 ? launch_fast<64>(p, items, smem, (cudaStream_t)stream)
-                                             : launch_fast<128>(p, items, smem, (cudaStream_t)stream);
+        const cudaError_t e = launch_attn(kern, threads, p, items, smem, (cudaStream_t)stream);
         if (e != cudaSuccess) return fail(FDMS_E_CUDA, "attn_decode_fast_kernel launch failed: %s", cudaGetErrorString(e));
         FDMS_CHECK_LAUNCH("attn_decode_fast_kernel");
         return FDMS_OK;
