@@ -30,6 +30,9 @@ _SIGNATURES = {
     "fdms_attn_decode_workspace_bytes": (I64, [I32, I32, I32]),
     "fdms_attn_decode": (I32, [P, I32, I64, I64, P, P, I32, I64, P, P, I64, P, I64, I64, I32, P, P,
                                P, I32, I64, I64, I32, I32, I32, I32, F, P, P, I64, P, I64, I32, P, P]),
+    "fdms_attn_decode_append": (I32, [P, P, P, I32, I64, I64, I64, I64, I64, I64, P, P, I32, I64, P, P, I64,
+                                      P, I64, I64, I32, P, P, P, I64, P, P, I64, DBL, DBL, P, I32, I64, I64,
+                                      I32, I32, I32, I32, F, P, I64, I32, P, P]),
     "fdms_attn_decode_noalloc": (I32, [P, I32, I64, I64, P, P, I32, I64, P, P, I64, P, I64, I64, I32, P, P,
                                        P, I32, I64, I64, I32, I32, I32, I32, F, P, P, I64, P, P]),
     "fdms_store_decode": (I32, [P, I64, I64, P, I64, I64, P, I64, I64, I32, P, I64, P, P, P, I32, I64,

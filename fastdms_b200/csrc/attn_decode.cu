@@ -155,6 +155,14 @@ struct AttnParams {
     int32_t* counters; float* part_ml; float* part_o;     // only used when chunks > 1
     int32_t* dev_status;
     int stages, splits, chunks, overlap;
+    // fused append (direct kernel only): the step's new K/V row is rotated, quantised, written to the
+    // pool and attended to in the same launch; q is rotated on the fly (rope_pos / rope_cs above)
+    int append;
+    const void* k_new; int64_t kn_sb, kn_sh;
+    const void* v_new; int64_t vn_sb, vn_sh;
+    uint8_t* k_pool_w; uint8_t* v_pool_w;
+    uint8_t* evict_out; int64_t evict_sb;
+    DecisionRule rule;
 };
 
 // ------------------------------------------------------------------------------------------------
@@ -227,6 +235,48 @@ __device__ __forceinline__ void load_q_frags(const AttnParams& p, int b, int h, 
                 qa[4 * ch + s][1] = pack_f16x2(x[2], x[3]);
             }
         }
+    }
+}
+
+// 8 consecutive activation elements (bf16 / f16 / f32) starting at element index `e0` as floats;
+// the address must be 16-byte aligned.
+__device__ __forceinline__ void load8_as_float(const void* base, int64_t e0, int dt, float (&x)[8]) {
+    if (dt == FDMS_F32) {
+        const float4* p4 = (const float4*)((const float*)base + e0);
+        const float4 a = p4[0], b = p4[1];
+        x[0] = a.x; x[1] = a.y; x[2] = a.z; x[3] = a.w; x[4] = b.x; x[5] = b.y; x[6] = b.z; x[7] = b.w;
+    } else {
+        const uint4 a = *(const uint4*)((const uint16_t*)base + e0);
+        const uint32_t w[4] = {a.x, a.y, a.z, a.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            if (dt == FDMS_BF16) {
+                x[2 * i] = __uint_as_float(w[i] << 16);
+                x[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+            } else {
+                const __half2 h2 = *(const __half2*)&w[i];
+                x[2 * i] = __low2float(h2);
+                x[2 * i + 1] = __high2float(h2);
+            }
+        }
+    }
+}
+
+__device__ __forceinline__ uint32_t quant4(float a, float b, float c, float d, bool divide, float scale) {
+    if (divide) { a = __fdiv_rn(a, scale); b = __fdiv_rn(b, scale); c = __fdiv_rn(c, scale); d = __fdiv_rn(d, scale); }
+    return (uint32_t)float_to_e4m3(a) | ((uint32_t)float_to_e4m3(b) << 8) | ((uint32_t)float_to_e4m3(c) << 16) |
+           ((uint32_t)float_to_e4m3(d) << 24);
+}
+
+// neox rotation of one 8-wide unit: lower-half elements x1[i] (index i0 + i) and their partners
+// x2[i] (index half + i0 + i), cos c[i] and sin sn[i] of index i0 + i.  float32, unfused, each result
+// rounded to the activation dtype `dt` -- the arithmetic of the separate store kernel, bit for bit.
+__device__ __forceinline__ void rotate8(const float (&x1)[8], const float (&x2)[8], const float (&c)[8], const float (&sn)[8],
+                                        int dt, float (&lo)[8], float (&hi)[8]) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        lo[i] = round_to_dtype(__fsub_rn(__fmul_rn(x1[i], c[i]), __fmul_rn(x2[i], sn[i])), dt);
+        hi[i] = round_to_dtype(__fadd_rn(__fmul_rn(x2[i], c[i]), __fmul_rn(x1[i], sn[i])), dt);
     }
 }
 
@@ -654,9 +704,16 @@ __global__ void __launch_bounds__(kFastThreads, (D == 64 ? 2 : 1)) attn_decode_f
 // ------------------------------------------------------------------------------------------------
 constexpr int kDirectThreads = kConsumerThreads;
 
-template <int D, int DEPTH>
+// APPEND = true is the fused store + attention launch: the step's new K/V row is not in the pool yet.
+// After the dependency wait a few threads build, through shared memory and once per CTA,
+//   * the rotated q of the whole head group (f16, what the MMA consumes), and
+//   * in the CTA that owns the span's last page, the new row: DMS decision, rotated K and V quantised
+//     to FP8, written to the pool and patched into the register image of that page.
+// Work is split in 8-element units so that every unit is one 16-byte load per operand.
+template <int D, int DEPTH, bool APPEND>
 __global__ void __launch_bounds__(kDirectThreads, (D == 64 ? 2 : 1)) attn_decode_direct_kernel(AttnParams p) {
     using C = FastCfg<D>;
+    constexpr int half = D / 2;
     extern __shared__ __align__(128) uint8_t smem[];
     const int S = p.splits, CH = p.chunks, G = p.group;
     float* s_m = (float*)smem;                                // [warps][8]
@@ -665,6 +722,8 @@ __global__ void __launch_bounds__(kDirectThreads, (D == 64 ? 2 : 1)) attn_decode
     float* r_ml = s_o + kConsumerWarps * kMaxGroup * D;       // [S][G][2]
     float* r_o = r_ml + S * G * 2;                            // [S][G][D]
     __shared__ int s_last;
+    __shared__ __align__(16) __half s_q[APPEND ? kMaxGroup * D : 8];     // rotated q, [G][D]
+    __shared__ __align__(16) uint8_t s_new[APPEND ? 2 * D : 16];         // new K row | new V row (FP8)
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int g = lane >> 2, t = lane & 3;
@@ -694,6 +753,37 @@ __global__ void __launch_bounds__(kDirectThreads, (D == 64 ? 2 : 1)) attn_decode
     const int64_t base = p.bt ? 0 : (int64_t)p.base[(int64_t)b * p.meta_sb + h];
     const int npg = (live + kPage - 1) / kPage;
     const int nw = pg0 < npg ? (npg - pg0 + stride_pg - 1) / stride_pg : 0;     // pages of this warp
+    const int tail_pi = npg - 1;
+
+    // ---- fused append: unit assignment and everything that does not depend on the previous kernel ----
+    // units [0, nq): q head gg, lower-half elements i0..i0+7 (and their partners)
+    // units [nq, nq + nk): the same for the new K row          (tail CTA only)
+    // units [nq + nk, nq + nk + nv): 8 elements of the new V row (tail CTA only)
+    constexpr int kUnitsPerRow = half / 8;
+    int unit_kind = -1, unit_gg = 0, unit_i0 = 0;        // 0 = q, 1 = k, 2 = v
+    float ucos[8], usin[8];
+    int64_t tail_row = -1;                               // pool row of the new token (tail CTA, unit threads)
+    bool tail_cta = false;
+    if (APPEND) {
+        tail_cta = live > 0 && (tail_pi % nparts) == part;
+        const int nq = G * kUnitsPerRow, nk = tail_cta ? kUnitsPerRow : 0, nv = tail_cta ? D / 8 : 0;
+        if (tid < nq) { unit_kind = 0; unit_gg = tid / kUnitsPerRow; unit_i0 = 8 * (tid % kUnitsPerRow); }
+        else if (tid < nq + nk) { unit_kind = 1; unit_i0 = 8 * (tid - nq); }
+        else if (tid < nq + nk + nv) { unit_kind = 2; unit_i0 = 8 * (tid - nq - nk); }
+        if (unit_kind == 0 || unit_kind == 1) {
+            const float* cs = p.rope_cs + p.rope_pos[b] * p.rope_stride;
+            const float4 c0 = *(const float4*)(cs + unit_i0), c1 = *(const float4*)(cs + unit_i0 + 4);
+            const float4 n0 = *(const float4*)(cs + half + unit_i0), n1 = *(const float4*)(cs + half + unit_i0 + 4);
+            ucos[0] = c0.x; ucos[1] = c0.y; ucos[2] = c0.z; ucos[3] = c0.w; ucos[4] = c1.x; ucos[5] = c1.y; ucos[6] = c1.z; ucos[7] = c1.w;
+            usin[0] = n0.x; usin[1] = n0.y; usin[2] = n0.z; usin[3] = n0.w; usin[4] = n1.x; usin[5] = n1.y; usin[6] = n1.z; usin[7] = n1.w;
+        }
+        if (unit_kind >= 1) {
+            const int64_t trow0 = btrow ? (tail_pi < p.bt_pages ? (int64_t)btrow[tail_pi] * kPage : -1)
+                                        : base + (int64_t)tail_pi * kPage;
+            const int64_t r = trow0 + (live - 1 - tail_pi * kPage);
+            tail_row = (trow0 >= 0 && r < p.pool_rows) ? r : -2;
+        }
+    }
 
     const LaneOffsets<D> lofs(g, t);
     PageFrags<D> buf[DEPTH];
@@ -709,7 +799,9 @@ __global__ void __launch_bounds__(kDirectThreads, (D == 64 ? 2 : 1)) attn_decode
             brow[s] = 0;
         } else {
             brow[s] = rows;
-            load_frags_global<D>(p.k_pool + row0 * D, p.v_pool + row0 * D, rows, g, t, lofs, buf[s]);
+            // in append mode the span's last row is not in the pool yet: it is patched in below
+            const int have = (APPEND && pi == tail_pi) ? rows - 1 : rows;
+            load_frags_global<D>(p.k_pool + row0 * D, p.v_pool + row0 * D, have, g, t, lofs, buf[s]);
         }
         const int nxt = pi + DEPTH * stride_pg;
         if (btrow && nxt < npg && nxt < p.bt_pages) idreg[s] = btrow[nxt];
@@ -717,18 +809,82 @@ __global__ void __launch_bounds__(kDirectThreads, (D == 64 ? 2 : 1)) attn_decode
 #pragma unroll
     for (int s = 0; s < DEPTH; ++s) {
         brow[s] = 0;
-        if (s < nw && pg0 + s * stride_pg != npg - 1) issue(s, s);
+        if (s < nw && pg0 + s * stride_pg != tail_pi) issue(s, s);
     }
-    // The span's last page holds the row written by the preceding kernel of the stream, and q was
-    // rotated in place by it: both are read only after the dependency has been resolved.
+    // The span's last page holds the row written by the preceding kernel of the stream (or, in append
+    // mode, older rows only), and q / k / v come from it: all are read only after the dependency has
+    // been resolved.
     grid_dependency_wait();
 #pragma unroll
     for (int s = 0; s < DEPTH; ++s)
-        if (s < nw && pg0 + s * stride_pg == npg - 1) issue(s, s);
+        if (s < nw && pg0 + s * stride_pg == tail_pi) issue(s, s);
 
     const float sl2 = p.scale * (p.k_scale ? p.k_scale[h] : 1.0f) * kLog2e;
     uint32_t qa[C::kKSteps][2];
-    load_q_frags<D>(p, b, h, g, t, qa);
+    if (APPEND) {
+        if (unit_kind == 0 || unit_kind == 1) {
+            const bool isq = unit_kind == 0;
+            const void* src = isq ? p.q : p.k_new;
+            const int64_t row = isq ? (int64_t)b * p.q_sb + (int64_t)(h * G + unit_gg) * p.q_sh
+                                    : (int64_t)b * p.kn_sb + (int64_t)h * p.kn_sh;
+            float x1[8], x2[8], lo[8], hi[8];
+            load8_as_float(src, row + unit_i0, p.q_dtype, x1);
+            load8_as_float(src, row + half + unit_i0, p.q_dtype, x2);
+            if (isq && unit_gg == 0 && unit_i0 == half - 8) {
+                // the group's first q head carries the DMS decision in its last channel
+                if (tail_cta && p.evict_out) p.evict_out[(int64_t)b * p.evict_sb + h] = p.rule.evict(x2[7]) ? 1 : 0;
+                x2[7] = 0.0f;
+            }
+            rotate8(x1, x2, ucos, usin, p.q_dtype, lo, hi);
+            if (isq) {
+                __half2* dl = (__half2*)(s_q + unit_gg * D + unit_i0);
+                __half2* dh = (__half2*)(s_q + unit_gg * D + half + unit_i0);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    dl[i] = __floats2half2_rn(lo[2 * i], lo[2 * i + 1]);
+                    dh[i] = __floats2half2_rn(hi[2 * i], hi[2 * i + 1]);
+                }
+            } else {
+                const float ksc = p.k_scale ? p.k_scale[h] : 1.0f;
+                const bool dv = p.k_scale != nullptr;
+                const uint2 bl = make_uint2(quant4(lo[0], lo[1], lo[2], lo[3], dv, ksc), quant4(lo[4], lo[5], lo[6], lo[7], dv, ksc));
+                const uint2 bh = make_uint2(quant4(hi[0], hi[1], hi[2], hi[3], dv, ksc), quant4(hi[4], hi[5], hi[6], hi[7], dv, ksc));
+                *(uint2*)(s_new + unit_i0) = bl;
+                *(uint2*)(s_new + half + unit_i0) = bh;
+                if (tail_row >= 0) {
+                    *(uint2*)(p.k_pool_w + tail_row * D + unit_i0) = bl;
+                    *(uint2*)(p.k_pool_w + tail_row * D + half + unit_i0) = bh;
+                }
+            }
+        } else if (unit_kind == 2) {
+            float x[8];
+            load8_as_float(p.v_new, (int64_t)b * p.vn_sb + (int64_t)h * p.vn_sh + unit_i0, p.q_dtype, x);
+            const float vsc = p.v_scale ? p.v_scale[h] : 1.0f;
+            const bool dv = p.v_scale != nullptr;
+            const uint2 bv = make_uint2(quant4(x[0], x[1], x[2], x[3], dv, vsc), quant4(x[4], x[5], x[6], x[7], dv, vsc));
+            *(uint2*)(s_new + D + unit_i0) = bv;
+            if (tail_row >= 0) *(uint2*)(p.v_pool_w + tail_row * D + unit_i0) = bv;
+        }
+        if (tail_row == -2 && unit_kind == 1 && unit_i0 == 0 && p.dev_status) atomicOr(p.dev_status, FDMS_DEV_BAD_INDEX);
+        __syncthreads();
+#pragma unroll
+        for (int ch = 0; ch < C::kCh; ++ch) {
+            uint4 w0 = make_uint4(0u, 0u, 0u, 0u), w1 = w0;
+            if (g < G) {
+                const uint4* src = (const uint4*)(s_q + g * D + 64 * ch + 16 * t);
+                w0 = src[0]; w1 = src[1];
+            }
+            qa[4 * ch + 0][0] = w0.x; qa[4 * ch + 0][1] = w0.y; qa[4 * ch + 1][0] = w0.z; qa[4 * ch + 1][1] = w0.w;
+            qa[4 * ch + 2][0] = w1.x; qa[4 * ch + 2][1] = w1.y; qa[4 * ch + 3][0] = w1.z; qa[4 * ch + 3][1] = w1.w;
+        }
+    } else {
+        load_q_frags<D>(p, b, h, g, t, qa);
+    }
+
+    // the warp that owns the span's last page patches the new row into its register image
+    const bool own_tail = APPEND && nw > 0 && tail_pi >= pg0 && (tail_pi - pg0) % stride_pg == 0;
+    const int r_new = live - 1 - tail_pi * kPage;            // row of the new token inside that page
+
     float m_run = -INFINITY, l_run = 0.0f;
     float o[C::kNT][2];
 #pragma unroll
@@ -739,6 +895,17 @@ __global__ void __launch_bounds__(kDirectThreads, (D == 64 ? 2 : 1)) attn_decode
         for (int s = 0; s < DEPTH; ++s) {
             const int i = i0 + s;
             if (i < nw) {
+                if (APPEND && own_tail && pg0 + i * stride_pg == tail_pi) {
+#pragma unroll
+                    for (int u = 0; u < 2; ++u) {
+#pragma unroll
+                        for (int ch = 0; ch < C::kCh; ++ch) {
+                            if (tokrow(u, g) == r_new) buf[s].k[u][ch] = *(const uint4*)(s_new + 64 * ch + 16 * t);
+                            if (tokrow(u, 2 * t) == r_new) buf[s].va[u][ch] = *(const uint2*)(s_new + D + 64 * ch + 8 * g);
+                            if (tokrow(u, 2 * t + 1) == r_new) buf[s].vb[u][ch] = *(const uint2*)(s_new + D + 64 * ch + 8 * g);
+                        }
+                    }
+                }
                 if (brow[s] > 0) process_page<D>(buf[s], brow[s], t, sl2, qa, m_run, l_run, o);
                 if (i + DEPTH < nw) issue(s, i + DEPTH);
             }
@@ -890,8 +1057,8 @@ static void fill_launch_config(cudaLaunchConfig_t& cfg, cudaLaunchAttribute* att
 // Whether a cluster of `splits` CTAs with `smem` bytes each can be resident on this device.
 // Asked once per (kernel variant, splits, smem) and remembered.
 static bool cluster_fits(AttnKernel kern, int variant, int threads, int splits, size_t smem) {
-    static size_t known_smem[4][kMaxSplits + 1] = {{0}};
-    static int known[4][kMaxSplits + 1] = {{0}};     // 0 unknown, 1 fits, -1 does not
+    static size_t known_smem[6][kMaxSplits + 1] = {{0}};
+    static int known[6][kMaxSplits + 1] = {{0}};     // 0 unknown, 1 fits, -1 does not
     if (splits == 1) return true;
     if (known[variant][splits] != 0 && known_smem[variant][splits] == smem) return known[variant][splits] > 0;
     bool ok = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) == cudaSuccess;
@@ -934,7 +1101,16 @@ extern "C" int64_t fdms_attn_decode_workspace_bytes(int32_t batch, int32_t num_k
     return counters + ml + po;
 }
 
-extern "C" int32_t fdms_attn_decode(
+namespace fdms {
+struct AppendArgs {
+    const void* k_new; int64_t kn_sb, kn_sh;
+    const void* v_new; int64_t vn_sb, vn_sh;
+    uint8_t* evict_out; int64_t evict_sb;
+    double alpha_scale, alpha_offset;
+};
+}  // namespace fdms
+
+static int32_t attn_decode_common(
     const void* q, int32_t q_dtype, int64_t q_stride_b, int64_t q_stride_h,
     const void* k_pool, const void* v_pool, int32_t kv_dtype, int64_t pool_rows,
     const int32_t* base_offsets, const int32_t* live_counts, int64_t meta_stride_b,
@@ -943,7 +1119,8 @@ extern "C" int32_t fdms_attn_decode(
     void* out, int32_t out_dtype, int64_t out_stride_b, int64_t out_stride_h,
     int32_t batch, int32_t num_q_heads, int32_t num_kv_heads, int32_t head_dim, float scale,
     const int64_t* q_rope_positions, const float* q_rope_cos_sin, int64_t cos_sin_stride,
-    void* workspace, int64_t workspace_bytes, int32_t flags, int32_t* dev_status, void* stream) {
+    void* workspace, int64_t workspace_bytes, int32_t flags, int32_t* dev_status, void* stream,
+    const fdms::AppendArgs* app) {
     clear_error();
     FDMS_REQUIRE(q && k_pool && v_pool && live_counts && out, FDMS_E_ARG, "fdms_attn_decode: null pointer");
     FDMS_REQUIRE(base_offsets || block_tables, FDMS_E_ARG, "fdms_attn_decode: base_offsets or block_tables required");
@@ -979,10 +1156,34 @@ extern "C" int32_t fdms_attn_decode(
     p.counters = nullptr; p.part_ml = nullptr; p.part_o = nullptr;
     p.dev_status = dev_status;
     p.stages = 0; p.splits = 1; p.chunks = 1; p.overlap = (flags & FDMS_ATTN_OVERLAP_PREVIOUS) ? 1 : 0;
+    p.append = 0;
+    p.k_new = nullptr; p.kn_sb = p.kn_sh = 0; p.v_new = nullptr; p.vn_sb = p.vn_sh = 0;
+    p.k_pool_w = nullptr; p.v_pool_w = nullptr; p.evict_out = nullptr; p.evict_sb = 0;
+    p.rule = make_rule(1.0, 0.0);
 
     const bool fast = kv_dtype == FDMS_E4M3 && (head_dim == 64 || head_dim == 128) && group <= kMaxGroup &&
                       items <= 65535 && ((uintptr_t)k_pool % 16 == 0) && ((uintptr_t)v_pool % 16 == 0) &&
                       env_int("FDMS_ATTN_FORCE_GENERIC", 0) == 0;
+    if (app) {
+        FDMS_REQUIRE(fast, FDMS_E_DTYPE,
+                     "fdms_attn_decode_append needs FP8 e4m3 pools, head_dim 64 or 128 and group size <= %d", kMaxGroup);
+        FDMS_REQUIRE(app->k_new && app->v_new && q_rope_positions && q_rope_cos_sin, FDMS_E_ARG,
+                     "fdms_attn_decode_append: k, v, positions and cos_sin_cache are required");
+        FDMS_REQUIRE(app->alpha_scale != 0.0 || !app->evict_out, FDMS_E_ARG, "alpha_scale must be non-zero");
+        const int64_t esz = q_dtype == FDMS_F32 ? 4 : 2;
+        const uintptr_t mis = (uintptr_t)q | (uintptr_t)app->k_new | (uintptr_t)(q_stride_b * esz) |
+                              (uintptr_t)(q_stride_h * esz) | (uintptr_t)(app->kn_sb * esz) | (uintptr_t)(app->kn_sh * esz) |
+                              (uintptr_t)app->v_new | (uintptr_t)(app->vn_sb * esz) | (uintptr_t)(app->vn_sh * esz);
+        FDMS_REQUIRE((((uintptr_t)q_rope_cos_sin | (uintptr_t)(cos_sin_stride * 4)) & 15) == 0, FDMS_E_ARG,
+                     "fdms_attn_decode_append: cos_sin_cache rows must be 16-byte aligned");
+        FDMS_REQUIRE((mis & 15) == 0, FDMS_E_ARG, "fdms_attn_decode_append: q, k and v rows must be 16-byte aligned");
+        p.append = 1;
+        p.k_new = app->k_new; p.kn_sb = app->kn_sb; p.kn_sh = app->kn_sh;
+        p.v_new = app->v_new; p.vn_sb = app->vn_sb; p.vn_sh = app->vn_sh;
+        p.k_pool_w = (uint8_t*)k_pool; p.v_pool_w = (uint8_t*)v_pool;
+        p.evict_out = app->evict_out; p.evict_sb = app->evict_sb;
+        p.rule = make_rule(app->alpha_scale, app->alpha_offset);
+    }
     if (fast) {
         const DeviceInfo di = device_info();
         FDMS_REQUIRE(di.ok && di.sms > 0, FDMS_E_CUDA, "fdms_attn_decode: cannot query the device");
@@ -993,12 +1194,12 @@ extern "C" int32_t fdms_attn_decode(
         // Loader: "direct" (default) reads pages straight into registers; "tma" stages them in shared
         // memory with bulk copies.
         const char* loader = getenv("FDMS_ATTN_LOADER");
-        const bool direct = !(loader && loader[0] == 't');
-        const int variant = (direct ? 0 : 2) + (head_dim == 64 ? 0 : 1);
-        AttnKernel kern = direct ? (head_dim == 64 ? (AttnKernel)attn_decode_direct_kernel<64, 3>
-                                                   : (AttnKernel)attn_decode_direct_kernel<128, 2>)
-                                 : (head_dim == 64 ? (AttnKernel)attn_decode_fast_kernel<64>
-                                                   : (AttnKernel)attn_decode_fast_kernel<128>);
+        const bool direct = app != nullptr || !(loader && loader[0] == 't');
+        const int variant = (app ? 4 : direct ? 0 : 2) + (head_dim == 64 ? 0 : 1);
+        AttnKernel kern;
+        if (app) kern = head_dim == 64 ? (AttnKernel)attn_decode_direct_kernel<64, 3, true> : (AttnKernel)attn_decode_direct_kernel<128, 2, true>;
+        else if (direct) kern = head_dim == 64 ? (AttnKernel)attn_decode_direct_kernel<64, 3, false> : (AttnKernel)attn_decode_direct_kernel<128, 2, false>;
+        else kern = head_dim == 64 ? (AttnKernel)attn_decode_fast_kernel<64> : (AttnKernel)attn_decode_fast_kernel<128>;
         const int threads = direct ? kDirectThreads : kFastThreads;
         auto smem_for = [&](int sp) {
             return direct ? direct_smem_bytes(head_dim, sp, group) : fast_smem_bytes(head_dim, stages, sp, group);
@@ -1050,6 +1251,47 @@ extern "C" int32_t fdms_attn_decode(
     attn_decode_generic_kernel<<<batch * num_q_heads, kGenWarps * 32, 0, (cudaStream_t)stream>>>(gp);
     FDMS_CHECK_LAUNCH("attn_decode_generic_kernel");
     return FDMS_OK;
+}
+
+extern "C" int32_t fdms_attn_decode(
+    const void* q, int32_t q_dtype, int64_t q_stride_b, int64_t q_stride_h,
+    const void* k_pool, const void* v_pool, int32_t kv_dtype, int64_t pool_rows,
+    const int32_t* base_offsets, const int32_t* live_counts, int64_t meta_stride_b,
+    const int32_t* block_tables, int64_t bt_stride_b, int64_t bt_stride_h, int32_t bt_max_pages,
+    const float* k_scale, const float* v_scale,
+    void* out, int32_t out_dtype, int64_t out_stride_b, int64_t out_stride_h,
+    int32_t batch, int32_t num_q_heads, int32_t num_kv_heads, int32_t head_dim, float scale,
+    const int64_t* q_rope_positions, const float* q_rope_cos_sin, int64_t cos_sin_stride,
+    void* workspace, int64_t workspace_bytes, int32_t flags, int32_t* dev_status, void* stream) {
+    return attn_decode_common(q, q_dtype, q_stride_b, q_stride_h, k_pool, v_pool, kv_dtype, pool_rows, base_offsets,
+                              live_counts, meta_stride_b, block_tables, bt_stride_b, bt_stride_h, bt_max_pages, k_scale,
+                              v_scale, out, out_dtype, out_stride_b, out_stride_h, batch, num_q_heads, num_kv_heads,
+                              head_dim, scale, q_rope_positions, q_rope_cos_sin, cos_sin_stride, workspace,
+                              workspace_bytes, flags, dev_status, stream, nullptr);
+}
+
+extern "C" int32_t fdms_attn_decode_append(
+    const void* q, const void* k, const void* v, int32_t act_dtype,
+    int64_t q_stride_b, int64_t q_stride_h, int64_t k_stride_b, int64_t k_stride_h, int64_t v_stride_b, int64_t v_stride_h,
+    void* k_pool, void* v_pool, int32_t kv_dtype, int64_t pool_rows,
+    const int32_t* base_offsets, const int32_t* live_counts, int64_t meta_stride_b,
+    const int32_t* block_tables, int64_t bt_stride_b, int64_t bt_stride_h, int32_t bt_max_pages,
+    const float* k_scale, const float* v_scale,
+    const float* cos_sin, int64_t cos_sin_stride, const int64_t* positions,
+    uint8_t* evict_out, int64_t evict_stride_b, double alpha_scale, double alpha_offset,
+    void* out, int32_t out_dtype, int64_t out_stride_b, int64_t out_stride_h,
+    int32_t batch, int32_t num_q_heads, int32_t num_kv_heads, int32_t head_dim, float scale,
+    void* workspace, int64_t workspace_bytes, int32_t flags, int32_t* dev_status, void* stream) {
+    fdms::AppendArgs app;
+    app.k_new = k; app.kn_sb = k_stride_b; app.kn_sh = k_stride_h;
+    app.v_new = v; app.vn_sb = v_stride_b; app.vn_sh = v_stride_h;
+    app.evict_out = evict_out; app.evict_sb = evict_stride_b;
+    app.alpha_scale = alpha_scale; app.alpha_offset = alpha_offset;
+    return attn_decode_common(q, act_dtype, q_stride_b, q_stride_h, k_pool, v_pool, kv_dtype, pool_rows, base_offsets,
+                              live_counts, meta_stride_b, block_tables, bt_stride_b, bt_stride_h, bt_max_pages, k_scale,
+                              v_scale, out, out_dtype, out_stride_b, out_stride_h, batch, num_q_heads, num_kv_heads,
+                              head_dim, scale, positions, cos_sin, cos_sin_stride, workspace, workspace_bytes, flags,
+                              dev_status, stream, &app);
 }
 
 // ------------------------------------------------------------------------------------------------

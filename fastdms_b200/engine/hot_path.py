@@ -4,11 +4,12 @@ Order of work inside a step (the reference's order: engine/model_runner.py:713-7
 models/llama.py:138-201 per layer, model_runner.py:681-711 record):
 
     expiry (all layers)  ->  decode metadata (all layers, live += 1)
-    ->  per layer: fused decision + RoPE + FP8 store, then compact attention
+    ->  per layer: DMS decision + RoPE + FP8 store + compact attention (one launch when the pools
+        are FP8 and head_dim is 64/128, else a store launch and an attention launch)
     ->  decision recording (all layers)  ->  positions += 1
 
 Everything is a launch on device-resident state, so the whole step is ONE graph replay:
-2 + 2 * layers + 1 kernels of this library plus one position increment.
+2 + layers + 1 kernels of this library (2 + 2 * layers + 1 unfused) plus one position increment.
 
 `DecodeHotPath` is driven either with activations that already sit in its device buffers
 (`step_device`) or with host buffers (`step_host`: pinned host -> device copies of the step's
@@ -21,14 +22,16 @@ import torch
 from fastdms_b200 import _lib
 from fastdms_b200.engine.compact_kv import CompactKVManager
 from fastdms_b200.layers.compact_attention import (compact_decode_attention,
-                                                   fused_dms_rope_store_compact_decode)
+                                                   fused_dms_rope_store_compact_decode,
+                                                   fused_store_decode_attention)
 
 
 class DecodeHotPath:
     def __init__(self, manager: CompactKVManager, seqs: list, *, num_q_heads: int, window_size: int,
                  alpha_scale: float, alpha_offset: float, cos_sin_cache: torch.Tensor,
                  act_dtype: torch.dtype = torch.bfloat16, scale: float | None = None,
-                 expire_every_step: bool = True, use_cuda_graph: bool = True, overlap: bool = True):
+                 expire_every_step: bool = True, use_cuda_graph: bool = True, overlap: bool = True,
+                 fuse_store: bool | None = None):
         self.m = manager
         self.seqs = list(seqs)
         self.states = manager._states(self.seqs)
@@ -59,7 +62,12 @@ class DecodeHotPath:
         self._h_q = self._h_k = self._h_v = self._h_out = self._h_pos = None
         self.graph = None
         self.use_cuda_graph = use_cuda_graph
-        self.launches_per_step = 2 + 2 * L + 1
+        can_fuse = (manager.compact_dtype == torch.float8_e4m3fn and D in (64, 128)
+                    and act_dtype in (torch.bfloat16, torch.float16, torch.float32))
+        if fuse_store and not can_fuse:
+            raise ValueError("fuse_store needs FP8 e4m3 pools and head_dim 64 or 128")
+        self.fuse_store = can_fuse if fuse_store is None else bool(fuse_store)
+        self.launches_per_step = 2 + (1 if self.fuse_store else 2) * L + 1
         _lib.attn_workspace(dev, B, Hk, D)          # allocate outside any capture
 
     # ---------------------------------------------------------------- the step itself
@@ -71,13 +79,23 @@ class DecodeHotPath:
         for l in range(self.L):
             ks, vs = m.layer_scales(l)
             ck, cv = m.compact_k_per_layer[l], m.compact_v_per_layer[l]
+            bt = None if self.block_tables is None else self.block_tables[l]
+            if self.fuse_store:
+                # Layer 0 follows the metadata kernel, whose outputs (live counts, bases) the attention
+                # prologue reads before its dependency wait: no overlap there.  Later layers follow the
+                # previous layer's attention, which writes nothing this launch reads before the wait.
+                fused_store_decode_attention(
+                    self.q[l], self.k[l], self.v[l], self.cos_sin_cache, ck, cv, self.base[l], self.live[l],
+                    self.evict_all[l], self.positions, num_kv_heads=self.Hk, alpha_scale=self.alpha_scale,
+                    alpha_offset=self.alpha_offset, scale=self.scale, block_tables=bt, k_scale=ks, v_scale=vs,
+                    out=self.out[l], overlap_previous_kernel=self.overlap and l > 0)
+                continue
             fused_dms_rope_store_compact_decode(
                 self.q[l], self.k[l], self.v[l], self.cos_sin_cache, ck, cv, self.slot[l], self.evict_all[l],
                 self.positions, num_kv_heads=self.Hk, alpha_scale=self.alpha_scale, alpha_offset=self.alpha_offset,
                 store_q=True, store_transient_k=False, k_scale=ks, v_scale=vs)
             compact_decode_attention(
-                self.q[l], ck, cv, self.base[l], self.live[l], scale=self.scale,
-                block_tables=None if self.block_tables is None else self.block_tables[l],
+                self.q[l], ck, cv, self.base[l], self.live[l], scale=self.scale, block_tables=bt,
                 k_scale=ks, v_scale=vs, out=self.out[l], overlap_previous_kernel=self.overlap)
         m.record_device(self.slots_t, self.positions, self.evict_all)
         self.positions.add_(1)

@@ -13,7 +13,8 @@ import torch
 import torch.nn.functional as F
 from torch import nn
 
-from fastdms_b200.layers.compact_attention import compact_decode_attention, store_compact_kvcache
+from fastdms_b200.layers.compact_attention import (compact_decode_attention, fused_store_decode_attention,
+                                                   store_compact_kvcache)
 from fastdms_b200.utils.context import get_context
 from fastdms_b200.utils.profiler import get_profiler
 
@@ -43,6 +44,30 @@ class Attention(nn.Module):
         self.compact_k_cache = self.compact_v_cache = torch.tensor([])
         self.compact_k_scale = self.compact_v_scale = None
         self.layer_id = -1
+
+    def can_fuse_store(self) -> bool:
+        """True when decision + RoPE + FP8 store + attention can run as one launch for this layer."""
+        return (self.compact_k_cache.numel() > 0 and self.compact_k_cache.dtype == torch.float8_e4m3fn
+                and self.head_dim in (64, 128) and self.num_heads // self.num_kv_heads <= 8)
+
+    def forward_fused_store(self, q, k, v, *, positions, cos_sin_cache, evict_out, alpha_scale, alpha_offset):
+        """Decode only: q/k/v are pre-RoPE; appends the new row to the compact pool and attends."""
+        context = get_context()
+        if context.is_prefill or not context.compact_kv_enabled:
+            raise RuntimeError("forward_fused_store is a compact-KV decode operation")
+        if context.compact_base_offsets is None or context.compact_live_counts is None:
+            raise RuntimeError("compact KV decode requires compact_base_offsets and compact_live_counts")
+        base, live, bt = context.compact_base_offsets, context.compact_live_counts, context.compact_block_tables
+        if base.ndim == 3:
+            base, live = base[self.layer_id], live[self.layer_id]
+        if bt is not None and bt.ndim == 4:
+            bt = bt[self.layer_id]
+        with get_profiler().cuda_phase("compact_store_decode_attn"):
+            return fused_store_decode_attention(
+                q, k, v, cos_sin_cache, self.compact_k_cache, self.compact_v_cache, base, live, evict_out, positions,
+                num_kv_heads=self.num_kv_heads, alpha_scale=alpha_scale, alpha_offset=alpha_offset, scale=self.scale,
+                block_tables=bt, k_scale=self.compact_k_scale, v_scale=self.compact_v_scale,
+                overlap_previous_kernel=context.overlap_store_and_attention)
 
     def forward(self, q, k, v, *, compact_append_stored: bool = False, compact_q_rope: bool = False,
                 positions: torch.Tensor | None = None, cos_sin_cache: torch.Tensor | None = None):

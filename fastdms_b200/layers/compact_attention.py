@@ -36,6 +36,14 @@ def dms_decode_store_transient_k_enabled() -> bool:
     return os.environ.get("FASTDMS_DMS_DECODE_STORE_TRANSIENT_K", "0").strip().lower() in {"1", "true", "yes", "on"}
 
 
+def fused_store_attention_enabled() -> bool:
+    """Whether decode layers with FP8 pools run decision + RoPE + store + attention as one launch
+    (`FDMS_FUSED_STORE_ATTENTION`, default on; off gives the reference's two-kernel sequence)."""
+    import os
+
+    return os.environ.get("FDMS_FUSED_STORE_ATTENTION", "1").strip().lower() in {"1", "true", "yes", "on"}
+
+
 def compact_attention_inline_q_rope_enabled() -> bool:
     return True
 
@@ -161,6 +169,107 @@ def compact_decode_attention(
             out.data_ptr(), _lib.dtype_code(out.dtype), out.stride(0), out.stride(1),
             batch, num_q_heads, num_kv_heads, head_dim, float(scale),
             _lib.ptr(rope_pos), _lib.ptr(rope_cs), cs_stride,
+            ws.data_ptr(), ws.numel(), _lib.ATTN_OVERLAP_PREVIOUS if overlap_previous_kernel else 0,
+            status.data_ptr(), _lib.stream_ptr(dev))
+    _lib.check(rc)
+    return out
+
+
+def fused_store_decode_attention(
+    q: torch.Tensor,
+    k: torch.Tensor,
+    v: torch.Tensor,
+    cos_sin_cache: torch.Tensor,
+    compact_k: torch.Tensor,
+    compact_v: torch.Tensor,
+    base_offsets: torch.Tensor,
+    live_counts: torch.Tensor,
+    evict_out: torch.Tensor | None,
+    positions: torch.Tensor,
+    *,
+    num_kv_heads: int,
+    alpha_scale: float,
+    alpha_offset: float,
+    scale: float | None = None,
+    block_tables: torch.Tensor | None = None,
+    k_scale: torch.Tensor | None = None,
+    v_scale: torch.Tensor | None = None,
+    out: torch.Tensor | None = None,
+    overlap_previous_kernel: bool = False,
+) -> torch.Tensor:
+    """`fused_dms_rope_store_compact_decode(store_q=False, store_transient_k=False)` followed by
+    `compact_decode_attention(q_rope_positions=..., q_rope_cos_sin_cache=...)` in ONE launch.
+
+    `live_counts` already counts the token being appended; its row is the last logical row of every
+    span (row base + live - 1, or through the block table).  The new K/V rows land in the pool with
+    the same bytes the separate store kernel writes, `evict_out` gets the same decisions, q/k/v are
+    left untouched, and the attention output is returned.  FP8 pools, head_dim 64 or 128 only."""
+    if q.ndim != 3 or k.ndim != 3 or v.ndim != 3:
+        raise ValueError("expected q/k/v as [batch, heads, head_dim]")
+    if k.shape != v.shape:
+        raise ValueError(f"k/value shape mismatch: {k.shape} != {v.shape}")
+    batch, num_q_heads, head_dim = q.shape
+    if k.shape != (batch, num_kv_heads, head_dim):
+        raise ValueError(f"q/k shape mismatch: q={q.shape}, k={k.shape}, num_kv_heads={num_kv_heads}")
+    if num_q_heads % num_kv_heads != 0:
+        raise ValueError(f"q_heads={num_q_heads} must be divisible by kv_heads={num_kv_heads}")
+    if compact_k.shape != compact_v.shape or compact_k.ndim != 2 or compact_k.shape[1] != head_dim:
+        raise ValueError(f"expected compact cache [slots, {head_dim}], got {compact_k.shape}/{compact_v.shape}")
+    if base_offsets.shape != (batch, num_kv_heads) or live_counts.shape != (batch, num_kv_heads):
+        raise ValueError("base_offsets and live_counts must both be [batch, kv_heads]")
+    if evict_out is not None and (evict_out.shape != (batch, num_kv_heads) or evict_out.dtype != torch.bool):
+        raise ValueError(f"expected evict_out bool {(batch, num_kv_heads)}, got {tuple(evict_out.shape)} {evict_out.dtype}")
+    if positions.shape != (batch,):
+        raise ValueError(f"expected positions {(batch,)}, got {tuple(positions.shape)}")
+    if cos_sin_cache.ndim != 3 or cos_sin_cache.shape[2] != head_dim:
+        raise ValueError(f"expected cos_sin_cache [positions, 1, {head_dim}], got {tuple(cos_sin_cache.shape)}")
+    if q.dtype != k.dtype or k.dtype != v.dtype:
+        raise ValueError("q, k and v must share a dtype")
+    _lib.require_cuda(q, k, v, compact_k, compact_v)
+    dev = q.device
+    for name, t in (("q", q), ("k", k), ("v", v)):
+        _inner_contiguous(t, name)
+    if not compact_k.is_contiguous() or not compact_v.is_contiguous():
+        raise ValueError("compact caches must be contiguous")
+    base_offsets = base_offsets.to(device=dev, dtype=torch.int32)
+    live_counts = live_counts.to(device=dev, dtype=torch.int32)
+    if base_offsets.stride(1) != 1 or live_counts.stride(1) != 1 or base_offsets.stride(0) != live_counts.stride(0):
+        base_offsets, live_counts = base_offsets.contiguous(), live_counts.contiguous()
+    bt_sb = bt_sh = bt_pages = 0
+    if block_tables is not None:
+        if block_tables.ndim != 3 or block_tables.shape[:2] != (batch, num_kv_heads):
+            raise ValueError(f"expected block_tables [batch, kv_heads, pages], got {tuple(block_tables.shape)}")
+        block_tables = block_tables.to(device=dev, dtype=torch.int32)
+        if block_tables.stride(2) != 1:
+            block_tables = block_tables.contiguous()
+        bt_sb, bt_sh, bt_pages = block_tables.stride(0), block_tables.stride(1), block_tables.shape[2]
+    k_scale, v_scale = _scales(k_scale, v_scale, num_kv_heads, dev)
+    positions = positions.to(device=dev, dtype=torch.int64).contiguous()
+    cos_sin_cache = cos_sin_cache.to(device=dev, dtype=torch.float32)
+    if cos_sin_cache.stride(2) != 1:
+        cos_sin_cache = cos_sin_cache.contiguous()
+    if out is None:
+        out = torch.empty_like(q)
+    elif out.shape != q.shape or out.stride(-1) != 1:
+        raise ValueError("out must have q's shape and a contiguous last dimension")
+    if scale is None:
+        scale = head_dim ** -0.5
+    ev_u8 = None if evict_out is None else evict_out.view(torch.uint8)
+    if ev_u8 is not None and ev_u8.stride(1) != 1:
+        raise ValueError("evict_out must be contiguous in its last dimension")
+    ws = _lib.attn_workspace(dev, batch, num_kv_heads, head_dim)
+    status = _lib.status_word(dev)
+    with torch.cuda.device(dev):
+        rc = _lib.lib().fdms_attn_decode_append(
+            q.data_ptr(), k.data_ptr(), v.data_ptr(), _lib.dtype_code(q.dtype),
+            q.stride(0), q.stride(1), k.stride(0), k.stride(1), v.stride(0), v.stride(1),
+            compact_k.data_ptr(), compact_v.data_ptr(), _lib.dtype_code(compact_k.dtype), compact_k.shape[0],
+            base_offsets.data_ptr(), live_counts.data_ptr(), live_counts.stride(0),
+            _lib.ptr(block_tables), bt_sb, bt_sh, bt_pages, _lib.ptr(k_scale), _lib.ptr(v_scale),
+            cos_sin_cache.data_ptr(), cos_sin_cache.stride(0), positions.data_ptr(),
+            _lib.ptr(ev_u8), ev_u8.stride(0) if ev_u8 is not None else 0, float(alpha_scale), float(alpha_offset),
+            out.data_ptr(), _lib.dtype_code(out.dtype), out.stride(0), out.stride(1),
+            batch, num_q_heads, num_kv_heads, head_dim, float(scale),
             ws.data_ptr(), ws.numel(), _lib.ATTN_OVERLAP_PREVIOUS if overlap_previous_kernel else 0,
             status.data_ptr(), _lib.stream_ptr(dev))
     _lib.check(rc)

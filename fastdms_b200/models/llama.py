@@ -17,7 +17,8 @@ from fastdms_b200.engine.dms import extract_dms_eviction_decisions
 from fastdms_b200.layers.activation import SiluAndMul
 from fastdms_b200.layers.attention import Attention
 from fastdms_b200.layers.compact_attention import (dms_decode_store_transient_k_enabled,
-                                                   fused_dms_rope_store_compact_decode)
+                                                   fused_dms_rope_store_compact_decode,
+                                                   fused_store_attention_enabled)
 from fastdms_b200.layers.embed_head import ParallelLMHead, VocabParallelEmbedding
 from fastdms_b200.layers.layernorm import RMSNorm
 from fastdms_b200.layers.linear import (MergedColumnParallelLinear, QKVParallelLinear, RowParallelLinear,
@@ -99,6 +100,14 @@ class LlamaAttention(nn.Module):
                     slot = slot[layer_id]
                 if evict_out is None:
                     evict_out = torch.empty((q.shape[0], self.num_kv_heads), device=q.device, dtype=torch.bool)
+                if (self.attn.can_fuse_store() and not dms_decode_store_transient_k_enabled()
+                        and fused_store_attention_enabled()):
+                    if context.dms_layer_evictions is not None:
+                        context.dms_layer_evictions[layer_id] = evict_out
+                    o = self.attn.forward_fused_store(
+                        q, k, v, positions=positions, cos_sin_cache=cache, evict_out=evict_out,
+                        alpha_scale=context.dms_alpha_scale, alpha_offset=context.dms_alpha_offset)
+                    return self.o_proj(o.flatten(1, -1))
                 with prof.cuda_phase("dms_rope_store"):
                     fused_dms_rope_store_compact_decode(
                         q, k, v, cache, self.attn.compact_k_cache, self.attn.compact_v_cache, slot, evict_out,

@@ -90,6 +90,28 @@ int32_t fdms_attn_decode(
     const int64_t* q_rope_positions, const float* q_rope_cos_sin, int64_t cos_sin_stride,
     void* workspace, int64_t workspace_bytes, int32_t flags, int32_t* dev_status, void* stream);
 
+/* Fused decode step of one layer: fdms_store_decode and fdms_attn_decode in ONE launch (the
+ * reference keeps them as two kernels, layers/compact_attention.py:1010-1113 and :1116-1336).
+ * live_counts must already count the new token (fdms_build_decode_metadata); its row is the last
+ * logical row of each span.  Per span, the CTA that owns the last page reads the DMS decision
+ * (evict_out, optional), rotates k, quantises k and v exactly like fdms_store_decode, writes the row to
+ * the pool and attends to it; every CTA rotates q on the fly (q itself is left untouched, as with
+ * store_q = 0).  FP8 e4m3 pools, head_dim 64 or 128, group size <= 8; q and k rows 16-byte aligned.
+ * With FDMS_ATTN_OVERLAP_PREVIOUS the preceding kernel may still be producing q, k and v: they are
+ * read after it has completed, pool pages are prefetched before. */
+int32_t fdms_attn_decode_append(
+    const void* q, const void* k, const void* v, int32_t act_dtype,
+    int64_t q_stride_b, int64_t q_stride_h, int64_t k_stride_b, int64_t k_stride_h, int64_t v_stride_b, int64_t v_stride_h,
+    void* k_pool, void* v_pool, int32_t kv_dtype, int64_t pool_rows,
+    const int32_t* base_offsets, const int32_t* live_counts, int64_t meta_stride_b,
+    const int32_t* block_tables, int64_t bt_stride_b, int64_t bt_stride_h, int32_t bt_max_pages,
+    const float* k_scale, const float* v_scale,
+    const float* cos_sin, int64_t cos_sin_stride, const int64_t* positions,
+    uint8_t* evict_out, int64_t evict_stride_b, double alpha_scale, double alpha_offset,
+    void* out, int32_t out_dtype, int64_t out_stride_b, int64_t out_stride_h,
+    int32_t batch, int32_t num_q_heads, int32_t num_kv_heads, int32_t head_dim, float scale,
+    void* workspace, int64_t workspace_bytes, int32_t flags, int32_t* dev_status, void* stream);
+
 /* Decode attention with the split-K scratch built into the library, for callers that cannot
  * allocate device memory (no counterpart in the reference, which allocates its partial buffers with
  * torch.empty on every call).  Same arguments and results as fdms_attn_decode without workspace and

@@ -321,6 +321,61 @@ def test_attention_inline_q_rope(ops_golden, dev):
                                  torch.from_numpy(live).to(dev), q_rope_positions=positions)
 
 
+@pytest.mark.parametrize("D,G,paged,scaled,mean", [(64, 4, True, True, 200), (64, 4, False, False, 200), (128, 4, True, False, 200),
+                                                   (64, 8, False, True, 200), (64, 4, True, True, 5000), (128, 2, False, True, 9000)])
+def test_fused_store_attention_equals_store_then_attention(dev, D, G, paged, scaled, mean):
+    """One launch (decision + RoPE + FP8 store + attention) against the two separate kernels:
+    identical decisions, identical pool bytes, identical attention output; spans whose new row
+    opens a fresh page (live % 16 == 1) and fills one (live % 16 == 0) are included."""
+    from fastdms_b200.layers.compact_attention import (compact_decode_attention, fused_dms_rope_store_compact_decode,
+                                                       fused_store_decode_attention)
+    rng = np.random.default_rng(70 + D + G)
+    B, Hk = 4, 2
+    qn, kq, vq, base, live, bt, ks, vs = _config2_case(rng, B, Hk, G, D, mean, 80, 17, paged)
+    live[0, 0], live[1, 1], live[2, 0] = 17, 32, 1                           # fresh page, full page, single row
+    qb = torch.from_numpy(qn).to(dev).to(torch.bfloat16)
+    qb[:, 0::G, -1] = torch.tensor([0.01, 0.06, 0.05, 0.08, 0.10, -0.01, 0.3, -0.2], device=dev).view(B, Hk).to(torch.bfloat16)
+    k = torch.from_numpy(rng.standard_normal((B, Hk, D)).astype(np.float32)).to(dev).to(torch.bfloat16)
+    v = torch.from_numpy(rng.standard_normal((B, Hk, D)).astype(np.float32)).to(dev).to(torch.bfloat16)
+    positions = torch.tensor([5, 100, 0, 777], device=dev)
+    half = D // 2
+    inv = 1.0 / (500000.0 ** (np.arange(half, dtype=np.float32) / half))
+    ang = np.arange(800, dtype=np.float32)[:, None] * inv[None, :]
+    cache = torch.from_numpy(np.concatenate([np.cos(ang), np.sin(ang)], axis=1).astype(np.float32)).to(dev).unsqueeze(1)
+    live_t, base_t = torch.from_numpy(live).to(dev), torch.from_numpy(base).to(dev)
+    bt_t = None if bt is None else torch.from_numpy(bt).to(dev)
+    kw = dict(k_scale=torch.from_numpy(ks).to(dev), v_scale=torch.from_numpy(vs).to(dev)) if scaled else {}
+    rows = kq.shape[0]
+    pool_k = torch.zeros((rows, D), dtype=torch.uint8, device=dev)
+    pool_k[: kq.shape[0]] = torch.from_numpy(kq).to(dev)
+    pool_v = torch.zeros((rows, D), dtype=torch.uint8, device=dev)
+    pool_v[: vq.shape[0]] = torch.from_numpy(vq).to(dev)
+    # slot of the appended row = logical row live - 1
+    idx = live - 1
+    slot = (np.take_along_axis(bt, (idx // 16)[..., None], axis=2)[..., 0] * 16 + idx % 16) if paged else base + idx
+    slot_t = torch.from_numpy(slot.astype(np.int32)).to(dev)
+
+    ck1, cv1 = pool_k.clone().view(torch.float8_e4m3fn), pool_v.clone().view(torch.float8_e4m3fn)
+    q1, k1 = qb.clone(), k.clone()
+    ev1 = torch.empty((B, Hk), dtype=torch.bool, device=dev)
+    fused_dms_rope_store_compact_decode(q1, k1, v, cache, ck1, cv1, slot_t, ev1, positions, num_kv_heads=Hk,
+                                        alpha_scale=100.0, alpha_offset=5.0, store_transient_k=False, **kw)
+    want = compact_decode_attention(q1, ck1, cv1, base_t, live_t, block_tables=bt_t, **kw)
+
+    ck2, cv2 = pool_k.clone().view(torch.float8_e4m3fn), pool_v.clone().view(torch.float8_e4m3fn)
+    q2 = qb.clone()
+    ev2 = torch.empty((B, Hk), dtype=torch.bool, device=dev)
+    got = fused_store_decode_attention(q2, k, v, cache, ck2, cv2, base_t, live_t, ev2, positions, num_kv_heads=Hk,
+                                       alpha_scale=100.0, alpha_offset=5.0, block_tables=bt_t, **kw)
+    assert torch.equal(ev1, ev2)
+    assert torch.equal(ck1.view(torch.uint8), ck2.view(torch.uint8)) and torch.equal(cv1.view(torch.uint8), cv2.view(torch.uint8))
+    assert torch.equal(q2, qb)                                     # q is left untouched
+    assert torch.equal(got, want)
+    with pytest.raises(ValueError):
+        fused_store_decode_attention(q2, k, v, cache, ck2.view(torch.uint8).float(), cv2.view(torch.uint8).float(), base_t,
+                                     live_t, ev2, positions, num_kv_heads=Hk, alpha_scale=100.0, alpha_offset=5.0)
+
+
 def test_attention_argument_errors(dev):
     from fastdms_b200.layers.compact_attention import compact_decode_attention
     q = torch.zeros((2, 8, 64), dtype=torch.bfloat16, device=dev)
