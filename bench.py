@@ -320,12 +320,19 @@ def time_attention_kernel(hp, dev, reps: int, overlap: bool):
     """Average duration of one attention launch: a CUDA graph of the 16 per-layer launches (16
     distinct pools, 168 MB of K/V in total, more than L2) replayed `reps` times between two events."""
     import torch
-    from fastdms_b200.layers.compact_attention import compact_decode_attention
+    from fastdms_b200.layers.compact_attention import compact_decode_attention, fused_store_decode_attention
     m = hp.m
 
     def enqueue():
         for l in range(L):
             ks, vs = m.layer_scales(l)
+            if hp.fuse_store:      # the launch the decode step makes: decision + RoPE + FP8 store + attention
+                fused_store_decode_attention(
+                    hp.q[l], hp.k[l], hp.v[l], hp.cos_sin_cache, m.compact_k_per_layer[l], m.compact_v_per_layer[l],
+                    hp.base[l], hp.live[l], hp.evict_all[l], hp.positions, num_kv_heads=HK, alpha_scale=ALPHA_SCALE,
+                    alpha_offset=ALPHA_OFFSET, block_tables=hp.block_tables[l], k_scale=ks, v_scale=vs, out=hp.out[l],
+                    overlap_previous_kernel=overlap and l > 0)
+                continue
             compact_decode_attention(hp.q[l], m.compact_k_per_layer[l], m.compact_v_per_layer[l], hp.base[l],
                                      hp.live[l], block_tables=hp.block_tables[l], k_scale=ks, v_scale=vs, out=hp.out[l],
                                      overlap_previous_kernel=overlap)
@@ -441,11 +448,12 @@ def run_ours(args) -> None:
             "e2e": {"value": e2e_value, "unit": "tok/s", "ms_per_step": e2e_ms,
                     "h2d_bytes_per_step": hp.h2d_bytes_per_step, "d2h_bytes_per_step": hp.d2h_bytes_per_step},
             "gpu_launches": hp.launches_per_step * args.steps,
-            "roofline": {"bound": "hbm", "kernel": "attn_decode_fast_kernel<64>", "achieved": achieved, "peak": peak,
+            "roofline": {"bound": "hbm", "kernel": "attn_decode_direct_kernel<64, 3, %s>" % ("true" if hp.fuse_store else "false"), "achieved": achieved, "peak": peak,
                          "unit": "GB/s", "frac": achieved / peak, "peak_source": f"{peak_kind} (MEASURED_PEAKS.json hbm_gbs)",
                          "traffic": None, "bytes_per_launch": bytes_per_launch, "us_per_launch": ov_launch_s * 1e6,
                          "us_per_launch_without_overlap": per_launch_s * 1e6, "launches_timed": attn_launches,
-                         "how": "CUDA events around a graph of the 16 per-layer launches replayed back to back; "
+                         "how": "CUDA events around a graph of the 16 per-layer launches (the fused decision + RoPE + "
+                                "FP8 store + attention launch of the decode step) replayed back to back; "
                                 "launches use programmatic dependent launch as in the decode step, so a launch's "
                                 "preamble and page prefetch overlap the tail of the one before it; "
                                 "us_per_launch_without_overlap is the same stream with ordinary launches"},
