@@ -83,10 +83,6 @@ __device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t by
         "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
         ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar)) : "memory");
 }
-// Barrier 2: the two helper warps that build the appended row (arrive) and the warp that owns the
-// span's last page (sync); 96 threads.
-__device__ __forceinline__ void newrow_arrive() { asm volatile("bar.arrive 2, 96;" ::: "memory"); }
-__device__ __forceinline__ void newrow_wait() { asm volatile("bar.sync 2, 96;" ::: "memory"); }
 __device__ __forceinline__ void consumer_bar() {
     asm volatile("bar.sync 1, %0;" ::"n"(kConsumerThreads) : "memory");
 }
@@ -766,20 +762,14 @@ __global__ void __launch_bounds__(kDirectThreads, (D == 64 ? 2 : 1)) attn_decode
     int unit_kind = -1, unit_gg = 0, unit_i0 = 0;        // 0 = q, 1 = k, 2 = v
     float ucos[8], usin[8];
     int64_t tail_row = -1;                               // pool row of the new token (tail CTA, unit threads)
-    bool tail_cta = false, helper = false;
+    bool tail_cta = false;
     if (APPEND) {
         tail_cta = live > 0 && (tail_pi % nparts) == part;
-        // q units sit in warps 0-1 (2-3 when those build the new row); K units and V units in the two
-        // warps after the one that owns the last page.  Kinds never share a warp, so their loads are in
-        // flight side by side, and only the owner of the last page waits for the new row.
-        const int wt = tail_cta ? ((tail_pi - part) / nparts) % kConsumerWarps : -4;
-        const int wk = (wt + 1) % kConsumerWarps, wv = (wt + 2) % kConsumerWarps;
-        const int wq0 = (tail_cta && (wk <= 1 || wv <= 1)) ? 2 + ((wk == 2 || wv == 2 || wk == 3 || wv == 3) ? 2 : 0) : 0;
-        const int qt = tid - 32 * wq0;
-        if (qt >= 0 && qt < G * kUnitsPerRow) { unit_kind = 0; unit_gg = qt / kUnitsPerRow; unit_i0 = 8 * (qt % kUnitsPerRow); }
-        else if (tail_cta && warp == wk && lane < kUnitsPerRow) { unit_kind = 1; unit_i0 = 8 * lane; }
-        else if (tail_cta && warp == wv && lane < D / 8) { unit_kind = 2; unit_i0 = 8 * lane; }
-        helper = tail_cta && (warp == wk || warp == wv);
+        // q units sit in warps 0-1, K units in warp 2, V units in warp 3: the three kinds wait for
+        // their loads side by side instead of one after the other inside a diverged warp
+        if (tid < G * kUnitsPerRow) { unit_kind = 0; unit_gg = tid / kUnitsPerRow; unit_i0 = 8 * (tid % kUnitsPerRow); }
+        else if (tail_cta && warp == 2 && lane < kUnitsPerRow) { unit_kind = 1; unit_i0 = 8 * lane; }
+        else if (tail_cta && warp == 3 && lane < D / 8) { unit_kind = 2; unit_i0 = 8 * lane; }
         if (unit_kind == 0 || unit_kind == 1) {
             const float* cs = p.rope_cs + p.rope_pos[b] * p.rope_stride;
             const float4 c0 = *(const float4*)(cs + unit_i0), c1 = *(const float4*)(cs + unit_i0 + 4);
@@ -832,58 +822,51 @@ __global__ void __launch_bounds__(kDirectThreads, (D == 64 ? 2 : 1)) attn_decode
     const float sl2 = p.scale * (p.k_scale ? p.k_scale[h] : 1.0f) * kLog2e;
     uint32_t qa[C::kKSteps][2];
     if (APPEND) {
-        // loads of every unit kind first (K / V units keep theirs in registers across the barrier) ...
-        float x1[8], x2[8];
         if (unit_kind == 0 || unit_kind == 1) {
-            const void* src = unit_kind == 0 ? p.q : p.k_new;
-            const int64_t row = unit_kind == 0 ? (int64_t)b * p.q_sb + (int64_t)(h * G + unit_gg) * p.q_sh
-                                               : (int64_t)b * p.kn_sb + (int64_t)h * p.kn_sh;
+            const bool isq = unit_kind == 0;
+            const void* src = isq ? p.q : p.k_new;
+            const int64_t row = isq ? (int64_t)b * p.q_sb + (int64_t)(h * G + unit_gg) * p.q_sh
+                                    : (int64_t)b * p.kn_sb + (int64_t)h * p.kn_sh;
+            float x1[8], x2[8], lo[8], hi[8];
             load8_as_float(src, row + unit_i0, p.q_dtype, x1);
             load8_as_float(src, row + half + unit_i0, p.q_dtype, x2);
-        } else if (unit_kind == 2) {
-            load8_as_float(p.v_new, (int64_t)b * p.vn_sb + (int64_t)h * p.vn_sh + unit_i0, p.q_dtype, x1);
-        }
-        // ... then the rotated q, which every warp waits for ...
-        if (unit_kind == 0) {
-            if (unit_gg == 0 && unit_i0 == half - 8) {
+            if (isq && unit_gg == 0 && unit_i0 == half - 8) {
                 // the group's first q head carries the DMS decision in its last channel
                 if (tail_cta && p.evict_out) p.evict_out[(int64_t)b * p.evict_sb + h] = p.rule.evict(x2[7]) ? 1 : 0;
                 x2[7] = 0.0f;
             }
-            float lo[8], hi[8];
             rotate8(x1, x2, ucos, usin, p.q_dtype, lo, hi);
-            __half2* dl = (__half2*)(s_q + unit_gg * D + unit_i0);
-            __half2* dh = (__half2*)(s_q + unit_gg * D + half + unit_i0);
+            if (isq) {
+                __half2* dl = (__half2*)(s_q + unit_gg * D + unit_i0);
+                __half2* dh = (__half2*)(s_q + unit_gg * D + half + unit_i0);
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                dl[i] = __floats2half2_rn(lo[2 * i], lo[2 * i + 1]);
-                dh[i] = __floats2half2_rn(hi[2 * i], hi[2 * i + 1]);
+                for (int i = 0; i < 4; ++i) {
+                    dl[i] = __floats2half2_rn(lo[2 * i], lo[2 * i + 1]);
+                    dh[i] = __floats2half2_rn(hi[2 * i], hi[2 * i + 1]);
+                }
+            } else {
+                const float ksc = p.k_scale ? p.k_scale[h] : 1.0f;
+                const bool dv = p.k_scale != nullptr;
+                const uint2 bl = make_uint2(quant4(lo[0], lo[1], lo[2], lo[3], dv, ksc), quant4(lo[4], lo[5], lo[6], lo[7], dv, ksc));
+                const uint2 bh = make_uint2(quant4(hi[0], hi[1], hi[2], hi[3], dv, ksc), quant4(hi[4], hi[5], hi[6], hi[7], dv, ksc));
+                *(uint2*)(s_new + unit_i0) = bl;
+                *(uint2*)(s_new + half + unit_i0) = bh;
+                if (tail_row >= 0) {
+                    *(uint2*)(p.k_pool_w + tail_row * D + unit_i0) = bl;
+                    *(uint2*)(p.k_pool_w + tail_row * D + half + unit_i0) = bh;
+                }
+                if (tail_row == -2 && unit_i0 == 0 && p.dev_status) atomicOr(p.dev_status, FDMS_DEV_BAD_INDEX);
             }
-        }
-        __syncthreads();
-        // ... then the new row, which only the owner of the last page waits for (barrier 2)
-        if (unit_kind == 1) {
-            float lo[8], hi[8];
-            rotate8(x1, x2, ucos, usin, p.q_dtype, lo, hi);
-            const float ksc = p.k_scale ? p.k_scale[h] : 1.0f;
-            const bool dv = p.k_scale != nullptr;
-            const uint2 bl = make_uint2(quant4(lo[0], lo[1], lo[2], lo[3], dv, ksc), quant4(lo[4], lo[5], lo[6], lo[7], dv, ksc));
-            const uint2 bh = make_uint2(quant4(hi[0], hi[1], hi[2], hi[3], dv, ksc), quant4(hi[4], hi[5], hi[6], hi[7], dv, ksc));
-            *(uint2*)(s_new + unit_i0) = bl;
-            *(uint2*)(s_new + half + unit_i0) = bh;
-            if (tail_row >= 0) {
-                *(uint2*)(p.k_pool_w + tail_row * D + unit_i0) = bl;
-                *(uint2*)(p.k_pool_w + tail_row * D + half + unit_i0) = bh;
-            }
-            if (tail_row == -2 && unit_i0 == 0 && p.dev_status) atomicOr(p.dev_status, FDMS_DEV_BAD_INDEX);
         } else if (unit_kind == 2) {
+            float x[8];
+            load8_as_float(p.v_new, (int64_t)b * p.vn_sb + (int64_t)h * p.vn_sh + unit_i0, p.q_dtype, x);
             const float vsc = p.v_scale ? p.v_scale[h] : 1.0f;
             const bool dv = p.v_scale != nullptr;
-            const uint2 bv = make_uint2(quant4(x1[0], x1[1], x1[2], x1[3], dv, vsc), quant4(x1[4], x1[5], x1[6], x1[7], dv, vsc));
+            const uint2 bv = make_uint2(quant4(x[0], x[1], x[2], x[3], dv, vsc), quant4(x[4], x[5], x[6], x[7], dv, vsc));
             *(uint2*)(s_new + D + unit_i0) = bv;
             if (tail_row >= 0) *(uint2*)(p.v_pool_w + tail_row * D + unit_i0) = bv;
         }
-        if (helper) newrow_arrive();
+        __syncthreads();
 #pragma unroll
         for (int ch = 0; ch < C::kCh; ++ch) {
             uint4 w0 = make_uint4(0u, 0u, 0u, 0u), w1 = w0;
@@ -913,7 +896,6 @@ __global__ void __launch_bounds__(kDirectThreads, (D == 64 ? 2 : 1)) attn_decode
             const int i = i0 + s;
             if (i < nw) {
                 if (APPEND && own_tail && pg0 + i * stride_pg == tail_pi) {
-                    newrow_wait();
 #pragma unroll
                     for (int u = 0; u < 2; ++u) {
 #pragma unroll
