@@ -238,48 +238,6 @@ __device__ __forceinline__ void load_q_frags(const AttnParams& p, int b, int h, 
     }
 }
 
-// 8 consecutive activation elements (bf16 / f16 / f32) starting at element index `e0` as floats;
-// the address must be 16-byte aligned.
-__device__ __forceinline__ void load8_as_float(const void* base, int64_t e0, int dt, float (&x)[8]) {
-    if (dt == FDMS_F32) {
-        const float4* p4 = (const float4*)((const float*)base + e0);
-        const float4 a = p4[0], b = p4[1];
-        x[0] = a.x; x[1] = a.y; x[2] = a.z; x[3] = a.w; x[4] = b.x; x[5] = b.y; x[6] = b.z; x[7] = b.w;
-    } else {
-        const uint4 a = *(const uint4*)((const uint16_t*)base + e0);
-        const uint32_t w[4] = {a.x, a.y, a.z, a.w};
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            if (dt == FDMS_BF16) {
-                x[2 * i] = __uint_as_float(w[i] << 16);
-                x[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
-            } else {
-                const __half2 h2 = *(const __half2*)&w[i];
-                x[2 * i] = __low2float(h2);
-                x[2 * i + 1] = __high2float(h2);
-            }
-        }
-    }
-}
-
-__device__ __forceinline__ uint32_t quant4(float a, float b, float c, float d, bool divide, float scale) {
-    if (divide) { a = __fdiv_rn(a, scale); b = __fdiv_rn(b, scale); c = __fdiv_rn(c, scale); d = __fdiv_rn(d, scale); }
-    return (uint32_t)float_to_e4m3(a) | ((uint32_t)float_to_e4m3(b) << 8) | ((uint32_t)float_to_e4m3(c) << 16) |
-           ((uint32_t)float_to_e4m3(d) << 24);
-}
-
-// neox rotation of one 8-wide unit: lower-half elements x1[i] (index i0 + i) and their partners
-// x2[i] (index half + i0 + i), cos c[i] and sin sn[i] of index i0 + i.  float32, unfused, each result
-// rounded to the activation dtype `dt` -- the arithmetic of the separate store kernel, bit for bit.
-__device__ __forceinline__ void rotate8(const float (&x1)[8], const float (&x2)[8], const float (&c)[8], const float (&sn)[8],
-                                        int dt, float (&lo)[8], float (&hi)[8]) {
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-        lo[i] = round_to_dtype(__fsub_rn(__fmul_rn(x1[i], c[i]), __fmul_rn(x2[i], sn[i])), dt);
-        hi[i] = round_to_dtype(__fadd_rn(__fmul_rn(x2[i], c[i]), __fmul_rn(x1[i], sn[i])), dt);
-    }
-}
-
 // Register image of one 16-row page in the MMA fragment layout of lane (g, t):
 //   k[u][ch]  : 16 bytes of K row tokrow(u, g), elements 64*ch + 16*t .. +15
 //   va/vb[u][ch]: 8 bytes of V rows tokrow(u, 2t) / tokrow(u, 2t+1), elements 64*ch + 8*g .. +7
@@ -755,35 +713,15 @@ __global__ void __launch_bounds__(kDirectThreads, (D == 64 ? 2 : 1)) attn_decode
     const int nw = pg0 < npg ? (npg - pg0 + stride_pg - 1) / stride_pg : 0;     // pages of this warp
     const int tail_pi = npg - 1;
 
-    // ---- fused append: unit assignment and everything that does not depend on the previous kernel ----
-    // q unit: head gg, lower-half elements i0..i0+7 and their partners; K unit: the same for the new
-    // K row; V unit: 8 elements of the new V row (K and V units in the tail CTA only)
-    constexpr int kUnitsPerRow = half / 8;
-    int unit_kind = -1, unit_gg = 0, unit_i0 = 0;        // 0 = q, 1 = k, 2 = v
-    float ucos[8], usin[8];
-    int64_t tail_row = -1;                               // pool row of the new token (tail CTA, unit threads)
-    bool tail_cta = false;
-    if (APPEND) {
-        tail_cta = live > 0 && (tail_pi % nparts) == part;
-        // q units sit in warps 0-1, K units in warp 2, V units in warp 3: the three kinds wait for
-        // their loads side by side instead of one after the other inside a diverged warp
-        if (tid < G * kUnitsPerRow) { unit_kind = 0; unit_gg = tid / kUnitsPerRow; unit_i0 = 8 * (tid % kUnitsPerRow); }
-        else if (tail_cta && warp == 2 && lane < kUnitsPerRow) { unit_kind = 1; unit_i0 = 8 * lane; }
-        else if (tail_cta && warp == 3 && lane < D / 8) { unit_kind = 2; unit_i0 = 8 * lane; }
-        if (unit_kind == 0 || unit_kind == 1) {
-            const float* cs = p.rope_cs + p.rope_pos[b] * p.rope_stride;
-            const float4 c0 = *(const float4*)(cs + unit_i0), c1 = *(const float4*)(cs + unit_i0 + 4);
-            const float4 n0 = *(const float4*)(cs + half + unit_i0), n1 = *(const float4*)(cs + half + unit_i0 + 4);
-            ucos[0] = c0.x; ucos[1] = c0.y; ucos[2] = c0.z; ucos[3] = c0.w; ucos[4] = c1.x; ucos[5] = c1.y; ucos[6] = c1.z; ucos[7] = c1.w;
-            usin[0] = n0.x; usin[1] = n0.y; usin[2] = n0.z; usin[3] = n0.w; usin[4] = n1.x; usin[5] = n1.y; usin[6] = n1.z; usin[7] = n1.w;
-        }
-        if (unit_kind >= 1) {
-            const int64_t trow0 = btrow ? (tail_pi < p.bt_pages ? (int64_t)btrow[tail_pi] * kPage : -1)
-                                        : base + (int64_t)tail_pi * kPage;
-            const int64_t r = trow0 + (live - 1 - tail_pi * kPage);
-            tail_row = (trow0 >= 0 && r < p.pool_rows) ? r : -2;
-        }
-    }
+    // ---- fused append ----
+    // After the dependency wait the CTA builds, one (lower, upper) rotation pair per thread so that no
+    // thread runs a long serial chain: the rotated q of the head group (G * D/2 pairs, every CTA) and,
+    // in the CTA that owns the span's last page, the new K row (D/2 pairs) and V row (2 elements per
+    // thread).  Only the position's cos/sin row address is resolved before the wait.
+    constexpr int kItemsK = half, kItemsV = D / 2;
+    const bool tail_cta = APPEND && live > 0 && (tail_pi % nparts) == part;
+    const int n_items = APPEND ? G * half + (tail_cta ? kItemsK + kItemsV : 0) : 0;
+    const float* cs_row = APPEND ? p.rope_cs + p.rope_pos[b] * p.rope_stride : nullptr;
 
     const LaneOffsets<D> lofs(g, t);
     PageFrags<D> buf[DEPTH];
@@ -822,49 +760,57 @@ __global__ void __launch_bounds__(kDirectThreads, (D == 64 ? 2 : 1)) attn_decode
     const float sl2 = p.scale * (p.k_scale ? p.k_scale[h] : 1.0f) * kLog2e;
     uint32_t qa[C::kKSteps][2];
     if (APPEND) {
-        if (unit_kind == 0 || unit_kind == 1) {
-            const bool isq = unit_kind == 0;
-            const void* src = isq ? p.q : p.k_new;
-            const int64_t row = isq ? (int64_t)b * p.q_sb + (int64_t)(h * G + unit_gg) * p.q_sh
-                                    : (int64_t)b * p.kn_sb + (int64_t)h * p.kn_sh;
-            float x1[8], x2[8], lo[8], hi[8];
-            load8_as_float(src, row + unit_i0, p.q_dtype, x1);
-            load8_as_float(src, row + half + unit_i0, p.q_dtype, x2);
-            if (isq && unit_gg == 0 && unit_i0 == half - 8) {
-                // the group's first q head carries the DMS decision in its last channel
-                if (tail_cta && p.evict_out) p.evict_out[(int64_t)b * p.evict_sb + h] = p.rule.evict(x2[7]) ? 1 : 0;
-                x2[7] = 0.0f;
-            }
-            rotate8(x1, x2, ucos, usin, p.q_dtype, lo, hi);
-            if (isq) {
-                __half2* dl = (__half2*)(s_q + unit_gg * D + unit_i0);
-                __half2* dh = (__half2*)(s_q + unit_gg * D + half + unit_i0);
-#pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    dl[i] = __floats2half2_rn(lo[2 * i], lo[2 * i + 1]);
-                    dh[i] = __floats2half2_rn(hi[2 * i], hi[2 * i + 1]);
+        int64_t tail_row = -1;                       // pool row of the new token
+        if (tail_cta) {
+            const int64_t trow0 = btrow ? (tail_pi < p.bt_pages ? (int64_t)btrow[tail_pi] * kPage : -1)
+                                        : base + (int64_t)tail_pi * kPage;
+            const int64_t r = trow0 + (live - 1 - tail_pi * kPage);
+            tail_row = (trow0 >= 0 && r < p.pool_rows) ? r : -2;
+        }
+        for (int it = tid; it < n_items; it += kDirectThreads) {
+            if (it < G * half + kItemsK) {
+                // one rotation pair of a q head (it < G * half) or of the new K row
+                const bool isq = it < G * half;
+                const int gg = isq ? it / half : 0, i = isq ? it - gg * half : it - G * half;
+                const void* src = isq ? p.q : p.k_new;
+                const int64_t row = isq ? (int64_t)b * p.q_sb + (int64_t)(h * G + gg) * p.q_sh
+                                        : (int64_t)b * p.kn_sb + (int64_t)h * p.kn_sh;
+                const float x1 = load_as_float(src, row + i, p.q_dtype);
+                float x2 = load_as_float(src, row + half + i, p.q_dtype);
+                const float c = cs_row[i], sn = cs_row[half + i];
+                if (isq && gg == 0 && i == half - 1) {
+                    // the group's first q head carries the DMS decision in its last channel
+                    if (tail_cta && p.evict_out) p.evict_out[(int64_t)b * p.evict_sb + h] = p.rule.evict(x2) ? 1 : 0;
+                    x2 = 0.0f;
+                }
+                // float32, unfused, rounded to the activation dtype: the store kernel's arithmetic
+                const float lo = round_to_dtype(__fsub_rn(__fmul_rn(x1, c), __fmul_rn(x2, sn)), p.q_dtype);
+                const float hi = round_to_dtype(__fadd_rn(__fmul_rn(x2, c), __fmul_rn(x1, sn)), p.q_dtype);
+                if (isq) {
+                    s_q[gg * D + i] = __float2half_rn(lo);
+                    s_q[gg * D + half + i] = __float2half_rn(hi);
+                } else {
+                    const float ksc = p.k_scale ? p.k_scale[h] : 1.0f;
+                    const uint8_t bl = float_to_e4m3(p.k_scale ? __fdiv_rn(lo, ksc) : lo);
+                    const uint8_t bh = float_to_e4m3(p.k_scale ? __fdiv_rn(hi, ksc) : hi);
+                    s_new[i] = bl;
+                    s_new[half + i] = bh;
+                    if (tail_row >= 0) {
+                        p.k_pool_w[tail_row * D + i] = bl;
+                        p.k_pool_w[tail_row * D + half + i] = bh;
+                    }
+                    if (tail_row == -2 && i == 0 && p.dev_status) atomicOr(p.dev_status, FDMS_DEV_BAD_INDEX);
                 }
             } else {
-                const float ksc = p.k_scale ? p.k_scale[h] : 1.0f;
-                const bool dv = p.k_scale != nullptr;
-                const uint2 bl = make_uint2(quant4(lo[0], lo[1], lo[2], lo[3], dv, ksc), quant4(lo[4], lo[5], lo[6], lo[7], dv, ksc));
-                const uint2 bh = make_uint2(quant4(hi[0], hi[1], hi[2], hi[3], dv, ksc), quant4(hi[4], hi[5], hi[6], hi[7], dv, ksc));
-                *(uint2*)(s_new + unit_i0) = bl;
-                *(uint2*)(s_new + half + unit_i0) = bh;
-                if (tail_row >= 0) {
-                    *(uint2*)(p.k_pool_w + tail_row * D + unit_i0) = bl;
-                    *(uint2*)(p.k_pool_w + tail_row * D + half + unit_i0) = bh;
-                }
-                if (tail_row == -2 && unit_i0 == 0 && p.dev_status) atomicOr(p.dev_status, FDMS_DEV_BAD_INDEX);
+                // two elements of the new V row
+                const int i = 2 * (it - G * half - kItemsK);
+                const int64_t e0 = (int64_t)b * p.vn_sb + (int64_t)h * p.vn_sh + i;
+                float y0 = load_as_float(p.v_new, e0, p.q_dtype), y1 = load_as_float(p.v_new, e0 + 1, p.q_dtype);
+                if (p.v_scale) { const float vsc = p.v_scale[h]; y0 = __fdiv_rn(y0, vsc); y1 = __fdiv_rn(y1, vsc); }
+                const uchar2 bv = make_uchar2(float_to_e4m3(y0), float_to_e4m3(y1));
+                *(uchar2*)(s_new + D + i) = bv;
+                if (tail_row >= 0) *(uchar2*)(p.v_pool_w + tail_row * D + i) = bv;
             }
-        } else if (unit_kind == 2) {
-            float x[8];
-            load8_as_float(p.v_new, (int64_t)b * p.vn_sb + (int64_t)h * p.vn_sh + unit_i0, p.q_dtype, x);
-            const float vsc = p.v_scale ? p.v_scale[h] : 1.0f;
-            const bool dv = p.v_scale != nullptr;
-            const uint2 bv = make_uint2(quant4(x[0], x[1], x[2], x[3], dv, vsc), quant4(x[4], x[5], x[6], x[7], dv, vsc));
-            *(uint2*)(s_new + D + unit_i0) = bv;
-            if (tail_row >= 0) *(uint2*)(p.v_pool_w + tail_row * D + unit_i0) = bv;
         }
         __syncthreads();
 #pragma unroll
@@ -1170,13 +1116,6 @@ static int32_t attn_decode_common(
         FDMS_REQUIRE(app->k_new && app->v_new && q_rope_positions && q_rope_cos_sin, FDMS_E_ARG,
                      "fdms_attn_decode_append: k, v, positions and cos_sin_cache are required");
         FDMS_REQUIRE(app->alpha_scale != 0.0 || !app->evict_out, FDMS_E_ARG, "alpha_scale must be non-zero");
-        const int64_t esz = q_dtype == FDMS_F32 ? 4 : 2;
-        const uintptr_t mis = (uintptr_t)q | (uintptr_t)app->k_new | (uintptr_t)(q_stride_b * esz) |
-                              (uintptr_t)(q_stride_h * esz) | (uintptr_t)(app->kn_sb * esz) | (uintptr_t)(app->kn_sh * esz) |
-                              (uintptr_t)app->v_new | (uintptr_t)(app->vn_sb * esz) | (uintptr_t)(app->vn_sh * esz);
-        FDMS_REQUIRE((((uintptr_t)q_rope_cos_sin | (uintptr_t)(cos_sin_stride * 4)) & 15) == 0, FDMS_E_ARG,
-                     "fdms_attn_decode_append: cos_sin_cache rows must be 16-byte aligned");
-        FDMS_REQUIRE((mis & 15) == 0, FDMS_E_ARG, "fdms_attn_decode_append: q, k and v rows must be 16-byte aligned");
         p.append = 1;
         p.k_new = app->k_new; p.kn_sb = app->kn_sb; p.kn_sh = app->kn_sh;
         p.v_new = app->v_new; p.vn_sb = app->vn_sb; p.vn_sh = app->vn_sh;

@@ -96,7 +96,7 @@ int32_t fdms_attn_decode(
  * logical row of each span.  Per span, the CTA that owns the last page reads the DMS decision
  * (evict_out, optional), rotates k, quantises k and v exactly like fdms_store_decode, writes the row to
  * the pool and attends to it; every CTA rotates q on the fly (q itself is left untouched, as with
- * store_q = 0).  FP8 e4m3 pools, head_dim 64 or 128, group size <= 8; q and k rows 16-byte aligned.
+ * store_q = 0).  FP8 e4m3 pools, head_dim 64 or 128, group size <= 8.
  * With FDMS_ATTN_OVERLAP_PREVIOUS the preceding kernel may still be producing q, k and v: they are
  * read after it has completed, pool pages are prefetched before. */
 int32_t fdms_attn_decode_append(
