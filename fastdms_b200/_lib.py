@@ -52,6 +52,8 @@ _SIGNATURES = {
                                     I32, I32, I32, I32, P, P]),
     "fdms_kv_quant": (I32, [P, I32, P, P, I64, I32, I32, P]),
     "fdms_kv_dequant": (I32, [P, P, I32, P, I64, I32, I32, P]),
+    "fdms_rmsnorm": (I32, [P, I64, P, I64, P, P, I64, P, I64, I32, I64, I32, F, P]),
+    "fdms_silu_and_mul": (I32, [P, I64, P, I64, I32, I64, I32, P]),
 }
 
 _lib = None

@@ -1,0 +1,142 @@
+"""Whole-model decode throughput on synthetic weights of the shapes the reference is benchmarked on
+(its WikiText-2 8192 + 128 runs, `benchmarks/bench_llama_wikitext2.py`; dataset and checkpoints are
+replaced by random token ids and random-init weights).
+
+    python -m fastdms_b200.bench_model --shape llama-1b                       # one GPU, c = 8
+    torchrun --nproc-per-node N -m fastdms_b200.bench_model --shape llama-1b  # N replicas, c = 8 each
+    torchrun --nproc-per-node N -m fastdms_b200.bench_model --shape qwen3-8b --tp N
+
+Replica mode (`--tp 1` under torchrun) shards sequences over the ranks with no data-path collective;
+`--tp N` splits KV heads over the ranks with NCCL all-reduces after o_proj and down_proj.
+Prints one JSON line on rank 0: prefill and decode tokens/s through `LLMEngine.step()` (host
+scheduling, graph replay, token read-back included), the measured KV compression and the per-step
+time.  The DMS decision channel of the random-init model is biased so that about 7/8 of the tokens
+are marked for eviction (needs a q bias, so the synthetic configs set `attention_bias`)."""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import time
+
+import torch
+import torch.distributed as dist
+
+SHAPES = {
+    # Llama-3.2-1B: 16 layers, hidden 2048, 32 q / 8 KV heads of 64, MLP 8192, vocab 128256
+    "llama-1b": dict(model_type="llama", hidden_size=2048, intermediate_size=8192, num_hidden_layers=16,
+                     num_attention_heads=32, num_key_value_heads=8, head_dim=64, vocab_size=128256,
+                     rms_norm_eps=1e-5, rope_theta=500000.0, tie_word_embeddings=False, hidden_act="silu"),
+    # Qwen3-8B: 36 layers, hidden 4096, 32 q / 8 KV heads of 128, q/k RMSNorm, MLP 12288, vocab 151936
+    "qwen3-8b": dict(model_type="qwen3", hidden_size=4096, intermediate_size=12288, num_hidden_layers=36,
+                     num_attention_heads=32, num_key_value_heads=8, head_dim=128, vocab_size=151936,
+                     rms_norm_eps=1e-6, rope_theta=1000000.0, tie_word_embeddings=False, hidden_act="silu"),
+    # small shape for tests
+    "tiny": dict(model_type="llama", hidden_size=256, intermediate_size=512, num_hidden_layers=2,
+                 num_attention_heads=8, num_key_value_heads=2, head_dim=64, vocab_size=1024,
+                 rms_norm_eps=1e-5, rope_theta=500000.0, tie_word_embeddings=False, hidden_act="silu"),
+}
+
+
+def run(args) -> dict:
+    from fastdms_b200 import _lib
+    from fastdms_b200.engine.llm_engine import LLMEngine
+    from fastdms_b200.sampling_params import SamplingParams
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1 and not dist.is_initialized():
+        dist.init_process_group("nccl", device_id=dev)
+    if args.tp not in (1, world):
+        raise SystemExit(f"--tp must be 1 (replicas) or the number of ranks ({world})")
+
+    hf = dict(SHAPES[args.shape])
+    hf.update(attention_bias=True, torch_dtype="bfloat16",
+              max_position_embeddings=args.prompt_len + args.decode_steps + 8)
+    c = args.concurrency
+    engine = LLMEngine(
+        f"synthetic-{args.shape}", hf_config=hf, random_init_seed=args.seed, device=dev,
+        max_model_len=args.prompt_len + args.decode_steps + 8, max_num_seqs=c,
+        max_num_batched_tokens=max(c * args.prompt_len, 16384), kv_cache_dtype="float8_e4m3fn",
+        tensor_parallel_size=args.tp, compact_kv_paged=args.paged, enforce_eager=args.eager,
+        dms_window_size=args.window, dms_expiry_interval=args.expiry_interval)
+    # replicas draw different prompts; tensor-parallel ranks must see the same ones
+    g = torch.Generator().manual_seed(args.seed + (rank if args.tp == 1 else 0))
+    vocab = hf["vocab_size"]
+    sp = SamplingParams(temperature=0.0, max_tokens=args.decode_steps + 2, ignore_eos=True)
+    seqs = [engine.add_request(torch.randint(0, vocab, (args.prompt_len,), generator=g).tolist(), sp) for _ in range(c)]
+
+    def sync():
+        torch.cuda.synchronize(dev)
+        if world > 1:
+            dist.barrier()
+
+    sync()
+    t0 = time.perf_counter()
+    prefill_steps = 0
+    while engine.scheduler.waiting:
+        engine.step()
+        prefill_steps += 1
+    sync()
+    t_prefill = time.perf_counter() - t0
+    m = engine.model_runner.compact_kv_manager
+    live0 = torch.stack([m.seq_states[s.seq_id].live_counts for s in seqs]).float()
+    # two untimed decode steps: the eager warm-up and the graph capture
+    warm = 0 if args.eager else 2
+    for _ in range(warm):
+        engine.step()
+    sync()
+    steps = args.decode_steps - warm
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        engine.step()
+    sync()
+    t_decode = time.perf_counter() - t0
+    live1 = torch.stack([m.seq_states[s.seq_id].live_counts for s in seqs]).float()
+    tokens = [s.completion_token_ids[-4:] for s in seqs[:2]]
+    while not engine.is_finished():
+        engine.step()
+    replicas = world if args.tp == 1 else 1
+    t = torch.tensor([t_prefill, t_decode], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    t_prefill, t_decode = (float(x) for x in t.tolist())
+    ctx_end = args.prompt_len + args.decode_steps
+    return {
+        "shape": args.shape, "n_gpus": world, "parallelism": f"tp{args.tp}" if args.tp > 1 else f"replicas x{world}",
+        "concurrency_per_replica": c, "prompt_len": args.prompt_len, "decode_steps_timed": steps,
+        "decode_tok_s": replicas * c * steps / t_decode, "decode_ms_per_step": t_decode / steps * 1e3,
+        "prefill_tok_s": replicas * c * args.prompt_len / t_prefill, "prefill_s": t_prefill, "prefill_steps": prefill_steps,
+        "kv_dtype": "float8_e4m3fn", "layout": "paged" if args.paged else "spans", "window": engine.model_runner.dms_metadata.window_size,
+        "mean_live_after_prefill": float(live0.mean()), "mean_live_at_end": float(live1.mean()),
+        "compression_at_end": ctx_end / float(live1.mean()), "sample_tokens": tokens,
+        "device_status": int(_lib.read_device_status(dev)),
+        "data": "synthetic: random-init bf16 weights, uniform random token ids",
+    }
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--shape", choices=sorted(SHAPES), default="llama-1b")
+    ap.add_argument("--concurrency", type=int, default=8)
+    ap.add_argument("--prompt-len", type=int, default=8192)
+    ap.add_argument("--decode-steps", type=int, default=128)
+    ap.add_argument("--tp", type=int, default=1)
+    ap.add_argument("--window", type=int, default=256)
+    ap.add_argument("--expiry-interval", type=int, default=1)
+    ap.add_argument("--paged", action="store_true")
+    ap.add_argument("--eager", action="store_true")
+    ap.add_argument("--seed", type=int, default=0)
+    args = ap.parse_args()
+    out = run(args)
+    if int(os.environ.get("RANK", "0")) == 0:
+        print(json.dumps(out))
+    if dist.is_initialized():
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,165 @@
+// Row-wise helpers of the decoder block that sit between the attention launches of a decode step:
+// RMSNorm with optional residual add, and SiLU(gate) * up.  16-bit activations (bf16 / f16), float32
+// statistics, one 16-byte vector (8 elements) per load; results are rounded where the reference's
+// torch ops round (fastdms/layers/layernorm.py:16-48, fastdms/layers/activation.py).
+#include "common.cuh"
+
+namespace fdms {
+
+constexpr int kNormThreads = 256;
+constexpr int kNormMaxVec = 4;        // 16-byte vectors per thread: hidden <= 8 * 4 * group size
+
+__device__ __forceinline__ void unpack8(const uint4& v, int dt, float (&f)[8]) {
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        if (dt == FDMS_BF16) {
+            f[2 * i] = __uint_as_float(w[i] << 16);
+            f[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+        } else {
+            const __half2 h = *(const __half2*)&w[i];
+            f[2 * i] = __low2float(h);
+            f[2 * i + 1] = __high2float(h);
+        }
+    }
+}
+
+__device__ __forceinline__ uint4 pack8(const float (&f)[8], int dt) {
+    uint32_t w[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        if (dt == FDMS_BF16) {
+            const __nv_bfloat162 b = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+            w[i] = *(const uint32_t*)&b;
+        } else {
+            const __half2 h = __floats2half2_rn(f[2 * i], f[2 * i + 1]);
+            w[i] = *(const uint32_t*)&h;
+        }
+    }
+    return make_uint4(w[0], w[1], w[2], w[3]);
+}
+
+// A group of `T` threads (a power of two, 32..256) owns one row; a CTA holds 256 / T rows.
+//   xf  = float(x) (+ float(residual))           residual_out = round(xf)
+//   out = round(round(xf * rsqrt(mean(xf^2) + eps)) * weight)
+__global__ void __launch_bounds__(kNormThreads) rmsnorm_kernel(
+    const uint16_t* x, int64_t x_stride, const uint16_t* residual, int64_t res_stride, const uint16_t* weight,
+    uint16_t* out, int64_t out_stride, uint16_t* residual_out, int64_t res_out_stride, int dt, int64_t rows, int hidden,
+    float eps, int T) {
+    __shared__ float s_part[kNormThreads / 32];
+    const int tid = threadIdx.x;
+    const int grp = tid / T, lig = tid - grp * T;          // group index, lane in group
+    const int64_t row = (int64_t)blockIdx.x * (kNormThreads / T) + grp;
+    const int nvec = hidden >> 3;
+    const bool live = row < rows;
+    float v[kNormMaxVec][8];
+    float ss = 0.0f;
+#pragma unroll
+    for (int j = 0; j < kNormMaxVec; ++j) {
+        const int c = lig + j * T;
+        if (live && c < nvec) {
+            unpack8(*(const uint4*)(x + row * x_stride + 8 * c), dt, v[j]);
+            if (residual) {
+                float r[8];
+                unpack8(*(const uint4*)(residual + row * res_stride + 8 * c), dt, r);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) v[j][i] += r[i];
+            }
+            if (residual_out) *(uint4*)(residual_out + row * res_out_stride + 8 * c) = pack8(v[j], dt);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) ss += v[j][i] * v[j][i];
+        }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    if (T > 32) {
+        if ((tid & 31) == 0) s_part[tid >> 5] = ss;
+        __syncthreads();
+        const int w0 = (grp * T) >> 5;
+        ss = 0.0f;
+        for (int w = 0; w < (T >> 5); ++w) ss += s_part[w0 + w];
+    }
+    const float inv = rsqrtf(ss / (float)hidden + eps);
+#pragma unroll
+    for (int j = 0; j < kNormMaxVec; ++j) {
+        const int c = lig + j * T;
+        if (live && c < nvec) {
+            float w[8], y[8];
+            unpack8(*(const uint4*)(weight + 8 * c), dt, w);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) y[i] = round_to_dtype(v[j][i] * inv, dt) * w[i];
+            *(uint4*)(out + row * out_stride + 8 * c) = pack8(y, dt);
+        }
+    }
+}
+
+// out[r, c] = round(round(silu(x[r, c])) * x[r, n + c]), 8 elements per thread.
+__global__ void silu_mul_kernel(const uint16_t* x, int64_t x_stride, uint16_t* out, int64_t out_stride, int dt,
+                                int64_t rows, int n) {
+    const int nvec = n >> 3;
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= rows * nvec) return;
+    const int64_t r = i / nvec;
+    const int c = (int)(i - r * nvec);
+    float a[8], b[8], y[8];
+    unpack8(*(const uint4*)(x + r * x_stride + 8 * c), dt, a);
+    unpack8(*(const uint4*)(x + r * x_stride + n + 8 * c), dt, b);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) y[k] = round_to_dtype(a[k] / (1.0f + __expf(-a[k])), dt) * b[k];
+    *(uint4*)(out + r * out_stride + 8 * c) = pack8(y, dt);
+}
+
+}  // namespace fdms
+
+using namespace fdms;
+
+static bool aligned16(const void* p, int64_t stride_elems) {
+    return ((uintptr_t)p & 15) == 0 && ((stride_elems * 2) & 15) == 0;
+}
+
+extern "C" int32_t fdms_rmsnorm(
+    const void* x, int64_t x_row_stride, const void* residual, int64_t residual_row_stride, const void* weight,
+    void* out, int64_t out_row_stride, void* residual_out, int64_t residual_out_row_stride,
+    int32_t dtype, int64_t rows, int32_t hidden, float eps, void* stream) {
+    clear_error();
+    FDMS_REQUIRE(x && weight && out, FDMS_E_ARG, "fdms_rmsnorm: null pointer");
+    FDMS_REQUIRE(dtype == FDMS_BF16 || dtype == FDMS_F16, FDMS_E_DTYPE, "fdms_rmsnorm: bf16 or f16 activations only");
+    FDMS_REQUIRE(rows >= 0 && hidden > 0 && hidden % 8 == 0, FDMS_E_ARG, "fdms_rmsnorm: hidden must be a positive multiple of 8");
+    FDMS_REQUIRE(aligned16(x, x_row_stride) && aligned16(out, out_row_stride) && aligned16(weight, 0) &&
+                     (!residual || aligned16(residual, residual_row_stride)) &&
+                     (!residual_out || aligned16(residual_out, residual_out_row_stride)),
+                 FDMS_E_ARG, "fdms_rmsnorm: pointers and row strides must be 16-byte aligned");
+    if (rows == 0) return FDMS_OK;
+    const int nvec = hidden / 8;
+    int T = 32;
+    while (T < kNormThreads && T * 2 <= nvec) T *= 2;          // about one vector per thread
+    while (T < kNormThreads && T * kNormMaxVec < nvec) T *= 2;
+    FDMS_REQUIRE(T * kNormMaxVec >= nvec, FDMS_E_CAPACITY, "fdms_rmsnorm: hidden=%d is larger than %d", hidden,
+                 kNormThreads * kNormMaxVec * 8);
+    const int rows_per_block = kNormThreads / T;
+    const int64_t blocks = (rows + rows_per_block - 1) / rows_per_block;
+    FDMS_REQUIRE(blocks < (1ll << 31), FDMS_E_CAPACITY, "fdms_rmsnorm: too many rows");
+    rmsnorm_kernel<<<(unsigned)blocks, kNormThreads, 0, (cudaStream_t)stream>>>(
+        (const uint16_t*)x, x_row_stride, (const uint16_t*)residual, residual_row_stride, (const uint16_t*)weight,
+        (uint16_t*)out, out_row_stride, (uint16_t*)residual_out, residual_out_row_stride, dtype, rows, hidden, eps, T);
+    FDMS_CHECK_LAUNCH("rmsnorm_kernel");
+    return FDMS_OK;
+}
+
+extern "C" int32_t fdms_silu_and_mul(const void* x, int64_t x_row_stride, void* out, int64_t out_row_stride,
+                                     int32_t dtype, int64_t rows, int32_t n, void* stream) {
+    clear_error();
+    FDMS_REQUIRE(x && out, FDMS_E_ARG, "fdms_silu_and_mul: null pointer");
+    FDMS_REQUIRE(dtype == FDMS_BF16 || dtype == FDMS_F16, FDMS_E_DTYPE, "fdms_silu_and_mul: bf16 or f16 activations only");
+    FDMS_REQUIRE(rows >= 0 && n > 0 && n % 8 == 0, FDMS_E_ARG, "fdms_silu_and_mul: n must be a positive multiple of 8");
+    FDMS_REQUIRE(aligned16(x, x_row_stride) && aligned16(out, out_row_stride), FDMS_E_ARG,
+                 "fdms_silu_and_mul: pointers and row strides must be 16-byte aligned");
+    if (rows == 0) return FDMS_OK;
+    const int64_t total = rows * (n / 8);
+    const int64_t blocks = (total + 255) / 256;
+    FDMS_REQUIRE(blocks < (1ll << 31), FDMS_E_CAPACITY, "fdms_silu_and_mul: too many elements");
+    silu_mul_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>((const uint16_t*)x, x_row_stride, (uint16_t*)out,
+                                                                         out_row_stride, dtype, rows, n);
+    FDMS_CHECK_LAUNCH("silu_mul_kernel");
+    return FDMS_OK;
+}

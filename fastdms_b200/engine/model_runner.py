@@ -56,8 +56,10 @@ class ModelRunner:
     def __init__(self, config: Config, device: torch.device | None = None):
         self.config = config
         hf = config.hf_config
-        self.world_size = dist.get_world_size() if dist.is_initialized() else 1
-        self.rank = dist.get_rank() if dist.is_initialized() else 0
+        from fastdms_b200.layers.linear import set_replica_mode, tp_world
+        # tensor_parallel_size 1 inside a multi-rank job = one full replica per rank (sequence sharding)
+        set_replica_mode(config.tensor_parallel_size == 1)
+        self.world_size, self.rank = tp_world()
         if self.world_size != config.tensor_parallel_size:
             raise RuntimeError(
                 f"tensor_parallel_size={config.tensor_parallel_size} needs that many ranks (torchrun); "

@@ -1,9 +1,47 @@
 """RMSNorm with optional fused residual add (float32 statistics, result in the input dtype), as in
-the reference's `fastdms/layers/layernorm.py`; plain torch ops (outside the CUDA hot path)."""
+the reference's `fastdms/layers/layernorm.py`.  16-bit CUDA activations take one launch of the
+library's `fdms_rmsnorm`; float32 (the reference's CPU-checkable configuration) stays on torch ops
+because that path reproduces the reference's aliasing exactly."""
 from __future__ import annotations
 
 import torch
 from torch import nn
+
+from fastdms_b200 import _lib
+
+
+def _fused_ok(x: torch.Tensor, weight: torch.Tensor) -> bool:
+    return (x.is_cuda and x.dtype in (torch.bfloat16, torch.float16) and weight.dtype == x.dtype
+            and x.shape[-1] % 8 == 0 and x.shape[-1] <= 8192 and x.stride(-1) == 1 and x.numel() > 0)
+
+
+def _rows(t: torch.Tensor) -> torch.Tensor:
+    """[rows, hidden] view with a single row stride (copy only if the layout needs one)."""
+    t2 = t.reshape(-1, t.shape[-1])
+    return t2 if t2.stride(-1) == 1 else t2.contiguous()
+
+
+def rmsnorm_cuda(x: torch.Tensor, weight: torch.Tensor, eps: float, residual: torch.Tensor | None = None):
+    """One launch: returns `out` or `(out, new_residual)` when `residual` is given."""
+    x2 = _rows(x)
+    rows, hidden = x2.shape
+    out = torch.empty((rows, hidden), dtype=x.dtype, device=x.device)
+    res2 = res_out = None
+    if residual is not None:
+        res2 = _rows(residual)
+        res_out = torch.empty((rows, hidden), dtype=x.dtype, device=x.device)
+    ok = all(t is None or (t.data_ptr() % 16 == 0 and (t.stride(0) * 2) % 16 == 0) for t in (x2, res2)) and \
+        weight.data_ptr() % 16 == 0 and weight.is_contiguous()
+    if not ok:
+        return None
+    with torch.cuda.device(x.device):
+        rc = _lib.lib().fdms_rmsnorm(
+            x2.data_ptr(), x2.stride(0), _lib.ptr(res2), res2.stride(0) if res2 is not None else 0, weight.data_ptr(),
+            out.data_ptr(), out.stride(0), _lib.ptr(res_out), res_out.stride(0) if res_out is not None else 0,
+            _lib.dtype_code(x.dtype), rows, hidden, float(eps), _lib.stream_ptr(x.device))
+    _lib.check(rc)
+    out = out.view(x.shape)
+    return out if residual is None else (out, res_out.view(x.shape))
 
 
 class RMSNorm(nn.Module):
@@ -14,6 +52,10 @@ class RMSNorm(nn.Module):
 
     def forward(self, x: torch.Tensor, residual: torch.Tensor | None = None):
         dtype = x.dtype
+        if _fused_ok(x, self.weight) and (residual is None or (residual.dtype == dtype and residual.shape == x.shape)):
+            y = rmsnorm_cuda(x, self.weight, self.eps, residual)
+            if y is not None:
+                return y
         if residual is None:
             xf = x.float()
             y = (xf * torch.rsqrt(xf.pow(2).mean(dim=-1, keepdim=True) + self.eps)).to(dtype) * self.weight

@@ -14,8 +14,20 @@ import torch.nn.functional as F
 from torch import nn
 
 
+_REPLICA_MODE = False
+
+
+def set_replica_mode(enabled: bool) -> None:
+    """Replica mode: every rank of the job holds the whole model (sequence sharding); the process
+    group is then only used to exchange results, never by the layers."""
+    global _REPLICA_MODE
+    _REPLICA_MODE = bool(enabled)
+
+
 def tp_world() -> tuple[int, int]:
-    if dist.is_available() and dist.is_initialized():
+    """(tensor-parallel size, rank) seen by the layers: the process group, or (1, 0) without one or
+    in replica mode."""
+    if not _REPLICA_MODE and dist.is_available() and dist.is_initialized():
         return dist.get_world_size(), dist.get_rank()
     return 1, 0
 

@@ -286,6 +286,24 @@ int32_t fdms_kv_quant(const void* x, int32_t x_dtype, uint8_t* out, const float*
 int32_t fdms_kv_dequant(const uint8_t* x, void* out, int32_t out_dtype, const float* scale,
                         int64_t n, int32_t num_kv_heads, int32_t head_dim, void* stream);
 
+/* ---------------------------------------------------------------------------------------------
+ * Callers either side of the path inside a decoder block (decode steps are launch-bound, so these
+ * are single launches instead of the reference's chains of torch ops under torch.compile).
+ * 16-bit activations (FDMS_BF16 / FDMS_F16) only; pointers and row strides 16-byte aligned.
+ *
+ * fdms_rmsnorm: RMSNorm.rms_forward / add_rms_forward (fastdms/layers/layernorm.py:16-48).
+ *   xf = float(x) (+ float(residual));  residual_out = round(xf) (optional);
+ *   out = round(round(xf * rsqrt(mean(xf^2) + eps)) * weight).   hidden % 8 == 0, hidden <= 8192.
+ *   out may alias x, residual_out may alias residual.
+ * fdms_silu_and_mul: SiluAndMul (fastdms/layers/activation.py): out[r, c] = silu(x[r, c]) * x[r, n + c].
+ * --------------------------------------------------------------------------------------------- */
+int32_t fdms_rmsnorm(
+    const void* x, int64_t x_row_stride, const void* residual, int64_t residual_row_stride, const void* weight,
+    void* out, int64_t out_row_stride, void* residual_out, int64_t residual_out_row_stride,
+    int32_t dtype, int64_t rows, int32_t hidden, float eps, void* stream);
+int32_t fdms_silu_and_mul(const void* x, int64_t x_row_stride, void* out, int64_t out_row_stride,
+                          int32_t dtype, int64_t rows, int32_t n, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -415,3 +415,44 @@ def test_kv_quant_dequant(dev):
     q1 = kv_quantize_fp8(y, sc)
     q2 = kv_quantize_fp8(kv_dequantize_fp8(q1, sc), sc)
     assert torch.equal(q1.view(torch.uint8), q2.view(torch.uint8))
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("rows,hidden", [(8, 2048), (3, 4096), (257, 256), (64, 128), (5, 8192)])
+def test_rmsnorm_and_silu_kernels_match_torch_ops(dev, dtype, rows, hidden):
+    """Single-launch RMSNorm (+ residual) and SiLU*up against the torch op chains they replace
+    (reference: layers/layernorm.py:16-48, layers/activation.py); tolerance = two roundings of the
+    16-bit type (the float32 sum is taken in a different order)."""
+    from fastdms_b200.layers.activation import SiluAndMul
+    from fastdms_b200.layers.layernorm import RMSNorm
+    g = torch.Generator(device=dev).manual_seed(rows * 131 + hidden)
+    x = torch.randn((rows, hidden), device=dev, generator=g).to(dtype)
+    res = torch.randn((rows, hidden), device=dev, generator=g).to(dtype)
+    norm = RMSNorm(hidden, eps=1e-5).to(dev).to(dtype)
+    norm.weight.data.copy_((1.0 + 0.1 * torch.randn(hidden, device=dev, generator=g)).to(dtype))
+
+    def ref(x, residual=None):
+        xf = x.float() if residual is None else x.float() + residual.float()
+        y = (xf * torch.rsqrt(xf.pow(2).mean(dim=-1, keepdim=True) + 1e-5)).to(dtype) * norm.weight
+        return y if residual is None else (y, xf.to(dtype))
+
+    tol = 2.0 ** (-6 if dtype == torch.bfloat16 else -9)       # two roundings, each up to one ulp apart
+    y = norm(x)
+    want = ref(x)
+    assert y.dtype == dtype and y.shape == x.shape
+    assert ((y.float() - want.float()).abs() <= tol * want.float().abs() + 1e-6).all()
+    y2, r2 = norm(x, res)
+    w2, wr2 = ref(x, res)
+    assert torch.equal(r2, wr2)
+    assert ((y2.float() - w2.float()).abs() <= tol * w2.float().abs() + 1e-6).all()
+    # strided rows (a view into a wider buffer) take the same path
+    wide = torch.randn((rows, 2 * hidden), device=dev, generator=g).to(dtype)
+    yv = norm(wide[:, :hidden])
+    wv = ref(wide[:, :hidden])
+    assert ((yv.float() - wv.float()).abs() <= tol * wv.float().abs() + 1e-6).all()
+    act = SiluAndMul()
+    z = act(wide)
+    a, b = wide.chunk(2, -1)
+    wz = torch.nn.functional.silu(a) * b
+    assert z.shape == wz.shape
+    assert ((z.float() - wz.float()).abs() <= 2 * tol * wz.float().abs() + 1e-6).all()
