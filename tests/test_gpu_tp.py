@@ -1,0 +1,99 @@
+"""Tensor parallelism by KV head (the 8B-shape partition) on two GPUs, checked on BASELINE config 0:
+two ranks, one KV head each, NCCL all-reduce after o_proj and down_proj, against the same reference
+trace as the single-GPU test.  DMS state is per KV head, so each rank's decisions and compact
+lengths must equal that head's columns of the trace; tokens must be identical.
+Skipped on boxes with fewer than two GPUs."""
+from __future__ import annotations
+
+import sys
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+
+ROOT = Path(__file__).resolve().parent.parent
+pytestmark = pytest.mark.gpu
+PORT = 29731
+
+
+def _rank_main(rank: int, world: int, kv_dtype: str, out_q) -> None:
+    import os
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(PORT), RANK=str(rank), WORLD_SIZE=str(world),
+                      LOCAL_RANK=str(rank))
+    sys.path.insert(0, str(ROOT))
+    sys.path.insert(0, str(ROOT / "tests" / "golden"))
+    import torch.distributed as dist
+    import make_golden_model as G
+    from fastdms_b200 import LLM, SamplingParams, _lib
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", device_id=torch.device("cuda", rank))
+    try:
+        with np.load(ROOT / "tests" / "golden" / "model_golden.npz") as z:
+            cos_sin = z["cos_sin_cache"]
+        llm = LLM("config0-tiny-llama", hf_config=dict(G.MODEL_CFG), random_init_seed=G.SEED, dtype="float32",
+                  kv_cache_dtype=kv_dtype, max_model_len=1024, max_num_seqs=4, max_num_batched_tokens=4096,
+                  compact_kv_capacity_tokens=8192, dms_window_size=G.WINDOW, dms_alpha_scale=G.ALPHA_SCALE,
+                  dms_alpha_offset=G.ALPHA_OFFSET, tensor_parallel_size=world, device=f"cuda:{rank}")
+        cache = llm.model_runner.model.model.layers[0].self_attn.rotary_emb.cos_sin_cache
+        ref = torch.from_numpy(cos_sin).to(cache.device)
+        cache[: ref.shape[0], 0].copy_(ref)
+        sp = SamplingParams(temperature=0.0, max_tokens=G.DECODE_STEPS + 1, ignore_eos=True)
+        seqs = [llm.add_request(p, sp) for p in G.make_prompts()]
+        mgr = llm.model_runner.compact_kv_manager
+        assert mgr.num_kv_heads == G.MODEL_CFG["num_key_value_heads"] // world
+        llm.step()
+        tokens = [[s.completion_token_ids[-1] for s in seqs]]
+        prefill_live = torch.stack([mgr.seq_states[s.seq_id].live_counts for s in seqs], dim=1).cpu().numpy()
+        evict, live, logits = [], [], []
+        for _ in range(G.DECODE_STEPS):
+            llm.step()
+            g = llm.model_runner.graphs[len(seqs)]
+            evict.append(g.evict_all.cpu().numpy().copy())
+            live.append(g.live.cpu().numpy().copy())
+            logits.append(g.logits.float().cpu().numpy().copy())
+            tokens.append([s.completion_token_ids[-1] for s in seqs])
+        out_q.put((rank, dict(tokens=np.array(tokens), prefill_live=prefill_live, evict=np.stack(evict),
+                              live=np.stack(live), logits=np.stack(logits),
+                              status=_lib.read_device_status(f"cuda:{rank}"), finished=llm.is_finished())))
+        out_q.close(); out_q.join_thread()
+        torch.cuda.synchronize()
+        dist.barrier()
+    finally:
+        # leave without interpreter teardown: destroying captured graphs that hold NCCL kernels after
+        # the peer has gone can block
+        sys.stdout.flush(); sys.stderr.flush()
+        os._exit(0 if sys.exc_info()[0] is None else 1)
+
+
+@pytest.mark.parametrize("tag,kv_dtype", [("f32", "float32"), ("fp8", "float8_e4m3fn")])
+def test_tp2_by_kv_head_matches_reference_trace(tag, kv_dtype):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_rank_main, args=(r, 2, kv_dtype, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    results = {}
+    try:
+        for _ in range(2):
+            rank, res = q.get(timeout=600)
+            results[rank] = res
+    finally:
+        for p in procs:
+            p.join(timeout=60)
+            if p.is_alive():
+                p.kill()
+    assert all(p.exitcode == 0 for p in procs)
+    with np.load(ROOT / "tests" / "golden" / "model_golden.npz") as z:
+        golden = {k: z[k] for k in z.files}
+    for rank in range(2):
+        r = results[rank]
+        assert r["status"] == 0 and r["finished"]
+        assert np.array_equal(r["tokens"], golden[f"{tag}_tokens"]), f"rank {rank}: greedy tokens differ"
+        assert np.array_equal(r["prefill_live"], golden[f"{tag}_prefill_live"][:, :, rank:rank + 1])
+        assert np.array_equal(r["evict"], golden[f"{tag}_evict"][:, :, :, rank:rank + 1]), f"rank {rank}: decisions differ"
+        assert np.array_equal(r["live"], golden[f"{tag}_live"][:, :, :, rank:rank + 1]), f"rank {rank}: compact lengths differ"
+        assert np.abs(r["logits"] - golden[f"{tag}_logits"]).max() < 2e-2
