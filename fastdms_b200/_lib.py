@@ -38,7 +38,7 @@ _SIGNATURES = {
     "fdms_store_decode": (I32, [P, I64, I64, P, I64, I64, P, I64, I64, I32, P, I64, P, P, P, I32, I64,
                                 P, I64, P, I64, P, P, I32, I32, I32, I32, DBL, DBL, I32, I32, I32, I32, P, P]),
     "fdms_extract_decisions": (I32, [P, I32, I64, I64, P, I64, I64, I32, I32, I32, DBL, DBL, P]),
-    "fdms_expire_compact": (I32, [P, I64, I64, I64, P, I64, I64, I64, P, P, I64, I64, P, P, I64, I32, I64,
+    "fdms_expire_compact": (I32, [P, I64, I64, I64, P, I64, I64, I64, P, P, P, I64, I64, P, P, I64, I32, I64,
                                   P, I64, I64, I64, P, P, I64, P, P, I32, I32, I32, I32, I32, I32, P, P, P]),
     "fdms_pack_count": (I32, [P, I64, P, P, P, I32, I32, I32, I32, P]),
     "fdms_pack_scatter": (I32, [P, P, I32, I64, I64, P, I64, P, P, I32, P, P, P, I32, I64, P, I64,

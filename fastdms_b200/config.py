@@ -52,6 +52,7 @@ class Config:
     # additions
     compact_kv_paged: bool = False            # 16-row pages + GPU free stack instead of first-fit spans
     dms_expiry_interval: int = 1              # 1 = exact expiry every step; N = when position % N == 0
+    compact_kv_row_indirection: bool = True   # expiry compacts metadata only and refills freed K/V rows
     random_init_seed: int | None = None       # synthetic weights when the directory has no safetensors
     dtype: str | None = None                  # overrides the checkpoint's dtype
 

@@ -106,6 +106,7 @@ class CompactKVManager:
         k_scale: torch.Tensor | None = None,
         v_scale: torch.Tensor | None = None,
         dms_expiry_interval: int = 1,
+        row_indirection: bool = False,
     ):
         if capacity_tokens <= 0:
             raise ValueError(f"capacity_tokens must be positive, got {capacity_tokens}")
@@ -126,6 +127,7 @@ class CompactKVManager:
         self.target_live_tokens_per_seq = target_live_tokens_per_seq
         self.paged = bool(paged)
         self.dms_expiry_interval = int(dms_expiry_interval)
+        self.row_indirection = bool(row_indirection)
         self.debug_checks = os.environ.get("FASTDMS_COMPACT_DEBUG_CHECKS") == "1"
         self.admission_denied_count = 0
         L, S, Hk, C = self.num_layers, self.max_active_seqs, self.num_kv_heads, self.max_model_len
@@ -143,6 +145,13 @@ class CompactKVManager:
         self.layer_major_live_counts = torch.zeros((L, S, Hk), device=dev, dtype=torch.int32)
         self.layer_major_token_positions = torch.full((L, S, Hk, C), -1, device=dev, dtype=torch.int32)
         self.layer_major_evict_mask = torch.zeros((L, S, Hk, C), device=dev, dtype=torch.bool)
+        # Optional logical slot -> physical row map of every span.  With it, expiry compacts only the
+        # metadata in order and keeps the span's K/V rows dense by refilling freed rows (one row copy
+        # per dropped token); without it K/V rows are shifted like the reference's.  Logical row i of
+        # a span is physical row layer_major_row_index[l, slot, h, i]; entries >= live equal i.
+        self.layer_major_row_index = None
+        if self.row_indirection:
+            self.layer_major_row_index = torch.arange(C, device=dev, dtype=torch.int32).expand(L, S, Hk, C).contiguous()
         self.free_active_slots: list[int] = list(range(S))
         self.active_slot_by_seq: dict[int, int] = {}
         self.seq_states: dict[int, CompactKVSequenceState] = {}
@@ -304,6 +313,8 @@ class CompactKVManager:
         live.zero_()
         pos.fill_(-1)
         ev.zero_()
+        if self.layer_major_row_index is not None:
+            self.layer_major_row_index[:, slot, :, :] = torch.arange(self.max_model_len, device=self.device, dtype=torch.int32)
         state = CompactKVSequenceState(
             seq_id=seq.seq_id, base_offsets=base, range_capacity=rcap, live_counts=live,
             token_positions=pos, evict_mask=ev, max_capacity_per_lh=cap,
@@ -497,7 +508,7 @@ class CompactKVManager:
         with torch.cuda.device(dev):
             rc = _lib.lib().fdms_expire_compact(
                 pos.data_ptr(), pos.stride(0), pos.stride(1), pos.stride(2),
-                ev.data_ptr(), ev.stride(0), ev.stride(1), ev.stride(2),
+                ev.data_ptr(), ev.stride(0), ev.stride(1), ev.stride(2), _lib.ptr(self.layer_major_row_index),
                 lc.data_ptr(), base_ptr, lc.stride(0), lc.stride(1),
                 self.compact_k.data_ptr(), self.compact_v.data_ptr(),
                 self.compact_k.stride(0) * self.compact_k.element_size(), row_bytes, self.capacity_tokens,

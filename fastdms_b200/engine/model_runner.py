@@ -173,7 +173,8 @@ class ModelRunner:
             num_layers=L, num_kv_heads=self.num_kv_heads, capacity_tokens=rows, max_model_len=c.max_model_len,
             device=self.device, target_live_tokens_per_seq=c.compact_kv_target_live_tokens_per_seq,
             head_dim=self.head_dim, compact_dtype=kv_dtype, max_active_seqs=c.max_num_seqs, paged=c.compact_kv_paged,
-            dms_expiry_interval=c.dms_expiry_interval)
+            dms_expiry_interval=c.dms_expiry_interval,
+            row_indirection=c.compact_kv_row_indirection)
 
     # ------------------------------------------------------------------ prefill
     @torch.inference_mode()

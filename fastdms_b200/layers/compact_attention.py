@@ -436,7 +436,7 @@ def _expiry_one_layer(mode, positions_per_lh, evict_per_lh, live_counts, base_of
     with torch.cuda.device(dev):
         rc = _lib.lib().fdms_expire_compact(
             positions_per_lh.data_ptr(), 0, positions_per_lh.stride(0), positions_per_lh.stride(1),
-            ev.data_ptr(), 0, ev.stride(0), ev.stride(1),
+            ev.data_ptr(), 0, ev.stride(0), ev.stride(1), None,
             live_counts.data_ptr(), base_offsets.data_ptr(), 0, live_counts.stride(0),
             compact_k.data_ptr(), compact_v.data_ptr(), 0, row_bytes, compact_k.shape[0],
             None, 0, 0, 0, None, None, 0,

@@ -183,10 +183,19 @@ int32_t fdms_extract_decisions(
  * current_positions: int64 [num_seqs].  stats: optional int64[5] {evicted, live_before_min,
  * live_before_max, live_after_min, live_after_max}; the caller initialises it to
  * {0, INT64_MAX, 0, INT64_MAX, 0}.
+ * row_index (optional, no counterpart in the reference; int32 with the shape and strides of
+ * token_positions): logical slot -> physical row of the span.  When given, positions, evict bits and
+ * the index are compacted in order as above, but K/V rows are not shifted: physical rows only stay
+ * dense in [0, live) -- a dropped slot's row below the new length is refilled with a row from at or
+ * above it, one row copy per dropped slot -- which attention, being independent of row order, reads
+ * as before.  Logical row i of the span is then physical row row_index[i]; entries at or beyond
+ * live equal their own position (the caller initialises the index to 0, 1, 2, ...), so appending at
+ * logical slot live needs no index write.
  * --------------------------------------------------------------------------------------------- */
 int32_t fdms_expire_compact(
     int32_t* token_positions, int64_t pos_stride_l, int64_t pos_stride_s, int64_t pos_stride_h,
     uint8_t* evict_mask, int64_t ev_stride_l, int64_t ev_stride_s, int64_t ev_stride_h,
+    int32_t* row_index,
     int32_t* live_counts, const int32_t* base_offsets,
     int64_t meta_stride_l, int64_t meta_stride_s,
     void* k_pool, void* v_pool, int64_t pool_layer_stride_bytes, int32_t row_bytes, int64_t pool_rows,

@@ -364,6 +364,79 @@ def test_windowed_cadence_matches_oracle_with_same_cadence(dev):
     assert np.array_equal(st.token_positions.cpu().numpy(), o_pos) and np.array_equal(st.evict_mask.cpu().numpy(), o_ev)
 
 
+@pytest.mark.parametrize("paged,interval,T0", [(False, 1, 600), (True, 1, 600), (False, 8, 600), (True, 8, 600),
+                                               (True, 1, 2600), (False, 8, 2600)])
+def test_row_index_expiry_keeps_logical_contents(dev, paged, interval, T0):
+    """Expiry with a row index (K/V rows stay dense but are not shifted): positions, evict bits and
+    compact lengths follow the oracle exactly, and the K/V rows read THROUGH the index are the
+    oracle's rows in logical order.  interval 8 drops several tokens per call (holes and movers in
+    the same call); spans of 600 tokens are handled from registers, spans of 2600 by the tiled path."""
+    rng = np.random.default_rng(11 + interval + int(paged) + T0)
+    L, Hk, D, W, steps = 1, 3, 64, 8, 40
+    C = 1024 if T0 < 1000 else 4096
+    m = _mgr(dev, num_layers=L, num_kv_heads=Hk, capacity_tokens=4 * C, max_model_len=C, head_dim=D,
+             compact_dtype=torch.float8_e4m3fn, max_active_seqs=2, paged=paged, dms_expiry_interval=interval,
+             row_indirection=True)
+    seq = _seq(range(T0), steps + 1)
+    m.allocate(seq)
+    ev0 = rng.random((T0, Hk)) > (0.5 if T0 < 1000 else 0.1)       # long spans keep most tokens
+    k = torch.randn((T0, Hk, D), device=dev, dtype=torch.bfloat16)
+    v = torch.randn((T0, Hk, D), device=dev, dtype=torch.bfloat16)
+    m.streaming_pack_layer(layer_id=0, k=k, v=v, evict_mask=torch.from_numpy(ev0).to(dev),
+                           cu_seqlens_q=torch.tensor([0, T0], dtype=torch.int32), seq_ids=[seq.seq_id], window_size=W)
+    st = m.seq_states[seq.seq_id]
+    ri = m.layer_major_row_index[:, st.active_slot]                        # [L, Hk, C]
+
+    def logical_rows(pool_u8, h, n):
+        base = 0 if paged else int(st.base_offsets[0, h])
+        bt = m.block_tables[0, st.active_slot, h].cpu().numpy() if paged else None
+        phys = O.gather_span(np.arange(m.capacity_tokens), base, n, bt)   # physical row r -> pool row
+        idx = ri[0, h, :n].cpu().numpy()
+        assert sorted(idx.tolist()) == list(range(n)), "the index of the live slots is a permutation of [0, live)"
+        return pool_u8[phys[idx]]
+
+    # oracle state: contiguous spans of its own, contents = the packed rows
+    o_pos, o_ev = st.token_positions.cpu().numpy().copy(), st.evict_mask.cpu().numpy().copy()
+    o_live = st.live_counts.cpu().numpy().copy()
+    o_base = (np.arange(Hk, dtype=np.int32) * C)[None]
+    o_k, o_v = np.zeros((Hk * C, D), np.uint8), np.zeros((Hk * C, D), np.uint8)
+    ck, cv = n_u8(m.compact_k_per_layer[0]), n_u8(m.compact_v_per_layer[0])
+    for h in range(Hk):
+        n = int(o_live[0, h])
+        o_k[o_base[0, h]:o_base[0, h] + n] = logical_rows(ck, h, n)
+        o_v[o_base[0, h]:o_base[0, h] + n] = logical_rows(cv, h, n)
+    for s in range(steps):
+        cur = T0 + s
+        m.apply_dms_evictions([seq], [cur], window_size=W, sync_stats=False)
+        if interval == 1 or s == 0 or cur % interval == 0:
+            O.expire_layer(o_pos[0][None], o_ev[0][None], o_live[0][None], o_base[0][None], o_k, o_v, [cur], W)
+        assert np.array_equal(st.live_counts.cpu().numpy(), o_live), f"compact lengths differ at step {s}"
+        _, _, slot, _ = m.prepare_decode_metadata([seq])
+        _, _, o_slot = O.prepare_decode_metadata(o_base[None], o_live[None])
+        newk = rng.integers(0, 120, size=(Hk, D), dtype=np.uint8)
+        newv = rng.integers(0, 120, size=(Hk, D), dtype=np.uint8)
+        idx = slot[0, 0].long()
+        m.compact_k_per_layer[0].view(torch.uint8)[idx] = torch.from_numpy(newk).to(dev)
+        m.compact_v_per_layer[0].view(torch.uint8)[idx] = torch.from_numpy(newv).to(dev)
+        o_k[o_slot[0, 0]], o_v[o_slot[0, 0]] = newk, newv
+        e = rng.random((L, 1, Hk)) > 0.5
+        m.record_appended_dms_decisions([seq], [cur], torch.from_numpy(e).to(dev), sync_stats=False)
+        O.record_decisions(o_pos[:, None], o_ev[:, None], o_live[:, None], e, [cur])
+        if s % 7 == 0 or s == steps - 1:
+            ck, cv = n_u8(m.compact_k_per_layer[0]), n_u8(m.compact_v_per_layer[0])
+            for h in range(Hk):
+                n, b = int(o_live[0, h]), int(o_base[0, h])
+                assert np.array_equal(logical_rows(ck, h, n), o_k[b:b + n]), f"K rows differ at step {s}, head {h}"
+                assert np.array_equal(logical_rows(cv, h, n), o_v[b:b + n]), f"V rows differ at step {s}, head {h}"
+                assert np.array_equal(ri[0, h, n:].cpu().numpy(), np.arange(n, ri.shape[-1])), "index tail is the identity"
+    assert np.array_equal(st.token_positions.cpu().numpy(), o_pos) and np.array_equal(st.evict_mask.cpu().numpy(), o_ev)
+    from fastdms_b200 import _lib
+    assert _lib.read_device_status(dev) == 0
+    m.free(seq.seq_id)
+    if paged:
+        assert m.free_page_counts.tolist() == [m.pages_per_layer] * L
+
+
 def test_capacity_errors(dev):
     m = _mgr(dev, num_layers=1, num_kv_heads=2, capacity_tokens=64, max_model_len=64, head_dim=16,
              compact_dtype=torch.float32, max_active_seqs=2)

@@ -24,7 +24,7 @@ def golden():
         return {k: z[k] for k in z.files}
 
 
-def _engine(golden, kv_dtype, paged, eager=False):
+def _engine(golden, kv_dtype, paged, eager=False, row_index=True):
     import make_golden_model as G
     from fastdms_b200 import LLM
     from fastdms_b200.layers import rotary_embedding
@@ -32,7 +32,8 @@ def _engine(golden, kv_dtype, paged, eager=False):
     llm = LLM("config0-tiny-llama", hf_config=dict(G.MODEL_CFG), random_init_seed=G.SEED, dtype="float32",
               kv_cache_dtype=kv_dtype, max_model_len=1024, max_num_seqs=4, max_num_batched_tokens=4096,
               compact_kv_capacity_tokens=8192, dms_window_size=G.WINDOW, dms_alpha_scale=G.ALPHA_SCALE,
-              dms_alpha_offset=G.ALPHA_OFFSET, compact_kv_paged=paged, enforce_eager=eager, device="cuda:0")
+              dms_alpha_offset=G.ALPHA_OFFSET, compact_kv_paged=paged, enforce_eager=eager, compact_kv_row_indirection=row_index,
+              device="cuda:0")
     # the rotary table the reference used (cos/sin of the same float32 angles can differ by an ulp
     # between math libraries; the table is an input of the path, not part of it)
     cache = llm.model_runner.model.model.layers[0].self_attn.rotary_emb.cos_sin_cache
@@ -41,12 +42,13 @@ def _engine(golden, kv_dtype, paged, eager=False):
     return llm, G
 
 
-@pytest.mark.parametrize("tag,kv_dtype,paged,eager", [
-    ("f32", "float32", False, False), ("fp8", "float8_e4m3fn", False, False),
-    ("fp8", "float8_e4m3fn", True, False), ("fp8", "float8_e4m3fn", False, True)])
-def test_config0_matches_reference_trace(golden, tag, kv_dtype, paged, eager):
+@pytest.mark.parametrize("tag,kv_dtype,paged,eager,row_index", [
+    ("f32", "float32", False, False, True), ("fp8", "float8_e4m3fn", False, False, True),
+    ("fp8", "float8_e4m3fn", True, False, True), ("fp8", "float8_e4m3fn", False, True, True),
+    ("f32", "float32", False, False, False), ("fp8", "float8_e4m3fn", True, False, False)])
+def test_config0_matches_reference_trace(golden, tag, kv_dtype, paged, eager, row_index):
     from fastdms_b200 import SamplingParams, _lib
-    llm, G = _engine(golden, kv_dtype, paged, eager)
+    llm, G = _engine(golden, kv_dtype, paged, eager, row_index)
     prompts = G.make_prompts()
     sp = SamplingParams(temperature=0.0, max_tokens=G.DECODE_STEPS + 1, ignore_eos=True)
     seqs = [llm.add_request(p, sp) for p in prompts]
