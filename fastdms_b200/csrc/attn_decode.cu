@@ -134,10 +134,15 @@ __device__ __forceinline__ void mma_top(float& c0, float& c1, uint32_t a0, uint3
     (void)d2; (void)d3;
 }
 
-// Physical row inside a page for MMA column n of n-tile u.  The permutation keeps the K reads
-// (rows tokrow(u, g), 16 bytes per lane) free of bank conflicts and the V reads (rows
-// tokrow(u, 2t), tokrow(u, 2t+1), 8 bytes per lane) at the 2-way minimum that 64-byte rows allow.
+// Physical row inside a page for MMA column n of n-tile u.  Two permutations:
+//  * staged loader (LIN = false): keeps the shared-memory K reads (rows tokrow(u, g), 16 bytes per
+//    lane) free of bank conflicts and the V reads (rows tokrow(u, 2t), tokrow(u, 2t+1), 8 bytes per
+//    lane) at the 2-way minimum that 64-byte rows allow;
+//  * direct loader (LIN = true): the four V rows one instruction reads (columns 2t, or 2t+1, of all
+//    quads) are consecutive rows, so that with 64-byte rows every V load covers whole 128-byte lines.
+template <bool LIN>
 __device__ __forceinline__ int tokrow(int u, int n) {
+    if (LIN) return 8 * u + (n >> 1) + 4 * (n & 1);
     const int tp = n >> 1;
     return 8 * u + 2 * tp + ((n & 1) ^ (tp & 1));
 }
@@ -254,7 +259,7 @@ __device__ __forceinline__ void load_frags_smem(const uint8_t* Ks, const uint8_t
     using C = FastCfg<D>;
 #pragma unroll
     for (int u = 0; u < 2; ++u) {
-        const int r = tokrow(u, g);
+        const int r = tokrow<false>(u, g);
         if (C::kCh == 1) {
             f.k[u][0] = *(const uint4*)(Ks + r * D + 16 * t);
         } else {
@@ -266,7 +271,7 @@ __device__ __forceinline__ void load_frags_smem(const uint8_t* Ks, const uint8_t
             f.k[u][0] = sw ? c : a;
             f.k[u][C::kCh - 1] = sw ? a : c;
         }
-        const int rA = tokrow(u, 2 * t), rB = tokrow(u, 2 * t + 1);
+        const int rA = tokrow<false>(u, 2 * t), rB = tokrow<false>(u, 2 * t + 1);
 #pragma unroll
         for (int ch = 0; ch < C::kCh; ++ch) {
             f.va[u][ch] = *(const uint2*)(Vs + rA * D + 64 * ch + 8 * g);
@@ -276,15 +281,15 @@ __device__ __forceinline__ void load_frags_smem(const uint8_t* Ks, const uint8_t
 }
 
 // Byte offsets inside a page of the fragments of lane (g, t); computed once per thread.
-template <int D>
+template <int D, bool LIN>
 struct LaneOffsets {
     int k[2], va[2], vb[2];
     __device__ __forceinline__ LaneOffsets(int g, int t) {
 #pragma unroll
         for (int u = 0; u < 2; ++u) {
-            k[u] = tokrow(u, g) * D + 16 * t;
-            va[u] = tokrow(u, 2 * t) * D + 8 * g;
-            vb[u] = tokrow(u, 2 * t + 1) * D + 8 * g;
+            k[u] = tokrow<LIN>(u, g) * D + 16 * t;
+            va[u] = tokrow<LIN>(u, 2 * t) * D + 8 * g;
+            vb[u] = tokrow<LIN>(u, 2 * t + 1) * D + 8 * g;
         }
     }
 };
@@ -293,9 +298,9 @@ struct LaneOffsets {
 // Per instruction a warp reads whole 32-byte sectors: K 8 rows x 64 bytes, V 4 rows x 64 bytes.
 // In a partial page, rows at or beyond `rows` are not read (they may lie outside the pool) and come
 // back as zeros.
-template <int D>
+template <int D, bool LIN>
 __device__ __forceinline__ void load_frags_global(const uint8_t* Kg, const uint8_t* Vg, int rows, int g, int t,
-                                                  const LaneOffsets<D>& lo, PageFrags<D>& f) {
+                                                  const LaneOffsets<D, LIN>& lo, PageFrags<D>& f) {
     using C = FastCfg<D>;
     if (rows == kPage) {
 #pragma unroll
@@ -311,8 +316,8 @@ __device__ __forceinline__ void load_frags_global(const uint8_t* Kg, const uint8
     }
 #pragma unroll
     for (int u = 0; u < 2; ++u) {
-        const int r = tokrow(u, g);
-        const int rA = tokrow(u, 2 * t), rB = tokrow(u, 2 * t + 1);
+        const int r = tokrow<LIN>(u, g);
+        const int rA = tokrow<LIN>(u, 2 * t), rB = tokrow<LIN>(u, 2 * t + 1);
 #pragma unroll
         for (int ch = 0; ch < C::kCh; ++ch) {
             f.k[u][ch] = r < rows ? __ldcs((const uint4*)(Kg + lo.k[u] + 64 * ch)) : make_uint4(0u, 0u, 0u, 0u);
@@ -324,7 +329,7 @@ __device__ __forceinline__ void load_frags_global(const uint8_t* Kg, const uint8
 
 // One page (`rows` of its 16 rows valid): online-softmax update of the warp's running (m, l, O) for
 // head g.  Fragments of invalid rows must hold finite values (they are masked, not trusted).
-template <int D>
+template <int D, bool LIN>
 __device__ __forceinline__ void process_page(const PageFrags<D>& f, int rows, int t, float sl2,
                                              const uint32_t (&qa)[FastCfg<D>::kKSteps][2], float& m_run, float& l_run,
                                              float (&o)[FastCfg<D>::kNT][2]) {
@@ -350,8 +355,8 @@ __device__ __forceinline__ void process_page(const PageFrags<D>& f, int rows, in
     if (rows < kPage) {
 #pragma unroll
         for (int u = 0; u < 2; ++u) {
-            if (tokrow(u, 2 * t) >= rows) sc[u][0] = -INFINITY;
-            if (tokrow(u, 2 * t + 1) >= rows) sc[u][1] = -INFINITY;
+            if (tokrow<LIN>(u, 2 * t) >= rows) sc[u][0] = -INFINITY;
+            if (tokrow<LIN>(u, 2 * t + 1) >= rows) sc[u][1] = -INFINITY;
         }
     }
     // ---- online softmax (row = head g, reduce over the 4 lanes of the quad) ----
@@ -380,8 +385,8 @@ __device__ __forceinline__ void process_page(const PageFrags<D>& f, int rows, in
         for (int u = 0; u < 2; ++u) {
             uint2 va = f.va[u][ch], vb = f.vb[u][ch];
             if (rows < kPage) {                   // stale bytes must not reach the MMA
-                if (tokrow(u, 2 * t) >= rows) va = make_uint2(0u, 0u);
-                if (tokrow(u, 2 * t + 1) >= rows) vb = make_uint2(0u, 0u);
+                if (tokrow<LIN>(u, 2 * t) >= rows) va = make_uint2(0u, 0u);
+                if (tokrow<LIN>(u, 2 * t + 1) >= rows) vb = make_uint2(0u, 0u);
             }
             const uint32_t x0 = __byte_perm(va.x, vb.x, 0x5140);
             const uint32_t x1 = __byte_perm(va.x, vb.x, 0x7362);
@@ -643,7 +648,7 @@ __global__ void __launch_bounds__(kFastThreads, (D == 64 ? 2 : 1)) attn_decode_f
             const int rows = min(kPage, live - (part + j * nparts) * kPage);
             PageFrags<D> f;
             load_frags_smem<D>(Ks, Ks + C::kPageBytes, g, t, f);
-            process_page<D>(f, rows, t, sl2, qa, m_run, l_run, o);
+            process_page<D, false>(f, rows, t, sl2, qa, m_run, l_run, o);
         }
         __syncwarp();
         if (lane == 0) mbar_arrive(&s_empty[slot]);
@@ -723,7 +728,7 @@ __global__ void __launch_bounds__(kDirectThreads, (D == 64 ? 2 : 1)) attn_decode
     const int n_items = APPEND ? G * half + (tail_cta ? kItemsK + kItemsV : 0) : 0;
     const float* cs_row = APPEND ? p.rope_cs + p.rope_pos[b] * p.rope_stride : nullptr;
 
-    const LaneOffsets<D> lofs(g, t);
+    const LaneOffsets<D, true> lofs(g, t);
     PageFrags<D> buf[DEPTH];
     int brow[DEPTH];
     // Issues the loads of warp-local page i into buffer slot s (page id taken from idreg[s]), then
@@ -739,7 +744,7 @@ __global__ void __launch_bounds__(kDirectThreads, (D == 64 ? 2 : 1)) attn_decode
             brow[s] = rows;
             // in append mode the span's last row is not in the pool yet: it is patched in below
             const int have = (APPEND && pi == tail_pi) ? rows - 1 : rows;
-            load_frags_global<D>(p.k_pool + row0 * D, p.v_pool + row0 * D, have, g, t, lofs, buf[s]);
+            load_frags_global<D, true>(p.k_pool + row0 * D, p.v_pool + row0 * D, have, g, t, lofs, buf[s]);
         }
         const int nxt = pi + DEPTH * stride_pg;
         if (btrow && nxt < npg && nxt < p.bt_pages) idreg[s] = btrow[nxt];
@@ -748,6 +753,13 @@ __global__ void __launch_bounds__(kDirectThreads, (D == 64 ? 2 : 1)) attn_decode
     for (int s = 0; s < DEPTH; ++s) {
         brow[s] = 0;
         if (s < nw && pg0 + s * stride_pg != tail_pi) issue(s, s);
+    }
+    int64_t tail_row = -1;                           // pool row of the new token (block tables are older state)
+    if (APPEND && tail_cta) {
+        const int64_t trow0 = btrow ? (tail_pi < p.bt_pages ? (int64_t)btrow[tail_pi] * kPage : -1)
+                                    : base + (int64_t)tail_pi * kPage;
+        const int64_t r = trow0 + (live - 1 - tail_pi * kPage);
+        tail_row = (trow0 >= 0 && r < p.pool_rows) ? r : -2;
     }
     // The span's last page holds the row written by the preceding kernel of the stream (or, in append
     // mode, older rows only), and q / k / v come from it: all are read only after the dependency has
@@ -760,13 +772,6 @@ __global__ void __launch_bounds__(kDirectThreads, (D == 64 ? 2 : 1)) attn_decode
     const float sl2 = p.scale * (p.k_scale ? p.k_scale[h] : 1.0f) * kLog2e;
     uint32_t qa[C::kKSteps][2];
     if (APPEND) {
-        int64_t tail_row = -1;                       // pool row of the new token
-        if (tail_cta) {
-            const int64_t trow0 = btrow ? (tail_pi < p.bt_pages ? (int64_t)btrow[tail_pi] * kPage : -1)
-                                        : base + (int64_t)tail_pi * kPage;
-            const int64_t r = trow0 + (live - 1 - tail_pi * kPage);
-            tail_row = (trow0 >= 0 && r < p.pool_rows) ? r : -2;
-        }
         for (int it = tid; it < n_items; it += kDirectThreads) {
             if (it < G * half + kItemsK) {
                 // one rotation pair of a q head (it < G * half) or of the new K row
@@ -846,13 +851,13 @@ __global__ void __launch_bounds__(kDirectThreads, (D == 64 ? 2 : 1)) attn_decode
                     for (int u = 0; u < 2; ++u) {
 #pragma unroll
                         for (int ch = 0; ch < C::kCh; ++ch) {
-                            if (tokrow(u, g) == r_new) buf[s].k[u][ch] = *(const uint4*)(s_new + 64 * ch + 16 * t);
-                            if (tokrow(u, 2 * t) == r_new) buf[s].va[u][ch] = *(const uint2*)(s_new + D + 64 * ch + 8 * g);
-                            if (tokrow(u, 2 * t + 1) == r_new) buf[s].vb[u][ch] = *(const uint2*)(s_new + D + 64 * ch + 8 * g);
+                            if (tokrow<true>(u, g) == r_new) buf[s].k[u][ch] = *(const uint4*)(s_new + 64 * ch + 16 * t);
+                            if (tokrow<true>(u, 2 * t) == r_new) buf[s].va[u][ch] = *(const uint2*)(s_new + D + 64 * ch + 8 * g);
+                            if (tokrow<true>(u, 2 * t + 1) == r_new) buf[s].vb[u][ch] = *(const uint2*)(s_new + D + 64 * ch + 8 * g);
                         }
                     }
                 }
-                if (brow[s] > 0) process_page<D>(buf[s], brow[s], t, sl2, qa, m_run, l_run, o);
+                if (brow[s] > 0) process_page<D, true>(buf[s], brow[s], t, sl2, qa, m_run, l_run, o);
                 if (i + DEPTH < nw) issue(s, i + DEPTH);
             }
         }
