@@ -66,6 +66,14 @@ def run(args) -> dict:
     # replicas draw different prompts; tensor-parallel ranks must see the same ones
     g = torch.Generator().manual_seed(args.seed + (rank if args.tp == 1 else 0))
     vocab = hf["vocab_size"]
+    if not args.no_warmup:
+        # one untimed round (library handles, autotuning, lazy allocations), like the reference's
+        # post-warm-up numbers
+        wsp = SamplingParams(temperature=0.0, max_tokens=3, ignore_eos=True)
+        for _ in range(c):
+            engine.add_request(torch.randint(0, vocab, (args.prompt_len,), generator=g).tolist(), wsp)
+        while not engine.is_finished():
+            engine.step()
     sp = SamplingParams(temperature=0.0, max_tokens=args.decode_steps + 2, ignore_eos=True)
     seqs = [engine.add_request(torch.randint(0, vocab, (args.prompt_len,), generator=g).tolist(), sp) for _ in range(c)]
 
@@ -129,6 +137,7 @@ def main() -> None:
     ap.add_argument("--expiry-interval", type=int, default=1)
     ap.add_argument("--paged", action="store_true")
     ap.add_argument("--eager", action="store_true")
+    ap.add_argument("--no-warmup", action="store_true")
     ap.add_argument("--seed", type=int, default=0)
     args = ap.parse_args()
     out = run(args)

@@ -1,0 +1,133 @@
+"""Continuous-batching stress of the compact-DMS engine on synthetic traffic: Poisson arrivals, prompt
+lengths log-uniform, generation lengths uniform, a cap on concurrent sequences and (optionally) on the
+compact KV pool.  Shapes and arrival process follow the reference's serving-style runs
+(`benchmarks/soak_compact_dms.py`, `benchmarks/bench_llama_wikitext2.py`); token ids are random.
+
+    python -m fastdms_b200.bench_serving --shape llama-1b --requests 256 --rate 20 \
+        --min-prompt 512 --max-prompt 32768 --min-gen 64 --max-gen 512 --max-concurrent 64 [--kv-gib 8]
+
+Requests are admitted by the scheduler when the token budget and the compact pool's worst-case
+reservation allow (no preemption: a request that does not fit waits, which `queue_wait_s` reports).
+Whole prompts are prefilled in one step.  Prints one JSON line: request and token throughput, time to
+first token, decode step statistics, peak live rows of the pool, and a check that every page / span
+went back to the pool at the end."""
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import time
+
+import numpy as np
+import torch
+
+
+def run(args) -> dict:
+    from fastdms_b200 import _lib
+    from fastdms_b200.bench_model import SHAPES
+    from fastdms_b200.engine.llm_engine import LLMEngine
+    from fastdms_b200.sampling_params import SamplingParams
+
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    rng = np.random.default_rng(args.seed)
+    n = args.requests
+    arrivals = np.cumsum(rng.exponential(1.0 / args.rate, size=n))
+    prompts = np.exp(rng.uniform(math.log(args.min_prompt), math.log(args.max_prompt), size=n)).astype(np.int64)
+    gens = rng.integers(args.min_gen, args.max_gen + 1, size=n)
+    hf = dict(SHAPES[args.shape])
+    max_len = int(args.max_prompt + args.max_gen + 8)
+    hf.update(attention_bias=True, torch_dtype="bfloat16", max_position_embeddings=max_len)
+    elem_rows = hf["num_hidden_layers"] * 2 * hf["head_dim"]                 # FP8 bytes per pool row over all layers
+    budget = int(args.kv_gib * (1 << 30)) if args.kv_gib else None
+    engine = LLMEngine(
+        f"synthetic-{args.shape}", hf_config=hf, random_init_seed=args.seed, device=dev, max_model_len=max_len,
+        max_num_seqs=args.max_concurrent, max_num_batched_tokens=max(2 * args.max_prompt, 16384),
+        kv_cache_dtype="float8_e4m3fn", compact_kv_paged=args.paged, compact_kv_budget_bytes=budget,
+        dms_window_size=args.window)
+    mgr = engine.model_runner.compact_kv_manager
+    vocab = hf["vocab_size"]
+    g = torch.Generator().manual_seed(args.seed)
+    token_lists = [torch.randint(0, vocab, (int(p),), generator=g).tolist() for p in prompts]
+
+    # warm-up: one short request through prefill and a few decode steps
+    engine.add_request(token_lists[0][:512], SamplingParams(temperature=0.0, max_tokens=4, ignore_eos=True))
+    while not engine.is_finished():
+        engine.step()
+    torch.cuda.synchronize(dev)
+
+    seqs, first_token_at, done_at = {}, {}, {}
+    nxt = 0
+    decode_ms, decode_batch, prefill_tokens, peak_live = [], [], 0, 0
+    t0 = time.perf_counter()
+    while len(done_at) < n:
+        now = time.perf_counter() - t0
+        while nxt < n and arrivals[nxt] <= now:
+            sp = SamplingParams(temperature=0.0, max_tokens=int(gens[nxt]), ignore_eos=True)
+            seqs[nxt] = engine.add_request(token_lists[nxt], sp)
+            nxt += 1
+        if engine.is_finished():
+            time.sleep(max(0.0, min(0.01, arrivals[nxt] - now)))
+            continue
+        ts = time.perf_counter()
+        _, num_tokens = engine.step()
+        te = time.perf_counter()
+        if num_tokens > 0:
+            prefill_tokens += num_tokens
+        else:
+            decode_ms.append((te - ts) * 1e3)
+            decode_batch.append(-num_tokens)
+        for i, s in seqs.items():
+            if i not in first_token_at and s.num_completion_tokens > 0:
+                first_token_at[i] = te - t0
+            if i not in done_at and s.is_finished:
+                done_at[i] = te - t0
+        if len(decode_ms) % 64 == 1:
+            peak_live = max(peak_live, int(mgr.layer_major_live_counts[0].sum().item()))
+    torch.cuda.synchronize(dev)
+    wall = time.perf_counter() - t0
+    out_tokens = int(sum(s.num_completion_tokens for s in seqs.values()))
+    ttft = np.array([first_token_at[i] - arrivals[i] for i in range(n)])
+    lat = np.array([done_at[i] - arrivals[i] for i in range(n)])
+    if mgr.paged:
+        pool_clean = mgr.free_page_counts.tolist() == [mgr.pages_per_layer] * mgr.num_layers
+    else:
+        pool_clean = mgr.free_ranges_per_layer == [[(0, mgr.capacity_tokens)]] * mgr.num_layers
+    dm = np.array(decode_ms) if decode_ms else np.zeros(1)
+    return {
+        "shape": args.shape, "requests": n, "arrival_rate_per_s": args.rate, "max_concurrent": args.max_concurrent,
+        "prompt_len": [int(prompts.min()), int(np.median(prompts)), int(prompts.max())],
+        "gen_len": [int(gens.min()), int(np.median(gens)), int(gens.max())],
+        "wall_s": wall, "requests_per_s": n / wall, "output_tok_s": out_tokens / wall,
+        "total_tok_s": (out_tokens + prefill_tokens) / wall, "prefill_tokens": int(prefill_tokens), "output_tokens": out_tokens,
+        "ttft_s": {"p50": float(np.median(ttft)), "p90": float(np.quantile(ttft, 0.9)), "max": float(ttft.max())},
+        "latency_s": {"p50": float(np.median(lat)), "p90": float(np.quantile(lat, 0.9)), "max": float(lat.max())},
+        "decode_steps": len(decode_ms), "decode_ms_per_step": {"p50": float(np.median(dm)), "p90": float(np.quantile(dm, 0.9))},
+        "mean_decode_batch": float(np.mean(decode_batch)) if decode_batch else 0.0,
+        "pool_rows_per_layer": mgr.capacity_tokens, "pool_gib": mgr.capacity_tokens * elem_rows / (1 << 30),
+        "peak_live_rows_layer0_sampled": peak_live, "admission_denied": int(mgr.admission_denied_count),
+        "pool_returned_clean": bool(pool_clean), "layout": "paged" if mgr.paged else "spans",
+        "device_status": int(_lib.read_device_status(dev)),
+        "data": "synthetic: random-init bf16 weights, uniform random token ids; no preemption (requests wait for capacity)",
+    }
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--shape", default="llama-1b")
+    ap.add_argument("--requests", type=int, default=256)
+    ap.add_argument("--rate", type=float, default=20.0)
+    ap.add_argument("--min-prompt", type=int, default=512)
+    ap.add_argument("--max-prompt", type=int, default=32768)
+    ap.add_argument("--min-gen", type=int, default=64)
+    ap.add_argument("--max-gen", type=int, default=512)
+    ap.add_argument("--max-concurrent", type=int, default=64)
+    ap.add_argument("--kv-gib", type=float, default=0.0)
+    ap.add_argument("--window", type=int, default=256)
+    ap.add_argument("--paged", action="store_true")
+    ap.add_argument("--seed", type=int, default=0)
+    print(json.dumps(run(ap.parse_args())))
+
+
+if __name__ == "__main__":
+    main()
