@@ -99,7 +99,7 @@ class ClockSampler:
                         self.reasons.add(k)
             except Exception:
                 pass
-            self._stop.wait(0.02)
+            self._stop.wait(0.002)
 
     def __enter__(self):
         if self.nv is not None:
@@ -386,12 +386,13 @@ def run_ours(args) -> None:
         hp.step_device()
     barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    with ClockSampler(local) as clocks:
-        e0.record()
-        for _ in range(args.steps):
-            hp.step_device()
-        e1.record()
-        barrier()
+    clocks = ClockSampler(local)        # samples SM clock and throttle reasons through every timed region below
+    clocks.__enter__()
+    e0.record()
+    for _ in range(args.steps):
+        hp.step_device()
+    e1.record()
+    barrier()
     step_ms = e0.elapsed_time(e1) / args.steps
     t = torch.tensor([step_ms], device=dev, dtype=torch.float64)
     if world > 1:
@@ -431,6 +432,7 @@ def run_ours(args) -> None:
     per_launch_s, bytes_per_launch, attn_launches = time_attention_kernel(hp, dev, reps=max(20, args.steps), overlap=False)
     ov_launch_s, _, _ = time_attention_kernel(hp, dev, reps=max(20, args.steps), overlap=True)
     peak, peak_kind = measured_peaks()
+    clocks.__exit__()
     achieved = bytes_per_launch / ov_launch_s / 1e9
     status = _lib.read_device_status(dev)
 
