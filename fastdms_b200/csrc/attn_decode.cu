@@ -408,6 +408,9 @@ __device__ __forceinline__ void process_page(const PageFrags<D>& f, int rows, in
 // distributed shared memory, and lets the leader (or, with several clusters per span, the last
 // leader to arrive) write the output.
 template <int D>
+constexpr int kPartialStride = D + 4;          // floats per (warp, head) row of the in-CTA partial buffer
+
+template <int D>
 __device__ __forceinline__ void fold_and_write(const AttnParams& p, float* s_m, float* s_l, float* s_o, float* r_ml,
                                                float* r_o, int* s_last_ptr, int tid, int warp, int g, int t, int b,
                                                int h, int item, int rank, int chunk, float m_run, float l_run,
@@ -419,12 +422,17 @@ __device__ __forceinline__ void fold_and_write(const AttnParams& p, float* s_m, 
     l_run += __shfl_xor_sync(0xffffffffu, l_run, 2);
     if (t == 0) { s_m[warp * kMaxGroup + g] = m_run; s_l[warp * kMaxGroup + g] = l_run; }
     if (g < G) {
-        float* so = s_o + ((size_t)warp * kMaxGroup + g) * D;
+        // a lane's 16 values of a 64-element chunk are consecutive elements 16t .. 16t+15: four 128-bit
+        // stores; rows are padded by 4 floats so that the eight lanes of a store phase hit four
+        // different bank groups (the unpadded scalar version was a 16-way bank conflict)
+        float* so = s_o + ((size_t)warp * kMaxGroup + g) * kPartialStride<D>;
 #pragma unroll
-        for (int jn = 0; jn < C::kNT; ++jn) {
-            const int ch = jn >> 3, jj = jn & 7;
-            so[64 * ch + 16 * t + jj] = o[jn][0];
-            so[64 * ch + 16 * t + 8 + jj] = o[jn][1];
+        for (int ch = 0; ch < C::kCh; ++ch) {
+            float4* dst = (float4*)(so + 64 * ch + 16 * t);
+            dst[0] = make_float4(o[8 * ch + 0][0], o[8 * ch + 1][0], o[8 * ch + 2][0], o[8 * ch + 3][0]);
+            dst[1] = make_float4(o[8 * ch + 4][0], o[8 * ch + 5][0], o[8 * ch + 6][0], o[8 * ch + 7][0]);
+            dst[2] = make_float4(o[8 * ch + 0][1], o[8 * ch + 1][1], o[8 * ch + 2][1], o[8 * ch + 3][1]);
+            dst[3] = make_float4(o[8 * ch + 4][1], o[8 * ch + 5][1], o[8 * ch + 6][1], o[8 * ch + 7][1]);
         }
     }
     consumer_bar();
@@ -442,7 +450,7 @@ __device__ __forceinline__ void fold_and_write(const AttnParams& p, float* s_m, 
 #pragma unroll
             for (int w = 0; w < kConsumerWarps; ++w) {
                 const float f = ex2(s_m[w * kMaxGroup + gg] - M);
-                acc += f * s_o[((size_t)w * kMaxGroup + gg) * D + d];
+                acc += f * s_o[((size_t)w * kMaxGroup + gg) * kPartialStride<D> + d];
                 Lsum += f * s_l[w * kMaxGroup + gg];
             }
         }
@@ -541,7 +549,7 @@ __global__ void __launch_bounds__(kFastThreads, (D == 64 ? 2 : 1)) attn_decode_f
     float* s_m = (float*)(s_empty + NS);                      // [warps][8]
     float* s_l = s_m + kConsumerWarps * kMaxGroup;            // [warps][8]
     float* s_o = s_l + kConsumerWarps * kMaxGroup;            // [warps][8][D]
-    float* r_ml = s_o + kConsumerWarps * kMaxGroup * D;       // [S][G][2]   partials received from the cluster
+    float* r_ml = s_o + kConsumerWarps * kMaxGroup * kPartialStride<D>;       // [S][G][2]   partials received from the cluster
     float* r_o = r_ml + S * G * 2;                            // [S][G][D]
     __shared__ int s_abort, s_last;
 
@@ -682,7 +690,7 @@ __global__ void __launch_bounds__(kDirectThreads, (D == 64 ? 2 : 1)) attn_decode
     float* s_m = (float*)smem;                                // [warps][8]
     float* s_l = s_m + kConsumerWarps * kMaxGroup;            // [warps][8]
     float* s_o = s_l + kConsumerWarps * kMaxGroup;            // [warps][8][D]
-    float* r_ml = s_o + kConsumerWarps * kMaxGroup * D;       // [S][G][2]
+    float* r_ml = s_o + kConsumerWarps * kMaxGroup * kPartialStride<D>;       // [S][G][2]
     float* r_o = r_ml + S * G * 2;                            // [S][G][D]
     __shared__ int s_last;
     __shared__ __align__(16) __half s_q[APPEND ? kMaxGroup * D : 8];     // rotated q, [G][D]
@@ -974,13 +982,13 @@ static int env_int(const char* name, int dflt) {
 static size_t fast_smem_bytes(int D, int stages, int splits, int group) {
     size_t s = (size_t)stages * 2 * kPage * D;          // ring
     s += (size_t)stages * 2 * sizeof(uint64_t);         // barriers
-    s += (size_t)kConsumerWarps * kMaxGroup * (2 + D) * sizeof(float);
+    s += (size_t)kConsumerWarps * kMaxGroup * (2 + D + 4) * sizeof(float);
     s += (size_t)splits * group * (2 + D) * sizeof(float);
     return s + 128;
 }
 
 static size_t direct_smem_bytes(int D, int splits, int group) {
-    return (size_t)kConsumerWarps * kMaxGroup * (2 + D) * sizeof(float) + (size_t)splits * group * (2 + D) * sizeof(float) + 128;
+    return (size_t)kConsumerWarps * kMaxGroup * (2 + D + 4) * sizeof(float) + (size_t)splits * group * (2 + D) * sizeof(float) + 128;
 }
 
 typedef void (*AttnKernel)(AttnParams);
