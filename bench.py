@@ -402,23 +402,25 @@ def run_ours(args) -> None:
 
     # ---- e2e: host buffers in, host buffers out, every step -----------------------------------------
     bank = 4
-    hq = [torch.randn(hp.q.shape, generator=torch.Generator().manual_seed(100 + i)).to(hp.q.dtype) for i in range(bank)]
-    hk = [torch.randn(hp.k.shape, generator=torch.Generator().manual_seed(200 + i)).to(hp.k.dtype) for i in range(bank)]
-    hv = [torch.randn(hp.v.shape, generator=torch.Generator().manual_seed(300 + i)).to(hp.v.dtype) for i in range(bank)]
-    for i in range(bank):
+    # the step's inputs live in pinned host memory, in blocks laid out like the device input block
+    # (what a serving process would keep as its staging buffers): one H2D copy per step
+    blocks = [hp.new_host_block() for _ in range(bank)]
+    for i, (_, bq, bk, bv, _) in enumerate(blocks):
+        bq.copy_(torch.randn(hp.q.shape, generator=torch.Generator().manual_seed(100 + i)).to(hp.q.dtype))
+        bk.copy_(torch.randn(hp.k.shape, generator=torch.Generator().manual_seed(200 + i)).to(hp.k.dtype))
+        bv.copy_(torch.randn(hp.v.shape, generator=torch.Generator().manual_seed(300 + i)).to(hp.v.dtype))
         lane = torch.where(torch.rand((L, B, HK), generator=torch.Generator().manual_seed(400 + i)) < EVICT_RATE, 1.0, -1.0)
-        hq[i][:, :, 0::HQ // HK, D - 1] = lane.to(hq[i].dtype)
+        bq[:, :, 0::HQ // HK, D - 1] = lane.to(bq.dtype)
     pos0 = int(hp.positions[0].item())
-    hpos = torch.empty((B,), dtype=torch.int64)
     for i in range(max(3, args.warmup)):
-        hpos.fill_(pos0); pos0 += 1
-        hp.step_host(hq[i % bank], hk[i % bank], hv[i % bank], hpos)
+        blocks[i % bank][4].fill_(pos0); pos0 += 1
+        hp.step_host_block(blocks[i % bank][0])
     barrier()
     t0 = time.perf_counter()
     e0.record()
     for i in range(args.steps):
-        hpos.fill_(pos0); pos0 += 1
-        hp.step_host(hq[i % bank], hk[i % bank], hv[i % bank], hpos)
+        blocks[i % bank][4].fill_(pos0); pos0 += 1
+        hp.step_host_block(blocks[i % bank][0])
     e1.record()
     barrier()
     e2e_ms = max(e0.elapsed_time(e1), (time.perf_counter() - t0) * 1e3) / args.steps

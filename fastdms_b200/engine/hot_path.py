@@ -47,11 +47,11 @@ class DecodeHotPath:
         self.cos_sin_cache = cos_sin_cache.to(device=dev, dtype=torch.float32).contiguous()
         self.slots_t = manager._slots_tensor(self.states)
         # device-resident step state
-        self.q = torch.zeros((L, B, self.Hq, D), device=dev, dtype=act_dtype)
-        self.k = torch.zeros((L, B, Hk, D), device=dev, dtype=act_dtype)
-        self.v = torch.zeros((L, B, Hk, D), device=dev, dtype=act_dtype)
+        # q | k | v | positions live in ONE device block so that a host-driven step needs one copy
+        self._act_dtype = act_dtype
+        self._in_block = torch.zeros((self._block_bytes(),), device=dev, dtype=torch.uint8)
+        self.q, self.k, self.v, self.positions = self._block_views(self._in_block)
         self.out = torch.zeros((L, B, self.Hq, D), device=dev, dtype=act_dtype)
-        self.positions = torch.zeros((B,), device=dev, dtype=torch.int64)
         self.evict_all = torch.zeros((L, B, Hk), device=dev, dtype=torch.bool)
         self.base = torch.zeros((L, B, Hk), device=dev, dtype=torch.int32)
         self.live = torch.zeros_like(self.base)
@@ -69,6 +69,32 @@ class DecodeHotPath:
         self.fuse_store = can_fuse if fuse_store is None else bool(fuse_store)
         self.launches_per_step = 2 + (1 if self.fuse_store else 2) * L + 1
         _lib.attn_workspace(dev, B, Hk, D)          # allocate outside any capture
+
+    # ---------------------------------------------------------------- input block layout
+    def _block_sizes(self):
+        e = torch.empty((), dtype=self._act_dtype).element_size()
+        nq = self.L * self.B * self.Hq * self.D * e
+        nk = self.L * self.B * self.Hk * self.D * e
+        return nq, nk, self.B * 8
+
+    def _block_bytes(self) -> int:
+        nq, nk, npos = self._block_sizes()
+        return nq + 2 * nk + npos                    # every part is a multiple of 16 bytes for head_dim >= 8
+
+    def _block_views(self, block: torch.Tensor):
+        nq, nk, npos = self._block_sizes()
+        L, B, D = self.L, self.B, self.D
+        q = block[:nq].view(self._act_dtype).view(L, B, self.Hq, D)
+        k = block[nq:nq + nk].view(self._act_dtype).view(L, B, self.Hk, D)
+        v = block[nq + nk:nq + 2 * nk].view(self._act_dtype).view(L, B, self.Hk, D)
+        pos = block[nq + 2 * nk:nq + 2 * nk + npos].view(torch.int64)
+        return q, k, v, pos
+
+    def new_host_block(self):
+        """A pinned host block with the layout of the device input block and its (q, k, v, positions)
+        views: fill the views, then `step_host_block(block)` moves all of it with one copy."""
+        block = torch.zeros((self._block_bytes(),), dtype=torch.uint8).pin_memory()
+        return (block, *self._block_views(block))
 
     # ---------------------------------------------------------------- the step itself
     def _enqueue(self) -> None:
@@ -134,18 +160,29 @@ class DecodeHotPath:
 
     def step_host(self, q_host: torch.Tensor, k_host: torch.Tensor, v_host: torch.Tensor,
                   positions_host: torch.Tensor) -> torch.Tensor:
-        """Host buffers in, host buffer out.  Inputs are staged through pinned memory, copied to
-        the device, the step runs, and the attention output [layers, batch, q_heads, head_dim] is
-        copied back.  Returns the pinned result tensor (overwritten by the next call)."""
+        """Host buffers in, host buffer out.  Inputs that already sit in pinned memory are copied to
+        the device directly; pageable ones are staged through pinned buffers first.  The step runs
+        and the attention output [layers, batch, q_heads, head_dim] is copied back.  Returns the
+        pinned result tensor (overwritten by the next call)."""
         self._ensure_pinned()
-        self._h_q.copy_(q_host)
-        self._h_k.copy_(k_host)
-        self._h_v.copy_(v_host)
-        self._h_pos.copy_(positions_host)
-        self.q.copy_(self._h_q, non_blocking=True)
-        self.k.copy_(self._h_k, non_blocking=True)
-        self.v.copy_(self._h_v, non_blocking=True)
-        self.positions.copy_(self._h_pos, non_blocking=True)
+        for dst, stage, src in ((self.q, self._h_q, q_host), (self.k, self._h_k, k_host), (self.v, self._h_v, v_host),
+                                (self.positions, self._h_pos, positions_host)):
+            if not (src.is_pinned() and src.dtype == dst.dtype and src.is_contiguous()):
+                stage.copy_(src)
+                src = stage
+            dst.copy_(src, non_blocking=True)
+        self.step_device()
+        self._h_out.copy_(self.out, non_blocking=True)
+        torch.cuda.current_stream(self.m.device).synchronize()
+        return self._h_out
+
+    def step_host_block(self, block: torch.Tensor) -> torch.Tensor:
+        """Like `step_host`, for inputs prepared in a block from `new_host_block()`: one host-to-device
+        copy, the step, one device-to-host copy of the outputs."""
+        if block.dtype != torch.uint8 or block.numel() != self._in_block.numel() or not block.is_pinned():
+            raise ValueError("step_host_block takes a pinned block made by new_host_block()")
+        self._ensure_pinned()
+        self._in_block.copy_(block, non_blocking=True)
         self.step_device()
         self._h_out.copy_(self.out, non_blocking=True)
         torch.cuda.current_stream(self.m.device).synchronize()
