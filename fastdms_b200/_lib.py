@@ -49,7 +49,7 @@ _SIGNATURES = {
     "fdms_build_decode_metadata": (I32, [P, P, I64, I64, P, I64, I64, I64, I32, P, P, I64, P,
                                          P, P, P, P, I32, I32, I32, P, P]),
     "fdms_record_decisions": (I32, [P, I64, I64, I64, P, I64, I64, I64, P, I64, I64, P, I64, I64, P, P,
-                                    I32, I32, I32, I32, P, P]),
+                                    I32, I32, I32, I32, P, I32, P]),
     "fdms_kv_quant": (I32, [P, I32, P, P, I64, I32, I32, P]),
     "fdms_kv_dequant": (I32, [P, P, I32, P, I64, I32, I32, P]),
     "fdms_rmsnorm": (I32, [P, I64, P, I64, P, P, I64, P, I64, I32, I64, I32, F, P]),

@@ -95,9 +95,12 @@ __global__ void record_decisions_kernel(
     uint8_t* ev, int64_t ev_sl, int64_t ev_ss, int64_t ev_sh,
     const int32_t* live, int64_t meta_sl, int64_t meta_ss,
     const uint8_t* evict_all, int64_t ea_sl, int64_t ea_sb,
-    const int64_t* positions, const int32_t* seq_slots,
-    int total, int batch, int hk, int capacity, unsigned long long* true_count) {
-    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    int64_t* positions, const int32_t* seq_slots,
+    int total, int batch, int hk, int capacity, unsigned long long* true_count, int advance) {
+  // With `advance` the launch is a single CTA that strides over all spans and, once every read of
+  // positions[] is done, adds one to each of them (the step's last use of the positions).
+  for (int i0 = blockIdx.x * blockDim.x; i0 < total; i0 += gridDim.x * blockDim.x) {     // uniform per CTA
+    const int i = i0 + threadIdx.x;
     bool e = false;
     if (i < total) {
         const int l = i / (batch * hk);
@@ -115,6 +118,11 @@ __global__ void record_decisions_kernel(
         const unsigned m = __ballot_sync(0xffffffffu, e);
         if ((threadIdx.x & 31) == 0 && m) atomicAdd(true_count, (unsigned long long)__popc(m));
     }
+  }
+  if (advance) {
+      __syncthreads();
+      for (int b = threadIdx.x; b < batch; b += blockDim.x) positions[b] += 1;
+  }
 }
 
 // Pops ceil(rows_needed / 16) pages per span from the layer's free stack into its block table
@@ -200,9 +208,9 @@ extern "C" int32_t fdms_record_decisions(
     uint8_t* evict_mask, int64_t ev_stride_l, int64_t ev_stride_s, int64_t ev_stride_h,
     const int32_t* live_counts, int64_t meta_stride_l, int64_t meta_stride_s,
     const uint8_t* evict_all, int64_t ea_stride_l, int64_t ea_stride_b,
-    const int64_t* positions, const int32_t* seq_slots,
+    int64_t* positions, const int32_t* seq_slots,
     int32_t num_layers, int32_t batch, int32_t num_kv_heads, int32_t capacity,
-    int64_t* true_count, void* stream) {
+    int64_t* true_count, int32_t advance_positions, void* stream) {
     clear_error();
     FDMS_REQUIRE(token_positions && evict_mask && live_counts && evict_all && positions, FDMS_E_ARG,
                  "fdms_record_decisions: null pointer");
@@ -211,11 +219,12 @@ extern "C" int32_t fdms_record_decisions(
     const int64_t total = (int64_t)num_layers * batch * num_kv_heads;
     if (total == 0) return FDMS_OK;
     FDMS_REQUIRE(total < (1ll << 31), FDMS_E_CAPACITY, "fdms_record_decisions: too many spans");
-    const int threads = 256;
-    record_decisions_kernel<<<(unsigned)((total + threads - 1) / threads), threads, 0, (cudaStream_t)stream>>>(
+    const int threads = advance_positions ? 1024 : 256;
+    const unsigned blocks = advance_positions ? 1u : (unsigned)((total + threads - 1) / threads);
+    record_decisions_kernel<<<blocks, threads, 0, (cudaStream_t)stream>>>(
         token_positions, pos_stride_l, pos_stride_s, pos_stride_h, evict_mask, ev_stride_l, ev_stride_s,
         ev_stride_h, live_counts, meta_stride_l, meta_stride_s, evict_all, ea_stride_l, ea_stride_b, positions,
-        seq_slots, (int)total, batch, num_kv_heads, capacity, (unsigned long long*)true_count);
+        seq_slots, (int)total, batch, num_kv_heads, capacity, (unsigned long long*)true_count, advance_positions ? 1 : 0);
     FDMS_CHECK_LAUNCH("record_decisions_kernel");
     return FDMS_OK;
 }

@@ -542,9 +542,10 @@ class CompactKVManager:
         _lib.check(rc)
 
     def record_device(self, slots_t: torch.Tensor, positions_t: torch.Tensor, evict_all: torch.Tensor,
-                      true_count: torch.Tensor | None = None) -> None:
+                      true_count: torch.Tensor | None = None, advance_positions: bool = False) -> None:
         """The decision-recording launch on device-resident arguments (capture-safe).
-        positions_t int64 [batch]; evict_all bool [layers, batch, kv_heads], head-contiguous."""
+        positions_t int64 [batch]; evict_all bool [layers, batch, kv_heads], head-contiguous.
+        `advance_positions` adds one to every position once all spans are recorded (same launch)."""
         dev = self.device
         pos, ev = self.layer_major_token_positions, self.layer_major_evict_mask.view(torch.uint8)
         lc = self.layer_major_live_counts
@@ -556,7 +557,7 @@ class CompactKVManager:
                 lc.data_ptr(), lc.stride(0), lc.stride(1),
                 ea.data_ptr(), ea.stride(0), ea.stride(1),
                 positions_t.data_ptr(), slots_t.data_ptr(), self.num_layers, slots_t.numel(), self.num_kv_heads,
-                self.max_model_len, _lib.ptr(true_count), _lib.stream_ptr(dev))
+                self.max_model_len, _lib.ptr(true_count), 1 if advance_positions else 0, _lib.stream_ptr(dev))
         _lib.check(rc)
 
     # ------------------------------------------------------------------ decode metadata

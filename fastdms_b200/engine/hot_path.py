@@ -9,7 +9,8 @@ models/llama.py:138-201 per layer, model_runner.py:681-711 record):
     ->  decision recording (all layers)  ->  positions += 1
 
 Everything is a launch on device-resident state, so the whole step is ONE graph replay:
-2 + layers + 1 kernels of this library (2 + 2 * layers + 1 unfused) plus one position increment.
+2 + layers + 1 kernels of this library (2 + 2 * layers + 1 unfused); the recording launch also
+advances the positions.
 
 `DecodeHotPath` is driven either with activations that already sit in its device buffers
 (`step_device`) or with host buffers (`step_host`: pinned host -> device copies of the step's
@@ -123,8 +124,7 @@ class DecodeHotPath:
             compact_decode_attention(
                 self.q[l], ck, cv, self.base[l], self.live[l], scale=self.scale, block_tables=bt,
                 k_scale=ks, v_scale=vs, out=self.out[l], overlap_previous_kernel=self.overlap)
-        m.record_device(self.slots_t, self.positions, self.evict_all)
-        self.positions.add_(1)
+        m.record_device(self.slots_t, self.positions, self.evict_all, advance_positions=True)
 
     def capture(self) -> None:
         """Runs one eager step (warm-up; it advances the state like any step) and records the graph."""

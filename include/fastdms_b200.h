@@ -275,15 +275,18 @@ int32_t fdms_build_decode_metadata(
 
 /* Replaces fastdms/engine/compact_kv.py:1562-1725 record_appended_dms_decisions (kernel :426-484):
  * token_positions[l, slot, h, live-1] = positions[b]; evict_mask[...] = evict_all[l,b,h];
- * true_count (optional int64, caller-zeroed) accumulates the number of true decisions. */
+ * true_count (optional int64, caller-zeroed) accumulates the number of true decisions.
+ * advance_positions != 0 (no counterpart in the reference): after every span has been recorded,
+ * positions[b] += 1 for the whole batch, in the same launch -- for callers that keep the step's
+ * positions on the device across steps. */
 int32_t fdms_record_decisions(
     int32_t* token_positions, int64_t pos_stride_l, int64_t pos_stride_s, int64_t pos_stride_h,
     uint8_t* evict_mask, int64_t ev_stride_l, int64_t ev_stride_s, int64_t ev_stride_h,
     const int32_t* live_counts, int64_t meta_stride_l, int64_t meta_stride_s,
     const uint8_t* evict_all, int64_t ea_stride_l, int64_t ea_stride_b,
-    const int64_t* positions, const int32_t* seq_slots,
+    int64_t* positions, const int32_t* seq_slots,
     int32_t num_layers, int32_t batch, int32_t num_kv_heads, int32_t capacity,
-    int64_t* true_count, void* stream);
+    int64_t* true_count, int32_t advance_positions, void* stream);
 
 /* ---------------------------------------------------------------------------------------------
  * (d) FP8 e4m3 KV quantise / dequantise with a per-KV-head scale, x [n, kv_heads, head_dim].
