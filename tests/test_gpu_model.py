@@ -119,3 +119,49 @@ def test_sampling_and_argument_errors(golden):
     assert res[1]["token_ids"] == golden["fp8_tokens"][:7, 1].tolist()     # the greedy request is unaffected
     with pytest.raises(ValueError):
         llm.add_request(list(range(1000)), SamplingParams(max_tokens=100))
+
+
+@pytest.mark.parametrize("kv_dtype,tol", [("float32", 2e-3), ("float8_e4m3fn", 0.15)])
+def test_no_eviction_window_equals_dense_attention(golden, kv_dtype, tol):
+    """Property the reference guards with benchmarks/check_no_evict_regression.py and
+    check_dms_compact_guard.py (window 1 000 000): when no token can leave the window, decoding
+    through the compact pool must give the logits of plain dense causal attention.  The dense side is
+    the same model in prefill mode over prompt + generated tokens (teacher forcing), so the two
+    sides share nothing of the compact decode path (store, metadata, expiry, compact attention).
+    With an FP8 pool the dense side still attends to unquantised K/V, so the bound is the FP8
+    rounding of the cache (the reference bounds that by KLD, benchmarks/check_fp8_kv_guard.py)."""
+    import make_golden_model as G
+    from fastdms_b200 import LLM, SamplingParams
+    from fastdms_b200.engine.sequence import Sequence
+    from fastdms_b200.layers import rotary_embedding
+    rotary_embedding._ROPE_CACHE.clear()
+    llm = LLM("config0-tiny-llama", hf_config=dict(G.MODEL_CFG), random_init_seed=G.SEED, dtype="float32",
+              kv_cache_dtype=kv_dtype, max_model_len=1024, max_num_seqs=4, max_num_batched_tokens=4096,
+              compact_kv_capacity_tokens=16384, dms_window_size=1_000_000, dms_alpha_scale=G.ALPHA_SCALE,
+              dms_alpha_offset=G.ALPHA_OFFSET, device="cuda:0")
+    prompts = G.make_prompts()[:3]
+    steps = 12
+    sp = SamplingParams(temperature=0.0, max_tokens=steps + 2, ignore_eos=True)      # still running after `steps`
+    seqs = [llm.add_request(p, sp) for p in prompts]
+    runner, mgr = llm.model_runner, llm.model_runner.compact_kv_manager
+    llm.step()
+    decode_logits = []
+    for _ in range(steps):
+        llm.step()
+        decode_logits.append(runner.graphs[len(seqs)].logits.float().cpu().numpy().copy())
+    # nothing was dropped: every span holds prompt + generated tokens
+    live = torch.stack([mgr.seq_states[s.seq_id].live_counts for s in seqs], dim=1).cpu().numpy()
+    for i, s in enumerate(seqs):
+        assert (live[:, i] == len(prompts[i]) + steps).all()
+    tokens = [list(s.token_ids) for s in seqs]
+    while not llm.is_finished():
+        llm.step()
+    for t in (0, 5, steps - 1):
+        # decode step t consumed token number len(prompt) + t and predicted the next one
+        dense = [Sequence(tokens[i][: len(prompts[i]) + t + 1], SamplingParams(max_tokens=1)) for i in range(len(seqs))]
+        logits = runner.run_prefill(dense).float().cpu().numpy()
+        runner.free_compact([d.seq_id for d in dense])
+        err = np.abs(logits - decode_logits[t]).max()
+        assert err < tol, f"decode step {t}: compact vs dense logits differ by {err}"
+        if kv_dtype == "float32":
+            assert (logits.argmax(-1) == decode_logits[t].argmax(-1)).all()
