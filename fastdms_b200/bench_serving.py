@@ -6,8 +6,9 @@ compact KV pool.  Shapes and arrival process follow the reference's serving-styl
     python -m fastdms_b200.bench_serving --shape llama-1b --requests 256 --rate 20 \
         --min-prompt 512 --max-prompt 32768 --min-gen 64 --max-gen 512 --max-concurrent 64 [--kv-gib 8]
 
-Requests are admitted by the scheduler when the token budget and the compact pool's worst-case
-reservation allow (no preemption: a request that does not fit waits, which `queue_wait_s` reports).
+Requests are admitted by the scheduler when the token budget and the compact pool allow: charged
+their worst case (`--admission reserve`) or an estimate of what DMS keeps, with a retry when a
+prefill does not fit (`--admission optimistic`, contiguous spans).  Nothing that runs is preempted.
 Whole prompts are prefilled in one step.  Prints one JSON line: request and token throughput, time to
 first token, decode step statistics, peak live rows of the pool, and a check that every page / span
 went back to the pool at the end."""
@@ -44,7 +45,8 @@ def run(args) -> dict:
         f"synthetic-{args.shape}", hf_config=hf, random_init_seed=args.seed, device=dev, max_model_len=max_len,
         max_num_seqs=args.max_concurrent, max_num_batched_tokens=max(2 * args.max_prompt, 16384),
         kv_cache_dtype="float8_e4m3fn", compact_kv_paged=args.paged, compact_kv_budget_bytes=budget,
-        dms_window_size=args.window)
+        dms_window_size=args.window, compact_kv_admission=args.admission,
+        compact_kv_admission_keep_estimate=args.keep_estimate)
     mgr = engine.model_runner.compact_kv_manager
     vocab = hf["vocab_size"]
     g = torch.Generator().manual_seed(args.seed)
@@ -105,7 +107,8 @@ def run(args) -> dict:
         "decode_steps": len(decode_ms), "decode_ms_per_step": {"p50": float(np.median(dm)), "p90": float(np.quantile(dm, 0.9))},
         "mean_decode_batch": float(np.mean(decode_batch)) if decode_batch else 0.0,
         "pool_rows_per_layer": mgr.capacity_tokens, "pool_gib": mgr.capacity_tokens * elem_rows / (1 << 30),
-        "peak_live_rows_layer0_sampled": peak_live, "admission_denied": int(mgr.admission_denied_count),
+        "peak_live_rows_layer0_sampled": peak_live, "admission": args.admission,
+        "admission_denied": int(mgr.admission_denied_count), "prefill_retries": int(engine.scheduler.prefill_retries),
         "pool_returned_clean": bool(pool_clean), "layout": "paged" if mgr.paged else "spans",
         "device_status": int(_lib.read_device_status(dev)),
         "data": "synthetic: random-init bf16 weights, uniform random token ids; no preemption (requests wait for capacity)",
@@ -125,6 +128,8 @@ def main() -> None:
     ap.add_argument("--kv-gib", type=float, default=0.0)
     ap.add_argument("--window", type=int, default=256)
     ap.add_argument("--paged", action="store_true")
+    ap.add_argument("--admission", choices=["reserve", "optimistic"], default="reserve")
+    ap.add_argument("--keep-estimate", type=float, default=0.2)
     ap.add_argument("--seed", type=int, default=0)
     print(json.dumps(run(ap.parse_args())))
 

@@ -53,6 +53,8 @@ class Config:
     compact_kv_paged: bool = False            # 16-row pages + GPU free stack instead of first-fit spans
     dms_expiry_interval: int = 1              # 1 = exact expiry every step; N = when position % N == 0
     compact_kv_row_indirection: bool = True   # expiry compacts metadata only and refills freed K/V rows
+    compact_kv_admission: str = "reserve"     # "reserve": worst case per request; "optimistic": estimate + retry
+    compact_kv_admission_keep_estimate: float = 0.25
     random_init_seed: int | None = None       # synthetic weights when the directory has no safetensors
     dtype: str | None = None                  # overrides the checkpoint's dtype
 

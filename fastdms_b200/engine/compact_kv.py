@@ -107,6 +107,9 @@ class CompactKVManager:
         v_scale: torch.Tensor | None = None,
         dms_expiry_interval: int = 1,
         row_indirection: bool = False,
+        admission: str = "reserve",
+        admission_keep_estimate: float = 0.25,
+        admission_window: int = 256,
     ):
         if capacity_tokens <= 0:
             raise ValueError(f"capacity_tokens must be positive, got {capacity_tokens}")
@@ -128,6 +131,14 @@ class CompactKVManager:
         self.paged = bool(paged)
         self.dms_expiry_interval = int(dms_expiry_interval)
         self.row_indirection = bool(row_indirection)
+        if admission not in ("reserve", "optimistic"):
+            raise ValueError(f"admission must be 'reserve' or 'optimistic', got {admission!r}")
+        if admission == "optimistic" and paged:
+            raise ValueError("optimistic admission needs contiguous spans: pages are taken during decode, "
+                             "where running out cannot be retried")
+        self.admission = admission
+        self.admission_keep_estimate = float(admission_keep_estimate)
+        self.admission_window = int(admission_window)
         self.debug_checks = os.environ.get("FASTDMS_COMPACT_DEBUG_CHECKS") == "1"
         self.admission_denied_count = 0
         L, S, Hk, C = self.num_layers, self.max_active_seqs, self.num_kv_heads, self.max_model_len
@@ -279,15 +290,34 @@ class CompactKVManager:
             return min(worst, max(1, int(self.target_live_tokens_per_seq)))
         return worst
 
-    def can_allocate(self, seq: Sequence) -> bool:
-        """Conservative admission: the worst-case reservation must fit in every layer."""
-        if not self.free_active_slots and seq.seq_id not in self.seq_states:
-            return False
-        needed = self._reservation_tokens(seq) * self.num_kv_heads
+    def admission_need(self, seq: Sequence) -> int:
+        """Pool rows per layer a new sequence is charged at admission.  `reserve`: its worst case
+        (every token kept).  `optimistic` (contiguous spans only): an estimate of what the DMS
+        prefill keeps, `prompt * admission_keep_estimate + window`, plus the decode headroom; the
+        engine retries a prefill that turns out not to fit."""
+        rows = self._reservation_tokens(seq)
+        if self.admission == "optimistic":
+            est = int(seq.num_prompt_tokens * self.admission_keep_estimate) + self.admission_window + int(seq.max_tokens) + 1
+            rows = min(rows, max(est, 1))
         if self.paged:
-            needed = ((self._reservation_tokens(seq) + PAGE - 1) // PAGE) * PAGE * self.num_kv_heads
-            return bool((self.free_page_counts.to(torch.int64) * PAGE >= needed).all().item())
-        return all(self.free_tokens_in_layer(l) >= needed for l in range(self.num_layers))
+            rows = ((rows + PAGE - 1) // PAGE) * PAGE
+        return rows * self.num_kv_heads
+
+    def admission_free(self) -> int:
+        """Free pool rows in the fullest layer."""
+        if self.paged:
+            return int(self.free_page_counts.min().item()) * PAGE
+        return min(self.free_tokens_in_layer(l) for l in range(self.num_layers))
+
+    def can_allocate(self, seq: Sequence, pending_rows: int = 0) -> bool:
+        """Admission check (the reference defines it, compact_kv.py:739-745, and never calls it):
+        an active slot is free and the charged rows, on top of `pending_rows` already promised to
+        requests admitted in the same scheduling pass, fit in every layer."""
+        ok = bool(self.free_active_slots or seq.seq_id in self.seq_states) and \
+            self.admission_need(seq) + pending_rows <= self.admission_free()
+        if not ok:
+            self.admission_denied_count += 1
+        return ok
 
     # ------------------------------------------------------------------ registration
     def allocate(self, seq: Sequence) -> CompactKVSequenceState:

@@ -19,7 +19,8 @@ class LLMEngine:
         self.model_runner = ModelRunner(config, device=kwargs.get("device"))
         self.tokenizer = None
         config.eos = int(getattr(config.hf_config, "eos_token_id", -1) or -1)
-        self.scheduler = Scheduler(config, can_allocate=self.model_runner.compact_kv_manager.can_allocate)
+        mgr = self.model_runner.compact_kv_manager
+        self.scheduler = Scheduler(config, can_allocate=mgr.can_allocate, admission_need=mgr.admission_need)
         self.last_decode_tok_s = 0.0
         self.last_prefill_tok_s = 0.0
 
@@ -44,7 +45,19 @@ class LLMEngine:
     def step(self):
         seqs, is_prefill = self.scheduler.schedule()
         num_tokens = sum(seq.num_scheduled_tokens for seq in seqs) if is_prefill else -len(seqs)
-        token_ids = self.model_runner.run(seqs, is_prefill)
+        if is_prefill:
+            try:
+                token_ids = self.model_runner.run(seqs, True)
+            except RuntimeError as e:
+                if "capacity exhausted" not in str(e):
+                    raise
+                # optimistic admission charged less than the prompts kept: give everything back and retry later
+                self.model_runner.free_compact([seq.seq_id for seq in seqs])
+                self.scheduler.requeue(seqs)
+                return [], 0
+            self.scheduler.prefill_succeeded()
+        else:
+            token_ids = self.model_runner.run(seqs, False)
         self.scheduler.postprocess(seqs, token_ids, is_prefill)
         freed = self.scheduler.consume_freed_seq_ids()
         if freed:

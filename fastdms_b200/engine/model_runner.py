@@ -174,7 +174,9 @@ class ModelRunner:
             device=self.device, target_live_tokens_per_seq=c.compact_kv_target_live_tokens_per_seq,
             head_dim=self.head_dim, compact_dtype=kv_dtype, max_active_seqs=c.max_num_seqs, paged=c.compact_kv_paged,
             dms_expiry_interval=c.dms_expiry_interval,
-            row_indirection=c.compact_kv_row_indirection)
+            row_indirection=c.compact_kv_row_indirection, admission=c.compact_kv_admission,
+            admission_keep_estimate=c.compact_kv_admission_keep_estimate,
+            admission_window=self.dms_metadata.window_size)
 
     # ------------------------------------------------------------------ prefill
     @torch.inference_mode()

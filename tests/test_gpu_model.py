@@ -165,3 +165,36 @@ def test_no_eviction_window_equals_dense_attention(golden, kv_dtype, tol):
         assert err < tol, f"decode step {t}: compact vs dense logits differ by {err}"
         if kv_dtype == "float32":
             assert (logits.argmax(-1) == decode_logits[t].argmax(-1)).all()
+
+
+def test_optimistic_admission_retries_prefills_that_do_not_fit(golden):
+    """A pool far smaller than the worst case, admission charged by an estimate: some prefill batches
+    do not fit, are released and retried; every request still completes with the tokens an
+    unconstrained engine produces, and the pool ends up empty."""
+    import make_golden_model as G
+    from fastdms_b200 import LLM, SamplingParams, _lib
+    from fastdms_b200.layers import rotary_embedding
+
+    def engine(**kw):
+        rotary_embedding._ROPE_CACHE.clear()
+        return LLM("config0-tiny-llama", hf_config=dict(G.MODEL_CFG), random_init_seed=G.SEED, dtype="float32",
+                   kv_cache_dtype="float32", max_model_len=1024, max_num_seqs=8, max_num_batched_tokens=8192,
+                   dms_window_size=G.WINDOW, dms_alpha_scale=G.ALPHA_SCALE, dms_alpha_offset=G.ALPHA_OFFSET,
+                   device="cuda:0", **kw)
+
+    prompts = G.make_prompts() + [p[: len(p) // 2 + 5] for p in G.make_prompts()]       # 8 requests
+    sp = SamplingParams(temperature=0.0, max_tokens=12, ignore_eos=True)
+    want = [r["token_ids"] for r in engine(compact_kv_capacity_tokens=65536).generate(prompts, sp)]
+    # worst case of the eight requests is about 2 * 1400 rows per layer; the pool holds 600, and the
+    # estimate (2 % of the prompt + window + generation) lets too many in at once
+    llm = engine(compact_kv_capacity_tokens=600, compact_kv_admission="optimistic", compact_kv_admission_keep_estimate=0.02)
+    got = [r["token_ids"] for r in llm.generate(prompts, sp)]
+    mgr = llm.model_runner.compact_kv_manager
+    assert llm.scheduler.prefill_retries > 0, "the test is meant to exercise the retry path"
+    assert [len(t) for t in got] == [12] * len(prompts)
+    assert got == want
+    assert mgr.free_ranges_per_layer == [[(0, mgr.capacity_tokens)]] * mgr.num_layers
+    assert sorted(mgr.free_active_slots) == list(range(mgr.max_active_seqs))
+    assert _lib.read_device_status("cuda:0") == 0
+    with pytest.raises(ValueError):
+        engine(compact_kv_capacity_tokens=600, compact_kv_admission="optimistic", compact_kv_paged=True)

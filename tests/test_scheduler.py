@@ -1,0 +1,107 @@
+"""Host-side scheduler logic (no GPU): admission accounting within one pass, and the retry policy of
+optimistic admission (requeue at the front, halved prefill batch, hold while requests are running)."""
+from __future__ import annotations
+
+from types import SimpleNamespace
+
+import pytest
+
+from fastdms_b200.engine.scheduler import Scheduler
+from fastdms_b200.engine.sequence import Sequence, SequenceStatus
+from fastdms_b200.sampling_params import SamplingParams
+
+
+class Pool:
+    """Stand-in for the manager's admission interface: every request is charged its prompt length."""
+
+    def __init__(self, free):
+        self.free = free
+        self.denied = 0
+
+    def need(self, seq):
+        return seq.num_prompt_tokens
+
+    def can_allocate(self, seq, pending=0):
+        ok = self.need(seq) + pending <= self.free
+        self.denied += not ok
+        return ok
+
+
+def _sched(pool, max_seqs=8, budget=10_000):
+    cfg = SimpleNamespace(max_num_seqs=max_seqs, max_num_batched_tokens=budget, eos=-1)
+    return Scheduler(cfg, can_allocate=pool.can_allocate, admission_need=pool.need)
+
+
+def _seq(n, max_tokens=2):
+    return Sequence(list(range(n)), SamplingParams(temperature=0.0, max_tokens=max_tokens, ignore_eos=True))
+
+
+def test_rows_promised_earlier_in_the_pass_count():
+    pool = Pool(free=100)
+    s = _sched(pool)
+    a, b = _seq(60), _seq(60)
+    s.add(a); s.add(b)
+    batch, is_prefill = s.schedule()
+    assert is_prefill and batch == [a] and list(s.waiting) == [b] and pool.denied == 1
+    pool.free -= 60                                   # the prefill took its rows
+    batch, is_prefill = s.schedule()                  # b still does not fit: decode a
+    assert not is_prefill and batch == [a]
+    s.postprocess([a], [7], False); s.postprocess([a], [7], False)
+    assert a.status == SequenceStatus.FINISHED and s.consume_freed_seq_ids() == [a.seq_id]
+    pool.free += 60
+    batch, is_prefill = s.schedule()
+    assert is_prefill and batch == [b]
+
+
+def test_failed_prefill_is_requeued_in_order_and_the_batch_halves():
+    pool = Pool(free=10_000)
+    s = _sched(pool)
+    seqs = [_seq(10 + i) for i in range(4)]
+    for q in seqs:
+        s.add(q)
+    batch, _ = s.schedule()
+    assert batch == seqs
+    s.requeue(batch)
+    assert list(s.waiting) == seqs and not s.running and s.prefill_retries == 1
+    assert all(q.status == SequenceStatus.WAITING for q in seqs)
+    batch, is_prefill = s.schedule()
+    assert is_prefill and batch == seqs[:2]           # half the failed batch
+    s.prefill_succeeded()
+    batch, is_prefill = s.schedule()
+    assert is_prefill and batch == seqs[2:]           # the limit is gone after a success
+
+
+def test_single_failure_waits_for_a_running_request_to_finish():
+    pool = Pool(free=10_000)
+    s = _sched(pool)
+    a, b = _seq(10, max_tokens=2), _seq(20)
+    s.add(a)
+    assert s.schedule() == ([a], True)
+    s.prefill_succeeded()
+    s.postprocess([a], [1], True)
+    s.add(b)
+    assert s.schedule() == ([b], True)
+    s.requeue([b])                                     # did not fit while a is running
+    assert s.hold_prefill and list(s.waiting) == [b]
+    assert s.schedule() == ([a], False)                # no new prefill attempt: decode
+    s.postprocess([a], [1], False)                     # a finishes -> capacity came back
+    assert a.status == SequenceStatus.FINISHED and not s.hold_prefill
+    assert s.schedule() == ([b], True)
+
+
+def test_request_that_cannot_fit_alone_raises():
+    pool = Pool(free=10_000)
+    s = _sched(pool)
+    a = _seq(10)
+    s.add(a)
+    batch, _ = s.schedule()
+    with pytest.raises(RuntimeError, match="even alone"):
+        s.requeue(batch)
+
+
+def test_nothing_admissible_and_nothing_running_raises():
+    pool = Pool(free=5)
+    s = _sched(pool)
+    s.add(_seq(10))
+    with pytest.raises(RuntimeError, match="no request fits"):
+        s.schedule()
