@@ -62,6 +62,7 @@ class DecodeHotPath:
         # pinned staging for the host-driven step
         self._h_q = self._h_k = self._h_v = self._h_out = self._h_pos = None
         self.graph = None
+        self._host_graphs: dict = {}
         self.use_cuda_graph = use_cuda_graph
         can_fuse = (manager.compact_dtype == torch.float8_e4m3fn and D in (64, 128)
                     and act_dtype in (torch.bfloat16, torch.float16, torch.float32))
@@ -178,13 +179,31 @@ class DecodeHotPath:
 
     def step_host_block(self, block: torch.Tensor) -> torch.Tensor:
         """Like `step_host`, for inputs prepared in a block from `new_host_block()`: one host-to-device
-        copy, the step, one device-to-host copy of the outputs."""
+        copy, the step, one device-to-host copy of the outputs.  With CUDA graphs enabled the two
+        copies are nodes of a graph captured once per block (the block's address is part of it), so a
+        call is one graph launch and one stream synchronisation."""
         if block.dtype != torch.uint8 or block.numel() != self._in_block.numel() or not block.is_pinned():
             raise ValueError("step_host_block takes a pinned block made by new_host_block()")
         self._ensure_pinned()
-        self._in_block.copy_(block, non_blocking=True)
-        self.step_device()
-        self._h_out.copy_(self.out, non_blocking=True)
+        stream = torch.cuda.current_stream(self.m.device)
+        if not self.use_cuda_graph:
+            self._in_block.copy_(block, non_blocking=True)
+            self._enqueue()
+            self._h_out.copy_(self.out, non_blocking=True)
+            stream.synchronize()
+            return self._h_out
+        if self.graph is None:
+            raise RuntimeError("call capture() before step_host_block()")
+        g = self._host_graphs.get(block.data_ptr())
+        if g is None:
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                self._in_block.copy_(block, non_blocking=True)
+                self._enqueue()
+                self._h_out.copy_(self.out, non_blocking=True)
+            self._host_graphs[block.data_ptr()] = (g, block)        # keeps the block alive with its graph
+            g = self._host_graphs[block.data_ptr()]
+        g[0].replay()
         torch.cuda.current_stream(self.m.device).synchronize()
         return self._h_out
 

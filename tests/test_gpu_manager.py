@@ -453,3 +453,105 @@ def test_capacity_errors(dev):
                                seq_ids=[12345], window_size=4)
     with pytest.raises(ValueError):
         _mgr(dev, num_layers=1, num_kv_heads=2, capacity_tokens=0, max_model_len=64, head_dim=16, compact_dtype=torch.float32)
+
+
+@pytest.mark.parametrize("paged", [False, True])
+def test_hot_path_step_equals_the_manual_kernel_sequence(dev, paged):
+    """DecodeHotPath (one graph replay: expiry, metadata, a fused store+attention launch per layer,
+    recording with position advance) against the same step issued kernel by kernel with the separate
+    store and attention launches on a twin manager: identical outputs and metadata after every step,
+    through step_device, step_host and step_host_block."""
+    from fastdms_b200.engine.hot_path import DecodeHotPath
+    from fastdms_b200.layers.compact_attention import compact_decode_attention, fused_dms_rope_store_compact_decode
+    L, B, Hk, G, D, W = 2, 3, 2, 4, 64, 16
+    Hq = Hk * G
+    T0 = [70, 300, 141]
+    rng = np.random.default_rng(5 + int(paged))
+    gen = torch.Generator(device=dev).manual_seed(9)
+    half = D // 2
+    inv = 1.0 / (500000.0 ** (np.arange(half, dtype=np.float32) / half))
+    ang = np.arange(1024, dtype=np.float32)[:, None] * inv[None, :]
+    cache = torch.from_numpy(np.concatenate([np.cos(ang), np.sin(ang)], axis=1).astype(np.float32)).to(dev).unsqueeze(1)
+    scales = (torch.tensor([[0.02, 0.03], [0.04, 0.01]], device=dev), torch.tensor([[0.025, 0.015], [0.02, 0.03]], device=dev))
+
+    def build():
+        m = _mgr(dev, num_layers=L, num_kv_heads=Hk, capacity_tokens=4096, max_model_len=512, head_dim=D,
+                 compact_dtype=torch.float8_e4m3fn, max_active_seqs=4, paged=paged, row_indirection=True,
+                 k_scale=scales[0], v_scale=scales[1])
+        seqs = [_seq(range(t), 64) for t in T0]
+        for s in seqs:
+            m.allocate(s)
+        cu = torch.tensor(np.concatenate([[0], np.cumsum(T0)]), dtype=torch.int32)
+        return m, seqs, cu
+
+    mA, seqsA, cu = build()
+    mB, seqsB, _ = build()
+    for l in range(L):
+        k = torch.randn((sum(T0), Hk, D), device=dev, generator=gen).to(torch.bfloat16)
+        v = torch.randn((sum(T0), Hk, D), device=dev, generator=gen).to(torch.bfloat16)
+        ev = torch.from_numpy(rng.random((sum(T0), Hk)) < 0.7).to(dev)
+        for m, seqs in ((mA, seqsA), (mB, seqsB)):
+            m.streaming_pack_layer(layer_id=l, k=k, v=v, evict_mask=ev, cu_seqlens_q=cu, seq_ids=[s.seq_id for s in seqs],
+                                   window_size=W)
+    hp = DecodeHotPath(mA, seqsA, num_q_heads=Hq, window_size=W, alpha_scale=100.0, alpha_offset=5.0, cos_sin_cache=cache)
+    assert hp.fuse_store and hp.launches_per_step == 2 + L + 1
+    pos0 = torch.tensor(T0, dtype=torch.int64)
+    hp.set_positions(pos0)
+    slotsB = mB._slots_tensor(mB._states(seqsB))
+    posB = pos0.to(dev)
+    base, live, slot = (torch.zeros((L, B, Hk), device=dev, dtype=torch.int32) for _ in range(3))
+    evB = torch.zeros((L, B, Hk), device=dev, dtype=torch.bool)
+    outB = torch.zeros((L, B, Hq, D), device=dev, dtype=torch.bfloat16)
+    btB = mB.decode_block_tables(seqsB)
+    host_block = None
+
+    def manual_step(q, k, v):
+        mB.expire_device(slotsB, posB, window_size=W)
+        mB.decode_metadata_device(slotsB, base, live, slot)
+        for l in range(L):
+            ks, vs = mB.layer_scales(l)
+            ql = q[l].clone()
+            fused_dms_rope_store_compact_decode(ql, k[l].clone(), v[l], cache, mB.compact_k_per_layer[l], mB.compact_v_per_layer[l],
+                                                slot[l], evB[l], posB, num_kv_heads=Hk, alpha_scale=100.0, alpha_offset=5.0,
+                                                store_transient_k=False, k_scale=ks, v_scale=vs)
+            compact_decode_attention(ql, mB.compact_k_per_layer[l], mB.compact_v_per_layer[l], base[l], live[l],
+                                     block_tables=None if btB is None else btB[l], k_scale=ks, v_scale=vs, out=outB[l])
+        mB.record_device(slotsB, posB, evB)
+        posB.add_(1)
+
+    def new_inputs():
+        q = torch.randn((L, B, Hq, D), device=dev, generator=gen).to(torch.bfloat16)
+        q[:, :, 0::G, D - 1] = torch.where(torch.rand((L, B, Hk), device=dev, generator=gen) < 0.7, 1.0, -1.0).to(torch.bfloat16)
+        k = torch.randn((L, B, Hk, D), device=dev, generator=gen).to(torch.bfloat16)
+        v = torch.randn((L, B, Hk, D), device=dev, generator=gen).to(torch.bfloat16)
+        return q, k, v
+
+    q, k, v = new_inputs()
+    hp.q.copy_(q); hp.k.copy_(k); hp.v.copy_(v)
+    hp.capture()                              # the warm-up inside capture() is a real step
+    manual_step(q, k, v)
+    for step in range(30):
+        q, k, v = new_inputs()
+        if step < 20:
+            hp.q.copy_(q); hp.k.copy_(k); hp.v.copy_(v)
+            hp.step_device()
+            got = hp.out
+        elif step < 25:
+            got = hp.step_host(q.cpu(), k.cpu(), v.cpu(), posB.cpu()).to(dev)
+        else:
+            if host_block is None:
+                host_block = hp.new_host_block()
+            blk, bq, bk, bv, bp = host_block
+            bq.copy_(q.cpu()); bk.copy_(k.cpu()); bv.copy_(v.cpu()); bp.copy_(posB.cpu())
+            got = hp.step_host_block(blk).to(dev)
+        manual_step(q, k, v)
+        assert torch.equal(got, outB), f"outputs differ at step {step}"
+        assert torch.equal(hp.evict_all, evB) and torch.equal(hp.live, live) and torch.equal(hp.positions, posB)
+    for a, b in ((mA.layer_major_live_counts, mB.layer_major_live_counts), (mA.layer_major_token_positions, mB.layer_major_token_positions),
+                 (mA.layer_major_evict_mask, mB.layer_major_evict_mask), (mA.layer_major_row_index, mB.layer_major_row_index)):
+        assert torch.equal(a, b)
+    if not paged:                              # identical first-fit spans: the pools are byte-identical too
+        assert torch.equal(mA.compact_k.view(torch.uint8), mB.compact_k.view(torch.uint8))
+        assert torch.equal(mA.compact_v.view(torch.uint8), mB.compact_v.view(torch.uint8))
+    from fastdms_b200 import _lib
+    assert _lib.read_device_status(dev) == 0
