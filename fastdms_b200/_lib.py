@@ -29,13 +29,13 @@ _SIGNATURES = {
     "fdms_last_error": (c_char_p, []),
     "fdms_attn_decode_workspace_bytes": (I64, [I32, I32, I32]),
     "fdms_attn_decode": (I32, [P, I32, I64, I64, P, P, I32, I64, P, P, I64, P, I64, I64, I32, P, P,
-                               P, I32, I64, I64, I32, I32, I32, I32, F, P, P, I64, P, I64, I32, P, P]),
+                               P, I32, I64, I64, I32, I32, I32, I32, F, P, P, I64, I64, P, I64, I32, P, P]),
     "fdms_attn_decode_append": (I32, [P, P, P, I32, I64, I64, I64, I64, I64, I64, P, P, I32, I64, P, P, I64,
-                                      P, I64, I64, I32, P, P, P, I64, P, P, I64, DBL, DBL, P, I32, I64, I64,
+                                      P, I64, I64, I32, P, P, P, I64, I64, P, P, I64, DBL, DBL, P, I32, I64, I64,
                                       I32, I32, I32, I32, F, P, I64, I32, P, P]),
     "fdms_attn_decode_noalloc": (I32, [P, I32, I64, I64, P, P, I32, I64, P, P, I64, P, I64, I64, I32, P, P,
-                                       P, I32, I64, I64, I32, I32, I32, I32, F, P, P, I64, P, P]),
-    "fdms_store_decode": (I32, [P, I64, I64, P, I64, I64, P, I64, I64, I32, P, I64, P, P, P, I32, I64,
+                                       P, I32, I64, I64, I32, I32, I32, I32, F, P, P, I64, I64, P, P]),
+    "fdms_store_decode": (I32, [P, I64, I64, P, I64, I64, P, I64, I64, I32, P, I64, I64, P, P, P, I32, I64,
                                 P, I64, P, I64, P, P, I32, I32, I32, I32, DBL, DBL, I32, I32, I32, I32, P, P]),
     "fdms_extract_decisions": (I32, [P, I32, I64, I64, P, I64, I64, I32, I32, I32, DBL, DBL, P]),
     "fdms_expire_compact": (I32, [P, I64, I64, I64, P, I64, I64, I64, P, P, P, I64, I64, P, P, I64, I32, I64,

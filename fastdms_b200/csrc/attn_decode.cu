@@ -147,6 +147,9 @@ __device__ __forceinline__ int tokrow(int u, int n) {
     return 8 * u + 2 * tp + ((n & 1) ^ (tp & 1));
 }
 
+struct AttnParams;
+__device__ __forceinline__ int64_t checked_rope_position(const AttnParams& p, int b);
+
 struct AttnParams {
     const void* q; int q_dtype; int64_t q_sb, q_sh;
     const uint8_t* k_pool; const uint8_t* v_pool; int64_t pool_rows;
@@ -156,7 +159,7 @@ struct AttnParams {
     void* out; int out_dtype; int64_t out_sb, out_sh;
     int batch, hq, hk, group;
     float scale;
-    const int64_t* rope_pos; const float* rope_cs; int64_t rope_stride;
+    const int64_t* rope_pos; const float* rope_cs; int64_t rope_stride; int64_t rope_rows;
     int32_t* counters; float* part_ml; float* part_o;     // only used when chunks > 1
     int32_t* dev_status;
     int stages, splits, chunks, overlap;
@@ -169,6 +172,17 @@ struct AttnParams {
     uint8_t* evict_out; int64_t evict_sb;
     DecisionRule rule;
 };
+
+// Position of sequence b for the cos/sin lookup; a value outside the table is flagged and replaced by 0
+// (positions are caller data: an index, so it is checked like slots and pages).
+__device__ __forceinline__ int64_t checked_rope_position(const AttnParams& p, int b) {
+    const int64_t pos = p.rope_pos[b];
+    if (pos < 0 || pos >= p.rope_rows) {
+        if (p.dev_status) atomicOr(p.dev_status, FDMS_DEV_BAD_INDEX);
+        return 0;
+    }
+    return pos;
+}
 
 // ------------------------------------------------------------------------------------------------
 // Fast kernel
@@ -193,7 +207,7 @@ __device__ __forceinline__ float load_q_elem(const AttnParams& p, int b, int hea
     float x1 = lower ? x : load_as_float(p.q, off + i, p.q_dtype);
     float x2 = lower ? load_as_float(p.q, off + half + i, p.q_dtype) : x;
     if (g == 0 && i == half - 1) x2 = 0.0f;      // the borrowed decision channel (head_dim - 1)
-    const float* cs = p.rope_cs + p.rope_pos[b] * p.rope_stride;
+    const float* cs = p.rope_cs + checked_rope_position(p, b) * p.rope_stride;
     const float c = cs[i], s = cs[half + i];
     return lower ? __fsub_rn(__fmul_rn(x1, c), __fmul_rn(x2, s)) : __fadd_rn(__fmul_rn(x2, c), __fmul_rn(x1, s));
 }
@@ -734,7 +748,7 @@ __global__ void __launch_bounds__(kDirectThreads, (D == 64 ? 2 : 1)) attn_decode
     constexpr int kItemsK = half, kItemsV = D / 2;
     const bool tail_cta = APPEND && live > 0 && (tail_pi % nparts) == part;
     const int n_items = APPEND ? G * half + (tail_cta ? kItemsK + kItemsV : 0) : 0;
-    const float* cs_row = APPEND ? p.rope_cs + p.rope_pos[b] * p.rope_stride : nullptr;
+    const float* cs_row = APPEND ? p.rope_cs + checked_rope_position(p, b) * p.rope_stride : nullptr;
 
     const LaneOffsets<D, true> lofs(g, t);
     PageFrags<D> buf[DEPTH];
@@ -1077,7 +1091,7 @@ static int32_t attn_decode_common(
     const float* k_scale, const float* v_scale,
     void* out, int32_t out_dtype, int64_t out_stride_b, int64_t out_stride_h,
     int32_t batch, int32_t num_q_heads, int32_t num_kv_heads, int32_t head_dim, float scale,
-    const int64_t* q_rope_positions, const float* q_rope_cos_sin, int64_t cos_sin_stride,
+    const int64_t* q_rope_positions, const float* q_rope_cos_sin, int64_t cos_sin_stride, int64_t cos_sin_rows,
     void* workspace, int64_t workspace_bytes, int32_t flags, int32_t* dev_status, void* stream,
     const fdms::AppendArgs* app) {
     clear_error();
@@ -1111,7 +1125,8 @@ static int32_t attn_decode_common(
     p.out = out; p.out_dtype = out_dtype; p.out_sb = out_stride_b; p.out_sh = out_stride_h;
     p.batch = batch; p.hq = num_q_heads; p.hk = num_kv_heads; p.group = group;
     p.scale = scale;
-    p.rope_pos = q_rope_positions; p.rope_cs = q_rope_cos_sin; p.rope_stride = cos_sin_stride;
+    p.rope_pos = q_rope_positions; p.rope_cs = q_rope_cos_sin; p.rope_stride = cos_sin_stride; p.rope_rows = cos_sin_rows;
+    FDMS_REQUIRE(q_rope_positions == nullptr || cos_sin_rows > 0, FDMS_E_ARG, "fdms_attn_decode: cos_sin_rows must be positive");
     p.counters = nullptr; p.part_ml = nullptr; p.part_o = nullptr;
     p.dev_status = dev_status;
     p.stages = 0; p.splits = 1; p.chunks = 1; p.overlap = (flags & FDMS_ATTN_OVERLAP_PREVIOUS) ? 1 : 0;
@@ -1213,12 +1228,12 @@ extern "C" int32_t fdms_attn_decode(
     const float* k_scale, const float* v_scale,
     void* out, int32_t out_dtype, int64_t out_stride_b, int64_t out_stride_h,
     int32_t batch, int32_t num_q_heads, int32_t num_kv_heads, int32_t head_dim, float scale,
-    const int64_t* q_rope_positions, const float* q_rope_cos_sin, int64_t cos_sin_stride,
+    const int64_t* q_rope_positions, const float* q_rope_cos_sin, int64_t cos_sin_stride, int64_t cos_sin_rows,
     void* workspace, int64_t workspace_bytes, int32_t flags, int32_t* dev_status, void* stream) {
     return attn_decode_common(q, q_dtype, q_stride_b, q_stride_h, k_pool, v_pool, kv_dtype, pool_rows, base_offsets,
                               live_counts, meta_stride_b, block_tables, bt_stride_b, bt_stride_h, bt_max_pages, k_scale,
                               v_scale, out, out_dtype, out_stride_b, out_stride_h, batch, num_q_heads, num_kv_heads,
-                              head_dim, scale, q_rope_positions, q_rope_cos_sin, cos_sin_stride, workspace,
+                              head_dim, scale, q_rope_positions, q_rope_cos_sin, cos_sin_stride, cos_sin_rows, workspace,
                               workspace_bytes, flags, dev_status, stream, nullptr);
 }
 
@@ -1229,7 +1244,7 @@ extern "C" int32_t fdms_attn_decode_append(
     const int32_t* base_offsets, const int32_t* live_counts, int64_t meta_stride_b,
     const int32_t* block_tables, int64_t bt_stride_b, int64_t bt_stride_h, int32_t bt_max_pages,
     const float* k_scale, const float* v_scale,
-    const float* cos_sin, int64_t cos_sin_stride, const int64_t* positions,
+    const float* cos_sin, int64_t cos_sin_stride, int64_t cos_sin_rows, const int64_t* positions,
     uint8_t* evict_out, int64_t evict_stride_b, double alpha_scale, double alpha_offset,
     void* out, int32_t out_dtype, int64_t out_stride_b, int64_t out_stride_h,
     int32_t batch, int32_t num_q_heads, int32_t num_kv_heads, int32_t head_dim, float scale,
@@ -1242,7 +1257,7 @@ extern "C" int32_t fdms_attn_decode_append(
     return attn_decode_common(q, act_dtype, q_stride_b, q_stride_h, k_pool, v_pool, kv_dtype, pool_rows, base_offsets,
                               live_counts, meta_stride_b, block_tables, bt_stride_b, bt_stride_h, bt_max_pages, k_scale,
                               v_scale, out, out_dtype, out_stride_b, out_stride_h, batch, num_q_heads, num_kv_heads,
-                              head_dim, scale, positions, cos_sin, cos_sin_stride, workspace, workspace_bytes, flags,
+                              head_dim, scale, positions, cos_sin, cos_sin_stride, cos_sin_rows, workspace, workspace_bytes, flags,
                               dev_status, stream, &app);
 }
 
@@ -1304,7 +1319,7 @@ extern "C" int32_t fdms_attn_decode_noalloc(
     const float* k_scale, const float* v_scale,
     void* out, int32_t out_dtype, int64_t out_stride_b, int64_t out_stride_h,
     int32_t batch, int32_t num_q_heads, int32_t num_kv_heads, int32_t head_dim, float scale,
-    const int64_t* q_rope_positions, const float* q_rope_cos_sin, int64_t cos_sin_stride,
+    const int64_t* q_rope_positions, const float* q_rope_cos_sin, int64_t cos_sin_stride, int64_t cos_sin_rows,
     int32_t* dev_status, void* stream) {
     clear_error();
     FDMS_REQUIRE(batch >= 0 && num_kv_heads > 0 && head_dim > 0, FDMS_E_ARG, "fdms_attn_decode_noalloc: bad sizes");
@@ -1327,6 +1342,6 @@ extern "C" int32_t fdms_attn_decode_noalloc(
     return fdms_attn_decode(q, q_dtype, q_stride_b, q_stride_h, k_pool, v_pool, kv_dtype, pool_rows, base_offsets,
                             live_counts, meta_stride_b, block_tables, bt_stride_b, bt_stride_h, bt_max_pages, k_scale,
                             v_scale, out, out_dtype, out_stride_b, out_stride_h, batch, num_q_heads, num_kv_heads,
-                            head_dim, scale, q_rope_positions, q_rope_cos_sin, cos_sin_stride, scratch,
+                            head_dim, scale, q_rope_positions, q_rope_cos_sin, cos_sin_stride, cos_sin_rows, scratch,
                             (int64_t)kStaticScratchBytes, 0, dev_status, stream);
 }

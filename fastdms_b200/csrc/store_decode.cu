@@ -31,7 +31,7 @@ struct StoreParams {
     void* k; int64_t k_sb, k_sh;
     const void* v; int64_t v_sb, v_sh;
     int act_dtype;
-    const float* cos_sin; int64_t cs_stride;
+    const float* cos_sin; int64_t cs_stride; int64_t cs_rows;
     const int64_t* positions;
     void* k_pool; void* v_pool; int kv_dtype; int64_t pool_rows;
     const int32_t* slot; int64_t slot_sb;
@@ -64,7 +64,11 @@ __global__ void store_decode_kernel(StoreParams p) {
     const bool rot_q = p.do_rope && p.store_q;
 
     // ---- round 1: independent loads ----
-    const int64_t pos = p.do_rope ? p.positions[b] : 0;
+    int64_t pos = p.do_rope ? p.positions[b] : 0;
+    if (pos < 0 || (p.do_rope && pos >= p.cs_rows)) {           // positions index the cos/sin table: checked, not trusted
+        if (lane == 0 && p.dev_status) atomicOr(p.dev_status, FDMS_DEV_BAD_INDEX);
+        pos = 0;
+    }
     const int32_t slot = p.slot ? p.slot[(int64_t)b * p.slot_sb + h] : -1;
     const float dv = p.do_decision ? load_as_float(p.q, q0 + p.dim - 1, adt) : 0.0f;
     const float ks = p.k_scale ? p.k_scale[h] : 1.0f;
@@ -166,7 +170,7 @@ extern "C" int32_t fdms_store_decode(
     void* q, int64_t q_stride_b, int64_t q_stride_h,
     void* k, int64_t k_stride_b, int64_t k_stride_h,
     const void* v, int64_t v_stride_b, int64_t v_stride_h, int32_t act_dtype,
-    const float* cos_sin, int64_t cos_sin_stride, const int64_t* positions,
+    const float* cos_sin, int64_t cos_sin_stride, int64_t cos_sin_rows, const int64_t* positions,
     void* k_pool, void* v_pool, int32_t kv_dtype, int64_t pool_rows,
     const int32_t* slot_mapping, int64_t slot_stride_b,
     uint8_t* evict_out, int64_t evict_stride_b,
@@ -188,6 +192,7 @@ extern "C" int32_t fdms_store_decode(
                  "fdms_store_decode: pool dtype %d not supported", kv_dtype);
     FDMS_REQUIRE(k && v, FDMS_E_ARG, "fdms_store_decode: k and v are required");
     FDMS_REQUIRE(!(do_decision || (do_rope && store_q)) || q, FDMS_E_ARG, "fdms_store_decode: q is required");
+    FDMS_REQUIRE(!do_rope || cos_sin_rows > 0, FDMS_E_ARG, "fdms_store_decode: cos_sin_rows must be positive");
     FDMS_REQUIRE(!do_rope || (cos_sin && positions), FDMS_E_ARG,
                  "fdms_store_decode: RoPE needs cos_sin and positions");
     FDMS_REQUIRE(!slot_mapping || (k_pool && v_pool), FDMS_E_ARG, "fdms_store_decode: pools are required");
@@ -198,7 +203,7 @@ extern "C" int32_t fdms_store_decode(
     p.k = k; p.k_sb = k_stride_b; p.k_sh = k_stride_h;
     p.v = v; p.v_sb = v_stride_b; p.v_sh = v_stride_h;
     p.act_dtype = act_dtype;
-    p.cos_sin = cos_sin; p.cs_stride = cos_sin_stride; p.positions = positions;
+    p.cos_sin = cos_sin; p.cs_stride = cos_sin_stride; p.cs_rows = cos_sin_rows; p.positions = positions;
     p.k_pool = k_pool; p.v_pool = v_pool; p.kv_dtype = kv_dtype; p.pool_rows = pool_rows;
     p.slot = slot_mapping; p.slot_sb = slot_stride_b;
     p.evict = evict_out; p.evict_sb = evict_stride_b;

@@ -168,7 +168,7 @@ def compact_decode_attention(
             _lib.ptr(k_scale), _lib.ptr(v_scale),
             out.data_ptr(), _lib.dtype_code(out.dtype), out.stride(0), out.stride(1),
             batch, num_q_heads, num_kv_heads, head_dim, float(scale),
-            _lib.ptr(rope_pos), _lib.ptr(rope_cs), cs_stride,
+            _lib.ptr(rope_pos), _lib.ptr(rope_cs), cs_stride, rope_cs.shape[0] if rope_cs is not None else 0,
             ws.data_ptr(), ws.numel(), _lib.ATTN_OVERLAP_PREVIOUS if overlap_previous_kernel else 0,
             status.data_ptr(), _lib.stream_ptr(dev))
     _lib.check(rc)
@@ -266,7 +266,7 @@ def fused_store_decode_attention(
             compact_k.data_ptr(), compact_v.data_ptr(), _lib.dtype_code(compact_k.dtype), compact_k.shape[0],
             base_offsets.data_ptr(), live_counts.data_ptr(), live_counts.stride(0),
             _lib.ptr(block_tables), bt_sb, bt_sh, bt_pages, _lib.ptr(k_scale), _lib.ptr(v_scale),
-            cos_sin_cache.data_ptr(), cos_sin_cache.stride(0), positions.data_ptr(),
+            cos_sin_cache.data_ptr(), cos_sin_cache.stride(0), cos_sin_cache.shape[0], positions.data_ptr(),
             _lib.ptr(ev_u8), ev_u8.stride(0) if ev_u8 is not None else 0, float(alpha_scale), float(alpha_offset),
             out.data_ptr(), _lib.dtype_code(out.dtype), out.stride(0), out.stride(1),
             batch, num_q_heads, num_kv_heads, head_dim, float(scale),
@@ -308,7 +308,8 @@ def _store_common(q, k, v, cos_sin_cache, compact_k, compact_v, slot_mapping, ev
             _lib.ptr(q), q.stride(0) if q is not None else 0, q.stride(1) if q is not None else 0,
             k.data_ptr(), k.stride(0), k.stride(1),
             v.data_ptr(), v.stride(0), v.stride(1), _lib.dtype_code(k.dtype),
-            _lib.ptr(cos_sin_cache) if do_rope else None, cs_stride, _lib.ptr(positions) if do_rope else None,
+            _lib.ptr(cos_sin_cache) if do_rope else None, cs_stride, cos_sin_cache.shape[0] if do_rope else 0,
+            _lib.ptr(positions) if do_rope else None,
             _lib.ptr(compact_k), _lib.ptr(compact_v),
             _lib.dtype_code(compact_k.dtype) if compact_k is not None else 0,
             compact_k.shape[0] if compact_k is not None else 0,

@@ -64,7 +64,8 @@ const char* fdms_last_error(void);
  * q/out [batch, q_heads, head_dim] with the given element strides (inner stride 1).
  * Optional inline neox RoPE of q at q_rope_positions[b] (int64) with the decision lane
  * (first head of each group, channel head_dim-1) zeroed first; cos_sin rows are
- * [cos(head_dim/2) | sin(head_dim/2)] float32 with row stride cos_sin_stride.
+ * [cos(head_dim/2) | sin(head_dim/2)] float32 with row stride cos_sin_stride and cos_sin_rows rows;
+ * a position outside [0, cos_sin_rows) raises FDMS_DEV_BAD_INDEX in the status word and is read as 0.
  * block_tables: optional int32 [batch, kv_heads, bt_max_pages] (element strides given).
  * workspace: fdms_attn_decode_workspace_bytes(...) bytes, 256-byte aligned.  Its first
  * `batch*kv_heads` int32 must be zero before the FIRST call; every call leaves them zero again.
@@ -87,7 +88,7 @@ int32_t fdms_attn_decode(
     const float* k_scale, const float* v_scale,
     void* out, int32_t out_dtype, int64_t out_stride_b, int64_t out_stride_h,
     int32_t batch, int32_t num_q_heads, int32_t num_kv_heads, int32_t head_dim, float scale,
-    const int64_t* q_rope_positions, const float* q_rope_cos_sin, int64_t cos_sin_stride,
+    const int64_t* q_rope_positions, const float* q_rope_cos_sin, int64_t cos_sin_stride, int64_t cos_sin_rows,
     void* workspace, int64_t workspace_bytes, int32_t flags, int32_t* dev_status, void* stream);
 
 /* Fused decode step of one layer: fdms_store_decode and fdms_attn_decode in ONE launch (the
@@ -106,7 +107,7 @@ int32_t fdms_attn_decode_append(
     const int32_t* base_offsets, const int32_t* live_counts, int64_t meta_stride_b,
     const int32_t* block_tables, int64_t bt_stride_b, int64_t bt_stride_h, int32_t bt_max_pages,
     const float* k_scale, const float* v_scale,
-    const float* cos_sin, int64_t cos_sin_stride, const int64_t* positions,
+    const float* cos_sin, int64_t cos_sin_stride, int64_t cos_sin_rows, const int64_t* positions,
     uint8_t* evict_out, int64_t evict_stride_b, double alpha_scale, double alpha_offset,
     void* out, int32_t out_dtype, int64_t out_stride_b, int64_t out_stride_h,
     int32_t batch, int32_t num_q_heads, int32_t num_kv_heads, int32_t head_dim, float scale,
@@ -132,7 +133,7 @@ int32_t fdms_attn_decode_noalloc(
     const float* k_scale, const float* v_scale,
     void* out, int32_t out_dtype, int64_t out_stride_b, int64_t out_stride_h,
     int32_t batch, int32_t num_q_heads, int32_t num_kv_heads, int32_t head_dim, float scale,
-    const int64_t* q_rope_positions, const float* q_rope_cos_sin, int64_t cos_sin_stride,
+    const int64_t* q_rope_positions, const float* q_rope_cos_sin, int64_t cos_sin_stride, int64_t cos_sin_rows,
     int32_t* dev_status, void* stream);
 
 /* ---------------------------------------------------------------------------------------------
@@ -149,7 +150,7 @@ int32_t fdms_store_decode(
     void* q, int64_t q_stride_b, int64_t q_stride_h,
     void* k, int64_t k_stride_b, int64_t k_stride_h,
     const void* v, int64_t v_stride_b, int64_t v_stride_h, int32_t act_dtype,
-    const float* cos_sin, int64_t cos_sin_stride, const int64_t* positions,
+    const float* cos_sin, int64_t cos_sin_stride, int64_t cos_sin_rows, const int64_t* positions,
     void* k_pool, void* v_pool, int32_t kv_dtype, int64_t pool_rows,
     const int32_t* slot_mapping, int64_t slot_stride_b,
     uint8_t* evict_out, int64_t evict_stride_b,

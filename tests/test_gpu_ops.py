@@ -456,3 +456,41 @@ def test_rmsnorm_and_silu_kernels_match_torch_ops(dev, dtype, rows, hidden):
     wz = torch.nn.functional.silu(a) * b
     assert z.shape == wz.shape
     assert ((z.float() - wz.float()).abs() <= 2 * tol * wz.float().abs() + 1e-6).all()
+
+
+def test_positions_outside_the_rotary_table_are_flagged_not_followed(dev):
+    """positions index the cos/sin table; a value outside it must raise FDMS_DEV_BAD_INDEX in the
+    status word (and be read as position 0), for the store kernel, the inline-RoPE attention and
+    the fused launch alike."""
+    from fastdms_b200 import _lib
+    from fastdms_b200.layers.compact_attention import (compact_decode_attention, fused_dms_rope_store_compact_decode,
+                                                       fused_store_decode_attention)
+    B, Hk, G, D = 2, 2, 4, 64
+    g = torch.Generator(device=dev).manual_seed(3)
+    q = torch.randn((B, Hk * G, D), device=dev, generator=g).to(torch.bfloat16)
+    k = torch.randn((B, Hk, D), device=dev, generator=g).to(torch.bfloat16)
+    v = torch.randn((B, Hk, D), device=dev, generator=g).to(torch.bfloat16)
+    cache = torch.randn((32, 1, D), device=dev, generator=g)
+    ck = torch.zeros((256, D), device=dev, dtype=torch.float8_e4m3fn)
+    cv = torch.zeros_like(ck)
+    base = torch.tensor([[0, 64], [128, 192]], device=dev, dtype=torch.int32)
+    live = torch.full((B, Hk), 20, device=dev, dtype=torch.int32)
+    ev = torch.empty((B, Hk), dtype=torch.bool, device=dev)
+    bad = torch.tensor([5, 1 << 40], device=dev)            # far beyond the 32 rows of the table
+    ok = torch.tensor([5, 31], device=dev)
+    assert _lib.read_device_status(dev) == 0
+    for call in (
+        lambda pos: fused_dms_rope_store_compact_decode(q.clone(), k.clone(), v, cache, ck, cv, (base + live - 1).contiguous(), ev,
+                                                        pos, num_kv_heads=Hk, alpha_scale=100.0, alpha_offset=5.0),
+        lambda pos: compact_decode_attention(q, ck, cv, base, live, q_rope_positions=pos, q_rope_cos_sin_cache=cache),
+        lambda pos: fused_store_decode_attention(q, k, v, cache, ck, cv, base, live, ev, pos, num_kv_heads=Hk,
+                                                 alpha_scale=100.0, alpha_offset=5.0),
+    ):
+        call(ok)
+        assert _lib.read_device_status(dev) == 0
+        call(bad)
+        assert _lib.read_device_status(dev) & 2, "FDMS_DEV_BAD_INDEX expected"
+        _lib.status_word(dev).zero_()
+        call(torch.tensor([-1, 3], device=dev))
+        assert _lib.read_device_status(dev) & 2
+        _lib.status_word(dev).zero_()

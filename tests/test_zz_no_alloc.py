@@ -25,7 +25,7 @@ def _call(fn, q, k, v, base, live, out, ws=None):
     Hk = base.shape[1]
     args = [q.data_ptr(), _lib.BF16, q.stride(0), q.stride(1), k.data_ptr(), v.data_ptr(), _lib.E4M3, k.shape[0],
             base.data_ptr(), live.data_ptr(), live.stride(0), None, 0, 0, 0, None, None,
-            out.data_ptr(), _lib.BF16, out.stride(0), out.stride(1), B, Hq, Hk, D, float(D ** -0.5), None, None, 0]
+            out.data_ptr(), _lib.BF16, out.stride(0), out.stride(1), B, Hq, Hk, D, float(D ** -0.5), None, None, 0, 0]
     if ws is not None:
         args += [ws.data_ptr(), ws.numel(), 0]
     args += [None, torch.cuda.current_stream().cuda_stream]
