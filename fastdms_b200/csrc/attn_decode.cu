@@ -1021,9 +1021,17 @@ static void fill_launch_config(cudaLaunchConfig_t& cfg, cudaLaunchAttribute* att
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     if (overlap) {
-        attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-        attr[1].val.programmaticStreamSerializationAllowed = 1;
-        cfg.numAttrs = 2;
+        attr[cfg.numAttrs].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[cfg.numAttrs].val.programmaticStreamSerializationAllowed = 1;
+        ++cfg.numAttrs;
+    }
+    // cluster placement: load balancing measured 2 % faster per launch than the default (spread) at 64 clusters of 4
+    const int policy = env_int("FDMS_ATTN_CLUSTER_POLICY", 2);      // 0 = driver default, 1 = spread, 2 = load balancing
+    if (policy == 1 || policy == 2) {
+        attr[cfg.numAttrs].id = cudaLaunchAttributeClusterSchedulingPolicyPreference;
+        attr[cfg.numAttrs].val.clusterSchedulingPolicyPreference =
+            policy == 1 ? cudaClusterSchedulingPolicySpread : cudaClusterSchedulingPolicyLoadBalancing;
+        ++cfg.numAttrs;
     }
 }
 
@@ -1038,7 +1046,7 @@ static bool cluster_fits(AttnKernel kern, int variant, int threads, int splits, 
     if (ok && splits > 8) ok = cudaFuncSetAttribute(kern, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) == cudaSuccess;
     if (ok) {
         cudaLaunchConfig_t cfg;
-        cudaLaunchAttribute attr[2];
+        cudaLaunchAttribute attr[3];
         fill_launch_config(cfg, attr, threads, splits, 1, 1, smem, nullptr);
         int n = 0;
         ok = cudaOccupancyMaxActiveClusters(&n, kern, &cfg) == cudaSuccess && n > 0;
@@ -1057,7 +1065,7 @@ static cudaError_t launch_attn(AttnKernel kern, int threads, const AttnParams& p
         if (e != cudaSuccess) return e;
     }
     cudaLaunchConfig_t cfg;
-    cudaLaunchAttribute attr[2];
+    cudaLaunchAttribute attr[3];
     fill_launch_config(cfg, attr, threads, p.splits, p.chunks, items, smem, stream, p.overlap != 0);
     return cudaLaunchKernelEx(&cfg, kern, p);
 }
