@@ -71,6 +71,10 @@ class ModelRunner:
         self.device = torch.device(device)
         torch.cuda.set_device(self.device)
         self.dtype = config.model_dtype()
+        if self.world_size > 1:
+            # small tensor-parallel sums go through NVLink peer memory instead of NCCL
+            from fastdms_b200.layers.peer_allreduce import init_peer_all_reduce
+            self.peer_all_reduce = init_peer_all_reduce(self.device)
         self.dms_metadata = self._load_dms_metadata()
         default_dtype = torch.get_default_dtype()
         torch.set_default_dtype(self.dtype)

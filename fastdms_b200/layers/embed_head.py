@@ -34,7 +34,8 @@ class VocabParallelEmbedding(nn.Module):
         y = F.embedding(x, self.weight)
         if self.tp_size > 1:
             y = mask.unsqueeze(1) * y
-            dist.all_reduce(y)
+            from fastdms_b200.layers.peer_allreduce import tp_all_reduce_
+            tp_all_reduce_(y)
         return y
 
 

@@ -112,5 +112,6 @@ class RowParallelLinear(LinearBase):
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         y = F.linear(x, self.weight, self.bias if self.tp_rank == 0 else None)
         if self.tp_size > 1:
-            dist.all_reduce(y)
+            from fastdms_b200.layers.peer_allreduce import tp_all_reduce_
+            tp_all_reduce_(y)
         return y

@@ -1,0 +1,106 @@
+"""One-shot all-reduce over NVLink peer memory for the small tensors of tensor-parallel decode (the
+library's `fdms_allreduce_oneshot`), with the plumbing it needs: every rank allocates one region,
+shares its CUDA IPC handle over the process group and opens its peers' handles with its own device
+current (the library's `fdms_ipc_region_*`).  Tensors that do not fit, or that are not
+16-byte friendly, go through `torch.distributed.all_reduce`.
+
+The reference sums tensor-parallel partials with NCCL (fastdms/layers/linear.py:1044-1048); the
+result here is the sum in rank order, identical on every rank."""
+from __future__ import annotations
+
+import os
+
+import torch
+import torch.distributed as dist
+
+from fastdms_b200 import _lib
+
+_STATE = None
+
+
+class PeerAllReduce:
+    def __init__(self, device: torch.device, group=None, max_bytes: int = 1 << 20):
+        import ctypes
+        self.group = group
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        self.device = torch.device(device)
+        self.max_bytes = int(max_bytes)
+        if not (2 <= self.world <= 8):
+            raise ValueError(f"peer all-reduce supports 2..8 ranks, got {self.world}")
+        lib = _lib.lib()
+        nbytes = lib.fdms_allreduce_region_bytes(self.world, self.max_bytes)
+        if nbytes <= 0:
+            raise ValueError("bad all-reduce region size")
+        self._own = ctypes.c_void_p()
+        self._opened: list[int] = []
+        handle = (ctypes.c_ubyte * 64)()
+        with torch.cuda.device(self.device):         # everything below happens with this rank's device current
+            _lib.check(lib.fdms_ipc_region_create(nbytes, ctypes.byref(self._own), handle))
+            handles = [None] * self.world
+            dist.all_gather_object(handles, bytes(handle), group=group)
+            ptrs = []
+            for r, h in enumerate(handles):
+                if r == self.rank:
+                    ptrs.append(self._own.value)
+                    continue
+                # The mapping belongs to the device that is current while the handle is opened, so it
+                # is opened here, under this rank's device, not under the exporting rank's index.
+                p = ctypes.c_void_p()
+                buf = (ctypes.c_ubyte * 64).from_buffer_copy(h)
+                _lib.check(lib.fdms_ipc_region_open(buf, ctypes.byref(p)))
+                self._opened.append(p.value)
+                ptrs.append(p.value)
+        self.ptrs = torch.tensor(ptrs, dtype=torch.int64)      # host array of pointers, indexed by rank
+        dist.barrier(group=group)            # every rank has mapped every region before anyone uses them
+
+    def close(self) -> None:
+        """Unmaps the peers' regions and frees this rank's (collective: no rank may still be inside a call)."""
+        if self._own.value is None:
+            return
+        dist.barrier(group=self.group)
+        lib = _lib.lib()
+        with torch.cuda.device(self.device):
+            torch.cuda.synchronize(self.device)
+            for p in self._opened:
+                lib.fdms_ipc_region_close(p)
+            self._opened = []
+            dist.barrier(group=self.group)
+            lib.fdms_ipc_region_destroy(self._own)
+        self._own = type(self._own)()
+
+    def fits(self, t: torch.Tensor) -> bool:
+        nb = t.numel() * t.element_size()
+        return (t.is_cuda and t.is_contiguous() and t.dtype in (torch.float32, torch.bfloat16, torch.float16)
+                and 0 < nb <= self.max_bytes and nb % 16 == 0 and t.data_ptr() % 16 == 0)
+
+    def all_reduce_(self, t: torch.Tensor) -> torch.Tensor:
+        """In-place sum over the ranks (the same call, with the same shape, on every rank)."""
+        with torch.cuda.device(self.device):
+            rc = _lib.lib().fdms_allreduce_oneshot(
+                self.ptrs.data_ptr(), self.rank, self.world, self.max_bytes, t.data_ptr(), t.data_ptr(), t.numel(),
+                _lib.dtype_code(t.dtype), _lib.status_word(self.device).data_ptr(), _lib.stream_ptr(self.device))
+        _lib.check(rc)
+        return t
+
+
+def init_peer_all_reduce(device, group=None, max_bytes: int = 1 << 20):
+    """Sets up the peer all-reduce for this process (collective over the group); returns it, or None
+    when it is switched off (`FDMS_PEER_ALLREDUCE=0`) or there is a single rank."""
+    global _STATE
+    _STATE = None
+    if os.environ.get("FDMS_PEER_ALLREDUCE", "1").strip().lower() in {"0", "false", "off", "no"}:
+        return None
+    if not dist.is_initialized() or dist.get_world_size(group) < 2:
+        return None
+    _STATE = PeerAllReduce(device, group, max_bytes)
+    return _STATE
+
+
+def tp_all_reduce_(t: torch.Tensor) -> torch.Tensor:
+    """Sum over the tensor-parallel ranks, in place: peer kernel when it is set up and the tensor fits,
+    NCCL otherwise."""
+    if _STATE is not None and _STATE.fits(t):
+        return _STATE.all_reduce_(t)
+    dist.all_reduce(t)
+    return t

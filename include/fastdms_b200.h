@@ -317,6 +317,35 @@ int32_t fdms_rmsnorm(
 int32_t fdms_silu_and_mul(const void* x, int64_t x_row_stride, void* out, int64_t out_row_stride,
                           int32_t dtype, int64_t rows, int32_t n, void* stream);
 
+/* ---------------------------------------------------------------------------------------------
+ * (e) tensor parallel by KV head: the all-reduce after o_proj and down_proj
+ * (fastdms/layers/linear.py:1044-1048 calls NCCL's all_reduce).  One-shot all-reduce over NVLink peer
+ * memory for tensors of at most max_bytes: every rank publishes its input in a peer-readable region,
+ * raises a flag in each peer's region, waits (bounded) for the peers' flags and sums all inputs in rank
+ * order, so every rank gets the same bits.  peer_regions[r] is rank r's region of
+ * fdms_allreduce_region_bytes(world, max_bytes) bytes, zero-filled once before the first call and
+ * mapped into this process with fdms_ipc_region_open; the same call sequence must run on every rank.  in/out: n
+ * elements of dtype (FDMS_F32 / FDMS_BF16 / FDMS_F16), 16-byte aligned, n * size a multiple of 16.
+ * A peer that does not answer within about a second raises FDMS_DEV_WAIT_TIMEOUT and is left out.
+ * --------------------------------------------------------------------------------------------- */
+int64_t fdms_allreduce_region_bytes(int32_t world, int64_t max_bytes);
+/* Peer regions (the one place this library allocates: the caller owns the result and destroys it).
+ * create: a zero-filled device allocation of `bytes` on the current device and its 64-byte CUDA IPC
+ * handle, to be sent to the peers.  open: maps a peer's region into the CURRENT device's address space
+ * (call it with the rank's own device current: a mapping opened under another device is not reachable
+ * from this device's kernels).  close / destroy undo open / create. */
+int32_t fdms_ipc_region_create(int64_t bytes, void** ptr, void* handle64);
+int32_t fdms_ipc_region_open(const void* handle64, void** ptr);
+int32_t fdms_ipc_region_close(void* ptr);
+int32_t fdms_ipc_region_destroy(void* ptr);
+/* Enables peer access from the current device to peer_device (the direction the kernel's loads and
+ * stores take; mapping a peer's region through CUDA IPC does not enable it).  Call once per peer,
+ * with the rank's own device current, before the first fdms_allreduce_oneshot. */
+int32_t fdms_enable_peer_access(int32_t peer_device);
+int32_t fdms_allreduce_oneshot(
+    void* const* peer_regions, int32_t rank, int32_t world, int64_t max_bytes,
+    const void* in, void* out, int64_t n, int32_t dtype, int32_t* dev_status, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -494,3 +494,55 @@ def test_positions_outside_the_rotary_table_are_flagged_not_followed(dev):
         call(torch.tensor([-1, 3], device=dev))
         assert _lib.read_device_status(dev) & 2
         _lib.status_word(dev).zero_()
+
+
+def test_peer_allreduce_kernel_with_a_staged_peer_and_with_a_silent_one(dev):
+    """The one-shot all-reduce kernel on one GPU.  (1) The peer is staged by the host: its data buffer
+    and its flags are already in place, so the kernel finds them at once and must return rank 0's input
+    plus the peer's, for three dtypes and two consecutive calls (buffer alternation).  (2) A peer whose
+    flag nothing sets: the bounded wait runs out after about a second, the kernel raises
+    FDMS_DEV_WAIT_TIMEOUT, leaves that peer out and returns; the context stays usable."""
+    import time
+    from fastdms_b200 import _lib
+    lib = _lib.lib()
+    max_bytes = 1 << 16
+    nbytes = lib.fdms_allreduce_region_bytes(2, max_bytes)
+    half = ((max_bytes + 255) // 256) * 256
+    g = torch.Generator(device=dev).manual_seed(1)
+    for dtype in (torch.float32, torch.bfloat16, torch.float16):
+        regions = [torch.zeros((nbytes,), dtype=torch.uint8, device=dev) for _ in range(2)]
+        ptrs = torch.tensor([r.data_ptr() for r in regions], dtype=torch.int64)
+        n = 8 * 1024
+        for call in (1, 2):
+            x0 = torch.randn((n,), device=dev, generator=g).to(dtype)
+            x1 = torch.randn((n,), device=dev, generator=g).to(dtype)
+            b = call & 1
+            regions[1][b * half: b * half + n * x1.element_size()] = x1.view(torch.uint8)     # the peer's published input
+            flags0 = regions[0][2 * half: 2 * half + 2 * 8 * 4].view(torch.int32).view(2, 8)
+            flags0[1] = call                                                                   # "peer 1 published call `call`"
+            out = torch.empty_like(x0)
+            _lib.check(lib.fdms_allreduce_oneshot(ptrs.data_ptr(), 0, 2, max_bytes, x0.data_ptr(), out.data_ptr(), n,
+                                                  _lib.dtype_code(dtype), _lib.status_word(dev).data_ptr(), _lib.stream_ptr(dev)))
+            want = (x0.float() + x1.float()).to(dtype)
+            assert torch.equal(out, want)
+            flags1 = regions[1][2 * half: 2 * half + 2 * 8 * 4].view(torch.int32).view(2, 8)
+            assert (flags1[0] == call).all(), "rank 0 announces its chunks in the peer's region"
+        assert _lib.read_device_status(dev) == 0
+    # a silent peer
+    regions = [torch.zeros((nbytes,), dtype=torch.uint8, device=dev) for _ in range(2)]
+    ptrs = torch.tensor([r.data_ptr() for r in regions], dtype=torch.int64)
+    x0 = torch.randn((4096,), device=dev, generator=g)
+    out = torch.empty_like(x0)
+    torch.cuda.synchronize(dev)
+    t0 = time.perf_counter()
+    _lib.check(lib.fdms_allreduce_oneshot(ptrs.data_ptr(), 0, 2, max_bytes, x0.data_ptr(), out.data_ptr(), 4096, _lib.F32,
+                                          _lib.status_word(dev).data_ptr(), _lib.stream_ptr(dev)))
+    torch.cuda.synchronize(dev)
+    waited = time.perf_counter() - t0
+    assert _lib.read_device_status(dev) & 1, "FDMS_DEV_WAIT_TIMEOUT expected"
+    assert waited < 20.0
+    assert torch.equal(out, x0)                      # the silent peer was left out
+    assert torch.equal(torch.ones(4, device=dev) + 1, torch.full((4,), 2.0, device=dev))    # context still fine
+    with pytest.raises(RuntimeError):
+        _lib.check(lib.fdms_allreduce_oneshot(ptrs.data_ptr(), 0, 2, max_bytes, x0.data_ptr(), out.data_ptr(), 1 << 20, _lib.F32,
+                                              None, _lib.stream_ptr(dev)))
