@@ -86,10 +86,13 @@ class PeerAllReduce:
 
 def init_peer_all_reduce(device, group=None, max_bytes: int = 1 << 20):
     """Sets up the peer all-reduce for this process (collective over the group); returns it, or None
-    when it is switched off (`FDMS_PEER_ALLREDUCE=0`) or there is a single rank."""
+    when it is not switched on (`FDMS_PEER_ALLREDUCE=1`) or there is a single rank.  It is opt-in:
+    measured on two B200s it is 18 % faster than NCCL for a lone [8, 4096] bf16 call (15.6 against
+    19.1 us, eager launches) but no faster inside the captured decode step of the 8B shape (4.51
+    against 4.42 ms per step), where NCCL's own launch cost disappears too."""
     global _STATE
     _STATE = None
-    if os.environ.get("FDMS_PEER_ALLREDUCE", "1").strip().lower() in {"0", "false", "off", "no"}:
+    if os.environ.get("FDMS_PEER_ALLREDUCE", "0").strip().lower() not in {"1", "true", "on", "yes"}:
         return None
     if not dist.is_initialized() or dist.get_world_size(group) < 2:
         return None

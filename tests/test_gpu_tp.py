@@ -1,7 +1,8 @@
 """Tensor parallelism by KV head (the 8B-shape partition) on two GPUs, checked on BASELINE config 0:
 two ranks, one KV head each, NCCL all-reduce after o_proj and down_proj, against the same reference
 trace as the single-GPU test.  DMS state is per KV head, so each rank's decisions and compact
-lengths must equal that head's columns of the trace; tokens must be identical.
+lengths must equal that head's columns of the trace; tokens must be identical.  The float32 case
+sums the partials with the library's NVLink peer all-reduce, the FP8 case with NCCL.
 Skipped on boxes with fewer than two GPUs."""
 from __future__ import annotations
 
@@ -20,7 +21,7 @@ PORT = 29731
 def _rank_main(rank: int, world: int, kv_dtype: str, out_q) -> None:
     import os
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(PORT), RANK=str(rank), WORLD_SIZE=str(world),
-                      LOCAL_RANK=str(rank))
+                      LOCAL_RANK=str(rank), FDMS_PEER_ALLREDUCE="1" if kv_dtype == "float32" else "0")
     sys.path.insert(0, str(ROOT))
     sys.path.insert(0, str(ROOT / "tests" / "golden"))
     import torch.distributed as dist
@@ -102,7 +103,7 @@ def test_tp2_by_kv_head_matches_reference_trace(tag, kv_dtype):
 def _allreduce_rank(rank: int, world: int, out_q) -> None:
     import os
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(PORT + 7), RANK=str(rank), WORLD_SIZE=str(world),
-                      LOCAL_RANK=str(rank))
+                      LOCAL_RANK=str(rank), FDMS_PEER_ALLREDUCE="1")
     sys.path.insert(0, str(ROOT))
     import torch.distributed as dist
     from fastdms_b200 import _lib
