@@ -62,6 +62,13 @@ def measured_peaks() -> tuple[float, str]:
 # ------------------------------------------------------------------------------------------------
 # clocks / throttle sampling (read-only NVML queries)
 # ------------------------------------------------------------------------------------------------
+# dram__bytes_read.sum + dram__bytes_write.sum of one fused attention launch of this (seeded, hence
+# reproducible) workload, from the ncu capture summarised under profiles/
+NCU_DRAM_BYTES_PER_LAUNCH = 10_747_648 + 0
+NCU_DRAM_SOURCE = ("ncu --set full capture of attn_decode_direct_kernel<64, 3, true> on this workload "
+                   "(profiles/attn_decode_direct_fused_config2.md): 10.75 MB read, ~0 written")
+
+
 class ClockSampler:
     def __init__(self, index: int):
         self.index = index
@@ -454,7 +461,8 @@ def run_ours(args) -> None:
             "gpu_launches": hp.launches_per_step * args.steps,
             "roofline": {"bound": "hbm", "kernel": "attn_decode_direct_kernel<64, 3, %s>" % ("true" if hp.fuse_store else "false"), "achieved": achieved, "peak": peak,
                          "unit": "GB/s", "frac": achieved / peak, "peak_source": f"{peak_kind} (MEASURED_PEAKS.json hbm_gbs)",
-                         "traffic": None, "bytes_per_launch": bytes_per_launch, "us_per_launch": ov_launch_s * 1e6,
+                         "traffic": NCU_DRAM_BYTES_PER_LAUNCH, "traffic_source": NCU_DRAM_SOURCE,
+                         "bytes_per_launch": bytes_per_launch, "us_per_launch": ov_launch_s * 1e6,
                          "us_per_launch_without_overlap": per_launch_s * 1e6, "launches_timed": attn_launches,
                          "how": "CUDA events around a graph of the 16 per-layer launches (the fused decision + RoPE + "
                                 "FP8 store + attention launch of the decode step) replayed back to back; "
