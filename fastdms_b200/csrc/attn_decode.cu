@@ -134,6 +134,21 @@ __device__ __forceinline__ void mma_top(float& c0, float& c1, uint32_t a0, uint3
     (void)d2; (void)d3;
 }
 
+// D(16x8, f32) += A(16x16, f16) * B(16x8, f16), all four A registers and accumulators in use.
+__device__ __forceinline__ void mma_full(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                         uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+// Transpose of an 8x8 matrix of 16-bit elements held one register per lane (row = lane / 4).
+__device__ __forceinline__ uint32_t movmatrix_trans(uint32_t a) {
+    uint32_t d;
+    asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(d) : "r"(a));
+    return d;
+}
+
 // Physical row inside a page for MMA column n of n-tile u.  Two permutations:
 //  * staged loader (LIN = false): keeps the shared-memory K reads (rows tokrow(u, g), 16 bytes per
 //    lane) free of bank conflicts and the V reads (rows tokrow(u, 2t), tokrow(u, 2t+1), 8 bytes per
@@ -341,79 +356,80 @@ __device__ __forceinline__ void load_frags_global(const uint8_t* Kg, const uint8
     }
 }
 
-// One page (`rows` of its 16 rows valid): online-softmax update of the warp's running (m, l, O) for
-// head g.  Fragments of invalid rows must hold finite values (they are masked, not trusted).
+// One page (`rows` of its 16 rows valid): online-softmax update of the warp's running state.
+// Tokens sit on the M side of both products, so a page costs 4 + 4 MMAs per 64 elements of head_dim
+// (no half-empty tiles):
+//   S^T[token, head] = K_page[token, d] q[head, d]      A = K (rows tokrow(0, g), tokrow(1, g)), B = q
+//   O^T[d, head]    += V_page^T[d, token] P^T[token, head]   A = V^T, B = P^T (movmatrix transpose of S^T's layout)
+// A lane (g, t) holds, for heads 2t and 2t+1: scores of tokens tokrow(0, g), tokrow(1, g); running
+// maximum m[e] (complete, reduced over g) and partial sum l[e] (this lane's tokens only); and
+// o[4 ch + j][2 r + e] = O[head 2t + e][64 ch + 8 g + 2 j + r].
+// Fragments of invalid rows must hold finite values (they are masked, not trusted).
 template <int D, bool LIN>
-__device__ __forceinline__ void process_page(const PageFrags<D>& f, int rows, int t, float sl2,
-                                             const uint32_t (&qa)[FastCfg<D>::kKSteps][2], float& m_run, float& l_run,
-                                             float (&o)[FastCfg<D>::kNT][2]) {
+__device__ __forceinline__ void process_page(const PageFrags<D>& f, int rows, int g, int t, float sl2,
+                                             const uint32_t (&qa)[FastCfg<D>::kKSteps][2], float (&m_run)[2],
+                                             float (&l_run)[2], float (&o)[FastCfg<D>::kNT / 2][4]) {
     using C = FastCfg<D>;
-    // ---- S = q K^T for the two 8-token n-tiles ----
-    float sc[2][2];
-#pragma unroll
-    for (int u = 0; u < 2; ++u) {
-        float c0 = 0.0f, c1 = 0.0f;
-#pragma unroll
-        for (int ch = 0; ch < C::kCh; ++ch) {
-            const uint32_t w4[4] = {f.k[u][ch].x, f.k[u][ch].y, f.k[u][ch].z, f.k[u][ch].w};
-#pragma unroll
-            for (int s = 0; s < 4; ++s) {
-                uint32_t b0, b1;
-                e4m3x4_to_f16x2x2(w4[s], b0, b1);
-                mma_top(c0, c1, qa[4 * ch + s][0], qa[4 * ch + s][1], b0, b1);
-            }
-        }
-        sc[u][0] = c0 * sl2;
-        sc[u][1] = c1 * sl2;
-    }
-    if (rows < kPage) {
-#pragma unroll
-        for (int u = 0; u < 2; ++u) {
-            if (tokrow<LIN>(u, 2 * t) >= rows) sc[u][0] = -INFINITY;
-            if (tokrow<LIN>(u, 2 * t + 1) >= rows) sc[u][1] = -INFINITY;
-        }
-    }
-    // ---- online softmax (row = head g, reduce over the 4 lanes of the quad) ----
-    float mx = fmaxf(fmaxf(sc[0][0], sc[0][1]), fmaxf(sc[1][0], sc[1][1]));
-    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
-    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
-    const float m_new = fmaxf(m_run, mx);
-    const float alpha = ex2(m_run - m_new);
-    float pr[2][2];
-#pragma unroll
-    for (int u = 0; u < 2; ++u) { pr[u][0] = ex2(sc[u][0] - m_new); pr[u][1] = ex2(sc[u][1] - m_new); }
-    l_run = l_run * alpha + (pr[0][0] + pr[0][1]) + (pr[1][0] + pr[1][1]);
-    m_run = m_new;
-    const uint32_t pa0 = pack_f16x2(pr[0][0], pr[0][1]);
-    const uint32_t pa2 = pack_f16x2(pr[1][0], pr[1][1]);
-    if (__any_sync(0xffffffffu, alpha != 1.0f)) {          // the running maxima rarely move after the first pages
-#pragma unroll
-        for (int jn = 0; jn < C::kNT; ++jn) { o[jn][0] *= alpha; o[jn][1] *= alpha; }
-    }
-
-    // ---- O += P V ----
+    // ---- S^T = K q^T ----
+    float c[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
     for (int ch = 0; ch < C::kCh; ++ch) {
-        uint32_t bf[2][8];
+        const uint32_t w0[4] = {f.k[0][ch].x, f.k[0][ch].y, f.k[0][ch].z, f.k[0][ch].w};
+        const uint32_t w1[4] = {f.k[1][ch].x, f.k[1][ch].y, f.k[1][ch].z, f.k[1][ch].w};
 #pragma unroll
-        for (int u = 0; u < 2; ++u) {
-            uint2 va = f.va[u][ch], vb = f.vb[u][ch];
-            if (rows < kPage) {                   // stale bytes must not reach the MMA
-                if (tokrow<LIN>(u, 2 * t) >= rows) va = make_uint2(0u, 0u);
-                if (tokrow<LIN>(u, 2 * t + 1) >= rows) vb = make_uint2(0u, 0u);
-            }
-            const uint32_t x0 = __byte_perm(va.x, vb.x, 0x5140);
-            const uint32_t x1 = __byte_perm(va.x, vb.x, 0x7362);
-            const uint32_t y0 = __byte_perm(va.y, vb.y, 0x5140);
-            const uint32_t y1 = __byte_perm(va.y, vb.y, 0x7362);
-            e4m3x4_to_f16x2x2(x0, bf[u][0], bf[u][1]);
-            e4m3x4_to_f16x2x2(x1, bf[u][2], bf[u][3]);
-            e4m3x4_to_f16x2x2(y0, bf[u][4], bf[u][5]);
-            e4m3x4_to_f16x2x2(y1, bf[u][6], bf[u][7]);
+        for (int s = 0; s < 4; ++s) {
+            uint32_t a0, a1, a2, a3;
+            e4m3x4_to_f16x2x2(w0[s], a0, a2);
+            e4m3x4_to_f16x2x2(w1[s], a1, a3);
+            mma_full(c, a0, a1, a2, a3, qa[4 * ch + s][0], qa[4 * ch + s][1]);
         }
+    }
+    float sc[2][2] = {{c[0] * sl2, c[1] * sl2}, {c[2] * sl2, c[3] * sl2}};      // [token row u][head e]
+    if (rows < kPage) {
 #pragma unroll
-        for (int jj = 0; jj < 8; ++jj)
-            mma_top(o[8 * ch + jj][0], o[8 * ch + jj][1], pa0, pa2, bf[0][jj], bf[1][jj]);
+        for (int u = 0; u < 2; ++u)
+            if (tokrow<LIN>(u, g) >= rows) { sc[u][0] = -INFINITY; sc[u][1] = -INFINITY; }
+    }
+    // ---- online softmax per head (column): reduce over the two rows and the eight row-lanes ----
+    float alpha[2], pr[2][2];
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+        float mx = fmaxf(sc[0][e], sc[1][e]);
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 4));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 8));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 16));
+        const float m_new = fmaxf(m_run[e], mx);
+        alpha[e] = ex2(m_run[e] - m_new);
+        pr[0][e] = ex2(sc[0][e] - m_new);
+        pr[1][e] = ex2(sc[1][e] - m_new);
+        l_run[e] = l_run[e] * alpha[e] + pr[0][e] + pr[1][e];
+        m_run[e] = m_new;
+    }
+    const uint32_t b0 = movmatrix_trans(pack_f16x2(pr[0][0], pr[0][1]));       // P^T for tokens 0..7 of the tile
+    const uint32_t b1 = movmatrix_trans(pack_f16x2(pr[1][0], pr[1][1]));       // ... tokens 8..15
+    if (__any_sync(0xffffffffu, alpha[0] != 1.0f || alpha[1] != 1.0f)) {       // the maxima rarely move after the first pages
+#pragma unroll
+        for (int j = 0; j < C::kNT / 2; ++j) { o[j][0] *= alpha[0]; o[j][1] *= alpha[1]; o[j][2] *= alpha[0]; o[j][3] *= alpha[1]; }
+    }
+    // ---- O^T += V^T P^T ----
+#pragma unroll
+    for (int ch = 0; ch < C::kCh; ++ch) {
+        uint2 va0 = f.va[0][ch], vb0 = f.vb[0][ch], va1 = f.va[1][ch], vb1 = f.vb[1][ch];
+        if (rows < kPage) {                       // stale bytes must not reach the MMA
+            if (tokrow<LIN>(0, 2 * t) >= rows) va0 = make_uint2(0u, 0u);
+            if (tokrow<LIN>(0, 2 * t + 1) >= rows) vb0 = make_uint2(0u, 0u);
+            if (tokrow<LIN>(1, 2 * t) >= rows) va1 = make_uint2(0u, 0u);
+            if (tokrow<LIN>(1, 2 * t + 1) >= rows) vb1 = make_uint2(0u, 0u);
+        }
+        const uint32_t lo0[2] = {va0.x, va0.y}, hi0[2] = {vb0.x, vb0.y}, lo1[2] = {va1.x, va1.y}, hi1[2] = {vb1.x, vb1.y};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const uint32_t sel = (j & 1) ? 0x7362u : 0x5140u;
+            uint32_t a0, a1, a2, a3;
+            e4m3x4_to_f16x2x2(__byte_perm(lo0[j >> 1], hi0[j >> 1], sel), a0, a1);
+            e4m3x4_to_f16x2x2(__byte_perm(lo1[j >> 1], hi1[j >> 1], sel), a2, a3);
+            mma_full(o[4 * ch + j], a0, a1, a2, a3, b0, b1);
+        }
     }
 }
 
@@ -427,26 +443,28 @@ constexpr int kPartialStride = D + 4;          // floats per (warp, head) row of
 template <int D>
 __device__ __forceinline__ void fold_and_write(const AttnParams& p, float* s_m, float* s_l, float* s_o, float* r_ml,
                                                float* r_o, int* s_last_ptr, int tid, int warp, int g, int t, int b,
-                                               int h, int item, int rank, int chunk, float m_run, float l_run,
-                                               float (&o)[FastCfg<D>::kNT][2]) {
+                                               int h, int item, int rank, int chunk, float (&m_run)[2], float (&l_run)[2],
+                                               float (&o)[FastCfg<D>::kNT / 2][4]) {
     using C = FastCfg<D>;
     const int S = p.splits, CH = p.chunks, G = p.group;
-    // ---- merge the warps' partial (m, l, O) ----
-    l_run += __shfl_xor_sync(0xffffffffu, l_run, 1);
-    l_run += __shfl_xor_sync(0xffffffffu, l_run, 2);
-    if (t == 0) { s_m[warp * kMaxGroup + g] = m_run; s_l[warp * kMaxGroup + g] = l_run; }
-    if (g < G) {
-        // a lane's 16 values of a 64-element chunk are consecutive elements 16t .. 16t+15: four 128-bit
-        // stores; rows are padded by 4 floats so that the eight lanes of a store phase hit four
-        // different bank groups (the unpadded scalar version was a 16-way bank conflict)
-        float* so = s_o + ((size_t)warp * kMaxGroup + g) * kPartialStride<D>;
+    // ---- merge the warps' partial (m, l, O): lane (g, t) holds heads 2t, 2t+1 and elements 8g .. 8g+7 ----
 #pragma unroll
-        for (int ch = 0; ch < C::kCh; ++ch) {
-            float4* dst = (float4*)(so + 64 * ch + 16 * t);
-            dst[0] = make_float4(o[8 * ch + 0][0], o[8 * ch + 1][0], o[8 * ch + 2][0], o[8 * ch + 3][0]);
-            dst[1] = make_float4(o[8 * ch + 4][0], o[8 * ch + 5][0], o[8 * ch + 6][0], o[8 * ch + 7][0]);
-            dst[2] = make_float4(o[8 * ch + 0][1], o[8 * ch + 1][1], o[8 * ch + 2][1], o[8 * ch + 3][1]);
-            dst[3] = make_float4(o[8 * ch + 4][1], o[8 * ch + 5][1], o[8 * ch + 6][1], o[8 * ch + 7][1]);
+    for (int e = 0; e < 2; ++e) {
+        float l = l_run[e];
+        l += __shfl_xor_sync(0xffffffffu, l, 4);
+        l += __shfl_xor_sync(0xffffffffu, l, 8);
+        l += __shfl_xor_sync(0xffffffffu, l, 16);
+        const int hh = 2 * t + e;
+        if (g == 0) { s_m[warp * kMaxGroup + hh] = m_run[e]; s_l[warp * kMaxGroup + hh] = l; }
+        if (hh < G) {
+            // eight consecutive elements per 64-element chunk: two 128-bit stores into the padded row
+            float* so = s_o + ((size_t)warp * kMaxGroup + hh) * kPartialStride<D>;
+#pragma unroll
+            for (int ch = 0; ch < C::kCh; ++ch) {
+                float4* dst = (float4*)(so + 64 * ch + 8 * g);
+                dst[0] = make_float4(o[4 * ch + 0][e], o[4 * ch + 0][2 + e], o[4 * ch + 1][e], o[4 * ch + 1][2 + e]);
+                dst[1] = make_float4(o[4 * ch + 2][e], o[4 * ch + 2][2 + e], o[4 * ch + 3][e], o[4 * ch + 3][2 + e]);
+            }
         }
     }
     consumer_bar();
@@ -652,10 +670,10 @@ __global__ void __launch_bounds__(kFastThreads, (D == 64 ? 2 : 1)) attn_decode_f
     uint32_t qa[C::kKSteps][2];
     load_q_frags<D>(p, b, h, g, t, qa);
 
-    float m_run = -INFINITY, l_run = 0.0f;
-    float o[C::kNT][2];
+    float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.0f, 0.0f};
+    float o[C::kNT / 2][4];
 #pragma unroll
-    for (int j = 0; j < C::kNT; ++j) { o[j][0] = 0.0f; o[j][1] = 0.0f; }
+    for (int j = 0; j < C::kNT / 2; ++j) { o[j][0] = 0.0f; o[j][1] = 0.0f; o[j][2] = 0.0f; o[j][3] = 0.0f; }
 
     for (int j = warp; j < npages; j += kConsumerWarps) {
         const int slot = j % NS;
@@ -670,7 +688,7 @@ __global__ void __launch_bounds__(kFastThreads, (D == 64 ? 2 : 1)) attn_decode_f
             const int rows = min(kPage, live - (part + j * nparts) * kPage);
             PageFrags<D> f;
             load_frags_smem<D>(Ks, Ks + C::kPageBytes, g, t, f);
-            process_page<D, false>(f, rows, t, sl2, qa, m_run, l_run, o);
+            process_page<D, false>(f, rows, g, t, sl2, qa, m_run, l_run, o);
         }
         __syncwarp();
         if (lane == 0) mbar_arrive(&s_empty[slot]);
@@ -858,10 +876,10 @@ __global__ void __launch_bounds__(kDirectThreads, (D == 64 ? 2 : 1)) attn_decode
     const bool own_tail = APPEND && nw > 0 && tail_pi >= pg0 && (tail_pi - pg0) % stride_pg == 0;
     const int r_new = live - 1 - tail_pi * kPage;            // row of the new token inside that page
 
-    float m_run = -INFINITY, l_run = 0.0f;
-    float o[C::kNT][2];
+    float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.0f, 0.0f};
+    float o[C::kNT / 2][4];
 #pragma unroll
-    for (int j = 0; j < C::kNT; ++j) { o[j][0] = 0.0f; o[j][1] = 0.0f; }
+    for (int j = 0; j < C::kNT / 2; ++j) { o[j][0] = 0.0f; o[j][1] = 0.0f; o[j][2] = 0.0f; o[j][3] = 0.0f; }
 
     for (int i0 = 0; i0 < nw; i0 += DEPTH) {
 #pragma unroll
@@ -879,7 +897,7 @@ __global__ void __launch_bounds__(kDirectThreads, (D == 64 ? 2 : 1)) attn_decode
                         }
                     }
                 }
-                if (brow[s] > 0) process_page<D, true>(buf[s], brow[s], t, sl2, qa, m_run, l_run, o);
+                if (brow[s] > 0) process_page<D, true>(buf[s], brow[s], g, t, sl2, qa, m_run, l_run, o);
                 if (i + DEPTH < nw) issue(s, i + DEPTH);
             }
         }
