@@ -390,27 +390,37 @@ __device__ __forceinline__ void process_page(const PageFrags<D>& f, int rows, in
         for (int u = 0; u < 2; ++u)
             if (tokrow<LIN>(u, g) >= rows) { sc[u][0] = -INFINITY; sc[u][1] = -INFINITY; }
     }
-    // ---- online softmax per head (column): reduce over the two rows and the eight row-lanes ----
-    float alpha[2], pr[2][2];
+    // ---- online softmax per head (column) with a lazily updated reference: the exponentials are taken
+    // relative to m_run, which is only raised (reduce over the two rows and the eight row-lanes, rescale
+    // l and O) when some score exceeds it by more than kMaxSlack, i.e. on the first page and rarely
+    // afterwards; weights stay below 2^kMaxSlack, far inside f16 / f32 range. ----
+    constexpr float kMaxSlack = 8.0f;
+    float alpha[2] = {1.0f, 1.0f}, pr[2][2];
+    const bool raise = fmaxf(sc[0][0], sc[1][0]) > m_run[0] + kMaxSlack || fmaxf(sc[0][1], sc[1][1]) > m_run[1] + kMaxSlack ||
+                       m_run[0] == -INFINITY || m_run[1] == -INFINITY;
+    if (__any_sync(0xffffffffu, raise)) {
 #pragma unroll
-    for (int e = 0; e < 2; ++e) {
-        float mx = fmaxf(sc[0][e], sc[1][e]);
-        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 4));
-        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 8));
-        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 16));
-        const float m_new = fmaxf(m_run[e], mx);
-        alpha[e] = ex2(m_run[e] - m_new);
-        pr[0][e] = ex2(sc[0][e] - m_new);
-        pr[1][e] = ex2(sc[1][e] - m_new);
-        l_run[e] = l_run[e] * alpha[e] + pr[0][e] + pr[1][e];
-        m_run[e] = m_new;
-    }
-    const uint32_t b0 = movmatrix_trans(pack_f16x2(pr[0][0], pr[0][1]));       // P^T for tokens 0..7 of the tile
-    const uint32_t b1 = movmatrix_trans(pack_f16x2(pr[1][0], pr[1][1]));       // ... tokens 8..15
-    if (__any_sync(0xffffffffu, alpha[0] != 1.0f || alpha[1] != 1.0f)) {       // the maxima rarely move after the first pages
+        for (int e = 0; e < 2; ++e) {
+            float mx = fmaxf(sc[0][e], sc[1][e]);
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 4));
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 8));
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 16));
+            const float m_new = fmaxf(m_run[e], mx);
+            alpha[e] = ex2(m_run[e] - m_new);
+            l_run[e] *= alpha[e];
+            m_run[e] = m_new;
+        }
 #pragma unroll
         for (int j = 0; j < C::kNT / 2; ++j) { o[j][0] *= alpha[0]; o[j][1] *= alpha[1]; o[j][2] *= alpha[0]; o[j][3] *= alpha[1]; }
     }
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+        pr[0][e] = ex2(sc[0][e] - m_run[e]);
+        pr[1][e] = ex2(sc[1][e] - m_run[e]);
+        l_run[e] += pr[0][e] + pr[1][e];
+    }
+    const uint32_t b0 = movmatrix_trans(pack_f16x2(pr[0][0], pr[0][1]));       // P^T for tokens 0..7 of the tile
+    const uint32_t b1 = movmatrix_trans(pack_f16x2(pr[1][0], pr[1][1]));       // ... tokens 8..15
     // ---- O^T += V^T P^T ----
 #pragma unroll
     for (int ch = 0; ch < C::kCh; ++ch) {
