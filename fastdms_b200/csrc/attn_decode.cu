@@ -371,7 +371,8 @@ __device__ __forceinline__ void process_page(const PageFrags<D>& f, int rows, in
                                              float (&l_run)[2], float (&o)[FastCfg<D>::kNT / 2][4]) {
     using C = FastCfg<D>;
     // ---- S^T = K q^T ----
-    float c[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    // two accumulators, even and odd k-steps: the dependent MMA chain is half as long
+    float c[4] = {0.0f, 0.0f, 0.0f, 0.0f}, c2[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
     for (int ch = 0; ch < C::kCh; ++ch) {
         const uint32_t w0[4] = {f.k[0][ch].x, f.k[0][ch].y, f.k[0][ch].z, f.k[0][ch].w};
@@ -381,10 +382,11 @@ __device__ __forceinline__ void process_page(const PageFrags<D>& f, int rows, in
             uint32_t a0, a1, a2, a3;
             e4m3x4_to_f16x2x2(w0[s], a0, a2);
             e4m3x4_to_f16x2x2(w1[s], a1, a3);
-            mma_full(c, a0, a1, a2, a3, qa[4 * ch + s][0], qa[4 * ch + s][1]);
+            if (s & 1) mma_full(c2, a0, a1, a2, a3, qa[4 * ch + s][0], qa[4 * ch + s][1]);
+            else mma_full(c, a0, a1, a2, a3, qa[4 * ch + s][0], qa[4 * ch + s][1]);
         }
     }
-    float sc[2][2] = {{c[0] * sl2, c[1] * sl2}, {c[2] * sl2, c[3] * sl2}};      // [token row u][head e]
+    float sc[2][2] = {{(c[0] + c2[0]) * sl2, (c[1] + c2[1]) * sl2}, {(c[2] + c2[2]) * sl2, (c[3] + c2[3]) * sl2}};   // [token row u][head e]
     if (rows < kPage) {
 #pragma unroll
         for (int u = 0; u < 2; ++u)
