@@ -163,3 +163,119 @@ extern "C" int32_t fdms_silu_and_mul(const void* x, int64_t x_row_stride, void* 
     FDMS_CHECK_LAUNCH("silu_mul_kernel");
     return FDMS_OK;
 }
+
+// ---------------------------------------------------------------------------------------------------
+// Greedy head: index of the largest logit of every row (the reference takes `logits.argmax(dim=-1)`
+// for temperature-0 requests, fastdms/engine/model_runner.py:1147-1151).  Ties go to the lowest
+// index and a NaN counts as the largest value, as torch's argmax does.  One launch: every CTA
+// reduces a slice of a row to a 64-bit key (ordered value bits | inverted index), merges it into the
+// row's key with an atomic max, and the last CTA of a row to finish decodes the key and clears the
+// row's two scratch words again (the scratch must be zero before the first call only).
+namespace fdms {
+
+constexpr int kArgmaxThreads = 256;
+constexpr int kArgmaxVecPerThread = 4;                 // 8 x 16-bit or 4 x 32-bit elements per vector
+
+__device__ __forceinline__ uint32_t ordered_bits(float f) {
+    const uint32_t b = __float_as_uint(f);
+    return (b & 0x80000000u) ? ~b : (b | 0x80000000u);
+}
+
+__device__ __forceinline__ unsigned long long argmax_key(float f, uint32_t idx) {
+    if (f != f) f = __uint_as_float(0x7fc00000u);      // any NaN -> the canonical positive one (above +inf)
+    return ((unsigned long long)ordered_bits(f) << 32) | (unsigned long long)(0xffffffffu - idx);
+}
+
+__global__ void __launch_bounds__(kArgmaxThreads) argmax_rows_kernel(
+    const void* x, int64_t row_stride, int dt, int64_t n, int per_cta, int ctas_per_row, int vec_ok,
+    unsigned long long* keys, unsigned int* done, int64_t* out) {
+    __shared__ unsigned long long s_key[kArgmaxThreads / 32];
+    const int row = blockIdx.y, tid = threadIdx.x;
+    const int64_t lo = (int64_t)blockIdx.x * per_cta;
+    const int64_t hi = lo + per_cta < n ? lo + per_cta : n;
+    const char* base = (const char*)x + row * row_stride * (dt == FDMS_F32 ? 4 : 2);
+    unsigned long long best = 0ull;
+    if (vec_ok) {
+        const int epv = dt == FDMS_F32 ? 4 : 8;        // elements per 16-byte vector
+        uint4 v[kArgmaxVecPerThread];
+        int64_t at[kArgmaxVecPerThread];
+#pragma unroll
+        for (int j = 0; j < kArgmaxVecPerThread; ++j) {
+            at[j] = lo + ((int64_t)j * kArgmaxThreads + tid) * epv;
+            v[j] = at[j] < hi ? __ldcs((const uint4*)(base + at[j] * (16 / epv))) : make_uint4(0u, 0u, 0u, 0u);
+        }
+#pragma unroll
+        for (int j = 0; j < kArgmaxVecPerThread; ++j) {
+            if (at[j] >= hi) continue;
+            if (dt == FDMS_F32) {
+                const float f[4] = {__uint_as_float(v[j].x), __uint_as_float(v[j].y), __uint_as_float(v[j].z), __uint_as_float(v[j].w)};
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const unsigned long long k = argmax_key(f[i], (uint32_t)(at[j] + i));
+                    best = k > best ? k : best;
+                }
+            } else {
+                float f[8];
+                unpack8(v[j], dt, f);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    const unsigned long long k = argmax_key(f[i], (uint32_t)(at[j] + i));
+                    best = k > best ? k : best;
+                }
+            }
+        }
+    } else {
+        for (int64_t i = lo + tid; i < hi; i += kArgmaxThreads) {
+            const unsigned long long k = argmax_key(load_as_float(base, i, dt), (uint32_t)i);
+            best = k > best ? k : best;
+        }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const unsigned long long other = __shfl_xor_sync(0xffffffffu, best, o);
+        best = other > best ? other : best;
+    }
+    if ((tid & 31) == 0) s_key[tid >> 5] = best;
+    __syncthreads();
+    if (tid == 0) {
+#pragma unroll
+        for (int w = 1; w < kArgmaxThreads / 32; ++w) best = s_key[w] > best ? s_key[w] : best;
+        atomicMax(&keys[row], best);
+        __threadfence();
+        if (atomicAdd(&done[row], 1u) == (unsigned)ctas_per_row - 1u) {
+            __threadfence();
+            const unsigned long long k = atomicExch(&keys[row], 0ull);
+            out[row] = (int64_t)(0xffffffffu - (uint32_t)(k & 0xffffffffull));
+            done[row] = 0u;
+        }
+    }
+}
+
+}  // namespace fdms
+
+extern "C" int64_t fdms_argmax_workspace_bytes(int64_t rows) { return rows > 0 ? rows * 16 : 0; }
+
+extern "C" int32_t fdms_argmax_rows(const void* x, int64_t row_stride, int32_t dtype, int64_t rows, int64_t n,
+                                    int64_t* out, void* workspace, int64_t workspace_bytes, void* stream) {
+    clear_error();
+    FDMS_REQUIRE(x && out && workspace, FDMS_E_ARG, "fdms_argmax_rows: null pointer");
+    FDMS_REQUIRE(dtype == FDMS_BF16 || dtype == FDMS_F16 || dtype == FDMS_F32, FDMS_E_DTYPE,
+                 "fdms_argmax_rows: bf16, f16 or f32 logits only");
+    FDMS_REQUIRE(rows >= 0 && rows < 65536 && n > 0 && n < (1ll << 32) - 1, FDMS_E_ARG,
+                 "fdms_argmax_rows: rows must be below 65536 and 0 < n < 2^32 - 1");
+    FDMS_REQUIRE(workspace_bytes >= fdms_argmax_workspace_bytes(rows) && ((uintptr_t)workspace & 7) == 0, FDMS_E_CAPACITY,
+                 "fdms_argmax_rows: workspace of %lld bytes needed (8-byte aligned, zeroed before the first call)",
+                 (long long)fdms_argmax_workspace_bytes(rows));
+    if (rows == 0) return FDMS_OK;
+    const int esz = dtype == FDMS_F32 ? 4 : 2, epv = 16 / esz;
+    const int vec_ok = ((uintptr_t)x & 15) == 0 && (row_stride * esz) % 16 == 0 && n % epv == 0;
+    const int per_cta = fdms::kArgmaxThreads * fdms::kArgmaxVecPerThread * epv;
+    const int64_t ctas = (n + per_cta - 1) / per_cta;
+    FDMS_REQUIRE(ctas < (1ll << 31), FDMS_E_CAPACITY, "fdms_argmax_rows: row too long");
+    unsigned long long* keys = (unsigned long long*)workspace;
+    unsigned int* done = (unsigned int*)(keys + rows);
+    fdms::argmax_rows_kernel<<<dim3((unsigned)ctas, (unsigned)rows), fdms::kArgmaxThreads, 0, (cudaStream_t)stream>>>(
+        x, row_stride, dtype, n, per_cta, (int)ctas, vec_ok, keys, done, out);
+    FDMS_CHECK_LAUNCH("argmax_rows_kernel");
+    return FDMS_OK;
+}

@@ -22,7 +22,7 @@ from fastdms_b200.config import Config
 from fastdms_b200.engine.compact_kv import CompactKVManager
 from fastdms_b200.engine.dms import DMSMetadata, load_dms_metadata
 from fastdms_b200.engine.sequence import Sequence
-from fastdms_b200.layers.sampler import Sampler
+from fastdms_b200.layers.sampler import Sampler, argmax_workspace, greedy_argmax
 from fastdms_b200.models.registry import build_model
 from fastdms_b200.utils.context import reset_context, set_context
 from fastdms_b200.utils.loader import load_model, load_state_dict
@@ -47,6 +47,7 @@ class _DecodeGraph:
         self.evict_all = torch.zeros((L, batch, Hk), device=dev, dtype=torch.bool)
         self.h_in = torch.zeros((3, batch), dtype=torch.int64, pin_memory=True)
         self.d_in = torch.zeros((3, batch), device=dev, dtype=torch.int64)
+        self.argmax_scratch = argmax_workspace(batch, dev)
         self.logits = None
         self.tokens = None
         self.graph = None
@@ -228,7 +229,7 @@ class ModelRunner:
             reset_context()
         m.record_device(g.slots, g.pos, g.evict_all)
         g.logits = self.model.compute_logits(hidden)
-        g.tokens = g.logits.argmax(dim=-1)
+        g.tokens = greedy_argmax(g.logits, g.argmax_scratch)
 
     def _decode_inputs(self, g: _DecodeGraph, seqs: list[Sequence]) -> None:
         m = self.compact_kv_manager
@@ -295,12 +296,12 @@ class ModelRunner:
             logits, greedy = g.logits, g.tokens
         temps = [seq.temperature for seq in seqs]
         if all(t <= 1e-10 for t in temps):
-            tokens = greedy if greedy is not None else logits.argmax(dim=-1)
+            tokens = greedy if greedy is not None else greedy_argmax(logits)
         else:
             t = torch.tensor([max(x, 1e-10) for x in temps], dtype=torch.float32, device=self.device)
             tokens = self.sampler(logits, t)
             if any(x <= 1e-10 for x in temps):
-                arg = logits.argmax(dim=-1)
+                arg = greedy_argmax(logits)
                 mask = torch.tensor([x <= 1e-10 for x in temps], device=self.device)
                 tokens = torch.where(mask, arg, tokens)
         return tokens.tolist()

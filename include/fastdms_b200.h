@@ -317,6 +317,17 @@ int32_t fdms_rmsnorm(
 int32_t fdms_silu_and_mul(const void* x, int64_t x_row_stride, void* out, int64_t out_row_stride,
                           int32_t dtype, int64_t rows, int32_t n, void* stream);
 
+/* Greedy head: out[r] = index of the largest of x[r, 0..n) -- `logits.argmax(dim=-1)` of the
+ * temperature-0 path (fastdms/engine/model_runner.py:1147-1151; the reference fuses it for one
+ * sequence only, fastdms/layers/embed_head.py:491-543).  Lowest index on ties, a NaN counts as the
+ * largest value (torch's convention).  dtype FDMS_F32 / FDMS_BF16 / FDMS_F16; row_stride in
+ * elements; rows < 65536, n < 2^32 - 1.  One launch, no host synchronisation.  `workspace`
+ * (fdms_argmax_workspace_bytes(rows) bytes, 8-byte aligned) must be zero before the FIRST call; every
+ * call leaves it zero again, so calls on one stream can share it. */
+int64_t fdms_argmax_workspace_bytes(int64_t rows);
+int32_t fdms_argmax_rows(const void* x, int64_t row_stride, int32_t dtype, int64_t rows, int64_t n,
+                         int64_t* out, void* workspace, int64_t workspace_bytes, void* stream);
+
 /* ---------------------------------------------------------------------------------------------
  * (e) tensor parallel by KV head: the all-reduce after o_proj and down_proj
  * (fastdms/layers/linear.py:1044-1048 calls NCCL's all_reduce).  One-shot all-reduce over NVLink peer

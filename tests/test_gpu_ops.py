@@ -417,6 +417,38 @@ def test_kv_quant_dequant(dev):
     assert torch.equal(q1.view(torch.uint8), q2.view(torch.uint8))
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
+@pytest.mark.parametrize("rows,n", [(8, 128256), (1, 151936), (3, 1024), (64, 8191), (5, 7), (2, 8193)])
+def test_greedy_argmax_kernel_equals_torch_argmax(dev, dtype, rows, n):
+    """One-launch row argmax of the greedy head against `logits.argmax(dim=-1)` (reference:
+    engine/model_runner.py:1147-1151): exact indices, lowest index on ties, NaN largest, strided
+    rows, and a scratch buffer that is left zeroed (shared by consecutive calls)."""
+    from fastdms_b200.layers.sampler import argmax_workspace, greedy_argmax
+    g = torch.Generator(device=dev).manual_seed(rows * 1000 + n)
+    ws = argmax_workspace(rows, dev)
+    x = torch.randn((rows, n), device=dev, generator=g).to(dtype)
+    assert torch.equal(greedy_argmax(x, ws), x.argmax(dim=-1))
+    # 16-bit logits tie often: the first of the equal maxima is the answer
+    assert torch.equal(greedy_argmax(x, ws), first_max(x))
+    # a planted tie and a planted NaN
+    y = x.clone()
+    y[:, n // 2] = 60000.0
+    y[:, n - 1] = 60000.0
+    assert greedy_argmax(y, ws).tolist() == [n // 2] * rows
+    y[0, n // 3] = float("nan")
+    assert int(greedy_argmax(y, ws)[0]) == n // 3
+    # all-negative rows, rows of a wider buffer (row stride != n), no scratch given
+    wide = -torch.rand((rows, n + 24), device=dev, generator=g).to(dtype) - 1.0
+    view = wide[:, 8:8 + n]
+    assert torch.equal(greedy_argmax(view), first_max(view))
+    assert int(ws.count_nonzero()) == 0
+
+
+def first_max(x):
+    idx = torch.arange(x.shape[1], device=x.device).expand_as(x)
+    return torch.where(x == x.max(dim=-1, keepdim=True).values, idx, x.shape[1]).min(dim=-1).values
+
+
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
 @pytest.mark.parametrize("rows,hidden", [(8, 2048), (3, 4096), (257, 256), (64, 128), (5, 8192)])
 def test_rmsnorm_and_silu_kernels_match_torch_ops(dev, dtype, rows, hidden):
