@@ -44,7 +44,13 @@ _SIGNATURES = {
     "fdms_pack_scatter": (I32, [P, P, I32, I64, I64, P, I64, P, P, I32, P, P, P, I32, I64, P, I64,
                                 P, I64, I64, P, P, I64, I64, P, I64, I64, P, I64, I32, P, P,
                                 I32, I32, I32, I32, P, P]),
+    "fdms_pack_scatter_append": (I32, [P, P, I32, I64, I64, P, I64, P, P, I32, P, P, P, P, P, I32, I64, P, I64,
+                                       P, I64, I64, P, P, I64, I64, P, I64, I64, P, I64, I32, P, P,
+                                       I32, I32, I32, I32, P, P]),
+    "fdms_prefix_attention": (I32, [P, I32, I64, I64, P, I32, P, P, I32, I64, P, P, I64, P, I64, I64, I32,
+                                    P, P, P, P, I64, I64, P, I64, I64, P, I64, I64, I32, I32, I32, I32, F, P, P]),
     "fdms_alloc_pages": (I32, [P, P, I64, I64, I32, P, P, P, I32, I32, P, P]),
+    "fdms_grow_pages": (I32, [P, P, P, I64, I64, I32, P, P, P, I32, I32, P, P]),
     "fdms_free_pages": (I32, [P, I64, P, I64, I64, I32, P, P, P, I64, I32, I32, P, P]),
     "fdms_build_decode_metadata": (I32, [P, P, I64, I64, P, I64, I64, I64, I32, P, P, I64, P,
                                          P, P, P, P, I32, I32, I32, P, P]),

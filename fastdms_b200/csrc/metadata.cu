@@ -150,6 +150,33 @@ __global__ void alloc_pages_kernel(const int32_t* rows_needed, int32_t* bt, int6
     for (int pg = 0; pg < n; ++pg) row[pg] = free_pages[top - 1 - pg];
 }
 
+// Pops the pages with indices [ceil(before/16), ceil(after/16)) of every listed span.
+__global__ void grow_pages_kernel(const int32_t* rows_before, const int32_t* rows_after, int32_t* bt, int64_t bt_ss,
+                                  int64_t bt_sh, int max_pages, const int32_t* seq_slots, int32_t* free_pages,
+                                  int32_t* free_count, int num_seqs, int hk, int32_t* dev_status) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= num_seqs * hk) return;
+    const int s = i / hk, h = i - s * hk;
+    const int srow = seq_slots ? seq_slots[s] : s;
+    int32_t* row = bt + (int64_t)srow * bt_ss + (int64_t)h * bt_sh;
+    const int have = (max(rows_before[i], 0) + 15) >> 4;
+    int want = (max(rows_after[i], 0) + 15) >> 4;
+    if (want > max_pages) {
+        want = max_pages;
+        if (dev_status) atomicOr(dev_status, FDMS_DEV_BAD_INDEX);
+    }
+    const int n = want - have;
+    if (n <= 0) return;
+    const int top = atomicSub(free_count, n);
+    if (top - n < 0) {
+        atomicAdd(free_count, n);
+        if (dev_status) atomicOr(dev_status, FDMS_DEV_BAD_INDEX);
+        for (int pg = have; pg < want; ++pg) row[pg] = -1;
+        return;
+    }
+    for (int pg = 0; pg < n; ++pg) row[have + pg] = free_pages[top - 1 - pg];
+}
+
 // Returns every page of the listed spans to the free stack and clears their block-table rows.
 __global__ void free_pages_kernel(const int32_t* live, int64_t meta_ss, int32_t* bt, int64_t bt_ss,
                                   int64_t bt_sh, int max_pages, const int32_t* seq_slots,
@@ -242,6 +269,22 @@ extern "C" int32_t fdms_alloc_pages(
         rows_needed, block_tables, bt_stride_s, bt_stride_h, max_pages, seq_slots, free_pages, free_count,
         num_seqs, num_kv_heads, dev_status);
     FDMS_CHECK_LAUNCH("alloc_pages_kernel");
+    return FDMS_OK;
+}
+
+extern "C" int32_t fdms_grow_pages(
+    const int32_t* rows_before, const int32_t* rows_after, int32_t* block_tables, int64_t bt_stride_s,
+    int64_t bt_stride_h, int32_t max_pages, const int32_t* seq_slots, int32_t* free_pages, int32_t* free_count,
+    int32_t num_seqs, int32_t num_kv_heads, int32_t* dev_status, void* stream) {
+    clear_error();
+    FDMS_REQUIRE(rows_before && rows_after && block_tables && free_pages && free_count, FDMS_E_ARG, "fdms_grow_pages: null pointer");
+    FDMS_REQUIRE(num_seqs >= 0 && num_kv_heads > 0 && max_pages > 0, FDMS_E_ARG, "fdms_grow_pages: bad sizes");
+    const int total = num_seqs * num_kv_heads;
+    if (total == 0) return FDMS_OK;
+    grow_pages_kernel<<<(total + 127) / 128, 128, 0, (cudaStream_t)stream>>>(
+        rows_before, rows_after, block_tables, bt_stride_s, bt_stride_h, max_pages, seq_slots, free_pages, free_count,
+        num_seqs, num_kv_heads, dev_status);
+    FDMS_CHECK_LAUNCH("grow_pages_kernel");
     return FDMS_OK;
 }
 

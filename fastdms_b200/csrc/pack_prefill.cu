@@ -50,6 +50,7 @@ struct ScatterParams {
     const uint8_t* evict; int64_t ev_st; const int32_t* cu;
     const int32_t* chunk_offsets; int max_chunks;
     const int32_t* live_in;
+    const int32_t* prior_live; const int32_t* pos_offsets;   // chunked prefill: rows already in the span, first position
     void* k_pool; void* v_pool; int kv_dtype; int64_t pool_rows;
     const int32_t* base; int64_t base_ss;
     const int32_t* bt; int64_t bt_ss, bt_sh;
@@ -70,7 +71,9 @@ __global__ void __launch_bounds__(kPackThreads) pack_scatter_kernel(ScatterParam
     const int srow = p.seq_slots ? p.seq_slots[s] : s;
     const int64_t tok0 = p.cu[s];
     const int T = p.cu[s + 1] - p.cu[s];
-    const int live = p.live_in[s * p.hk + h];
+    const int prior = p.prior_live ? p.prior_live[s * p.hk + h] : 0;
+    const int pos0 = p.pos_offsets ? p.pos_offsets[s] : 0;
+    const int live = prior + p.live_in[s * p.hk + h];
     int32_t* pos = p.pos + (int64_t)srow * p.pos_ss + (int64_t)h * p.pos_sh;
     uint8_t* evm = p.evm + (int64_t)srow * p.ev_ss + (int64_t)h * p.ev_sh;
 
@@ -94,13 +97,13 @@ __global__ void __launch_bounds__(kPackThreads) pack_scatter_kernel(ScatterParam
         if (w < warp) before += s_warp[w];
         total += s_warp[w];
     }
-    const int chunk_off = p.chunk_offsets[((int64_t)s * p.hk + h) * p.max_chunks + c];
+    const int chunk_off = prior + p.chunk_offsets[((int64_t)s * p.hk + h) * p.max_chunks + c];
     const int r = before + __popc(ballot & ((1u << lane) - 1u));
     if (keep) {
         s_src[r] = t;
         const int idx = chunk_off + r;
         if (idx < p.capacity) {
-            pos[idx] = t;
+            pos[idx] = pos0 + t;
             evm[idx] = p.evict[(tok0 + t) * p.ev_st + h];
         } else if (p.dev_status) {
             atomicOr(p.dev_status, FDMS_DEV_BAD_INDEX);
@@ -150,10 +153,11 @@ extern "C" int32_t fdms_pack_count(
     return FDMS_OK;
 }
 
-extern "C" int32_t fdms_pack_scatter(
+extern "C" int32_t fdms_pack_scatter_append(
     const void* k, const void* v, int32_t act_dtype, int64_t kv_stride_t, int64_t kv_stride_h,
     const uint8_t* evict, int64_t evict_stride_t, const int32_t* cu_seqlens,
     const int32_t* chunk_offsets, int32_t max_chunks, const int32_t* live_in,
+    const int32_t* prior_live, const int32_t* pos_offsets,
     void* k_pool, void* v_pool, int32_t kv_dtype, int64_t pool_rows,
     const int32_t* base_offsets, int64_t base_stride_s,
     const int32_t* block_tables, int64_t bt_stride_s, int64_t bt_stride_h,
@@ -181,6 +185,7 @@ extern "C" int32_t fdms_pack_scatter(
     p.k = k; p.v = v; p.act_dtype = act_dtype; p.kv_st = kv_stride_t; p.kv_sh = kv_stride_h;
     p.evict = evict; p.ev_st = evict_stride_t; p.cu = cu_seqlens;
     p.chunk_offsets = chunk_offsets; p.max_chunks = max_chunks; p.live_in = live_in;
+    p.prior_live = prior_live; p.pos_offsets = pos_offsets;
     p.k_pool = k_pool; p.v_pool = v_pool; p.kv_dtype = kv_dtype; p.pool_rows = pool_rows;
     p.base = base_offsets; p.base_ss = base_stride_s;
     p.bt = block_tables; p.bt_ss = bt_stride_s; p.bt_sh = bt_stride_h;
@@ -194,4 +199,25 @@ extern "C" int32_t fdms_pack_scatter(
     pack_scatter_kernel<<<grid, kPackThreads, 0, (cudaStream_t)stream>>>(p);
     FDMS_CHECK_LAUNCH("pack_scatter_kernel");
     return FDMS_OK;
+}
+
+extern "C" int32_t fdms_pack_scatter(
+    const void* k, const void* v, int32_t act_dtype, int64_t kv_stride_t, int64_t kv_stride_h,
+    const uint8_t* evict, int64_t evict_stride_t, const int32_t* cu_seqlens,
+    const int32_t* chunk_offsets, int32_t max_chunks, const int32_t* live_in,
+    void* k_pool, void* v_pool, int32_t kv_dtype, int64_t pool_rows,
+    const int32_t* base_offsets, int64_t base_stride_s,
+    const int32_t* block_tables, int64_t bt_stride_s, int64_t bt_stride_h,
+    const int32_t* seq_slots,
+    int32_t* token_positions, int64_t pos_stride_s, int64_t pos_stride_h,
+    uint8_t* evict_mask, int64_t ev_stride_s, int64_t ev_stride_h,
+    int32_t* live_counts, int64_t meta_stride_s, int32_t capacity,
+    const float* k_scale, const float* v_scale,
+    int32_t num_seqs, int32_t num_kv_heads, int32_t head_dim, int32_t window,
+    int32_t* dev_status, void* stream) {
+    return fdms_pack_scatter_append(
+        k, v, act_dtype, kv_stride_t, kv_stride_h, evict, evict_stride_t, cu_seqlens, chunk_offsets, max_chunks, live_in,
+        nullptr, nullptr, k_pool, v_pool, kv_dtype, pool_rows, base_offsets, base_stride_s, block_tables, bt_stride_s,
+        bt_stride_h, seq_slots, token_positions, pos_stride_s, pos_stride_h, evict_mask, ev_stride_s, ev_stride_h,
+        live_counts, meta_stride_s, capacity, k_scale, v_scale, num_seqs, num_kv_heads, head_dim, window, dev_status, stream);
 }

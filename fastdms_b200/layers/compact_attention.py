@@ -175,6 +175,96 @@ def compact_decode_attention(
     return out
 
 
+def compact_prefix_attention(
+    q: torch.Tensor,
+    compact_k: torch.Tensor,
+    compact_v: torch.Tensor,
+    base_offsets: torch.Tensor | None,
+    live_counts: torch.Tensor,
+    cu_seqlens_q: torch.Tensor,
+    max_q_len: int,
+    out: torch.Tensor,
+    dense_lse: torch.Tensor | None = None,
+    scale: float | None = None,
+    *,
+    seq_slots: torch.Tensor | None = None,
+    block_tables: torch.Tensor | None = None,
+    k_scale: torch.Tensor | None = None,
+    v_scale: torch.Tensor | None = None,
+    lse_out: torch.Tensor | None = None,
+) -> torch.Tensor:
+    """Prefill-tail attention of a chunked prefill (no counterpart in the reference, whose prefill is
+    one dense pass, `layers/attention.py:85-92`): the chunk's queries `q [tokens, q_heads, head_dim]`
+    (post-RoPE, sequences delimited by `cu_seqlens_q`) attend to the rows their (sequence, KV head)
+    span already holds -- `base_offsets` / `live_counts` `[rows, kv_heads]` addressed through
+    `seq_slots` (or row i = sequence i), `block_tables [rows, kv_heads, pages]` for the paged layout --
+    and the result is merged IN PLACE into `out`, which on entry holds the chunk's own causal
+    attention with `dense_lse [q_heads, tokens]` its natural-log log-sum-exp.  `dense_lse=None`
+    overwrites `out` with the attention over the span rows alone.  Spans with no rows leave `out`
+    untouched.  One launch of `fdms_prefix_attention`."""
+    if q.ndim != 3 or out.shape != q.shape or out.dtype != q.dtype:
+        raise ValueError(f"expected q and out as [tokens, q_heads, head_dim] of one dtype, got {tuple(q.shape)} / {tuple(out.shape)}")
+    tokens, num_q_heads, head_dim = q.shape
+    if live_counts.ndim != 2:
+        raise ValueError(f"expected live_counts [rows, kv_heads], got {tuple(live_counts.shape)}")
+    num_kv_heads = live_counts.shape[1]
+    if num_q_heads % num_kv_heads != 0:
+        raise ValueError(f"q heads {num_q_heads} not divisible by kv heads {num_kv_heads}")
+    if base_offsets is None and block_tables is None:
+        raise ValueError("base_offsets or block_tables required")
+    if compact_k.shape != compact_v.shape or compact_k.ndim != 2 or compact_k.shape[1] != head_dim:
+        raise ValueError(f"expected compact_k/v as [slots, {head_dim}], got {tuple(compact_k.shape)} / {tuple(compact_v.shape)}")
+    _lib.require_cuda(q, compact_k, compact_v, out)
+    dev = q.device
+    _inner_contiguous(q, "q")
+    _inner_contiguous(out, "out")
+    num_seqs = cu_seqlens_q.numel() - 1
+    cu = cu_seqlens_q.to(device=dev, dtype=torch.int32).contiguous()
+    live_counts = live_counts.to(device=dev, dtype=torch.int32)
+    if live_counts.stride(1) != 1:
+        live_counts = live_counts.contiguous()
+    if base_offsets is not None:
+        base_offsets = base_offsets.to(device=dev, dtype=torch.int32)
+        if base_offsets.stride() != live_counts.stride():
+            base_offsets, live_counts = base_offsets.contiguous(), live_counts.contiguous()
+    bt_ss = bt_sh = bt_pages = 0
+    if block_tables is not None:
+        if block_tables.ndim != 3 or block_tables.shape[1] != num_kv_heads or block_tables.stride(2) != 1:
+            raise ValueError(f"expected block_tables [rows, kv_heads, pages] (last dim contiguous), got {tuple(block_tables.shape)}")
+        if block_tables.dtype != torch.int32:
+            raise ValueError("block_tables must be int32")
+        bt_ss, bt_sh, bt_pages = block_tables.stride(0), block_tables.stride(1), block_tables.shape[2]
+    if seq_slots is not None:
+        seq_slots = seq_slots.to(device=dev, dtype=torch.int32).contiguous()
+    elif live_counts.shape[0] < num_seqs:
+        raise ValueError("live_counts has fewer rows than sequences and no seq_slots were given")
+    k_scale, v_scale = _scales(k_scale, v_scale, num_kv_heads, dev)
+    lse_sh = lse_st = lo_sh = lo_st = 0
+    if dense_lse is not None:
+        if dense_lse.shape != (num_q_heads, tokens) or dense_lse.dtype != torch.float32:
+            raise ValueError(f"expected float32 dense_lse {(num_q_heads, tokens)}, got {tuple(dense_lse.shape)} {dense_lse.dtype}")
+        lse_sh, lse_st = dense_lse.stride()
+    if lse_out is not None:
+        if lse_out.shape != (num_q_heads, tokens) or lse_out.dtype != torch.float32:
+            raise ValueError(f"expected float32 lse_out {(num_q_heads, tokens)}")
+        lo_sh, lo_st = lse_out.stride()
+    if scale is None:
+        scale = head_dim ** -0.5
+    status = _lib.status_word(dev)
+    with torch.cuda.device(dev):
+        rc = _lib.lib().fdms_prefix_attention(
+            q.data_ptr(), _lib.dtype_code(q.dtype), q.stride(0), q.stride(1), cu.data_ptr(), int(max_q_len),
+            compact_k.data_ptr(), compact_v.data_ptr(), _lib.dtype_code(compact_k.dtype), compact_k.shape[0],
+            _lib.ptr(base_offsets), live_counts.data_ptr(), live_counts.stride(0),
+            _lib.ptr(block_tables), bt_ss, bt_sh, bt_pages, _lib.ptr(seq_slots),
+            _lib.ptr(k_scale), _lib.ptr(v_scale),
+            out.data_ptr(), out.stride(0), out.stride(1),
+            _lib.ptr(dense_lse), lse_sh, lse_st, _lib.ptr(lse_out), lo_sh, lo_st,
+            num_seqs, num_q_heads, num_kv_heads, head_dim, float(scale), status.data_ptr(), _lib.stream_ptr(dev))
+    _lib.check(rc)
+    return out
+
+
 def fused_store_decode_attention(
     q: torch.Tensor,
     k: torch.Tensor,

@@ -240,6 +240,55 @@ int32_t fdms_pack_scatter(
     int32_t num_seqs, int32_t num_kv_heads, int32_t head_dim, int32_t window,
     int32_t* dev_status, void* stream);
 
+/* Chunked prefill: the same scatter for a chunk [pos_offsets[s], pos_offsets[s] + T) of a prompt whose
+ * earlier chunks already sit in the span (no counterpart in the reference, which packs a prompt in one
+ * pass).  prior_live int32 [num_seqs, kv_heads] = rows the span holds before this chunk (after the
+ * expiry run with the chunk's last position): kept tokens go to logical rows prior_live + rank, their
+ * recorded position is pos_offsets[s] + index within the chunk, live_counts = prior_live + live_in and
+ * the metadata rows are reset beyond that.  The keep rule is the chunk-local one of fdms_pack_scatter,
+ * which equals the global rule evaluated at the chunk's last position.  NULL prior_live / pos_offsets
+ * read as zeros (then the call is fdms_pack_scatter). */
+int32_t fdms_pack_scatter_append(
+    const void* k, const void* v, int32_t act_dtype, int64_t kv_stride_t, int64_t kv_stride_h,
+    const uint8_t* evict, int64_t evict_stride_t, const int32_t* cu_seqlens,
+    const int32_t* chunk_offsets, int32_t max_chunks, const int32_t* live_in,
+    const int32_t* prior_live, const int32_t* pos_offsets,
+    void* k_pool, void* v_pool, int32_t kv_dtype, int64_t pool_rows,
+    const int32_t* base_offsets, int64_t base_stride_s,
+    const int32_t* block_tables, int64_t bt_stride_s, int64_t bt_stride_h,
+    const int32_t* seq_slots,
+    int32_t* token_positions, int64_t pos_stride_s, int64_t pos_stride_h,
+    uint8_t* evict_mask, int64_t ev_stride_s, int64_t ev_stride_h,
+    int32_t* live_counts, int64_t meta_stride_s, int32_t capacity,
+    const float* k_scale, const float* v_scale,
+    int32_t num_seqs, int32_t num_kv_heads, int32_t head_dim, int32_t window,
+    int32_t* dev_status, void* stream);
+
+/* Prefill-tail attention (no counterpart in the reference, whose prefill is one dense pass,
+ * fastdms/layers/attention.py:85-92): the queries of a prefill chunk against the rows their span
+ * already holds, merged in place with the chunk's own causal attention.
+ *   q [total_q, q_heads, head_dim] post-RoPE, cu_seqlens_q int32 [num_seqs+1], max_q_len = longest chunk;
+ *   pools / base_offsets / live_counts / block tables / seq_slots / scales as in fdms_attn_decode, the
+ *   metadata being the layer's [seqs, kv_heads] slices addressed through seq_slots (live = rows in the
+ *   span BEFORE the chunk is packed);
+ *   out [total_q, q_heads, head_dim] activation dtype: on entry the normalised causal attention of the
+ *   chunk over its own K/V, with dense_lse[h * lse_stride_h + token * lse_stride_t] its natural-log
+ *   log-sum-exp of the scaled scores; on return softmax over (span rows + chunk tokens <= query).
+ *   dense_lse NULL: out is overwritten with the attention over the span rows alone.  Spans with
+ *   live = 0 leave out untouched.  lse_out (optional, same indexing with its own strides) receives
+ *   the merged log-sum-exp.  head_dim 64 or 128, at most 8 q heads per KV head. */
+int32_t fdms_prefix_attention(
+    const void* q, int32_t act_dtype, int64_t q_stride_t, int64_t q_stride_h, const int32_t* cu_seqlens_q,
+    int32_t max_q_len, const void* k_pool, const void* v_pool, int32_t kv_dtype, int64_t pool_rows,
+    const int32_t* base_offsets, const int32_t* live_counts, int64_t meta_stride_s,
+    const int32_t* block_tables, int64_t bt_stride_s, int64_t bt_stride_h, int32_t bt_max_pages,
+    const int32_t* seq_slots, const float* k_scale, const float* v_scale,
+    void* out, int64_t out_stride_t, int64_t out_stride_h,
+    const float* dense_lse, int64_t lse_stride_h, int64_t lse_stride_t,
+    float* lse_out, int64_t lse_out_stride_h, int64_t lse_out_stride_t,
+    int32_t num_seqs, int32_t num_q_heads, int32_t num_kv_heads, int32_t head_dim, float scale,
+    int32_t* dev_status, void* stream);
+
 /* Page allocator of the paged layout (no counterpart in the reference, whose spans are contiguous
  * ranges handed out by a host first-fit list, fastdms/engine/compact_kv.py:705-737).
  * fdms_alloc_pages pops ceil(rows_needed[s,h] / 16) pages per span from one layer's free stack into
@@ -248,6 +297,12 @@ int32_t fdms_pack_scatter(
 int32_t fdms_alloc_pages(
     const int32_t* rows_needed, int32_t* block_tables, int64_t bt_stride_s, int64_t bt_stride_h,
     int32_t max_pages, const int32_t* seq_slots, int32_t* free_pages, int32_t* free_count,
+    int32_t num_seqs, int32_t num_kv_heads, int32_t* dev_status, void* stream);
+/* fdms_grow_pages: pops the pages with indices [ceil(rows_before/16), ceil(rows_after/16)) of every
+ * listed span (chunked prefill appends to spans that already hold rows). */
+int32_t fdms_grow_pages(
+    const int32_t* rows_before, const int32_t* rows_after, int32_t* block_tables, int64_t bt_stride_s,
+    int64_t bt_stride_h, int32_t max_pages, const int32_t* seq_slots, int32_t* free_pages, int32_t* free_count,
     int32_t num_seqs, int32_t num_kv_heads, int32_t* dev_status, void* stream);
 int32_t fdms_free_pages(
     const int32_t* live_counts, int64_t meta_stride_s, int32_t* block_tables, int64_t bt_stride_s,

@@ -346,6 +346,59 @@ def decode_attention(q, compact_k, compact_v, base_offsets, live_counts, scale=N
     return round_to(out, out_dtype)
 
 
+def chunk_attention(q, k_chunk, v_chunk, prefix_k, prefix_v, scale=None):
+    """Attention of one prefill chunk of one sequence under chunked prefill (an extension: the
+    reference prefills densely in one pass, fastdms/layers/attention.py:85-92; parity unpinned).
+    A query at chunk index i sees every prefix row (the rows its KV head's span held when the chunk
+    started, already dequantised: prefix_k/v[h] float32 [n_h, D]) and chunk tokens 0..i.
+    q [T,Hq,D], k_chunk/v_chunk [T,Hk,D] float32 values.  Returns (out [T,Hq,D],
+    lse_dense [Hq,T], lse_total [Hq,T]) in float32; the log-sum-exps are natural-log, of the scaled scores."""
+    T, Hq, D = q.shape
+    Hk = k_chunk.shape[1]
+    G = Hq // Hk
+    if scale is None:
+        scale = D ** -0.5
+    out = np.zeros((T, Hq, D), np.float32)
+    lse_d = np.zeros((Hq, T), np.float32)
+    lse_t = np.zeros((Hq, T), np.float32)
+    causal = np.tril(np.ones((T, T), bool))
+    for h in range(Hk):
+        pk, pv = np.asarray(prefix_k[h], np.float32), np.asarray(prefix_v[h], np.float32)
+        n = pk.shape[0]
+        for g in range(G):
+            qh = h * G + g
+            qq = q[:, qh].astype(np.float32)
+            sd = (qq @ k_chunk[:, h].astype(np.float32).T) * np.float32(scale)
+            sd = np.where(causal, sd, -np.inf)
+            sp = (qq @ pk.T) * np.float32(scale) if n else np.zeros((T, 0), np.float32)
+            s = np.concatenate([sp, sd], axis=1).astype(np.float64)
+            m = s.max(axis=1, keepdims=True)
+            e = np.exp(s - m)
+            z = e.sum(axis=1, keepdims=True)
+            vv = np.concatenate([pv, v_chunk[:, h].astype(np.float32)], axis=0).astype(np.float64)
+            out[:, qh] = ((e / z) @ vv).astype(np.float32)
+            lse_t[qh] = (m[:, 0] + np.log(z[:, 0])).astype(np.float32)
+            md = sd.max(axis=1)
+            lse_d[qh] = (md + np.log(np.exp(sd.astype(np.float64) - md[:, None]).sum(axis=1))).astype(np.float32)
+    return out, lse_d, lse_t
+
+
+def chunked_prefill_state(evict, window_size, chunk):
+    """Logical contents (prompt positions, ascending) of one (layer, seq, head) span after the prompt
+    was prefilled in chunks of `chunk` tokens: after every chunk ending at position e-1 the span is
+    expired with cur = e-1 (rule of expire_span) and the chunk's tokens that pass pack_keep (chunk-
+    local rule = the global rule at cur = e-1) are appended.  evict bool [T].  The final contents
+    equal those of the one-pass pack, pack_keep(evict, window_size), for every chunk size."""
+    T = len(evict)
+    kept: list[int] = []
+    for s0 in range(0, T, chunk):
+        e = min(T, s0 + chunk)
+        cur = e - 1
+        kept = [t for t in kept if (not evict[t]) or cur - t <= window_size]
+        kept += [t for t in range(s0, e) if (not evict[t]) or cur - t <= window_size]
+    return np.asarray(kept, np.int64)
+
+
 # --------------------------------------------------------------------------------------
 # FP8 KV quantise / dequantise with a per-head scale
 # --------------------------------------------------------------------------------------
