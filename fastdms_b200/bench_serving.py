@@ -9,7 +9,7 @@ compact KV pool.  Shapes and arrival process follow the reference's serving-styl
 Requests are admitted by the scheduler when the token budget and the compact pool allow: charged
 their worst case (`--admission reserve`) or an estimate of what DMS keeps, with a retry when a
 prefill does not fit (`--admission optimistic`, contiguous spans).  Nothing that runs is preempted.
-Whole prompts are prefilled in one step.  Prints one JSON line: request and token throughput, time to
+Whole prompts are prefilled in one step, or in `--prefill-chunk`-token pieces.  Prints one JSON line: request and token throughput, time to
 first token, decode step statistics, peak live rows of the pool, and a check that every page / span
 went back to the pool at the end."""
 from __future__ import annotations
@@ -43,10 +43,11 @@ def run(args) -> dict:
     budget = int(args.kv_gib * (1 << 30)) if args.kv_gib else None
     engine = LLMEngine(
         f"synthetic-{args.shape}", hf_config=hf, random_init_seed=args.seed, device=dev, max_model_len=max_len,
-        max_num_seqs=args.max_concurrent, max_num_batched_tokens=max(2 * args.max_prompt, 16384),
+        max_num_seqs=args.max_concurrent,
+        max_num_batched_tokens=max(4 * args.prefill_chunk, 8192) if args.prefill_chunk else max(2 * args.max_prompt, 16384),
         kv_cache_dtype="float8_e4m3fn", compact_kv_paged=args.paged, compact_kv_budget_bytes=budget,
         dms_window_size=args.window, compact_kv_admission=args.admission,
-        compact_kv_admission_keep_estimate=args.keep_estimate)
+        compact_kv_admission_keep_estimate=args.keep_estimate, prefill_chunk_size=args.prefill_chunk or None)
     mgr = engine.model_runner.compact_kv_manager
     vocab = hf["vocab_size"]
     g = torch.Generator().manual_seed(args.seed)
@@ -107,7 +108,7 @@ def run(args) -> dict:
         "decode_steps": len(decode_ms), "decode_ms_per_step": {"p50": float(np.median(dm)), "p90": float(np.quantile(dm, 0.9))},
         "mean_decode_batch": float(np.mean(decode_batch)) if decode_batch else 0.0,
         "pool_rows_per_layer": mgr.capacity_tokens, "pool_gib": mgr.capacity_tokens * elem_rows / (1 << 30),
-        "peak_live_rows_layer0_sampled": peak_live, "admission": args.admission,
+        "peak_live_rows_layer0_sampled": peak_live, "admission": args.admission, "prefill_chunk": args.prefill_chunk,
         "admission_denied": int(mgr.admission_denied_count), "prefill_retries": int(engine.scheduler.prefill_retries),
         "pool_returned_clean": bool(pool_clean), "layout": "paged" if mgr.paged else "spans",
         "device_status": int(_lib.read_device_status(dev)),
@@ -130,6 +131,7 @@ def main() -> None:
     ap.add_argument("--paged", action="store_true")
     ap.add_argument("--admission", choices=["reserve", "optimistic"], default="reserve")
     ap.add_argument("--keep-estimate", type=float, default=0.2)
+    ap.add_argument("--prefill-chunk", type=int, default=0, help="prefill prompts in chunks of this many tokens (0: one pass)")
     ap.add_argument("--seed", type=int, default=0)
     print(json.dumps(run(ap.parse_args())))
 

@@ -55,6 +55,7 @@ class Config:
     compact_kv_row_indirection: bool = True   # expiry compacts metadata only and refills freed K/V rows
     compact_kv_admission: str = "reserve"     # "reserve": worst case per request; "optimistic": estimate + retry
     compact_kv_admission_keep_estimate: float = 0.25
+    prefill_chunk_size: int | None = None          # prompts are prefilled in chunks of this many tokens (None: one pass)
     random_init_seed: int | None = None       # synthetic weights when the directory has no safetensors
     dtype: str | None = None                  # overrides the checkpoint's dtype
 

@@ -392,10 +392,17 @@ class CompactKVManager:
 
     # ------------------------------------------------------------------ prefill pack
     def streaming_pack_layer(self, *, layer_id: int, k: torch.Tensor, v: torch.Tensor, evict_mask: torch.Tensor,
-                             cu_seqlens_q: torch.Tensor, seq_ids: list[int], window_size: int) -> None:
+                             cu_seqlens_q: torch.Tensor, seq_ids: list[int], window_size: int,
+                             chunk_starts: list[int] | None = None, remaining: list[int] | None = None) -> None:
         """Packs one layer's post-RoPE K / raw V of a prefill batch into compact spans
         (reference: compact_kv.py:915-1099).  k, v [total_tokens, kv_heads, head_dim];
-        evict_mask bool [total_tokens, kv_heads]; cu_seqlens_q int32 [num_seqs + 1]."""
+        evict_mask bool [total_tokens, kv_heads]; cu_seqlens_q int32 [num_seqs + 1].
+
+        Chunked prefill (an extension): `chunk_starts[i]` is the prompt position of sequence i's first
+        token in this batch and `remaining[i]` the prompt tokens still to come after it.  The layer's
+        spans are first expired with the chunk's last position, then the chunk's kept tokens are
+        appended behind the rows the span already holds.  Contiguous spans are reserved at the first
+        chunk for the worst case of the rest of the prompt; paged spans grow page by page."""
         _lib.require_cuda(k, v, evict_mask)
         states = []
         for sid in seq_ids:
@@ -428,27 +435,51 @@ class CompactKVManager:
         status = _lib.status_word(dev)
         lib = _lib.lib()
         slots_t = self._slots_tensor(states)
+        chunked = chunk_starts is not None
+        prior = starts_t = None
+        if chunked:
+            if len(chunk_starts) != n or remaining is None or len(remaining) != n:
+                raise ValueError("chunk_starts / remaining need one entry per sequence")
+            if any(int(c) > 0 for c in chunk_starts):
+                cur = torch.tensor([int(c) + cu_host[i + 1] - cu_host[i] - 1 for i, c in enumerate(chunk_starts)],
+                                   dtype=torch.int64).to(dev, non_blocking=True)
+                self.expire_device(slots_t, cur, window_size=window_size, layer_id=layer_id)
+            starts_t = torch.tensor([int(c) for c in chunk_starts], dtype=torch.int32).to(dev, non_blocking=True)
+            prior = self.layer_major_live_counts[layer_id].index_select(0, slots_t.long()).contiguous()
         with torch.cuda.device(dev):
             _lib.check(lib.fdms_pack_count(ev_u8.data_ptr(), ev_u8.stride(0), cu.data_ptr(), live.data_ptr(),
                                            chunk_offsets.data_ptr(), max_chunks, n, Hk, int(window_size), stream))
             capacity = self.max_model_len
             if self.paged:
                 bt = self.block_tables[layer_id]
-                _lib.check(lib.fdms_alloc_pages(
-                    live.data_ptr(), bt.data_ptr(), bt.stride(0), bt.stride(1), self.max_pages,
-                    slots_t.data_ptr(), self.free_pages[layer_id].data_ptr(),
-                    self.free_page_counts[layer_id:].data_ptr(), n, Hk, status.data_ptr(), stream))
+                if chunked:
+                    after = prior + live
+                    _lib.check(lib.fdms_grow_pages(
+                        prior.data_ptr(), after.data_ptr(), bt.data_ptr(), bt.stride(0), bt.stride(1), self.max_pages,
+                        slots_t.data_ptr(), self.free_pages[layer_id].data_ptr(),
+                        self.free_page_counts[layer_id:].data_ptr(), n, Hk, status.data_ptr(), stream))
+                else:
+                    _lib.check(lib.fdms_alloc_pages(
+                        live.data_ptr(), bt.data_ptr(), bt.stride(0), bt.stride(1), self.max_pages,
+                        slots_t.data_ptr(), self.free_pages[layer_id].data_ptr(),
+                        self.free_page_counts[layer_id:].data_ptr(), n, Hk, status.data_ptr(), stream))
                 base_ptr, base_ss = None, 0
                 bt_args = (bt.data_ptr(), bt.stride(0), bt.stride(1))
             else:
                 live_host = live.tolist()        # the host first-fit allocator needs the counts
                 all_bases, all_sizes = [], []
-                for st, row in zip(states, live_host):
-                    if max(row) > st.max_capacity_per_lh:
+                for i, (st, row) in enumerate(zip(states, live_host)):
+                    if chunked and st.host_ranges[layer_id][0] is not None:
+                        # a later chunk: the span was reserved for the whole prompt at the first one
+                        all_bases.append([r[0] for r in st.host_ranges[layer_id]])
+                        all_sizes.append([r[1] for r in st.host_ranges[layer_id]])
+                        continue
+                    extra = int(remaining[i]) if chunked else 0
+                    if max(row) + extra > st.max_capacity_per_lh:
                         raise RuntimeError(
-                            f"streaming pack live count {max(row)} exceeds metadata capacity "
+                            f"streaming pack live count {max(row) + extra} exceeds metadata capacity "
                             f"{st.max_capacity_per_lh} (layer {layer_id}, seq {st.seq_id})")
-                    b, s = self._reserve_layer(st, layer_id, row)
+                    b, s = self._reserve_layer(st, layer_id, [r + extra for r in row])
                     all_bases.append(b)
                     all_sizes.append(s)
                 hi = max(b + s for bs, ss in zip(all_bases, all_sizes) for b, s in zip(bs, ss))
@@ -465,10 +496,10 @@ class CompactKVManager:
             lc = self.layer_major_live_counts[layer_id]
             ks, vs = self.layer_scales(layer_id)
             ck, cv = self.compact_k_per_layer[layer_id], self.compact_v_per_layer[layer_id]
-            _lib.check(lib.fdms_pack_scatter(
+            _lib.check(lib.fdms_pack_scatter_append(
                 k.data_ptr(), v.data_ptr(), _lib.dtype_code(k.dtype), k.stride(0), k.stride(1),
                 ev_u8.data_ptr(), ev_u8.stride(0), cu.data_ptr(),
-                chunk_offsets.data_ptr(), max_chunks, live.data_ptr(),
+                chunk_offsets.data_ptr(), max_chunks, live.data_ptr(), _lib.ptr(prior), _lib.ptr(starts_t),
                 ck.data_ptr(), cv.data_ptr(), _lib.dtype_code(ck.dtype), ck.shape[0],
                 base_ptr, base_ss, *bt_args,
                 slots_t.data_ptr(),
@@ -519,18 +550,24 @@ class CompactKVManager:
         return {k: stats[i] for i, k in enumerate(keys)}
 
     def expire_device(self, slots_t: torch.Tensor, cur_positions_t: torch.Tensor, *, window_size: int,
-                      incremental: bool = False, stats: torch.Tensor | None = None) -> None:
+                      incremental: bool = False, stats: torch.Tensor | None = None,
+                      layer_id: int | None = None) -> None:
         """The expiry launch itself, on device-resident arguments only (no allocation, no host
         synchronisation; safe inside CUDA-graph capture).  slots_t int32 [n] active slots,
-        cur_positions_t int64 [n]; stats optional int64[5] initialised by the caller."""
+        cur_positions_t int64 [n]; stats optional int64[5] initialised by the caller.  `layer_id`
+        restricts the launch to one layer (chunked prefill expires a layer right before it appends
+        the chunk to it)."""
         dev = self.device
-        pos, ev = self.layer_major_token_positions, self.layer_major_evict_mask.view(torch.uint8)
-        lc, base = self.layer_major_live_counts, self.layer_major_base_offsets
+        ls = slice(None) if layer_id is None else slice(layer_id, layer_id + 1)
+        pos, ev = self.layer_major_token_positions[ls], self.layer_major_evict_mask.view(torch.uint8)[ls]
+        lc, base = self.layer_major_live_counts[ls], self.layer_major_base_offsets[ls]
+        ck, cv = self.compact_k[ls], self.compact_v[ls]
+        row_index = None if self.layer_major_row_index is None else self.layer_major_row_index[ls]
         row_bytes = self.head_dim * self.compact_k.element_size()
         if self.paged:
-            bt = self.block_tables
+            bt = self.block_tables[ls]
             bt_args = (bt.data_ptr(), bt.stride(0), bt.stride(1), bt.stride(2),
-                       self.free_pages.data_ptr(), self.free_page_counts.data_ptr(), self.pages_per_layer)
+                       self.free_pages[ls].data_ptr(), self.free_page_counts[ls].data_ptr(), self.pages_per_layer)
             base_ptr = None
         else:
             bt_args = (None, 0, 0, 0, None, None, 0)
@@ -538,13 +575,13 @@ class CompactKVManager:
         with torch.cuda.device(dev):
             rc = _lib.lib().fdms_expire_compact(
                 pos.data_ptr(), pos.stride(0), pos.stride(1), pos.stride(2),
-                ev.data_ptr(), ev.stride(0), ev.stride(1), ev.stride(2), _lib.ptr(self.layer_major_row_index),
+                ev.data_ptr(), ev.stride(0), ev.stride(1), ev.stride(2), _lib.ptr(row_index),
                 lc.data_ptr(), base_ptr, lc.stride(0), lc.stride(1),
-                self.compact_k.data_ptr(), self.compact_v.data_ptr(),
+                ck.data_ptr(), cv.data_ptr(),
                 self.compact_k.stride(0) * self.compact_k.element_size(), row_bytes, self.capacity_tokens,
                 *bt_args,
                 slots_t.data_ptr(), cur_positions_t.data_ptr(),
-                self.num_layers, slots_t.numel(), self.num_kv_heads, self.max_model_len,
+                pos.shape[0], slots_t.numel(), self.num_kv_heads, self.max_model_len,
                 int(window_size), 1 if incremental else 0, _lib.ptr(stats),
                 _lib.status_word(dev).data_ptr(), _lib.stream_ptr(dev))
         _lib.check(rc)

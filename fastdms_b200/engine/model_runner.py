@@ -186,15 +186,26 @@ class ModelRunner:
     # ------------------------------------------------------------------ prefill
     @torch.inference_mode()
     def run_prefill(self, seqs: list[Sequence]) -> torch.Tensor:
-        """Whole prompts of `seqs` in one forward; returns the logits of each last prompt token."""
+        """One prefill forward: whole prompts, or -- with `Config.prefill_chunk_size` -- the next
+        `num_scheduled_tokens` prompt tokens of every sequence (tokens before `num_cached_tokens` are
+        already in its compact spans).  Returns the logits of each sequence's last token of the batch."""
         md, m, dev = self.dms_metadata, self.compact_kv_manager, self.device
         ids, pos, cu = [], [], [0]
+        starts, remaining = [], []
         for seq in seqs:
-            n = len(seq)
-            ids.extend(seq[0:n])
-            pos.extend(range(n))
+            total = len(seq)
+            a = int(seq.num_cached_tokens) if self.config.prefill_chunk_size else 0
+            n = int(seq.num_scheduled_tokens) if self.config.prefill_chunk_size and seq.num_scheduled_tokens else total - a
+            ids.extend(seq[a:a + n])
+            pos.extend(range(a, a + n))
             cu.append(cu[-1] + n)
+            starts.append(a)
+            remaining.append(total - a - n)
             m.allocate(seq)
+        chunked = bool(self.config.prefill_chunk_size)
+        prefix_slots = None
+        if chunked and any(a > 0 for a in starts):
+            prefix_slots = m._slots_tensor(m._states(seqs))
         ids_t = torch.tensor(ids, dtype=torch.int64, pin_memory=True).to(dev, non_blocking=True)
         pos_t = torch.tensor(pos, dtype=torch.int64, pin_memory=True).to(dev, non_blocking=True)
         cu_t = torch.tensor(cu, dtype=torch.int32, pin_memory=True).to(dev, non_blocking=True)
@@ -202,7 +213,8 @@ class ModelRunner:
                     compact_kv_enabled=True, dms_capture_enabled=True, dms_alpha_scale=md.alpha_scale,
                     dms_alpha_offset=md.alpha_offset, dms_layer_evictions={}, streaming_pack_manager=m,
                     streaming_pack_seq_ids=[s.seq_id for s in seqs], streaming_pack_window_size=md.window_size,
-                    cu_seqlens_host=cu)
+                    cu_seqlens_host=cu, prefill_chunk_starts=starts if chunked else None,
+                    prefill_chunk_remaining=remaining if chunked else None, compact_prefix_slots=prefix_slots)
         try:
             with get_profiler().cuda_phase("model_forward_prefill"):
                 hidden = self.model(ids_t, pos_t)

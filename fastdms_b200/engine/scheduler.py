@@ -12,7 +12,13 @@ Two admission modes (the manager's `admission`):
     of the queue, the next prefill batch is at most half as large, and while requests are running no
     new prefill is tried until one of them finishes (its spans come back).  Running requests own
     their spans including the decode headroom, so decode itself never runs out: nothing that has
-    started is ever preempted."""
+    started is ever preempted.
+
+With `prefill_chunk_size` set, a prompt enters the pool in chunks of that many tokens (an extension:
+the reference prefills in one pass).  A step then carries the next chunk of every request whose
+prompt is only partly in, plus first chunks of newly admitted requests while the token budget
+lasts; decode steps run when no prompt is pending.  Only the chunk that ends a prompt yields a
+token."""
 from __future__ import annotations
 
 from collections import deque
@@ -33,6 +39,9 @@ class Scheduler:
         self.prefill_batch_limit: int | None = None     # set after a prefill that did not fit
         self.hold_prefill = False                        # wait for a running request to finish first
         self.prefill_retries = 0
+        self.prefill_chunk_size = getattr(config, "prefill_chunk_size", None) or None
+        if self.prefill_chunk_size is not None and not 0 < self.prefill_chunk_size <= self.max_num_batched_tokens:
+            raise ValueError("prefill_chunk_size must be positive and at most max_num_batched_tokens")
 
     def is_finished(self) -> bool:
         return not self.waiting and not self.running
@@ -46,10 +55,23 @@ class Scheduler:
         pending = 0
         limit = self.prefill_batch_limit if self.prefill_batch_limit is not None else self.max_num_seqs
         hold = self.hold_prefill and bool(self.running)
+        chunk = self.prefill_chunk_size
+        continuing: list[Sequence] = []
+        if chunk:
+            for seq in self.running:
+                left = seq.num_prompt_tokens - seq.num_cached_tokens
+                if left <= 0:
+                    continue
+                n = min(chunk, left)
+                if n > budget:
+                    break
+                seq.num_scheduled_tokens = n
+                continuing.append(seq)
+                budget -= n
         while (not hold and self.waiting and len(scheduled) < limit
                and len(self.running) + len(scheduled) < self.max_num_seqs):
             seq = self.waiting[0]
-            n = seq.num_tokens
+            n = min(chunk, seq.num_tokens) if chunk else seq.num_tokens
             if n > self.max_num_batched_tokens:
                 raise RuntimeError(f"prompt of {n} tokens exceeds max_num_batched_tokens={self.max_num_batched_tokens}")
             if n > budget or not self.can_allocate(seq, pending):
@@ -60,9 +82,9 @@ class Scheduler:
             self.waiting.popleft()
             scheduled.append(seq)
             budget -= n
-        if scheduled:
+        if scheduled or continuing:
             self.running.extend(scheduled)
-            return scheduled, True
+            return continuing + scheduled, True
         if not self.running:
             raise RuntimeError("no request fits the compact KV pool / token budget")
         batch = list(self.running)[: self.max_num_seqs]
@@ -78,6 +100,7 @@ class Scheduler:
             self.running.remove(seq)
             seq.status = SequenceStatus.WAITING
             seq.num_scheduled_tokens = 0
+            seq.num_cached_tokens = 0
             self.waiting.appendleft(seq)
         self.prefill_retries += 1
         if len(seqs) > 1:
@@ -90,6 +113,11 @@ class Scheduler:
 
     def postprocess(self, seqs: list[Sequence], token_ids: list[int], is_prefill: bool) -> None:
         for seq, token_id in zip(seqs, token_ids):
+            if is_prefill and self.prefill_chunk_size:
+                seq.num_cached_tokens += seq.num_scheduled_tokens
+                if seq.num_cached_tokens < seq.num_prompt_tokens:      # more of the prompt to come: no token yet
+                    seq.num_scheduled_tokens = 0
+                    continue
             seq.append_token(token_id)
             seq.num_cached_tokens = seq.num_tokens
             seq.num_scheduled_tokens = 0

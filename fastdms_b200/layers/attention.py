@@ -13,8 +13,8 @@ import torch
 import torch.nn.functional as F
 from torch import nn
 
-from fastdms_b200.layers.compact_attention import (compact_decode_attention, fused_store_decode_attention,
-                                                   store_compact_kvcache)
+from fastdms_b200.layers.compact_attention import (compact_decode_attention, compact_prefix_attention,
+                                                   fused_store_decode_attention, store_compact_kvcache)
 from fastdms_b200.utils.context import get_context
 from fastdms_b200.utils.profiler import get_profiler
 
@@ -32,6 +32,34 @@ def dense_causal_prefill(q, k, v, cu_seqlens: list[int], scale: float) -> torch.
             v[s:e].transpose(0, 1).unsqueeze(0), is_causal=True, scale=scale, enable_gqa=gqa)
         out[s:e] = o.squeeze(0).transpose(0, 1)
     return out
+
+
+def dense_causal_prefill_lse(q, k, v, cu_seqlens: list[int], scale: float):
+    """As `dense_causal_prefill`, also returning the natural-log log-sum-exp of the scaled scores,
+    float32 [Hq, T] (what the prefill-tail kernel needs to merge the compact prefix in).  16-bit CUDA
+    activations go through torch's flash kernel, which reports it; anything else through plain
+    float32 matrix ops."""
+    T, Hq, _ = q.shape
+    out = torch.empty_like(q)
+    lse = torch.empty((Hq, T), dtype=torch.float32, device=q.device)
+    G = Hq // k.shape[1]
+    for i in range(len(cu_seqlens) - 1):
+        s, e = cu_seqlens[i], cu_seqlens[i + 1]
+        if e <= s:
+            continue
+        qq, kk, vv = (x[s:e].transpose(0, 1).unsqueeze(0) for x in (q, k, v))
+        if q.is_cuda and q.dtype in (torch.bfloat16, torch.float16):
+            if G > 1:
+                kk, vv = kk.repeat_interleave(G, dim=1), vv.repeat_interleave(G, dim=1)
+            res = torch.ops.aten._scaled_dot_product_flash_attention(qq, kk, vv, 0.0, True, False, scale=scale)
+            out[s:e] = res[0].squeeze(0).transpose(0, 1)
+            lse[:, s:e] = res[1].squeeze(0)[:, :e - s]
+            continue
+        sc = (qq.squeeze(0).float() @ kk.squeeze(0).float().repeat_interleave(G, dim=0).transpose(1, 2)) * scale
+        sc = sc.masked_fill(~torch.tril(torch.ones(e - s, e - s, dtype=torch.bool, device=q.device)), float("-inf"))
+        lse[:, s:e] = torch.logsumexp(sc, dim=-1)
+        out[s:e] = (torch.softmax(sc, dim=-1) @ vv.squeeze(0).float().repeat_interleave(G, dim=0)).transpose(0, 1).to(q.dtype)
+    return out, lse
 
 
 class Attention(nn.Module):
@@ -77,6 +105,20 @@ class Attention(nn.Module):
             cu = context.cu_seqlens_host
             if cu is None:
                 cu = context.cu_seqlens_q.tolist()
+            if context.compact_prefix_slots is not None:
+                # a chunk of a longer prompt: its own causal block, then the rows the spans already hold
+                m = context.streaming_pack_manager
+                with prof.cuda_phase("dense_prefill_attn"):
+                    out, lse = dense_causal_prefill_lse(q, k, v, cu, self.scale)
+                with prof.cuda_phase("prefix_attn"):
+                    l = self.layer_id
+                    return compact_prefix_attention(
+                        q, self.compact_k_cache, self.compact_v_cache,
+                        None if m.paged else m.layer_major_base_offsets[l], m.layer_major_live_counts[l],
+                        context.cu_seqlens_q, context.max_seqlen_q, out, lse, self.scale,
+                        seq_slots=context.compact_prefix_slots,
+                        block_tables=m.block_tables[l] if m.paged else None,
+                        k_scale=self.compact_k_scale, v_scale=self.compact_v_scale)
             with prof.cuda_phase("dense_prefill_attn"):
                 return dense_causal_prefill(q, k, v, cu, self.scale)
         if not context.compact_kv_enabled:

@@ -127,14 +127,23 @@ class LlamaAttention(nn.Module):
                 context.dms_layer_evictions[layer_id] = evict_mask
         if not fused:
             q, k = self.rotary_emb(positions, q, k)
-        if (context.is_prefill and context.streaming_pack_manager is not None
-                and context.streaming_pack_seq_ids and context.dms_capture_enabled):
+        pack = (context.is_prefill and context.streaming_pack_manager is not None
+                and context.streaming_pack_seq_ids and context.dms_capture_enabled)
+        chunked = pack and context.prefill_chunk_starts is not None
+        o = None
+        if chunked:
+            # the chunk attends to what the spans held BEFORE it is packed (expiry + append follow)
+            o = self.attn(q, k, v, compact_append_stored=fused, compact_q_rope=False, positions=positions,
+                          cos_sin_cache=cache)
+        if pack:
             with prof.cuda_phase("streaming_pack"):
                 context.streaming_pack_manager.streaming_pack_layer(
                     layer_id=layer_id, k=k, v=v, evict_mask=evict_mask, cu_seqlens_q=context.cu_seqlens_q,
-                    seq_ids=context.streaming_pack_seq_ids, window_size=context.streaming_pack_window_size)
-        o = self.attn(q, k, v, compact_append_stored=fused, compact_q_rope=False, positions=positions,
-                      cos_sin_cache=cache)
+                    seq_ids=context.streaming_pack_seq_ids, window_size=context.streaming_pack_window_size,
+                    chunk_starts=context.prefill_chunk_starts, remaining=context.prefill_chunk_remaining)
+        if o is None:
+            o = self.attn(q, k, v, compact_append_stored=fused, compact_q_rope=False, positions=positions,
+                          cos_sin_cache=cache)
         return self.o_proj(o.flatten(1, -1))
 
 

@@ -105,3 +105,48 @@ def test_nothing_admissible_and_nothing_running_raises():
     s.add(_seq(10))
     with pytest.raises(RuntimeError, match="no request fits"):
         s.schedule()
+
+
+def test_chunked_prefill_schedules_prompts_in_pieces():
+    """prefill_chunk_size: continuing prompts first, new ones while the token budget lasts; only the
+    chunk that ends a prompt yields a token; decode starts when no prompt is pending."""
+    pool = Pool(free=10_000)
+    cfg = SimpleNamespace(max_num_seqs=8, max_num_batched_tokens=100, eos=-1, prefill_chunk_size=64)
+    s = Scheduler(cfg, can_allocate=pool.can_allocate, admission_need=pool.need)
+    a, b = _seq(150), _seq(40)
+    s.add(a)
+    s.add(b)
+    batch, is_prefill = s.schedule()                     # a: 64 of 150; b: 36 left in the budget < 40 -> waits
+    assert is_prefill and batch == [a] and a.num_scheduled_tokens == 64
+    s.postprocess(batch, [7], True)
+    assert a.num_cached_tokens == 64 and a.num_completion_tokens == 0
+    batch, is_prefill = s.schedule()                     # a continues (64), b does not fit beside it (36 < 40)
+    assert is_prefill and batch == [a] and a.num_scheduled_tokens == 64
+    s.postprocess(batch, [7], True)
+    batch, is_prefill = s.schedule()                     # a's last 22 tokens + b's 40
+    assert is_prefill and batch == [a, b] and (a.num_scheduled_tokens, b.num_scheduled_tokens) == (22, 40)
+    s.postprocess(batch, [11, 12], True)
+    assert a.completion_token_ids == [11] and b.completion_token_ids == [12]
+    assert a.num_cached_tokens == a.num_tokens == 151
+    batch, is_prefill = s.schedule()
+    assert not is_prefill and batch == [a, b]
+    s.postprocess(batch, [1, 2], False)
+    assert a.is_finished and b.is_finished and s.is_finished()
+    with pytest.raises(ValueError):
+        Scheduler(SimpleNamespace(max_num_seqs=8, max_num_batched_tokens=100, eos=-1, prefill_chunk_size=128))
+
+
+def test_requeue_restarts_a_chunked_prompt():
+    pool = Pool(free=10_000)
+    cfg = SimpleNamespace(max_num_seqs=8, max_num_batched_tokens=100, eos=-1, prefill_chunk_size=64)
+    s = Scheduler(cfg, can_allocate=pool.can_allocate, admission_need=pool.need)
+    a, b = _seq(100), _seq(30)
+    s.add(a)
+    s.add(b)
+    batch, _ = s.schedule()
+    assert batch == [a, b]
+    s.postprocess(batch, [5, 6], True)                   # b is done prefilling, a is half way
+    batch, _ = s.schedule()
+    assert batch == [a]
+    s.requeue([a])                                       # its second chunk did not fit the pool
+    assert a.num_cached_tokens == 0 and a.status == SequenceStatus.WAITING and s.waiting[0] is a
