@@ -509,6 +509,33 @@ class CompactKVManager:
                 _lib.ptr(ks), _lib.ptr(vs),
                 n, Hk, D, int(window_size), status.data_ptr(), stream))
 
+    def trim_spans(self, seq_ids: list[int]) -> None:
+        """Contiguous spans only: gives back the part of every span that a chunked prefill reserved for
+        the worst case and did not fill -- each span shrinks to min(live + decode headroom, C) rows, the
+        size a one-pass prefill reserves (reference sizing: compact_kv.py:830-857).  One device read."""
+        if self.paged or not seq_ids:
+            return
+        states = [self.seq_states[sid] for sid in seq_ids if sid in self.seq_states]
+        if not states:
+            return
+        slots = self._slots_tensor(states).long()
+        live = self.layer_major_live_counts.index_select(1, slots).cpu()          # [L, n, Hk]
+        for i, st in enumerate(states):
+            new_cap = torch.zeros((self.num_layers, self.num_kv_heads), dtype=torch.int32)
+            for l in range(self.num_layers):
+                for h in range(self.num_kv_heads):
+                    r = st.host_ranges[l][h]
+                    if r is None:
+                        continue
+                    b, size = r
+                    want = max(min(int(live[l, i, h]) + int(st.decode_headroom), st.max_capacity_per_lh), 1)
+                    if want < size:
+                        self._free_range(l, b + want, size - want)
+                        st.host_ranges[l][h] = (b, want)
+                        size = want
+                    new_cap[l, h] = size
+            st.range_capacity.copy_(new_cap.to(self.device, non_blocking=True))
+
     # ------------------------------------------------------------------ expiry
     def apply_dms_evictions(self, seqs: list[Sequence], current_positions: list[int], *, window_size: int,
                             compact_k=None, compact_v=None, sync_stats: bool = True,

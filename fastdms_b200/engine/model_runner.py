@@ -219,7 +219,11 @@ class ModelRunner:
             with get_profiler().cuda_phase("model_forward_prefill"):
                 hidden = self.model(ids_t, pos_t)
             last = hidden[cu_t[1:].long() - 1]
-            return self.model.compute_logits(last)
+            logits = self.model.compute_logits(last)
+            if chunked:
+                # prompts that are now complete give back what the chunked reservation did not use
+                m.trim_spans([s.seq_id for s, rest, a in zip(seqs, remaining, starts) if rest == 0 and a > 0])
+            return logits
         finally:
             reset_context()
 
