@@ -127,8 +127,58 @@ __device__ __forceinline__ void pfx_stage_tile(const PrefixParams& p, int base, 
     }
 }
 
+// FP8 pools, software-pipelined: the bytes of the NEXT tile are fetched into registers (one 16-byte K
+// and V vector per thread and pass) while the warps compute on the tile in shared memory.
 template <int D>
-__global__ void __launch_bounds__(kPfxMaxWarps * 32) prefix_attention_kernel(PrefixParams p) {
+struct PfxFetch {
+    static constexpr int kPasses = (kPfxTile * (D / 16) + kPfxMaxWarps * 32 - 1) / (kPfxMaxWarps * 32);
+    uint4 k[kPasses], v[kPasses];
+};
+
+template <int D>
+__device__ __forceinline__ void pfx_fetch_tile(const PrefixParams& p, int base, const int32_t* bt, int live, int i0,
+                                               PfxFetch<D>& f, int tid, int nthreads) {
+    constexpr int VPR = D / 16;
+#pragma unroll
+    for (int j = 0; j < PfxFetch<D>::kPasses; ++j) {
+        const int x = tid + j * nthreads;
+        f.k[j] = make_uint4(0u, 0u, 0u, 0u);
+        f.v[j] = f.k[j];
+        if (x >= kPfxTile * VPR) continue;
+        const int r = x / VPR, c = x - r * VPR;
+        if (i0 + r >= live) continue;
+        const int64_t row = span_row(base, bt, i0 + r);
+        if (row >= 0 && row < p.pool_rows) {
+            f.k[j] = *(const uint4*)((const uint8_t*)p.k_pool + row * D + 16 * c);
+            f.v[j] = *(const uint4*)((const uint8_t*)p.v_pool + row * D + 16 * c);
+        } else if (p.dev_status) {
+            atomicOr(p.dev_status, FDMS_DEV_BAD_INDEX);
+        }
+    }
+}
+
+template <int D>
+__device__ __forceinline__ void pfx_commit_tile(const PfxFetch<D>& f, __half* Ks, __half* Vs, int tid, int nthreads) {
+    constexpr int LD = D + 8, VPR = D / 16;
+#pragma unroll
+    for (int j = 0; j < PfxFetch<D>::kPasses; ++j) {
+        const int x = tid + j * nthreads;
+        if (x >= kPfxTile * VPR) continue;
+        const int r = x / VPR, c = x - r * VPR;
+        uint4 lo, hi;
+        pfx_e4m3x4_to_f16x2x2(f.k[j].x, lo.x, lo.y); pfx_e4m3x4_to_f16x2x2(f.k[j].y, lo.z, lo.w);
+        pfx_e4m3x4_to_f16x2x2(f.k[j].z, hi.x, hi.y); pfx_e4m3x4_to_f16x2x2(f.k[j].w, hi.z, hi.w);
+        *(uint4*)(Ks + r * LD + 16 * c) = lo;
+        *(uint4*)(Ks + r * LD + 16 * c + 8) = hi;
+        pfx_e4m3x4_to_f16x2x2(f.v[j].x, lo.x, lo.y); pfx_e4m3x4_to_f16x2x2(f.v[j].y, lo.z, lo.w);
+        pfx_e4m3x4_to_f16x2x2(f.v[j].z, hi.x, hi.y); pfx_e4m3x4_to_f16x2x2(f.v[j].w, hi.z, hi.w);
+        *(uint4*)(Vs + r * LD + 16 * c) = lo;
+        *(uint4*)(Vs + r * LD + 16 * c + 8) = hi;
+    }
+}
+
+template <int D>
+__global__ void __launch_bounds__(kPfxMaxWarps * 32, D == 64 ? 2 : 1) prefix_attention_kernel(PrefixParams p) {
     constexpr int LD = D + 8, KS = D / 16, NT = D / 8;
     __shared__ __align__(16) __half Ks[kPfxTile * LD];
     __shared__ __align__(16) __half Vs[kPfxTile * LD];
@@ -149,7 +199,7 @@ __global__ void __launch_bounds__(kPfxMaxWarps * 32) prefix_attention_kernel(Pre
     }
     const int hq = h * p.group + warp % p.group;
     const int tq = q0 + (warp / p.group) * 16;            // first query token of this warp
-    const bool active = tq < T;
+    const bool active = warp < p.group * p.tiles_per_cta && tq < T;   // spare warps only help staging
     const int r0 = tq + g, r1 = tq + g + 8;               // the lane's two query rows
     const bool ok0 = active && r0 < T, ok1 = active && r1 < T;
 
@@ -169,10 +219,15 @@ __global__ void __launch_bounds__(kPfxMaxWarps * 32) prefix_attention_kernel(Pre
     for (int j = 0; j < NT; ++j) { o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.0f; }
     const int mat = lane >> 3, mrow = lane & 7;           // ldmatrix: this lane addresses row mrow of matrix mat
 
+    const bool fp8 = p.kv_dtype == FDMS_E4M3;
+    PfxFetch<D> nxt;
+    if (fp8) pfx_fetch_tile<D>(p, base, bt, live, 0, nxt, tid, nthreads);
     for (int i0 = 0; i0 < live; i0 += kPfxTile) {
         __syncthreads();                                  // the previous tile has been consumed
-        pfx_stage_tile<D>(p, base, bt, live, i0, Ks, Vs, tid, nthreads);
+        if (fp8) pfx_commit_tile<D>(nxt, Ks, Vs, tid, nthreads);
+        else pfx_stage_tile<D>(p, base, bt, live, i0, Ks, Vs, tid, nthreads);
         __syncthreads();
+        if (fp8 && i0 + kPfxTile < live) pfx_fetch_tile<D>(p, base, bt, live, i0 + kPfxTile, nxt, tid, nthreads);
         if (!active) continue;
         // ---- S = Q K^T for 64 span rows ----
         float sc[8][4];
@@ -322,7 +377,7 @@ extern "C" int32_t fdms_prefix_attention(
     p.scale = scale; p.dev_status = dev_status;
     const int q_per_cta = 16 * p.tiles_per_cta;
     dim3 grid((max_q_len + q_per_cta - 1) / q_per_cta, num_kv_heads, num_seqs);
-    const int threads = group * p.tiles_per_cta * 32;
+    const int threads = kPfxMaxWarps * 32;              // always 8 warps: the staging passes are sized for them
     if (head_dim == 64) prefix_attention_kernel<64><<<grid, threads, 0, (cudaStream_t)stream>>>(p);
     else prefix_attention_kernel<128><<<grid, threads, 0, (cudaStream_t)stream>>>(p);
     FDMS_CHECK_LAUNCH("prefix_attention_kernel");
