@@ -8,7 +8,8 @@ compact KV pool.  Shapes and arrival process follow the reference's serving-styl
 
 Requests are admitted by the scheduler when the token budget and the compact pool allow: charged
 their worst case (`--admission reserve`) or an estimate of what DMS keeps, with a retry when a
-prefill does not fit (`--admission optimistic`, contiguous spans).  Nothing that runs is preempted.
+prefill does not fit (`--admission optimistic`).  With `--paged`, a decode step that could run out of
+pages preempts the youngest request (it is prefilled again later); spans own their decode headroom.
 Whole prompts are prefilled in one step, or in `--prefill-chunk`-token pieces.  Prints one JSON line: request and token throughput, time to
 first token, decode step statistics, peak live rows of the pool, and a check that every page / span
 went back to the pool at the end."""
@@ -110,9 +111,10 @@ def run(args) -> dict:
         "pool_rows_per_layer": mgr.capacity_tokens, "pool_gib": mgr.capacity_tokens * elem_rows / (1 << 30),
         "peak_live_rows_layer0_sampled": peak_live, "admission": args.admission, "prefill_chunk": args.prefill_chunk,
         "admission_denied": int(mgr.admission_denied_count), "prefill_retries": int(engine.scheduler.prefill_retries),
+        "preemptions": int(engine.scheduler.preemptions),
         "pool_returned_clean": bool(pool_clean), "layout": "paged" if mgr.paged else "spans",
         "device_status": int(_lib.read_device_status(dev)),
-        "data": "synthetic: random-init bf16 weights, uniform random token ids; no preemption (requests wait for capacity)",
+        "data": "synthetic: random-init bf16 weights, uniform random token ids",
     }
 
 

@@ -133,10 +133,10 @@ class CompactKVManager:
         self.row_indirection = bool(row_indirection)
         if admission not in ("reserve", "optimistic"):
             raise ValueError(f"admission must be 'reserve' or 'optimistic', got {admission!r}")
-        if admission == "optimistic" and paged:
-            raise ValueError("optimistic admission needs contiguous spans: pages are taken during decode, "
-                             "where running out cannot be retried")
         self.admission = admission
+        # paged layout: host-side lower bound of the free pages of the fullest layer (None = unknown)
+        self._free_pages_lb: int | None = None
+        self.preemption_guard_refreshes = 0
         self.admission_keep_estimate = float(admission_keep_estimate)
         self.admission_window = int(admission_window)
         self.debug_checks = os.environ.get("FASTDMS_COMPACT_DEBUG_CHECKS") == "1"
@@ -292,21 +292,40 @@ class CompactKVManager:
 
     def admission_need(self, seq: Sequence) -> int:
         """Pool rows per layer a new sequence is charged at admission.  `reserve`: its worst case
-        (every token kept).  `optimistic` (contiguous spans only): an estimate of what the DMS
+        (every token kept).  `optimistic`: an estimate of what the DMS
         prefill keeps, `prompt * admission_keep_estimate + window`, plus the decode headroom; the
         engine retries a prefill that turns out not to fit."""
         rows = self._reservation_tokens(seq)
         if self.admission == "optimistic":
-            est = int(seq.num_prompt_tokens * self.admission_keep_estimate) + self.admission_window + int(seq.max_tokens) + 1
+            est = int(seq.num_tokens * self.admission_keep_estimate) + self.admission_window + \
+                max(int(seq.max_tokens) - seq.num_completion_tokens, 0) + 1
             rows = min(rows, max(est, 1))
         if self.paged:
             rows = ((rows + PAGE - 1) // PAGE) * PAGE
         return rows * self.num_kv_heads
 
+    def decode_pages_guaranteed(self, batch: int) -> bool:
+        """Paged layout: True when every span of a decode batch of `batch` sequences can take a new
+        page in this step (the worst case: all of them cross a page boundary at once) in every layer.
+        Works on a host-side lower bound of the free pages that is decremented by that worst case per
+        step and refreshed from the device only when it runs low, so a roomy pool costs no
+        synchronisation.  Contiguous spans own their decode headroom: always True."""
+        if not self.paged:
+            return True
+        need = batch * self.num_kv_heads
+        if self._free_pages_lb is None or self._free_pages_lb < need:
+            self._free_pages_lb = int(self.free_page_counts.min().item())
+            self.preemption_guard_refreshes += 1
+        if self._free_pages_lb < need:
+            return False
+        self._free_pages_lb -= need
+        return True
+
     def admission_free(self) -> int:
         """Free pool rows in the fullest layer."""
         if self.paged:
-            return int(self.free_page_counts.min().item()) * PAGE
+            self._free_pages_lb = int(self.free_page_counts.min().item())
+            return self._free_pages_lb * PAGE
         return min(self.free_tokens_in_layer(l) for l in range(self.num_layers))
 
     def can_allocate(self, seq: Sequence, pending_rows: int = 0) -> bool:
@@ -437,6 +456,7 @@ class CompactKVManager:
         slots_t = self._slots_tensor(states)
         chunked = chunk_starts is not None
         prior = starts_t = None
+        self._free_pages_lb = None                       # a prefill takes pages: the host bound is stale
         if chunked:
             if len(chunk_starts) != n or remaining is None or len(remaining) != n:
                 raise ValueError("chunk_starts / remaining need one entry per sequence")

@@ -57,6 +57,12 @@ class LLMEngine:
                 return [], 0
             self.scheduler.prefill_succeeded()
         else:
+            mgr = self.model_runner.compact_kv_manager
+            while not mgr.decode_pages_guaranteed(len(seqs)):
+                victim = self.scheduler.preempt_youngest(seqs)
+                seqs.remove(victim)
+                self.model_runner.free_compact([victim.seq_id])
+            num_tokens = -len(seqs)
             token_ids = self.model_runner.run(seqs, False)
         self.scheduler.postprocess(seqs, token_ids, is_prefill)
         freed = self.scheduler.consume_freed_seq_ids()

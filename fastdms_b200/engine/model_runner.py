@@ -220,6 +220,11 @@ class ModelRunner:
                 hidden = self.model(ids_t, pos_t)
             last = hidden[cu_t[1:].long() - 1]
             logits = self.model.compute_logits(last)
+            if m.paged and m.admission == "optimistic":
+                # pages are popped on the device: a stack that ran dry shows in the status word
+                from fastdms_b200 import _lib
+                if _lib.read_device_status(dev) & _lib.DEV_BAD_INDEX:
+                    raise RuntimeError("compact KV capacity exhausted: the page pool ran dry during a prefill")
             if chunked:
                 # prompts that are now complete give back what the chunked reservation did not use
                 m.trim_spans([s.seq_id for s, rest, a in zip(seqs, remaining, starts) if rest == 0 and a > 0])

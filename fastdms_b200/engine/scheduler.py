@@ -11,8 +11,11 @@ Two admission modes (the manager's `admission`):
     fit, the engine releases what it had taken and calls `requeue`: the requests go back to the front
     of the queue, the next prefill batch is at most half as large, and while requests are running no
     new prefill is tried until one of them finishes (its spans come back).  Running requests own
-    their spans including the decode headroom, so decode itself never runs out: nothing that has
-    started is ever preempted.
+    their spans including the decode headroom, so decode itself never runs out.  With the paged
+    layout pages are taken during decode: before a decode step the engine asks the manager whether every
+    span could take a page (`decode_pages_guaranteed`); if not, `preempt_youngest` sends the request
+    that started last back to the queue (preempt-by-recompute: it is prefilled again later over prompt
+    + generated tokens) until the step is safe.
 
 With `prefill_chunk_size` set, a prompt enters the pool in chunks of that many tokens (an extension:
 the reference prefills in one pass).  A step then carries the next chunk of every request whose
@@ -39,6 +42,7 @@ class Scheduler:
         self.prefill_batch_limit: int | None = None     # set after a prefill that did not fit
         self.hold_prefill = False                        # wait for a running request to finish first
         self.prefill_retries = 0
+        self.preemptions = 0
         self.prefill_chunk_size = getattr(config, "prefill_chunk_size", None) or None
         if self.prefill_chunk_size is not None and not 0 < self.prefill_chunk_size <= self.max_num_batched_tokens:
             raise ValueError("prefill_chunk_size must be positive and at most max_num_batched_tokens")
@@ -59,7 +63,7 @@ class Scheduler:
         continuing: list[Sequence] = []
         if chunk:
             for seq in self.running:
-                left = seq.num_prompt_tokens - seq.num_cached_tokens
+                left = seq.num_tokens - seq.num_cached_tokens
                 if left <= 0:
                     continue
                 n = min(chunk, left)
@@ -108,6 +112,23 @@ class Scheduler:
         else:
             self.hold_prefill = True
 
+    def preempt_youngest(self, batch: list[Sequence]) -> Sequence:
+        """Preempt-by-recompute (paged layout, when a decode step could run out of pages): the request
+        that started last leaves the running set, its pages are freed by the caller, and it goes to the
+        front of the queue to be prefilled again later over prompt + generated tokens."""
+        if len(batch) <= 1:
+            raise RuntimeError("the compact KV pool cannot hold even one running request")
+        seq = batch[-1]
+        self.running.remove(seq)
+        seq.status = SequenceStatus.WAITING
+        seq.num_scheduled_tokens = 0
+        seq.num_cached_tokens = 0
+        seq.num_preemptions += 1
+        self.waiting.appendleft(seq)
+        self.hold_prefill = True                     # wait for a running request to finish before retrying
+        self.preemptions += 1
+        return seq
+
     def prefill_succeeded(self) -> None:
         self.prefill_batch_limit = None
 
@@ -115,7 +136,7 @@ class Scheduler:
         for seq, token_id in zip(seqs, token_ids):
             if is_prefill and self.prefill_chunk_size:
                 seq.num_cached_tokens += seq.num_scheduled_tokens
-                if seq.num_cached_tokens < seq.num_prompt_tokens:      # more of the prompt to come: no token yet
+                if seq.num_cached_tokens < seq.num_tokens:             # more of the prompt to come: no token yet
                     seq.num_scheduled_tokens = 0
                     continue
             seq.append_token(token_id)

@@ -196,5 +196,47 @@ def test_optimistic_admission_retries_prefills_that_do_not_fit(golden):
     assert mgr.free_ranges_per_layer == [[(0, mgr.capacity_tokens)]] * mgr.num_layers
     assert sorted(mgr.free_active_slots) == list(range(mgr.max_active_seqs))
     assert _lib.read_device_status("cuda:0") == 0
-    with pytest.raises(ValueError):
-        engine(compact_kv_capacity_tokens=600, compact_kv_admission="optimistic", compact_kv_paged=True)
+
+
+def test_paged_pool_preempts_by_recompute_when_decode_would_run_dry(golden):
+    """Paged layout, admission by estimate, a pool smaller than what the running requests grow to (a
+    window longer than any request, so nothing is dropped and every decoded token adds a row): before a decode step that could not give every span
+    a page the youngest request is preempted, its pages go back, and it is prefilled again later over
+    prompt + generated tokens.  Every request completes with the tokens of an unconstrained engine and
+    the page stacks end up full."""
+    import make_golden_model as G
+    from fastdms_b200 import LLM, SamplingParams, _lib
+    from fastdms_b200.layers import rotary_embedding
+
+    def engine(window=4096, **kw):
+        rotary_embedding._ROPE_CACHE.clear()
+        return LLM("config0-tiny-llama", hf_config=dict(G.MODEL_CFG), random_init_seed=G.SEED, dtype="float32",
+                   kv_cache_dtype="float32", max_model_len=1024, max_num_seqs=8, max_num_batched_tokens=8192,
+                   dms_window_size=window, dms_alpha_scale=G.ALPHA_SCALE, dms_alpha_offset=G.ALPHA_OFFSET,
+                   compact_kv_paged=True, device="cuda:0", **kw)
+
+    prompts = G.make_prompts()                                       # 37 / 128 / 200 / 511 tokens
+    sp = SamplingParams(temperature=0.0, max_tokens=40, ignore_eos=True)
+    want = [r["token_ids"] for r in engine(compact_kv_capacity_tokens=65536).generate(prompts, sp)]
+    # the prompts take 112 of the 125 pages of a layer, the finished requests would need 132
+    llm = engine(compact_kv_capacity_tokens=2000, compact_kv_admission="optimistic", compact_kv_admission_keep_estimate=0.02)
+    got = [r["token_ids"] for r in llm.generate(prompts, sp)]
+    mgr = llm.model_runner.compact_kv_manager
+    assert llm.scheduler.preemptions > 0, "the test is meant to exercise preemption"
+    assert [len(t) for t in got] == [40] * len(prompts)
+    assert got == want
+    assert mgr.free_page_counts.tolist() == [mgr.pages_per_layer] * mgr.num_layers
+    assert sorted(mgr.free_active_slots) == list(range(mgr.max_active_seqs))
+    assert _lib.read_device_status("cuda:0") == 0
+    # the reference window, two long prompts admitted together by a low estimate into a pool of 15 pages
+    # that holds only one of them (about 11 pages each): the prefill itself runs dry, is released and retried
+    prompts = [G.make_prompts()[3], G.make_prompts()[3][::-1]]
+    sp = SamplingParams(temperature=0.0, max_tokens=8, ignore_eos=True)
+    want = [r["token_ids"] for r in engine(G.WINDOW, compact_kv_capacity_tokens=65536).generate(prompts, sp)]
+    llm = engine(G.WINDOW, compact_kv_capacity_tokens=240, compact_kv_admission="optimistic",
+                 compact_kv_admission_keep_estimate=0.0)
+    got = [r["token_ids"] for r in llm.generate(prompts, sp)]
+    mgr = llm.model_runner.compact_kv_manager
+    assert llm.scheduler.prefill_retries > 0 and got == want
+    assert mgr.free_page_counts.tolist() == [mgr.pages_per_layer] * mgr.num_layers
+    assert _lib.read_device_status("cuda:0") == 0

@@ -150,3 +150,29 @@ def test_requeue_restarts_a_chunked_prompt():
     assert batch == [a]
     s.requeue([a])                                       # its second chunk did not fit the pool
     assert a.num_cached_tokens == 0 and a.status == SequenceStatus.WAITING and s.waiting[0] is a
+
+
+def test_preempt_youngest_requeues_for_recompute():
+    pool = Pool(free=10_000)
+    s = _sched(pool)
+    a, b, c = _seq(10, max_tokens=5), _seq(20, max_tokens=5), _seq(30, max_tokens=5)
+    for x in (a, b, c):
+        s.add(x)
+    batch, _ = s.schedule()
+    s.postprocess(batch, [1, 2, 3], True)
+    batch, is_prefill = s.schedule()
+    assert not is_prefill and batch == [a, b, c]
+    victim = s.preempt_youngest(batch)
+    assert victim is c and c.status == SequenceStatus.WAITING and s.waiting[0] is c
+    assert c.num_cached_tokens == 0 and c.num_preemptions == 1 and c.num_tokens == 31
+    assert list(s.running) == [a, b] and s.hold_prefill
+    batch, is_prefill = s.schedule()                     # held while others run
+    assert not is_prefill and batch == [a, b]
+    for _ in range(4):
+        batch, _ = s.schedule()
+        s.postprocess(batch, [4] * len(batch), False)
+    assert a.is_finished and b.is_finished
+    batch, is_prefill = s.schedule()                     # capacity came back: prompt + generated token again
+    assert is_prefill and batch == [c] and c.num_scheduled_tokens == 31
+    with pytest.raises(RuntimeError):
+        s.preempt_youngest([c])
