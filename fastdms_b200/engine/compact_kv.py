@@ -321,6 +321,19 @@ class CompactKVManager:
         self._free_pages_lb -= need
         return True
 
+    def prefill_pages_guaranteed(self, tokens: int, num_seqs: int) -> bool:
+        """Paged layout, chunked prefill: True when a prefill step of `tokens` tokens over `num_seqs`
+        sequences finds its pages in every layer even if every token is kept (one partly filled page
+        per span on top).  Same host-side bound as `decode_pages_guaranteed`; a check only -- the pack
+        marks the bound stale, so it is read again before the next step."""
+        if not self.paged:
+            return True
+        need = ((int(tokens) + PAGE - 1) // PAGE + int(num_seqs)) * self.num_kv_heads
+        if self._free_pages_lb is None or self._free_pages_lb < need:
+            self._free_pages_lb = int(self.free_page_counts.min().item())
+            self.preemption_guard_refreshes += 1
+        return self._free_pages_lb >= need
+
     def admission_free(self) -> int:
         """Free pool rows in the fullest layer."""
         if self.paged:

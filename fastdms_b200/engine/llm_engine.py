@@ -20,7 +20,9 @@ class LLMEngine:
         self.tokenizer = None
         config.eos = int(getattr(config.hf_config, "eos_token_id", -1) or -1)
         mgr = self.model_runner.compact_kv_manager
-        self.scheduler = Scheduler(config, can_allocate=mgr.can_allocate, admission_need=mgr.admission_need)
+        guard = mgr.prefill_pages_guaranteed if (mgr.paged and config.prefill_chunk_size) else None
+        self.scheduler = Scheduler(config, can_allocate=mgr.can_allocate, admission_need=mgr.admission_need,
+                                   prefill_guard=guard)
         self.last_decode_tok_s = 0.0
         self.last_prefill_tok_s = 0.0
 
@@ -44,6 +46,9 @@ class LLMEngine:
 
     def step(self):
         seqs, is_prefill = self.scheduler.schedule()
+        if not seqs:                      # a partly prefilled request was sent back to free its pages
+            self.model_runner.free_compact(self.scheduler.consume_freed_seq_ids())
+            return [], 0
         num_tokens = sum(seq.num_scheduled_tokens for seq in seqs) if is_prefill else -len(seqs)
         if is_prefill:
             try:

@@ -30,12 +30,15 @@ from fastdms_b200.engine.sequence import Sequence, SequenceStatus
 
 
 class Scheduler:
-    def __init__(self, config, can_allocate=None, admission_need=None):
+    def __init__(self, config, can_allocate=None, admission_need=None, prefill_guard=None):
         self.max_num_seqs = config.max_num_seqs
         self.max_num_batched_tokens = config.max_num_batched_tokens
         self.eos = config.eos
         self.can_allocate = can_allocate or (lambda seq, pending=0: True)
         self.admission_need = admission_need or (lambda seq: 0)
+        # chunked prefill over a paged pool: prefill_guard(tokens, seqs) says whether a prefill step of
+        # that size is certain to find its pages (None: prefills are tried and retried instead)
+        self.prefill_guard = prefill_guard
         self.waiting: deque[Sequence] = deque()
         self.running: deque[Sequence] = deque()
         self.freed_seq_ids: list[int] = []
@@ -61,6 +64,9 @@ class Scheduler:
         hold = self.hold_prefill and bool(self.running)
         chunk = self.prefill_chunk_size
         continuing: list[Sequence] = []
+        guard = self.prefill_guard if chunk else None
+        taken = 0                                        # tokens of this prefill step so far
+        blocked = False                                  # the page guard stopped the batch from growing
         if chunk:
             for seq in self.running:
                 left = seq.num_tokens - seq.num_cached_tokens
@@ -69,9 +75,14 @@ class Scheduler:
                 n = min(chunk, left)
                 if n > budget:
                     break
+                if guard is not None and not guard(taken + n, len(continuing) + 1):
+                    blocked = True
+                    break
                 seq.num_scheduled_tokens = n
                 continuing.append(seq)
                 budget -= n
+                taken += n
+        hold = hold or blocked
         while (not hold and self.waiting and len(scheduled) < limit
                and len(self.running) + len(scheduled) < self.max_num_seqs):
             seq = self.waiting[0]
@@ -80,6 +91,10 @@ class Scheduler:
                 raise RuntimeError(f"prompt of {n} tokens exceeds max_num_batched_tokens={self.max_num_batched_tokens}")
             if n > budget or not self.can_allocate(seq, pending):
                 break
+            if guard is not None and not guard(taken + n, len(continuing) + len(scheduled) + 1):
+                blocked = True
+                break
+            taken += n
             pending += self.admission_need(seq)
             seq.num_scheduled_tokens = n
             seq.status = SequenceStatus.RUNNING
@@ -91,10 +106,29 @@ class Scheduler:
             return continuing + scheduled, True
         if not self.running:
             raise RuntimeError("no request fits the compact KV pool / token budget")
-        batch = list(self.running)[: self.max_num_seqs]
+        batch = [seq for seq in self.running if not chunk or seq.num_cached_tokens >= seq.num_tokens][: self.max_num_seqs]
+        if not batch:
+            # only partly prefilled prompts are running and the pool cannot take another chunk: the one
+            # that started last gives its pages back (the caller frees them) and waits
+            partly = list(self.running)
+            if len(partly) <= 1:
+                raise RuntimeError("the compact KV pool cannot take the next chunk of a lone request")
+            self._send_back(partly[-1])
+            self.freed_seq_ids.append(partly[-1].seq_id)
+            return [], True
         for seq in batch:
             seq.num_scheduled_tokens = 1
         return batch, False
+
+    def _send_back(self, seq: Sequence) -> None:
+        self.running.remove(seq)
+        seq.status = SequenceStatus.WAITING
+        seq.num_scheduled_tokens = 0
+        seq.num_cached_tokens = 0
+        seq.num_preemptions += 1
+        self.waiting.appendleft(seq)
+        self.hold_prefill = True                     # wait for a running request to finish before retrying
+        self.preemptions += 1
 
     def requeue(self, seqs: list[Sequence]) -> None:
         """A prefill of `seqs` did not fit: put them back at the front, in order, and back off."""
@@ -119,14 +153,7 @@ class Scheduler:
         if len(batch) <= 1:
             raise RuntimeError("the compact KV pool cannot hold even one running request")
         seq = batch[-1]
-        self.running.remove(seq)
-        seq.status = SequenceStatus.WAITING
-        seq.num_scheduled_tokens = 0
-        seq.num_cached_tokens = 0
-        seq.num_preemptions += 1
-        self.waiting.appendleft(seq)
-        self.hold_prefill = True                     # wait for a running request to finish before retrying
-        self.preemptions += 1
+        self._send_back(seq)
         return seq
 
     def prefill_succeeded(self) -> None:
