@@ -28,6 +28,14 @@ void clear_error();
             return ::fdms::fail(FDMS_E_CUDA, "%s launch failed: %s", (name), cudaGetErrorString(e__)); \
     } while (0)
 
+// Wraps a runtime call that returns cudaError_t.
+#define FDMS_CUDA_OK(expr)                                                                   \
+    do {                                                                                     \
+        cudaError_t e__ = (expr);                                                            \
+        if (e__ != cudaSuccess)                                                              \
+            return ::fdms::fail(FDMS_E_CUDA, "%s failed: %s", #expr, cudaGetErrorString(e__)); \
+    } while (0)
+
 __host__ __device__ inline int dtype_size(int dt) {
     return dt == FDMS_F32 ? 4 : (dt == FDMS_E4M3 ? 1 : 2);
 }
@@ -96,6 +104,37 @@ inline DecisionRule make_rule(double alpha_scale, double alpha_offset) {
 __device__ __forceinline__ int64_t span_row(int32_t base, const int32_t* bt, int32_t i) {
     if (bt == nullptr) return (int64_t)base + i;
     return (int64_t)bt[i >> 4] * 16 + (i & 15);
+}
+
+
+// Programmatic dependent launch for chains of small kernels.  `pdl_trigger` lets the next kernel of the
+// stream (if it was launched with `launch_chained`) start its preamble while this one runs;
+// `pdl_wait` returns once the preceding kernel has completed and its writes are visible (at once when
+// the launch was an ordinary one).  Code before `pdl_wait` may only touch memory that no kernel of
+// the stream writes (weights).
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_chained(void (*kernel)(KArgs...), dim3 grid, dim3 block, cudaStream_t stream, bool chained,
+                                  Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = 0;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = chained ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+
+// FDMS_PDL_CHAIN=0 launches the decoder-block helpers (norm, activation, decode-sized linear) as ordinary kernels.
+inline bool chain_launches() {
+    static const bool on = [] { const char* e = getenv("FDMS_PDL_CHAIN"); return !(e && e[0] == '0'); }();
+    return on;
 }
 
 }  // namespace fdms

@@ -47,6 +47,8 @@ __global__ void __launch_bounds__(kNormThreads) rmsnorm_kernel(
     uint16_t* out, int64_t out_stride, uint16_t* residual_out, int64_t res_out_stride, int dt, int64_t rows, int hidden,
     float eps, int T) {
     __shared__ float s_part[kNormThreads / 32];
+    pdl_trigger();                                         // the next kernel may start streaming its weights
+    pdl_wait();                                            // x / residual come from the preceding kernel
     const int tid = threadIdx.x;
     const int grp = tid / T, lig = tid - grp * T;          // group index, lane in group
     const int64_t row = (int64_t)blockIdx.x * (kNormThreads / T) + grp;
@@ -98,6 +100,8 @@ __global__ void silu_mul_kernel(const uint16_t* x, int64_t x_stride, uint16_t* o
                                 int64_t rows, int n) {
     const int nvec = n >> 3;
     const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    pdl_trigger();
+    pdl_wait();
     if (i >= rows * nvec) return;
     const int64_t r = i / nvec;
     const int c = (int)(i - r * nvec);
@@ -139,9 +143,10 @@ extern "C" int32_t fdms_rmsnorm(
     const int rows_per_block = kNormThreads / T;
     const int64_t blocks = (rows + rows_per_block - 1) / rows_per_block;
     FDMS_REQUIRE(blocks < (1ll << 31), FDMS_E_CAPACITY, "fdms_rmsnorm: too many rows");
-    rmsnorm_kernel<<<(unsigned)blocks, kNormThreads, 0, (cudaStream_t)stream>>>(
+    FDMS_CUDA_OK(launch_chained(
+        rmsnorm_kernel, dim3((unsigned)blocks), dim3(kNormThreads), (cudaStream_t)stream, chain_launches(),
         (const uint16_t*)x, x_row_stride, (const uint16_t*)residual, residual_row_stride, (const uint16_t*)weight,
-        (uint16_t*)out, out_row_stride, (uint16_t*)residual_out, residual_out_row_stride, dtype, rows, hidden, eps, T);
+        (uint16_t*)out, out_row_stride, (uint16_t*)residual_out, residual_out_row_stride, (int)dtype, rows, (int)hidden, eps, T));
     FDMS_CHECK_LAUNCH("rmsnorm_kernel");
     return FDMS_OK;
 }
@@ -158,8 +163,8 @@ extern "C" int32_t fdms_silu_and_mul(const void* x, int64_t x_row_stride, void* 
     const int64_t total = rows * (n / 8);
     const int64_t blocks = (total + 255) / 256;
     FDMS_REQUIRE(blocks < (1ll << 31), FDMS_E_CAPACITY, "fdms_silu_and_mul: too many elements");
-    silu_mul_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>((const uint16_t*)x, x_row_stride, (uint16_t*)out,
-                                                                         out_row_stride, dtype, rows, n);
+    FDMS_CUDA_OK(launch_chained(silu_mul_kernel, dim3((unsigned)blocks), dim3(256), (cudaStream_t)stream, chain_launches(),
+                                (const uint16_t*)x, x_row_stride, (uint16_t*)out, out_row_stride, (int)dtype, rows, (int)n));
     FDMS_CHECK_LAUNCH("silu_mul_kernel");
     return FDMS_OK;
 }

@@ -41,7 +41,8 @@ class VocabParallelEmbedding(nn.Module):
 
 class ParallelLMHead(VocabParallelEmbedding):
     def forward(self, x: torch.Tensor) -> torch.Tensor:
-        logits = F.linear(x, self.weight)
+        from fastdms_b200.layers.linear import linear
+        logits = linear(x, self.weight)
         if self.tp_size > 1:
             parts = [torch.empty_like(logits) for _ in range(self.tp_size)]
             dist.all_gather(parts, logits)

@@ -1,4 +1,6 @@
-"""Tensor-parallel linear layers (bf16/fp32 weights, torch GEMMs).
+"""Tensor-parallel linear layers (bf16/fp32 weights; torch GEMMs, and for decode-sized inputs of at
+most 8 rows the library's weight-streaming kernel `fdms_linear_decode`, `FDMS_DECODE_LINEAR=0` turns
+it off).
 
 Same class names, parameter layout and `weight_loader` protocol as the reference's
 `fastdms/layers/linear.py` (:946-1048), so checkpoints load the same way: QKV and gate/up are
@@ -8,10 +10,37 @@ compact-DMS decode path and are not provided.
 """
 from __future__ import annotations
 
+import os
+
 import torch
 import torch.distributed as dist
 import torch.nn.functional as F
 from torch import nn
+
+from fastdms_b200 import _lib
+
+_DECODE_LINEAR = os.environ.get("FDMS_DECODE_LINEAR", "1") != "0"
+
+
+def linear(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None = None) -> torch.Tensor:
+    """`F.linear`, except that 16-bit CUDA inputs of at most 8 rows go through one launch of
+    `fdms_linear_decode` (weights streamed once, f32 accumulation) when the shapes allow it; very wide
+    outputs (the LM head) stay on the library GEMM, which streams them faster."""
+    if (_DECODE_LINEAR and x.is_cuda and x.dtype in (torch.bfloat16, torch.float16) and weight.dtype == x.dtype
+            and x.dim() == 2 and 0 < x.shape[0] <= 8 and x.stride(1) == 1 and weight.is_contiguous()
+            and weight.shape[0] % 16 == 0 and weight.shape[0] < 65536 and weight.shape[1] % 2048 == 0 and (bias is None or bias.dtype == x.dtype)
+            and x.data_ptr() % 16 == 0 and (x.stride(0) * 2) % 16 == 0 and weight.data_ptr() % 16 == 0
+            and not torch.is_grad_enabled()):
+        rows, n = x.shape[0], weight.shape[0]
+        y = torch.empty((rows, n), dtype=x.dtype, device=x.device)
+        with torch.cuda.device(x.device):
+            rc = _lib.lib().fdms_linear_decode(
+                x.data_ptr(), x.stride(0), weight.data_ptr(), weight.stride(0),
+                bias.data_ptr() if bias is not None else None, y.data_ptr(), y.stride(0),
+                _lib.dtype_code(x.dtype), rows, n, weight.shape[1], _lib.stream_ptr(x.device))
+        _lib.check(rc)
+        return y
+    return F.linear(x, weight, bias)
 
 
 _REPLICA_MODE = False
@@ -51,7 +80,7 @@ class LinearBase(nn.Module):
             self.register_parameter("bias", None)
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
-        return F.linear(x, self.weight, self.bias)
+        return linear(x, self.weight, self.bias)
 
 
 class ReplicatedLinear(LinearBase):
@@ -110,7 +139,7 @@ class RowParallelLinear(LinearBase):
         param.data.copy_(loaded_weight.narrow(1, self.tp_rank * shard, shard))
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
-        y = F.linear(x, self.weight, self.bias if self.tp_rank == 0 else None)
+        y = linear(x, self.weight, self.bias if self.tp_rank == 0 else None)
         if self.tp_size > 1:
             from fastdms_b200.layers.peer_allreduce import tp_all_reduce_
             tp_all_reduce_(y)

@@ -372,6 +372,16 @@ int32_t fdms_rmsnorm(
 int32_t fdms_silu_and_mul(const void* x, int64_t x_row_stride, void* out, int64_t out_row_stride,
                           int32_t dtype, int64_t rows, int32_t n, void* stream);
 
+/* Decode-sized linear layer: y[rows, out] = x[rows, in] * weight[out, in]^T (+ bias), rows <= 8, the
+ * weight streamed once from HBM (the reference calls F.linear -> cuBLAS for qkv_proj, o_proj,
+ * gate_up_proj, down_proj and the LM head, fastdms/layers/linear.py:635-662, 1044-1048,
+ * fastdms/layers/embed_head.py).  dtype FDMS_BF16 / FDMS_F16 for x, weight, bias and y; f32
+ * accumulation, one rounding at the end; row strides in elements; out % 16 == 0, in % 2048 == 0,
+ * x and weight rows 16-byte aligned.  bias may be NULL. */
+int32_t fdms_linear_decode(const void* x, int64_t x_row_stride, const void* weight, int64_t w_row_stride,
+                           const void* bias, void* y, int64_t y_row_stride, int32_t dtype, int32_t rows,
+                           int32_t out_features, int32_t in_features, void* stream);
+
 /* Greedy head: out[r] = index of the largest of x[r, 0..n) -- `logits.argmax(dim=-1)` of the
  * temperature-0 path (fastdms/engine/model_runner.py:1147-1151; the reference fuses it for one
  * sequence only, fastdms/layers/embed_head.py:491-543).  Lowest index on ties, a NaN counts as the

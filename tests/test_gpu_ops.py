@@ -578,3 +578,31 @@ def test_peer_allreduce_kernel_with_a_staged_peer_and_with_a_silent_one(dev):
     with pytest.raises(RuntimeError):
         _lib.check(lib.fdms_allreduce_oneshot(ptrs.data_ptr(), 0, 2, max_bytes, x0.data_ptr(), out.data_ptr(), 1 << 20, _lib.F32,
                                               None, _lib.stream_ptr(dev)))
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("rows,n,k,bias", [(8, 3072, 2048, True), (8, 2048, 2048, False), (8, 16384, 2048, False),
+                                           (8, 2048, 8192, False), (1, 128256, 2048, False), (5, 6144, 4096, True),
+                                           (3, 48, 2048, True)])
+def test_decode_linear_kernel_matches_float32_reference(dev, dtype, rows, n, k, bias):
+    """Weight-streaming linear layer for <= 8 rows against x @ W^T (+ b) in float32 (the reference
+    calls F.linear, layers/linear.py:1044-1048): one rounding of the 16-bit output type."""
+    from fastdms_b200.layers.linear import linear
+    g = torch.Generator(device=dev).manual_seed(rows * 7 + n + k)
+    x = torch.randn((rows, k), device=dev, generator=g).to(dtype)
+    w = (torch.randn((n, k), device=dev, generator=g) * k ** -0.5).to(dtype)
+    b = torch.randn((n,), device=dev, generator=g).to(dtype) if bias else None
+    with torch.inference_mode():
+        y = linear(x, w, b)
+        # rows of a wider buffer (row stride != k)
+        wide = torch.randn((rows, k + 64), device=dev, generator=g).to(dtype)
+        y2 = linear(wide[:, 8:8 + k], w, b)
+    ref = x.float() @ w.float().t() + (b.float() if bias else 0.0)
+    ref2 = wide[:, 8:8 + k].float() @ w.float().t() + (b.float() if bias else 0.0)
+    eps = 2.0 ** -8 if dtype == torch.bfloat16 else 2.0 ** -11
+    assert y.shape == (rows, n) and y.dtype == dtype
+    assert ((y.float() - ref).abs() <= eps * ref.abs() + 1e-3).all()
+    assert ((y2.float() - ref2).abs() <= eps * ref2.abs() + 1e-3).all()
+    # the library kernel is what ran: torch's own GEMM rounds an f32 accumulation too, so the two agree to one ulp
+    t = torch.nn.functional.linear(x, w, b)
+    assert ((y.float() - t.float()).abs() <= 2 * eps * ref.abs() + 2e-3).all()
