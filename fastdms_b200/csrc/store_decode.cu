@@ -63,7 +63,7 @@ __global__ void store_decode_kernel(StoreParams p) {
     const int64_t v0 = (int64_t)b * p.v_sb + (int64_t)h * p.v_sh;
     const bool rot_q = p.do_rope && p.store_q;
 
-    // ---- round 1: independent loads ----
+    // ---- phase 1: independent loads ----
     int64_t pos = p.do_rope ? p.positions[b] : 0;
     if (pos < 0 || (p.do_rope && pos >= p.cs_rows)) {           // positions index the cos/sin table: checked, not trusted
         if (lane == 0 && p.dev_status) atomicOr(p.dev_status, FDMS_DEV_BAD_INDEX);
@@ -89,7 +89,7 @@ __global__ void store_decode_kernel(StoreParams p) {
             qx[g][n][1] = qin ? load_as_float(p.q, q0 + (int64_t)g * p.q_sh + half + i, adt) : 0.0f;
         }
     }
-    // ---- round 2: cos / sin of this sequence's position ----
+    // ---- phase 2: cos / sin of this sequence's position ----
     float cs[NP][2];
 #pragma unroll
     for (int n = 0; n < NP; ++n) {

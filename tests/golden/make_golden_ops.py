@@ -404,7 +404,7 @@ def gen_expiry_random(ref, out: dict) -> None:
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", required=True, help="path of a FastDMS checkout (the directory that holds the fastdms package)")
     args = ap.parse_args()
     os.environ.setdefault("TORCHDYNAMO_DISABLE", "1")
     os.environ.setdefault("FASTDMS_DMS_EXPIRY_TRITON", "0")
