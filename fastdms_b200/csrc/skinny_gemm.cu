@@ -27,11 +27,49 @@ __device__ __forceinline__ void sg_mma(float (&c)[4], uint32_t a0, uint32_t a1, 
                      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-template <bool BF16, int NT>
+// Eight consecutive 16-bit elements <-> float.
+template <bool BF16>
+__device__ __forceinline__ void sg_unpack8(const uint4& v, float (&f)[8]) {
+    const uint32_t u[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        if (BF16) {
+            f[2 * i] = __uint_as_float(u[i] << 16);
+            f[2 * i + 1] = __uint_as_float(u[i] & 0xffff0000u);
+        } else {
+            const __half2 h = *(const __half2*)&u[i];
+            f[2 * i] = __low2float(h);
+            f[2 * i + 1] = __high2float(h);
+        }
+    }
+}
+template <bool BF16>
+__device__ __forceinline__ uint4 sg_pack8(const float (&f)[8]) {
+    uint32_t u[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        if (BF16) { const __nv_bfloat162 b = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]); u[i] = *(const uint32_t*)&b; }
+        else { const __half2 h = __floats2half2_rn(f[2 * i], f[2 * i + 1]); u[i] = *(const uint32_t*)&h; }
+    }
+    return make_uint4(u[0], u[1], u[2], u[3]);
+}
+
+// Arguments of the fused RMSNorm (+ residual add) in front of the linear layer (NORM = true):
+//   xf = float(x) (+ float(residual));  residual_out = round(xf) (written by CTA 0);
+//   the GEMM's input row is round(round(xf * rsqrt(mean(xf^2) + eps)) * norm_weight),
+// the arithmetic of rmsnorm_kernel; every CTA recomputes the 8 row statistics (the rows are small).
+struct SgNorm {
+    const uint16_t* residual; int64_t res_stride;
+    const uint16_t* norm_weight; float eps;
+    uint16_t* residual_out; int64_t res_out_stride;
+};
+
+template <bool BF16, int NT, bool NORM>
 __global__ void __launch_bounds__(kSgWarps * 32) skinny_gemm_kernel(
     const uint16_t* __restrict__ x, int64_t x_stride, const uint16_t* __restrict__ w, int64_t w_stride,
-    const uint16_t* __restrict__ bias, uint16_t* __restrict__ y, int64_t y_stride, int M, int N, int K) {
+    const uint16_t* __restrict__ bias, uint16_t* __restrict__ y, int64_t y_stride, int M, int N, int K, SgNorm nrm) {
     __shared__ float s_part[kSgWarps][NT][128];
+    __shared__ float s_ss[kSgWarps][8];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
     const int n0 = blockIdx.x * 16 * NT;
     const int kslice = K / kSgWarps, k_begin = warp * kslice;
@@ -53,11 +91,59 @@ __global__ void __launch_bounds__(kSgWarps * 32) skinny_gemm_kernel(
         }
     }
     pdl_wait();
+    constexpr int DT = BF16 ? FDMS_BF16 : FDMS_F16;
+    const uint16_t* rr = NORM && nrm.residual ? nrm.residual + (int64_t)g * nrm.res_stride + k_begin + 8 * t : nullptr;
+    float inv = 0.0f;
+    if (NORM) {
+        // row statistics over the whole row: this warp's slice, then the 8 warps through shared memory
+        float ss = 0.0f;
+        if (g < M) {
+            for (int ks = 0; ks < kslice; ks += kSgStep) {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    float f[8];
+                    sg_unpack8<BF16>(*(const uint4*)(xr + ks + 32 * j), f);
+                    if (rr) {
+                        float r[8];
+                        sg_unpack8<BF16>(*(const uint4*)(rr + ks + 32 * j), r);
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) f[i] += r[i];
+                    }
+                    if (blockIdx.x == 0 && nrm.residual_out)
+                        *(uint4*)(nrm.residual_out + (int64_t)g * nrm.res_out_stride + k_begin + 8 * t + ks + 32 * j) = sg_pack8<BF16>(f);
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) ss += f[i] * f[i];
+                }
+            }
+        }
+        ss += __shfl_xor_sync(0xffffffffu, ss, 1);
+        ss += __shfl_xor_sync(0xffffffffu, ss, 2);
+        if (t == 0) s_ss[warp][g] = ss;
+        __syncthreads();
+        float tot = 0.0f;
+#pragma unroll
+        for (int wv = 0; wv < kSgWarps; ++wv) tot += s_ss[wv][g];
+        inv = rsqrtf(tot / (float)K + nrm.eps);
+    }
     for (int ks = 0; ks < kslice; ks += kSgStep) {
         uint4 xb[8];
 #pragma unroll
-        for (int j = 0; j < 8; ++j)
-            xb[j] = g < M ? __ldg((const uint4*)(xr + ks + 32 * j)) : make_uint4(0u, 0u, 0u, 0u);
+        for (int j = 0; j < 8; ++j) {
+            if (g >= M) { xb[j] = make_uint4(0u, 0u, 0u, 0u); continue; }
+            if (!NORM) { xb[j] = __ldg((const uint4*)(xr + ks + 32 * j)); continue; }
+            float f[8], nw[8];
+            sg_unpack8<BF16>(*(const uint4*)(xr + ks + 32 * j), f);
+            if (rr) {
+                float r[8];
+                sg_unpack8<BF16>(*(const uint4*)(rr + ks + 32 * j), r);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) f[i] += r[i];
+            }
+            sg_unpack8<BF16>(__ldg((const uint4*)(nrm.norm_weight + k_begin + 8 * t + ks + 32 * j)), nw);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) f[i] = round_to_dtype(f[i] * inv, DT) * nw[i];
+            xb[j] = sg_pack8<BF16>(f);
+        }
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt) {
             const int row = n0 + nt * 16 + g;                       // rows row and row + 8 of W
@@ -103,10 +189,9 @@ __global__ void __launch_bounds__(kSgWarps * 32) skinny_gemm_kernel(
 
 using namespace fdms;
 
-extern "C" int32_t fdms_linear_decode(const void* x, int64_t x_row_stride, const void* weight, int64_t w_row_stride,
-                                      const void* bias, void* y, int64_t y_row_stride, int32_t dtype, int32_t rows,
-                                      int32_t out_features, int32_t in_features, void* stream) {
-    clear_error();
+static int32_t linear_decode_launch(const void* x, int64_t x_row_stride, const void* weight, int64_t w_row_stride,
+                                    const void* bias, void* y, int64_t y_row_stride, int32_t dtype, int32_t rows,
+                                    int32_t out_features, int32_t in_features, const SgNorm* norm, void* stream) {
     FDMS_REQUIRE(x && weight && y, FDMS_E_ARG, "fdms_linear_decode: null pointer");
     FDMS_REQUIRE(dtype == FDMS_BF16 || dtype == FDMS_F16, FDMS_E_DTYPE, "fdms_linear_decode: bf16 or f16 only");
     FDMS_REQUIRE(rows >= 0 && rows <= 8, FDMS_E_CAPACITY, "fdms_linear_decode: at most 8 rows, got %d", rows);
@@ -116,20 +201,57 @@ extern "C" int32_t fdms_linear_decode(const void* x, int64_t x_row_stride, const
     FDMS_REQUIRE(((uintptr_t)x & 15) == 0 && ((uintptr_t)weight & 15) == 0 && (x_row_stride * 2) % 16 == 0 &&
                      (w_row_stride * 2) % 16 == 0,
                  FDMS_E_ARG, "fdms_linear_decode: x and weight rows must be 16-byte aligned");
+    if (norm) {
+        FDMS_REQUIRE(norm->norm_weight && ((uintptr_t)norm->norm_weight & 15) == 0, FDMS_E_ARG,
+                     "fdms_linear_decode_norm: norm weight missing or not 16-byte aligned");
+        FDMS_REQUIRE((!norm->residual || (((uintptr_t)norm->residual & 15) == 0 && (norm->res_stride * 2) % 16 == 0)) &&
+                         (!norm->residual_out || (((uintptr_t)norm->residual_out & 15) == 0 && (norm->res_out_stride * 2) % 16 == 0)),
+                     FDMS_E_ARG, "fdms_linear_decode_norm: residual rows must be 16-byte aligned");
+        FDMS_REQUIRE(!norm->residual_out || (norm->residual_out != x && norm->residual_out != norm->residual), FDMS_E_ARG,
+                     "fdms_linear_decode_norm: residual_out must not alias x or residual (other CTAs still read them)");
+    }
     if (rows == 0) return FDMS_OK;
     const int tiles = out_features / 16;
     const int nt = tiles >= 4096 ? 4 : (tiles >= 1024 ? 2 : 1);
     const unsigned grid = (unsigned)((tiles + nt - 1) / nt);
     const bool bf = dtype == FDMS_BF16;
     cudaStream_t st = (cudaStream_t)stream;
-#define FDMS_SG_LAUNCH(B, T)                                                                                   \
-    FDMS_CUDA_OK(launch_chained(skinny_gemm_kernel<B, T>, dim3(grid), dim3(kSgWarps * 32), st, chain_launches(),   \
-                                (const uint16_t*)x, x_row_stride, (const uint16_t*)weight, w_row_stride,            \
-                                (const uint16_t*)bias, (uint16_t*)y, y_row_stride, (int)rows, (int)out_features,    \
-                                (int)in_features))
-    if (bf) { if (nt == 4) FDMS_SG_LAUNCH(true, 4); else if (nt == 2) FDMS_SG_LAUNCH(true, 2); else FDMS_SG_LAUNCH(true, 1); }
-    else { if (nt == 4) FDMS_SG_LAUNCH(false, 4); else if (nt == 2) FDMS_SG_LAUNCH(false, 2); else FDMS_SG_LAUNCH(false, 1); }
+    const SgNorm nrm = norm ? *norm : SgNorm{nullptr, 0, nullptr, 0.0f, nullptr, 0};
+#define FDMS_SG_LAUNCH(B, T, NM)                                                                                \
+    FDMS_CUDA_OK(launch_chained(skinny_gemm_kernel<B, T, NM>, dim3(grid), dim3(kSgWarps * 32), st, chain_launches(), \
+                                (const uint16_t*)x, x_row_stride, (const uint16_t*)weight, w_row_stride,         \
+                                (const uint16_t*)bias, (uint16_t*)y, y_row_stride, (int)rows, (int)out_features, \
+                                (int)in_features, nrm))
+#define FDMS_SG_PICK(B, NM)                                                                    \
+    do {                                                                                       \
+        if (nt == 4) FDMS_SG_LAUNCH(B, 4, NM); else if (nt == 2) FDMS_SG_LAUNCH(B, 2, NM); else FDMS_SG_LAUNCH(B, 1, NM); \
+    } while (0)
+    if (norm) { if (bf) FDMS_SG_PICK(true, true); else FDMS_SG_PICK(false, true); }
+    else { if (bf) FDMS_SG_PICK(true, false); else FDMS_SG_PICK(false, false); }
+#undef FDMS_SG_PICK
 #undef FDMS_SG_LAUNCH
     FDMS_CHECK_LAUNCH("skinny_gemm_kernel");
     return FDMS_OK;
+}
+
+extern "C" int32_t fdms_linear_decode(const void* x, int64_t x_row_stride, const void* weight, int64_t w_row_stride,
+                                      const void* bias, void* y, int64_t y_row_stride, int32_t dtype, int32_t rows,
+                                      int32_t out_features, int32_t in_features, void* stream) {
+    clear_error();
+    return linear_decode_launch(x, x_row_stride, weight, w_row_stride, bias, y, y_row_stride, dtype, rows, out_features,
+                                in_features, nullptr, stream);
+}
+
+extern "C" int32_t fdms_linear_decode_norm(
+    const void* x, int64_t x_row_stride, const void* residual, int64_t residual_row_stride, const void* norm_weight,
+    float eps, void* residual_out, int64_t residual_out_row_stride, const void* weight, int64_t w_row_stride,
+    const void* bias, void* y, int64_t y_row_stride, int32_t dtype, int32_t rows, int32_t out_features,
+    int32_t in_features, void* stream) {
+    clear_error();
+    SgNorm n;
+    n.residual = (const uint16_t*)residual; n.res_stride = residual_row_stride;
+    n.norm_weight = (const uint16_t*)norm_weight; n.eps = eps;
+    n.residual_out = (uint16_t*)residual_out; n.res_out_stride = residual_out_row_stride;
+    return linear_decode_launch(x, x_row_stride, weight, w_row_stride, bias, y, y_row_stride, dtype, rows, out_features,
+                                in_features, &n, stream);
 }

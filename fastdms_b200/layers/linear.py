@@ -22,15 +22,54 @@ from fastdms_b200 import _lib
 _DECODE_LINEAR = os.environ.get("FDMS_DECODE_LINEAR", "1") != "0"
 
 
+# Opt-in: the fused norm + linear launch measured SLOWER in the 1B decode step (0.91 against 0.78 ms per
+# graph replay): every CTA of the projection recomputes the row statistics and the normalised input
+# after the dependency wait, which costs more than the chained RMSNorm launch it removes.
+_FUSE_NORM = os.environ.get("FDMS_FUSE_NORM_LINEAR", "0") == "1"
+
+
+def _decode_linear_ok(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None) -> bool:
+    return (_DECODE_LINEAR and x.is_cuda and x.dtype in (torch.bfloat16, torch.float16) and weight.dtype == x.dtype
+            and x.dim() == 2 and 0 < x.shape[0] <= 8 and x.stride(1) == 1 and weight.is_contiguous()
+            and weight.shape[0] % 16 == 0 and weight.shape[0] < 65536 and weight.shape[1] % 2048 == 0
+            and x.shape[1] == weight.shape[1] and (bias is None or bias.dtype == x.dtype)
+            and x.data_ptr() % 16 == 0 and (x.stride(0) * 2) % 16 == 0 and weight.data_ptr() % 16 == 0
+            and not torch.is_grad_enabled())
+
+
+def norm_linear(x: torch.Tensor, residual: torch.Tensor | None, norm, lin) -> tuple[torch.Tensor, torch.Tensor]:
+    """`h, r = norm(x, residual); return lin(h), r` of a decoder block (`norm` an RMSNorm, `lin` a
+    column-parallel linear layer; with `residual=None` the new residual is `x`, as in the reference's
+    `models/llama.py` decoder layer).  With `FDMS_FUSE_NORM_LINEAR=1` decode-sized 16-bit
+    inputs take ONE launch of `fdms_linear_decode_norm`; otherwise the two modules run."""
+    w, b = lin.weight, lin.bias
+    if (_FUSE_NORM and _decode_linear_ok(x, w, b) and norm.weight.dtype == x.dtype and norm.weight.is_contiguous()
+            and norm.weight.data_ptr() % 16 == 0
+            and (residual is None or (residual.dtype == x.dtype and residual.shape == x.shape and residual.stride(1) == 1
+                                      and residual.data_ptr() % 16 == 0 and (residual.stride(0) * 2) % 16 == 0))):
+        rows, n = x.shape[0], w.shape[0]
+        y = torch.empty((rows, n), dtype=x.dtype, device=x.device)
+        res_out = torch.empty_like(x) if residual is not None else None
+        with torch.cuda.device(x.device):
+            rc = _lib.lib().fdms_linear_decode_norm(
+                x.data_ptr(), x.stride(0), _lib.ptr(residual), residual.stride(0) if residual is not None else 0,
+                norm.weight.data_ptr(), float(norm.eps), _lib.ptr(res_out), res_out.stride(0) if res_out is not None else 0,
+                w.data_ptr(), w.stride(0), b.data_ptr() if b is not None else None, y.data_ptr(), y.stride(0),
+                _lib.dtype_code(x.dtype), rows, n, w.shape[1], _lib.stream_ptr(x.device))
+        _lib.check(rc)
+        return y, (res_out if residual is not None else x)
+    if residual is None:
+        h, r = norm(x), x
+    else:
+        h, r = norm(x, residual)
+    return lin(h), r
+
+
 def linear(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None = None) -> torch.Tensor:
     """`F.linear`, except that 16-bit CUDA inputs of at most 8 rows go through one launch of
     `fdms_linear_decode` (weights streamed once, f32 accumulation) when the shapes allow it; very wide
     outputs (the LM head) stay on the library GEMM, which streams them faster."""
-    if (_DECODE_LINEAR and x.is_cuda and x.dtype in (torch.bfloat16, torch.float16) and weight.dtype == x.dtype
-            and x.dim() == 2 and 0 < x.shape[0] <= 8 and x.stride(1) == 1 and weight.is_contiguous()
-            and weight.shape[0] % 16 == 0 and weight.shape[0] < 65536 and weight.shape[1] % 2048 == 0 and (bias is None or bias.dtype == x.dtype)
-            and x.data_ptr() % 16 == 0 and (x.stride(0) * 2) % 16 == 0 and weight.data_ptr() % 16 == 0
-            and not torch.is_grad_enabled()):
+    if _decode_linear_ok(x, weight, bias):
         rows, n = x.shape[0], weight.shape[0]
         y = torch.empty((rows, n), dtype=x.dtype, device=x.device)
         with torch.cuda.device(x.device):

@@ -22,7 +22,7 @@ from fastdms_b200.layers.compact_attention import (dms_decode_store_transient_k_
 from fastdms_b200.layers.embed_head import ParallelLMHead, VocabParallelEmbedding
 from fastdms_b200.layers.layernorm import RMSNorm
 from fastdms_b200.layers.linear import (MergedColumnParallelLinear, QKVParallelLinear, RowParallelLinear,
-                                        tp_world)
+                                        norm_linear, tp_world)
 from fastdms_b200.layers.rotary_embedding import get_rope
 from fastdms_b200.utils.context import get_context
 from fastdms_b200.utils.profiler import get_profiler
@@ -69,8 +69,11 @@ class LlamaAttention(nn.Module):
             self.q_norm = RMSNorm(self.head_dim, eps=config.rms_norm_eps)
             self.k_norm = RMSNorm(self.head_dim, eps=config.rms_norm_eps)
 
-    def forward(self, positions: torch.Tensor, hidden_states: torch.Tensor) -> torch.Tensor:
-        qkv = self.qkv_proj(hidden_states)
+    def forward(self, positions: torch.Tensor, hidden_states: torch.Tensor | None,
+                qkv: torch.Tensor | None = None) -> torch.Tensor:
+        """`qkv` given: the projection was already taken (fused with the preceding norm)."""
+        if qkv is None:
+            qkv = self.qkv_proj(hidden_states)
         q, k, v = qkv.split([self.q_size, self.kv_size, self.kv_size], dim=-1)
         q = q.view(-1, self.num_heads, self.head_dim)
         k = k.view(-1, self.num_kv_heads, self.head_dim)
@@ -159,6 +162,9 @@ class LlamaMLP(nn.Module):
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         return self.down_proj(self.act_fn(self.gate_up_proj(x)))
 
+    def from_gate_up(self, gate_up: torch.Tensor) -> torch.Tensor:
+        return self.down_proj(self.act_fn(gate_up))
+
 
 class LlamaDecoderLayer(nn.Module):
     attention_cls = LlamaAttention
@@ -171,13 +177,11 @@ class LlamaDecoderLayer(nn.Module):
         self.post_attention_layernorm = RMSNorm(config.hidden_size, eps=config.rms_norm_eps)
 
     def forward(self, positions, hidden_states, residual):
-        if residual is None:
-            hidden_states, residual = self.input_layernorm(hidden_states), hidden_states
-        else:
-            hidden_states, residual = self.input_layernorm(hidden_states, residual)
-        hidden_states = self.self_attn(positions, hidden_states)
-        hidden_states, residual = self.post_attention_layernorm(hidden_states, residual)
-        hidden_states = self.mlp(hidden_states)
+        # norm -> projection pairs go through `norm_linear` (the two modules; one fused launch is an opt-in)
+        qkv, residual = norm_linear(hidden_states, residual, self.input_layernorm, self.self_attn.qkv_proj)
+        hidden_states = self.self_attn(positions, None, qkv=qkv)
+        gate_up, residual = norm_linear(hidden_states, residual, self.post_attention_layernorm, self.mlp.gate_up_proj)
+        hidden_states = self.mlp.from_gate_up(gate_up)
         return hidden_states, residual
 
 

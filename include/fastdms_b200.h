@@ -382,6 +382,17 @@ int32_t fdms_linear_decode(const void* x, int64_t x_row_stride, const void* weig
                            const void* bias, void* y, int64_t y_row_stride, int32_t dtype, int32_t rows,
                            int32_t out_features, int32_t in_features, void* stream);
 
+/* The same with the decoder block's RMSNorm (+ residual add) in front (the reference runs
+ * RMSNorm.add_rms_forward, fastdms/layers/layernorm.py:16-48, then F.linear):
+ *   xf = float(x) (+ float(residual));  residual_out = round(xf) (optional, must not alias x / residual);
+ *   y = round(round(xf * rsqrt(mean(xf^2) + eps)) * norm_weight) * weight^T (+ bias).
+ * residual may be NULL (first layer).  Same shape and alignment rules; norm_weight has in_features elements. */
+int32_t fdms_linear_decode_norm(
+    const void* x, int64_t x_row_stride, const void* residual, int64_t residual_row_stride, const void* norm_weight,
+    float eps, void* residual_out, int64_t residual_out_row_stride, const void* weight, int64_t w_row_stride,
+    const void* bias, void* y, int64_t y_row_stride, int32_t dtype, int32_t rows, int32_t out_features,
+    int32_t in_features, void* stream);
+
 /* Greedy head: out[r] = index of the largest of x[r, 0..n) -- `logits.argmax(dim=-1)` of the
  * temperature-0 path (fastdms/engine/model_runner.py:1147-1151; the reference fuses it for one
  * sequence only, fastdms/layers/embed_head.py:491-543).  Lowest index on ties, a NaN counts as the

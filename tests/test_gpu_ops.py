@@ -606,3 +606,39 @@ def test_decode_linear_kernel_matches_float32_reference(dev, dtype, rows, n, k, 
     # the library kernel is what ran: torch's own GEMM rounds an f32 accumulation too, so the two agree to one ulp
     t = torch.nn.functional.linear(x, w, b)
     assert ((y.float() - t.float()).abs() <= 2 * eps * ref.abs() + 2e-3).all()
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("rows,n,k,with_res", [(8, 3072, 2048, True), (8, 16384, 2048, True), (3, 6144, 4096, True),
+                                               (8, 3072, 2048, False)])
+def test_fused_norm_linear_matches_the_two_modules(dev, dtype, rows, n, k, with_res):
+    """RMSNorm (+ residual add) fused in front of the decode linear kernel against the two separate
+    launches: the new residual is bit-identical, the projection agrees to one rounding of the 16-bit
+    type (the row statistics are summed in a different order)."""
+    from fastdms_b200.layers.layernorm import RMSNorm
+    from fastdms_b200.layers.linear import ReplicatedLinear, norm_linear
+    import fastdms_b200.layers.linear as L
+    g = torch.Generator(device=dev).manual_seed(rows + n + k)
+    norm = RMSNorm(k, eps=1e-5).to(dev)
+    norm.weight.data = (1.0 + 0.1 * torch.randn(k, device=dev, generator=g)).to(dtype)
+    lin = ReplicatedLinear(k, n, bias=True).to(dev)
+    lin.weight.data = (torch.randn((n, k), device=dev, generator=g) * k ** -0.5).to(dtype)
+    lin.bias.data = torch.randn(n, device=dev, generator=g).to(dtype)
+    x = torch.randn((rows, k), device=dev, generator=g).to(dtype)
+    res = torch.randn((rows, k), device=dev, generator=g).to(dtype) if with_res else None
+    saved = L._FUSE_NORM
+    with torch.inference_mode():
+        try:
+            L._FUSE_NORM = True
+            y, r = norm_linear(x, res, norm, lin)
+            L._FUSE_NORM = False
+            y0, r0 = norm_linear(x.clone(), None if res is None else res.clone(), norm, lin)
+        finally:
+            L._FUSE_NORM = saved
+    assert torch.equal(r, r0 if with_res else x)
+    xf = x.float() + (res.float() if with_res else 0.0)
+    h = ((xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + 1e-5)).to(dtype).float() * norm.weight.float()).to(dtype)
+    ref = h.float() @ lin.weight.float().t() + lin.bias.float()
+    eps = 2.0 ** -6 if dtype == torch.bfloat16 else 2.0 ** -9
+    assert ((y.float() - ref).abs() <= eps * ref.abs() + 2e-2).all()
+    assert ((y.float() - y0.float()).abs() <= eps * ref.abs() + 2e-2).all()
