@@ -42,3 +42,23 @@ def test_chunk_attention_limits():
     out0, d0, t0 = O.chunk_attention(q, k, v, [np.zeros((0, D), np.float32)] * Hk, [np.zeros((0, D), np.float32)] * Hk)
     assert np.allclose(d0, t0, atol=1e-6)
     assert np.abs(out0[0, 0] - v[0, 0]).max() < 1e-6          # the first token sees only itself
+
+
+def test_chunked_state_property_random_chunk_schedules():
+    """Hypothesis: for any evict pattern, window and chunk size the chunked state equals the one-pass
+    state, and every intermediate state is what the decode-time rule keeps at that position."""
+    from hypothesis import given, settings, strategies as st
+
+    @settings(max_examples=150, deadline=None)
+    @given(st.lists(st.booleans(), min_size=1, max_size=300), st.integers(0, 64), st.integers(1, 320))
+    def check(evict, window, chunk):
+        ev = np.asarray(evict, bool)
+        want = np.nonzero(O.pack_keep(ev[:, None], window)[:, 0])[0]
+        assert np.array_equal(O.chunked_prefill_state(ev, window, chunk), want)
+        # the state after the first chunk alone = live_mask of the decode rule at cur = chunk end - 1
+        e = min(len(ev), chunk)
+        first = O.chunked_prefill_state(ev[:e], window, chunk)
+        keep = O.live_mask(ev[:e][None, :], e - 1, window)[0]
+        assert np.array_equal(first, np.nonzero(keep)[0])
+
+    check()
