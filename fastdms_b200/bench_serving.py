@@ -4,7 +4,8 @@ compact KV pool.  Shapes and arrival process follow the reference's serving-styl
 (`benchmarks/soak_compact_dms.py`, `benchmarks/bench_llama_wikitext2.py`); token ids are random.
 
     python -m fastdms_b200.bench_serving --shape llama-1b --requests 256 --rate 20 \
-        --min-prompt 512 --max-prompt 32768 --min-gen 64 --max-gen 512 --max-concurrent 64 [--kv-gib 8]
+        --min-prompt 512 --max-prompt 32768 --min-gen 64 --max-gen 512 --max-concurrent 64 \
+        [--kv-gib 8] [--prefill-chunk 2048] [--paged] [--admission optimistic]
 
 Requests are admitted by the scheduler when the token budget and the compact pool allow: charged
 their worst case (`--admission reserve`) or an estimate of what DMS keeps, with a retry when a
@@ -133,7 +134,7 @@ def main() -> None:
     ap.add_argument("--paged", action="store_true")
     ap.add_argument("--admission", choices=["reserve", "optimistic"], default="reserve")
     ap.add_argument("--keep-estimate", type=float, default=0.2)
-    ap.add_argument("--prefill-chunk", type=int, default=0, help="prefill prompts in chunks of this many tokens (0: one pass)")
+    ap.add_argument("--prefill-chunk", type=int, default=2048, help="prefill prompts in chunks of this many tokens (0: one pass)")
     ap.add_argument("--seed", type=int, default=0)
     print(json.dumps(run(ap.parse_args())))
 
