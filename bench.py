@@ -2,7 +2,7 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
 
-Workload (BASELINE.json configs[1], the op-level compact decode on Llama-3.2-1B shapes, laid out
+Workload (the op-level compact decode on Llama-3.2-1B shapes, laid out
 as the 16 layers of that model so that a "step" is one decode step of the hot path): 32 q heads,
 8 KV heads, head_dim 64, c = 8 sequences at 8192 context; per (layer, sequence, KV head) the
 compact span holds 1024 + U(-128, 128) retained prompt tokens plus the 256-token window; K/V ~
@@ -36,7 +36,7 @@ import numpy as np
 ROOT = Path(__file__).resolve().parent
 sys.path.insert(0, str(ROOT))
 
-# ---- the workload: BASELINE.json configs[1] on the 16 layers of the Llama-3.2-1B shape ----------
+# ---- the workload: op-level compact decode on the 16 layers of the Llama-3.2-1B shape -------------
 L, B, HQ, HK, D = 16, 8, 32, 8, 64
 CTX, WINDOW = 8192, 256
 RETAIN_MEAN, RETAIN_JITTER = 1024, 128

@@ -3,7 +3,7 @@ reference's `benchmarks/bench_compact_decode.py`, default lengths `:101`): for e
 distinct FP8 pools (so that one replay streams more than L2 holds) with randomly permuted 16-row
 pages, one CUDA graph of `layers` launches replayed between two CUDA events.
 
-    python -m fastdms_b200.bench_attention [--lengths 1280,2048,4096,8192,16384] [--head-dim 64] [--batch 8]
+    python -m benchmarks.bench_attention [--lengths 1280,2048,4096,8192,16384] [--head-dim 64] [--batch 8]
 
 Prints one JSON line per length: µs per launch, achieved GB/s on the algorithmic bytes
 (sum of live * 2 * head_dim FP8 bytes) and the fraction of `--peak-gbs`."""

@@ -3,7 +3,7 @@ on the projection shapes of a decoder block, 8 rows of bf16 activations.  Each s
 enough distinct weight matrices to exceed L2, inside one CUDA graph replayed between two events.
 Prints one JSON line per shape: µs per launch and GB/s on the algorithmic bytes (the weight matrix).
 
-    python -m fastdms_b200.bench_linear [--shapes 3072x2048,2048x2048,16384x2048,2048x8192] [--rows 8]"""
+    python -m benchmarks.bench_linear [--shapes 3072x2048,2048x2048,16384x2048,2048x8192] [--rows 8]"""
 from __future__ import annotations
 
 import argparse

@@ -2,9 +2,9 @@
 (its WikiText-2 8192 + 128 runs, `benchmarks/bench_llama_wikitext2.py`; dataset and checkpoints are
 replaced by random token ids and random-init weights).
 
-    python -m fastdms_b200.bench_model --shape llama-1b                       # one GPU, c = 8
-    torchrun --nproc-per-node N -m fastdms_b200.bench_model --shape llama-1b  # N replicas, c = 8 each
-    torchrun --nproc-per-node N -m fastdms_b200.bench_model --shape qwen3-8b --tp N
+    python -m benchmarks.bench_model --shape llama-1b                       # one GPU, c = 8
+    torchrun --nproc-per-node N -m benchmarks.bench_model --shape llama-1b  # N replicas, c = 8 each
+    torchrun --nproc-per-node N -m benchmarks.bench_model --shape qwen3-8b --tp N
 
 Replica mode (`--tp 1` under torchrun) shards sequences over the ranks with no data-path collective;
 `--tp N` splits KV heads over the ranks with NCCL all-reduces after o_proj and down_proj.
@@ -22,20 +22,7 @@ import time
 import torch
 import torch.distributed as dist
 
-SHAPES = {
-    # Llama-3.2-1B: 16 layers, hidden 2048, 32 q / 8 KV heads of 64, MLP 8192, vocab 128256
-    "llama-1b": dict(model_type="llama", hidden_size=2048, intermediate_size=8192, num_hidden_layers=16,
-                     num_attention_heads=32, num_key_value_heads=8, head_dim=64, vocab_size=128256,
-                     rms_norm_eps=1e-5, rope_theta=500000.0, tie_word_embeddings=False, hidden_act="silu"),
-    # Qwen3-8B: 36 layers, hidden 4096, 32 q / 8 KV heads of 128, q/k RMSNorm, MLP 12288, vocab 151936
-    "qwen3-8b": dict(model_type="qwen3", hidden_size=4096, intermediate_size=12288, num_hidden_layers=36,
-                     num_attention_heads=32, num_key_value_heads=8, head_dim=128, vocab_size=151936,
-                     rms_norm_eps=1e-6, rope_theta=1000000.0, tie_word_embeddings=False, hidden_act="silu"),
-    # small shape for tests
-    "tiny": dict(model_type="llama", hidden_size=256, intermediate_size=512, num_hidden_layers=2,
-                 num_attention_heads=8, num_key_value_heads=2, head_dim=64, vocab_size=1024,
-                 rms_norm_eps=1e-5, rope_theta=500000.0, tie_word_embeddings=False, hidden_act="silu"),
-}
+from fastdms_b200.utils.shapes import SHAPES  # noqa: E402
 
 
 def run(args) -> dict:

@@ -3,7 +3,7 @@ of `--queries` tokens against `--rows` FP8 rows per KV-head span (contiguous spa
 given dense result.  Prints one JSON line per (head_dim, queries, rows): µs per launch and TFLOP/s on
 the algorithmic flops 4 * queries * q_heads * rows * head_dim.
 
-    python -m fastdms_b200.bench_prefix_attention [--cases 64:2048:1280,64:2048:4096,128:2048:4096]"""
+    python -m benchmarks.bench_prefix_attention [--cases 64:2048:1280,64:2048:4096,128:2048:4096]"""
 from __future__ import annotations
 
 import argparse

@@ -3,7 +3,7 @@ lengths log-uniform, generation lengths uniform, a cap on concurrent sequences a
 compact KV pool.  Shapes and arrival process follow the reference's serving-style runs
 (`benchmarks/soak_compact_dms.py`, `benchmarks/bench_llama_wikitext2.py`); token ids are random.
 
-    python -m fastdms_b200.bench_serving --shape llama-1b --requests 256 --rate 20 \
+    python -m benchmarks.bench_serving --shape llama-1b --requests 256 --rate 20 \
         --min-prompt 512 --max-prompt 32768 --min-gen 64 --max-gen 512 --max-concurrent 64 \
         [--kv-gib 8] [--prefill-chunk 2048] [--paged] [--admission optimistic]
 
@@ -27,7 +27,7 @@ import torch
 
 def run(args) -> dict:
     from fastdms_b200 import _lib
-    from fastdms_b200.bench_model import SHAPES
+    from fastdms_b200.utils.shapes import SHAPES
     from fastdms_b200.engine.llm_engine import LLMEngine
     from fastdms_b200.sampling_params import SamplingParams
 

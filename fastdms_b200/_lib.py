@@ -153,14 +153,27 @@ def read_device_status(device: torch.device | str = "cuda", clear: bool = True) 
     return v
 
 
+# Sized for the largest problem the fast kernels accept (65 535 spans, head_dim 256): about 8.7 MB.
+_WS_MAX_SPANS, _WS_MAX_HEAD_DIM = 65535, 256
+_retired_workspaces: list[torch.Tensor] = []
+
+
 def attn_workspace(device: torch.device, batch: int, num_kv_heads: int, head_dim: int) -> torch.Tensor:
-    """Zero-initialised split-K workspace, one per device, grown on demand and reused (the kernel
-    leaves its counters at zero).  Launches that use it are ordered by the stream they run on;
-    callers that drive several streams at once must pass their own workspace instead."""
+    """Zero-initialised split-K workspace, one per device (the kernel leaves its counters at zero).
+
+    CUDA graphs captured by the engine hold the workspace's raw address, so the tensor is allocated
+    ONCE per device at the size of the largest problem the fast kernels take and is never replaced
+    by a bigger one while smaller batches' graphs may still point at it.  A request beyond that size
+    (not reachable through the fast kernels) gets a larger tensor and the old one is kept alive.
+    Launches that use the workspace are ordered by the stream they run on; callers that drive
+    several streams at once must pass their own workspace instead."""
     need = lib().fdms_attn_decode_workspace_bytes(batch, num_kv_heads, head_dim)
     idx = device.index if device.index is not None else torch.cuda.current_device()
     ws = _workspaces.get(idx)
     if ws is None or ws.numel() < need:
-        ws = torch.zeros(need, dtype=torch.uint8, device=device)
+        full = lib().fdms_attn_decode_workspace_bytes(_WS_MAX_SPANS, 1, _WS_MAX_HEAD_DIM)
+        if ws is not None:
+            _retired_workspaces.append(ws)          # graphs captured earlier may still reference it
+        ws = torch.zeros(max(need, full), dtype=torch.uint8, device=device)
         _workspaces[idx] = ws
     return ws

@@ -31,6 +31,8 @@
 #include <cuda.h>
 #include <stdlib.h>
 
+#include <atomic>
+
 #include "common.cuh"
 
 namespace fdms {
@@ -1121,18 +1123,12 @@ struct AppendArgs {
 };
 }  // namespace fdms
 
-static int32_t attn_decode_common(
-    const void* q, int32_t q_dtype, int64_t q_stride_b, int64_t q_stride_h,
-    const void* k_pool, const void* v_pool, int32_t kv_dtype, int64_t pool_rows,
-    const int32_t* base_offsets, const int32_t* live_counts, int64_t meta_stride_b,
-    const int32_t* block_tables, int64_t bt_stride_b, int64_t bt_stride_h, int32_t bt_max_pages,
-    const float* k_scale, const float* v_scale,
-    void* out, int32_t out_dtype, int64_t out_stride_b, int64_t out_stride_h,
-    int32_t batch, int32_t num_q_heads, int32_t num_kv_heads, int32_t head_dim, float scale,
-    const int64_t* q_rope_positions, const float* q_rope_cos_sin, int64_t cos_sin_stride, int64_t cos_sin_rows,
-    void* workspace, int64_t workspace_bytes, int32_t flags, int32_t* dev_status, void* stream,
-    const fdms::AppendArgs* app) {
-    clear_error();
+// Argument checks shared by every attention entry point (nothing is enqueued before they pass).
+static int32_t validate_attn_args(
+    const void* q, int32_t q_dtype, const void* k_pool, const void* v_pool, int32_t kv_dtype,
+    const int32_t* base_offsets, const int32_t* live_counts, const int32_t* block_tables, int32_t bt_max_pages,
+    const void* out, int32_t out_dtype, int32_t batch, int32_t num_q_heads, int32_t num_kv_heads, int32_t head_dim,
+    const int64_t* q_rope_positions, const float* q_rope_cos_sin, int64_t cos_sin_rows) {
     FDMS_REQUIRE(q && k_pool && v_pool && live_counts && out, FDMS_E_ARG, "fdms_attn_decode: null pointer");
     FDMS_REQUIRE(base_offsets || block_tables, FDMS_E_ARG, "fdms_attn_decode: base_offsets or block_tables required");
     FDMS_REQUIRE(!block_tables || bt_max_pages > 0, FDMS_E_ARG, "fdms_attn_decode: bt_max_pages must be positive");
@@ -1150,6 +1146,28 @@ static int32_t attn_decode_common(
     FDMS_REQUIRE((q_rope_positions == nullptr) == (q_rope_cos_sin == nullptr), FDMS_E_ARG,
                  "inline q RoPE requires both positions and cos_sin_cache");
     FDMS_REQUIRE(!q_rope_positions || head_dim % 2 == 0, FDMS_E_ARG, "inline q RoPE requires even head_dim, got %d", head_dim);
+    FDMS_REQUIRE(q_rope_positions == nullptr || cos_sin_rows > 0, FDMS_E_ARG, "fdms_attn_decode: cos_sin_rows must be positive");
+    return FDMS_OK;
+}
+
+static int32_t attn_decode_common(
+    const void* q, int32_t q_dtype, int64_t q_stride_b, int64_t q_stride_h,
+    const void* k_pool, const void* v_pool, int32_t kv_dtype, int64_t pool_rows,
+    const int32_t* base_offsets, const int32_t* live_counts, int64_t meta_stride_b,
+    const int32_t* block_tables, int64_t bt_stride_b, int64_t bt_stride_h, int32_t bt_max_pages,
+    const float* k_scale, const float* v_scale,
+    void* out, int32_t out_dtype, int64_t out_stride_b, int64_t out_stride_h,
+    int32_t batch, int32_t num_q_heads, int32_t num_kv_heads, int32_t head_dim, float scale,
+    const int64_t* q_rope_positions, const float* q_rope_cos_sin, int64_t cos_sin_stride, int64_t cos_sin_rows,
+    void* workspace, int64_t workspace_bytes, int32_t flags, int32_t* dev_status, void* stream,
+    const fdms::AppendArgs* app) {
+    clear_error();
+    {
+        const int32_t rc = validate_attn_args(q, q_dtype, k_pool, v_pool, kv_dtype, base_offsets, live_counts, block_tables,
+                                              bt_max_pages, out, out_dtype, batch, num_q_heads, num_kv_heads, head_dim,
+                                              q_rope_positions, q_rope_cos_sin, cos_sin_rows);
+        if (rc != FDMS_OK) return rc;
+    }
     if (batch == 0) return FDMS_OK;
     const int group = num_q_heads / num_kv_heads;
     const int items = batch * num_kv_heads;
@@ -1164,7 +1182,6 @@ static int32_t attn_decode_common(
     p.batch = batch; p.hq = num_q_heads; p.hk = num_kv_heads; p.group = group;
     p.scale = scale;
     p.rope_pos = q_rope_positions; p.rope_cs = q_rope_cos_sin; p.rope_stride = cos_sin_stride; p.rope_rows = cos_sin_rows;
-    FDMS_REQUIRE(q_rope_positions == nullptr || cos_sin_rows > 0, FDMS_E_ARG, "fdms_attn_decode: cos_sin_rows must be positive");
     p.counters = nullptr; p.part_ml = nullptr; p.part_o = nullptr;
     p.dev_status = dev_status;
     p.stages = 0; p.splits = 1; p.chunks = 1; p.overlap = (flags & FDMS_ATTN_OVERLAP_PREVIOUS) ? 1 : 0;
@@ -1333,19 +1350,21 @@ constexpr size_t kStaticScratchBytes = kStaticCounterBytes + (size_t)kMaxPartial
 static __device__ __align__(256) unsigned char g_attn_static_scratch[kStaticScratchBytes];
 
 // Device address of the scratch array on the current device (nullptr + error code on failure).
+// The per-device cache is written with atomic stores: two host threads that race on the first call
+// both resolve the same address, and neither can read a half-written pointer.
 static void* static_scratch_address(cudaError_t* err) {
-    static void* cached[64] = {nullptr};
+    static std::atomic<void*> cached[64];
     int dev = 0;
     *err = cudaGetDevice(&dev);
     if (*err != cudaSuccess) return nullptr;
     if (dev < 0 || dev >= 64) { *err = cudaErrorInvalidDevice; return nullptr; }
-    if (cached[dev] == nullptr) {
-        void* ptr = nullptr;
+    void* ptr = cached[dev].load(std::memory_order_acquire);
+    if (ptr == nullptr) {
         *err = cudaGetSymbolAddress(&ptr, g_attn_static_scratch);
         if (*err != cudaSuccess) return nullptr;
-        cached[dev] = ptr;
+        cached[dev].store(ptr, std::memory_order_release);
     }
-    return cached[dev];
+    return ptr;
 }
 }  // namespace fdms
 
@@ -1368,6 +1387,13 @@ extern "C" int32_t fdms_attn_decode_noalloc(
     FDMS_REQUIRE(head_dim <= kStaticMaxHeadDim, FDMS_E_CAPACITY,
                  "fdms_attn_decode_noalloc: head_dim=%d exceeds the built-in scratch limit of %d; "
                  "use fdms_attn_decode with a caller workspace", head_dim, kStaticMaxHeadDim);
+    {
+        // every argument check of the ordinary entry point runs before anything is enqueued
+        const int32_t rc = validate_attn_args(q, q_dtype, k_pool, v_pool, kv_dtype, base_offsets, live_counts, block_tables,
+                                              bt_max_pages, out, out_dtype, batch, num_q_heads, num_kv_heads, head_dim,
+                                              q_rope_positions, q_rope_cos_sin, cos_sin_rows);
+        if (rc != FDMS_OK) return rc;
+    }
     if (batch == 0) return FDMS_OK;
     cudaError_t e = cudaSuccess;
     void* scratch = static_scratch_address(&e);

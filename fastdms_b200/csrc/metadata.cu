@@ -9,6 +9,24 @@ namespace fdms {
 
 constexpr int kMetaThreads = 256;
 
+// All-or-nothing pop of n entries from a free stack whose size is *count: returns the old top (the
+// caller owns entries [top - n, top)) or -1 when fewer than n are left, in which case the counter is
+// not touched.  A subtract-then-undo pop is not safe when spans ask for different amounts: between a
+// failed subtract and its undo the counter is too low, a concurrent smaller pop can fail although
+// pages are left or succeed from a stale top, and the stack ends up with duplicates.  The compare-
+// and-swap retries only when another pop or push got in between, so it always makes progress; the
+// iteration limit is a backstop that fails the pop instead of looping.
+__device__ __forceinline__ int pop_pages(int32_t* count, int n) {
+    int cur = *(volatile int32_t*)count;
+    for (int it = 0; it < (1 << 20); ++it) {
+        if (cur < n) return -1;
+        const int seen = atomicCAS(count, cur, cur - n);
+        if (seen == cur) return cur;
+        cur = seen;
+    }
+    return -1;
+}
+
 struct MetaParams {
     int32_t* live; const int32_t* base; int64_t meta_sl, meta_ss;
     int32_t* bt; int64_t bt_sl, bt_ss, bt_sh; int max_pages;
@@ -47,11 +65,10 @@ __global__ void __launch_bounds__(kMetaThreads) build_decode_metadata_kernel(Met
                     if (p.dev_status) atomicOr(p.dev_status, FDMS_DEV_BAD_INDEX);
                 } else {
                     if ((live & 15) == 0) {
-                        const int at = atomicSub(&p.free_counts[l], 1) - 1;
-                        if (at >= 0) {
-                            bt[pg] = p.free_pages[(int64_t)l * p.pages_per_layer + at];
-                        } else {                       // pool exhausted: undo, flag, skip the append
-                            atomicAdd(&p.free_counts[l], 1);
+                        const int top = pop_pages(&p.free_counts[l], 1);
+                        if (top > 0) {
+                            bt[pg] = p.free_pages[(int64_t)l * p.pages_per_layer + top - 1];
+                        } else {                       // pool exhausted: flag, skip the append
                             if (p.dev_status) atomicOr(p.dev_status, FDMS_DEV_BAD_INDEX);
                             bt[pg] = -1;
                         }
@@ -126,7 +143,7 @@ __global__ void record_decisions_kernel(
 }
 
 // Pops ceil(rows_needed / 16) pages per span from the layer's free stack into its block table
-// (prefill of the paged layout).  One thread per span; the pop is a single atomic per span.
+// (prefill of the paged layout).  One thread per span; the pop is all-or-nothing per span.
 __global__ void alloc_pages_kernel(const int32_t* rows_needed, int32_t* bt, int64_t bt_ss, int64_t bt_sh,
                                    int max_pages, const int32_t* seq_slots, int32_t* free_pages,
                                    int32_t* free_count, int num_seqs, int hk, int32_t* dev_status) {
@@ -140,9 +157,8 @@ __global__ void alloc_pages_kernel(const int32_t* rows_needed, int32_t* bt, int6
         n = max_pages;
         if (dev_status) atomicOr(dev_status, FDMS_DEV_BAD_INDEX);
     }
-    const int top = atomicSub(free_count, n);      // pages [top-n, top) of the stack are ours
-    if (top - n < 0) {
-        atomicAdd(free_count, n);
+    const int top = pop_pages(free_count, n);      // pages [top-n, top) of the stack are ours
+    if (top < 0) {
         if (dev_status) atomicOr(dev_status, FDMS_DEV_BAD_INDEX);
         for (int pg = 0; pg < n; ++pg) row[pg] = -1;
         return;
@@ -167,9 +183,8 @@ __global__ void grow_pages_kernel(const int32_t* rows_before, const int32_t* row
     }
     const int n = want - have;
     if (n <= 0) return;
-    const int top = atomicSub(free_count, n);
-    if (top - n < 0) {
-        atomicAdd(free_count, n);
+    const int top = pop_pages(free_count, n);
+    if (top < 0) {
         if (dev_status) atomicOr(dev_status, FDMS_DEV_BAD_INDEX);
         for (int pg = have; pg < want; ++pg) row[pg] = -1;
         return;

@@ -14,6 +14,7 @@ B200-first layout (differences from the reference are storage only, results are 
 """
 from __future__ import annotations
 
+import bisect
 import os
 from dataclasses import dataclass
 
@@ -57,28 +58,6 @@ class CompactKVSequenceState:
     last_dms_expiry_position: int = -1
     # host mirror of the reserved ranges: (base, size) per [layer][head]; avoids device reads on free
     host_ranges: list | None = None
-
-
-def build_emulated_dms_live_mask(*, num_layers: int, num_kv_heads: int, num_tokens: int, mode: str,
-                                 stride: int, recent_tokens: int, device) -> torch.Tensor:
-    """Synthetic retention masks used by the reference's non-DMS modes (compact_kv.py:523-551)."""
-    if mode == "all":
-        return torch.ones((num_layers, num_kv_heads, num_tokens), device=device, dtype=torch.bool)
-    if mode != "dms_stride":
-        raise ValueError(f"unknown compact KV retention mode: {mode}")
-    if stride <= 0:
-        raise ValueError(f"stride must be positive, got {stride}")
-    if recent_tokens < 0:
-        raise ValueError(f"recent_tokens must be non-negative, got {recent_tokens}")
-    pos = torch.arange(num_tokens, device=device)
-    l = torch.arange(num_layers, device=device).view(-1, 1, 1)
-    h = torch.arange(num_kv_heads, device=device).view(1, -1, 1)
-    mask = (pos.view(1, 1, -1) + l + h) % stride == 0
-    if recent_tokens:
-        mask[..., max(0, num_tokens - recent_tokens):] = True
-    if num_tokens:
-        mask[..., -1] = True
-    return mask
 
 
 def expiry_interval_from_env(default: int) -> int:
@@ -255,34 +234,39 @@ class CompactKVManager:
         return sum(self.free_tokens_in_layer(l) for l in range(self.num_layers))
 
     def _alloc_range(self, layer_id: int, length: int) -> int:
-        """First fit over the layer's sorted free list (reference: compact_kv.py:705-718)."""
-        free = self.free_ranges_per_layer[layer_id]
-        for idx, (start, available) in enumerate(free):
-            if available < length:
-                continue
-            if available == length:
-                free.pop(idx)
-            else:
-                free[idx] = (start + length, available - length)
-            return start
-        raise RuntimeError(
-            f"compact KV capacity exhausted in layer {layer_id}: requested {length}, "
-            f"free {self.free_tokens_in_layer(layer_id)}")
+        """Takes `length` rows from the lowest free range of the layer that can hold them and
+        returns the first row.  The list is kept sorted by start and coalesced, so this first-fit
+        rule hands out the same bases as the reference's allocator (compact_kv.py:705-718) for the
+        same sequence of requests, which the slot-index parity tests rely on."""
+        ranges = self.free_ranges_per_layer[layer_id]
+        hit = next((i for i, (_, size) in enumerate(ranges) if size >= length), None)
+        if hit is None:
+            raise RuntimeError(f"compact KV capacity exhausted in layer {layer_id}: {length} rows requested, "
+                               f"{self.free_tokens_in_layer(layer_id)} free in {len(ranges)} ranges")
+        first, size = ranges[hit]
+        if size > length:
+            ranges[hit] = (first + length, size - length)
+        else:
+            del ranges[hit]
+        return first
 
     def _free_range(self, layer_id: int, start: int, length: int) -> None:
+        """Gives rows [start, start + length) back: inserted at its sorted place and fused with the
+        free neighbour on either side (reference: compact_kv.py:720-737)."""
         if length <= 0:
             return
-        free = self.free_ranges_per_layer[layer_id]
-        free.append((start, length))
-        free.sort()
-        merged: list[tuple[int, int]] = []
-        for s, n in free:
-            if merged and s <= merged[-1][0] + merged[-1][1]:
-                ps, pn = merged[-1]
-                merged[-1] = (ps, max(ps + pn, s + n) - ps)
-            else:
-                merged.append((s, n))
-        self.free_ranges_per_layer[layer_id] = merged
+        ranges = self.free_ranges_per_layer[layer_id]
+        at = bisect.bisect_left(ranges, (start, 0))
+        lo, hi = start, start + length
+        if at > 0 and ranges[at - 1][0] + ranges[at - 1][1] >= lo:          # touches the range below
+            at -= 1
+            lo = ranges[at][0]
+            hi = max(hi, ranges[at][0] + ranges[at][1])
+            del ranges[at]
+        while at < len(ranges) and ranges[at][0] <= hi:                      # swallows ranges above
+            hi = max(hi, ranges[at][0] + ranges[at][1])
+            del ranges[at]
+        ranges.insert(at, (lo, hi - lo))
 
     def _reservation_tokens(self, seq: Sequence) -> int:
         worst = min(self.max_model_len, seq.num_prompt_tokens + seq.max_tokens)

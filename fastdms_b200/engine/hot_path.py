@@ -58,7 +58,14 @@ class DecodeHotPath:
         self.live = torch.zeros_like(self.base)
         self.slot = torch.zeros_like(self.base)
         self.cu_live = torch.zeros((L, B * Hk + 1), device=dev, dtype=torch.int32)
+        # Block tables of the batch.  With contiguous active slots this is a VIEW of the manager's
+        # table, which the metadata and expiry kernels update in place (a new page every 16 tokens,
+        # released pages at expiry).  With gaps in the slots it has to be a gathered copy; the copy is
+        # refreshed inside every step, after the metadata launch (see _enqueue).
         self.block_tables = manager.decode_block_tables(self.seqs)
+        self._bt_gathered = (self.block_tables is not None
+                             and manager._contiguous_active_slot_start(self.states) is None)
+        self._slots_long = self.slots_t.long()
         # pinned staging for the host-driven step
         self._h_q = self._h_k = self._h_v = self._h_out = self._h_pos = None
         self.graph = None
@@ -104,6 +111,8 @@ class DecodeHotPath:
         if self.expire_every_step:
             m.expire_device(self.slots_t, self.positions, window_size=self.window_size)
         m.decode_metadata_device(self.slots_t, self.base, self.live, self.slot, self.cu_live)
+        if self._bt_gathered:
+            torch.index_select(m.block_tables, 1, self._slots_long, out=self.block_tables)
         for l in range(self.L):
             ks, vs = m.layer_scales(l)
             ck, cv = m.compact_k_per_layer[l], m.compact_v_per_layer[l]

@@ -290,21 +290,12 @@ class ModelRunner:
             return g
         if g.graph == "pending":
             graph = torch.cuda.CUDAGraph()
-            saved = self._snapshot_metadata()
-            with torch.cuda.graph(graph):
+            with torch.cuda.graph(graph):          # nothing executes during capture: the state does not advance
                 self._decode_body(g)
-            self._restore_metadata(saved)          # capture must not advance the state
             g.graph = graph
         with get_profiler().cuda_phase("model_forward_decode"):
             g.graph.replay()
         return g
-
-    def _snapshot_metadata(self):
-        # Nothing executes during capture, so the state is untouched; kept as an explicit hook.
-        return None
-
-    def _restore_metadata(self, saved) -> None:
-        return None
 
     # ------------------------------------------------------------------ run / free
     @torch.inference_mode()

@@ -48,6 +48,8 @@ def synth_llama_state_dict(cfg: dict, seed: int = 0, *, evict_rate: float | None
     sd: dict[str, torch.Tensor] = {}
     sd["model.embed_tokens.weight"] = synth_tensor("embed", (V, H), 1.0, seed)
     sd["lm_head.weight"] = synth_tensor("lm_head", (V, H), cfg.get("lm_head_std", 0.5), seed)
+    if cfg.get("lm_head_factor") is not None:       # float32 product, applied before any cast of the weights
+        sd["lm_head.weight"] = sd["lm_head.weight"] * float(cfg["lm_head_factor"])
     sd["model.norm.weight"] = torch.ones(H)
     w_std = H ** -0.5
     for l in range(L):

@@ -1,11 +1,20 @@
-"""Generate the end-to-end golden trace (BASELINE config 0) by running the REFERENCE model classes
+"""Generate the end-to-end golden trace of the tiny CPU-runnable model by running the REFERENCE model classes
 and its CompactKVManager on CPU.
 
     PYTHONDONTWRITEBYTECODE=1 python tests/golden/make_golden_model.py --reference /path/to/FastDMS
 
 Tiny Llama-style DMS model, float32, 2 layers, hidden 256, 4 q / 2 KV heads, head_dim 64, MLP
 1024, vocab 1024, RoPE theta 500000, DMS window 16, eviction rate ~7/8; four ragged prompts of
-37/128/200/511 tokens; 32 greedy decode steps; compact KV in float32 and in FP8 e4m3.
+37/128/200/511 tokens; 128 greedy decode steps; compact KV in float32 and in FP8 e4m3.  Logits are
+kept for the first 32 steps and every 8th step after that (`logit_steps`), everything else for all
+steps.
+
+A third run ("bf16") loads the same weights rounded to bfloat16 (the LM head scaled by 0.2 so that
+logits stay below 2 in magnitude, where a bfloat16 ulp is well under the 2e-2 tolerance), keeps the
+FP8 compact KV and additionally records the raw DMS decision value of every (step, layer, sequence,
+KV head) -- the number that is compared with the threshold -- so that a test can tell a decision
+that sits on the threshold from one that does not.  Its greedy tokens are the history a test forces
+on the implementation under test.
 Weights and prompts come from `fastdms_b200.utils.synth` (an integer hash), so the tests rebuild
 the identical model without a checkpoint.
 
@@ -38,7 +47,9 @@ MODEL_CFG = dict(
     synthetic_hash_weights=True, torch_dtype="float32",
 )
 PROMPT_LENS = [37, 128, 200, 511]
-DECODE_STEPS = 32
+DECODE_STEPS = 128
+LOGIT_STEPS = sorted(set(range(32)) | set(range(32, DECODE_STEPS, 8)) | {DECODE_STEPS - 1})
+BF16_LM_HEAD_FACTOR = 0.2
 WINDOW, ALPHA_SCALE, ALPHA_OFFSET = 16, 100.0, 5.0
 SEED = 0
 
@@ -74,7 +85,7 @@ def index_store(key, value, compact_k, compact_v, slot_mapping):
     compact_v[flat] = value.reshape(-1, value.shape[-1]).to(compact_v.dtype)
 
 
-def run(reference: str, kv_dtype: torch.dtype, tag: str, out: dict) -> None:
+def run(reference: str, kv_dtype: torch.dtype, tag: str, out: dict, model_dtype: torch.dtype = torch.float32) -> None:
     import torch.distributed as dist
     from transformers import LlamaConfig
 
@@ -84,6 +95,7 @@ def run(reference: str, kv_dtype: torch.dtype, tag: str, out: dict) -> None:
     from fastdms.layers.compact_attention import compact_decode_attention_ref
     from fastdms.models.llama import LlamaForCausalLM
     from fastdms.sampling_params import SamplingParams
+    import fastdms.models.llama as ref_llama
     from fastdms.utils.context import get_context, reset_context, set_context
     from fastdms_b200.utils.synth import synth_llama_state_dict
 
@@ -94,11 +106,27 @@ def run(reference: str, kv_dtype: torch.dtype, tag: str, out: dict) -> None:
     ref_attention.compact_decode_attention = (
         lambda q, ck, cv, base, live, scale=None, **kw: compact_decode_attention_ref(q, ck, cv, base, live, scale=scale))
 
+    # raw decision values, in call order (one call per layer per forward)
+    decision_log: list[torch.Tensor] = []
+    original_extract = getattr(ref_llama.extract_dms_eviction_decisions, "__wrapped__", ref_llama.extract_dms_eviction_decisions)
+
+    def recording_extract(q, *, num_kv_heads, num_qo_heads, head_dim, **kw):
+        view = q.view(q.shape[0], num_kv_heads, num_qo_heads // num_kv_heads, head_dim)
+        decision_log.append(view[:, :, 0, -1].float().clone())
+        return original_extract(q, num_kv_heads=num_kv_heads, num_qo_heads=num_qo_heads, head_dim=head_dim, **kw)
+
+    recording_extract.__wrapped__ = original_extract
+    ref_llama.extract_dms_eviction_decisions = recording_extract
+
     cfg = {k: v for k, v in MODEL_CFG.items() if k not in ("lm_head_std", "synthetic_hash_weights", "torch_dtype", "model_type")}
     hf = LlamaConfig(**cfg)
-    torch.set_default_dtype(torch.float32)
+    torch.set_default_dtype(model_dtype)
     model = LlamaForCausalLM(hf)
-    sd = synth_llama_state_dict(MODEL_CFG, seed=SEED, alpha_scale=ALPHA_SCALE, alpha_offset=ALPHA_OFFSET)
+    torch.set_default_dtype(torch.float32)
+    synth_cfg = dict(MODEL_CFG)
+    if model_dtype != torch.float32:
+        synth_cfg["lm_head_factor"] = BF16_LM_HEAD_FACTOR
+    sd = synth_llama_state_dict(synth_cfg, seed=SEED, alpha_scale=ALPHA_SCALE, alpha_offset=ALPHA_OFFSET)
     packed = model.packed_modules_mapping
     for name, tensor in sd.items():
         for key, (target, shard) in packed.items():
@@ -121,7 +149,7 @@ def run(reference: str, kv_dtype: torch.dtype, tag: str, out: dict) -> None:
     seqs = [Sequence(p, SamplingParams(temperature=0.0, max_tokens=DECODE_STEPS + 1, ignore_eos=True)) for p in prompts]
     B = len(seqs)
     cache = model.model.layers[0].self_attn.rotary_emb.cos_sin_cache
-    out["cos_sin_cache"] = cache[: max(PROMPT_LENS) + DECODE_STEPS + 2, 0].numpy().copy()
+    out["cos_sin_cache"] = cache[: max(PROMPT_LENS) + DECODE_STEPS + 2, 0].float().numpy().copy()
 
     with torch.inference_mode():
         # ---- prefill (engine/model_runner.py:594-679) ----
@@ -136,16 +164,18 @@ def run(reference: str, kv_dtype: torch.dtype, tag: str, out: dict) -> None:
                     None, None, dms_capture_enabled=True, dms_alpha_scale=ALPHA_SCALE, dms_alpha_offset=ALPHA_OFFSET,
                     dms_layer_evictions={}, streaming_pack_manager=manager,
                     streaming_pack_seq_ids=[s.seq_id for s in seqs], streaming_pack_window_size=WINDOW)
+        decision_log.clear()
         hidden = model(torch.tensor(ids), torch.tensor(pos))
-        logits = model.compute_logits(hidden)
+        logits = model.compute_logits(hidden).float()
         ctx = get_context()
         out[f"{tag}_prefill_evict"] = torch.stack([ctx.dms_layer_evictions[l] for l in range(L)]).numpy().copy()
+        out[f"{tag}_prefill_decision_values"] = torch.stack(decision_log).numpy().copy()     # [L, tokens, Hk]
         reset_context()
         out[f"{tag}_prefill_logits"] = logits.numpy().copy()
         live0 = torch.stack([manager.seq_states[s.seq_id].live_counts for s in seqs], dim=1)     # [L, B, Hk]
         out[f"{tag}_prefill_live"] = live0.numpy().copy()
         tokens = logits.argmax(dim=-1).tolist()
-        all_tokens, step_logits, step_evict, step_live, step_slot = [tokens], [], [], [], []
+        all_tokens, step_logits, step_evict, step_live, step_slot, step_values = [tokens], [], [], [], [], []
         for s, t in zip(seqs, tokens):
             s.append_token(t)
         # ---- decode (engine/model_runner.py:713-772, 1105-1145) ----
@@ -156,8 +186,10 @@ def run(reference: str, kv_dtype: torch.dtype, tag: str, out: dict) -> None:
             set_context(False, compact_kv_enabled=True, compact_base_offsets=base, compact_live_counts=live,
                         compact_slot_mapping=slot, compact_max_live_count=cap, dms_capture_enabled=True,
                         dms_alpha_scale=ALPHA_SCALE, dms_alpha_offset=ALPHA_OFFSET, dms_layer_evictions={})
+            decision_log.clear()
             hidden = model(torch.tensor([s.last_token for s in seqs]), torch.tensor(positions))
-            logits = model.compute_logits(hidden)
+            logits = model.compute_logits(hidden).float()
+            step_values.append(torch.stack(decision_log).numpy().copy())                         # [L, B, Hk]
             ctx = get_context()
             ev = torch.stack([ctx.dms_layer_evictions[l] for l in range(L)])                     # [L, B, Hk]
             manager.record_appended_dms_decisions(seqs, positions, ctx.dms_layer_evictions, sync_stats=False)
@@ -166,12 +198,14 @@ def run(reference: str, kv_dtype: torch.dtype, tag: str, out: dict) -> None:
             for s, t in zip(seqs, tokens):
                 s.append_token(t)
             all_tokens.append(tokens)
-            step_logits.append(logits.numpy().copy())
+            if step in LOGIT_STEPS:
+                step_logits.append(logits.numpy().copy())
             step_evict.append(ev.numpy().copy())
             step_live.append(live.numpy().copy())
             step_slot.append((slot - base).numpy().copy())         # logical slot index of the appended row
     out[f"{tag}_tokens"] = np.array(all_tokens, dtype=np.int64)                 # [steps + 1, B]
-    out[f"{tag}_logits"] = np.stack(step_logits)                               # [steps, B, V]
+    out[f"{tag}_logits"] = np.stack(step_logits)                               # [len(LOGIT_STEPS), B, V]
+    out[f"{tag}_decision_values"] = np.stack(step_values)                      # [steps, L, B, Hk]
     out[f"{tag}_evict"] = np.stack(step_evict)                                 # [steps, L, B, Hk]
     out[f"{tag}_live"] = np.stack(step_live)                                   # [steps, L, B, Hk]
     out[f"{tag}_slot"] = np.stack(step_slot)                                   # [steps, L, B, Hk]
@@ -200,7 +234,9 @@ def main() -> None:
     out: dict[str, np.ndarray] = {}
     run(args.reference, torch.float32, "f32", out)
     run(args.reference, torch.float8_e4m3fn, "fp8", out)
+    run(args.reference, torch.float8_e4m3fn, "bf16", out, model_dtype=torch.bfloat16)
     out["prompt_lens"] = np.array(PROMPT_LENS)
+    out["logit_steps"] = np.array(LOGIT_STEPS)
     path = HERE / "model_golden.npz"
     np.savez_compressed(path, **out)
     print(f"wrote {path} ({path.stat().st_size / 1024:.1f} KiB)")

@@ -227,7 +227,7 @@ def test_chunked_pack_leaves_the_one_pass_state(dev, paged, row_index, chunk):
 
 
 def _tiny_engine(dev, chunk, paged, dtype="bfloat16", kv="float8_e4m3fn"):
-    from fastdms_b200.bench_model import SHAPES
+    from fastdms_b200.utils.shapes import SHAPES
     from fastdms_b200.engine.llm_engine import LLMEngine
     hf = dict(SHAPES["tiny"])
     hf.update(attention_bias=True, torch_dtype=dtype, max_position_embeddings=1024)

@@ -1,4 +1,4 @@
-"""Full-size checks on the benchmark workload (BASELINE configs[1] as 16 layer pools: c=8, 32 q / 8 KV
+"""Full-size checks on the benchmark workload (the op-level compact decode on Llama-3.2-1B shapes, as 16 layer pools: c=8, 32 q / 8 KV
 heads, head_dim 64, about 1280 live rows per span, FP8 + per-head scales, permuted 16-row pages),
 through properties that do not need the CPU oracle at this size:
   * attention against a float32 torch computation on the dequantised, gathered pool;

@@ -455,17 +455,19 @@ def test_capacity_errors(dev):
         _mgr(dev, num_layers=1, num_kv_heads=2, capacity_tokens=0, max_model_len=64, head_dim=16, compact_dtype=torch.float32)
 
 
-@pytest.mark.parametrize("paged", [False, True])
-def test_hot_path_step_equals_the_manual_kernel_sequence(dev, paged):
+@pytest.mark.parametrize("paged,gap", [(False, False), (True, False), (True, True), (False, True)])
+def test_hot_path_step_equals_the_manual_kernel_sequence(dev, paged, gap):
     """DecodeHotPath (one graph replay: expiry, metadata, a fused store+attention launch per layer,
     recording with position advance) against the same step issued kernel by kernel with the separate
     store and attention launches on a twin manager: identical outputs and metadata after every step,
-    through step_device, step_host and step_host_block."""
+    through step_device, step_host and step_host_block.  With `gap` an earlier sequence has been freed,
+    so the active slots are not contiguous (0, 2, 3) and the batch's block tables are a gathered copy
+    that has to follow the pages the 30 steps add (every span crosses a 16-row page boundary)."""
     from fastdms_b200.engine.hot_path import DecodeHotPath
     from fastdms_b200.layers.compact_attention import compact_decode_attention, fused_dms_rope_store_compact_decode
     L, B, Hk, G, D, W = 2, 3, 2, 4, 64, 16
     Hq = Hk * G
-    T0 = [70, 300, 141]
+    T0 = [70, 50, 300, 141] if gap else [70, 300, 141]
     rng = np.random.default_rng(5 + int(paged))
     gen = torch.Generator(device=dev).manual_seed(9)
     half = D // 2
@@ -493,6 +495,11 @@ def test_hot_path_step_equals_the_manual_kernel_sequence(dev, paged):
         for m, seqs in ((mA, seqsA), (mB, seqsB)):
             m.streaming_pack_layer(layer_id=l, k=k, v=v, evict_mask=ev, cu_seqlens_q=cu, seq_ids=[s.seq_id for s in seqs],
                                    window_size=W)
+    if gap:
+        for m, seqs in ((mA, seqsA), (mB, seqsB)):
+            m.free(seqs.pop(1).seq_id)
+        T0 = [T0[0]] + T0[2:]
+        assert mA._contiguous_active_slot_start(mA._states(seqsA)) is None
     hp = DecodeHotPath(mA, seqsA, num_q_heads=Hq, window_size=W, alpha_scale=100.0, alpha_offset=5.0, cos_sin_cache=cache)
     assert hp.fuse_store and hp.launches_per_step == 2 + L + 1
     pos0 = torch.tensor(T0, dtype=torch.int64)
@@ -502,12 +509,12 @@ def test_hot_path_step_equals_the_manual_kernel_sequence(dev, paged):
     base, live, slot = (torch.zeros((L, B, Hk), device=dev, dtype=torch.int32) for _ in range(3))
     evB = torch.zeros((L, B, Hk), device=dev, dtype=torch.bool)
     outB = torch.zeros((L, B, Hq, D), device=dev, dtype=torch.bfloat16)
-    btB = mB.decode_block_tables(seqsB)
     host_block = None
 
     def manual_step(q, k, v):
         mB.expire_device(slotsB, posB, window_size=W)
         mB.decode_metadata_device(slotsB, base, live, slot)
+        btB = mB.decode_block_tables(seqsB)        # after the metadata launch: it may have added pages
         for l in range(L):
             ks, vs = mB.layer_scales(l)
             ql = q[l].clone()

@@ -230,7 +230,7 @@ def test_attention_ragged_scaled(dev, D, G, paged):
 
 
 def test_attention_config2_shape(dev):
-    """BASELINE config 2: 8 sequences, 32 q / 8 KV heads, head_dim 64, live = 1024 +- 128 + 256,
+    """The op-level benchmark shape: 8 sequences, 32 q / 8 KV heads, head_dim 64, live = 1024 +- 128 + 256,
     16-row pages with randomly permuted block tables, per-head absmax scales."""
     from fastdms_b200.layers.compact_attention import compact_decode_attention
     rng = np.random.default_rng(0)
@@ -642,3 +642,78 @@ def test_fused_norm_linear_matches_the_two_modules(dev, dtype, rows, n, k, with_
     eps = 2.0 ** -6 if dtype == torch.bfloat16 else 2.0 ** -9
     assert ((y.float() - ref).abs() <= eps * ref.abs() + 2e-2).all()
     assert ((y.float() - y0.float()).abs() <= eps * ref.abs() + 2e-2).all()
+
+
+def test_page_pops_are_all_or_nothing_when_the_stack_runs_dry(dev):
+    """160 spans ask for 1..12 pages each from a stack that holds about half of the total.  A span
+    gets all of its pages or none; granted ids are distinct and disjoint from what is left on the
+    stack; the counter equals initial - granted; after freeing, the stack is a permutation of every id."""
+    from fastdms_b200 import _lib
+    lib = _lib.lib()
+    rng = np.random.default_rng(77)
+    num_seqs, hk, max_pages = 20, 8, 12
+    need_pages = rng.integers(1, max_pages + 1, size=(num_seqs, hk)).astype(np.int32)
+    total = int(need_pages.sum()) // 2
+    rows = torch.from_numpy((need_pages * 16 - rng.integers(0, 16, size=need_pages.shape)).astype(np.int32)).to(dev)
+    bt = torch.full((num_seqs, hk, max_pages), -1, dtype=torch.int32, device=dev)
+    stack = torch.from_numpy(rng.permutation(total).astype(np.int32)).to(dev)
+    count = torch.tensor([total], dtype=torch.int32, device=dev)
+    status = _lib.status_word(dev)
+    for _ in range(2):                                   # second round: the same pops on the refilled stack
+        with torch.cuda.device(dev):
+            _lib.check(lib.fdms_alloc_pages(rows.data_ptr(), bt.data_ptr(), bt.stride(0), bt.stride(1), max_pages, None,
+                                            stack.data_ptr(), count.data_ptr(), num_seqs, hk, status.data_ptr(),
+                                            _lib.stream_ptr(dev)))
+        assert _lib.read_device_status(dev) == _lib.DEV_BAD_INDEX      # some spans must have been refused
+        got = bt.cpu().numpy()
+        left = int(count.item())
+        granted = []
+        for s in range(num_seqs):
+            for h in range(hk):
+                n = int(need_pages[s, h])
+                ids = got[s, h, :n]
+                assert (ids >= 0).all() or (ids == -1).all(), "a span was given part of its pages"
+                assert (got[s, h, n:] == -1).all()
+                if ids[0] >= 0:
+                    granted.extend(ids.tolist())
+        assert 0 <= left and left + len(granted) == total, "pages were lost or invented"
+        remaining = stack.cpu().numpy()[:left].tolist()
+        assert sorted(granted + remaining) == list(range(total)), "a page is owned twice or leaked"
+        live = torch.zeros((num_seqs, hk), dtype=torch.int32, device=dev)
+        with torch.cuda.device(dev):
+            _lib.check(lib.fdms_free_pages(live.data_ptr(), live.stride(0), bt.data_ptr(), bt.stride(0), bt.stride(1), max_pages,
+                                           None, stack.data_ptr(), count.data_ptr(), total, num_seqs, hk, status.data_ptr(),
+                                           _lib.stream_ptr(dev)))
+        assert int(count.item()) == total and sorted(stack.cpu().numpy().tolist()) == list(range(total))
+        assert (bt.cpu().numpy() == -1).all()
+
+
+def test_split_k_workspace_survives_growth_of_the_batch(dev, monkeypatch):
+    """A graph captured for a small batch keeps the raw address of the split-K workspace.  Asking for
+    a workspace for a larger problem afterwards must not move or free it: the replay after other
+    allocations still equals the eager result."""
+    from fastdms_b200 import _lib
+    from fastdms_b200.layers.compact_attention import compact_decode_attention
+    monkeypatch.setenv("FDMS_ATTN_SPLITS", "2")
+    monkeypatch.setenv("FDMS_ATTN_CHUNKS", "3")          # several clusters per span: the workspace is used
+    rng = np.random.default_rng(3)
+    q, kq, vq, base, live, bt, ks, vs = _config2_case(rng, 2, 2, 4, 64, 700, 100, 9, True)
+    qb = torch.from_numpy(q).to(dev).to(torch.bfloat16)
+    args = (qb, t_fp8(kq, dev), t_fp8(vq, dev), torch.from_numpy(base).to(dev), torch.from_numpy(live).to(dev))
+    kw = dict(block_tables=torch.from_numpy(bt).to(dev), k_scale=torch.from_numpy(ks).to(dev), v_scale=torch.from_numpy(vs).to(dev))
+    out = torch.empty_like(qb)
+    want = compact_decode_attention(*args, **kw).clone()
+    before = _lib.attn_workspace(dev, 2, 2, 64).data_ptr()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        compact_decode_attention(*args, out=out, **kw)
+    # a larger batch and a larger head_dim, then unrelated allocations that would reuse a freed block
+    assert _lib.attn_workspace(dev, 4096, 8, 128).data_ptr() == before
+    assert _lib.attn_workspace(dev, 9, 8, 256).data_ptr() == before
+    junk = [torch.full((1 << 20,), 7.0, device=dev) for _ in range(8)]
+    for _ in range(3):
+        out.zero_()
+        g.replay()
+        torch.cuda.synchronize(dev)
+        assert torch.equal(out, want)
+    del junk

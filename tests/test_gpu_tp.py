@@ -1,4 +1,4 @@
-"""Tensor parallelism by KV head (the 8B-shape partition) on two GPUs, checked on BASELINE config 0:
+"""Tensor parallelism by KV head (the 8B-shape partition) on two GPUs, checked on the tiny CPU-runnable model:
 two ranks, one KV head each, NCCL all-reduce after o_proj and down_proj, against the same reference
 trace as the single-GPU test.  DMS state is per KV head, so each rank's decisions and compact
 lengths must equal that head's columns of the trace; tokens must be identical.  The float32 case
@@ -97,7 +97,7 @@ def test_tp2_by_kv_head_matches_reference_trace(tag, kv_dtype):
         assert np.array_equal(r["prefill_live"], golden[f"{tag}_prefill_live"][:, :, rank:rank + 1])
         assert np.array_equal(r["evict"], golden[f"{tag}_evict"][:, :, :, rank:rank + 1]), f"rank {rank}: decisions differ"
         assert np.array_equal(r["live"], golden[f"{tag}_live"][:, :, :, rank:rank + 1]), f"rank {rank}: compact lengths differ"
-        assert np.abs(r["logits"] - golden[f"{tag}_logits"]).max() < 2e-2
+        assert np.abs(r["logits"][golden["logit_steps"]] - golden[f"{tag}_logits"]).max() < 2e-2
 
 
 def _allreduce_rank(rank: int, world: int, out_q) -> None:
