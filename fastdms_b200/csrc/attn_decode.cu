@@ -40,7 +40,6 @@ namespace fdms {
 constexpr int kPage = 16;
 constexpr int kConsumerWarps = 8;
 constexpr int kConsumerThreads = kConsumerWarps * 32;
-constexpr int kFastThreads = kConsumerThreads + 32;   // + one producer warp
 constexpr int kMaxGroup = 8;
 constexpr int kMaxSplits = 16;           // cluster size limit (8 portable, 16 with the opt-in attribute)
 constexpr int kMaxChunks = 64;           // clusters per span
@@ -582,132 +581,243 @@ __device__ __forceinline__ void fold_and_write(const AttnParams& p, float* s_m, 
     }
 }
 
-template <int D>
-__global__ void __launch_bounds__(kFastThreads, (D == 64 ? 2 : 1)) attn_decode_fast_kernel(AttnParams p) {
+// ------------------------------------------------------------------------------------------------
+// Staged variant of the fast kernel.  Every warp owns a ring of R page slots in shared memory (a slot
+// holds the K page and the V page of one 16-row page) and one mbarrier per slot.  Lane s of the warp
+// is the issuer of slot s: it resolves the page (block table or span base), arms the barrier with the
+// byte count and starts two bulk asynchronous copies (cp.async.bulk, the TMA unit's untiled form,
+// no multicast) that complete on it; all lanes then wait on the barrier, read their MMA fragments from
+// the slot and lane s refills it with the warp's page R further on.  There is no producer warp and no
+// CTA-wide barrier in the page loop: eight issuers per CTA run in parallel, the prefetch depth costs
+// no registers, and a CTA whose range fits its rings (R pages per warp) has ALL of its K/V in flight
+// before the dependency on the preceding kernel is resolved.  With one CTA per SM and at most half an
+// SM's shared memory per CTA, the CTAs of the next launch of the stream are resident next to this
+// launch's, so their copies run under this launch's math and merge.
+// Every mbarrier wait is bounded; when one runs out the warp raises FDMS_DEV_WAIT_TIMEOUT, stops
+// issuing, gives its copies in flight a short time to land and goes on to the merge.
+// ------------------------------------------------------------------------------------------------
+constexpr int kMaxRing = 8;
+
+template <int D, bool APPEND>
+__global__ void __launch_bounds__(kConsumerThreads, (D == 64 ? 2 : 1)) attn_decode_staged_kernel(AttnParams p) {
     using C = FastCfg<D>;
+    constexpr int half = D / 2;
     extern __shared__ __align__(128) uint8_t smem[];
-    const int NS = p.stages;
+    const int R = p.stages;                       // ring slots per warp, 1..kMaxRing
     const int S = p.splits, CH = p.chunks, G = p.group;
-    // shared memory carve-up
-    uint8_t* s_stage = smem;
-    uint64_t* s_full = (uint64_t*)(s_stage + (size_t)NS * C::kStageBytes);
-    uint64_t* s_empty = s_full + NS;
-    float* s_m = (float*)(s_empty + NS);                      // [warps][8]
-    float* s_l = s_m + kConsumerWarps * kMaxGroup;            // [warps][8]
-    float* s_o = s_l + kConsumerWarps * kMaxGroup;            // [warps][8][D]
-    float* r_ml = s_o + kConsumerWarps * kMaxGroup * kPartialStride<D>;       // [S][G][2]   partials received from the cluster
-    float* r_o = r_ml + S * G * 2;                            // [S][G][D]
-    __shared__ int s_abort, s_last;
+    uint8_t* s_ring = smem;                                                   // [warps][R][K page | V page]
+    uint64_t* s_bar = (uint64_t*)(s_ring + (size_t)kConsumerWarps * R * C::kStageBytes);   // [warps][R]
+    float* s_m = (float*)(s_bar + kConsumerWarps * kMaxRing);                 // [warps][8]
+    float* s_l = s_m + kConsumerWarps * kMaxGroup;                            // [warps][8]
+    float* s_o = s_l + kConsumerWarps * kMaxGroup;                            // [warps][8][D + 4]
+    float* r_ml = s_o + kConsumerWarps * kMaxGroup * kPartialStride<D>;       // [S][G][2]
+    float* r_o = r_ml + S * G * 2;                                            // [S][G][D]
+    __shared__ int s_last;
+    __shared__ __align__(16) __half s_q[APPEND ? kMaxGroup * D : 8];          // rotated q, [G][D]
+    __shared__ __align__(16) uint8_t s_new[APPEND ? 2 * D : 16];              // new K row | new V row (FP8)
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int g = lane >> 2, t = lane & 3;
     const int item = blockIdx.y;
-    const int rank = blockIdx.x % S;            // == rank of this CTA in its cluster
+    const int rank = blockIdx.x % S;
     const int chunk = blockIdx.x / S;
     const int part = chunk * S + rank, nparts = S * CH;
     const int b = item / p.hk, h = item - b * p.hk;
 
     if (S > 1) cluster_arrive_relaxed();        // phase 1: "every CTA of the cluster has started"
     grid_launch_dependents();
+    if (tid == 0) s_last = 0;
 
-    // Pages are dealt round-robin: this CTA owns pages part, part + nparts, ... of the span, so the
-    // producer can fetch its block-table entries before the span length is known.
-    const bool producer = warp == kConsumerWarps;
+    uint8_t* ring = s_ring + (size_t)warp * R * C::kStageBytes;
+    uint64_t* bars = s_bar + warp * kMaxRing;
+    if (lane < R) mbar_init(&bars[lane], 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    __syncwarp();
+
+    // Pages are dealt round-robin twice, as in the direct kernel: warp-local page i is span page
+    // pg0 + i * stride_pg.  Lane s looks after the pages i = s, s + R, s + 2R, ...
     const int32_t* btrow = p.bt ? p.bt + (int64_t)b * p.bt_sb + (int64_t)h * p.bt_sh : nullptr;
-    int32_t bt_first = -1;
-    if (producer && btrow) {
-        const int pi = part + lane * nparts;
-        if (pi < p.bt_pages) bt_first = btrow[pi];
+    const int stride_pg = kConsumerWarps * nparts;
+    const int pg0 = part + warp * nparts;
+    int32_t my_id = 0;                           // page id of the page this lane issues next
+    if (btrow && lane < R) {
+        const int pi = pg0 + lane * stride_pg;
+        if (pi < p.bt_pages) my_id = btrow[pi];
     }
     const int live = max(0, p.live[(int64_t)b * p.meta_sb + h]);
+    const int64_t base = p.bt ? 0 : (int64_t)p.base[(int64_t)b * p.meta_sb + h];
     const int npg = (live + kPage - 1) / kPage;
-    const int npages = part < npg ? (npg - part + nparts - 1) / nparts : 0;
+    const int nw = pg0 < npg ? (npg - pg0 + stride_pg - 1) / stride_pg : 0;     // pages of this warp
+    const int tail_pi = npg - 1;
 
-    if (tid == 0) { s_abort = 0; s_last = 0; }
-    for (int s = tid; s < NS; s += kFastThreads) { mbar_init(&s_full[s], 1); mbar_init(&s_empty[s], 1); }
-    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    __syncthreads();
-    volatile int* v_abort = &s_abort;
-
-    if (producer) {
-        // =============================== producer warp =========================================
-        // The span's last page holds the row that the store kernel of this step has just written;
-        // it is fetched only after the dependency on the preceding kernel has been resolved.
-        const int64_t base = p.bt ? 0 : (int64_t)p.base[(int64_t)b * p.meta_sb + h];
-        auto issue = [&](int j, int pi, int32_t page_id) {
-            const int rows = min(kPage, live - pi * kPage);
-            const int64_t row0 = btrow ? (int64_t)page_id * kPage : base + (int64_t)pi * kPage;
-            const int slot = j % NS;
-            bool ok = true;
-            if (j >= NS) ok = mbar_wait(&s_empty[slot], ((j / NS) - 1) & 1, kWaitLimit);
-            if (!ok) {
-                *v_abort = 1;
-                if (p.dev_status) atomicOr(p.dev_status, FDMS_DEV_WAIT_TIMEOUT);
-            } else if (row0 < 0 || row0 + rows > p.pool_rows) {
-                // bad address: flag it and complete the stage without copying
-                if (p.dev_status) atomicOr(p.dev_status, FDMS_DEV_BAD_INDEX);
-                mbar_arrive(&s_full[slot]);
-            } else {
-                const uint32_t bytes = (uint32_t)rows * D;
-                uint8_t* dst = s_stage + (size_t)slot * C::kStageBytes;
-                mbar_expect_tx(&s_full[slot], 2 * bytes);
-                bulk_g2s(dst, p.k_pool + row0 * D, bytes, &s_full[slot]);
-                bulk_g2s(dst + C::kPageBytes, p.v_pool + row0 * D, bytes, &s_full[slot]);
-            }
-        };
-        int tail_j = -1;
-        int32_t tail_id = -1;
-        for (int j0 = 0; j0 < npages; j0 += 32) {
-            const int j = j0 + lane;
-            const int pi = part + j * nparts;
-            if (j < npages && *v_abort == 0) {
-                const int32_t id = btrow ? (j0 == 0 ? bt_first : btrow[pi]) : 0;
-                if (pi == npg - 1) { tail_j = j; tail_id = id; }       // fetched after the dependency wait
-                else issue(j, pi, id);
-            }
-            __syncwarp();
-        }
-        grid_dependency_wait();
-        if (tail_j >= 0 && *v_abort == 0) issue(tail_j, part + tail_j * nparts, tail_id);
-        __syncwarp();
-        if (S > 1) {                             // the producer takes part in both cluster phases
-            cluster_wait_acquire();
-            cluster_arrive_release();
-            cluster_wait_acquire();
-        }
-        return;
+    // fused append: see the direct kernel
+    constexpr int kItemsK = half, kItemsV = D / 2;
+    const bool tail_cta = APPEND && live > 0 && (tail_pi % nparts) == part;
+    const int n_items = APPEND ? G * half + (tail_cta ? kItemsK + kItemsV : 0) : 0;
+    const float* cs_row = APPEND ? p.rope_cs + checked_rope_position(p, b) * p.rope_stride : nullptr;
+    // the cos/sin pair of this thread's first rotation item does not depend on the preceding kernel
+    float pre_c = 1.0f, pre_s = 0.0f;
+    if (APPEND && tid < n_items && tid < G * half + kItemsK) {
+        const int i = tid < G * half ? tid % half : tid - G * half;
+        pre_c = cs_row[i];
+        pre_s = cs_row[half + i];
     }
 
-    // ================================= consumer warps ===========================================
-    const int g = lane >> 2, t = lane & 3;
-    const float sl2 = p.scale * (p.k_scale ? p.k_scale[h] : 1.0f) * kLog2e;
-    grid_dependency_wait();                      // q is written by the preceding kernel (RoPE in place)
-    uint32_t qa[C::kKSteps][2];
-    load_q_frags<D>(p, b, h, g, t, qa);
+    // Issues warp-local page i into slot i % R (called by the slot's lane only).  Returns false when
+    // the page address is out of range: the slot's barrier is completed without a copy and the page is
+    // skipped by the consumer.
+    auto issue = [&](int i, int32_t id) -> bool {
+        const int s = i % R;
+        const int pi = pg0 + i * stride_pg;
+        const int rows = min(kPage, live - pi * kPage);
+        // in append mode the span's last row is not in the pool yet: it is patched into the slot
+        const int have = (APPEND && pi == tail_pi) ? rows - 1 : rows;
+        const int64_t row0 = btrow ? (int64_t)id * kPage : base + (int64_t)pi * kPage;
+        if (row0 < 0 || row0 + rows > p.pool_rows) {
+            if (p.dev_status) atomicOr(p.dev_status, FDMS_DEV_BAD_INDEX);
+            mbar_arrive(&bars[s]);
+            return false;
+        }
+        if (have == 0) { mbar_arrive(&bars[s]); return true; }
+        const uint32_t bytes = (uint32_t)have * D;
+        uint8_t* dst = ring + (size_t)s * C::kStageBytes;
+        // the warp's reads of the slot (generic proxy) are ordered before the copy's writes (async proxy)
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        mbar_expect_tx(&bars[s], 2 * bytes);
+        bulk_g2s(dst, p.k_pool + row0 * D, bytes, &bars[s]);
+        bulk_g2s(dst + C::kPageBytes, p.v_pool + row0 * D, bytes, &bars[s]);
+        return true;
+    };
+    auto next_id = [&](int i) {                  // start fetching the id of warp-local page i
+        const int pi = pg0 + i * stride_pg;
+        if (btrow && pi < npg && pi < p.bt_pages) my_id = btrow[pi];
+    };
 
+    bool my_ok = true;
+    // Without append the span's last page holds the row that the preceding kernel of the stream (the
+    // store) has just written; it is fetched only after the dependency has been resolved.
+    const bool my_first = lane < R && lane < nw;
+    const bool deferred = !APPEND && my_first && pg0 + lane * stride_pg == tail_pi;
+    if (my_first && !deferred) {
+        my_ok = issue(lane, my_id);
+        next_id(lane + R);
+    }
+    int64_t tail_row = -1;                           // pool row of the new token (block tables are older state)
+    if (APPEND && tail_cta) {
+        const int64_t trow0 = btrow ? (tail_pi < p.bt_pages ? (int64_t)btrow[tail_pi] * kPage : -1)
+                                    : base + (int64_t)tail_pi * kPage;
+        const int64_t r = trow0 + (live - 1 - tail_pi * kPage);
+        tail_row = (trow0 >= 0 && r < p.pool_rows) ? r : -2;
+    }
+    grid_dependency_wait();
+    if (deferred) {
+        my_ok = issue(lane, my_id);
+        next_id(lane + R);
+    }
+
+    const float sl2 = p.scale * (p.k_scale ? p.k_scale[h] : 1.0f) * kLog2e;
+    uint32_t qa[C::kKSteps][2];
+    if (APPEND) {
+        for (int it = tid; it < n_items; it += kConsumerThreads) {
+            if (it < G * half + kItemsK) {
+                // one rotation pair of a q head (it < G * half) or of the new K row
+                const bool isq = it < G * half;
+                const int gg = isq ? it / half : 0, i = isq ? it - gg * half : it - G * half;
+                const void* src = isq ? p.q : p.k_new;
+                const int64_t row = isq ? (int64_t)b * p.q_sb + (int64_t)(h * G + gg) * p.q_sh
+                                        : (int64_t)b * p.kn_sb + (int64_t)h * p.kn_sh;
+                const float x1 = load_as_float(src, row + i, p.q_dtype);
+                float x2 = load_as_float(src, row + half + i, p.q_dtype);
+                const float c = it == tid ? pre_c : cs_row[i], sn = it == tid ? pre_s : cs_row[half + i];
+                if (isq && gg == 0 && i == half - 1) {
+                    // the group's first q head carries the DMS decision in its last channel
+                    if (tail_cta && p.evict_out) p.evict_out[(int64_t)b * p.evict_sb + h] = p.rule.evict(x2) ? 1 : 0;
+                    x2 = 0.0f;
+                }
+                // float32, unfused, rounded to the activation dtype: the store kernel's arithmetic
+                const float lo = round_to_dtype(__fsub_rn(__fmul_rn(x1, c), __fmul_rn(x2, sn)), p.q_dtype);
+                const float hi = round_to_dtype(__fadd_rn(__fmul_rn(x2, c), __fmul_rn(x1, sn)), p.q_dtype);
+                if (isq) {
+                    s_q[gg * D + i] = __float2half_rn(lo);
+                    s_q[gg * D + half + i] = __float2half_rn(hi);
+                } else {
+                    const float ksc = p.k_scale ? p.k_scale[h] : 1.0f;
+                    const uint8_t bl = float_to_e4m3(p.k_scale ? __fdiv_rn(lo, ksc) : lo);
+                    const uint8_t bh = float_to_e4m3(p.k_scale ? __fdiv_rn(hi, ksc) : hi);
+                    s_new[i] = bl;
+                    s_new[half + i] = bh;
+                    if (tail_row >= 0) {
+                        p.k_pool_w[tail_row * D + i] = bl;
+                        p.k_pool_w[tail_row * D + half + i] = bh;
+                    }
+                    if (tail_row == -2 && i == 0 && p.dev_status) atomicOr(p.dev_status, FDMS_DEV_BAD_INDEX);
+                }
+            } else {
+                // two elements of the new V row
+                const int i = 2 * (it - G * half - kItemsK);
+                const int64_t e0 = (int64_t)b * p.vn_sb + (int64_t)h * p.vn_sh + i;
+                float y0 = load_as_float(p.v_new, e0, p.q_dtype), y1 = load_as_float(p.v_new, e0 + 1, p.q_dtype);
+                if (p.v_scale) { const float vsc = p.v_scale[h]; y0 = __fdiv_rn(y0, vsc); y1 = __fdiv_rn(y1, vsc); }
+                const uchar2 bv = make_uchar2(float_to_e4m3(y0), float_to_e4m3(y1));
+                *(uchar2*)(s_new + D + i) = bv;
+                if (tail_row >= 0) *(uchar2*)(p.v_pool_w + tail_row * D + i) = bv;
+            }
+        }
+        __syncthreads();
+#pragma unroll
+        for (int ch = 0; ch < C::kCh; ++ch) {
+            uint4 w0 = make_uint4(0u, 0u, 0u, 0u), w1 = w0;
+            if (g < G) {
+                const uint4* src = (const uint4*)(s_q + g * D + 64 * ch + 16 * t);
+                w0 = src[0]; w1 = src[1];
+            }
+            qa[4 * ch + 0][0] = w0.x; qa[4 * ch + 0][1] = w0.y; qa[4 * ch + 1][0] = w0.z; qa[4 * ch + 1][1] = w0.w;
+            qa[4 * ch + 2][0] = w1.x; qa[4 * ch + 2][1] = w1.y; qa[4 * ch + 3][0] = w1.z; qa[4 * ch + 3][1] = w1.w;
+        }
+    } else {
+        load_q_frags<D>(p, b, h, g, t, qa);
+    }
+
+    const int r_new = live - 1 - tail_pi * kPage;            // row of the new token inside the span's last page
     float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.0f, 0.0f};
     float o[C::kNT / 2][4];
 #pragma unroll
     for (int j = 0; j < C::kNT / 2; ++j) { o[j][0] = 0.0f; o[j][1] = 0.0f; o[j][2] = 0.0f; o[j][3] = 0.0f; }
 
-    for (int j = warp; j < npages; j += kConsumerWarps) {
-        const int slot = j % NS;
-        const bool aborted = *v_abort != 0;
-        const bool ok = mbar_wait(&s_full[slot], (j / NS) & 1, aborted ? kWaitLimitDrain : kWaitLimit);
-        if (!ok && !aborted) {
-            *v_abort = 1;
+    int issued = min(nw, R);                     // warp-local pages whose slot has been armed
+    int s = 0;
+    uint32_t phase = 0;
+    for (int i = 0; i < nw; ++i) {
+        const bool landed = mbar_wait(&bars[s], phase, kWaitLimit);
+        if (!__all_sync(0xffffffffu, landed)) {
             if (lane == 0 && p.dev_status) atomicOr(p.dev_status, FDMS_DEV_WAIT_TIMEOUT);
+            for (int j = i + 1; j < issued; ++j) mbar_wait(&bars[j % R], (uint32_t)(j / R) & 1u, kWaitLimitDrain);
+            break;
         }
-        if (ok && !aborted) {
-            const uint8_t* Ks = s_stage + (size_t)slot * C::kStageBytes;
-            const int rows = min(kPage, live - (part + j * nparts) * kPage);
+        const int pi = pg0 + i * stride_pg;
+        const int rows = min(kPage, live - pi * kPage);
+        const bool good = __shfl_sync(0xffffffffu, my_ok, s);
+        uint8_t* Ks = ring + (size_t)s * C::kStageBytes;
+        if (APPEND && pi == tail_pi) {
+            // the new row of the span is not in the pool image the copy brought: write it into the slot
+            if (lane < D / 16) *(uint4*)(Ks + r_new * D + 16 * lane) = *(const uint4*)(s_new + 16 * lane);
+            else if (lane < D / 8) *(uint4*)(Ks + C::kPageBytes + r_new * D + 16 * (lane - D / 16)) = *(const uint4*)(s_new + D + 16 * (lane - D / 16));
+            __syncwarp();
+        }
+        if (good) {
             PageFrags<D> f;
             load_frags_smem<D>(Ks, Ks + C::kPageBytes, g, t, f);
             process_page<D, false>(f, rows, g, t, sl2, qa, m_run, l_run, o);
         }
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&s_empty[slot]);
+        __syncwarp();                             // every lane has consumed its fragments of the slot
+        if (i + R < nw && lane == s) {
+            my_ok = issue(i + R, my_id);
+            next_id(i + 2 * R);
+        }
+        if (i + R < nw) ++issued;
+        if (++s == R) { s = 0; phase ^= 1u; }
     }
-
+    __syncthreads();                              // s_last initialised, all warps done with their pages
     fold_and_write<D>(p, s_m, s_l, s_o, r_ml, r_o, &s_last, tid, warp, g, t, b, h, item, rank, chunk, m_run, l_run, o);
 }
 
@@ -1025,9 +1135,9 @@ static int env_int(const char* name, int dflt) {
     return atoi(v);
 }
 
-static size_t fast_smem_bytes(int D, int stages, int splits, int group) {
-    size_t s = (size_t)stages * 2 * kPage * D;          // ring
-    s += (size_t)stages * 2 * sizeof(uint64_t);         // barriers
+static size_t staged_smem_bytes(int D, int ring, int splits, int group) {
+    size_t s = (size_t)kConsumerWarps * ring * 2 * kPage * D;       // per-warp rings
+    s += (size_t)kConsumerWarps * kMaxRing * sizeof(uint64_t);     // barriers
     s += (size_t)kConsumerWarps * kMaxGroup * (2 + D + 4) * sizeof(float);
     s += (size_t)splits * group * (2 + D) * sizeof(float);
     return s + 128;
@@ -1070,8 +1180,8 @@ static void fill_launch_config(cudaLaunchConfig_t& cfg, cudaLaunchAttribute* att
 // Whether a cluster of `splits` CTAs with `smem` bytes each can be resident on this device.
 // Asked once per (kernel variant, splits, smem) and remembered.
 static bool cluster_fits(AttnKernel kern, int variant, int threads, int splits, size_t smem) {
-    static size_t known_smem[6][kMaxSplits + 1] = {{0}};
-    static int known[6][kMaxSplits + 1] = {{0}};     // 0 unknown, 1 fits, -1 does not
+    static size_t known_smem[8][kMaxSplits + 1] = {{0}};
+    static int known[8][kMaxSplits + 1] = {{0}};     // 0 unknown, 1 fits, -1 does not
     if (splits == 1) return true;
     if (known[variant][splits] != 0 && known_smem[variant][splits] == smem) return known[variant][splits] > 0;
     bool ok = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) == cudaSuccess;
@@ -1209,24 +1319,35 @@ static int32_t attn_decode_common(
     if (fast) {
         const DeviceInfo di = device_info();
         FDMS_REQUIRE(di.ok && di.sms > 0, FDMS_E_CUDA, "fdms_attn_decode: cannot query the device");
-        const int ctas_per_sm = head_dim == 64 ? 2 : 1;
-        const int target = di.sms * ctas_per_sm;
-        int stages = env_int("FDMS_ATTN_STAGES", 32);
-        if (stages < 32) stages = 32;
-        // Loader: "direct" (default) reads pages straight into registers; "tma" stages them in shared
-        // memory with bulk copies.
+        // Loader: "direct" reads pages straight into registers; "staged" (FDMS_ATTN_LOADER=staged)
+        // brings them into per-warp shared-memory rings with bulk copies.
         const char* loader = getenv("FDMS_ATTN_LOADER");
-        const bool direct = app != nullptr || !(loader && loader[0] == 't');
-        const int variant = (app ? 4 : direct ? 0 : 2) + (head_dim == 64 ? 0 : 1);
+        const bool direct = !(loader && loader[0] == 's');
+        const int ctas_per_sm = head_dim == 64 ? 2 : 1;
+        // The staged kernel aims at ONE CTA per SM and at most half of an SM's shared memory per CTA
+        // (head_dim 64), so that the next launch of the stream is resident beside this one and its
+        // copies run under this launch's math; FDMS_ATTN_WAVE=2 fills both CTA slots with one launch.
+        int wave = env_int("FDMS_ATTN_WAVE", 0);
+        if (wave < 1) wave = direct ? ctas_per_sm : 1;
+        if (wave > ctas_per_sm) wave = ctas_per_sm;
+        const int target = di.sms * wave;
+        int ring = env_int("FDMS_ATTN_RING", 0);
+        if (ring < 1) ring = 5;
+        if (ring > kMaxRing) ring = kMaxRing;
+        const int variant = (app ? 2 : 0) + (head_dim == 64 ? 0 : 1) + (direct ? 0 : 4);
         AttnKernel kern;
-        if (app) kern = head_dim == 64 ? (AttnKernel)attn_decode_direct_kernel<64, 3, true> : (AttnKernel)attn_decode_direct_kernel<128, 2, true>;
-        else if (direct) kern = head_dim == 64 ? (AttnKernel)attn_decode_direct_kernel<64, 3, false> : (AttnKernel)attn_decode_direct_kernel<128, 2, false>;
-        else kern = head_dim == 64 ? (AttnKernel)attn_decode_fast_kernel<64> : (AttnKernel)attn_decode_fast_kernel<128>;
-        const int threads = direct ? kDirectThreads : kFastThreads;
+        if (direct) {
+            if (app) kern = head_dim == 64 ? (AttnKernel)attn_decode_direct_kernel<64, 3, true> : (AttnKernel)attn_decode_direct_kernel<128, 2, true>;
+            else kern = head_dim == 64 ? (AttnKernel)attn_decode_direct_kernel<64, 3, false> : (AttnKernel)attn_decode_direct_kernel<128, 2, false>;
+        } else {
+            if (app) kern = head_dim == 64 ? (AttnKernel)attn_decode_staged_kernel<64, true> : (AttnKernel)attn_decode_staged_kernel<128, true>;
+            else kern = head_dim == 64 ? (AttnKernel)attn_decode_staged_kernel<64, false> : (AttnKernel)attn_decode_staged_kernel<128, false>;
+        }
+        const int threads = kConsumerThreads;
         auto smem_for = [&](int sp) {
-            return direct ? direct_smem_bytes(head_dim, sp, group) : fast_smem_bytes(head_dim, stages, sp, group);
+            return direct ? direct_smem_bytes(head_dim, sp, group) : staged_smem_bytes(head_dim, ring, sp, group);
         };
-        // splits: largest power of two that keeps the grid within about one wave
+        // splits: largest power of two that keeps the grid within the target number of CTAs
         int max_splits = env_int("FDMS_ATTN_MAX_SPLITS", 8);
         if (max_splits > kMaxSplits) max_splits = kMaxSplits;
         int splits = 1;
@@ -1261,10 +1382,10 @@ static int32_t attn_decode_common(
         const size_t smem = smem_for(splits);
         FDMS_REQUIRE(smem <= (size_t)di.smem_optin, FDMS_E_CAPACITY,
                      "fdms_attn_decode: %zu bytes of shared memory needed (limit %d)", smem, di.smem_optin);
-        p.stages = stages; p.splits = splits; p.chunks = chunks;
+        p.stages = ring; p.splits = splits; p.chunks = chunks;
         const cudaError_t e = launch_attn(kern, threads, p, items, smem, (cudaStream_t)stream);
-        if (e != cudaSuccess) return fail(FDMS_E_CUDA, "attn_decode_fast_kernel launch failed: %s", cudaGetErrorString(e));
-        FDMS_CHECK_LAUNCH("attn_decode_fast_kernel");
+        if (e != cudaSuccess) return fail(FDMS_E_CUDA, "attention kernel launch failed: %s", cudaGetErrorString(e));
+        FDMS_CHECK_LAUNCH("attention kernel");
         return FDMS_OK;
     }
 

@@ -12,6 +12,10 @@ from fastdms_b200.sampling_params import SamplingParams
 
 
 class LLMEngine:
+    # run-ahead decode state (class-level defaults: "nothing in flight")
+    _ahead = None
+    _deferred_free: list = []
+
     def __init__(self, model, **kwargs):
         names = {f.name for f in fields(Config)}
         config = Config(model, **{k: v for k, v in kwargs.items() if k in names})
@@ -25,6 +29,10 @@ class LLMEngine:
                                    prefill_guard=guard)
         self.last_decode_tok_s = 0.0
         self.last_prefill_tok_s = 0.0
+        # run-ahead decode (Config.decode_run_ahead): the step launched during the previous call,
+        # as (sequences, read-back handle), and finished requests whose spans it may still be using
+        self._ahead = None
+        self._deferred_free: list[int] = []
 
     def _tokenizer(self):
         if self.tokenizer is None:
@@ -44,7 +52,41 @@ class LLMEngine:
         self.scheduler.add(seq)
         return seq
 
+    def _may_launch_next(self, seqs) -> bool:
+        """Whether the step AFTER the one in flight can be launched before its tokens are known:
+        same batch for certain (nobody reaches max_tokens, nothing waits to be prefilled, nobody has
+        finished), greedy, graph captured, and -- paged layout -- a page certain for every span."""
+        mgr = self.model_runner.compact_kv_manager
+        return (not self.scheduler.waiting
+                and all(not s.is_finished and s.num_completion_tokens + 1 < s.max_tokens for s in seqs)
+                and self.model_runner.can_run_ahead(seqs)
+                and mgr.decode_pages_guaranteed(len(seqs)))
+
+    def _finish_decode(self, seqs, handle):
+        """Second half of a run-ahead decode step: launch the following step from the tokens that
+        are still on the device, then read this step's tokens and do the host bookkeeping."""
+        runner = self.model_runner
+        nxt = (seqs, runner.launch_decode(seqs, device_fed=True)) if self._may_launch_next(seqs) else None
+        tokens = runner.resolve_decode(handle)
+        # a request that ended on EOS one call ago is still part of a step launched before that was known
+        kept = [(s, t) for s, t in zip(seqs, tokens) if not s.is_finished]
+        self.scheduler.postprocess([s for s, _ in kept], [t for _, t in kept], False)
+        done, self._deferred_free = self._deferred_free, []          # the step that used them has completed
+        freed = self.scheduler.consume_freed_seq_ids()
+        if nxt is not None:
+            self._deferred_free = freed                              # the step in flight still reads their spans
+        else:
+            done += freed
+        if done:
+            runner.free_compact(done)
+        self._ahead = nxt
+        return [(s.seq_id, s.completion_token_ids) for s, _ in kept if s.is_finished], -len(kept)
+
     def step(self):
+        if self._ahead is not None:
+            seqs, handle = self._ahead
+            self._ahead = None
+            return self._finish_decode(seqs, handle)
         seqs, is_prefill = self.scheduler.schedule()
         if not seqs:                      # a partly prefilled request was sent back to free its pages
             self.model_runner.free_compact(self.scheduler.consume_freed_seq_ids())
@@ -68,6 +110,8 @@ class LLMEngine:
                 seqs.remove(victim)
                 self.model_runner.free_compact([victim.seq_id])
             num_tokens = -len(seqs)
+            if getattr(self.config, "decode_run_ahead", False) and self.model_runner.can_run_ahead(seqs):
+                return self._finish_decode(seqs, self.model_runner.launch_decode(seqs, device_fed=False))
             token_ids = self.model_runner.run(seqs, False)
         self.scheduler.postprocess(seqs, token_ids, is_prefill)
         freed = self.scheduler.consume_freed_seq_ids()
@@ -77,7 +121,8 @@ class LLMEngine:
         return outputs, num_tokens
 
     def is_finished(self) -> bool:
-        return self.scheduler.is_finished()
+        # a run-ahead step still in flight has to be resolved (and its requests' spans released)
+        return self.scheduler.is_finished() and self._ahead is None
 
     def generate(self, prompts, sampling_params, use_tqdm: bool = False) -> list[dict]:
         if not isinstance(sampling_params, list):

@@ -51,6 +51,10 @@ class _DecodeGraph:
         self.logits = None
         self.tokens = None
         self.graph = None
+        # run-ahead decode: token read-back of the last two steps (pinned) and the events that guard them
+        self.h_tok = torch.zeros((2, batch), dtype=torch.int64, pin_memory=True)
+        self.tok_events = [torch.cuda.Event(), torch.cuda.Event()]
+        self.tok_turn = 0
 
 
 class ModelRunner:
@@ -248,9 +252,14 @@ class ModelRunner:
             hidden = self.model(g.ids, g.pos)
         finally:
             reset_context()
-        m.record_device(g.slots, g.pos, g.evict_all)
+        # With run-ahead the step leaves the NEXT step's inputs on the device: the recording launch
+        # advances the positions and the argmax writes the greedy tokens into the id buffer (the
+        # reference feeds tokens back on the device for a single sequence only,
+        # fastdms/engine/model_runner.py:971-1053).  Host-provided inputs simply overwrite them.
+        feed = self.config.decode_run_ahead
+        m.record_device(g.slots, g.pos, g.evict_all, advance_positions=feed)
         g.logits = self.model.compute_logits(hidden)
-        g.tokens = greedy_argmax(g.logits, g.argmax_scratch)
+        g.tokens = greedy_argmax(g.logits, g.argmax_scratch, out=g.ids if feed else None)
 
     def _decode_inputs(self, g: _DecodeGraph, seqs: list[Sequence]) -> None:
         m = self.compact_kv_manager
@@ -264,8 +273,34 @@ class ModelRunner:
         g.pos.copy_(g.d_in[1])
         g.slots.copy_(g.d_in[2])
 
+    def can_run_ahead(self, seqs: list[Sequence]) -> bool:
+        """Whether the decode step of `seqs` can be replayed from device-resident inputs: greedy
+        requests only, expiry inside the graph, and the graph of this batch size already captured."""
+        g = self.graphs.get(len(seqs))
+        return (self.config.decode_run_ahead and not self.config.enforce_eager
+                and self.compact_kv_manager.dms_expiry_interval == 1
+                and g is not None and isinstance(g.graph, torch.cuda.CUDAGraph)
+                and all(seq.temperature <= 1e-10 for seq in seqs))
+
     @torch.inference_mode()
-    def run_decode(self, seqs: list[Sequence]) -> _DecodeGraph:
+    def launch_decode(self, seqs: list[Sequence], device_fed: bool):
+        """Enqueues one decode step and the read-back of its greedy tokens without waiting for
+        either; `resolve_decode` returns the tokens.  With `device_fed` the step reads the token
+        ids, positions and slots the previous step of the same batch left on the device."""
+        g = self.run_decode(seqs, device_fed=device_fed)
+        turn = g.tok_turn
+        g.tok_turn ^= 1
+        g.h_tok[turn].copy_(g.tokens, non_blocking=True)
+        g.tok_events[turn].record()
+        return g, turn
+
+    def resolve_decode(self, handle) -> list[int]:
+        g, turn = handle
+        g.tok_events[turn].synchronize()
+        return g.h_tok[turn].tolist()
+
+    @torch.inference_mode()
+    def run_decode(self, seqs: list[Sequence], device_fed: bool = False) -> _DecodeGraph:
         """One decode step for `seqs`; returns the buffers holding logits and greedy tokens."""
         m, md = self.compact_kv_manager, self.dms_metadata
         B = len(seqs)
@@ -273,6 +308,10 @@ class ModelRunner:
         if g is None:
             g = _DecodeGraph(self, B)
             self.graphs[B] = g
+        if device_fed:
+            with get_profiler().cuda_phase("model_forward_decode"):
+                g.graph.replay()
+            return g
         if m.dms_expiry_interval != 1:
             with get_profiler().cuda_phase("dms_decode_expire"):
                 self.last_dms_decode_stats.append(m.apply_dms_evictions(

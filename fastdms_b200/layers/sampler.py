@@ -10,15 +10,22 @@ def argmax_workspace(rows: int, device) -> torch.Tensor:
     return torch.zeros(max(int(_lib.lib().fdms_argmax_workspace_bytes(rows)), 16), dtype=torch.uint8, device=device)
 
 
-def greedy_argmax(logits: torch.Tensor, workspace: torch.Tensor | None = None) -> torch.Tensor:
+def greedy_argmax(logits: torch.Tensor, workspace: torch.Tensor | None = None,
+                  out: torch.Tensor | None = None) -> torch.Tensor:
     """`logits.argmax(dim=-1)` of a `[rows, vocab]` CUDA tensor in one launch of the library's
-    `fdms_argmax_rows` (lowest index on ties, NaN largest, like torch); other inputs take torch's."""
+    `fdms_argmax_rows` (lowest index on ties, NaN largest, like torch); other inputs take torch's.
+    `out` (int64 [rows], contiguous) receives the result in place, e.g. the token-id buffer the next
+    decode step reads."""
     if not (logits.is_cuda and logits.dim() == 2 and logits.stride(1) == 1 and 0 < logits.shape[0] < 65536
             and logits.shape[1] > 0 and logits.dtype in (torch.float32, torch.bfloat16, torch.float16)):
-        return logits.argmax(dim=-1)
+        res = logits.argmax(dim=-1)
+        return res if out is None else out.copy_(res)
     rows, n = logits.shape
     ws = workspace if workspace is not None else argmax_workspace(rows, logits.device)
-    out = torch.empty(rows, dtype=torch.int64, device=logits.device)
+    if out is None:
+        out = torch.empty(rows, dtype=torch.int64, device=logits.device)
+    elif out.dtype != torch.int64 or out.shape != (rows,) or not out.is_contiguous():
+        raise ValueError("out must be a contiguous int64 tensor with one element per row")
     with torch.cuda.device(logits.device):
         rc = _lib.lib().fdms_argmax_rows(logits.data_ptr(), logits.stride(0), _lib.dtype_code(logits.dtype), rows, n,
                                          out.data_ptr(), ws.data_ptr(), ws.numel(), _lib.stream_ptr(logits.device))

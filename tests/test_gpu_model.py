@@ -27,7 +27,7 @@ def golden():
         return {k: z[k] for k in z.files}
 
 
-def _engine(golden, kv_dtype, paged, eager=False, row_index=True, model_dtype="float32"):
+def _engine(golden, kv_dtype, paged, eager=False, row_index=True, model_dtype="float32", **extra):
     import make_golden_model as G
     from fastdms_b200 import LLM
     from fastdms_b200.layers import rotary_embedding
@@ -39,7 +39,7 @@ def _engine(golden, kv_dtype, paged, eager=False, row_index=True, model_dtype="f
               kv_cache_dtype=kv_dtype, max_model_len=1024, max_num_seqs=4, max_num_batched_tokens=4096,
               compact_kv_capacity_tokens=8192, dms_window_size=G.WINDOW, dms_alpha_scale=G.ALPHA_SCALE,
               dms_alpha_offset=G.ALPHA_OFFSET, compact_kv_paged=paged, enforce_eager=eager, compact_kv_row_indirection=row_index,
-              device="cuda:0")
+              device="cuda:0", **extra)
     # the rotary table the reference used (cos/sin of the same float32 angles can differ by an ulp
     # between math libraries; the table is an input of the path, not part of it)
     cache = llm.model_runner.model.model.layers[0].self_attn.rotary_emb.cos_sin_cache
@@ -177,6 +177,35 @@ def test_config0_final_metadata_and_generate_api(golden):
     llm2, _ = _engine(golden, "float8_e4m3fn", True)
     res = llm2.generate(G.make_prompts(), SamplingParams(temperature=0.0, max_tokens=G.DECODE_STEPS, ignore_eos=True))
     assert [r["token_ids"] for r in res] == out
+
+
+@pytest.mark.parametrize("paged", [False, True])
+def test_run_ahead_decode_gives_the_reference_tokens(golden, paged):
+    """With `decode_run_ahead` the engine launches step n+1 from the tokens step n left on the device
+    and reads step n's tokens afterwards.  Tokens must be those of the reference trace; requests that
+    stop at different lengths, and one that stops on an end-of-sequence token while the next step is
+    already in flight, leave the batch cleanly and the pool comes back whole."""
+    from fastdms_b200 import SamplingParams, _lib
+    want = golden["fp8_tokens"]                                           # [steps + 1, B]
+    llm, G = _engine(golden, "float8_e4m3fn", paged, decode_run_ahead=True)
+    lens = [G.DECODE_STEPS, 40, 97, 128]
+    # sequence 1 ends on an EOS id: the token the reference emits for it at its 25th decode step
+    eos = int(want[24, 1])
+    first = int(np.argmax(want[:, 1] == eos))
+    llm.scheduler.eos = eos
+    sps = [SamplingParams(temperature=0.0, max_tokens=n, ignore_eos=(i != 1)) for i, n in enumerate(lens)]
+    res = llm.generate(G.make_prompts(), sps)
+    for i, r in enumerate(res):
+        n = first + 1 if i == 1 else lens[i]
+        assert r["token_ids"] == want[:n, i].tolist(), f"sequence {i}"
+    mgr = llm.model_runner.compact_kv_manager
+    if paged:
+        assert mgr.free_page_counts.tolist() == [mgr.pages_per_layer] * mgr.num_layers
+    else:
+        assert mgr.free_ranges_per_layer == [[(0, mgr.capacity_tokens)]] * mgr.num_layers
+    assert sorted(mgr.free_active_slots) == list(range(mgr.max_active_seqs))
+    assert llm._ahead is None and not llm._deferred_free
+    assert _lib.read_device_status("cuda:0") == 0
 
 
 def test_sampling_and_argument_errors(golden):

@@ -32,6 +32,14 @@ def _status_clean(dev):
     assert _lib.read_device_status(dev) == 0, "a kernel raised a device status bit"
 
 
+@pytest.fixture(params=["direct", "staged"])
+def loader(request, monkeypatch):
+    """Both page loaders of the FP8 attention kernels: per-lane loads into registers, and bulk copies
+    into per-warp shared-memory rings."""
+    monkeypatch.setenv("FDMS_ATTN_LOADER", request.param)
+    return request.param
+
+
 def t_bf16(a, dev):
     return torch.from_numpy(a.view(np.int16).copy()).view(torch.bfloat16).to(dev)
 
@@ -162,7 +170,7 @@ def test_attention_reference_f32_fixture(ops_golden, dev):
 
 @pytest.mark.parametrize("tag,scale", [("fp8d64", None), ("fp8d128", 0.11)])
 @pytest.mark.parametrize("generic", [False, True])
-def test_attention_fp8_golden(ops_golden, dev, tag, scale, generic, monkeypatch):
+def test_attention_fp8_golden(ops_golden, dev, tag, scale, generic, monkeypatch, loader):
     z = ops_golden
     if generic:
         monkeypatch.setenv("FDMS_ATTN_FORCE_GENERIC", "1")
@@ -215,7 +223,7 @@ def _config2_case(rng, B, Hk, G, D, mean, jitter, recent, paged, pool_pages_extr
 
 @pytest.mark.parametrize("D,G", [(64, 4), (128, 4), (64, 8), (64, 1)])
 @pytest.mark.parametrize("paged", [False, True])
-def test_attention_ragged_scaled(dev, D, G, paged):
+def test_attention_ragged_scaled(dev, D, G, paged, loader):
     from fastdms_b200.layers.compact_attention import compact_decode_attention
     rng = np.random.default_rng(100 + D + G + int(paged))
     B, Hk = 3, 2
@@ -229,7 +237,7 @@ def test_attention_ragged_scaled(dev, D, G, paged):
     assert np.abs(n_bf16(out) - want).max() < ATTN_TOL
 
 
-def test_attention_config2_shape(dev):
+def test_attention_config2_shape(dev, loader):
     """The op-level benchmark shape: 8 sequences, 32 q / 8 KV heads, head_dim 64, live = 1024 +- 128 + 256,
     16-row pages with randomly permuted block tables, per-head absmax scales."""
     from fastdms_b200.layers.compact_attention import compact_decode_attention
@@ -248,7 +256,7 @@ def test_attention_config2_shape(dev):
 
 
 @pytest.mark.parametrize("splits,chunks", [(1, 1), (2, 1), (8, 1), (16, 1), (1, 3), (4, 5), (8, 64)])
-def test_attention_split_shapes(dev, splits, chunks, monkeypatch):
+def test_attention_split_shapes(dev, splits, chunks, monkeypatch, loader):
     """Every split-K shape (cluster size x clusters per span) gives the same answer, including
     shapes with more CTAs than pages; repeated calls leave the workspace counters at zero."""
     from fastdms_b200.layers.compact_attention import compact_decode_attention
@@ -267,7 +275,7 @@ def test_attention_split_shapes(dev, splits, chunks, monkeypatch):
         assert np.abs(n_bf16(out) - want).max() < ATTN_TOL
 
 
-def test_attention_edge_lengths(dev):
+def test_attention_edge_lengths(dev, loader):
     """live = 1, exact page multiples, one long span next to tiny ones, and an empty span."""
     from fastdms_b200.layers.compact_attention import compact_decode_attention
     rng = np.random.default_rng(5)
@@ -292,7 +300,7 @@ def test_attention_edge_lengths(dev):
     assert np.all(got[2, G:] == 0)            # an empty span yields zeros, not NaN
 
 
-def test_attention_inline_q_rope(ops_golden, dev):
+def test_attention_inline_q_rope(ops_golden, dev, loader):
     """q rotated inside the attention kernel == q rotated by the store kernel first."""
     from fastdms_b200.layers.compact_attention import compact_decode_attention
     z = ops_golden
@@ -323,7 +331,7 @@ def test_attention_inline_q_rope(ops_golden, dev):
 
 @pytest.mark.parametrize("D,G,paged,scaled,mean", [(64, 4, True, True, 200), (64, 4, False, False, 200), (128, 4, True, False, 200),
                                                    (64, 8, False, True, 200), (64, 4, True, True, 5000), (128, 2, False, True, 9000)])
-def test_fused_store_attention_equals_store_then_attention(dev, D, G, paged, scaled, mean):
+def test_fused_store_attention_equals_store_then_attention(dev, D, G, paged, scaled, mean, loader):
     """One launch (decision + RoPE + FP8 store + attention) against the two separate kernels:
     identical decisions, identical pool bytes, identical attention output; spans whose new row
     opens a fresh page (live % 16 == 1) and fills one (live % 16 == 0) are included."""
