@@ -10,7 +10,7 @@ PKG = Path(__file__).resolve().parent
 CSRC = PKG / "csrc"
 LIB = PKG / "libfastdms_b200.so"
 SOURCES = ["store_decode.cu", "attn_decode.cu", "expiry.cu", "pack_prefill.cu", "metadata.cu", "kv_quant.cu",
-           "elementwise.cu", "allreduce.cu", "prefix_attention.cu", "skinny_gemm.cu"]
+           "elementwise.cu", "allreduce.cu", "prefix_attention.cu", "skinny_gemm.cu", "linear_allreduce.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC", "-shared", "--use_fast_math", "-Xptxas", "-v",

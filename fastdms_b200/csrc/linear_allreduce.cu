@@ -1,0 +1,263 @@
+// Row-parallel linear layer of tensor-parallel decode fused with its all-reduce:
+//   y[M, N] = sum over ranks r of  x_r[M, K_r] * W_r[N, K_r]^T   (+ bias),  M <= 8 rows,
+// in ONE kernel per rank (the reference runs F.linear and then NCCL's all_reduce on the [batch, hidden]
+// result after o_proj and down_proj, fastdms/layers/linear.py:1044-1048: two launches and a collective
+// whose cost at 64 KB is pure latency, 72 times per decode step of the 8B shape).
+//
+// A CTA owns 16 * TPC output columns.  Its 8 warps split (tile, K range): with K_r / 256 >= 8 steps all
+// eight warps share one tile's K; narrower shards (K_r = 512 at eight ranks) put several tiles on one
+// CTA.  Weight rows sit on the M side of mma.sync.m16n8k16, the <= 8 activation rows on N, exactly as in
+// the decode linear kernel; partial tiles of the warps are summed through shared memory in float32.
+//
+// Epilogue = the collective.  The CTA PUSHES its float32 partial tile into a slot of every rank's
+// peer-mapped region (plain stores over NVLink, one traversal), makes them visible
+// (__threadfence_system), raises a per-(source rank, CTA) flag in every peer (st.release.sys), waits for
+// the peers' flags of the same CTA index (ld.acquire.sys, bounded), then adds the slots of all ranks
+// from its OWN memory in rank order, adds the bias once, rounds once and stores y.  Every rank ends up
+// with identical bits; partials cross the link in float32, so the result is rounded once instead of
+// once per rank.  No multicast objects, no library kernel touches peer memory.
+//
+// Region of a rank:  slots[2][world][kLarMaxCtas][kLarSlotFloats] float32 | flags[world][kLarMaxCtas] |
+// epoch[kLarMaxCtas].  Slots are indexed by CTA, not by column, so a CTA's slot is only ever touched by
+// the CTAs of the same index; call e uses parity e & 1.  A rank can be at most one call ahead of a peer
+// (to start call e + 2 it needs the peer's flag of call e + 1, which the peer's CTA raises only after it
+// has finished reading call e), so two parities are enough.  The epoch lives on the device so that a
+// captured CUDA graph replays the call.
+//
+// A wait that runs out (about a second) raises FDMS_DEV_WAIT_TIMEOUT, leaves the silent rank out of the
+// sum and returns.  After that the ranks' epochs may disagree: the status bit is FATAL for the region,
+// which must be re-created collectively before it is used again.
+#include <string.h>
+
+#include "common.cuh"
+
+namespace fdms {
+
+constexpr int kLarWarps = 8;
+constexpr int kLarThreads = kLarWarps * 32;
+constexpr int kLarStep = 256;              // k elements per warp and step
+constexpr int kLarMaxTpc = 8;              // tiles of 16 columns per CTA
+constexpr int kLarSlotFloats = kLarMaxTpc * 128;      // 8 rows x 16 columns per tile
+constexpr int kLarMaxCtas = 512;
+constexpr int kLarMaxWorld = 8;
+constexpr unsigned kLarSpinLimit = 1u << 21;
+
+struct LarParams {
+    const uint16_t* x; int64_t x_stride;
+    const uint16_t* w; int64_t w_stride;
+    const uint16_t* bias;
+    uint16_t* y; int64_t y_stride;
+    int M, N, K, ks, tpc;                  // ks K-splits x tpc tiles = 8 warps
+    float* slots[kLarMaxWorld];            // region of every rank (index = rank)
+    uint32_t* flags[kLarMaxWorld];
+    uint32_t* epoch;                       // local
+    int rank, world;
+    int32_t* dev_status;
+};
+
+__device__ __forceinline__ uint32_t lar_ld_acquire(const uint32_t* p) {
+    uint32_t v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void lar_st_release(uint32_t* p, uint32_t v) {
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ float4 lar_ld_volatile(const float4* p) {
+    float4 v;
+    asm volatile("ld.volatile.global.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p) : "memory");
+    return v;
+}
+
+template <bool BF16>
+__device__ __forceinline__ void lar_mma(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    if (BF16)
+        asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                     : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+    else
+        asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                     : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// Offset (in floats) of the slot of (parity, source rank, CTA) inside a region.
+__device__ __forceinline__ size_t lar_slot(int parity, int src, int cta, int world) {
+    return (((size_t)parity * world + src) * kLarMaxCtas + cta) * kLarSlotFloats;
+}
+
+template <bool BF16>
+__global__ void __launch_bounds__(kLarThreads) linear_allreduce_kernel(LarParams p) {
+    __shared__ float s_part[kLarWarps][128];             // per warp: its tile's 16 columns x 8 rows
+    __shared__ __align__(16) float s_sum[kLarMaxTpc * 128];
+    __shared__ int s_missing[kLarMaxWorld];
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
+    const int c = blockIdx.x;
+    const int tile_local = warp / p.ks, split = warp - tile_local * p.ks;
+    const int tile = c * p.tpc + tile_local;
+    const int n0 = tile * 16;
+    const int steps = p.K / kLarStep;
+    const int s_begin = (int)((int64_t)split * steps / p.ks), s_end = (int)((int64_t)(split + 1) * steps / p.ks);
+    const bool active = n0 < p.N && s_begin < s_end;
+    if (tid < kLarMaxWorld) s_missing[tid] = 0;
+
+    float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    // Weights do not depend on the preceding kernel: the first step's vectors are requested before the
+    // dependency is resolved.
+    pdl_trigger();
+    uint4 wa[8], wb[8];
+    const uint16_t* w0 = p.w + (int64_t)(n0 + g) * p.w_stride + 8 * t;
+    const uint16_t* w1 = w0 + 8 * p.w_stride;
+    if (active) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            wa[j] = __ldcs((const uint4*)(w0 + s_begin * kLarStep + 32 * j));
+            wb[j] = __ldcs((const uint4*)(w1 + s_begin * kLarStep + 32 * j));
+        }
+    }
+    pdl_wait();
+    if (active) {
+        const uint16_t* xr = p.x + (int64_t)g * p.x_stride + 8 * t;
+        for (int s = s_begin; s < s_end; ++s) {
+            uint4 xb[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+                xb[j] = g < p.M ? __ldg((const uint4*)(xr + s * kLarStep + 32 * j)) : make_uint4(0u, 0u, 0u, 0u);
+            if (s != s_begin) {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    wa[j] = __ldcs((const uint4*)(w0 + s * kLarStep + 32 * j));
+                    wb[j] = __ldcs((const uint4*)(w1 + s * kLarStep + 32 * j));
+                }
+            }
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                lar_mma<BF16>(acc, wa[j].x, wb[j].x, wa[j].y, wb[j].y, xb[j].x, xb[j].y);
+                lar_mma<BF16>(acc, wa[j].z, wb[j].z, wa[j].w, wb[j].w, xb[j].z, xb[j].w);
+            }
+        }
+    }
+    // acc[0..1]: column n0 + g, rows 2t, 2t+1;  acc[2..3]: column n0 + g + 8.  Layout of a tile: [column][row].
+    *(float2*)&s_part[warp][g * 8 + 2 * t] = make_float2(acc[0], acc[1]);
+    *(float2*)&s_part[warp][(g + 8) * 8 + 2 * t] = make_float2(acc[2], acc[3]);
+    __syncthreads();
+    const int tile_floats = p.tpc * 128;
+    for (int idx = tid; idx < tile_floats; idx += kLarThreads) {
+        const int tl = idx >> 7, r = idx & 127;
+        float sum = 0.0f;
+        for (int s = 0; s < p.ks; ++s) sum += s_part[tl * p.ks + s][r];
+        s_sum[idx] = sum;
+    }
+    __syncthreads();
+
+    // ---- the collective ----
+    const uint32_t e = p.epoch[c] + 1;
+    const int parity = (int)(e & 1u);
+    const int vecs = tile_floats / 4;
+    for (int i = tid; i < p.world * vecs; i += kLarThreads) {
+        const int r = i / vecs, v = i - r * vecs;
+        ((float4*)(p.slots[r] + lar_slot(parity, p.rank, c, p.world)))[v] = ((const float4*)s_sum)[v];
+    }
+    __threadfence_system();
+    __syncthreads();
+    if (tid < p.world && tid != p.rank) {
+        lar_st_release(p.flags[tid] + p.rank * kLarMaxCtas + c, e);        // "this rank's partial of CTA c, call e, is in your memory"
+        const uint32_t* f = p.flags[p.rank] + tid * kLarMaxCtas + c;
+        unsigned spins = 0;
+        while ((int32_t)(lar_ld_acquire(f) - e) < 0) {
+            if (++spins >= kLarSpinLimit) {
+                s_missing[tid] = 1;
+                if (p.dev_status) atomicOr(p.dev_status, FDMS_DEV_WAIT_TIMEOUT);
+                break;
+            }
+            __nanosleep(32);
+        }
+    }
+    __syncthreads();
+    // sum in rank order from this rank's own memory, bias once, one rounding
+    const float* mine = p.slots[p.rank];
+    for (int v = tid; v < vecs; v += kLarThreads) {
+        float4 sum = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        for (int r = 0; r < p.world; ++r) {
+            if (s_missing[r]) continue;
+            const float4 a = lar_ld_volatile((const float4*)(mine + lar_slot(parity, r, c, p.world)) + v);
+            sum.x += a.x; sum.y += a.y; sum.z += a.z; sum.w += a.w;
+        }
+        // vector v = tile v / 32, column (v % 32) / 2, rows 4 * (v & 1) .. + 3
+        const int tl = v >> 5, col = (v & 31) >> 1, row0 = (v & 1) * 4;
+        const int n = (c * p.tpc + tl) * 16 + col;
+        if (n >= p.N) continue;
+        float b = 0.0f;
+        if (p.bias) b = BF16 ? __uint_as_float((uint32_t)p.bias[n] << 16) : __half2float(*(const __half*)&p.bias[n]);
+        const float vals[4] = {sum.x + b, sum.y + b, sum.z + b, sum.w + b};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int m = row0 + i;
+            if (m >= p.M) continue;
+            uint16_t o;
+            if (BF16) { const __nv_bfloat16 bb = __float2bfloat16_rn(vals[i]); o = *(const uint16_t*)&bb; }
+            else { const __half hh = __float2half_rn(vals[i]); o = *(const uint16_t*)&hh; }
+            p.y[(int64_t)m * p.y_stride + n] = o;
+        }
+    }
+    __syncthreads();
+    if (tid == 0) p.epoch[c] = e;
+}
+
+}  // namespace fdms
+
+using namespace fdms;
+
+extern "C" int64_t fdms_linear_allreduce_region_bytes(int32_t world) {
+    if (world < 2 || world > kLarMaxWorld) return -1;
+    const int64_t slots = 2ll * world * kLarMaxCtas * kLarSlotFloats * 4;
+    const int64_t flags = (int64_t)world * kLarMaxCtas * 4;
+    const int64_t epoch = (int64_t)kLarMaxCtas * 4;
+    return slots + flags + epoch;
+}
+
+extern "C" int32_t fdms_linear_decode_allreduce(
+    const void* x, int64_t x_row_stride, const void* weight, int64_t w_row_stride, const void* bias,
+    void* y, int64_t y_row_stride, int32_t dtype, int32_t rows, int32_t out_features, int32_t in_features,
+    void* const* peer_regions, int32_t rank, int32_t world, int32_t* dev_status, void* stream) {
+    clear_error();
+    FDMS_REQUIRE(x && weight && y && peer_regions, FDMS_E_ARG, "fdms_linear_decode_allreduce: null pointer");
+    FDMS_REQUIRE(dtype == FDMS_BF16 || dtype == FDMS_F16, FDMS_E_DTYPE, "fdms_linear_decode_allreduce: bf16 or f16 only");
+    FDMS_REQUIRE(world >= 2 && world <= kLarMaxWorld && rank >= 0 && rank < world, FDMS_E_ARG,
+                 "fdms_linear_decode_allreduce: world must be 2..%d and rank inside it", kLarMaxWorld);
+    FDMS_REQUIRE(rows >= 0 && rows <= 8, FDMS_E_CAPACITY, "fdms_linear_decode_allreduce: at most 8 rows, got %d", rows);
+    FDMS_REQUIRE(out_features > 0 && out_features % 16 == 0 && in_features > 0 && in_features % kLarStep == 0, FDMS_E_ARG,
+                 "fdms_linear_decode_allreduce: out_features %% 16 and in_features %% %d must be 0 (got %d, %d)", kLarStep,
+                 out_features, in_features);
+    FDMS_REQUIRE(((uintptr_t)x & 15) == 0 && ((uintptr_t)weight & 15) == 0 && (x_row_stride * 2) % 16 == 0 &&
+                     (w_row_stride * 2) % 16 == 0,
+                 FDMS_E_ARG, "fdms_linear_decode_allreduce: x and weight rows must be 16-byte aligned");
+    if (rows == 0) return FDMS_OK;
+    const int steps = in_features / kLarStep;
+    int ks = 1;
+    while (ks * 2 <= kLarWarps && ks * 2 <= steps) ks *= 2;
+    const int tpc = kLarWarps / ks;
+    const int tiles = out_features / 16;
+    const int ctas = (tiles + tpc - 1) / tpc;
+    FDMS_REQUIRE(ctas <= kLarMaxCtas, FDMS_E_CAPACITY,
+                 "fdms_linear_decode_allreduce: %d CTAs needed, the region has slots for %d (out_features too large)", ctas,
+                 kLarMaxCtas);
+    LarParams p;
+    p.x = (const uint16_t*)x; p.x_stride = x_row_stride; p.w = (const uint16_t*)weight; p.w_stride = w_row_stride;
+    p.bias = (const uint16_t*)bias; p.y = (uint16_t*)y; p.y_stride = y_row_stride;
+    p.M = rows; p.N = out_features; p.K = in_features; p.ks = ks; p.tpc = tpc;
+    const size_t slot_floats = 2ull * world * kLarMaxCtas * kLarSlotFloats;
+    for (int r = 0; r < kLarMaxWorld; ++r) { p.slots[r] = nullptr; p.flags[r] = nullptr; }
+    for (int r = 0; r < world; ++r) {
+        FDMS_REQUIRE(peer_regions[r] != nullptr, FDMS_E_ARG, "fdms_linear_decode_allreduce: region of rank %d is null", r);
+        p.slots[r] = (float*)peer_regions[r];
+        p.flags[r] = (uint32_t*)(p.slots[r] + slot_floats);
+    }
+    p.epoch = p.flags[rank] + (size_t)world * kLarMaxCtas;
+    p.rank = rank; p.world = world; p.dev_status = dev_status;
+    cudaStream_t st = (cudaStream_t)stream;
+    if (dtype == FDMS_BF16)
+        FDMS_CUDA_OK(launch_chained(linear_allreduce_kernel<true>, dim3((unsigned)ctas), dim3(kLarThreads), st, chain_launches(), p));
+    else
+        FDMS_CUDA_OK(launch_chained(linear_allreduce_kernel<false>, dim3((unsigned)ctas), dim3(kLarThreads), st, chain_launches(), p));
+    FDMS_CHECK_LAUNCH("linear_allreduce_kernel");
+    return FDMS_OK;
+}

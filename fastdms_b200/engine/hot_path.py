@@ -14,7 +14,10 @@ advances the positions.
 
 `DecodeHotPath` is driven either with activations that already sit in its device buffers
 (`step_device`) or with host buffers (`step_host`: pinned host -> device copies of the step's
-q/k/v and positions, graph replay, device -> host copy of the attention output).
+q/k/v and positions, graph replay, device -> host copy of the attention output).  For a stream of
+host-driven steps, `submit_host_block` / `wait_host_block` pipeline them: two banks of device
+buffers, the upload of step n+1 and the download of step n-1 on copy streams of their own while the
+kernels of step n run.
 """
 from __future__ import annotations
 
@@ -62,6 +65,10 @@ class DecodeHotPath:
         # table, which the metadata and expiry kernels update in place (a new page every 16 tokens,
         # released pages at expiry).  With gaps in the slots it has to be a gathered copy; the copy is
         # refreshed inside every step, after the metadata launch (see _enqueue).
+        # second bank of activation / output buffers for pipelined host-driven steps (made on first use)
+        self._banks = [(self.q, self.k, self.v, self.positions, self.out, self._in_block)]
+        self._bank_graphs: list = [None, None]
+        self._pipe = None
         self.block_tables = manager.decode_block_tables(self.seqs)
         self._bt_gathered = (self.block_tables is not None
                              and manager._contiguous_active_slot_start(self.states) is None)
@@ -106,10 +113,11 @@ class DecodeHotPath:
         return (block, *self._block_views(block))
 
     # ---------------------------------------------------------------- the step itself
-    def _enqueue(self) -> None:
+    def _enqueue(self, bank: int = 0) -> None:
         m = self.m
+        q_all, k_all, v_all, positions, out_all, _ = self._banks[bank]
         if self.expire_every_step:
-            m.expire_device(self.slots_t, self.positions, window_size=self.window_size)
+            m.expire_device(self.slots_t, positions, window_size=self.window_size)
         m.decode_metadata_device(self.slots_t, self.base, self.live, self.slot, self.cu_live)
         if self._bt_gathered:
             torch.index_select(m.block_tables, 1, self._slots_long, out=self.block_tables)
@@ -122,19 +130,19 @@ class DecodeHotPath:
                 # prologue reads before its dependency wait: no overlap there.  Later layers follow the
                 # previous layer's attention, which writes nothing this launch reads before the wait.
                 fused_store_decode_attention(
-                    self.q[l], self.k[l], self.v[l], self.cos_sin_cache, ck, cv, self.base[l], self.live[l],
-                    self.evict_all[l], self.positions, num_kv_heads=self.Hk, alpha_scale=self.alpha_scale,
+                    q_all[l], k_all[l], v_all[l], self.cos_sin_cache, ck, cv, self.base[l], self.live[l],
+                    self.evict_all[l], positions, num_kv_heads=self.Hk, alpha_scale=self.alpha_scale,
                     alpha_offset=self.alpha_offset, scale=self.scale, block_tables=bt, k_scale=ks, v_scale=vs,
-                    out=self.out[l], overlap_previous_kernel=self.overlap and l > 0)
+                    out=out_all[l], overlap_previous_kernel=self.overlap and l > 0)
                 continue
             fused_dms_rope_store_compact_decode(
-                self.q[l], self.k[l], self.v[l], self.cos_sin_cache, ck, cv, self.slot[l], self.evict_all[l],
-                self.positions, num_kv_heads=self.Hk, alpha_scale=self.alpha_scale, alpha_offset=self.alpha_offset,
+                q_all[l], k_all[l], v_all[l], self.cos_sin_cache, ck, cv, self.slot[l], self.evict_all[l],
+                positions, num_kv_heads=self.Hk, alpha_scale=self.alpha_scale, alpha_offset=self.alpha_offset,
                 store_q=True, store_transient_k=False, k_scale=ks, v_scale=vs)
             compact_decode_attention(
-                self.q[l], ck, cv, self.base[l], self.live[l], scale=self.scale, block_tables=bt,
-                k_scale=ks, v_scale=vs, out=self.out[l], overlap_previous_kernel=self.overlap)
-        m.record_device(self.slots_t, self.positions, self.evict_all, advance_positions=True)
+                q_all[l], ck, cv, self.base[l], self.live[l], scale=self.scale, block_tables=bt,
+                k_scale=ks, v_scale=vs, out=out_all[l], overlap_previous_kernel=self.overlap)
+        m.record_device(self.slots_t, positions, self.evict_all, advance_positions=True)
 
     def capture(self) -> None:
         """Runs one eager step (warm-up; it advances the state like any step) and records the graph."""
@@ -215,6 +223,71 @@ class DecodeHotPath:
         g[0].replay()
         torch.cuda.current_stream(self.m.device).synchronize()
         return self._h_out
+
+    # ---------------------------------------------------------------- pipelined host-driven steps
+    def _ensure_pipeline(self) -> None:
+        if self._pipe is not None:
+            return
+        if not self.use_cuda_graph or self.graph is None:
+            raise RuntimeError("call capture() before submit_host_block()")
+        dev = self.m.device
+        block2 = torch.zeros_like(self._in_block)
+        q2, k2, v2, pos2 = self._block_views(block2)
+        self._banks.append((q2, k2, v2, pos2, torch.zeros_like(self.out), block2))
+        self._bank_graphs[0] = self.graph
+        # The kernels keep running on the stream the path was captured on; capturing the second bank's
+        # graph executes nothing.
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            self._enqueue(bank=1)
+        self._bank_graphs[1] = g
+        pin = lambda t: torch.empty(t.shape, dtype=t.dtype, pin_memory=True)
+        self._pipe = {
+            "up": torch.cuda.Stream(dev), "down": torch.cuda.Stream(dev), "h_out": [pin(self.out), pin(self.out)],
+            "uploaded": [torch.cuda.Event(), torch.cuda.Event()], "computed": [torch.cuda.Event(), torch.cuda.Event()],
+            "downloaded": [torch.cuda.Event(), torch.cuda.Event()], "count": 0,
+        }
+
+    def submit_host_block(self, block: torch.Tensor) -> int:
+        """Enqueues one host-driven step without waiting for it and returns a ticket for
+        `wait_host_block`.  Steps alternate between two banks of device buffers: the upload of this
+        step's block runs on a copy stream while the previous step's kernels are still running, the
+        kernels wait for the upload, and the download of the outputs runs on a third stream.  At most
+        two steps may be outstanding: wait for ticket n-1 before submitting n+1.  The block must stay
+        unchanged until its step's ticket has been waited for."""
+        if block.dtype != torch.uint8 or block.numel() != self._in_block.numel() or not block.is_pinned():
+            raise ValueError("submit_host_block takes a pinned block made by new_host_block()")
+        self._ensure_pipeline()
+        pp = self._pipe
+        n = pp["count"]
+        bank = n & 1
+        main = torch.cuda.current_stream(self.m.device)
+        up, down = pp["up"], pp["down"]
+        if n >= 2:
+            up.wait_event(pp["computed"][bank])       # the bank's previous kernels have read their inputs
+        with torch.cuda.stream(up):
+            self._banks[bank][5].copy_(block, non_blocking=True)
+            pp["uploaded"][bank].record(up)
+        main.wait_event(pp["uploaded"][bank])
+        if n >= 2:
+            main.wait_event(pp["downloaded"][bank])   # the bank's previous outputs have left the device
+        self._bank_graphs[bank].replay()
+        pp["computed"][bank].record(main)
+        down.wait_event(pp["computed"][bank])
+        with torch.cuda.stream(down):
+            pp["h_out"][bank].copy_(self._banks[bank][4], non_blocking=True)
+            pp["downloaded"][bank].record(down)
+        pp["count"] = n + 1
+        return n
+
+    def wait_host_block(self, ticket: int) -> torch.Tensor:
+        """Outputs [layers, batch, q_heads, head_dim] of the step `ticket` in pinned host memory
+        (overwritten when the second step after it is submitted)."""
+        pp = self._pipe
+        if pp is None or not (pp["count"] - 2 <= ticket < pp["count"]):
+            raise ValueError("unknown or expired ticket")
+        pp["downloaded"][ticket & 1].synchronize()
+        return pp["h_out"][ticket & 1]
 
     @property
     def h2d_bytes_per_step(self) -> int:

@@ -78,8 +78,9 @@ class ModelRunner:
         self.dtype = config.model_dtype()
         if self.world_size > 1:
             # small tensor-parallel sums go through NVLink peer memory instead of NCCL
-            from fastdms_b200.layers.peer_allreduce import init_peer_all_reduce
+            from fastdms_b200.layers.peer_allreduce import init_fused_row_parallel, init_peer_all_reduce
             self.peer_all_reduce = init_peer_all_reduce(self.device)
+            self.fused_row_parallel = init_fused_row_parallel(self.device)
         self.dms_metadata = self._load_dms_metadata()
         default_dtype = torch.get_default_dtype()
         torch.set_default_dtype(self.dtype)

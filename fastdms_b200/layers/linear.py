@@ -178,8 +178,13 @@ class RowParallelLinear(LinearBase):
         param.data.copy_(loaded_weight.narrow(1, self.tp_rank * shard, shard))
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
-        y = linear(x, self.weight, self.bias if self.tp_rank == 0 else None)
         if self.tp_size > 1:
-            from fastdms_b200.layers.peer_allreduce import tp_all_reduce_
+            from fastdms_b200.layers.peer_allreduce import fused_row_parallel, tp_all_reduce_
+            fused = fused_row_parallel()
+            if fused is not None and _DECODE_LINEAR and fused.fits(x, self.weight, self.bias):
+                # decode-sized input: GEMM and all-reduce in one launch (the bias is added once, after the sum)
+                return fused.linear_all_reduce(x, self.weight, self.bias)
+            y = linear(x, self.weight, self.bias if self.tp_rank == 0 else None)
             tp_all_reduce_(y)
-        return y
+            return y
+        return linear(x, self.weight, self.bias)

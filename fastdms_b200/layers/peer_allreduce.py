@@ -16,22 +16,23 @@ import torch.distributed as dist
 from fastdms_b200 import _lib
 
 _STATE = None
+_FUSED = None
 
 
-class PeerAllReduce:
-    def __init__(self, device: torch.device, group=None, max_bytes: int = 1 << 20):
+class _PeerRegions:
+    """One zero-filled device region per rank, mapped into every rank (collective over the group)."""
+
+    def __init__(self, device: torch.device, group, nbytes: int):
         import ctypes
         self.group = group
         self.world = dist.get_world_size(group)
         self.rank = dist.get_rank(group)
         self.device = torch.device(device)
-        self.max_bytes = int(max_bytes)
         if not (2 <= self.world <= 8):
-            raise ValueError(f"peer all-reduce supports 2..8 ranks, got {self.world}")
-        lib = _lib.lib()
-        nbytes = lib.fdms_allreduce_region_bytes(self.world, self.max_bytes)
+            raise ValueError(f"peer regions support 2..8 ranks, got {self.world}")
         if nbytes <= 0:
-            raise ValueError("bad all-reduce region size")
+            raise ValueError("bad region size")
+        lib = _lib.lib()
         self._own = ctypes.c_void_p()
         self._opened: list[int] = []
         handle = (ctypes.c_ubyte * 64)()
@@ -69,6 +70,14 @@ class PeerAllReduce:
             lib.fdms_ipc_region_destroy(self._own)
         self._own = type(self._own)()
 
+
+
+class PeerAllReduce(_PeerRegions):
+    def __init__(self, device: torch.device, group=None, max_bytes: int = 1 << 20):
+        self.max_bytes = int(max_bytes)
+        world = dist.get_world_size(group)
+        super().__init__(device, group, _lib.lib().fdms_allreduce_region_bytes(world, self.max_bytes))
+
     def fits(self, t: torch.Tensor) -> bool:
         nb = t.numel() * t.element_size()
         return (t.is_cuda and t.is_contiguous() and t.dtype in (torch.float32, torch.bfloat16, torch.float16)
@@ -82,6 +91,60 @@ class PeerAllReduce:
                 _lib.dtype_code(t.dtype), _lib.status_word(self.device).data_ptr(), _lib.stream_ptr(self.device))
         _lib.check(rc)
         return t
+
+
+class FusedRowParallel(_PeerRegions):
+    """The row-parallel linear layer of tensor-parallel decode and its all-reduce in one launch per rank
+    (`fdms_linear_decode_allreduce`): CTAs push float32 partial tiles into every rank's region and sum
+    them in rank order, so all ranks hold identical results.  The reference does F.linear followed by
+    NCCL's all_reduce (fastdms/layers/linear.py:1044-1048)."""
+
+    def __init__(self, device: torch.device, group=None):
+        world = dist.get_world_size(group)
+        super().__init__(device, group, _lib.lib().fdms_linear_allreduce_region_bytes(world))
+
+    @staticmethod
+    def fits(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None) -> bool:
+        n, k = weight.shape
+        steps = k // 256
+        ks = 1
+        while ks * 2 <= 8 and ks * 2 <= steps:
+            ks *= 2
+        ctas = -(-(n // 16) // (8 // ks)) if k % 256 == 0 and steps > 0 else 1 << 30
+        return (x.is_cuda and x.dtype in (torch.bfloat16, torch.float16) and weight.dtype == x.dtype and x.dim() == 2
+                and 0 < x.shape[0] <= 8 and x.stride(1) == 1 and weight.is_contiguous() and n % 16 == 0 and k % 256 == 0
+                and ctas <= 512 and x.shape[1] == k and (bias is None or bias.dtype == x.dtype)
+                and x.data_ptr() % 16 == 0 and (x.stride(0) * 2) % 16 == 0 and weight.data_ptr() % 16 == 0
+                and not torch.is_grad_enabled())
+
+    def linear_all_reduce(self, x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None) -> torch.Tensor:
+        """sum over ranks of x_r @ weight_r.T (+ bias once): the same call on every rank."""
+        rows, n = x.shape[0], weight.shape[0]
+        y = torch.empty((rows, n), dtype=x.dtype, device=x.device)
+        with torch.cuda.device(self.device):
+            rc = _lib.lib().fdms_linear_decode_allreduce(
+                x.data_ptr(), x.stride(0), weight.data_ptr(), weight.stride(0), _lib.ptr(bias), y.data_ptr(), y.stride(0),
+                _lib.dtype_code(x.dtype), rows, n, weight.shape[1], self.ptrs.data_ptr(), self.rank, self.world,
+                _lib.status_word(self.device).data_ptr(), _lib.stream_ptr(self.device))
+        _lib.check(rc)
+        return y
+
+
+def init_fused_row_parallel(device, group=None):
+    """Sets up the fused linear + all-reduce for this process (collective over the group).  Switched
+    on with `FDMS_FUSED_ROW_PARALLEL=1`; otherwise the two-step path (linear, then all-reduce) runs."""
+    global _FUSED
+    _FUSED = None
+    if os.environ.get("FDMS_FUSED_ROW_PARALLEL", "0").strip().lower() in {"0", "false", "off", "no"}:
+        return None
+    if not dist.is_initialized() or dist.get_world_size(group) < 2:
+        return None
+    _FUSED = FusedRowParallel(device, group)
+    return _FUSED
+
+
+def fused_row_parallel():
+    return _FUSED
 
 
 def init_peer_all_reduce(device, group=None, max_bytes: int = 1 << 20):

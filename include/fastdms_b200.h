@@ -433,6 +433,25 @@ int32_t fdms_allreduce_oneshot(
     void* const* peer_regions, int32_t rank, int32_t world, int64_t max_bytes,
     const void* in, void* out, int64_t n, int32_t dtype, int32_t* dev_status, void* stream);
 
+/* Row-parallel linear layer fused with its all-reduce, for decode-sized inputs (rows <= 8):
+ *   y = sum over ranks of x_r W_r^T (+ bias), one kernel per rank instead of F.linear + NCCL all_reduce
+ * (fastdms/layers/linear.py:1044-1048, the o_proj / down_proj call sites).  Every CTA pushes its float32
+ * partial tile into a slot of each rank's peer-mapped region (plain peer stores), raises a flag in each
+ * peer, waits (bounded) for the peers' flags and sums the ranks' slots from its own memory in rank
+ * order: identical bits on every rank, one rounding.  x [rows, in_features] and weight
+ * [out_features, in_features] are this rank's shards (bf16 or f16, rows 16-byte aligned,
+ * in_features % 256 == 0, out_features % 16 == 0, at most 512 CTAs: out_features <= 8192 for
+ * in_features >= 2048); bias (may be null) is added once, pass the same vector on every rank.
+ * peer_regions[r]: rank r's region of fdms_linear_allreduce_region_bytes(world) bytes, zero-filled once,
+ * mapped with fdms_ipc_region_open; the same call sequence must run on every rank.  A peer that does not
+ * answer within about a second raises FDMS_DEV_WAIT_TIMEOUT and is left out of the sum; after that the
+ * region must not be used again (re-create it collectively). */
+int64_t fdms_linear_allreduce_region_bytes(int32_t world);
+int32_t fdms_linear_decode_allreduce(
+    const void* x, int64_t x_row_stride, const void* weight, int64_t w_row_stride, const void* bias,
+    void* y, int64_t y_row_stride, int32_t dtype, int32_t rows, int32_t out_features, int32_t in_features,
+    void* const* peer_regions, int32_t rank, int32_t world, int32_t* dev_status, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -554,6 +554,24 @@ def test_hot_path_step_equals_the_manual_kernel_sequence(dev, paged, gap):
         manual_step(q, k, v)
         assert torch.equal(got, outB), f"outputs differ at step {step}"
         assert torch.equal(hp.evict_all, evB) and torch.equal(hp.live, live) and torch.equal(hp.positions, posB)
+    # pipelined host-driven steps: step n+1 is submitted before step n's outputs are waited for
+    blocks = [hp.new_host_block() for _ in range(3)]
+    pending = None                                   # (ticket, inputs) of the step not yet checked
+    for step in range(30, 41):
+        q, k, v = new_inputs()
+        blk, bq, bk, bv, bp = blocks[step % 3]
+        bq.copy_(q.cpu()); bk.copy_(k.cpu()); bv.copy_(v.cpu()); bp.copy_(posB.cpu() + (0 if pending is None else 1))
+        ticket = hp.submit_host_block(blk)
+        if pending is not None:
+            manual_step(*pending[1])
+            assert torch.equal(hp.wait_host_block(pending[0]).to(dev), outB), f"pipelined outputs differ at step {step - 1}"
+        pending = (ticket, (q, k, v))
+    manual_step(*pending[1])
+    assert torch.equal(hp.wait_host_block(pending[0]).to(dev), outB), "pipelined outputs differ at the last step"
+    with pytest.raises(ValueError):
+        hp.wait_host_block(pending[0] - 2)
+    torch.cuda.synchronize(dev)
+    assert torch.equal(hp.evict_all, evB) and torch.equal(hp.live, live)
     for a, b in ((mA.layer_major_live_counts, mB.layer_major_live_counts), (mA.layer_major_token_positions, mB.layer_major_token_positions),
                  (mA.layer_major_evict_mask, mB.layer_major_evict_mask), (mA.layer_major_row_index, mB.layer_major_row_index)):
         assert torch.equal(a, b)

@@ -725,3 +725,95 @@ def test_split_k_workspace_survives_growth_of_the_batch(dev, monkeypatch):
         torch.cuda.synchronize(dev)
         assert torch.equal(out, want)
     del junk
+
+
+def _lar_layout(n, k):
+    """(k-splits, tiles per CTA, CTAs) the fused linear + all-reduce kernel uses for a [n, k] shard."""
+    steps, ks = k // 256, 1
+    while ks * 2 <= 8 and ks * 2 <= steps:
+        ks *= 2
+    tpc = 8 // ks
+    return ks, tpc, -(-(n // 16) // tpc)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("rows,n,k,bias", [(8, 4096, 2048, False), (8, 4096, 512, True), (3, 4096, 1536, True),
+                                            (8, 2064, 256, False), (1, 2048, 6144, True)])
+def test_fused_linear_allreduce_with_a_staged_peer(dev, dtype, rows, n, k, bias):
+    """The row-parallel linear layer fused with its all-reduce, run as rank 0 of 2 on one GPU.  The peer
+    is staged by the host: its float32 partial tiles already sit in rank 0's region and its flags are
+    raised, so the kernel finds them at once.  Result = this rank's x W^T + the staged partial (+ bias),
+    compared with a float32 computation; two calls in a row use the two halves of the region; rank 0's
+    own partial must have been pushed into the peer's region with its flags."""
+    from fastdms_b200 import _lib
+    lib = _lib.lib()
+    MAXC, SLOT = 512, 1024
+    ks, tpc, ctas = _lar_layout(n, k)
+    nbytes = lib.fdms_linear_allreduce_region_bytes(2)
+    assert nbytes == 2 * 2 * MAXC * SLOT * 4 + 2 * MAXC * 4 + MAXC * 4
+    regions = [torch.zeros((nbytes,), dtype=torch.uint8, device=dev) for _ in range(2)]
+    ptrs = torch.tensor([r.data_ptr() for r in regions], dtype=torch.int64)
+    slot_bytes = 2 * 2 * MAXC * SLOT * 4
+    slots = [r[:slot_bytes].view(torch.float32).view(2, 2, MAXC, SLOT) for r in regions]       # [parity][source][cta][...]
+    flags = [r[slot_bytes: slot_bytes + 2 * MAXC * 4].view(torch.int32).view(2, MAXC) for r in regions]
+    g = torch.Generator(device=dev).manual_seed(rows + n + k)
+    w = (torch.randn((n, k), device=dev, generator=g) * k ** -0.5).to(dtype)
+    b = torch.randn((n,), device=dev, generator=g).to(dtype) if bias else None
+    npad = ctas * tpc * 16
+
+    def to_slots(partial):                      # [rows, n] float32 -> [ctas, tpc * 128] in the kernel's tile layout
+        full = torch.zeros((8, npad), device=dev)
+        full[:rows, :n] = partial
+        return full.t().reshape(ctas, tpc * 128)
+
+    for call in (1, 2):
+        x = torch.randn((rows, k), device=dev, generator=g).to(dtype)
+        peer = torch.randn((rows, n), device=dev, generator=g)
+        slots[0][call & 1, 1, :ctas, : tpc * 128] = to_slots(peer)
+        flags[0][1, :ctas] = call
+        y = torch.full((rows, n), float("nan"), device=dev, dtype=dtype)
+        _lib.check(lib.fdms_linear_decode_allreduce(
+            x.data_ptr(), x.stride(0), w.data_ptr(), w.stride(0), _lib.ptr(b), y.data_ptr(), y.stride(0),
+            _lib.dtype_code(dtype), rows, n, k, ptrs.data_ptr(), 0, 2, _lib.status_word(dev).data_ptr(), _lib.stream_ptr(dev)))
+        own = x.float() @ w.float().t()
+        ref = own + peer + (b.float() if bias else 0.0)
+        tol = 2.0 ** -7 * float(ref.abs().max())
+        assert torch.isfinite(y.float()).all() and float((y.float() - ref).abs().max()) <= tol
+        # this rank's partial went to the peer's region (and to its own), with the flag of this call
+        pushed = slots[1][call & 1, 0, :ctas, : tpc * 128]
+        assert float((pushed - to_slots(own)).abs().max()) <= 2e-3 * float(own.abs().max()) + 1e-5
+        assert torch.equal(slots[0][call & 1, 0, :ctas, : tpc * 128], pushed)
+        assert (flags[1][0, :ctas] == call).all()
+    assert _lib.read_device_status(dev) == 0
+
+
+def test_fused_linear_allreduce_leaves_a_silent_peer_out(dev):
+    """A peer that never raises its flags: every bounded wait runs out after about a second, the kernel
+    raises FDMS_DEV_WAIT_TIMEOUT, sums what it has (its own partial) and returns; the context stays usable."""
+    import time
+    from fastdms_b200 import _lib
+    lib = _lib.lib()
+    rows, n, k = 4, 1024, 2048
+    nbytes = lib.fdms_linear_allreduce_region_bytes(2)
+    regions = [torch.zeros((nbytes,), dtype=torch.uint8, device=dev) for _ in range(2)]
+    ptrs = torch.tensor([r.data_ptr() for r in regions], dtype=torch.int64)
+    g = torch.Generator(device=dev).manual_seed(5)
+    x = torch.randn((rows, k), device=dev, generator=g).to(torch.bfloat16)
+    w = (torch.randn((n, k), device=dev, generator=g) * k ** -0.5).to(torch.bfloat16)
+    y = torch.empty((rows, n), device=dev, dtype=torch.bfloat16)
+    torch.cuda.synchronize(dev)
+    t0 = time.perf_counter()
+    _lib.check(lib.fdms_linear_decode_allreduce(
+        x.data_ptr(), x.stride(0), w.data_ptr(), w.stride(0), None, y.data_ptr(), y.stride(0), _lib.BF16, rows, n, k,
+        ptrs.data_ptr(), 0, 2, _lib.status_word(dev).data_ptr(), _lib.stream_ptr(dev)))
+    torch.cuda.synchronize(dev)
+    assert time.perf_counter() - t0 < 30.0
+    assert _lib.read_device_status(dev) & _lib.DEV_WAIT_TIMEOUT, "FDMS_DEV_WAIT_TIMEOUT expected"
+    ref = x.float() @ w.float().t()
+    assert float((y.float() - ref).abs().max()) <= 2.0 ** -7 * float(ref.abs().max())
+    assert torch.equal(torch.ones(4, device=dev) + 1, torch.full((4,), 2.0, device=dev))
+    with pytest.raises(ValueError):
+        lib_rc = lib.fdms_linear_decode_allreduce(
+            x.data_ptr(), x.stride(0), w.data_ptr(), w.stride(0), None, y.data_ptr(), y.stride(0), _lib.BF16, rows, n, k,
+            ptrs.data_ptr(), 2, 2, None, _lib.stream_ptr(dev))
+        _lib.check(lib_rc)
