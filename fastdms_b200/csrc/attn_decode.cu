@@ -1199,9 +1199,15 @@ static bool cluster_fits(AttnKernel kern, int variant, int threads, int splits, 
     return ok;
 }
 
-static cudaError_t launch_attn(AttnKernel kern, int threads, const AttnParams& p, int items, size_t smem, cudaStream_t stream) {
+static cudaError_t launch_attn(AttnKernel kern, int threads, const AttnParams& p, int items, size_t smem, cudaStream_t stream,
+                               bool max_shared) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
+    if (max_shared) {
+        // the staged kernel wants two CTAs of about 100 KB on an SM: ask for the largest shared-memory carve-out
+        e = cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+        if (e != cudaSuccess) return e;
+    }
     if (p.splits > 8) {
         e = cudaFuncSetAttribute(kern, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
         if (e != cudaSuccess) return e;
@@ -1383,7 +1389,7 @@ static int32_t attn_decode_common(
         FDMS_REQUIRE(smem <= (size_t)di.smem_optin, FDMS_E_CAPACITY,
                      "fdms_attn_decode: %zu bytes of shared memory needed (limit %d)", smem, di.smem_optin);
         p.stages = ring; p.splits = splits; p.chunks = chunks;
-        const cudaError_t e = launch_attn(kern, threads, p, items, smem, (cudaStream_t)stream);
+        const cudaError_t e = launch_attn(kern, threads, p, items, smem, (cudaStream_t)stream, !direct);
         if (e != cudaSuccess) return fail(FDMS_E_CUDA, "attention kernel launch failed: %s", cudaGetErrorString(e));
         FDMS_CHECK_LAUNCH("attention kernel");
         return FDMS_OK;

@@ -7,7 +7,10 @@ Tiny Llama-style DMS model, float32, 2 layers, hidden 256, 4 q / 2 KV heads, hea
 1024, vocab 1024, RoPE theta 500000, DMS window 16, eviction rate ~7/8; four ragged prompts of
 37/128/200/511 tokens; 128 greedy decode steps; compact KV in float32 and in FP8 e4m3.  Logits are
 kept for the first 32 steps and every 8th step after that (`logit_steps`), everything else for all
-steps.
+steps.  `*_top2_gap` / `*_runner_up` give the margin of every greedy choice (a model with random
+weights produces near-ties: with 1024 logits of spread 1.6 about one choice in a hundred has a
+margin below 5e-3, which is the size of FP8 rounding effects, so a test can only demand the
+reference's token where the margin is larger than the logit tolerance).
 
 A third run ("bf16") loads the same weights rounded to bfloat16 (the LM head scaled by 0.2 so that
 logits stay below 2 in magnitude, where a bfloat16 ulp is well under the 2e-2 tolerance), keeps the
@@ -175,6 +178,7 @@ def run(reference: str, kv_dtype: torch.dtype, tag: str, out: dict, model_dtype:
         live0 = torch.stack([manager.seq_states[s.seq_id].live_counts for s in seqs], dim=1)     # [L, B, Hk]
         out[f"{tag}_prefill_live"] = live0.numpy().copy()
         tokens = logits.argmax(dim=-1).tolist()
+        top2 = [logits.topk(2, dim=-1)]              # per step: the two largest logits and their ids
         all_tokens, step_logits, step_evict, step_live, step_slot, step_values = [tokens], [], [], [], [], []
         for s, t in zip(seqs, tokens):
             s.append_token(t)
@@ -195,6 +199,7 @@ def run(reference: str, kv_dtype: torch.dtype, tag: str, out: dict, model_dtype:
             manager.record_appended_dms_decisions(seqs, positions, ctx.dms_layer_evictions, sync_stats=False)
             reset_context()
             tokens = logits.argmax(dim=-1).tolist()
+            top2.append(logits.topk(2, dim=-1))
             for s, t in zip(seqs, tokens):
                 s.append_token(t)
             all_tokens.append(tokens)
@@ -204,6 +209,9 @@ def run(reference: str, kv_dtype: torch.dtype, tag: str, out: dict, model_dtype:
             step_live.append(live.numpy().copy())
             step_slot.append((slot - base).numpy().copy())         # logical slot index of the appended row
     out[f"{tag}_tokens"] = np.array(all_tokens, dtype=np.int64)                 # [steps + 1, B]
+    # margin of every greedy choice: top logit minus runner-up, and the runner-up's id
+    out[f"{tag}_top2_gap"] = np.stack([(t.values[:, 0] - t.values[:, 1]).numpy() for t in top2]).astype(np.float32)
+    out[f"{tag}_runner_up"] = np.stack([t.indices[:, 1].numpy() for t in top2]).astype(np.int64)
     out[f"{tag}_logits"] = np.stack(step_logits)                               # [len(LOGIT_STEPS), B, V]
     out[f"{tag}_decision_values"] = np.stack(step_values)                      # [steps, L, B, Hk]
     out[f"{tag}_evict"] = np.stack(step_evict)                                 # [steps, L, B, Hk]
