@@ -11,7 +11,10 @@ from pathlib import Path
 
 import torch
 
-LIB_PATH = Path(__file__).resolve().parent / "libfastdms_b200.so"
+import os
+
+# FDMS_B200_LIB selects another build of the same library (the probe build of `build.py --probe`)
+LIB_PATH = Path(os.environ.get("FDMS_B200_LIB") or Path(__file__).resolve().parent / "libfastdms_b200.so")
 
 FDMS_OK = 0
 FDMS_E_ARG, FDMS_E_DTYPE, FDMS_E_WORKSPACE, FDMS_E_CUDA, FDMS_E_CAPACITY = -1, -2, -3, -4, -5

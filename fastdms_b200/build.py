@@ -32,8 +32,20 @@ def needs_build() -> bool:
     return newest > LIB.stat().st_mtime
 
 
-def build(force: bool = False, verbose: bool = False) -> Path:
-    """Compile every kernel for sm_100a into one shared library next to the package."""
+PROBE_LIB = PKG / "libfastdms_b200_probe.so"
+
+
+def build(force: bool = False, verbose: bool = False, probe: bool = False) -> Path:
+    """Compile every kernel for sm_100a into one shared library next to the package.  `probe=True`
+    builds a second library, libfastdms_b200_probe.so, whose attention kernels record phase timestamps
+    (-DFDMS_ATTN_PROBE); load it by setting FDMS_B200_LIB to its path."""
+    if probe:
+        cmd = [_nvcc(), *NVCC_FLAGS, "-DFDMS_ATTN_PROBE", "-o", str(PROBE_LIB), *[str(CSRC / s) for s in SOURCES]]
+        proc = subprocess.run(cmd, capture_output=True, text=True)
+        if proc.returncode != 0:
+            print(proc.stdout, proc.stderr)
+            raise RuntimeError(f"nvcc failed with exit code {proc.returncode}")
+        return PROBE_LIB
     if not force and not needs_build():
         return LIB
     cmd = [_nvcc(), *NVCC_FLAGS, "-o", str(LIB), *[str(CSRC / s) for s in SOURCES]]
@@ -48,4 +60,8 @@ def build(force: bool = False, verbose: bool = False) -> Path:
 
 
 if __name__ == "__main__":
-    build(force=True, verbose=True)
+    import sys
+    if "--probe" in sys.argv:
+        print(build(probe=True))
+    else:
+        build(force=True, verbose=True)

@@ -163,6 +163,27 @@ __device__ __forceinline__ int tokrow(int u, int n) {
     return 8 * u + 2 * tp + ((n & 1) ^ (tp & 1));
 }
 
+// Phase probe (compiled in only with -DFDMS_ATTN_PROBE, e.g. `python -m fastdms_b200.build --probe`):
+// thread 0 of every CTA of the fast kernels records the global nanosecond timer at the phases below,
+// and fdms_attn_probe_read copies the table of the most recent launch to the host
+// (benchmarks/attn_timeline.py prints it).  Off by default: the production kernels carry no probe code.
+enum { kProbeStart = 0, kProbeIssued, kProbeDependency, kProbeQReady, kProbePagesDone, kProbeCtaFolded, kProbeEnd, kProbePhases };
+constexpr int kProbeMaxCtas = 4096;
+#ifdef FDMS_ATTN_PROBE
+__device__ unsigned long long g_attn_probe[kProbePhases][kProbeMaxCtas];
+#define FDMS_PROBE(phase)                                                                      \
+    do {                                                                                       \
+        if (threadIdx.x == 0) {                                                                \
+            const unsigned cta_ = blockIdx.y * gridDim.x + blockIdx.x;                         \
+            unsigned long long t_;                                                             \
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_));                             \
+            if (cta_ < (unsigned)kProbeMaxCtas) g_attn_probe[(phase)][cta_] = t_;              \
+        }                                                                                      \
+    } while (0)
+#else
+#define FDMS_PROBE(phase) do { } while (0)
+#endif
+
 struct AttnParams;
 __device__ __forceinline__ int64_t checked_rope_position(const AttnParams& p, int b);
 
@@ -513,6 +534,7 @@ __device__ __forceinline__ void fold_and_write(const AttnParams& p, float* s_m, 
             }
         }
     }
+    FDMS_PROBE(kProbeCtaFolded);
     if (S == 1 && CH == 1) return;
     if (S > 1) {
         cluster_arrive_release();               // phase 2: partials are in the leader's shared memory
@@ -547,6 +569,7 @@ __device__ __forceinline__ void fold_and_write(const AttnParams& p, float* s_m, 
             }
         }
     }
+    FDMS_PROBE(kProbeEnd);
     if (CH == 1) return;
 
     // ---- several clusters per span: the last leader to arrive folds the chunk partials ----
@@ -624,6 +647,7 @@ __global__ void __launch_bounds__(kConsumerThreads, (D == 64 ? 2 : 1)) attn_deco
     const int part = chunk * S + rank, nparts = S * CH;
     const int b = item / p.hk, h = item - b * p.hk;
 
+    FDMS_PROBE(kProbeStart);
     if (S > 1) cluster_arrive_relaxed();        // phase 1: "every CTA of the cluster has started"
     grid_launch_dependents();
     if (tid == 0) s_last = 0;
@@ -709,7 +733,9 @@ __global__ void __launch_bounds__(kConsumerThreads, (D == 64 ? 2 : 1)) attn_deco
         const int64_t r = trow0 + (live - 1 - tail_pi * kPage);
         tail_row = (trow0 >= 0 && r < p.pool_rows) ? r : -2;
     }
+    FDMS_PROBE(kProbeIssued);
     grid_dependency_wait();
+    FDMS_PROBE(kProbeDependency);
     if (deferred) {
         my_ok = issue(lane, my_id);
         next_id(lane + R);
@@ -777,6 +803,7 @@ __global__ void __launch_bounds__(kConsumerThreads, (D == 64 ? 2 : 1)) attn_deco
     } else {
         load_q_frags<D>(p, b, h, g, t, qa);
     }
+    FDMS_PROBE(kProbeQReady);
 
     const int r_new = live - 1 - tail_pi * kPage;            // row of the new token inside the span's last page
     float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.0f, 0.0f};
@@ -818,6 +845,7 @@ __global__ void __launch_bounds__(kConsumerThreads, (D == 64 ? 2 : 1)) attn_deco
         if (++s == R) { s = 0; phase ^= 1u; }
     }
     __syncthreads();                              // s_last initialised, all warps done with their pages
+    FDMS_PROBE(kProbePagesDone);
     fold_and_write<D>(p, s_m, s_l, s_o, r_ml, r_o, &s_last, tid, warp, g, t, b, h, item, rank, chunk, m_run, l_run, o);
 }
 
@@ -860,6 +888,7 @@ __global__ void __launch_bounds__(kDirectThreads, (D == 64 ? 2 : 1)) attn_decode
     const int part = chunk * S + rank, nparts = S * CH;
     const int b = item / p.hk, h = item - b * p.hk;
 
+    FDMS_PROBE(kProbeStart);
     if (S > 1) cluster_arrive_relaxed();        // phase 1: "every CTA of the cluster has started"
     grid_launch_dependents();
     if (tid == 0) s_last = 0;
@@ -928,7 +957,9 @@ __global__ void __launch_bounds__(kDirectThreads, (D == 64 ? 2 : 1)) attn_decode
     // The span's last page holds the row written by the preceding kernel of the stream (or, in append
     // mode, older rows only), and q / k / v come from it: all are read only after the dependency has
     // been resolved.
+    FDMS_PROBE(kProbeIssued);
     grid_dependency_wait();
+    FDMS_PROBE(kProbeDependency);
 #pragma unroll
     for (int s = 0; s < DEPTH; ++s)
         if (s < nw && pg0 + s * stride_pg == tail_pi) issue(s, s);
@@ -995,6 +1026,7 @@ __global__ void __launch_bounds__(kDirectThreads, (D == 64 ? 2 : 1)) attn_decode
     } else {
         load_q_frags<D>(p, b, h, g, t, qa);
     }
+    FDMS_PROBE(kProbeQReady);
 
     // the warp that owns the span's last page patches the new row into its register image
     const bool own_tail = APPEND && nw > 0 && tail_pi >= pg0 && (tail_pi - pg0) % stride_pg == 0;
@@ -1027,6 +1059,7 @@ __global__ void __launch_bounds__(kDirectThreads, (D == 64 ? 2 : 1)) attn_decode
         }
     }
     __syncthreads();                              // s_last initialised, all warps done with their pages
+    FDMS_PROBE(kProbePagesDone);
     fold_and_write<D>(p, s_m, s_l, s_o, r_ml, r_o, &s_last, tid, warp, g, t, b, h, item, rank, chunk, m_run, l_run, o);
 }
 
@@ -1536,3 +1569,18 @@ extern "C" int32_t fdms_attn_decode_noalloc(
                             head_dim, scale, q_rope_positions, q_rope_cos_sin, cos_sin_stride, cos_sin_rows, scratch,
                             (int64_t)kStaticScratchBytes, 0, dev_status, stream);
 }
+
+#ifdef FDMS_ATTN_PROBE
+// Probe builds only: copies the phase table of the most recent fast-kernel launch, [phases][ctas] nanoseconds
+// of the global timer, to `host` (phases * ctas values, ctas <= 4096).  Synchronises the device.
+extern "C" int32_t fdms_attn_probe_read(unsigned long long* host, int32_t phases, int32_t ctas) {
+    clear_error();
+    FDMS_REQUIRE(host && phases > 0 && phases <= kProbePhases && ctas > 0 && ctas <= kProbeMaxCtas, FDMS_E_ARG,
+                 "fdms_attn_probe_read: bad arguments");
+    FDMS_CUDA_OK(cudaDeviceSynchronize());
+    for (int ph = 0; ph < phases; ++ph)
+        FDMS_CUDA_OK(cudaMemcpyFromSymbol(host + (size_t)ph * ctas, g_attn_probe, (size_t)ctas * sizeof(unsigned long long),
+                                          (size_t)ph * kProbeMaxCtas * sizeof(unsigned long long), cudaMemcpyDeviceToHost));
+    return FDMS_OK;
+}
+#endif
