@@ -50,7 +50,8 @@ def run(args) -> dict:
         max_num_batched_tokens=max(c * args.prompt_len, 16384), kv_cache_dtype="float8_e4m3fn",
         tensor_parallel_size=args.tp, compact_kv_paged=args.paged, enforce_eager=args.eager,
         dms_window_size=args.window, dms_expiry_interval=args.expiry_interval,
-        prefill_chunk_size=args.prefill_chunk or None, decode_run_ahead=getattr(args, "run_ahead", False))
+        prefill_chunk_size=args.prefill_chunk or None, decode_run_ahead=getattr(args, "run_ahead", False),
+        fp8_weights=getattr(args, "fp8_weights", False))
     # replicas draw different prompts; tensor-parallel ranks must see the same ones
     g = torch.Generator().manual_seed(args.seed + (rank if args.tp == 1 else 0))
     vocab = hf["vocab_size"]
@@ -106,7 +107,7 @@ def run(args) -> dict:
         "concurrency_per_replica": c, "prompt_len": args.prompt_len, "decode_steps_timed": steps,
         "decode_tok_s": replicas * c * steps / t_decode, "decode_ms_per_step": t_decode / steps * 1e3,
         "prefill_tok_s": replicas * c * args.prompt_len / t_prefill, "prefill_s": t_prefill, "prefill_steps": prefill_steps,
-        "prefill_chunk": args.prefill_chunk, "run_ahead": bool(getattr(args, "run_ahead", False)), "kv_dtype": "float8_e4m3fn", "layout": "paged" if args.paged else "spans", "window": engine.model_runner.dms_metadata.window_size,
+        "prefill_chunk": args.prefill_chunk, "run_ahead": bool(getattr(args, "run_ahead", False)), "fp8_weights": bool(getattr(args, "fp8_weights", False)), "kv_dtype": "float8_e4m3fn", "layout": "paged" if args.paged else "spans", "window": engine.model_runner.dms_metadata.window_size,
         "mean_live_after_prefill": float(live0.mean()), "mean_live_at_end": float(live1.mean()),
         "compression_at_end": ctx_end / float(live1.mean()), "sample_tokens": tokens,
         "device_status": int(_lib.read_device_status(dev)),
@@ -126,6 +127,7 @@ def main() -> None:
     ap.add_argument("--paged", action="store_true")
     ap.add_argument("--prefill-chunk", type=int, default=0, help="prefill in chunks of this many tokens per prompt (0: one pass)")
     ap.add_argument("--eager", action="store_true")
+    ap.add_argument("--fp8-weights", action="store_true", help="decode streams FP8 e4m3 copies of the linear weights")
     ap.add_argument("--run-ahead", action="store_true",
                     help="launch the next decode step from device-resident tokens before this step's are read")
     ap.add_argument("--no-warmup", action="store_true")

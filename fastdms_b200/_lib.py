@@ -74,6 +74,7 @@ _SIGNATURES = {
     "fdms_ipc_region_close": (I32, [P]),
     "fdms_ipc_region_destroy": (I32, [P]),
     "fdms_allreduce_oneshot": (I32, [P, I32, I32, I64, P, P, I64, I32, P, P]),
+    "fdms_linear_decode_fp8": (I32, [P, I64, P, I64, P, P, P, I64, I32, I32, I32, I32, P]),
     "fdms_linear_allreduce_region_bytes": (I64, [I32]),
     "fdms_linear_decode_allreduce": (I32, [P, I64, P, I64, P, P, I64, I32, I32, I32, I32, P, I32, I32, P, P]),
 }

@@ -56,6 +56,7 @@ class Config:
     compact_kv_admission: str = "reserve"     # "reserve": worst case per request; "optimistic": estimate + retry
     compact_kv_admission_keep_estimate: float = 0.25
     prefill_chunk_size: int | None = None          # prompts are prefilled in chunks of this many tokens (None: one pass)
+    fp8_weights: bool = False                 # linear layers keep an FP8 e4m3 copy (per-column scale) that decode-sized inputs stream
     decode_run_ahead: bool = False            # greedy decode: next step launched from device-resident tokens before this step's are read
     random_init_seed: int | None = None       # synthetic weights when the directory has no safetensors
     dtype: str | None = None                  # overrides the checkpoint's dtype

@@ -467,6 +467,119 @@ __device__ __forceinline__ void process_page(const PageFrags<D>& f, int rows, in
     }
 }
 
+// Two pages at once (the staged kernel, head_dim 64): the same arithmetic as two calls of process_page,
+// with the two pages' instruction streams interleaved by hand.  A page's work is one long dependent
+// chain (fragment loads -> FP8 converts -> score MMAs -> softmax -> transpose -> output MMAs); the MMAs and
+// transposes are volatile asm statements that the compiler keeps in program order, so two calls in a row
+// would run the chains back to back.  Interleaved, the score MMAs of the second page issue behind those
+// of the first, one vote decides about raising the running maximum for both pages, and the output MMAs of
+// the two pages alternate on the same accumulators.  Results are bit-identical to the one-page path only
+// when no page is processed alone in one path and in a pair in the other (the maximum may be raised at
+// different pages); the fused and the plain launch pair pages identically, so they stay bit-identical.
+template <int D, bool LIN>
+__device__ __forceinline__ void process_pair(const PageFrags<D>& fa, const PageFrags<D>& fb, int rows_a, int rows_b, int g, int t,
+                                             float sl2, const uint32_t (&qa)[FastCfg<D>::kKSteps][2], float (&m_run)[2],
+                                             float (&l_run)[2], float (&o)[FastCfg<D>::kNT / 2][4]) {
+    using C = FastCfg<D>;
+    float ca[4] = {0.0f, 0.0f, 0.0f, 0.0f}, ca2[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    float cb[4] = {0.0f, 0.0f, 0.0f, 0.0f}, cb2[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+    for (int ch = 0; ch < C::kCh; ++ch) {
+        const uint32_t a0w[4] = {fa.k[0][ch].x, fa.k[0][ch].y, fa.k[0][ch].z, fa.k[0][ch].w};
+        const uint32_t a1w[4] = {fa.k[1][ch].x, fa.k[1][ch].y, fa.k[1][ch].z, fa.k[1][ch].w};
+        const uint32_t b0w[4] = {fb.k[0][ch].x, fb.k[0][ch].y, fb.k[0][ch].z, fb.k[0][ch].w};
+        const uint32_t b1w[4] = {fb.k[1][ch].x, fb.k[1][ch].y, fb.k[1][ch].z, fb.k[1][ch].w};
+#pragma unroll
+        for (int s = 0; s < 4; ++s) {
+            uint32_t a0, a1, a2, a3, e0, e1, e2, e3;
+            e4m3x4_to_f16x2x2(a0w[s], a0, a2);
+            e4m3x4_to_f16x2x2(a1w[s], a1, a3);
+            e4m3x4_to_f16x2x2(b0w[s], e0, e2);
+            e4m3x4_to_f16x2x2(b1w[s], e1, e3);
+            if (s & 1) {
+                mma_full(ca2, a0, a1, a2, a3, qa[4 * ch + s][0], qa[4 * ch + s][1]);
+                mma_full(cb2, e0, e1, e2, e3, qa[4 * ch + s][0], qa[4 * ch + s][1]);
+            } else {
+                mma_full(ca, a0, a1, a2, a3, qa[4 * ch + s][0], qa[4 * ch + s][1]);
+                mma_full(cb, e0, e1, e2, e3, qa[4 * ch + s][0], qa[4 * ch + s][1]);
+            }
+        }
+    }
+    // scores [page][token row u][head e]
+    float sc[2][2][2] = {{{(ca[0] + ca2[0]) * sl2, (ca[1] + ca2[1]) * sl2}, {(ca[2] + ca2[2]) * sl2, (ca[3] + ca2[3]) * sl2}},
+                         {{(cb[0] + cb2[0]) * sl2, (cb[1] + cb2[1]) * sl2}, {(cb[2] + cb2[2]) * sl2, (cb[3] + cb2[3]) * sl2}}};
+    if (rows_a < kPage || rows_b < kPage) {
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+            if (tokrow<LIN>(u, g) >= rows_a) { sc[0][u][0] = -INFINITY; sc[0][u][1] = -INFINITY; }
+            if (tokrow<LIN>(u, g) >= rows_b) { sc[1][u][0] = -INFINITY; sc[1][u][1] = -INFINITY; }
+        }
+    }
+    constexpr float kMaxSlack = 8.0f;
+    float mx[2] = {fmaxf(fmaxf(sc[0][0][0], sc[0][1][0]), fmaxf(sc[1][0][0], sc[1][1][0])),
+                   fmaxf(fmaxf(sc[0][0][1], sc[0][1][1]), fmaxf(sc[1][0][1], sc[1][1][1]))};
+    const bool raise = mx[0] > m_run[0] + kMaxSlack || mx[1] > m_run[1] + kMaxSlack || m_run[0] == -INFINITY || m_run[1] == -INFINITY;
+    if (__any_sync(0xffffffffu, raise)) {
+        float alpha[2];
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+            float v = mx[e];
+            v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 4));
+            v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 8));
+            v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 16));
+            const float m_new = fmaxf(m_run[e], v);
+            alpha[e] = ex2(m_run[e] - m_new);
+            l_run[e] *= alpha[e];
+            m_run[e] = m_new;
+        }
+#pragma unroll
+        for (int j = 0; j < C::kNT / 2; ++j) { o[j][0] *= alpha[0]; o[j][1] *= alpha[1]; o[j][2] *= alpha[0]; o[j][3] *= alpha[1]; }
+    }
+    float pr[2][2][2];
+#pragma unroll
+    for (int pg = 0; pg < 2; ++pg)
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+            pr[pg][0][e] = ex2(sc[pg][0][e] - m_run[e]);
+            pr[pg][1][e] = ex2(sc[pg][1][e] - m_run[e]);
+        }
+#pragma unroll
+    for (int e = 0; e < 2; ++e) l_run[e] += (pr[0][0][e] + pr[0][1][e]) + (pr[1][0][e] + pr[1][1][e]);
+    const uint32_t pa0 = movmatrix_trans(pack_f16x2(pr[0][0][0], pr[0][0][1]));
+    const uint32_t pb0 = movmatrix_trans(pack_f16x2(pr[1][0][0], pr[1][0][1]));
+    const uint32_t pa1 = movmatrix_trans(pack_f16x2(pr[0][1][0], pr[0][1][1]));
+    const uint32_t pb1 = movmatrix_trans(pack_f16x2(pr[1][1][0], pr[1][1][1]));
+#pragma unroll
+    for (int ch = 0; ch < C::kCh; ++ch) {
+        uint2 va[2][2] = {{fa.va[0][ch], fa.va[1][ch]}, {fb.va[0][ch], fb.va[1][ch]}};     // [page][u]
+        uint2 vb[2][2] = {{fa.vb[0][ch], fa.vb[1][ch]}, {fb.vb[0][ch], fb.vb[1][ch]}};
+        if (rows_a < kPage || rows_b < kPage) {                                             // stale bytes must not reach the MMA
+#pragma unroll
+            for (int u = 0; u < 2; ++u) {
+                if (tokrow<LIN>(u, 2 * t) >= rows_a) va[0][u] = make_uint2(0u, 0u);
+                if (tokrow<LIN>(u, 2 * t + 1) >= rows_a) vb[0][u] = make_uint2(0u, 0u);
+                if (tokrow<LIN>(u, 2 * t) >= rows_b) va[1][u] = make_uint2(0u, 0u);
+                if (tokrow<LIN>(u, 2 * t + 1) >= rows_b) vb[1][u] = make_uint2(0u, 0u);
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const uint32_t sel = (j & 1) ? 0x7362u : 0x5140u;
+            uint32_t a0, a1, a2, a3, e0, e1, e2, e3;
+            const uint32_t la0 = (j >> 1) ? va[0][0].y : va[0][0].x, ha0 = (j >> 1) ? vb[0][0].y : vb[0][0].x;
+            const uint32_t la1 = (j >> 1) ? va[0][1].y : va[0][1].x, ha1 = (j >> 1) ? vb[0][1].y : vb[0][1].x;
+            const uint32_t lb0 = (j >> 1) ? va[1][0].y : va[1][0].x, hb0 = (j >> 1) ? vb[1][0].y : vb[1][0].x;
+            const uint32_t lb1 = (j >> 1) ? va[1][1].y : va[1][1].x, hb1 = (j >> 1) ? vb[1][1].y : vb[1][1].x;
+            e4m3x4_to_f16x2x2(__byte_perm(la0, ha0, sel), a0, a1);
+            e4m3x4_to_f16x2x2(__byte_perm(la1, ha1, sel), a2, a3);
+            e4m3x4_to_f16x2x2(__byte_perm(lb0, hb0, sel), e0, e1);
+            e4m3x4_to_f16x2x2(__byte_perm(lb1, hb1, sel), e2, e3);
+            mma_full(o[4 * ch + j], a0, a1, a2, a3, pa0, pa1);
+            mma_full(o[4 * ch + j], e0, e1, e2, e3, pb0, pb1);
+        }
+    }
+}
+
 // Shared tail of the fast kernels (called by the 256 consumer threads of a CTA): folds the warps'
 // partial (m, l, O) in shared memory, sends the CTA's partial to the cluster leader through
 // distributed shared memory, and lets the leader (or, with several clusters per span, the last
@@ -602,6 +715,82 @@ __device__ __forceinline__ void fold_and_write(const AttnParams& p, float* s_m, 
                              Lsum > 0.0f ? acc / Lsum * vs : 0.0f);
         }
     }
+}
+
+constexpr int kDirectFoldLimit = 16;       // splits * group up to which the one-level merge is used
+
+// One-level merge for the staged kernel, used when splits * group <= 16 and there is one cluster per span:
+// every warp of every CTA of the cluster writes its partial (m, l, O) straight into the LEADER's shared
+// memory (distributed shared memory stores), one cluster barrier publishes them, and the leader folds the
+// splits * 8 partials and writes the output.  Compared with fold_and_write this drops the CTA-local
+// staging pass and its barrier from the critical path of the launch.  Slot layout in the leader, reusing
+// the s_m / s_l / s_o area:  [splits * 8 warps][group][D + 4] floats (O in 0..D-1, m at D, l at D + 1).
+__device__ __forceinline__ void st_cluster_v4(uint32_t addr, float4 v) {
+    asm volatile("st.shared::cluster.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w) : "memory");
+}
+__device__ __forceinline__ void st_cluster_v2(uint32_t addr, float2 v) {
+    asm volatile("st.shared::cluster.v2.f32 [%0], {%1, %2};" ::"r"(addr), "f"(v.x), "f"(v.y) : "memory");
+}
+
+template <int D>
+__device__ __forceinline__ void fold_direct(const AttnParams& p, float* s_slots, int tid, int warp, int g, int t, int b, int h,
+                                            int rank, float (&m_run)[2], float (&l_run)[2], float (&o)[FastCfg<D>::kNT / 2][4]) {
+    using C = FastCfg<D>;
+    constexpr int kRow = D + 4;
+    const int S = p.splits, G = p.group;
+    if (S > 1) cluster_wait_acquire();          // phase 1 complete: the leader's shared memory exists
+    const uint32_t base = S > 1 ? map_to_rank(s_slots, 0) : smem_u32(s_slots);
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+        float l = l_run[e];
+        l += __shfl_xor_sync(0xffffffffu, l, 4);
+        l += __shfl_xor_sync(0xffffffffu, l, 8);
+        l += __shfl_xor_sync(0xffffffffu, l, 16);
+        const int hh = 2 * t + e;
+        if (hh < G) {
+            const uint32_t row = base + (uint32_t)((((rank * kConsumerWarps + warp) * G + hh) * kRow) * 4);
+#pragma unroll
+            for (int ch = 0; ch < C::kCh; ++ch) {
+                const uint32_t dst = row + (uint32_t)((64 * ch + 8 * g) * 4);
+                const float4 lo = make_float4(o[4 * ch + 0][e], o[4 * ch + 0][2 + e], o[4 * ch + 1][e], o[4 * ch + 1][2 + e]);
+                const float4 hi = make_float4(o[4 * ch + 2][e], o[4 * ch + 2][2 + e], o[4 * ch + 3][e], o[4 * ch + 3][2 + e]);
+                if (S > 1) { st_cluster_v4(dst, lo); st_cluster_v4(dst + 16, hi); }
+                else { *(float4*)(s_slots + (dst - base) / 4) = lo; *(float4*)(s_slots + (dst - base) / 4 + 4) = hi; }
+            }
+            if (g == 0) {
+                if (S > 1) st_cluster_v2(row + (uint32_t)(D * 4), make_float2(m_run[e], l));
+                else *(float2*)(s_slots + (row - base) / 4 + D) = make_float2(m_run[e], l);
+            }
+        }
+    }
+    FDMS_PROBE(kProbeCtaFolded);
+    if (S > 1) {
+        cluster_arrive_release();               // phase 2: every warp's partial is in the leader's shared memory
+        cluster_wait_acquire();
+        if (rank != 0) return;
+    } else {
+        consumer_bar();
+    }
+    const float vs = p.v_scale ? p.v_scale[h] : 1.0f;
+    const int slots = S * kConsumerWarps;
+    for (int e = tid; e < G * D; e += kConsumerThreads) {
+        const int gg = e / D, d = e - gg * D;
+        const float* col = s_slots + (size_t)gg * kRow;
+        float M = -INFINITY;
+        for (int w = 0; w < slots; ++w) M = fmaxf(M, col[(size_t)w * G * kRow + D]);
+        float acc = 0.0f, Lsum = 0.0f;
+        if (M != -INFINITY) {
+            for (int w = 0; w < slots; ++w) {
+                const float* r = col + (size_t)w * G * kRow;
+                const float f = ex2(r[D] - M);
+                acc += f * r[d];
+                Lsum += f * r[D + 1];
+            }
+        }
+        store_from_float(p.out, (int64_t)b * p.out_sb + (int64_t)(h * G + gg) * p.out_sh + d, p.out_dtype,
+                         Lsum > 0.0f ? acc / Lsum * vs : 0.0f);
+    }
+    FDMS_PROBE(kProbeEnd);
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -812,40 +1001,69 @@ __global__ void __launch_bounds__(kConsumerThreads, (D == 64 ? 2 : 1)) attn_deco
     for (int j = 0; j < C::kNT / 2; ++j) { o[j][0] = 0.0f; o[j][1] = 0.0f; o[j][2] = 0.0f; o[j][3] = 0.0f; }
 
     int issued = min(nw, R);                     // warp-local pages whose slot has been armed
+    constexpr bool kPairs = D == 64;             // two pages per round (process_pair); 128-wide heads have no registers for it
     int s = 0;
     uint32_t phase = 0;
-    for (int i = 0; i < nw; ++i) {
-        const bool landed = mbar_wait(&bars[s], phase, kWaitLimit);
+    for (int i = 0; i < nw;) {
+        const bool pair = kPairs && R >= 2 && i + 1 < nw;
+        int s2 = s + 1;
+        uint32_t phase2 = phase;
+        if (s2 == R) { s2 = 0; phase2 ^= 1u; }
+        bool landed = mbar_wait(&bars[s], phase, kWaitLimit);
+        if (pair) landed = mbar_wait(&bars[s2], phase2, kWaitLimit) && landed;
         if (!__all_sync(0xffffffffu, landed)) {
             if (lane == 0 && p.dev_status) atomicOr(p.dev_status, FDMS_DEV_WAIT_TIMEOUT);
-            for (int j = i + 1; j < issued; ++j) mbar_wait(&bars[j % R], (uint32_t)(j / R) & 1u, kWaitLimitDrain);
+            for (int j = i; j < issued; ++j) mbar_wait(&bars[j % R], (uint32_t)(j / R) & 1u, kWaitLimitDrain);
             break;
         }
-        const int pi = pg0 + i * stride_pg;
+        const int pi = pg0 + i * stride_pg, pi2 = pi + stride_pg;
         const int rows = min(kPage, live - pi * kPage);
+        const int rows2 = pair ? min(kPage, live - pi2 * kPage) : 0;
         const bool good = __shfl_sync(0xffffffffu, my_ok, s);
+        const bool good2 = pair && __shfl_sync(0xffffffffu, my_ok, s2);
         uint8_t* Ks = ring + (size_t)s * C::kStageBytes;
-        if (APPEND && pi == tail_pi) {
+        uint8_t* Ks2 = ring + (size_t)s2 * C::kStageBytes;
+        if (APPEND && (pi == tail_pi || (pair && pi2 == tail_pi))) {
             // the new row of the span is not in the pool image the copy brought: write it into the slot
-            if (lane < D / 16) *(uint4*)(Ks + r_new * D + 16 * lane) = *(const uint4*)(s_new + 16 * lane);
-            else if (lane < D / 8) *(uint4*)(Ks + C::kPageBytes + r_new * D + 16 * (lane - D / 16)) = *(const uint4*)(s_new + D + 16 * (lane - D / 16));
+            uint8_t* Kt = pi == tail_pi ? Ks : Ks2;
+            if (lane < D / 16) *(uint4*)(Kt + r_new * D + 16 * lane) = *(const uint4*)(s_new + 16 * lane);
+            else if (lane < D / 8) *(uint4*)(Kt + C::kPageBytes + r_new * D + 16 * (lane - D / 16)) = *(const uint4*)(s_new + D + 16 * (lane - D / 16));
             __syncwarp();
         }
-        if (good) {
-            PageFrags<D> f;
-            load_frags_smem<D>(Ks, Ks + C::kPageBytes, g, t, f);
-            process_page<D, false>(f, rows, g, t, sl2, qa, m_run, l_run, o);
+        if (kPairs && pair && good && good2) {
+            PageFrags<D> fa, fb;
+            load_frags_smem<D>(Ks, Ks + C::kPageBytes, g, t, fa);
+            load_frags_smem<D>(Ks2, Ks2 + C::kPageBytes, g, t, fb);
+            process_pair<D, false>(fa, fb, rows, rows2, g, t, sl2, qa, m_run, l_run, o);
+        } else {
+            if (good) {
+                PageFrags<D> f;
+                load_frags_smem<D>(Ks, Ks + C::kPageBytes, g, t, f);
+                process_page<D, false>(f, rows, g, t, sl2, qa, m_run, l_run, o);
+            }
+            if (good2) {
+                PageFrags<D> f;
+                load_frags_smem<D>(Ks2, Ks2 + C::kPageBytes, g, t, f);
+                process_page<D, false>(f, rows2, g, t, sl2, qa, m_run, l_run, o);
+            }
         }
-        __syncwarp();                             // every lane has consumed its fragments of the slot
-        if (i + R < nw && lane == s) {
-            my_ok = issue(i + R, my_id);
-            next_id(i + 2 * R);
+        __syncwarp();                             // every lane has consumed its fragments of the slot(s)
+        if (i + R < nw) {
+            if (lane == s) { my_ok = issue(i + R, my_id); next_id(i + 2 * R); }
+            ++issued;
         }
-        if (i + R < nw) ++issued;
+        if (pair && i + 1 + R < nw) {
+            if (lane == s2) { my_ok = issue(i + 1 + R, my_id); next_id(i + 1 + 2 * R); }
+            ++issued;
+        }
+        if (pair) { i += 2; s = s2; phase = phase2; } else { i += 1; }
         if (++s == R) { s = 0; phase ^= 1u; }
     }
     __syncthreads();                              // s_last initialised, all warps done with their pages
     FDMS_PROBE(kProbePagesDone);
+    if (CH == 1 && S * G <= kDirectFoldLimit)
+        fold_direct<D>(p, s_m, tid, warp, g, t, b, h, rank, m_run, l_run, o);
+    else
     fold_and_write<D>(p, s_m, s_l, s_o, r_ml, r_o, &s_last, tid, warp, g, t, b, h, item, rank, chunk, m_run, l_run, o);
 }
 
@@ -1171,7 +1389,12 @@ static int env_int(const char* name, int dflt) {
 static size_t staged_smem_bytes(int D, int ring, int splits, int group) {
     size_t s = (size_t)kConsumerWarps * ring * 2 * kPage * D;       // per-warp rings
     s += (size_t)kConsumerWarps * kMaxRing * sizeof(uint64_t);     // barriers
-    s += (size_t)kConsumerWarps * kMaxGroup * (2 + D + 4) * sizeof(float);
+    size_t fold = (size_t)kConsumerWarps * kMaxGroup * (2 + D + 4) * sizeof(float);      // two-level merge: CTA-local partials
+    if (splits * group <= kDirectFoldLimit) {                      // one-level merge: every warp of the cluster has a slot
+        const size_t slots = (size_t)splits * kConsumerWarps * group * (D + 4) * sizeof(float);
+        if (slots > fold) fold = slots;
+    }
+    s += fold;
     s += (size_t)splits * group * (2 + D) * sizeof(float);
     return s + 128;
 }

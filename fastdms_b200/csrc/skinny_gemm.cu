@@ -255,3 +255,167 @@ extern "C" int32_t fdms_linear_decode_norm(
     return linear_decode_launch(x, x_row_stride, weight, w_row_stride, bias, y, y_row_stride, dtype, rows, out_features,
                                 in_features, &n, stream);
 }
+
+// ------------------------------------------------------------------------------------------------
+// FP8 (e4m3) weights with one float32 scale per output column: y = (x W8^T) * scale (+ bias).
+// Half the weight bytes of the 16-bit kernel for the same layer (the reference's opt-in FP8 weight path,
+// fastdms/layers/linear.py:548-662, quantises the activations as well and calls torch._scaled_mm; here
+// the activations stay 16-bit and only the weights are stored in FP8).  Same decomposition as above:
+// 8 warps split K, weight rows on the M side of mma.sync.m16n8k16.  A lane streams 16-byte vectors of
+// 16 weights; the bytes are converted EXACTLY to f16 pairs in registers (cvt.rn.f16x2.e4m3x2) and the
+// activations are converted to f16 once per CTA (exact for bf16 values inside the f16 range, which
+// decode activations are), so the products are exact and the accumulation is float32.  The MMA's k
+// index is again a fixed permutation of memory order shared by both operands: a lane's eight k-pairs
+// are the eight byte pairs of its weight vector and the eight 32-bit words of the matching 32 bytes of x.
+// ------------------------------------------------------------------------------------------------
+namespace fdms {
+
+constexpr int kSg8Vecs = 4;            // 16-byte weight vectors per lane, row and step: 256 k elements per warp and step
+
+__device__ __forceinline__ void sg8_cvt(uint32_t w, uint32_t& lo, uint32_t& hi) {       // 4 e4m3 bytes -> 2 f16x2
+    asm("{\n\t.reg .b16 a, b;\n\tmov.b32 {a, b}, %2;\n\tcvt.rn.f16x2.e4m3x2 %0, a;\n\tcvt.rn.f16x2.e4m3x2 %1, b;\n\t}"
+        : "=r"(lo), "=r"(hi) : "r"(w));
+}
+__device__ __forceinline__ void sg8_mma(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+// 8 consecutive 16-bit activations -> 4 f16x2 words
+template <bool BF16>
+__device__ __forceinline__ void sg8_x_to_f16(const uint4& v, uint32_t (&o)[4]) {
+    const uint32_t u[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        if (BF16) {
+            const __half2 h = __floats2half2_rn(__uint_as_float(u[i] << 16), __uint_as_float(u[i] & 0xffff0000u));
+            o[i] = *(const uint32_t*)&h;
+        } else {
+            o[i] = u[i];
+        }
+    }
+}
+
+template <bool BF16, int NT>
+__global__ void __launch_bounds__(kSgWarps * 32) skinny_gemm_fp8_kernel(
+    const uint16_t* __restrict__ x, int64_t x_stride, const uint8_t* __restrict__ w, int64_t w_stride,
+    const float* __restrict__ scale, const uint16_t* __restrict__ bias, uint16_t* __restrict__ y, int64_t y_stride,
+    int M, int N, int K) {
+    __shared__ float s_part[kSgWarps][NT][128];
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
+    const int n0 = blockIdx.x * 16 * NT;
+    const int kslice = K / kSgWarps, k_begin = warp * kslice;
+    float acc[NT][4];
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) { acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.0f; }
+    pdl_trigger();
+    // first tile's weight vectors before the dependency is resolved (weights are written by nobody)
+    uint4 wa[kSg8Vecs], wb[kSg8Vecs];
+    {
+        const uint8_t* w0 = w + (int64_t)(n0 + g) * w_stride + k_begin + 16 * t;
+        const uint8_t* w1 = w0 + 8 * w_stride;
+#pragma unroll
+        for (int j = 0; j < kSg8Vecs; ++j) {
+            wa[j] = __ldcs((const uint4*)(w0 + 64 * j));
+            wb[j] = __ldcs((const uint4*)(w1 + 64 * j));
+        }
+    }
+    pdl_wait();
+    const uint16_t* xr = x + (int64_t)g * x_stride + k_begin + 16 * t;
+    for (int ks = 0; ks < kslice; ks += kSgStep) {
+        uint32_t xb[kSg8Vecs][8];
+#pragma unroll
+        for (int j = 0; j < kSg8Vecs; ++j) {
+            if (g >= M) {
+#pragma unroll
+                for (int i = 0; i < 8; ++i) xb[j][i] = 0u;
+                continue;
+            }
+            uint32_t lo[4], hi[4];
+            sg8_x_to_f16<BF16>(__ldg((const uint4*)(xr + ks + 64 * j)), lo);
+            sg8_x_to_f16<BF16>(__ldg((const uint4*)(xr + ks + 64 * j + 8)), hi);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) { xb[j][i] = lo[i]; xb[j][4 + i] = hi[i]; }
+        }
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) {
+            if (n0 + nt * 16 >= N) break;                           // uniform: the last CTA may own fewer tiles
+            const uint8_t* w0 = w + (int64_t)(n0 + nt * 16 + g) * w_stride + k_begin + ks + 16 * t;
+            const uint8_t* w1 = w0 + 8 * w_stride;
+            if (ks != 0 || nt != 0) {
+#pragma unroll
+                for (int j = 0; j < kSg8Vecs; ++j) {
+                    wa[j] = __ldcs((const uint4*)(w0 + 64 * j));
+                    wb[j] = __ldcs((const uint4*)(w1 + 64 * j));
+                }
+            }
+#pragma unroll
+            for (int j = 0; j < kSg8Vecs; ++j) {
+                const uint32_t aw[4] = {wa[j].x, wa[j].y, wa[j].z, wa[j].w}, bw[4] = {wb[j].x, wb[j].y, wb[j].z, wb[j].w};
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    uint32_t a0, a2, a1, a3;
+                    sg8_cvt(aw[i], a0, a2);                        // bytes 4i, 4i+1 | 4i+2, 4i+3 of row g
+                    sg8_cvt(bw[i], a1, a3);                        // the same bytes of row g + 8
+                    sg8_mma(acc[nt], a0, a1, a2, a3, xb[j][2 * i], xb[j][2 * i + 1]);
+                }
+            }
+        }
+    }
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+        *(float2*)&s_part[warp][nt][g * 8 + 2 * t] = make_float2(acc[nt][0], acc[nt][1]);
+        *(float2*)&s_part[warp][nt][(g + 8) * 8 + 2 * t] = make_float2(acc[nt][2], acc[nt][3]);
+    }
+    __syncthreads();
+    for (int idx = tid; idx < NT * 128; idx += kSgWarps * 32) {
+        const int nt = idx >> 7, r = idx & 127, m = r & 7, nl = r >> 3;
+        const int n = n0 + nt * 16 + nl;
+        if (m >= M || n >= N) continue;
+        float sum = 0.0f;
+#pragma unroll
+        for (int wv = 0; wv < kSgWarps; ++wv) sum += s_part[wv][nt][nl * 8 + m];
+        sum *= scale[n];
+        if (bias) sum += BF16 ? __uint_as_float((uint32_t)bias[n] << 16) : __half2float(*(const __half*)&bias[n]);
+        uint16_t o;
+        if (BF16) { const __nv_bfloat16 b = __float2bfloat16_rn(sum); o = *(const uint16_t*)&b; }
+        else { const __half hh = __float2half_rn(sum); o = *(const uint16_t*)&hh; }
+        y[(int64_t)m * y_stride + n] = o;
+    }
+}
+
+}  // namespace fdms
+
+extern "C" int32_t fdms_linear_decode_fp8(const void* x, int64_t x_row_stride, const void* weight_e4m3, int64_t w_row_stride,
+                                          const float* scale, const void* bias, void* y, int64_t y_row_stride, int32_t dtype,
+                                          int32_t rows, int32_t out_features, int32_t in_features, void* stream) {
+    clear_error();
+    FDMS_REQUIRE(x && weight_e4m3 && scale && y, FDMS_E_ARG, "fdms_linear_decode_fp8: null pointer");
+    FDMS_REQUIRE(dtype == FDMS_BF16 || dtype == FDMS_F16, FDMS_E_DTYPE, "fdms_linear_decode_fp8: bf16 or f16 activations only");
+    FDMS_REQUIRE(rows >= 0 && rows <= 8, FDMS_E_CAPACITY, "fdms_linear_decode_fp8: at most 8 rows, got %d", rows);
+    FDMS_REQUIRE(out_features > 0 && out_features % 16 == 0 && in_features > 0 && in_features % (kSgWarps * kSgStep) == 0,
+                 FDMS_E_ARG, "fdms_linear_decode_fp8: out_features %% 16 and in_features %% %d must be 0 (got %d, %d)",
+                 kSgWarps * kSgStep, out_features, in_features);
+    FDMS_REQUIRE(((uintptr_t)x & 15) == 0 && ((uintptr_t)weight_e4m3 & 15) == 0 && (x_row_stride * 2) % 16 == 0 &&
+                     w_row_stride % 16 == 0,
+                 FDMS_E_ARG, "fdms_linear_decode_fp8: x and weight rows must be 16-byte aligned");
+    if (rows == 0) return FDMS_OK;
+    const int tiles = out_features / 16;
+    const int nt = tiles >= 4096 ? 4 : (tiles >= 1024 ? 2 : 1);
+    const unsigned grid = (unsigned)((tiles + nt - 1) / nt);
+    const bool bf = dtype == FDMS_BF16;
+    cudaStream_t st = (cudaStream_t)stream;
+#define FDMS_SG8_LAUNCH(B, T)                                                                                    \
+    FDMS_CUDA_OK(launch_chained(skinny_gemm_fp8_kernel<B, T>, dim3(grid), dim3(kSgWarps * 32), st, chain_launches(), \
+                                (const uint16_t*)x, x_row_stride, (const uint8_t*)weight_e4m3, w_row_stride, scale,   \
+                                (const uint16_t*)bias, (uint16_t*)y, y_row_stride, (int)rows, (int)out_features,      \
+                                (int)in_features))
+#define FDMS_SG8_PICK(B)                                                                         \
+    do {                                                                                         \
+        if (nt == 4) FDMS_SG8_LAUNCH(B, 4); else if (nt == 2) FDMS_SG8_LAUNCH(B, 2); else FDMS_SG8_LAUNCH(B, 1); \
+    } while (0)
+    if (bf) FDMS_SG8_PICK(true); else FDMS_SG8_PICK(false);
+#undef FDMS_SG8_PICK
+#undef FDMS_SG8_LAUNCH
+    FDMS_CHECK_LAUNCH("skinny_gemm_fp8_kernel");
+    return FDMS_OK;
+}

@@ -91,6 +91,11 @@ class ModelRunner:
             torch.set_default_dtype(default_dtype)
         self.model.to(self.device)       # also moves the (float32, CPU-built) rotary tables
         self._load_weights()
+        if config.fp8_weights:
+            from fastdms_b200.layers.linear import LinearBase
+            for mod in self.model.modules():
+                if isinstance(mod, LinearBase) and mod.weight.dtype in (torch.bfloat16, torch.float16):
+                    mod.quantize_fp8()
         self.model.eval()
         for p in self.model.parameters():
             p.requires_grad_(False)

@@ -65,6 +65,34 @@ def norm_linear(x: torch.Tensor, residual: torch.Tensor | None, norm, lin) -> tu
     return lin(h), r
 
 
+def quantize_weight_fp8(weight: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """Per-output-column FP8 quantisation of a [out, in] weight: returns (e4m3 bytes, float32 scale per
+    row, the dequantised weight in the original dtype).  scale = absmax / 448, stored = w / scale."""
+    w = weight.detach().float()
+    scale = (w.abs().amax(dim=1) / 448.0).clamp_min(1e-12).contiguous()
+    w8 = (w / scale[:, None]).to(torch.float8_e4m3fn).contiguous()
+    return w8, scale, (w8.float() * scale[:, None]).to(weight.dtype)
+
+
+def linear_fp8(x: torch.Tensor, weight_fp8: torch.Tensor, scale: torch.Tensor, bias: torch.Tensor | None) -> torch.Tensor:
+    """One launch of `fdms_linear_decode_fp8` (decode-sized 16-bit input, FP8 weights)."""
+    rows, n = x.shape[0], weight_fp8.shape[0]
+    y = torch.empty((rows, n), dtype=x.dtype, device=x.device)
+    with torch.cuda.device(x.device):
+        rc = _lib.lib().fdms_linear_decode_fp8(
+            x.data_ptr(), x.stride(0), weight_fp8.data_ptr(), weight_fp8.stride(0), scale.data_ptr(), _lib.ptr(bias),
+            y.data_ptr(), y.stride(0), _lib.dtype_code(x.dtype), rows, n, weight_fp8.shape[1], _lib.stream_ptr(x.device))
+    _lib.check(rc)
+    return y
+
+
+def _fp8_linear_ok(x: torch.Tensor, w8: torch.Tensor, bias: torch.Tensor | None) -> bool:
+    return (_DECODE_LINEAR and x.is_cuda and x.dtype in (torch.bfloat16, torch.float16) and x.dim() == 2
+            and 0 < x.shape[0] <= 8 and x.stride(1) == 1 and w8.shape[0] % 16 == 0 and w8.shape[1] % 2048 == 0
+            and x.shape[1] == w8.shape[1] and (bias is None or bias.dtype == x.dtype)
+            and x.data_ptr() % 16 == 0 and (x.stride(0) * 2) % 16 == 0 and not torch.is_grad_enabled())
+
+
 def linear(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None = None) -> torch.Tensor:
     """`F.linear`, except that 16-bit CUDA inputs of at most 8 rows go through one launch of
     `fdms_linear_decode` (weights streamed once, f32 accumulation) when the shapes allow it; very wide
@@ -118,7 +146,19 @@ class LinearBase(nn.Module):
         else:
             self.register_parameter("bias", None)
 
+        self.weight_fp8 = None          # set by quantize_fp8(): e4m3 copy of the weight and its per-row scale
+        self.weight_scale = None
+
+    def quantize_fp8(self) -> None:
+        """Keeps an FP8 copy of the weight for decode-sized inputs and replaces the 16-bit weight by its
+        dequantised value, so that prefill (library GEMM) and decode (FP8 stream) use the same numbers."""
+        w8, scale, deq = quantize_weight_fp8(self.weight.data)
+        self.weight_fp8, self.weight_scale = w8, scale
+        self.weight.data.copy_(deq)
+
     def forward(self, x: torch.Tensor) -> torch.Tensor:
+        if self.weight_fp8 is not None and _fp8_linear_ok(x, self.weight_fp8, self.bias):
+            return linear_fp8(x, self.weight_fp8, self.weight_scale, self.bias)
         return linear(x, self.weight, self.bias)
 
 
@@ -187,4 +227,4 @@ class RowParallelLinear(LinearBase):
             y = linear(x, self.weight, self.bias if self.tp_rank == 0 else None)
             tp_all_reduce_(y)
             return y
-        return linear(x, self.weight, self.bias)
+        return LinearBase.forward(self, x)

@@ -433,6 +433,16 @@ int32_t fdms_allreduce_oneshot(
     void* const* peer_regions, int32_t rank, int32_t world, int64_t max_bytes,
     const void* in, void* out, int64_t n, int32_t dtype, int32_t* dev_status, void* stream);
 
+/* The decode-sized linear layer with FP8 (e4m3) weights and one float32 scale per output column:
+ * y = (x W8^T) * scale (+ bias); x and y 16-bit, weight_e4m3 [out_features, in_features] bytes with
+ * 16-byte aligned rows, in_features % 2048 == 0, out_features % 16 == 0, rows <= 8.  Weight-only
+ * quantisation: the bytes are converted exactly to f16 in registers and accumulated in float32 (the
+ * reference's opt-in FP8 weight path, fastdms/layers/linear.py:548-662, also quantises the activations and
+ * calls torch._scaled_mm). */
+int32_t fdms_linear_decode_fp8(const void* x, int64_t x_row_stride, const void* weight_e4m3, int64_t w_row_stride,
+                               const float* scale, const void* bias, void* y, int64_t y_row_stride, int32_t dtype,
+                               int32_t rows, int32_t out_features, int32_t in_features, void* stream);
+
 /* Row-parallel linear layer fused with its all-reduce, for decode-sized inputs (rows <= 8):
  *   y = sum over ranks of x_r W_r^T (+ bias), one kernel per rank instead of F.linear + NCCL all_reduce
  * (fastdms/layers/linear.py:1044-1048, the o_proj / down_proj call sites).  Every CTA pushes its float32

@@ -12,8 +12,9 @@ weights produces near-ties: with 1024 logits of spread 1.6 about one choice in a
 margin below 5e-3, which is the size of FP8 rounding effects, so a test can only demand the
 reference's token where the margin is larger than the logit tolerance).
 
-A third run ("bf16") loads the same weights rounded to bfloat16 (the LM head scaled by 0.2 so that
-logits stay below 2 in magnitude, where a bfloat16 ulp is well under the 2e-2 tolerance), keeps the
+A third run ("bf16") loads the same weights rounded to bfloat16 (the LM head scaled by 0.05 so that
+logits stay below 0.5 in magnitude: two bfloat16 runs of the same model differ by a few units in the last
+place of their logits, and only at that scale are a few such units well under the 2e-2 tolerance), keeps the
 FP8 compact KV and additionally records the raw DMS decision value of every (step, layer, sequence,
 KV head) -- the number that is compared with the threshold -- so that a test can tell a decision
 that sits on the threshold from one that does not.  Its greedy tokens are the history a test forces
@@ -52,7 +53,7 @@ MODEL_CFG = dict(
 PROMPT_LENS = [37, 128, 200, 511]
 DECODE_STEPS = 128
 LOGIT_STEPS = sorted(set(range(32)) | set(range(32, DECODE_STEPS, 8)) | {DECODE_STEPS - 1})
-BF16_LM_HEAD_FACTOR = 0.2
+BF16_LM_HEAD_FACTOR = 0.05
 WINDOW, ALPHA_SCALE, ALPHA_OFFSET = 16, 100.0, 5.0
 SEED = 0
 

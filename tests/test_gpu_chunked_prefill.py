@@ -271,3 +271,51 @@ def test_engine_chunked_prefill(dev, paged):
                 # the decode token appended before the snapshot may be in both; compare the prompt part
                 k1, k0 = p1 < 10_000, p0 < 10_000
                 assert np.array_equal(p1[k1], p0[k0]) and np.array_equal(e1[k1], e0[k0])
+
+
+def test_chunked_prefill_quality_guard_against_one_pass(dev):
+    """Quality guard in the pattern of the reference's benchmarks/check_dms_compact_guard.py:195-249:
+    a one-pass prefill run gives the token history, a chunked-prefill run (128-token chunks: later
+    chunks see only the rows DMS retained from earlier ones) is forced onto that history, and the two
+    runs' next-token distributions are compared step by step.  Chunking must not change what the model
+    says: mean KL divergence and the number of greedy disagreements stay under the bounds below, and a
+    chunk size that covers the prompt gives zero divergence.  (Measured on a B200: mean KLD 3.5e-3, max
+    7.9e-3, 15 of 72 greedy choices differ -- a model with random weights has many near-ties, so the
+    divergence is the meaningful figure and the bound on disagreements is loose.)"""
+    import torch.nn.functional as F
+    from fastdms_b200.sampling_params import SamplingParams
+    g = torch.Generator().manual_seed(1)
+    prompts = [torch.randint(0, 1024, (n,), generator=g).tolist() for n in (300, 511, 640)]
+    steps = 24
+
+    def run(chunk, forced=None):
+        eng = _tiny_engine(dev, chunk, False, dtype="float32", kv="float32")
+        sp = SamplingParams(temperature=0.0, max_tokens=steps + 1, ignore_eos=True)
+        seqs = [eng.add_request(p, sp) for p in prompts]
+        while any(s.num_completion_tokens == 0 for s in seqs):
+            eng.step()
+        used, logits = [[s.token_ids[-1] for s in seqs]], []
+        if forced is not None:
+            for s, t in zip(seqs, forced[0]):
+                s.token_ids[-1] = t; s.last_token = t
+        for step in range(steps):
+            eng.step()
+            logits.append(eng.model_runner.graphs[len(seqs)].logits.float().clone())
+            used.append([s.token_ids[-1] for s in seqs])
+            if forced is not None:
+                for s, t in zip(seqs, forced[step + 1]):
+                    s.token_ids[-1] = t; s.last_token = t
+        while not eng.is_finished():
+            eng.step()
+        return used, torch.stack(logits)                         # [steps, seqs, vocab]
+
+    ref_used, ref_logits = run(None)
+    for chunk, max_kld, max_flips in ((1024, 1e-9, 0), (128, 0.02, 24)):
+        used, logits = run(chunk, forced=ref_used)
+        lp_ref, lp = F.log_softmax(ref_logits, dim=-1), F.log_softmax(logits, dim=-1)
+        kld = (lp_ref.exp() * (lp_ref - lp)).sum(dim=-1)         # per (step, sequence)
+        flips = sum(int(a != b) for ra, ca in zip(ref_used[1:], used[1:]) for a, b in zip(ra, ca))
+        print(f"chunk {chunk}: mean KLD {float(kld.mean()):.3e}, max KLD {float(kld.max()):.3e}, greedy disagreements {flips}")
+        assert torch.isfinite(kld).all()
+        assert float(kld.mean()) <= max_kld, f"chunk {chunk}: mean KLD {float(kld.mean())}"
+        assert flips <= max_flips, f"chunk {chunk}: {flips} greedy disagreements"

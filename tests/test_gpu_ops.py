@@ -817,3 +817,28 @@ def test_fused_linear_allreduce_leaves_a_silent_peer_out(dev):
             x.data_ptr(), x.stride(0), w.data_ptr(), w.stride(0), None, y.data_ptr(), y.stride(0), _lib.BF16, rows, n, k,
             ptrs.data_ptr(), 2, 2, None, _lib.stream_ptr(dev))
         _lib.check(lib_rc)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("rows,n,k,bias", [(8, 3072, 2048, True), (8, 2048, 8192, False), (3, 16384, 2048, False),
+                                            (1, 128256, 2048, False), (8, 4096, 4096, True)])
+def test_fp8_weight_decode_linear_matches_float32_reference(dev, dtype, rows, n, k, bias):
+    """`fdms_linear_decode_fp8`: e4m3 weights with one scale per output column, 16-bit activations.  The
+    kernel's products are exact (FP8 bytes and activations both converted exactly to f16) and it
+    accumulates in float32, so the result is the float32 product with the dequantised weights rounded
+    once to the activation dtype."""
+    from fastdms_b200 import _lib
+    lib = _lib.lib()
+    g = torch.Generator(device=dev).manual_seed(rows + n + k)
+    w = torch.randn((n, k), device=dev, generator=g) * k ** -0.5
+    scale = (w.abs().amax(dim=1) / 448.0).float().contiguous()
+    w8 = (w / scale[:, None]).to(torch.float8_e4m3fn).contiguous()
+    x = torch.randn((rows, k), device=dev, generator=g).to(dtype)
+    b = torch.randn((n,), device=dev, generator=g).to(dtype) if bias else None
+    y = torch.full((rows, n), float("nan"), device=dev, dtype=dtype)
+    _lib.check(lib.fdms_linear_decode_fp8(x.data_ptr(), x.stride(0), w8.data_ptr(), w8.stride(0), scale.data_ptr(), _lib.ptr(b),
+                                          y.data_ptr(), y.stride(0), _lib.dtype_code(dtype), rows, n, k, _lib.stream_ptr(dev)))
+    ref = (x.float() @ w8.float().t()) * scale[None, :] + (b.float() if bias else 0.0)
+    err = (y.float() - ref).abs()
+    ulp = ref.abs() * (2.0 ** -8 if dtype == torch.bfloat16 else 2.0 ** -11) + 1e-4
+    assert torch.isfinite(y.float()).all() and bool((err <= 1.01 * ulp).all()), float((err / ulp).max())
