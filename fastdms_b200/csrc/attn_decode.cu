@@ -32,6 +32,7 @@
 #include <stdlib.h>
 
 #include <atomic>
+#include <type_traits>
 
 #include "common.cuh"
 
@@ -143,6 +144,65 @@ __device__ __forceinline__ void mma_full(float (&c)[4], uint32_t a0, uint32_t a1
         : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
+// D(16x8, f32) += A(16x32, e4m3) * B(32x8, e4m3): the FP8 form of the warp-level MMA.  The pool's K bytes
+// go in as the A operand exactly as they were loaded, no conversion.
+__device__ __forceinline__ void mma_fp8(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                        uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k32.row.col.f32.e4m3.e4m3.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// q as the FP8 B operand of the score product, used by warps that own many pages (long spans): it removes
+// the FP8 -> f16 conversion of K, a third of the instructions of a page, at the price of quantising q once
+// per warp, which a warp with two or three pages does not earn back (those keep the f16 product).
+// A lane holds 16 consecutive elements of its head per 64-element chunk (the f16 pairs of `qa`).  They are scaled by a power of two c chosen from the largest
+// magnitude in the head group so that c * |q| lies in [128, 256), then split into two e4m3 values:
+//   hi = e4m3(c q),   lo = e4m3(16 (c q - hi)),   c q = hi + lo / 16 up to 2^-8 relative
+// (q itself is a 16-bit activation with 2^-9 relative rounding).  The score of a token is then
+// (K . hi + (K . lo) / 16) / c with both products exact in the MMA's float32 accumulator; K needs no
+// conversion at all.  Every warp of every CTA of a span derives the same c from the same q.
+constexpr float kQLoGain = 16.0f;
+constexpr int kQk8MinPages = 8;            // a warp with at least this many pages takes the FP8 score product
+template <int D>
+__device__ __forceinline__ void quantize_q(uint32_t (&qa)[D / 16][2], float& inv_c) {
+    float x[D / 4];
+#pragma unroll
+    for (int w = 0; w < D / 16; ++w) {
+        const __half2 p0 = *(const __half2*)&qa[w][0], p1 = *(const __half2*)&qa[w][1];
+        x[4 * w + 0] = __low2float(p0); x[4 * w + 1] = __high2float(p0);
+        x[4 * w + 2] = __low2float(p1); x[4 * w + 3] = __high2float(p1);
+    }
+    float mx = 0.0f;
+#pragma unroll
+    for (int i = 0; i < D / 4; ++i) mx = fmaxf(mx, fabsf(x[i]));
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    // c = 2^(7 - floor(log2 mx)), from the exponent field (exact, identical in every warp)
+    const int e = (__float_as_int(mx) >> 23) & 0xff;
+    const bool ok = e >= 8 && e <= 250;
+    const float c = ok ? __int_as_float((261 - e) << 23) : 1.0f;
+    inv_c = ok ? __int_as_float((e - 7) << 23) : 1.0f;
+#pragma unroll
+    for (int w = 0; w < D / 16; ++w) {
+        uint32_t hi = 0u, lo = 0u;
+#pragma unroll
+        for (int pr = 0; pr < 2; ++pr) {
+            const float a = x[4 * w + 2 * pr] * c, b = x[4 * w + 2 * pr + 1] * c;
+            const __nv_fp8x2_storage_t h2 = __nv_cvt_float2_to_fp8x2(make_float2(a, b), __NV_SATFINITE, __NV_E4M3);
+            const __half2_raw back = __nv_cvt_fp8x2_to_halfraw2(h2, __NV_E4M3);
+            const __half2 bh = *(const __half2*)&back;
+            const float ra = (a - __low2float(bh)) * kQLoGain, rb = (b - __high2float(bh)) * kQLoGain;
+            const __nv_fp8x2_storage_t l2 = __nv_cvt_float2_to_fp8x2(make_float2(ra, rb), __NV_SATFINITE, __NV_E4M3);
+            hi |= (uint32_t)h2 << (16 * pr);
+            lo |= (uint32_t)l2 << (16 * pr);
+        }
+        qa[w][0] = hi;          // from here on the array holds the two e4m3 parts, word by word
+        qa[w][1] = lo;
+    }
+}
+
 // Transpose of an 8x8 matrix of 16-bit elements held one register per lane (row = lane / 4).
 __device__ __forceinline__ uint32_t movmatrix_trans(uint32_t a) {
     uint32_t d;
@@ -387,28 +447,49 @@ __device__ __forceinline__ void load_frags_global(const uint8_t* Kg, const uint8
 // maximum m[e] (complete, reduced over g) and partial sum l[e] (this lane's tokens only); and
 // o[4 ch + j][2 r + e] = O[head 2t + e][64 ch + 8 g + 2 j + r].
 // Fragments of invalid rows must hold finite values (they are masked, not trusted).
-template <int D, bool LIN>
+template <int D, bool LIN, bool QK8>
 __device__ __forceinline__ void process_page(const PageFrags<D>& f, int rows, int g, int t, float sl2,
-                                             const uint32_t (&qa)[FastCfg<D>::kKSteps][2], float (&m_run)[2],
+                                             const uint32_t (&qa)[D / 16][2], float (&m_run)[2],
                                              float (&l_run)[2], float (&o)[FastCfg<D>::kNT / 2][4]) {
     using C = FastCfg<D>;
     // ---- S^T = K q^T ----
-    // two accumulators, even and odd k-steps: the dependent MMA chain is half as long
     float c[4] = {0.0f, 0.0f, 0.0f, 0.0f}, c2[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    float sc[2][2];                                  // [token row u][head e]
+    if (QK8) {
+        // FP8 product: the K bytes are the A operand as loaded (rows tokrow(0, g) and tokrow(1, g); a lane's 16 bytes
+        // per row are two k-groups of 8), q is the B operand in two e4m3 parts (qa[w][0] high part, qa[w][1] low
+        // part of word w); `sl2` carries 1 / c
 #pragma unroll
-    for (int ch = 0; ch < C::kCh; ++ch) {
-        const uint32_t w0[4] = {f.k[0][ch].x, f.k[0][ch].y, f.k[0][ch].z, f.k[0][ch].w};
-        const uint32_t w1[4] = {f.k[1][ch].x, f.k[1][ch].y, f.k[1][ch].z, f.k[1][ch].w};
+        for (int ch = 0; ch < C::kCh; ++ch) {
+            const uint32_t w0[4] = {f.k[0][ch].x, f.k[0][ch].y, f.k[0][ch].z, f.k[0][ch].w};
+            const uint32_t w1[4] = {f.k[1][ch].x, f.k[1][ch].y, f.k[1][ch].z, f.k[1][ch].w};
 #pragma unroll
-        for (int s = 0; s < 4; ++s) {
-            uint32_t a0, a1, a2, a3;
-            e4m3x4_to_f16x2x2(w0[s], a0, a2);
-            e4m3x4_to_f16x2x2(w1[s], a1, a3);
-            if (s & 1) mma_full(c2, a0, a1, a2, a3, qa[4 * ch + s][0], qa[4 * ch + s][1]);
-            else mma_full(c, a0, a1, a2, a3, qa[4 * ch + s][0], qa[4 * ch + s][1]);
+            for (int m = 0; m < 2; ++m) {
+                mma_fp8(c, w0[2 * m], w1[2 * m], w0[2 * m + 1], w1[2 * m + 1], qa[4 * ch + 2 * m][0], qa[4 * ch + 2 * m + 1][0]);
+                mma_fp8(c2, w0[2 * m], w1[2 * m], w0[2 * m + 1], w1[2 * m + 1], qa[4 * ch + 2 * m][1], qa[4 * ch + 2 * m + 1][1]);
+            }
         }
+        constexpr float kLo = 1.0f / kQLoGain;
+        sc[0][0] = (c[0] + c2[0] * kLo) * sl2; sc[0][1] = (c[1] + c2[1] * kLo) * sl2;
+        sc[1][0] = (c[2] + c2[2] * kLo) * sl2; sc[1][1] = (c[3] + c2[3] * kLo) * sl2;
+    } else {
+        // f16 product: two accumulators, even and odd k-steps, so that the dependent MMA chain is half as long
+#pragma unroll
+        for (int ch = 0; ch < C::kCh; ++ch) {
+            const uint32_t w0[4] = {f.k[0][ch].x, f.k[0][ch].y, f.k[0][ch].z, f.k[0][ch].w};
+            const uint32_t w1[4] = {f.k[1][ch].x, f.k[1][ch].y, f.k[1][ch].z, f.k[1][ch].w};
+#pragma unroll
+            for (int s = 0; s < 4; ++s) {
+                uint32_t a0, a1, a2, a3;
+                e4m3x4_to_f16x2x2(w0[s], a0, a2);
+                e4m3x4_to_f16x2x2(w1[s], a1, a3);
+                if (s & 1) mma_full(c2, a0, a1, a2, a3, qa[4 * ch + s][0], qa[4 * ch + s][1]);
+                else mma_full(c, a0, a1, a2, a3, qa[4 * ch + s][0], qa[4 * ch + s][1]);
+            }
+        }
+        sc[0][0] = (c[0] + c2[0]) * sl2; sc[0][1] = (c[1] + c2[1]) * sl2;
+        sc[1][0] = (c[2] + c2[2]) * sl2; sc[1][1] = (c[3] + c2[3]) * sl2;
     }
-    float sc[2][2] = {{(c[0] + c2[0]) * sl2, (c[1] + c2[1]) * sl2}, {(c[2] + c2[2]) * sl2, (c[3] + c2[3]) * sl2}};   // [token row u][head e]
     if (rows < kPage) {
 #pragma unroll
         for (int u = 0; u < 2; ++u)
@@ -463,119 +544,6 @@ __device__ __forceinline__ void process_page(const PageFrags<D>& f, int rows, in
             e4m3x4_to_f16x2x2(__byte_perm(lo0[j >> 1], hi0[j >> 1], sel), a0, a1);
             e4m3x4_to_f16x2x2(__byte_perm(lo1[j >> 1], hi1[j >> 1], sel), a2, a3);
             mma_full(o[4 * ch + j], a0, a1, a2, a3, b0, b1);
-        }
-    }
-}
-
-// Two pages at once (the staged kernel, head_dim 64): the same arithmetic as two calls of process_page,
-// with the two pages' instruction streams interleaved by hand.  A page's work is one long dependent
-// chain (fragment loads -> FP8 converts -> score MMAs -> softmax -> transpose -> output MMAs); the MMAs and
-// transposes are volatile asm statements that the compiler keeps in program order, so two calls in a row
-// would run the chains back to back.  Interleaved, the score MMAs of the second page issue behind those
-// of the first, one vote decides about raising the running maximum for both pages, and the output MMAs of
-// the two pages alternate on the same accumulators.  Results are bit-identical to the one-page path only
-// when no page is processed alone in one path and in a pair in the other (the maximum may be raised at
-// different pages); the fused and the plain launch pair pages identically, so they stay bit-identical.
-template <int D, bool LIN>
-__device__ __forceinline__ void process_pair(const PageFrags<D>& fa, const PageFrags<D>& fb, int rows_a, int rows_b, int g, int t,
-                                             float sl2, const uint32_t (&qa)[FastCfg<D>::kKSteps][2], float (&m_run)[2],
-                                             float (&l_run)[2], float (&o)[FastCfg<D>::kNT / 2][4]) {
-    using C = FastCfg<D>;
-    float ca[4] = {0.0f, 0.0f, 0.0f, 0.0f}, ca2[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-    float cb[4] = {0.0f, 0.0f, 0.0f, 0.0f}, cb2[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-#pragma unroll
-    for (int ch = 0; ch < C::kCh; ++ch) {
-        const uint32_t a0w[4] = {fa.k[0][ch].x, fa.k[0][ch].y, fa.k[0][ch].z, fa.k[0][ch].w};
-        const uint32_t a1w[4] = {fa.k[1][ch].x, fa.k[1][ch].y, fa.k[1][ch].z, fa.k[1][ch].w};
-        const uint32_t b0w[4] = {fb.k[0][ch].x, fb.k[0][ch].y, fb.k[0][ch].z, fb.k[0][ch].w};
-        const uint32_t b1w[4] = {fb.k[1][ch].x, fb.k[1][ch].y, fb.k[1][ch].z, fb.k[1][ch].w};
-#pragma unroll
-        for (int s = 0; s < 4; ++s) {
-            uint32_t a0, a1, a2, a3, e0, e1, e2, e3;
-            e4m3x4_to_f16x2x2(a0w[s], a0, a2);
-            e4m3x4_to_f16x2x2(a1w[s], a1, a3);
-            e4m3x4_to_f16x2x2(b0w[s], e0, e2);
-            e4m3x4_to_f16x2x2(b1w[s], e1, e3);
-            if (s & 1) {
-                mma_full(ca2, a0, a1, a2, a3, qa[4 * ch + s][0], qa[4 * ch + s][1]);
-                mma_full(cb2, e0, e1, e2, e3, qa[4 * ch + s][0], qa[4 * ch + s][1]);
-            } else {
-                mma_full(ca, a0, a1, a2, a3, qa[4 * ch + s][0], qa[4 * ch + s][1]);
-                mma_full(cb, e0, e1, e2, e3, qa[4 * ch + s][0], qa[4 * ch + s][1]);
-            }
-        }
-    }
-    // scores [page][token row u][head e]
-    float sc[2][2][2] = {{{(ca[0] + ca2[0]) * sl2, (ca[1] + ca2[1]) * sl2}, {(ca[2] + ca2[2]) * sl2, (ca[3] + ca2[3]) * sl2}},
-                         {{(cb[0] + cb2[0]) * sl2, (cb[1] + cb2[1]) * sl2}, {(cb[2] + cb2[2]) * sl2, (cb[3] + cb2[3]) * sl2}}};
-    if (rows_a < kPage || rows_b < kPage) {
-#pragma unroll
-        for (int u = 0; u < 2; ++u) {
-            if (tokrow<LIN>(u, g) >= rows_a) { sc[0][u][0] = -INFINITY; sc[0][u][1] = -INFINITY; }
-            if (tokrow<LIN>(u, g) >= rows_b) { sc[1][u][0] = -INFINITY; sc[1][u][1] = -INFINITY; }
-        }
-    }
-    constexpr float kMaxSlack = 8.0f;
-    float mx[2] = {fmaxf(fmaxf(sc[0][0][0], sc[0][1][0]), fmaxf(sc[1][0][0], sc[1][1][0])),
-                   fmaxf(fmaxf(sc[0][0][1], sc[0][1][1]), fmaxf(sc[1][0][1], sc[1][1][1]))};
-    const bool raise = mx[0] > m_run[0] + kMaxSlack || mx[1] > m_run[1] + kMaxSlack || m_run[0] == -INFINITY || m_run[1] == -INFINITY;
-    if (__any_sync(0xffffffffu, raise)) {
-        float alpha[2];
-#pragma unroll
-        for (int e = 0; e < 2; ++e) {
-            float v = mx[e];
-            v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 4));
-            v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 8));
-            v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 16));
-            const float m_new = fmaxf(m_run[e], v);
-            alpha[e] = ex2(m_run[e] - m_new);
-            l_run[e] *= alpha[e];
-            m_run[e] = m_new;
-        }
-#pragma unroll
-        for (int j = 0; j < C::kNT / 2; ++j) { o[j][0] *= alpha[0]; o[j][1] *= alpha[1]; o[j][2] *= alpha[0]; o[j][3] *= alpha[1]; }
-    }
-    float pr[2][2][2];
-#pragma unroll
-    for (int pg = 0; pg < 2; ++pg)
-#pragma unroll
-        for (int e = 0; e < 2; ++e) {
-            pr[pg][0][e] = ex2(sc[pg][0][e] - m_run[e]);
-            pr[pg][1][e] = ex2(sc[pg][1][e] - m_run[e]);
-        }
-#pragma unroll
-    for (int e = 0; e < 2; ++e) l_run[e] += (pr[0][0][e] + pr[0][1][e]) + (pr[1][0][e] + pr[1][1][e]);
-    const uint32_t pa0 = movmatrix_trans(pack_f16x2(pr[0][0][0], pr[0][0][1]));
-    const uint32_t pb0 = movmatrix_trans(pack_f16x2(pr[1][0][0], pr[1][0][1]));
-    const uint32_t pa1 = movmatrix_trans(pack_f16x2(pr[0][1][0], pr[0][1][1]));
-    const uint32_t pb1 = movmatrix_trans(pack_f16x2(pr[1][1][0], pr[1][1][1]));
-#pragma unroll
-    for (int ch = 0; ch < C::kCh; ++ch) {
-        uint2 va[2][2] = {{fa.va[0][ch], fa.va[1][ch]}, {fb.va[0][ch], fb.va[1][ch]}};     // [page][u]
-        uint2 vb[2][2] = {{fa.vb[0][ch], fa.vb[1][ch]}, {fb.vb[0][ch], fb.vb[1][ch]}};
-        if (rows_a < kPage || rows_b < kPage) {                                             // stale bytes must not reach the MMA
-#pragma unroll
-            for (int u = 0; u < 2; ++u) {
-                if (tokrow<LIN>(u, 2 * t) >= rows_a) va[0][u] = make_uint2(0u, 0u);
-                if (tokrow<LIN>(u, 2 * t + 1) >= rows_a) vb[0][u] = make_uint2(0u, 0u);
-                if (tokrow<LIN>(u, 2 * t) >= rows_b) va[1][u] = make_uint2(0u, 0u);
-                if (tokrow<LIN>(u, 2 * t + 1) >= rows_b) vb[1][u] = make_uint2(0u, 0u);
-            }
-        }
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            const uint32_t sel = (j & 1) ? 0x7362u : 0x5140u;
-            uint32_t a0, a1, a2, a3, e0, e1, e2, e3;
-            const uint32_t la0 = (j >> 1) ? va[0][0].y : va[0][0].x, ha0 = (j >> 1) ? vb[0][0].y : vb[0][0].x;
-            const uint32_t la1 = (j >> 1) ? va[0][1].y : va[0][1].x, ha1 = (j >> 1) ? vb[0][1].y : vb[0][1].x;
-            const uint32_t lb0 = (j >> 1) ? va[1][0].y : va[1][0].x, hb0 = (j >> 1) ? vb[1][0].y : vb[1][0].x;
-            const uint32_t lb1 = (j >> 1) ? va[1][1].y : va[1][1].x, hb1 = (j >> 1) ? vb[1][1].y : vb[1][1].x;
-            e4m3x4_to_f16x2x2(__byte_perm(la0, ha0, sel), a0, a1);
-            e4m3x4_to_f16x2x2(__byte_perm(la1, ha1, sel), a2, a3);
-            e4m3x4_to_f16x2x2(__byte_perm(lb0, hb0, sel), e0, e1);
-            e4m3x4_to_f16x2x2(__byte_perm(lb1, hb1, sel), e2, e3);
-            mma_full(o[4 * ch + j], a0, a1, a2, a3, pa0, pa1);
-            mma_full(o[4 * ch + j], e0, e1, e2, e3, pb0, pb1);
         }
     }
 }
@@ -717,82 +685,6 @@ __device__ __forceinline__ void fold_and_write(const AttnParams& p, float* s_m, 
     }
 }
 
-constexpr int kDirectFoldLimit = 16;       // splits * group up to which the one-level merge is used
-
-// One-level merge for the staged kernel, used when splits * group <= 16 and there is one cluster per span:
-// every warp of every CTA of the cluster writes its partial (m, l, O) straight into the LEADER's shared
-// memory (distributed shared memory stores), one cluster barrier publishes them, and the leader folds the
-// splits * 8 partials and writes the output.  Compared with fold_and_write this drops the CTA-local
-// staging pass and its barrier from the critical path of the launch.  Slot layout in the leader, reusing
-// the s_m / s_l / s_o area:  [splits * 8 warps][group][D + 4] floats (O in 0..D-1, m at D, l at D + 1).
-__device__ __forceinline__ void st_cluster_v4(uint32_t addr, float4 v) {
-    asm volatile("st.shared::cluster.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w) : "memory");
-}
-__device__ __forceinline__ void st_cluster_v2(uint32_t addr, float2 v) {
-    asm volatile("st.shared::cluster.v2.f32 [%0], {%1, %2};" ::"r"(addr), "f"(v.x), "f"(v.y) : "memory");
-}
-
-template <int D>
-__device__ __forceinline__ void fold_direct(const AttnParams& p, float* s_slots, int tid, int warp, int g, int t, int b, int h,
-                                            int rank, float (&m_run)[2], float (&l_run)[2], float (&o)[FastCfg<D>::kNT / 2][4]) {
-    using C = FastCfg<D>;
-    constexpr int kRow = D + 4;
-    const int S = p.splits, G = p.group;
-    if (S > 1) cluster_wait_acquire();          // phase 1 complete: the leader's shared memory exists
-    const uint32_t base = S > 1 ? map_to_rank(s_slots, 0) : smem_u32(s_slots);
-#pragma unroll
-    for (int e = 0; e < 2; ++e) {
-        float l = l_run[e];
-        l += __shfl_xor_sync(0xffffffffu, l, 4);
-        l += __shfl_xor_sync(0xffffffffu, l, 8);
-        l += __shfl_xor_sync(0xffffffffu, l, 16);
-        const int hh = 2 * t + e;
-        if (hh < G) {
-            const uint32_t row = base + (uint32_t)((((rank * kConsumerWarps + warp) * G + hh) * kRow) * 4);
-#pragma unroll
-            for (int ch = 0; ch < C::kCh; ++ch) {
-                const uint32_t dst = row + (uint32_t)((64 * ch + 8 * g) * 4);
-                const float4 lo = make_float4(o[4 * ch + 0][e], o[4 * ch + 0][2 + e], o[4 * ch + 1][e], o[4 * ch + 1][2 + e]);
-                const float4 hi = make_float4(o[4 * ch + 2][e], o[4 * ch + 2][2 + e], o[4 * ch + 3][e], o[4 * ch + 3][2 + e]);
-                if (S > 1) { st_cluster_v4(dst, lo); st_cluster_v4(dst + 16, hi); }
-                else { *(float4*)(s_slots + (dst - base) / 4) = lo; *(float4*)(s_slots + (dst - base) / 4 + 4) = hi; }
-            }
-            if (g == 0) {
-                if (S > 1) st_cluster_v2(row + (uint32_t)(D * 4), make_float2(m_run[e], l));
-                else *(float2*)(s_slots + (row - base) / 4 + D) = make_float2(m_run[e], l);
-            }
-        }
-    }
-    FDMS_PROBE(kProbeCtaFolded);
-    if (S > 1) {
-        cluster_arrive_release();               // phase 2: every warp's partial is in the leader's shared memory
-        cluster_wait_acquire();
-        if (rank != 0) return;
-    } else {
-        consumer_bar();
-    }
-    const float vs = p.v_scale ? p.v_scale[h] : 1.0f;
-    const int slots = S * kConsumerWarps;
-    for (int e = tid; e < G * D; e += kConsumerThreads) {
-        const int gg = e / D, d = e - gg * D;
-        const float* col = s_slots + (size_t)gg * kRow;
-        float M = -INFINITY;
-        for (int w = 0; w < slots; ++w) M = fmaxf(M, col[(size_t)w * G * kRow + D]);
-        float acc = 0.0f, Lsum = 0.0f;
-        if (M != -INFINITY) {
-            for (int w = 0; w < slots; ++w) {
-                const float* r = col + (size_t)w * G * kRow;
-                const float f = ex2(r[D] - M);
-                acc += f * r[d];
-                Lsum += f * r[D + 1];
-            }
-        }
-        store_from_float(p.out, (int64_t)b * p.out_sb + (int64_t)(h * G + gg) * p.out_sh + d, p.out_dtype,
-                         Lsum > 0.0f ? acc / Lsum * vs : 0.0f);
-    }
-    FDMS_PROBE(kProbeEnd);
-}
-
 // ------------------------------------------------------------------------------------------------
 // Staged variant of the fast kernel.  Every warp owns a ring of R page slots in shared memory (a slot
 // holds the K page and the V page of one 16-row page) and one mbarrier per slot.  Lane s of the warp
@@ -811,7 +703,7 @@ __device__ __forceinline__ void fold_direct(const AttnParams& p, float* s_slots,
 constexpr int kMaxRing = 8;
 
 template <int D, bool APPEND>
-__global__ void __launch_bounds__(kConsumerThreads, (D == 64 ? 2 : 1)) attn_decode_staged_kernel(AttnParams p) {
+__global__ void __launch_bounds__(kConsumerThreads, (D == 64 ? 3 : 1)) attn_decode_staged_kernel(AttnParams p) {
     using C = FastCfg<D>;
     constexpr int half = D / 2;
     extern __shared__ __align__(128) uint8_t smem[];
@@ -868,19 +760,24 @@ __global__ void __launch_bounds__(kConsumerThreads, (D == 64 ? 2 : 1)) attn_deco
     const bool tail_cta = APPEND && live > 0 && (tail_pi % nparts) == part;
     const int n_items = APPEND ? G * half + (tail_cta ? kItemsK + kItemsV : 0) : 0;
     const float* cs_row = APPEND ? p.rope_cs + checked_rope_position(p, b) * p.rope_stride : nullptr;
-    // the cos/sin pair of this thread's first rotation item does not depend on the preceding kernel
+    // The cos/sin pair of this thread's first rotation item does not depend on the preceding kernel; the
+    // activation it will rotate does, so only its cache line is requested into L2 here (a hint: the value
+    // itself is read after the dependency has been resolved).
     float pre_c = 1.0f, pre_s = 0.0f;
     if (APPEND && tid < n_items && tid < G * half + kItemsK) {
-        const int i = tid < G * half ? tid % half : tid - G * half;
+        const bool isq = tid < G * half;
+        const int gg = isq ? tid / half : 0, i = isq ? tid - gg * half : tid - G * half;
         pre_c = cs_row[i];
         pre_s = cs_row[half + i];
+        const int64_t row = isq ? (int64_t)b * p.q_sb + (int64_t)(h * G + gg) * p.q_sh : (int64_t)b * p.kn_sb + (int64_t)h * p.kn_sh;
+        const char* src = (const char*)(isq ? p.q : p.k_new) + (row + i) * dtype_size(p.q_dtype);
+        asm volatile("prefetch.global.L2 [%0];" ::"l"(src));
     }
 
     // Issues warp-local page i into slot i % R (called by the slot's lane only).  Returns false when
     // the page address is out of range: the slot's barrier is completed without a copy and the page is
     // skipped by the consumer.
-    auto issue = [&](int i, int32_t id) -> bool {
-        const int s = i % R;
+    auto issue = [&](int i, int s, int32_t id) -> bool {
         const int pi = pg0 + i * stride_pg;
         const int rows = min(kPage, live - pi * kPage);
         // in append mode the span's last row is not in the pool yet: it is patched into the slot
@@ -912,7 +809,7 @@ __global__ void __launch_bounds__(kConsumerThreads, (D == 64 ? 2 : 1)) attn_deco
     const bool my_first = lane < R && lane < nw;
     const bool deferred = !APPEND && my_first && pg0 + lane * stride_pg == tail_pi;
     if (my_first && !deferred) {
-        my_ok = issue(lane, my_id);
+        my_ok = issue(lane, lane, my_id);
         next_id(lane + R);
     }
     int64_t tail_row = -1;                           // pool row of the new token (block tables are older state)
@@ -926,7 +823,7 @@ __global__ void __launch_bounds__(kConsumerThreads, (D == 64 ? 2 : 1)) attn_deco
     grid_dependency_wait();
     FDMS_PROBE(kProbeDependency);
     if (deferred) {
-        my_ok = issue(lane, my_id);
+        my_ok = issue(lane, lane, my_id);
         next_id(lane + R);
     }
 
@@ -1000,70 +897,51 @@ __global__ void __launch_bounds__(kConsumerThreads, (D == 64 ? 2 : 1)) attn_deco
 #pragma unroll
     for (int j = 0; j < C::kNT / 2; ++j) { o[j][0] = 0.0f; o[j][1] = 0.0f; o[j][2] = 0.0f; o[j][3] = 0.0f; }
 
-    int issued = min(nw, R);                     // warp-local pages whose slot has been armed
-    constexpr bool kPairs = D == 64;             // two pages per round (process_pair); 128-wide heads have no registers for it
-    int s = 0;
-    uint32_t phase = 0;
-    for (int i = 0; i < nw;) {
-        const bool pair = kPairs && R >= 2 && i + 1 < nw;
-        int s2 = s + 1;
-        uint32_t phase2 = phase;
-        if (s2 == R) { s2 = 0; phase2 ^= 1u; }
-        bool landed = mbar_wait(&bars[s], phase, kWaitLimit);
-        if (pair) landed = mbar_wait(&bars[s2], phase2, kWaitLimit) && landed;
-        if (!__all_sync(0xffffffffu, landed)) {
-            if (lane == 0 && p.dev_status) atomicOr(p.dev_status, FDMS_DEV_WAIT_TIMEOUT);
-            for (int j = i; j < issued; ++j) mbar_wait(&bars[j % R], (uint32_t)(j / R) & 1u, kWaitLimitDrain);
-            break;
-        }
-        const int pi = pg0 + i * stride_pg, pi2 = pi + stride_pg;
-        const int rows = min(kPage, live - pi * kPage);
-        const int rows2 = pair ? min(kPage, live - pi2 * kPage) : 0;
-        const bool good = __shfl_sync(0xffffffffu, my_ok, s);
-        const bool good2 = pair && __shfl_sync(0xffffffffu, my_ok, s2);
-        uint8_t* Ks = ring + (size_t)s * C::kStageBytes;
-        uint8_t* Ks2 = ring + (size_t)s2 * C::kStageBytes;
-        if (APPEND && (pi == tail_pi || (pair && pi2 == tail_pi))) {
-            // the new row of the span is not in the pool image the copy brought: write it into the slot
-            uint8_t* Kt = pi == tail_pi ? Ks : Ks2;
-            if (lane < D / 16) *(uint4*)(Kt + r_new * D + 16 * lane) = *(const uint4*)(s_new + 16 * lane);
-            else if (lane < D / 8) *(uint4*)(Kt + C::kPageBytes + r_new * D + 16 * (lane - D / 16)) = *(const uint4*)(s_new + D + 16 * (lane - D / 16));
-            __syncwarp();
-        }
-        if (kPairs && pair && good && good2) {
-            PageFrags<D> fa, fb;
-            load_frags_smem<D>(Ks, Ks + C::kPageBytes, g, t, fa);
-            load_frags_smem<D>(Ks2, Ks2 + C::kPageBytes, g, t, fb);
-            process_pair<D, false>(fa, fb, rows, rows2, g, t, sl2, qa, m_run, l_run, o);
-        } else {
+    // The page loop, once per form of the score product; a warp with many pages quantises q and takes the FP8 form.
+    auto page_loop = [&](auto qk8_tag, float sl2w) {
+        constexpr bool QK8 = decltype(qk8_tag)::value;
+        int issued = min(nw, R);                 // warp-local pages whose slot has been armed
+        int s = 0;
+        uint32_t phase = 0;
+        for (int i = 0; i < nw; ++i) {
+            const bool landed = mbar_wait(&bars[s], phase, kWaitLimit);
+            if (!__all_sync(0xffffffffu, landed)) {
+                if (lane == 0 && p.dev_status) atomicOr(p.dev_status, FDMS_DEV_WAIT_TIMEOUT);
+                for (int j = i; j < issued; ++j) mbar_wait(&bars[j % R], (uint32_t)(j / R) & 1u, kWaitLimitDrain);
+                break;
+            }
+            const int pi = pg0 + i * stride_pg;
+            const int rows = min(kPage, live - pi * kPage);
+            const bool good = __shfl_sync(0xffffffffu, my_ok, s);
+            uint8_t* Ks = ring + (size_t)s * C::kStageBytes;
+            if (APPEND && pi == tail_pi) {
+                // the new row of the span is not in the pool image the copy brought: write it into the slot
+                if (lane < D / 16) *(uint4*)(Ks + r_new * D + 16 * lane) = *(const uint4*)(s_new + 16 * lane);
+                else if (lane < D / 8) *(uint4*)(Ks + C::kPageBytes + r_new * D + 16 * (lane - D / 16)) = *(const uint4*)(s_new + D + 16 * (lane - D / 16));
+                __syncwarp();
+            }
             if (good) {
                 PageFrags<D> f;
                 load_frags_smem<D>(Ks, Ks + C::kPageBytes, g, t, f);
-                process_page<D, false>(f, rows, g, t, sl2, qa, m_run, l_run, o);
+                process_page<D, false, QK8>(f, rows, g, t, sl2w, qa, m_run, l_run, o);
             }
-            if (good2) {
-                PageFrags<D> f;
-                load_frags_smem<D>(Ks2, Ks2 + C::kPageBytes, g, t, f);
-                process_page<D, false>(f, rows2, g, t, sl2, qa, m_run, l_run, o);
+            __syncwarp();                         // every lane has consumed its fragments of the slot
+            if (i + R < nw) {
+                if (lane == s) { my_ok = issue(i + R, s, my_id); next_id(i + 2 * R); }
+                ++issued;
             }
+            if (++s == R) { s = 0; phase ^= 1u; }
         }
-        __syncwarp();                             // every lane has consumed its fragments of the slot(s)
-        if (i + R < nw) {
-            if (lane == s) { my_ok = issue(i + R, my_id); next_id(i + 2 * R); }
-            ++issued;
-        }
-        if (pair && i + 1 + R < nw) {
-            if (lane == s2) { my_ok = issue(i + 1 + R, my_id); next_id(i + 1 + 2 * R); }
-            ++issued;
-        }
-        if (pair) { i += 2; s = s2; phase = phase2; } else { i += 1; }
-        if (++s == R) { s = 0; phase ^= 1u; }
+    };
+    if (nw >= kQk8MinPages) {
+        float inv_c;
+        quantize_q<D>(qa, inv_c);
+        page_loop(std::true_type{}, sl2 * inv_c);
+    } else {
+        page_loop(std::false_type{}, sl2);
     }
     __syncthreads();                              // s_last initialised, all warps done with their pages
     FDMS_PROBE(kProbePagesDone);
-    if (CH == 1 && S * G <= kDirectFoldLimit)
-        fold_direct<D>(p, s_m, tid, warp, g, t, b, h, rank, m_run, l_run, o);
-    else
     fold_and_write<D>(p, s_m, s_l, s_o, r_ml, r_o, &s_last, tid, warp, g, t, b, h, item, rank, chunk, m_run, l_run, o);
 }
 
@@ -1138,6 +1016,19 @@ __global__ void __launch_bounds__(kDirectThreads, (D == 64 ? 2 : 1)) attn_decode
     const bool tail_cta = APPEND && live > 0 && (tail_pi % nparts) == part;
     const int n_items = APPEND ? G * half + (tail_cta ? kItemsK + kItemsV : 0) : 0;
     const float* cs_row = APPEND ? p.rope_cs + checked_rope_position(p, b) * p.rope_stride : nullptr;
+    // The cos/sin pair of this thread's first rotation item does not depend on the preceding kernel; the
+    // activation it will rotate does, so only its cache line is requested into L2 here (a hint: the value
+    // itself is read after the dependency has been resolved).
+    float pre_c = 1.0f, pre_s = 0.0f;
+    if (APPEND && tid < n_items && tid < G * half + kItemsK) {
+        const bool isq = tid < G * half;
+        const int gg = isq ? tid / half : 0, i = isq ? tid - gg * half : tid - G * half;
+        pre_c = cs_row[i];
+        pre_s = cs_row[half + i];
+        const int64_t row = isq ? (int64_t)b * p.q_sb + (int64_t)(h * G + gg) * p.q_sh : (int64_t)b * p.kn_sb + (int64_t)h * p.kn_sh;
+        const char* src = (const char*)(isq ? p.q : p.k_new) + (row + i) * dtype_size(p.q_dtype);
+        asm volatile("prefetch.global.L2 [%0];" ::"l"(src));
+    }
 
     const LaneOffsets<D, true> lofs(g, t);
     PageFrags<D> buf[DEPTH];
@@ -1195,7 +1086,7 @@ __global__ void __launch_bounds__(kDirectThreads, (D == 64 ? 2 : 1)) attn_decode
                                         : (int64_t)b * p.kn_sb + (int64_t)h * p.kn_sh;
                 const float x1 = load_as_float(src, row + i, p.q_dtype);
                 float x2 = load_as_float(src, row + half + i, p.q_dtype);
-                const float c = cs_row[i], sn = cs_row[half + i];
+                const float c = it == tid ? pre_c : cs_row[i], sn = it == tid ? pre_s : cs_row[half + i];
                 if (isq && gg == 0 && i == half - 1) {
                     // the group's first q head carries the DMS decision in its last channel
                     if (tail_cta && p.evict_out) p.evict_out[(int64_t)b * p.evict_sb + h] = p.rule.evict(x2) ? 1 : 0;
@@ -1255,26 +1146,37 @@ __global__ void __launch_bounds__(kDirectThreads, (D == 64 ? 2 : 1)) attn_decode
 #pragma unroll
     for (int j = 0; j < C::kNT / 2; ++j) { o[j][0] = 0.0f; o[j][1] = 0.0f; o[j][2] = 0.0f; o[j][3] = 0.0f; }
 
-    for (int i0 = 0; i0 < nw; i0 += DEPTH) {
+    // The page loop, once per form of the score product; a warp with many pages quantises q and takes the FP8 form.
+    auto page_loop = [&](auto qk8_tag, float sl2w) {
+        constexpr bool QK8 = decltype(qk8_tag)::value;
+        for (int i0 = 0; i0 < nw; i0 += DEPTH) {
 #pragma unroll
-        for (int s = 0; s < DEPTH; ++s) {
-            const int i = i0 + s;
-            if (i < nw) {
-                if (APPEND && own_tail && pg0 + i * stride_pg == tail_pi) {
+            for (int s = 0; s < DEPTH; ++s) {
+                const int i = i0 + s;
+                if (i < nw) {
+                    if (APPEND && own_tail && pg0 + i * stride_pg == tail_pi) {
 #pragma unroll
-                    for (int u = 0; u < 2; ++u) {
+                        for (int u = 0; u < 2; ++u) {
 #pragma unroll
-                        for (int ch = 0; ch < C::kCh; ++ch) {
-                            if (tokrow<true>(u, g) == r_new) buf[s].k[u][ch] = *(const uint4*)(s_new + 64 * ch + 16 * t);
-                            if (tokrow<true>(u, 2 * t) == r_new) buf[s].va[u][ch] = *(const uint2*)(s_new + D + 64 * ch + 8 * g);
-                            if (tokrow<true>(u, 2 * t + 1) == r_new) buf[s].vb[u][ch] = *(const uint2*)(s_new + D + 64 * ch + 8 * g);
+                            for (int ch = 0; ch < C::kCh; ++ch) {
+                                if (tokrow<true>(u, g) == r_new) buf[s].k[u][ch] = *(const uint4*)(s_new + 64 * ch + 16 * t);
+                                if (tokrow<true>(u, 2 * t) == r_new) buf[s].va[u][ch] = *(const uint2*)(s_new + D + 64 * ch + 8 * g);
+                                if (tokrow<true>(u, 2 * t + 1) == r_new) buf[s].vb[u][ch] = *(const uint2*)(s_new + D + 64 * ch + 8 * g);
+                            }
                         }
                     }
+                    if (brow[s] > 0) process_page<D, true, QK8>(buf[s], brow[s], g, t, sl2w, qa, m_run, l_run, o);
+                    if (i + DEPTH < nw) issue(s, i + DEPTH);
                 }
-                if (brow[s] > 0) process_page<D, true>(buf[s], brow[s], g, t, sl2, qa, m_run, l_run, o);
-                if (i + DEPTH < nw) issue(s, i + DEPTH);
             }
         }
+    };
+    if (nw >= kQk8MinPages) {
+        float inv_c;
+        quantize_q<D>(qa, inv_c);
+        page_loop(std::true_type{}, sl2 * inv_c);
+    } else {
+        page_loop(std::false_type{}, sl2);
     }
     __syncthreads();                              // s_last initialised, all warps done with their pages
     FDMS_PROBE(kProbePagesDone);
@@ -1389,12 +1291,7 @@ static int env_int(const char* name, int dflt) {
 static size_t staged_smem_bytes(int D, int ring, int splits, int group) {
     size_t s = (size_t)kConsumerWarps * ring * 2 * kPage * D;       // per-warp rings
     s += (size_t)kConsumerWarps * kMaxRing * sizeof(uint64_t);     // barriers
-    size_t fold = (size_t)kConsumerWarps * kMaxGroup * (2 + D + 4) * sizeof(float);      // two-level merge: CTA-local partials
-    if (splits * group <= kDirectFoldLimit) {                      // one-level merge: every warp of the cluster has a slot
-        const size_t slots = (size_t)splits * kConsumerWarps * group * (D + 4) * sizeof(float);
-        if (slots > fold) fold = slots;
-    }
-    s += fold;
+    s += (size_t)kConsumerWarps * kMaxGroup * (2 + D + 4) * sizeof(float);
     s += (size_t)splits * group * (2 + D) * sizeof(float);
     return s + 128;
 }
@@ -1585,16 +1482,16 @@ static int32_t attn_decode_common(
         // brings them into per-warp shared-memory rings with bulk copies.
         const char* loader = getenv("FDMS_ATTN_LOADER");
         const bool direct = !(loader && loader[0] == 's');
-        const int ctas_per_sm = head_dim == 64 ? 2 : 1;
+        const int ctas_per_sm = head_dim == 64 ? (direct ? 2 : 3) : 1;
         // The staged kernel aims at ONE CTA per SM and at most half of an SM's shared memory per CTA
         // (head_dim 64), so that the next launch of the stream is resident beside this one and its
         // copies run under this launch's math; FDMS_ATTN_WAVE=2 fills both CTA slots with one launch.
         int wave = env_int("FDMS_ATTN_WAVE", 0);
-        if (wave < 1) wave = direct ? ctas_per_sm : 1;
+        if (wave < 1) wave = ctas_per_sm;
         if (wave > ctas_per_sm) wave = ctas_per_sm;
         const int target = di.sms * wave;
         int ring = env_int("FDMS_ATTN_RING", 0);
-        if (ring < 1) ring = 5;
+        if (ring < 1) ring = 3;
         if (ring > kMaxRing) ring = kMaxRing;
         const int variant = (app ? 2 : 0) + (head_dim == 64 ? 0 : 1) + (direct ? 0 : 4);
         AttnKernel kern;
