@@ -41,6 +41,11 @@ def run(args) -> dict:
         raise SystemExit(f"--tp must be 1 (replicas) or the number of ranks ({world})")
 
     hf = dict(SHAPES[args.shape])
+    if args.shard > 1:
+        # one rank's slice of an N-way tensor-parallel model on one GPU, collectives left out: the kernels one
+        # rank launches per step, for a launch list of the tensor-parallel step
+        for key in ("num_attention_heads", "num_key_value_heads", "intermediate_size", "vocab_size"):
+            hf[key] = hf[key] // args.shard
     hf.update(attention_bias=True, torch_dtype="bfloat16",
               max_position_embeddings=args.prompt_len + args.decode_steps + 8)
     c = args.concurrency
@@ -103,7 +108,7 @@ def run(args) -> dict:
     t_prefill, t_decode = (float(x) for x in t.tolist())
     ctx_end = args.prompt_len + args.decode_steps
     return {
-        "shape": args.shape, "n_gpus": world, "parallelism": f"tp{args.tp}" if args.tp > 1 else f"replicas x{world}",
+        "shape": args.shape + (f" (slice 1/{args.shard})" if args.shard > 1 else ""), "n_gpus": world, "parallelism": f"tp{args.tp}" if args.tp > 1 else f"replicas x{world}",
         "concurrency_per_replica": c, "prompt_len": args.prompt_len, "decode_steps_timed": steps,
         "decode_tok_s": replicas * c * steps / t_decode, "decode_ms_per_step": t_decode / steps * 1e3,
         "prefill_tok_s": replicas * c * args.prompt_len / t_prefill, "prefill_s": t_prefill, "prefill_steps": prefill_steps,
@@ -122,6 +127,7 @@ def main() -> None:
     ap.add_argument("--prompt-len", type=int, default=8192)
     ap.add_argument("--decode-steps", type=int, default=128)
     ap.add_argument("--tp", type=int, default=1)
+    ap.add_argument("--shard", type=int, default=1, help="run one rank's slice of an N-way tensor-parallel model (no collectives)")
     ap.add_argument("--window", type=int, default=256)
     ap.add_argument("--expiry-interval", type=int, default=1)
     ap.add_argument("--paged", action="store_true")

@@ -10,16 +10,21 @@
 //     wave of 2 CTAs per SM.  Very long spans at tiny batch use several clusters per span
 //     (`chunks` > 1); only then do cluster leaders meet in the global workspace, where the last one
 //     to arrive at a per-span counter folds the chunk partials (threadfence + atomic, no spinning).
-//   * A producer warp resolves each page's address (span base or block table) and stages K and V
-//     pages into a shared-memory ring with bulk asynchronous copies (cp.async.bulk, the TMA unit's
-//     untiled form) that complete on per-stage mbarriers.  A CTA's whole range is normally in
-//     flight at once: one layer's working set is only a few times the bandwidth-delay product of
-//     HBM, so latency is hidden by issuing everything up front, not by occupancy.
-//   * Eight consumer warps each own every 8th page.  Per page a warp computes the GQA-packed
-//     S = q K^T and O += P V tiles with mma.sync.m16n8k16 (f16 operands, f32 accumulate): q heads
-//     sit on the M axis, FP8 K/V bytes are converted exactly to f16 in registers, the softmax is
-//     the online form with warp-shuffle row reductions in the log2 domain.
-// Every wait on an mbarrier is bounded; on expiry the kernel raises FDMS_DEV_WAIT_TIMEOUT in the
+//   * Eight warps per CTA each own every 8th 16-row page of the CTA's range and there is no barrier in the
+//     page loop.  Two kernels share the page math and differ in how a page reaches the warp:
+//       - direct (default): every lane loads its K and V MMA fragments straight from the pool (16 bytes of K
+//         and two 8-byte V pieces per lane and page), `DEPTH` pages ahead in registers;
+//       - staged (FDMS_ATTN_LOADER=staged): lane s of a warp issues two 1 KiB bulk asynchronous copies
+//         (cp.async.bulk, the TMA unit's untiled form) into slot s of the warp's own shared-memory ring;
+//         they complete on a per-slot mbarrier and the warp reads its fragments from shared memory.
+//   * Per page a warp computes the GQA-packed S = q K^T and O += P V tiles with tensor-core MMAs (q heads on
+//     the M axis, f32 accumulate).  Warps with few pages convert the FP8 K bytes exactly to f16
+//     (mma.sync.m16n8k16); warps with `kQk8MinPages` or more use the K bytes as an e4m3 operand as they are
+//     (mma.sync.m16n8k32) against q split into an e4m3 value and an amplified e4m3 residual.  V is always
+//     converted to f16.  The softmax is the online form with warp-shuffle row reductions in the log2 domain.
+//   * With FDMS_ATTN_OVERLAP_PREVIOUS everything that does not depend on the preceding kernel (metadata, block
+//     tables, cos/sin, the first pages) is issued before `griddepcontrol.wait`.
+// Every wait on an mbarrier is bounded; on expiry the staged kernel raises FDMS_DEV_WAIT_TIMEOUT in the
 // status word, stops issuing copies, drains with short waits and still takes part in every
 // cluster barrier before it returns.
 //

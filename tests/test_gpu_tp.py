@@ -226,79 +226,86 @@ def _fused_linear_rank(rank: int, world: int, out_q) -> None:
     dist.init_process_group("nccl", device_id=dev)
     ok, detail = True, ""
     try:
-        fused = init_fused_row_parallel(dev)
-        assert fused is not None
-        g = torch.Generator(device=dev).manual_seed(500 + rank)
-        # (rows, out_features, this rank's share of in_features): o_proj / down_proj shards of the 8B shape at 2, 4, 8 ranks
-        shapes = [(8, 4096, 2048), (8, 4096, 6144), (8, 4096, 1024), (3, 4096, 1536), (8, 4096, 512), (1, 2048, 256)]
-        weights = {s: (torch.randn((s[1], s[2]), device=dev, generator=g) * (world * s[2]) ** -0.5).to(torch.bfloat16) for s in shapes}
-        bias = {s: torch.randn((s[1],), device=dev, generator=torch.Generator(device=dev).manual_seed(9)).to(torch.bfloat16) for s in shapes}
-        calls = 0
-        for it in range(40):
-            for s in shapes:
-                rows, n, k = s
-                x = torch.randn((rows, k), device=dev, generator=g).to(torch.bfloat16)
-                b = bias[s] if (it + calls) % 2 else None
-                assert fused.fits(x, weights[s], b)
-                y = fused.linear_all_reduce(x, weights[s], b)
-                calls += 1
-                # float32 reference: every rank's partial, summed in rank order
-                part = x.float() @ weights[s].float().t()
-                parts = [torch.empty_like(part) for _ in range(world)]
-                dist.all_gather(parts, part)
-                ref = parts[0]
-                for p in parts[1:]:
-                    ref = ref + p
-                if b is not None:
-                    ref = ref + b.float()
-                ys = [torch.empty_like(y) for _ in range(world)]
-                dist.all_gather(ys, y)
-                if not all(torch.equal(ys[0], o) for o in ys[1:]):
-                    ok, detail = False, f"ranks disagree at call {calls} {s}"
-                err = float((y.float() - ref).abs().max())
-                if not err <= 2.0 ** -7 * float(ref.abs().max()):
-                    ok, detail = False, f"error {err} at call {calls} {s}"
-        # 300 calls without host synchronisation, then a replayed CUDA graph of a two-layer chain
-        s = shapes[0]
-        x = torch.randn((8, s[2]), device=dev, generator=g).to(torch.bfloat16)
-        want = fused.linear_all_reduce(x, weights[s], None).clone()
-        outs = [fused.linear_all_reduce(x, weights[s], None) for _ in range(300)]
-        torch.cuda.synchronize(dev)
-        ok = ok and all(torch.equal(o, want) for o in outs)
-        s2 = shapes[1]
-        x2 = torch.randn((8, s2[2]), device=dev, generator=g).to(torch.bfloat16)
-        want2 = fused.linear_all_reduce(x2, weights[s2], None).clone()
-        torch.cuda.synchronize(dev)
-        graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph):
-            o1 = fused.linear_all_reduce(x, weights[s], None)
-            o2 = fused.linear_all_reduce(x2, weights[s2], None)
-        for _ in range(50):
-            graph.replay()
-        torch.cuda.synchronize(dev)
-        ok = ok and torch.equal(o1, want) and torch.equal(o2, want2)
+      with torch.inference_mode():
+          fused = init_fused_row_parallel(dev)
+          assert fused is not None
+          g = torch.Generator(device=dev).manual_seed(500 + rank)
+          # (rows, out_features, this rank's share of in_features): o_proj / down_proj shards of the 8B shape at 2, 4, 8 ranks
+          shapes = [(8, 4096, 2048), (8, 4096, 6144), (8, 4096, 1024), (3, 4096, 1536), (8, 4096, 512), (1, 2048, 256)]
+          weights = {s: (torch.randn((s[1], s[2]), device=dev, generator=g) * (world * s[2]) ** -0.5).to(torch.bfloat16) for s in shapes}
+          bias = {s: torch.randn((s[1],), device=dev, generator=torch.Generator(device=dev).manual_seed(9)).to(torch.bfloat16) for s in shapes}
+          calls = 0
+          for it in range(40):
+              for s in shapes:
+                  rows, n, k = s
+                  x = torch.randn((rows, k), device=dev, generator=g).to(torch.bfloat16)
+                  b = bias[s] if (it + calls) % 2 else None
+                  assert fused.fits(x, weights[s], b)
+                  y = fused.linear_all_reduce(x, weights[s], b)
+                  calls += 1
+                  # float32 reference: every rank's partial, summed in rank order
+                  part = x.float() @ weights[s].float().t()
+                  parts = [torch.empty_like(part) for _ in range(world)]
+                  dist.all_gather(parts, part)
+                  ref = parts[0]
+                  for p in parts[1:]:
+                      ref = ref + p
+                  if b is not None:
+                      ref = ref + b.float()
+                  ys = [torch.empty_like(y) for _ in range(world)]
+                  dist.all_gather(ys, y)
+                  if not all(torch.equal(ys[0], o) for o in ys[1:]):
+                      ok, detail = False, f"ranks disagree at call {calls} {s}"
+                  err = float((y.float() - ref).abs().max())
+                  if not err <= 2.0 ** -7 * float(ref.abs().max()):
+                      ok, detail = False, f"error {err} at call {calls} {s}"
+          # 300 calls without host synchronisation, then a replayed CUDA graph of a two-layer chain
+          s = shapes[0]
+          x = torch.randn((8, s[2]), device=dev, generator=g).to(torch.bfloat16)
+          want = fused.linear_all_reduce(x, weights[s], None).clone()
+          outs = [fused.linear_all_reduce(x, weights[s], None) for _ in range(300)]
+          torch.cuda.synchronize(dev)
+          ok = ok and all(torch.equal(o, want) for o in outs)
+          s2 = shapes[1]
+          x2 = torch.randn((8, s2[2]), device=dev, generator=g).to(torch.bfloat16)
+          want2 = fused.linear_all_reduce(x2, weights[s2], None).clone()
+          torch.cuda.synchronize(dev)
+          graph = torch.cuda.CUDAGraph()
+          with torch.cuda.graph(graph):
+              o1 = fused.linear_all_reduce(x, weights[s], None)
+              o2 = fused.linear_all_reduce(x2, weights[s2], None)
+          for _ in range(50):
+              graph.replay()
+          torch.cuda.synchronize(dev)
+          ok = ok and torch.equal(o1, want) and torch.equal(o2, want2)
 
-        def timeit(fn, n=200):
-            for _ in range(20):
-                fn()
-            torch.cuda.synchronize(dev); dist.barrier()
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            e0.record()
-            for _ in range(n):
-                fn()
-            e1.record(); torch.cuda.synchronize(dev)
-            return e0.elapsed_time(e1) / n * 1e3
+          def timeit(fn, n=200):
+              for _ in range(20):
+                  fn()
+              torch.cuda.synchronize(dev); dist.barrier()
+              e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+              e0.record()
+              for _ in range(n):
+                  fn()
+              e1.record(); torch.cuda.synchronize(dev)
+              return e0.elapsed_time(e1) / n * 1e3
 
-        def two_step():
-            y = linear(x, weights[s])
-            dist.all_reduce(y)
-        t_fused = timeit(lambda: fused.linear_all_reduce(x, weights[s], None))
-        t_two = timeit(two_step)
-        status = _lib.read_device_status(dev)
-        out_q.put((rank, ok and status == 0, detail, t_fused, t_two))
+          def two_step():
+              y = linear(x, weights[s])
+              dist.all_reduce(y)
+          t_fused = timeit(lambda: fused.linear_all_reduce(x, weights[s], None))
+          t_two = timeit(two_step)
+          status = _lib.read_device_status(dev)
+          out_q.put((rank, ok and status == 0, detail, t_fused, t_two))
+          out_q.close(); out_q.join_thread()
+          torch.cuda.synchronize(dev)
+          dist.barrier()
+    except BaseException:
+        import traceback
+        traceback.print_exc()
+        out_q.put((rank, False, traceback.format_exc()[-400:], 0.0, 0.0))
         out_q.close(); out_q.join_thread()
-        torch.cuda.synchronize(dev)
-        dist.barrier()
+        raise
     finally:
         sys.stdout.flush(); sys.stderr.flush()
         os._exit(0 if sys.exc_info()[0] is None else 1)
