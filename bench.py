@@ -64,9 +64,9 @@ def measured_peaks() -> tuple[float, str]:
 # ------------------------------------------------------------------------------------------------
 # dram__bytes_read.sum + dram__bytes_write.sum of one fused attention launch of this (seeded, hence
 # reproducible) workload, from the ncu capture summarised under profiles/
-NCU_DRAM_BYTES_PER_LAUNCH = 10_747_648 + 0
+NCU_DRAM_BYTES_PER_LAUNCH = 10_688_512 + 0
 NCU_DRAM_SOURCE = ("ncu --set full capture of attn_decode_direct_kernel<64, 3, true> on this workload "
-                   "(profiles/attn_decode_direct_fused_config2.md): 10.75 MB read, ~0 written")
+                   "(profiles/attn_decode_direct_fused_config2.md): 10.69 MB read, 0 written")
 
 
 class ClockSampler:

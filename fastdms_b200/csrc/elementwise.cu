@@ -95,6 +95,42 @@ __global__ void __launch_bounds__(kNormThreads) rmsnorm_kernel(
     }
 }
 
+// Per-head RMSNorm of the q and k heads of a fused projection output, in place, one launch: a warp owns one
+// (row, head) of head_dim <= 256 elements (one 16-byte vector per lane).  Same arithmetic as rmsnorm_kernel.
+__global__ void __launch_bounds__(kNormThreads) qk_rmsnorm_kernel(
+    uint16_t* q, int64_t q_sb, int64_t q_sh, int q_heads, const uint16_t* q_weight,
+    uint16_t* k, int64_t k_sb, int64_t k_sh, int k_heads, const uint16_t* k_weight,
+    int dt, int64_t rows, int head_dim, float eps) {
+    pdl_trigger();
+    pdl_wait();
+    const int lane = threadIdx.x & 31;
+    const int heads = q_heads + k_heads;
+    const int64_t unit = (int64_t)blockIdx.x * (kNormThreads / 32) + (threadIdx.x >> 5);
+    if (unit >= rows * heads) return;
+    const int64_t row = unit / heads;
+    const int head = (int)(unit - row * heads);
+    const bool isq = head < q_heads;
+    uint16_t* x = isq ? q + row * q_sb + (int64_t)head * q_sh : k + row * k_sb + (int64_t)(head - q_heads) * k_sh;
+    const uint16_t* weight = isq ? q_weight : k_weight;
+    const bool have = lane < (head_dim >> 3);
+    float v[8], ss = 0.0f;
+    if (have) {
+        unpack8(*(const uint4*)(x + 8 * lane), dt, v);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) ss += v[i] * v[i];
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    const float inv = rsqrtf(ss / (float)head_dim + eps);
+    if (have) {
+        float w[8], y[8];
+        unpack8(*(const uint4*)(weight + 8 * lane), dt, w);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) y[i] = round_to_dtype(v[i] * inv, dt) * w[i];
+        *(uint4*)(x + 8 * lane) = pack8(y, dt);
+    }
+}
+
 // out[r, c] = round(round(silu(x[r, c])) * x[r, n + c]), 8 elements per thread.
 __global__ void silu_mul_kernel(const uint16_t* x, int64_t x_stride, uint16_t* out, int64_t out_stride, int dt,
                                 int64_t rows, int n) {
@@ -148,6 +184,31 @@ extern "C" int32_t fdms_rmsnorm(
         (const uint16_t*)x, x_row_stride, (const uint16_t*)residual, residual_row_stride, (const uint16_t*)weight,
         (uint16_t*)out, out_row_stride, (uint16_t*)residual_out, residual_out_row_stride, (int)dtype, rows, (int)hidden, eps, T));
     FDMS_CHECK_LAUNCH("rmsnorm_kernel");
+    return FDMS_OK;
+}
+
+extern "C" int32_t fdms_qk_rmsnorm(
+    void* q, int64_t q_stride_row, int64_t q_stride_head, int32_t q_heads, const void* q_weight,
+    void* k, int64_t k_stride_row, int64_t k_stride_head, int32_t k_heads, const void* k_weight,
+    int32_t dtype, int64_t rows, int32_t head_dim, float eps, void* stream) {
+    clear_error();
+    FDMS_REQUIRE(q && k && q_weight && k_weight, FDMS_E_ARG, "fdms_qk_rmsnorm: null pointer");
+    FDMS_REQUIRE(dtype == FDMS_BF16 || dtype == FDMS_F16, FDMS_E_DTYPE, "fdms_qk_rmsnorm: bf16 or f16 activations only");
+    FDMS_REQUIRE(rows >= 0 && q_heads > 0 && k_heads > 0 && head_dim > 0 && head_dim % 8 == 0 && head_dim <= 256, FDMS_E_ARG,
+                 "fdms_qk_rmsnorm: head_dim must be a multiple of 8 up to 256, got %d", head_dim);
+    FDMS_REQUIRE(aligned16(q, q_stride_row) && aligned16(q, q_stride_head) && aligned16(k, k_stride_row) &&
+                     aligned16(k, k_stride_head) && aligned16(q_weight, 0) && aligned16(k_weight, 0),
+                 FDMS_E_ARG, "fdms_qk_rmsnorm: pointers and strides must be 16-byte aligned");
+    if (rows == 0) return FDMS_OK;
+    const int64_t units = rows * (q_heads + k_heads);
+    const int64_t blocks = (units + kNormThreads / 32 - 1) / (kNormThreads / 32);
+    FDMS_REQUIRE(blocks < (1ll << 31), FDMS_E_CAPACITY, "fdms_qk_rmsnorm: too many rows");
+    FDMS_CUDA_OK(launch_chained(
+        qk_rmsnorm_kernel, dim3((unsigned)blocks), dim3(kNormThreads), (cudaStream_t)stream, chain_launches(),
+        (uint16_t*)q, q_stride_row, q_stride_head, (int)q_heads, (const uint16_t*)q_weight,
+        (uint16_t*)k, k_stride_row, k_stride_head, (int)k_heads, (const uint16_t*)k_weight,
+        (int)dtype, rows, (int)head_dim, eps));
+    FDMS_CHECK_LAUNCH("qk_rmsnorm_kernel");
     return FDMS_OK;
 }
 

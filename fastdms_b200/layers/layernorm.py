@@ -44,6 +44,29 @@ def rmsnorm_cuda(x: torch.Tensor, weight: torch.Tensor, eps: float, residual: to
     return out if residual is None else (out, res_out.view(x.shape))
 
 
+def qk_rmsnorm_(q: torch.Tensor, k: torch.Tensor, q_norm: "RMSNorm", k_norm: "RMSNorm") -> bool:
+    """Per-head RMSNorm of q [rows, heads, head_dim] and k [rows, kv_heads, head_dim] (views into the fused
+    projection output are fine) in ONE launch of `fdms_qk_rmsnorm`, in place.  Returns False, having done
+    nothing, when the tensors do not qualify (the caller then applies the two modules)."""
+    d = q.shape[-1]
+    ok = (q.is_cuda and q.dtype in (torch.bfloat16, torch.float16) and k.dtype == q.dtype and q.dim() == 3 and k.dim() == 3
+          and k.shape[-1] == d and k.shape[0] == q.shape[0] and d % 8 == 0 and d <= 256 and q.stride(2) == 1 and k.stride(2) == 1
+          and q_norm.weight.dtype == q.dtype and k_norm.weight.dtype == q.dtype and q_norm.eps == k_norm.eps
+          and q_norm.weight.is_contiguous() and k_norm.weight.is_contiguous() and q.numel() > 0
+          and not torch.is_grad_enabled()
+          and all(v % 16 == 0 for v in (q.data_ptr(), k.data_ptr(), q_norm.weight.data_ptr(), k_norm.weight.data_ptr(),
+                                        q.stride(0) * 2, q.stride(1) * 2, k.stride(0) * 2, k.stride(1) * 2)))
+    if not ok:
+        return False
+    with torch.cuda.device(q.device):
+        rc = _lib.lib().fdms_qk_rmsnorm(
+            q.data_ptr(), q.stride(0), q.stride(1), q.shape[1], q_norm.weight.data_ptr(),
+            k.data_ptr(), k.stride(0), k.stride(1), k.shape[1], k_norm.weight.data_ptr(),
+            _lib.dtype_code(q.dtype), q.shape[0], d, float(q_norm.eps), _lib.stream_ptr(q.device))
+    _lib.check(rc)
+    return True
+
+
 class RMSNorm(nn.Module):
     def __init__(self, hidden_size: int, eps: float = 1e-6) -> None:
         super().__init__()

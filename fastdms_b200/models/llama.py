@@ -20,7 +20,7 @@ from fastdms_b200.layers.compact_attention import (dms_decode_store_transient_k_
                                                    fused_dms_rope_store_compact_decode,
                                                    fused_store_attention_enabled)
 from fastdms_b200.layers.embed_head import ParallelLMHead, VocabParallelEmbedding
-from fastdms_b200.layers.layernorm import RMSNorm
+from fastdms_b200.layers.layernorm import RMSNorm, qk_rmsnorm_
 from fastdms_b200.layers.linear import (MergedColumnParallelLinear, QKVParallelLinear, RowParallelLinear,
                                         norm_linear, tp_world)
 from fastdms_b200.layers.rotary_embedding import get_rope
@@ -79,8 +79,9 @@ class LlamaAttention(nn.Module):
         k = k.view(-1, self.num_kv_heads, self.head_dim)
         v = v.view(-1, self.num_kv_heads, self.head_dim)
         if self.qk_norm:                      # Qwen3: per-head RMSNorm before the decision is read
-            q = self.q_norm(q)
-            k = self.k_norm(k)
+            if not qk_rmsnorm_(q, k, self.q_norm, self.k_norm):     # one launch, in place in the projection output
+                q = self.q_norm(q)
+                k = self.k_norm(k)
         context = get_context()
         prof = get_profiler()
         cache = self.rotary_emb.cos_sin_cache

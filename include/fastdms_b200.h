@@ -371,6 +371,15 @@ int32_t fdms_rmsnorm(
     int32_t dtype, int64_t rows, int32_t hidden, float eps, void* stream);
 int32_t fdms_silu_and_mul(const void* x, int64_t x_row_stride, void* out, int64_t out_row_stride,
                           int32_t dtype, int64_t rows, int32_t n, void* stream);
+/* Per-head RMSNorm of q and k before RoPE (the Qwen3 attention block: fastdms/models/qwen3.py applies
+ * RMSNorm(head_dim) to q.view(-1, heads, head_dim) and k.view(-1, kv_heads, head_dim), two calls of
+ * layernorm.py:16-25), both in ONE launch and in place: q [rows, q_heads, head_dim] and k [rows, k_heads, head_dim]
+ * with the given row and head strides in elements (views into the fused qkv projection output), inner stride 1.
+ * Same arithmetic as fdms_rmsnorm.  head_dim % 8 == 0, head_dim <= 256, 16-byte aligned pointers and strides. */
+int32_t fdms_qk_rmsnorm(
+    void* q, int64_t q_stride_row, int64_t q_stride_head, int32_t q_heads, const void* q_weight,
+    void* k, int64_t k_stride_row, int64_t k_stride_head, int32_t k_heads, const void* k_weight,
+    int32_t dtype, int64_t rows, int32_t head_dim, float eps, void* stream);
 
 /* Decode-sized linear layer: y[rows, out] = x[rows, in] * weight[out, in]^T (+ bias), rows <= 8, the
  * weight streamed once from HBM (the reference calls F.linear -> cuBLAS for qkv_proj, o_proj,

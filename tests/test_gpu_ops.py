@@ -452,6 +452,28 @@ def test_greedy_argmax_kernel_equals_torch_argmax(dev, dtype, rows, n):
     assert int(ws.count_nonzero()) == 0
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("rows,hq,hk,d", [(8, 32, 8, 128), (3, 16, 4, 128), (300, 8, 2, 64), (1, 4, 4, 256)])
+def test_qk_rmsnorm_equals_two_rmsnorm_calls(dev, dtype, rows, hq, hk, d):
+    """The one-launch per-head RMSNorm of q and k (in place in the fused projection output) gives the bits of
+    the two RMSNorm modules it replaces (reference: two calls of layers/layernorm.py:16-25 in the Qwen3 block)."""
+    from fastdms_b200.layers.layernorm import RMSNorm, qk_rmsnorm_
+    g = torch.Generator(device=dev).manual_seed(rows + hq + d)
+    qkv = torch.randn((rows, (hq + 2 * hk) * d), device=dev, generator=g).to(dtype)
+    qn, kn = RMSNorm(d, eps=1e-6).to(dev).to(dtype), RMSNorm(d, eps=1e-6).to(dev).to(dtype)
+    qn.weight.data.copy_((1.0 + 0.1 * torch.randn(d, device=dev, generator=g)).to(dtype))
+    kn.weight.data.copy_((1.0 + 0.1 * torch.randn(d, device=dev, generator=g)).to(dtype))
+    q, k, v = qkv.split([hq * d, hk * d, hk * d], dim=-1)
+    want_q = qn(q.reshape(rows, hq, d).contiguous())
+    want_k = kn(k.reshape(rows, hk, d).contiguous())
+    want_v = v.clone()
+    with torch.inference_mode():
+        assert qk_rmsnorm_(q.view(rows, hq, d), k.view(rows, hk, d), qn, kn)
+    assert torch.equal(q.reshape(rows, hq, d), want_q)
+    assert torch.equal(k.reshape(rows, hk, d), want_k)
+    assert torch.equal(v, want_v)                      # the neighbouring v columns are untouched
+
+
 def first_max(x):
     idx = torch.arange(x.shape[1], device=x.device).expand_as(x)
     return torch.where(x == x.max(dim=-1, keepdim=True).values, idx, x.shape[1]).min(dim=-1).values
