@@ -9,20 +9,21 @@
 // CTA.  Weight rows sit on the M side of mma.sync.m16n8k16, the <= 8 activation rows on N, exactly as in
 // the decode linear kernel; partial tiles of the warps are summed through shared memory in float32.
 //
-// Epilogue = the collective.  The CTA PUSHES its float32 partial tile into a slot of every rank's
-// peer-mapped region (plain stores over NVLink, one traversal), makes them visible
-// (__threadfence_system), raises a per-(source rank, CTA) flag in every peer (st.release.sys), waits for
-// the peers' flags of the same CTA index (ld.acquire.sys, bounded), then adds the slots of all ranks
-// from its OWN memory in rank order, adds the bias once, rounds once and stores y.  Every rank ends up
-// with identical bits; partials cross the link in float32, so the result is rounded once instead of
-// once per rank.  No multicast objects, no library kernel touches peer memory.
+// Epilogue = the collective, in the style of a low-latency all-reduce.  The CTA PUSHES its float32 partial tile
+// into a slot of every peer's mapped region over NVLink, each pair of values as one 16-byte store
+// {value, epoch, value, epoch}: an 8-byte half of such a store arrives whole, so the epoch word next to a value says
+// that the value is the one of this call, and no fence, flag or second round trip is needed.  It then reads the
+// slots the peers pushed into its OWN memory, polling every 16-byte word until both epoch words match (bounded),
+// adds the ranks' partials in rank order (its own from shared memory), adds the bias once, rounds once and stores
+// y.  Every rank ends up with identical bits; partials cross the link in float32, so the result is rounded once
+// instead of once per rank.  No multicast objects, no library kernel touches peer memory.
 //
-// Region of a rank:  slots[2][world][kLarMaxCtas][kLarSlotFloats] float32 | flags[world][kLarMaxCtas] |
-// epoch[kLarMaxCtas].  Slots are indexed by CTA, not by column, so a CTA's slot is only ever touched by
-// the CTAs of the same index; call e uses parity e & 1.  A rank can be at most one call ahead of a peer
-// (to start call e + 2 it needs the peer's flag of call e + 1, which the peer's CTA raises only after it
-// has finished reading call e), so two parities are enough.  The epoch lives on the device so that a
-// captured CUDA graph replays the call.
+// Region of a rank:  slots[2][world][kLarMaxCtas][2 * kLarSlotFloats] 32-bit words | epoch[kLarMaxCtas].  Slots are
+// indexed by CTA, not by column, so a CTA's slot is only ever touched by the CTAs of the same index; call e uses
+// parity e & 1.  A rank can be at most one call ahead of a peer (to start call e + 2 it has finished call e + 1,
+// for which it needed the peer's values of call e + 1, which the peer's CTA pushes only after it has finished
+// reading call e), so two parities are enough and a stale slot carries epoch e - 2.  The epoch lives on the
+// device so that a captured CUDA graph replays the call; the region starts zeroed and epochs start at 1.
 //
 // A wait that runs out (about a second) raises FDMS_DEV_WAIT_TIMEOUT, leaves the silent rank out of the
 // sum and returns.  After that the ranks' epochs may disagree: the status bit is FATAL for the region,
@@ -40,7 +41,7 @@ constexpr int kLarMaxTpc = 8;              // tiles of 16 columns per CTA
 constexpr int kLarSlotFloats = kLarMaxTpc * 128;      // 8 rows x 16 columns per tile
 constexpr int kLarMaxCtas = 512;
 constexpr int kLarMaxWorld = 8;
-constexpr unsigned kLarSpinLimit = 1u << 21;
+constexpr unsigned kLarSpinLimit = 1u << 20;      // polls of one word before giving up (about a second)
 
 struct LarParams {
     const uint16_t* x; int64_t x_stride;
@@ -48,24 +49,19 @@ struct LarParams {
     const uint16_t* bias;
     uint16_t* y; int64_t y_stride;
     int M, N, K, ks, tpc;                  // ks K-splits x tpc tiles = 8 warps
-    float* slots[kLarMaxWorld];            // region of every rank (index = rank)
-    uint32_t* flags[kLarMaxWorld];
+    uint32_t* slots[kLarMaxWorld];         // region of every rank (index = rank)
     uint32_t* epoch;                       // local
     int rank, world;
     int32_t* dev_status;
 };
 
-__device__ __forceinline__ uint32_t lar_ld_acquire(const uint32_t* p) {
-    uint32_t v;
-    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-    return v;
+// 16 bytes {value, epoch, value, epoch}; system-scope relaxed accesses that bypass L1
+__device__ __forceinline__ void lar_st_pair(uint32_t* p, float a, float b, uint32_t e) {
+    asm volatile("st.volatile.global.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(__float_as_uint(a)), "r"(e), "r"(__float_as_uint(b)), "r"(e) : "memory");
 }
-__device__ __forceinline__ void lar_st_release(uint32_t* p, uint32_t v) {
-    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
-__device__ __forceinline__ float4 lar_ld_volatile(const float4* p) {
-    float4 v;
-    asm volatile("ld.volatile.global.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p) : "memory");
+__device__ __forceinline__ uint4 lar_ld_pair(const uint32_t* p) {
+    uint4 v;
+    asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
     return v;
 }
 
@@ -79,16 +75,16 @@ __device__ __forceinline__ void lar_mma(float (&c)[4], uint32_t a0, uint32_t a1,
                      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-// Offset (in floats) of the slot of (parity, source rank, CTA) inside a region.
+// Offset (in 32-bit words) of the slot of (parity, source rank, CTA) inside a region.
 __device__ __forceinline__ size_t lar_slot(int parity, int src, int cta, int world) {
-    return (((size_t)parity * world + src) * kLarMaxCtas + cta) * kLarSlotFloats;
+    return (((size_t)parity * world + src) * kLarMaxCtas + cta) * (2 * kLarSlotFloats);
 }
 
 template <bool BF16>
 __global__ void __launch_bounds__(kLarThreads) linear_allreduce_kernel(LarParams p) {
     __shared__ float s_part[kLarWarps][128];             // per warp: its tile's 16 columns x 8 rows
     __shared__ __align__(16) float s_sum[kLarMaxTpc * 128];
-    __shared__ int s_missing[kLarMaxWorld];
+    __shared__ volatile int s_missing[kLarMaxWorld];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
     const int c = blockIdx.x;
     const int tile_local = warp / p.ks, split = warp - tile_local * p.ks;
@@ -151,34 +147,39 @@ __global__ void __launch_bounds__(kLarThreads) linear_allreduce_kernel(LarParams
     // ---- the collective ----
     const uint32_t e = p.epoch[c] + 1;
     const int parity = (int)(e & 1u);
+    const int pairs = tile_floats / 2;
+    for (int i = tid; i < (p.world - 1) * pairs; i += kLarThreads) {
+        int r = i / pairs;
+        const int v = i - r * pairs;
+        r += r >= p.rank ? 1 : 0;                                   // peers only
+        lar_st_pair(p.slots[r] + lar_slot(parity, p.rank, c, p.world) + 4 * v, s_sum[2 * v], s_sum[2 * v + 1], e);
+    }
+    // sum in rank order (own partial from shared memory, the peers' from this rank's region), bias once, one rounding
+    const uint32_t* mine = p.slots[p.rank];
     const int vecs = tile_floats / 4;
-    for (int i = tid; i < p.world * vecs; i += kLarThreads) {
-        const int r = i / vecs, v = i - r * vecs;
-        ((float4*)(p.slots[r] + lar_slot(parity, p.rank, c, p.world)))[v] = ((const float4*)s_sum)[v];
-    }
-    __threadfence_system();
-    __syncthreads();
-    if (tid < p.world && tid != p.rank) {
-        lar_st_release(p.flags[tid] + p.rank * kLarMaxCtas + c, e);        // "this rank's partial of CTA c, call e, is in your memory"
-        const uint32_t* f = p.flags[p.rank] + tid * kLarMaxCtas + c;
-        unsigned spins = 0;
-        while ((int32_t)(lar_ld_acquire(f) - e) < 0) {
-            if (++spins >= kLarSpinLimit) {
-                s_missing[tid] = 1;
-                if (p.dev_status) atomicOr(p.dev_status, FDMS_DEV_WAIT_TIMEOUT);
-                break;
-            }
-            __nanosleep(32);
-        }
-    }
-    __syncthreads();
-    // sum in rank order from this rank's own memory, bias once, one rounding
-    const float* mine = p.slots[p.rank];
     for (int v = tid; v < vecs; v += kLarThreads) {
         float4 sum = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
         for (int r = 0; r < p.world; ++r) {
-            if (s_missing[r]) continue;
-            const float4 a = lar_ld_volatile((const float4*)(mine + lar_slot(parity, r, c, p.world)) + v);
+            float4 a;
+            if (r == p.rank) {
+                a = ((const float4*)s_sum)[v];
+            } else {
+                const uint32_t* src = mine + lar_slot(parity, r, c, p.world) + 8 * v;
+                uint4 lo = lar_ld_pair(src), hi = lar_ld_pair(src + 4);
+                unsigned spins = 0;
+                while (lo.y != e || lo.w != e || hi.y != e || hi.w != e) {
+                    if (s_missing[r] || ++spins >= kLarSpinLimit) {
+                        if (!s_missing[r]) {
+                            s_missing[r] = 1;
+                            if (p.dev_status) atomicOr(p.dev_status, FDMS_DEV_WAIT_TIMEOUT);
+                        }
+                        break;
+                    }
+                    lo = lar_ld_pair(src); hi = lar_ld_pair(src + 4);
+                }
+                if (lo.y != e || lo.w != e || hi.y != e || hi.w != e) continue;      // silent rank: left out
+                a = make_float4(__uint_as_float(lo.x), __uint_as_float(lo.z), __uint_as_float(hi.x), __uint_as_float(hi.z));
+            }
             sum.x += a.x; sum.y += a.y; sum.z += a.z; sum.w += a.w;
         }
         // vector v = tile v / 32, column (v % 32) / 2, rows 4 * (v & 1) .. + 3
@@ -208,10 +209,9 @@ using namespace fdms;
 
 extern "C" int64_t fdms_linear_allreduce_region_bytes(int32_t world) {
     if (world < 2 || world > kLarMaxWorld) return -1;
-    const int64_t slots = 2ll * world * kLarMaxCtas * kLarSlotFloats * 4;
-    const int64_t flags = (int64_t)world * kLarMaxCtas * 4;
+    const int64_t slots = 2ll * world * kLarMaxCtas * (2 * kLarSlotFloats) * 4;
     const int64_t epoch = (int64_t)kLarMaxCtas * 4;
-    return slots + flags + epoch;
+    return slots + epoch;
 }
 
 extern "C" int32_t fdms_linear_decode_allreduce(
@@ -244,14 +244,13 @@ extern "C" int32_t fdms_linear_decode_allreduce(
     p.x = (const uint16_t*)x; p.x_stride = x_row_stride; p.w = (const uint16_t*)weight; p.w_stride = w_row_stride;
     p.bias = (const uint16_t*)bias; p.y = (uint16_t*)y; p.y_stride = y_row_stride;
     p.M = rows; p.N = out_features; p.K = in_features; p.ks = ks; p.tpc = tpc;
-    const size_t slot_floats = 2ull * world * kLarMaxCtas * kLarSlotFloats;
-    for (int r = 0; r < kLarMaxWorld; ++r) { p.slots[r] = nullptr; p.flags[r] = nullptr; }
+    const size_t slot_words = 2ull * world * kLarMaxCtas * (2 * kLarSlotFloats);
+    for (int r = 0; r < kLarMaxWorld; ++r) p.slots[r] = nullptr;
     for (int r = 0; r < world; ++r) {
         FDMS_REQUIRE(peer_regions[r] != nullptr, FDMS_E_ARG, "fdms_linear_decode_allreduce: region of rank %d is null", r);
-        p.slots[r] = (float*)peer_regions[r];
-        p.flags[r] = (uint32_t*)(p.slots[r] + slot_floats);
+        p.slots[r] = (uint32_t*)peer_regions[r];
     }
-    p.epoch = p.flags[rank] + (size_t)world * kLarMaxCtas;
+    p.epoch = p.slots[rank] + slot_words;
     p.rank = rank; p.world = world; p.dev_status = dev_status;
     cudaStream_t st = (cudaStream_t)stream;
     if (dtype == FDMS_BF16)

@@ -131,11 +131,13 @@ class FusedRowParallel(_PeerRegions):
 
 
 def init_fused_row_parallel(device, group=None):
-    """Sets up the fused linear + all-reduce for this process (collective over the group).  Switched
-    on with `FDMS_FUSED_ROW_PARALLEL=1`; otherwise the two-step path (linear, then all-reduce) runs."""
+    """Sets up the fused linear + all-reduce for this process (collective over the group).  On by
+    default under tensor parallelism (measured on two B200s inside a replayed graph: 6.2 us per o_proj call of
+    the 8B shape against 15.3 us for the decode linear kernel followed by NCCL, 3.9 us for the linear kernel
+    alone; the 8B decode step 2.68 against 3.52 ms); `FDMS_FUSED_ROW_PARALLEL=0` keeps the two-step path."""
     global _FUSED
     _FUSED = None
-    if os.environ.get("FDMS_FUSED_ROW_PARALLEL", "0").strip().lower() in {"0", "false", "off", "no"}:
+    if os.environ.get("FDMS_FUSED_ROW_PARALLEL", "1").strip().lower() in {"0", "false", "off", "no"}:
         return None
     if not dist.is_initialized() or dist.get_world_size(group) < 2:
         return None

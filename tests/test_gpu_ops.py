@@ -763,21 +763,21 @@ def _lar_layout(n, k):
                                             (8, 2064, 256, False), (1, 2048, 6144, True)])
 def test_fused_linear_allreduce_with_a_staged_peer(dev, dtype, rows, n, k, bias):
     """The row-parallel linear layer fused with its all-reduce, run as rank 0 of 2 on one GPU.  The peer
-    is staged by the host: its float32 partial tiles already sit in rank 0's region and its flags are
-    raised, so the kernel finds them at once.  Result = this rank's x W^T + the staged partial (+ bias),
-    compared with a float32 computation; two calls in a row use the two halves of the region; rank 0's
-    own partial must have been pushed into the peer's region with its flags."""
+    is staged by the host: its float32 partial tiles already sit in rank 0's region, every value next to the
+    epoch of the call, so the kernel finds them at once.  Result = this rank's x W^T + the staged partial
+    (+ bias), compared with a float32 computation; two calls in a row use the two halves of the region; rank
+    0's own partial must have been pushed into the peer's region, value by value with the call's epoch."""
     from fastdms_b200 import _lib
     lib = _lib.lib()
     MAXC, SLOT = 512, 1024
     ks, tpc, ctas = _lar_layout(n, k)
     nbytes = lib.fdms_linear_allreduce_region_bytes(2)
-    assert nbytes == 2 * 2 * MAXC * SLOT * 4 + 2 * MAXC * 4 + MAXC * 4
+    assert nbytes == 2 * 2 * MAXC * (2 * SLOT) * 4 + MAXC * 4
     regions = [torch.zeros((nbytes,), dtype=torch.uint8, device=dev) for _ in range(2)]
     ptrs = torch.tensor([r.data_ptr() for r in regions], dtype=torch.int64)
-    slot_bytes = 2 * 2 * MAXC * SLOT * 4
-    slots = [r[:slot_bytes].view(torch.float32).view(2, 2, MAXC, SLOT) for r in regions]       # [parity][source][cta][...]
-    flags = [r[slot_bytes: slot_bytes + 2 * MAXC * 4].view(torch.int32).view(2, MAXC) for r in regions]
+    slot_bytes = 2 * 2 * MAXC * (2 * SLOT) * 4
+    # [parity][source][cta][value index][value bits, epoch]
+    slots = [r[:slot_bytes].view(torch.int32).view(2, 2, MAXC, SLOT, 2) for r in regions]
     g = torch.Generator(device=dev).manual_seed(rows + n + k)
     w = (torch.randn((n, k), device=dev, generator=g) * k ** -0.5).to(dtype)
     b = torch.randn((n,), device=dev, generator=g).to(dtype) if bias else None
@@ -791,8 +791,8 @@ def test_fused_linear_allreduce_with_a_staged_peer(dev, dtype, rows, n, k, bias)
     for call in (1, 2):
         x = torch.randn((rows, k), device=dev, generator=g).to(dtype)
         peer = torch.randn((rows, n), device=dev, generator=g)
-        slots[0][call & 1, 1, :ctas, : tpc * 128] = to_slots(peer)
-        flags[0][1, :ctas] = call
+        slots[0][call & 1, 1, :ctas, : tpc * 128, 0] = to_slots(peer).contiguous().view(torch.int32)
+        slots[0][call & 1, 1, :ctas, : tpc * 128, 1] = call
         y = torch.full((rows, n), float("nan"), device=dev, dtype=dtype)
         _lib.check(lib.fdms_linear_decode_allreduce(
             x.data_ptr(), x.stride(0), w.data_ptr(), w.stride(0), _lib.ptr(b), y.data_ptr(), y.stride(0),
@@ -801,16 +801,15 @@ def test_fused_linear_allreduce_with_a_staged_peer(dev, dtype, rows, n, k, bias)
         ref = own + peer + (b.float() if bias else 0.0)
         tol = 2.0 ** -7 * float(ref.abs().max())
         assert torch.isfinite(y.float()).all() and float((y.float() - ref).abs().max()) <= tol
-        # this rank's partial went to the peer's region (and to its own), with the flag of this call
-        pushed = slots[1][call & 1, 0, :ctas, : tpc * 128]
+        # this rank's partial went to the peer's region, every value with the epoch of this call
+        pushed = slots[1][call & 1, 0, :ctas, : tpc * 128, 0].contiguous().view(torch.float32)
         assert float((pushed - to_slots(own)).abs().max()) <= 2e-3 * float(own.abs().max()) + 1e-5
-        assert torch.equal(slots[0][call & 1, 0, :ctas, : tpc * 128], pushed)
-        assert (flags[1][0, :ctas] == call).all()
+        assert (slots[1][call & 1, 0, :ctas, : tpc * 128, 1] == call).all()
     assert _lib.read_device_status(dev) == 0
 
 
 def test_fused_linear_allreduce_leaves_a_silent_peer_out(dev):
-    """A peer that never raises its flags: every bounded wait runs out after about a second, the kernel
+    """A peer that never pushes its values: the bounded waits run out after about a second, the kernel
     raises FDMS_DEV_WAIT_TIMEOUT, sums what it has (its own partial) and returns; the context stays usable."""
     import time
     from fastdms_b200 import _lib

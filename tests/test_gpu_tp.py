@@ -338,3 +338,90 @@ def test_fused_linear_allreduce_two_gpus():
     assert all(p.exitcode == 0 for p in procs)
     for rank in range(2):
         assert results[rank][0], f"rank {rank}: {results[rank][1]}"
+
+
+def _tp_bf16_rank(rank: int, world: int, out_q) -> None:
+    import os
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(PORT + 21), RANK=str(rank), WORLD_SIZE=str(world),
+                      LOCAL_RANK=str(rank), FDMS_PEER_ALLREDUCE="0")
+    sys.path.insert(0, str(ROOT))
+    sys.path.insert(0, str(ROOT / "tests" / "golden"))
+    import torch.distributed as dist
+    import make_golden_model as G
+    from fastdms_b200 import LLM, SamplingParams, _lib
+    from fastdms_b200.layers import peer_allreduce
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", device_id=torch.device("cuda", rank))
+    try:
+        try:
+            runs = {}
+            for fused in ("1", "0"):
+                os.environ["FDMS_FUSED_ROW_PARALLEL"] = fused
+                cfg = dict(G.MODEL_CFG)
+                cfg.update(torch_dtype="bfloat16", lm_head_factor=G.BF16_LM_HEAD_FACTOR)
+                llm = LLM("config0-tiny-llama", hf_config=cfg, random_init_seed=G.SEED, dtype="bfloat16",
+                          kv_cache_dtype="float8_e4m3fn", max_model_len=1024, max_num_seqs=4, max_num_batched_tokens=4096,
+                          compact_kv_capacity_tokens=8192, dms_window_size=G.WINDOW, dms_alpha_scale=G.ALPHA_SCALE,
+                          dms_alpha_offset=G.ALPHA_OFFSET, tensor_parallel_size=world, device=f"cuda:{rank}")
+                assert (peer_allreduce.fused_row_parallel() is not None) == (fused == "1")
+                sp = SamplingParams(temperature=0.0, max_tokens=6, ignore_eos=True)
+                seqs = [llm.add_request(p, sp) for p in G.make_prompts()]
+                llm.step()
+                logits = []
+                for _ in range(4):
+                    llm.step()
+                    logits.append(llm.model_runner.graphs[len(seqs)].logits.float().cpu().numpy().copy())
+                    # follow the same history in both runs: a near-tie must not send them apart
+                    if fused == "1":
+                        runs.setdefault("tokens", []).append([s.completion_token_ids[-1] for s in seqs])
+                    else:
+                        for s, tok in zip(seqs, runs["tokens"][len(logits) - 1]):
+                            s.token_ids[-1] = tok
+                            s.last_token = tok
+                runs[fused] = np.stack(logits)
+                torch.cuda.synchronize()
+                dist.barrier()
+            out_q.put((rank, True, "", runs["1"], runs["0"], _lib.read_device_status(f"cuda:{rank}")))
+        except BaseException:
+            import traceback
+            traceback.print_exc()
+            out_q.put((rank, False, traceback.format_exc()[-600:], None, None, -1))
+            raise
+        finally:
+            out_q.close(); out_q.join_thread()
+    finally:
+        sys.stdout.flush(); sys.stderr.flush()
+        os._exit(0 if sys.exc_info()[0] is None else 1)
+
+
+def test_tp2_bf16_fused_row_parallel_matches_nccl_path():
+    """The tiny model in bf16 on two GPUs, decode steps with the row-parallel layers fused with their all-reduce
+    against the same steps with the linear kernel followed by NCCL, on the same token history: logits within
+    16-bit rounding of each other (the fused path rounds the sum once, NCCL adds rounded partials), identical
+    on both ranks."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_tp_bf16_rank, args=(r, 2, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    results = {}
+    try:
+        for _ in range(2):
+            rank, ok, detail, fused, nccl, status = q.get(timeout=240)
+            results[rank] = (ok, detail, fused, nccl, status)
+    finally:
+        for p in procs:
+            p.join(timeout=60)
+            if p.is_alive():
+                p.kill()
+    for rank in range(2):
+        ok, detail, fused, nccl, status = results[rank]
+        assert ok, f"rank {rank}: {detail}"
+        assert status == 0
+        scale = float(np.abs(nccl).max())
+        assert np.abs(fused - nccl).max() <= 3e-2 * scale, (np.abs(fused - nccl).max(), scale)
+    assert np.array_equal(results[0][2], results[1][2]), "ranks disagree on the fused path's logits"
+    assert all(p.exitcode == 0 for p in procs)
