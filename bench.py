@@ -368,12 +368,10 @@ def run_model_block(dev, world: int, steps: int) -> dict:
     2048, 32 q / 8 KV heads of 64, MLP 8192, vocab 128256; random-init bf16 weights, FP8 compact KV,
     window 256, eviction rate 7/8), c = 8 prompts of 8192 random token ids per GPU, greedy decode
     through `LLMEngine.step()` (scheduler, graph replay and token read-back included)."""
-    import argparse as _ap
-
     import torch
-    from benchmarks.bench_model import run as run_model
-    ns = _ap.Namespace(shape="llama-1b", concurrency=B, prompt_len=CTX, decode_steps=steps, tp=1, window=WINDOW,
-                       expiry_interval=1, paged=False, prefill_chunk=0, eager=False, no_warmup=False, seed=0, run_ahead=True)
+    from benchmarks.bench_model import build_parser, run as run_model
+    ns = build_parser().parse_args(["--shape", "llama-1b", "--concurrency", str(B), "--prompt-len", str(CTX),
+                                    "--decode-steps", str(steps), "--window", str(WINDOW), "--run-ahead"])
     r = run_model(ns)
     params = 16 * (2048 * (32 + 16) * 64 + 2048 * 2048 + 3 * 2048 * 8192) + 128256 * 2048        # streamed once per step
     kv_bytes = r["mean_live_at_end"] * 16 * B * HK * 2 * D

@@ -41,11 +41,12 @@ def run(args) -> dict:
         raise SystemExit(f"--tp must be 1 (replicas) or the number of ranks ({world})")
 
     hf = dict(SHAPES[args.shape])
-    if args.shard > 1:
+    shard = getattr(args, "shard", 1)
+    if shard > 1:
         # one rank's slice of an N-way tensor-parallel model on one GPU, collectives left out: the kernels one
         # rank launches per step, for a launch list of the tensor-parallel step
         for key in ("num_attention_heads", "num_key_value_heads", "intermediate_size", "vocab_size"):
-            hf[key] = hf[key] // args.shard
+            hf[key] = hf[key] // shard
     hf.update(attention_bias=True, torch_dtype="bfloat16",
               max_position_embeddings=args.prompt_len + args.decode_steps + 8)
     c = args.concurrency
@@ -108,7 +109,7 @@ def run(args) -> dict:
     t_prefill, t_decode = (float(x) for x in t.tolist())
     ctx_end = args.prompt_len + args.decode_steps
     return {
-        "shape": args.shape + (f" (slice 1/{args.shard})" if args.shard > 1 else ""), "n_gpus": world, "parallelism": f"tp{args.tp}" if args.tp > 1 else f"replicas x{world}",
+        "shape": args.shape + (f" (slice 1/{shard})" if shard > 1 else ""), "n_gpus": world, "parallelism": f"tp{args.tp}" if args.tp > 1 else f"replicas x{world}",
         "concurrency_per_replica": c, "prompt_len": args.prompt_len, "decode_steps_timed": steps,
         "decode_tok_s": replicas * c * steps / t_decode, "decode_ms_per_step": t_decode / steps * 1e3,
         "prefill_tok_s": replicas * c * args.prompt_len / t_prefill, "prefill_s": t_prefill, "prefill_steps": prefill_steps,
@@ -120,7 +121,7 @@ def run(args) -> dict:
     }
 
 
-def main() -> None:
+def build_parser() -> argparse.ArgumentParser:
     ap = argparse.ArgumentParser()
     ap.add_argument("--shape", choices=sorted(SHAPES), default="llama-1b")
     ap.add_argument("--concurrency", type=int, default=8)
@@ -138,7 +139,11 @@ def main() -> None:
                     help="launch the next decode step from device-resident tokens before this step's are read")
     ap.add_argument("--no-warmup", action="store_true")
     ap.add_argument("--seed", type=int, default=0)
-    args = ap.parse_args()
+    return ap
+
+
+def main() -> None:
+    args = build_parser().parse_args()
     out = run(args)
     if int(os.environ.get("RANK", "0")) == 0:
         print(json.dumps(out))

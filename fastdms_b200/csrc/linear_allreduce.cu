@@ -158,16 +158,28 @@ __global__ void __launch_bounds__(kLarThreads) linear_allreduce_kernel(LarParams
     const uint32_t* mine = p.slots[p.rank];
     const int vecs = tile_floats / 4;
     for (int v = tid; v < vecs; v += kLarThreads) {
+        // every peer's words are requested at once (one round trip when they have all arrived); only then does the
+        // thread wait, peer by peer in rank order, for those whose epoch words do not match yet
+        uint4 lo[kLarMaxWorld], hi[kLarMaxWorld];
+#pragma unroll
+        for (int r = 0; r < kLarMaxWorld; ++r) {
+            if (r < p.world && r != p.rank) {
+                const uint32_t* src = mine + lar_slot(parity, r, c, p.world) + 8 * v;
+                lo[r] = lar_ld_pair(src);
+                hi[r] = lar_ld_pair(src + 4);
+            }
+        }
         float4 sum = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-        for (int r = 0; r < p.world; ++r) {
+#pragma unroll
+        for (int r = 0; r < kLarMaxWorld; ++r) {
+            if (r >= p.world) continue;
             float4 a;
             if (r == p.rank) {
                 a = ((const float4*)s_sum)[v];
             } else {
                 const uint32_t* src = mine + lar_slot(parity, r, c, p.world) + 8 * v;
-                uint4 lo = lar_ld_pair(src), hi = lar_ld_pair(src + 4);
                 unsigned spins = 0;
-                while (lo.y != e || lo.w != e || hi.y != e || hi.w != e) {
+                while (lo[r].y != e || lo[r].w != e || hi[r].y != e || hi[r].w != e) {
                     if (s_missing[r] || ++spins >= kLarSpinLimit) {
                         if (!s_missing[r]) {
                             s_missing[r] = 1;
@@ -175,10 +187,11 @@ __global__ void __launch_bounds__(kLarThreads) linear_allreduce_kernel(LarParams
                         }
                         break;
                     }
-                    lo = lar_ld_pair(src); hi = lar_ld_pair(src + 4);
+                    lo[r] = lar_ld_pair(src);
+                    hi[r] = lar_ld_pair(src + 4);
                 }
-                if (lo.y != e || lo.w != e || hi.y != e || hi.w != e) continue;      // silent rank: left out
-                a = make_float4(__uint_as_float(lo.x), __uint_as_float(lo.z), __uint_as_float(hi.x), __uint_as_float(hi.z));
+                if (lo[r].y != e || lo[r].w != e || hi[r].y != e || hi[r].w != e) continue;      // silent rank: left out
+                a = make_float4(__uint_as_float(lo[r].x), __uint_as_float(lo[r].z), __uint_as_float(hi[r].x), __uint_as_float(hi[r].z));
             }
             sum.x += a.x; sum.y += a.y; sum.z += a.z; sum.w += a.w;
         }

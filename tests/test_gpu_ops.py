@@ -759,25 +759,25 @@ def _lar_layout(n, k):
 
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
-@pytest.mark.parametrize("rows,n,k,bias", [(8, 4096, 2048, False), (8, 4096, 512, True), (3, 4096, 1536, True),
-                                            (8, 2064, 256, False), (1, 2048, 6144, True)])
-def test_fused_linear_allreduce_with_a_staged_peer(dev, dtype, rows, n, k, bias):
-    """The row-parallel linear layer fused with its all-reduce, run as rank 0 of 2 on one GPU.  The peer
-    is staged by the host: its float32 partial tiles already sit in rank 0's region, every value next to the
-    epoch of the call, so the kernel finds them at once.  Result = this rank's x W^T + the staged partial
+@pytest.mark.parametrize("rows,n,k,bias,world", [(8, 4096, 2048, False, 2), (8, 4096, 512, True, 8), (3, 4096, 1536, True, 4),
+                                                  (8, 2064, 256, False, 3), (1, 2048, 6144, True, 2)])
+def test_fused_linear_allreduce_with_a_staged_peer(dev, dtype, rows, n, k, bias, world):
+    """The row-parallel linear layer fused with its all-reduce, run as rank 0 of `world` on one GPU.  The peers
+    are staged by the host: their float32 partial tiles already sit in rank 0's region, every value next to the
+    epoch of the call, so the kernel finds them at once.  Result = this rank's x W^T + the staged partials
     (+ bias), compared with a float32 computation; two calls in a row use the two halves of the region; rank
-    0's own partial must have been pushed into the peer's region, value by value with the call's epoch."""
+    0's own partial must have been pushed into every peer's region, value by value with the call's epoch."""
     from fastdms_b200 import _lib
     lib = _lib.lib()
     MAXC, SLOT = 512, 1024
     ks, tpc, ctas = _lar_layout(n, k)
-    nbytes = lib.fdms_linear_allreduce_region_bytes(2)
-    assert nbytes == 2 * 2 * MAXC * (2 * SLOT) * 4 + MAXC * 4
-    regions = [torch.zeros((nbytes,), dtype=torch.uint8, device=dev) for _ in range(2)]
+    nbytes = lib.fdms_linear_allreduce_region_bytes(world)
+    assert nbytes == 2 * world * MAXC * (2 * SLOT) * 4 + MAXC * 4
+    regions = [torch.zeros((nbytes,), dtype=torch.uint8, device=dev) for _ in range(world)]
     ptrs = torch.tensor([r.data_ptr() for r in regions], dtype=torch.int64)
-    slot_bytes = 2 * 2 * MAXC * (2 * SLOT) * 4
+    slot_bytes = 2 * world * MAXC * (2 * SLOT) * 4
     # [parity][source][cta][value index][value bits, epoch]
-    slots = [r[:slot_bytes].view(torch.int32).view(2, 2, MAXC, SLOT, 2) for r in regions]
+    slots = [r[:slot_bytes].view(torch.int32).view(2, world, MAXC, SLOT, 2) for r in regions]
     g = torch.Generator(device=dev).manual_seed(rows + n + k)
     w = (torch.randn((n, k), device=dev, generator=g) * k ** -0.5).to(dtype)
     b = torch.randn((n,), device=dev, generator=g).to(dtype) if bias else None
@@ -790,21 +790,23 @@ def test_fused_linear_allreduce_with_a_staged_peer(dev, dtype, rows, n, k, bias)
 
     for call in (1, 2):
         x = torch.randn((rows, k), device=dev, generator=g).to(dtype)
-        peer = torch.randn((rows, n), device=dev, generator=g)
-        slots[0][call & 1, 1, :ctas, : tpc * 128, 0] = to_slots(peer).contiguous().view(torch.int32)
-        slots[0][call & 1, 1, :ctas, : tpc * 128, 1] = call
+        peers = [torch.randn((rows, n), device=dev, generator=g) for _ in range(world - 1)]
+        for r, peer in enumerate(peers, start=1):
+            slots[0][call & 1, r, :ctas, : tpc * 128, 0] = to_slots(peer).contiguous().view(torch.int32)
+            slots[0][call & 1, r, :ctas, : tpc * 128, 1] = call
         y = torch.full((rows, n), float("nan"), device=dev, dtype=dtype)
         _lib.check(lib.fdms_linear_decode_allreduce(
             x.data_ptr(), x.stride(0), w.data_ptr(), w.stride(0), _lib.ptr(b), y.data_ptr(), y.stride(0),
-            _lib.dtype_code(dtype), rows, n, k, ptrs.data_ptr(), 0, 2, _lib.status_word(dev).data_ptr(), _lib.stream_ptr(dev)))
+            _lib.dtype_code(dtype), rows, n, k, ptrs.data_ptr(), 0, world, _lib.status_word(dev).data_ptr(), _lib.stream_ptr(dev)))
         own = x.float() @ w.float().t()
-        ref = own + peer + (b.float() if bias else 0.0)
+        ref = own + sum(peers) + (b.float() if bias else 0.0)
         tol = 2.0 ** -7 * float(ref.abs().max())
         assert torch.isfinite(y.float()).all() and float((y.float() - ref).abs().max()) <= tol
-        # this rank's partial went to the peer's region, every value with the epoch of this call
-        pushed = slots[1][call & 1, 0, :ctas, : tpc * 128, 0].contiguous().view(torch.float32)
-        assert float((pushed - to_slots(own)).abs().max()) <= 2e-3 * float(own.abs().max()) + 1e-5
-        assert (slots[1][call & 1, 0, :ctas, : tpc * 128, 1] == call).all()
+        # this rank's partial went to every peer's region, every value with the epoch of this call
+        for r in range(1, world):
+            pushed = slots[r][call & 1, 0, :ctas, : tpc * 128, 0].contiguous().view(torch.float32)
+            assert float((pushed - to_slots(own)).abs().max()) <= 2e-3 * float(own.abs().max()) + 1e-5
+            assert (slots[r][call & 1, 0, :ctas, : tpc * 128, 1] == call).all()
     assert _lib.read_device_status(dev) == 0
 
 
