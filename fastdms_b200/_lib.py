@@ -65,6 +65,7 @@ _SIGNATURES = {
     "fdms_silu_and_mul": (I32, [P, I64, P, I64, I32, I64, I32, P]),
     "fdms_qk_rmsnorm": (I32, [P, I64, I64, I32, P, P, I64, I64, I32, P, I32, I64, I32, F, P]),
     "fdms_linear_decode": (I32, [P, I64, P, I64, P, P, I64, I32, I32, I32, I32, P]),
+    "fdms_linear_decode_gated": (I32, [P, I64, P, I64, P, P, I64, I32, I32, I32, I32, P]),
     "fdms_linear_decode_norm": (I32, [P, I64, P, I64, P, F, P, I64, P, I64, P, P, I64, I32, I32, I32, I32, P]),
     "fdms_argmax_workspace_bytes": (I64, [I64]),
     "fdms_argmax_rows": (I32, [P, I64, I32, I64, I64, P, P, I64, P]),

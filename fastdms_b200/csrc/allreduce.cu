@@ -1,49 +1,44 @@
 // One-shot all-reduce over NVLink peer memory for the small tensors of tensor-parallel decode
 // ([batch, hidden] after o_proj and down_proj: 64 KB at batch 8, hidden 4096; the reference calls
 // NCCL's all_reduce there, fastdms/layers/linear.py:1044-1048).  At this size an all-reduce is pure
-// latency, so every rank pushes nothing and pulls everything: it publishes its input in a buffer the
-// peers can read, raises a flag in every peer's memory, waits for the peers' flags, then reads all
-// buffers and adds them in rank order (the same order on every rank: all ranks get identical bits).
+// latency, so the exchange is one NVLink traversal: every rank PUSHES its input into a slot of every
+// peer's region, each 32-bit word next to the call's epoch (16-byte stores {word, epoch, word, epoch} whose
+// 8-byte halves arrive whole), then reads the slots the peers pushed into its OWN memory, waiting (bounded)
+// for the words whose epoch does not match yet, and adds all inputs in rank order (the same order on every
+// rank: all ranks get identical bits).  No fence, no flag, no load from a peer.
 //
 // Memory, per rank, all in one peer-mapped allocation:
-//   data[2][max_bytes]           two buffers, used alternately by consecutive calls
-//   flags[world][kArCtas]        flags[r][c]: epoch of the last call whose chunk c rank r has published
-//   epoch[kArCtas]               this rank's call counter, one per CTA (kept on the device so that a
-//                                captured CUDA graph can replay the call)
-// Protocol for call e (buffer e & 1), CTA c of every rank working on chunk c:
-//   copy own chunk -> data[e & 1]; __threadfence_system(); flag (rank, c) := e in every peer;
-//   wait until flags[r][c] >= e for every peer r (a peer may already be one call ahead: it cannot be
-//   two ahead, because for that it needs this rank's flag of call e + 1, which is raised only after
-//   this call has finished reading); sum the chunk over ranks 0..world-1; store.
-// Every wait is bounded: after kArSpinLimit polls the CTA raises FDMS_DEV_WAIT_TIMEOUT in the status
-// word, skips the peers that did not answer and returns, so a missing peer costs seconds, not a hang.
+//   slots[2][world][2 * max_bytes]   two halves used alternately by consecutive calls; slot (half, r) holds
+//                                    what rank r pushed, as (word, epoch) pairs
+//   epoch[kArCtas]                   this rank's call counter, one per CTA (kept on the device so that a
+//                                    captured CUDA graph can replay the call); the region starts zeroed
+// A rank can be at most one call ahead of a peer (to start call e + 2 it has finished call e + 1, for which it
+// needed the peer's words of call e + 1, which the peer pushes only after it has finished reading call e), so
+// two halves are enough and a stale slot carries epoch e - 2.
+// Every wait is bounded: after kArSpinLimit polls of a word the CTA raises FDMS_DEV_WAIT_TIMEOUT in the status
+// word, leaves the silent peer out and returns, so a missing peer costs seconds, not a hang.  After a timeout
+// the ranks' epochs may disagree: the bit is fatal for the region, which must be re-created collectively.
 #include <string.h>
 
 #include "common.cuh"
 
 namespace fdms {
 
-constexpr int kArCtas = 8;                 // CTAs per call, fixed: part of the flag layout
+constexpr int kArCtas = 8;                 // CTAs per call, fixed: part of the epoch layout
 constexpr int kArThreads = 256;
 constexpr int kArMaxWorld = 8;
-constexpr unsigned kArSpinLimit = 1u << 21;       // polls of a local flag: about a second
+constexpr unsigned kArSpinLimit = 1u << 20;       // polls of one word: about a second
 
 struct ArParams {
-    uint8_t* data[kArMaxWorld];            // peers' data regions (index = rank), [2][max_bytes]
-    uint32_t* flags[kArMaxWorld];          // peers' flag arrays, [world][kArCtas]
+    uint8_t* slots[kArMaxWorld];           // peers' regions (index = rank)
     uint32_t* epoch;                       // local, [kArCtas]
     const void* in; void* out;
-    int64_t n; int dtype; int rank, world; int64_t max_bytes;
+    int64_t n; int dtype; int rank, world; int64_t max_bytes;     // max_bytes rounded up to 256
     int32_t* dev_status;
 };
 
-__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
-    uint32_t v;
-    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-    return v;
-}
-__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
-    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+__device__ __forceinline__ void st_pair16(void* p, uint32_t a, uint32_t b, uint32_t e) {
+    asm volatile("st.volatile.global.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(a), "r"(e), "r"(b), "r"(e) : "memory");
 }
 __device__ __forceinline__ uint4 ld_volatile16(const void* p) {
     uint4 v;
@@ -71,8 +66,13 @@ __device__ __forceinline__ void accumulate16(const uint4& v, int dt, float (&acc
     }
 }
 
+// Byte offset of slot (half, source rank) inside a region.
+__device__ __forceinline__ int64_t ar_slot(int half, int src, int world, int64_t max_bytes) {
+    return ((int64_t)half * world + src) * 2 * max_bytes;
+}
+
 __global__ void __launch_bounds__(kArThreads) allreduce_oneshot_kernel(ArParams p) {
-    __shared__ int s_missing[kArMaxWorld];
+    __shared__ volatile int s_missing[kArMaxWorld];
     const int c = blockIdx.x, tid = threadIdx.x;
     const int esz = p.dtype == FDMS_F32 ? 4 : 2;
     const int64_t bytes = p.n * esz;
@@ -80,36 +80,56 @@ __global__ void __launch_bounds__(kArThreads) allreduce_oneshot_kernel(ArParams 
     const int64_t per = (vecs + kArCtas - 1) / kArCtas;
     const int64_t v0 = (int64_t)c * per, v1 = min(vecs, v0 + per);
     const uint32_t e = p.epoch[c] + 1;
-    uint8_t* mine = p.data[p.rank] + (int64_t)(e & 1u) * p.max_bytes;
+    const int half = (int)(e & 1u);
     if (tid < kArMaxWorld) s_missing[tid] = 0;
-    // publish this rank's chunk
-    for (int64_t i = v0 + tid; i < v1; i += kArThreads) ((uint4*)mine)[i] = ((const uint4*)p.in)[i];
-    __threadfence_system();
     __syncthreads();
-    if (tid < p.world && tid != p.rank) {
-        st_release_sys(p.flags[tid] + p.rank * kArCtas + c, e);       // "rank's chunk c of call e is readable"
-        // wait for the same announcement from that peer (bounded)
-        const uint32_t* f = p.flags[p.rank] + tid * kArCtas + c;
-        unsigned spins = 0;
-        while ((int32_t)(ld_acquire_sys(f) - e) < 0) {
-            if (++spins >= kArSpinLimit) {
-                s_missing[tid] = 1;
-                if (p.dev_status) atomicOr(p.dev_status, FDMS_DEV_WAIT_TIMEOUT);
-                break;
-            }
-            __nanosleep(32);
+    // push this rank's chunk to every peer: vector i becomes two 16-byte (word, epoch) stores at 32 * i
+    for (int64_t i = v0 + tid; i < v1; i += kArThreads) {
+        const uint4 v = ((const uint4*)p.in)[i];
+        for (int r = 0; r < p.world; ++r) {
+            if (r == p.rank) continue;
+            uint8_t* dst = p.slots[r] + ar_slot(half, p.rank, p.world, p.max_bytes) + (i << 5);
+            st_pair16(dst, v.x, v.y, e);
+            st_pair16(dst + 16, v.z, v.w, e);
         }
     }
-    __syncthreads();
-    // sum in rank order
+    // sum in rank order: own input from `in`, the peers' from this rank's region
+    const uint8_t* mine = p.slots[p.rank];
     for (int64_t i = v0 + tid; i < v1; i += kArThreads) {
+        uint4 lo[kArMaxWorld], hi[kArMaxWorld];
+#pragma unroll
+        for (int r = 0; r < kArMaxWorld; ++r) {
+            if (r < p.world && r != p.rank) {
+                const uint8_t* src = mine + ar_slot(half, r, p.world, p.max_bytes) + (i << 5);
+                lo[r] = ld_volatile16(src);
+                hi[r] = ld_volatile16(src + 16);
+            }
+        }
         float acc[8];
 #pragma unroll
         for (int j = 0; j < 8; ++j) acc[j] = 0.0f;
-        for (int r = 0; r < p.world; ++r) {
-            if (s_missing[r]) continue;
-            const uint8_t* src = p.data[r] + (int64_t)(e & 1u) * p.max_bytes;
-            accumulate16(ld_volatile16(src + (i << 4)), p.dtype, acc);
+#pragma unroll
+        for (int r = 0; r < kArMaxWorld; ++r) {
+            if (r >= p.world) continue;
+            if (r == p.rank) {
+                accumulate16(((const uint4*)p.in)[i], p.dtype, acc);
+                continue;
+            }
+            const uint8_t* src = mine + ar_slot(half, r, p.world, p.max_bytes) + (i << 5);
+            unsigned spins = 0;
+            while (lo[r].y != e || lo[r].w != e || hi[r].y != e || hi[r].w != e) {
+                if (s_missing[r] || ++spins >= kArSpinLimit) {
+                    if (!s_missing[r]) {
+                        s_missing[r] = 1;
+                        if (p.dev_status) atomicOr(p.dev_status, FDMS_DEV_WAIT_TIMEOUT);
+                    }
+                    break;
+                }
+                lo[r] = ld_volatile16(src);
+                hi[r] = ld_volatile16(src + 16);
+            }
+            if (lo[r].y != e || lo[r].w != e || hi[r].y != e || hi[r].w != e) continue;       // silent peer: left out
+            accumulate16(make_uint4(lo[r].x, lo[r].z, hi[r].x, hi[r].z), p.dtype, acc);
         }
         uint4 o;
         if (p.dtype == FDMS_F32) {
@@ -231,8 +251,8 @@ extern "C" int32_t fdms_ipc_region_destroy(void* ptr) {
 
 extern "C" int64_t fdms_allreduce_region_bytes(int32_t world, int64_t max_bytes) {
     if (world < 1 || world > kArMaxWorld || max_bytes <= 0) return -1;
-    const int64_t data = 2 * ((max_bytes + 255) / 256) * 256;
-    return data + 256 * ((world * kArCtas * 4 + kArCtas * 4 + 255) / 256);
+    const int64_t half = ((max_bytes + 255) / 256) * 256;
+    return 2 * world * 2 * half + 256;             // (word, epoch) slots of both halves, then the epoch counters
 }
 
 extern "C" int32_t fdms_allreduce_oneshot(
@@ -252,13 +272,12 @@ extern "C" int32_t fdms_allreduce_oneshot(
                  "fdms_allreduce_oneshot: in and out must be 16-byte aligned");
     const int64_t half = ((max_bytes + 255) / 256) * 256;
     ArParams p;
-    for (int r = 0; r < kArMaxWorld; ++r) { p.data[r] = nullptr; p.flags[r] = nullptr; }
+    for (int r = 0; r < kArMaxWorld; ++r) p.slots[r] = nullptr;
     for (int r = 0; r < world; ++r) {
         FDMS_REQUIRE(peer_regions[r] != nullptr, FDMS_E_ARG, "fdms_allreduce_oneshot: region of rank %d is null", r);
-        p.data[r] = (uint8_t*)peer_regions[r];
-        p.flags[r] = (uint32_t*)((uint8_t*)peer_regions[r] + 2 * half);
+        p.slots[r] = (uint8_t*)peer_regions[r];
     }
-    p.epoch = p.flags[rank] + world * kArCtas;
+    p.epoch = (uint32_t*)(p.slots[rank] + 2 * (int64_t)world * 2 * half);
     p.in = in; p.out = out; p.n = n; p.dtype = dtype; p.rank = rank; p.world = world; p.max_bytes = half;
     p.dev_status = dev_status;
     allreduce_oneshot_kernel<<<kArCtas, kArThreads, 0, (cudaStream_t)stream>>>(p);

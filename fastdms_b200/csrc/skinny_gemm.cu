@@ -64,14 +64,19 @@ struct SgNorm {
     uint16_t* residual_out; int64_t res_out_stride;
 };
 
-template <bool BF16, int NT, bool NORM>
+// GATED = true (NT = 2) is the gate_up projection of a gated MLP with its activation: the CTA's two tiles are the
+// gate columns n0 .. n0 + 15 and the up columns N/2 + n0 .. of W[N, K], and it writes
+//   y[m, n0 + j] = round(round(silu(gate)) * up),  gate and up rounded to the activation dtype first,
+// the arithmetic of the projection followed by silu_mul_kernel (fastdms/layers/activation.py: SiluAndMul), [M, N/2].
+template <bool BF16, int NT, bool NORM, bool GATED = false>
 __global__ void __launch_bounds__(kSgWarps * 32) skinny_gemm_kernel(
     const uint16_t* __restrict__ x, int64_t x_stride, const uint16_t* __restrict__ w, int64_t w_stride,
     const uint16_t* __restrict__ bias, uint16_t* __restrict__ y, int64_t y_stride, int M, int N, int K, SgNorm nrm) {
     __shared__ float s_part[kSgWarps][NT][128];
     __shared__ float s_ss[kSgWarps][8];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
-    const int n0 = blockIdx.x * 16 * NT;
+    static_assert(!GATED || NT == 2, "the gated form pairs one gate tile with one up tile");
+    const int n0 = blockIdx.x * 16 * (GATED ? 1 : NT);
     const int kslice = K / kSgWarps, k_begin = warp * kslice;
     float acc[NT][4];
 #pragma unroll
@@ -146,8 +151,8 @@ __global__ void __launch_bounds__(kSgWarps * 32) skinny_gemm_kernel(
         }
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt) {
-            const int row = n0 + nt * 16 + g;                       // rows row and row + 8 of W
-            if (n0 + nt * 16 >= N) break;                           // uniform: the last CTA may own fewer tiles
+            const int row = (GATED ? n0 + nt * (N / 2) : n0 + nt * 16) + g;       // rows row and row + 8 of W
+            if (!GATED && n0 + nt * 16 >= N) break;                 // uniform: the last CTA may own fewer tiles
             const uint16_t* w0 = w + (int64_t)row * w_stride + k_begin + ks + 8 * t;
             const uint16_t* w1 = w0 + 8 * w_stride;
             if (ks != 0 || nt != 0) {
@@ -170,6 +175,27 @@ __global__ void __launch_bounds__(kSgWarps * 32) skinny_gemm_kernel(
         *(float2*)&s_part[warp][nt][(g + 8) * 8 + 2 * t] = make_float2(acc[nt][2], acc[nt][3]);
     }
     __syncthreads();
+    if constexpr (GATED) {
+        for (int idx = tid; idx < 128; idx += kSgWarps * 32) {
+            const int m = idx >> 4, nl = idx & 15;
+            const int n = n0 + nl;
+            if (m >= M || n >= N / 2) continue;
+            float gate = 0.0f, up = 0.0f;
+#pragma unroll
+            for (int wv = 0; wv < kSgWarps; ++wv) { gate += s_part[wv][0][nl * 8 + m]; up += s_part[wv][NT - 1][nl * 8 + m]; }
+            if (bias) {
+                gate += BF16 ? __uint_as_float((uint32_t)bias[n] << 16) : __half2float(*(const __half*)&bias[n]);
+                up += BF16 ? __uint_as_float((uint32_t)bias[N / 2 + n] << 16) : __half2float(*(const __half*)&bias[N / 2 + n]);
+            }
+            gate = round_to_dtype(gate, DT);
+            up = round_to_dtype(up, DT);
+            const float out = round_to_dtype(gate / (1.0f + __expf(-gate)), DT) * up;
+            uint16_t o;
+            if (BF16) { const __nv_bfloat16 b = __float2bfloat16_rn(out); o = *(const uint16_t*)&b; }
+            else { const __half hh = __float2half_rn(out); o = *(const uint16_t*)&hh; }
+            y[(int64_t)m * y_stride + n] = o;
+        }
+    } else {
     for (int idx = tid; idx < NT * 128; idx += kSgWarps * 32) {
         const int nt = idx >> 7, r = idx & 127, m = r >> 4, nl = r & 15;
         const int n = n0 + nt * 16 + nl;
@@ -182,6 +208,7 @@ __global__ void __launch_bounds__(kSgWarps * 32) skinny_gemm_kernel(
         if (BF16) { const __nv_bfloat16 b = __float2bfloat16_rn(sum); o = *(const uint16_t*)&b; }
         else { const __half hh = __float2half_rn(sum); o = *(const uint16_t*)&hh; }
         y[(int64_t)m * y_stride + n] = o;
+    }
     }
 }
 
@@ -240,6 +267,35 @@ extern "C" int32_t fdms_linear_decode(const void* x, int64_t x_row_stride, const
     clear_error();
     return linear_decode_launch(x, x_row_stride, weight, w_row_stride, bias, y, y_row_stride, dtype, rows, out_features,
                                 in_features, nullptr, stream);
+}
+
+extern "C" int32_t fdms_linear_decode_gated(const void* x, int64_t x_row_stride, const void* weight, int64_t w_row_stride,
+                                            const void* bias, void* y, int64_t y_row_stride, int32_t dtype, int32_t rows,
+                                            int32_t out_features, int32_t in_features, void* stream) {
+    clear_error();
+    FDMS_REQUIRE(x && weight && y, FDMS_E_ARG, "fdms_linear_decode_gated: null pointer");
+    FDMS_REQUIRE(dtype == FDMS_BF16 || dtype == FDMS_F16, FDMS_E_DTYPE, "fdms_linear_decode_gated: bf16 or f16 only");
+    FDMS_REQUIRE(rows >= 0 && rows <= 8, FDMS_E_CAPACITY, "fdms_linear_decode_gated: at most 8 rows, got %d", rows);
+    FDMS_REQUIRE(out_features > 0 && out_features % 32 == 0 && in_features > 0 && in_features % (kSgWarps * kSgStep) == 0,
+                 FDMS_E_ARG, "fdms_linear_decode_gated: out_features %% 32 and in_features %% %d must be 0 (got %d, %d)",
+                 kSgWarps * kSgStep, out_features, in_features);
+    FDMS_REQUIRE(((uintptr_t)x & 15) == 0 && ((uintptr_t)weight & 15) == 0 && (x_row_stride * 2) % 16 == 0 &&
+                     (w_row_stride * 2) % 16 == 0,
+                 FDMS_E_ARG, "fdms_linear_decode_gated: x and weight rows must be 16-byte aligned");
+    if (rows == 0) return FDMS_OK;
+    const unsigned grid = (unsigned)(out_features / 32);
+    cudaStream_t st = (cudaStream_t)stream;
+    const SgNorm nrm{nullptr, 0, nullptr, 0.0f, nullptr, 0};
+    if (dtype == FDMS_BF16)
+        FDMS_CUDA_OK(launch_chained(skinny_gemm_kernel<true, 2, false, true>, dim3(grid), dim3(kSgWarps * 32), st, chain_launches(),
+                                    (const uint16_t*)x, x_row_stride, (const uint16_t*)weight, w_row_stride, (const uint16_t*)bias,
+                                    (uint16_t*)y, y_row_stride, (int)rows, (int)out_features, (int)in_features, nrm));
+    else
+        FDMS_CUDA_OK(launch_chained(skinny_gemm_kernel<false, 2, false, true>, dim3(grid), dim3(kSgWarps * 32), st, chain_launches(),
+                                    (const uint16_t*)x, x_row_stride, (const uint16_t*)weight, w_row_stride, (const uint16_t*)bias,
+                                    (uint16_t*)y, y_row_stride, (int)rows, (int)out_features, (int)in_features, nrm));
+    FDMS_CHECK_LAUNCH("skinny_gemm_kernel (gated)");
+    return FDMS_OK;
 }
 
 extern "C" int32_t fdms_linear_decode_norm(

@@ -110,6 +110,36 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None = No
     return F.linear(x, weight, bias)
 
 
+def gated_linear(x: torch.Tensor, lin) -> torch.Tensor | None:
+    """`SiluAndMul(lin(x))` for a merged gate_up projection (gate rows first, then up rows) in ONE launch of
+    `fdms_linear_decode_gated` when the decode linear kernel applies (same bits as the two launches), else None."""
+    w, b = lin.weight, lin.bias
+    if getattr(lin, "weight_fp8", None) is not None or not _decode_linear_ok(x, w, b) or w.shape[0] % 32 != 0:
+        return None
+    rows, n = x.shape[0], w.shape[0]
+    y = torch.empty((rows, n // 2), dtype=x.dtype, device=x.device)
+    with torch.cuda.device(x.device):
+        rc = _lib.lib().fdms_linear_decode_gated(
+            x.data_ptr(), x.stride(0), w.data_ptr(), w.stride(0), b.data_ptr() if b is not None else None,
+            y.data_ptr(), y.stride(0), _lib.dtype_code(x.dtype), rows, n, w.shape[1], _lib.stream_ptr(x.device))
+    _lib.check(rc)
+    return y
+
+
+def norm_gated_linear(x: torch.Tensor, residual: torch.Tensor | None, norm, lin, act_fn) -> tuple[torch.Tensor, torch.Tensor]:
+    """`h, r = norm(x, residual); return act_fn(lin(h)), r` of a decoder block's MLP entry, with the projection and
+    the activation in one launch at decode sizes."""
+    if _FUSE_NORM:
+        gate_up, r = norm_linear(x, residual, norm, lin)
+        return act_fn(gate_up), r
+    if residual is None:
+        h, r = norm(x), x
+    else:
+        h, r = norm(x, residual)
+    y = gated_linear(h, lin)
+    return (y if y is not None else act_fn(lin(h))), r
+
+
 _REPLICA_MODE = False
 
 

@@ -22,7 +22,7 @@ from fastdms_b200.layers.compact_attention import (dms_decode_store_transient_k_
 from fastdms_b200.layers.embed_head import ParallelLMHead, VocabParallelEmbedding
 from fastdms_b200.layers.layernorm import RMSNorm, qk_rmsnorm_
 from fastdms_b200.layers.linear import (MergedColumnParallelLinear, QKVParallelLinear, RowParallelLinear,
-                                        norm_linear, tp_world)
+                                        norm_gated_linear, norm_linear, tp_world)
 from fastdms_b200.layers.rotary_embedding import get_rope
 from fastdms_b200.utils.context import get_context
 from fastdms_b200.utils.profiler import get_profiler
@@ -163,9 +163,6 @@ class LlamaMLP(nn.Module):
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         return self.down_proj(self.act_fn(self.gate_up_proj(x)))
 
-    def from_gate_up(self, gate_up: torch.Tensor) -> torch.Tensor:
-        return self.down_proj(self.act_fn(gate_up))
-
 
 class LlamaDecoderLayer(nn.Module):
     attention_cls = LlamaAttention
@@ -181,8 +178,9 @@ class LlamaDecoderLayer(nn.Module):
         # norm -> projection pairs go through `norm_linear` (the two modules; one fused launch is an opt-in)
         qkv, residual = norm_linear(hidden_states, residual, self.input_layernorm, self.self_attn.qkv_proj)
         hidden_states = self.self_attn(positions, None, qkv=qkv)
-        gate_up, residual = norm_linear(hidden_states, residual, self.post_attention_layernorm, self.mlp.gate_up_proj)
-        hidden_states = self.mlp.from_gate_up(gate_up)
+        act, residual = norm_gated_linear(hidden_states, residual, self.post_attention_layernorm, self.mlp.gate_up_proj,
+                                          self.mlp.act_fn)
+        hidden_states = self.mlp.down_proj(act)
         return hidden_states, residual
 
 

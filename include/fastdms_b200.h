@@ -390,6 +390,14 @@ int32_t fdms_qk_rmsnorm(
 int32_t fdms_linear_decode(const void* x, int64_t x_row_stride, const void* weight, int64_t w_row_stride,
                            const void* bias, void* y, int64_t y_row_stride, int32_t dtype, int32_t rows,
                            int32_t out_features, int32_t in_features, void* stream);
+/* The gate_up projection of a gated MLP with its activation in one launch (the reference runs F.linear and then
+ * SiluAndMul, fastdms/models/llama.py MLP.forward, fastdms/layers/activation.py):
+ *   y[rows, out/2] = round(round(silu(g)) * u),  g = round(x W[:out/2]^T + b[:out/2]),  u = round(x W[out/2:]^T + b[out/2:]),
+ * bit for bit what fdms_linear_decode followed by fdms_silu_and_mul gives.  Same limits as fdms_linear_decode;
+ * out_features (gate and up together) % 32 == 0. */
+int32_t fdms_linear_decode_gated(const void* x, int64_t x_row_stride, const void* weight, int64_t w_row_stride,
+                                 const void* bias, void* y, int64_t y_row_stride, int32_t dtype, int32_t rows,
+                                 int32_t out_features, int32_t in_features, void* stream);
 
 /* The same with the decoder block's RMSNorm (+ residual add) in front (the reference runs
  * RMSNorm.add_rms_forward, fastdms/layers/layernorm.py:16-48, then F.linear):

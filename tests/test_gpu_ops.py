@@ -474,6 +474,31 @@ def test_qk_rmsnorm_equals_two_rmsnorm_calls(dev, dtype, rows, hq, hk, d):
     assert torch.equal(v, want_v)                      # the neighbouring v columns are untouched
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("rows,inter,k,bias", [(8, 8192, 2048, False), (3, 6144, 4096, True), (1, 1536, 2048, True), (8, 16, 2048, False)])
+def test_gated_decode_linear_equals_linear_then_silu_mul(dev, dtype, rows, inter, k, bias):
+    """gate_up projection + SiLU(gate) * up in one launch (`fdms_linear_decode_gated`): the bits of the decode
+    linear kernel followed by the SiLU-and-multiply kernel (reference: models/llama.py MLP.forward,
+    layers/activation.py SiluAndMul)."""
+    from fastdms_b200 import _lib
+    from fastdms_b200.layers.activation import SiluAndMul
+    from fastdms_b200.layers.linear import linear
+    lib = _lib.lib()
+    g = torch.Generator(device=dev).manual_seed(rows + inter + k)
+    w = (torch.randn((2 * inter, k), device=dev, generator=g) * k ** -0.5).to(dtype)
+    b = torch.randn((2 * inter,), device=dev, generator=g).to(dtype) if bias else None
+    x = (2.0 * torch.randn((rows, k), device=dev, generator=g)).to(dtype)
+    with torch.inference_mode():
+        want = SiluAndMul()(linear(x, w, b))
+        y = torch.full((rows, inter), float("nan"), device=dev, dtype=dtype)
+        _lib.check(lib.fdms_linear_decode_gated(x.data_ptr(), x.stride(0), w.data_ptr(), w.stride(0), _lib.ptr(b), y.data_ptr(),
+                                                y.stride(0), _lib.dtype_code(dtype), rows, 2 * inter, k, _lib.stream_ptr(dev)))
+    assert torch.equal(y, want)
+    ref = torch.nn.functional.silu((x.float() @ w[:inter].float().t()) + (b[:inter].float() if bias else 0.0)) * \
+        ((x.float() @ w[inter:].float().t()) + (b[inter:].float() if bias else 0.0))
+    assert float((y.float() - ref).abs().max()) <= 3 * 2.0 ** (-8 if dtype == torch.bfloat16 else -11) * float(ref.abs().max()) + 1e-3
+
+
 def first_max(x):
     idx = torch.arange(x.shape[1], device=x.device).expand_as(x)
     return torch.where(x == x.max(dim=-1, keepdim=True).values, idx, x.shape[1]).min(dim=-1).values
@@ -559,10 +584,11 @@ def test_positions_outside_the_rotary_table_are_flagged_not_followed(dev):
 
 
 def test_peer_allreduce_kernel_with_a_staged_peer_and_with_a_silent_one(dev):
-    """The one-shot all-reduce kernel on one GPU.  (1) The peer is staged by the host: its data buffer
-    and its flags are already in place, so the kernel finds them at once and must return rank 0's input
-    plus the peer's, for three dtypes and two consecutive calls (buffer alternation).  (2) A peer whose
-    flag nothing sets: the bounded wait runs out after about a second, the kernel raises
+    """The one-shot all-reduce kernel on one GPU.  (1) The peer is staged by the host: its input already sits
+    in rank 0's region, every 32-bit word next to the epoch of the call, so the kernel finds it at once and
+    must return rank 0's input plus the peer's, for three dtypes and two consecutive calls (the two halves of
+    the region); rank 0's own input must have been pushed into the peer's region in the same form.  (2) A
+    peer that never pushes: the bounded wait runs out after about a second, the kernel raises
     FDMS_DEV_WAIT_TIMEOUT, leaves that peer out and returns; the context stays usable."""
     import time
     from fastdms_b200 import _lib
@@ -570,25 +596,27 @@ def test_peer_allreduce_kernel_with_a_staged_peer_and_with_a_silent_one(dev):
     max_bytes = 1 << 16
     nbytes = lib.fdms_allreduce_region_bytes(2, max_bytes)
     half = ((max_bytes + 255) // 256) * 256
+    assert nbytes == 2 * 2 * 2 * half + 256
     g = torch.Generator(device=dev).manual_seed(1)
     for dtype in (torch.float32, torch.bfloat16, torch.float16):
         regions = [torch.zeros((nbytes,), dtype=torch.uint8, device=dev) for _ in range(2)]
         ptrs = torch.tensor([r.data_ptr() for r in regions], dtype=torch.int64)
+        # [half][source rank][word index][word, epoch]
+        slots = [r[: 2 * 2 * 2 * half].view(torch.int32).view(2, 2, half // 4, 2) for r in regions]
         n = 8 * 1024
         for call in (1, 2):
             x0 = torch.randn((n,), device=dev, generator=g).to(dtype)
             x1 = torch.randn((n,), device=dev, generator=g).to(dtype)
-            b = call & 1
-            regions[1][b * half: b * half + n * x1.element_size()] = x1.view(torch.uint8)     # the peer's published input
-            flags0 = regions[0][2 * half: 2 * half + 2 * 8 * 4].view(torch.int32).view(2, 8)
-            flags0[1] = call                                                                   # "peer 1 published call `call`"
+            words = n * x1.element_size() // 4
+            slots[0][call & 1, 1, :words, 0] = x1.view(torch.int32)          # the peer's input, pushed into rank 0's region
+            slots[0][call & 1, 1, :words, 1] = call
             out = torch.empty_like(x0)
             _lib.check(lib.fdms_allreduce_oneshot(ptrs.data_ptr(), 0, 2, max_bytes, x0.data_ptr(), out.data_ptr(), n,
                                                   _lib.dtype_code(dtype), _lib.status_word(dev).data_ptr(), _lib.stream_ptr(dev)))
             want = (x0.float() + x1.float()).to(dtype)
             assert torch.equal(out, want)
-            flags1 = regions[1][2 * half: 2 * half + 2 * 8 * 4].view(torch.int32).view(2, 8)
-            assert (flags1[0] == call).all(), "rank 0 announces its chunks in the peer's region"
+            assert torch.equal(slots[1][call & 1, 0, :words, 0].contiguous(), x0.view(torch.int32)), "rank 0 pushes its input to the peer"
+            assert (slots[1][call & 1, 0, :words, 1] == call).all()
         assert _lib.read_device_status(dev) == 0
     # a silent peer
     regions = [torch.zeros((nbytes,), dtype=torch.uint8, device=dev) for _ in range(2)]
