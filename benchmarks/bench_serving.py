@@ -6,6 +6,11 @@ compact KV pool.  Shapes and arrival process follow the reference's serving-styl
     python -m benchmarks.bench_serving --shape llama-1b --requests 256 --rate 20 \
         --min-prompt 512 --max-prompt 32768 --min-gen 64 --max-gen 512 --max-concurrent 64 \
         [--kv-gib 8] [--prefill-chunk 2048] [--paged] [--admission optimistic]
+    torchrun --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 -m benchmarks.bench_serving ...     # N replicas
+
+Under torchrun every rank runs its own engine on its own GPU and serves request i of the one arrival
+stream when i mod N is its rank (sequence sharding, no data-path collective); rank 0 prints the
+aggregate (wall time = the slowest rank, throughputs summed, latencies over all requests).
 
 Requests are admitted by the scheduler when the token budget and the compact pool allow: charged
 their worst case (`--admission reserve`) or an estimate of what DMS keeps, with a retry when a
@@ -19,6 +24,7 @@ from __future__ import annotations
 import argparse
 import json
 import math
+import os
 import time
 
 import numpy as np
@@ -31,13 +37,22 @@ def run(args) -> dict:
     from fastdms_b200.engine.llm_engine import LLMEngine
     from fastdms_b200.sampling_params import SamplingParams
 
-    dev = torch.device("cuda", 0)
+    import torch.distributed as dist
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    dev = torch.device("cuda", local)
     torch.cuda.set_device(dev)
+    if world > 1 and not dist.is_initialized():
+        dist.init_process_group("nccl", device_id=dev)
     rng = np.random.default_rng(args.seed)
-    n = args.requests
-    arrivals = np.cumsum(rng.exponential(1.0 / args.rate, size=n))
-    prompts = np.exp(rng.uniform(math.log(args.min_prompt), math.log(args.max_prompt), size=n)).astype(np.int64)
-    gens = rng.integers(args.min_gen, args.max_gen + 1, size=n)
+    n_all = args.requests
+    arrivals = np.cumsum(rng.exponential(1.0 / args.rate, size=n_all))
+    prompts = np.exp(rng.uniform(math.log(args.min_prompt), math.log(args.max_prompt), size=n_all)).astype(np.int64)
+    gens = rng.integers(args.min_gen, args.max_gen + 1, size=n_all)
+    mine = np.arange(rank, n_all, world)                 # request i goes to rank i mod N
+    arrivals, prompts, gens = arrivals[mine], prompts[mine], gens[mine]
+    n = len(mine)
     hf = dict(SHAPES[args.shape])
     max_len = int(args.max_prompt + args.max_gen + 8)
     hf.update(attention_bias=True, torch_dtype="bfloat16", max_position_embeddings=max_len)
@@ -52,7 +67,7 @@ def run(args) -> dict:
         compact_kv_admission_keep_estimate=args.keep_estimate, prefill_chunk_size=args.prefill_chunk or None)
     mgr = engine.model_runner.compact_kv_manager
     vocab = hf["vocab_size"]
-    g = torch.Generator().manual_seed(args.seed)
+    g = torch.Generator().manual_seed(args.seed + rank)
     token_lists = [torch.randint(0, vocab, (int(p),), generator=g).tolist() for p in prompts]
 
     # warm-up: one short request through prefill and a few decode steps
@@ -64,6 +79,8 @@ def run(args) -> dict:
     seqs, first_token_at, done_at = {}, {}, {}
     nxt = 0
     decode_ms, decode_batch, prefill_tokens, peak_live = [], [], 0, 0
+    if world > 1:
+        dist.barrier()                                   # the ranks share one arrival clock
     t0 = time.perf_counter()
     while len(done_at) < n:
         now = time.perf_counter() - t0
@@ -99,7 +116,32 @@ def run(args) -> dict:
     else:
         pool_clean = mgr.free_ranges_per_layer == [[(0, mgr.capacity_tokens)]] * mgr.num_layers
     dm = np.array(decode_ms) if decode_ms else np.zeros(1)
+    status = int(_lib.read_device_status(dev))
+    if world > 1:
+        # one exchange after the timed region; every figure below is over all ranks
+        part = dict(wall=wall, out=out_tokens, prefill=int(prefill_tokens), ttft=ttft, lat=lat, dm=dm, batch=decode_batch,
+                    peak=peak_live, denied=int(mgr.admission_denied_count), retries=int(engine.scheduler.prefill_retries),
+                    preempt=int(engine.scheduler.preemptions), clean=bool(pool_clean), status=status, prompts=prompts, gens=gens)
+        parts = [None] * world
+        dist.all_gather_object(parts, part)
+        wall = max(q["wall"] for q in parts)
+        out_tokens = sum(q["out"] for q in parts)
+        prefill_tokens = sum(q["prefill"] for q in parts)
+        ttft = np.concatenate([q["ttft"] for q in parts]); lat = np.concatenate([q["lat"] for q in parts])
+        dm = np.concatenate([q["dm"] for q in parts])
+        decode_batch = [b for q in parts for b in q["batch"]]
+        peak_live = max(q["peak"] for q in parts)
+        pool_clean = all(q["clean"] for q in parts)
+        status = 0
+        for q in parts:
+            status |= q["status"]
+        prompts = np.concatenate([q["prompts"] for q in parts]); gens = np.concatenate([q["gens"] for q in parts])
+        denied, retries, preempt = (sum(q[k] for q in parts) for k in ("denied", "retries", "preempt"))
+        n = n_all
+    else:
+        denied, retries, preempt = int(mgr.admission_denied_count), int(engine.scheduler.prefill_retries), int(engine.scheduler.preemptions)
     return {
+        "n_gpus": world, "parallelism": f"replicas x{world}, request i -> rank i mod {world}" if world > 1 else "one GPU",
         "shape": args.shape, "requests": n, "arrival_rate_per_s": args.rate, "max_concurrent": args.max_concurrent,
         "prompt_len": [int(prompts.min()), int(np.median(prompts)), int(prompts.max())],
         "gen_len": [int(gens.min()), int(np.median(gens)), int(gens.max())],
@@ -111,10 +153,9 @@ def run(args) -> dict:
         "mean_decode_batch": float(np.mean(decode_batch)) if decode_batch else 0.0,
         "pool_rows_per_layer": mgr.capacity_tokens, "pool_gib": mgr.capacity_tokens * elem_rows / (1 << 30),
         "peak_live_rows_layer0_sampled": peak_live, "admission": args.admission, "prefill_chunk": args.prefill_chunk,
-        "admission_denied": int(mgr.admission_denied_count), "prefill_retries": int(engine.scheduler.prefill_retries),
-        "preemptions": int(engine.scheduler.preemptions),
+        "admission_denied": denied, "prefill_retries": retries, "preemptions": preempt,
         "pool_returned_clean": bool(pool_clean), "layout": "paged" if mgr.paged else "spans",
-        "device_status": int(_lib.read_device_status(dev)),
+        "device_status": status,
         "data": "synthetic: random-init bf16 weights, uniform random token ids",
     }
 
@@ -136,7 +177,14 @@ def main() -> None:
     ap.add_argument("--keep-estimate", type=float, default=0.2)
     ap.add_argument("--prefill-chunk", type=int, default=2048, help="prefill prompts in chunks of this many tokens (0: one pass)")
     ap.add_argument("--seed", type=int, default=0)
-    print(json.dumps(run(ap.parse_args())))
+    out = run(ap.parse_args())
+    if int(os.environ.get("RANK", "0")) == 0:
+        print(json.dumps(out))
+    import torch.distributed as dist
+    if dist.is_initialized():
+        torch.cuda.synchronize()
+        dist.barrier()
+        os._exit(0)           # captured graphs and the process group are not torn down in order by the interpreter
 
 
 if __name__ == "__main__":
