@@ -42,7 +42,7 @@ _SIGNATURES = {
                                 P, I64, P, I64, P, P, I32, I32, I32, I32, DBL, DBL, I32, I32, I32, I32, P, P]),
     "fdms_extract_decisions": (I32, [P, I32, I64, I64, P, I64, I64, I32, I32, I32, DBL, DBL, P]),
     "fdms_expire_compact": (I32, [P, I64, I64, I64, P, I64, I64, I64, P, P, P, I64, I64, P, P, I64, I32, I64,
-                                  P, I64, I64, I64, P, P, I64, P, P, I32, I32, I32, I32, I32, I32, P, P, P]),
+                                  P, I64, I64, I64, P, P, I64, P, P, I32, I32, I32, I32, I32, I32, P, P, P, P]),
     "fdms_pack_count": (I32, [P, I64, P, P, P, I32, I32, I32, I32, P]),
     "fdms_pack_scatter": (I32, [P, P, I32, I64, I64, P, I64, P, P, I32, P, P, P, I32, I64, P, I64,
                                 P, I64, I64, P, P, I64, I64, P, I64, I64, P, I64, I32, P, P,
@@ -146,7 +146,10 @@ def status_word(device: torch.device) -> torch.Tensor:
     idx = device.index if device.index is not None else torch.cuda.current_device()
     w = _status_words.get(idx)
     if w is None:
-        w = torch.zeros(1, dtype=torch.int32, device=device)
+        # an ordinary tensor even when the first caller runs under inference mode (the engine does): callers
+        # outside it clear the word in place
+        with torch.inference_mode(False):
+            w = torch.zeros(1, dtype=torch.int32, device=device)
         _status_words[idx] = w
     return w
 
@@ -182,6 +185,7 @@ def attn_workspace(device: torch.device, batch: int, num_kv_heads: int, head_dim
         full = lib().fdms_attn_decode_workspace_bytes(_WS_MAX_SPANS, 1, _WS_MAX_HEAD_DIM)
         if ws is not None:
             _retired_workspaces.append(ws)          # graphs captured earlier may still reference it
-        ws = torch.zeros(max(need, full), dtype=torch.uint8, device=device)
+        with torch.inference_mode(False):
+            ws = torch.zeros(max(need, full), dtype=torch.uint8, device=device)
         _workspaces[idx] = ws
     return ws

@@ -29,6 +29,7 @@ struct ExpiryParams {
     const int32_t* seq_slots; const int64_t* cur;
     int layers, seqs, hk, capacity, window, mode;
     long long* stats; int32_t* dev_status;
+    long long* exact;                              // optional, layout of `live`: position up to which a span is known to hold no expired slot
 };
 
 // Exclusive scan of one flag per thread over the CTA; returns this thread's rank and the total.
@@ -286,7 +287,58 @@ __global__ void __launch_bounds__(kIdxThreads, 7) expire_indexed_kernel(ExpiryPa
     const bool active = live > 0 && (sp.bt != nullptr || sp.base >= 0);
     const int live_in = live;
 
-    if (active && live <= kIdxFast) {
+    // ---- steady state of a decode loop: the span was left without an expired slot at position cur - 1 (recorded in
+    // `exact` by that call) and one token has been appended since.  Slots are in position order and the tokens of the
+    // window are all present, so the only slot that can have expired is the one at position cur - window - 1, which
+    // sits window + 1 slots from the end (window + 2 if the token at `cur` is already in the span); and the physical
+    // rows are dense with the newest token in the last one, so that row is the one that moves into the hole.  One slot
+    // is inspected instead of the whole span; anything that does not match these expectations takes the general
+    // path below. ----
+    bool handled = false;
+    if (active && p.exact && p.mode == 0 && p.exact[moff] == cur - 1) {
+        int idx = live - p.window - 1;
+        if (idx >= 1 && (long long)pos[idx] != cur - p.window - 1) --idx;
+        if (idx >= 0 && (long long)pos[idx] == cur - p.window - 1 && ri[live - 1] == live - 1) {
+            handled = true;
+            if (ev[idx] != 0) {
+                const int r = ri[idx];
+                const int new_live = live - 1;
+                // the window's slots and the new token move down by one; loads of all threads before any store
+                constexpr int kPer = 4;
+                int mp[kPer], mr[kPer];
+                uint8_t me[kPer];
+#pragma unroll
+                for (int j = 0; j < kPer; ++j) {
+                    const int i = idx + 1 + tid + j * kIdxThreads;
+                    if (i < live) { mp[j] = pos[i]; me[j] = ev[i]; mr[j] = ri[i]; }
+                }
+                const bool fits = live - (idx + 1) <= kPer * kIdxThreads;
+                bool moved = true;
+                if (tid == 0 && r != new_live) moved = fits && idx_copy_row<VecT>(p, sp, new_live, r);
+                __syncthreads();
+                if (fits) {
+#pragma unroll
+                    for (int j = 0; j < kPer; ++j) {
+                        const int i = idx + 1 + tid + j * kIdxThreads;
+                        if (i < live) {
+                            pos[i - 1] = mp[j];
+                            ev[i - 1] = me[j];
+                            ri[i - 1] = (i == live - 1 && r != new_live) ? r : mr[j];
+                        }
+                    }
+                    if (tid == 0) { pos[live - 1] = -1; ev[live - 1] = 0; ri[live - 1] = live - 1; }
+                    live = new_live;
+                } else {
+                    handled = false;              // a window wider than this path holds: nothing was written
+                }
+                (void)moved;
+            }
+        }
+    }
+
+    if (handled) {
+        // nothing else to do for this span
+    } else if (active && live <= kIdxFast) {
         // ---- short spans (the common case): the span's metadata is staged in shared memory with
         // asynchronous 16-byte copies (one memory round trip, no registers held), every thread then
         // owns a run of consecutive slots.  Loops stay rolled: the kernel runs once per span, so its
@@ -442,6 +494,8 @@ __global__ void __launch_bounds__(kIdxThreads, 7) expire_indexed_kernel(ExpiryPa
         }
         if (tid == 0) p.live[moff] = live;
     }
+    // an all-slots call leaves no expired slot behind; an incremental one may
+    if (p.exact && tid == 0) p.exact[moff] = (active && p.mode == 0) ? cur : -1;
     const int new_live_out = active ? live : old_live;
     if (tid == 0 && p.stats) {
         atomicAdd((unsigned long long*)&p.stats[0], (unsigned long long)(old_live - new_live_out));
@@ -467,7 +521,7 @@ extern "C" int32_t fdms_expire_compact(
     int32_t* free_pages, int32_t* free_counts, int64_t pages_per_layer,
     const int32_t* seq_slots, const int64_t* current_positions,
     int32_t num_layers, int32_t num_seqs, int32_t num_kv_heads, int32_t capacity,
-    int32_t window, int32_t mode, int64_t* stats, int32_t* dev_status, void* stream) {
+    int32_t window, int32_t mode, int64_t* stats, int64_t* exact_through, int32_t* dev_status, void* stream) {
     clear_error();
     FDMS_REQUIRE(token_positions && evict_mask && live_counts && k_pool && v_pool && current_positions,
                  FDMS_E_ARG, "fdms_expire_compact: null pointer");
@@ -494,6 +548,7 @@ extern "C" int32_t fdms_expire_compact(
     p.seq_slots = seq_slots; p.cur = current_positions;
     p.layers = num_layers; p.seqs = num_seqs; p.hk = num_kv_heads; p.capacity = capacity;
     p.window = window; p.mode = mode; p.stats = (long long*)stats; p.dev_status = dev_status;
+    p.exact = row_index ? (long long*)exact_through : nullptr;        // the steady-state path exists with a row index only
     const bool vec16 = row_bytes % 16 == 0 && ((uintptr_t)k_pool % 16 == 0) && ((uintptr_t)v_pool % 16 == 0) &&
                        pool_layer_stride_bytes % 16 == 0;
     if (row_index) {

@@ -142,6 +142,12 @@ class CompactKVManager:
         self.layer_major_row_index = None
         if self.row_indirection:
             self.layer_major_row_index = torch.arange(C, device=dev, dtype=torch.int32).expand(L, S, Hk, C).contiguous()
+        # Position up to which a span is known to hold no expired slot (-1: unknown): lets the per-step expiry of a
+        # decode loop inspect one slot per span instead of the whole span (`fdms_expire_compact: exact_through`).
+        # Written by the expiry launch; reset here whenever slots are written by other means (pack, release).
+        self.layer_major_exact_through = None
+        if self.layer_major_row_index is not None:
+            self.layer_major_exact_through = torch.full((L, S, Hk), -1, device=dev, dtype=torch.int64)
         self.free_active_slots: list[int] = list(range(S))
         self.active_slot_by_seq: dict[int, int] = {}
         self.seq_states: dict[int, CompactKVSequenceState] = {}
@@ -361,6 +367,7 @@ class CompactKVManager:
         ev.zero_()
         if self.layer_major_row_index is not None:
             self.layer_major_row_index[:, slot, :, :] = torch.arange(self.max_model_len, device=self.device, dtype=torch.int32)
+            self.layer_major_exact_through[:, slot, :].fill_(-1)
         state = CompactKVSequenceState(
             seq_id=seq.seq_id, base_offsets=base, range_capacity=rcap, live_counts=live,
             token_positions=pos, evict_mask=ev, max_capacity_per_lh=cap,
@@ -463,6 +470,8 @@ class CompactKVManager:
                 self.expire_device(slots_t, cur, window_size=window_size, layer_id=layer_id)
             starts_t = torch.tensor([int(c) for c in chunk_starts], dtype=torch.int32).to(dev, non_blocking=True)
             prior = self.layer_major_live_counts[layer_id].index_select(0, slots_t.long()).contiguous()
+        if self.layer_major_exact_through is not None:
+            self.layer_major_exact_through[layer_id].index_fill_(0, slots_t.long(), -1)      # the pack writes slots
         with torch.cuda.device(dev):
             _lib.check(lib.fdms_pack_count(ev_u8.data_ptr(), ev_u8.stride(0), cu.data_ptr(), live.data_ptr(),
                                            chunk_offsets.data_ptr(), max_chunks, n, Hk, int(window_size), stream))
@@ -627,6 +636,7 @@ class CompactKVManager:
                 slots_t.data_ptr(), cur_positions_t.data_ptr(),
                 pos.shape[0], slots_t.numel(), self.num_kv_heads, self.max_model_len,
                 int(window_size), 1 if incremental else 0, _lib.ptr(stats),
+                _lib.ptr(None if self.layer_major_exact_through is None else self.layer_major_exact_through[ls]),
                 _lib.status_word(dev).data_ptr(), _lib.stream_ptr(dev))
         _lib.check(rc)
 
@@ -771,6 +781,8 @@ class CompactKVManager:
         self.layer_major_base_offsets[:, slot, :].fill_(-1)
         self.layer_major_range_capacity[:, slot, :].zero_()
         self.layer_major_live_counts[:, slot, :].zero_()
+        if self.layer_major_exact_through is not None:
+            self.layer_major_exact_through[:, slot, :].fill_(-1)
         self.layer_major_token_positions[:, slot, :, :state.max_capacity_per_lh].fill_(-1)
         self.layer_major_evict_mask[:, slot, :, :state.max_capacity_per_lh].zero_()
         self.free_active_slots.append(slot)

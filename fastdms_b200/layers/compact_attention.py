@@ -532,7 +532,7 @@ def _expiry_one_layer(mode, positions_per_lh, evict_per_lh, live_counts, base_of
             compact_k.data_ptr(), compact_v.data_ptr(), 0, row_bytes, compact_k.shape[0],
             None, 0, 0, 0, None, None, 0,
             None, cur.data_ptr(),
-            1, num_seqs, num_kv_heads, capacity, int(window_size), mode, None,
+            1, num_seqs, num_kv_heads, capacity, int(window_size), mode, None, None,
             status.data_ptr(), _lib.stream_ptr(dev))
     _lib.check(rc)
 

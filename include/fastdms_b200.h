@@ -192,6 +192,12 @@ int32_t fdms_extract_decisions(
  * as before.  Logical row i of the span is then physical row row_index[i]; entries at or beyond
  * live equal their own position (the caller initialises the index to 0, 1, 2, ...), so appending at
  * logical slot live needs no index write.
+ * exact_through (optional, with row_index only; int64 with the shape and strides of live_counts, -1 = unknown): the
+ * position up to which a span is known to hold no expired slot.  An all-slots call (mode 0) sets it to the call's
+ * current position, an incremental call to -1.  A mode-0 call that finds `current position - 1` there inspects only
+ * the one slot that can have expired since (decode steps append one token in position order) instead of the whole
+ * span; the result is the same.  The caller sets it to -1 whenever it writes slots of a span by other means (pack,
+ * release).
  * --------------------------------------------------------------------------------------------- */
 int32_t fdms_expire_compact(
     int32_t* token_positions, int64_t pos_stride_l, int64_t pos_stride_s, int64_t pos_stride_h,
@@ -204,7 +210,7 @@ int32_t fdms_expire_compact(
     int32_t* free_pages, int32_t* free_counts, int64_t pages_per_layer,
     const int32_t* seq_slots, const int64_t* current_positions,
     int32_t num_layers, int32_t num_seqs, int32_t num_kv_heads, int32_t capacity,
-    int32_t window, int32_t mode, int64_t* stats, int32_t* dev_status, void* stream);
+    int32_t window, int32_t mode, int64_t* stats, int64_t* exact_through, int32_t* dev_status, void* stream);
 
 /* ---------------------------------------------------------------------------------------------
  * (b) prefill pack of one layer, two launches around the span / page allocation.

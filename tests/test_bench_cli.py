@@ -22,3 +22,20 @@ def test_model_block_arguments_cover_what_run_reads():
     assert ns.run_ahead and ns.shard == 1 and ns.tp == 1
     # bench.py builds its arguments with the same parser
     assert "build_parser().parse_args(" in (ROOT / "bench.py").read_text()
+
+
+def test_cached_scratch_is_not_an_inference_tensor():
+    """The per-device status word is created on first use, possibly by the engine under inference mode; code
+    outside inference mode clears it in place, which an inference tensor would refuse."""
+    import torch
+    from fastdms_b200 import _lib
+    saved = dict(_lib._status_words)
+    _lib._status_words.clear()
+    try:
+        with torch.inference_mode():
+            w = _lib.status_word(torch.device("cpu", 0))
+        assert not w.is_inference()
+        w.zero_()
+    finally:
+        _lib._status_words.clear()
+        _lib._status_words.update(saved)

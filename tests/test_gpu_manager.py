@@ -364,13 +364,17 @@ def test_windowed_cadence_matches_oracle_with_same_cadence(dev):
     assert np.array_equal(st.token_positions.cpu().numpy(), o_pos) and np.array_equal(st.evict_mask.cpu().numpy(), o_ev)
 
 
+@pytest.mark.parametrize("steady", [True, False])
 @pytest.mark.parametrize("paged,interval,T0", [(False, 1, 600), (True, 1, 600), (False, 8, 600), (True, 8, 600),
                                                (True, 1, 2600), (False, 8, 2600)])
-def test_row_index_expiry_keeps_logical_contents(dev, paged, interval, T0):
+def test_row_index_expiry_keeps_logical_contents(dev, paged, interval, T0, steady):
     """Expiry with a row index (K/V rows stay dense but are not shifted): positions, evict bits and
     compact lengths follow the oracle exactly, and the K/V rows read THROUGH the index are the
     oracle's rows in logical order.  interval 8 drops several tokens per call (holes and movers in
-    the same call); spans of 600 tokens are handled from registers, spans of 2600 by the tiled path."""
+    the same call); spans of 600 tokens are handled from registers, spans of 2600 by the tiled path.
+    With interval 1 every call after the first finds the span exact through the previous position and
+    inspects one slot only (`steady`); with the record wiped before each call it takes the general path:
+    both must give the oracle's state."""
     rng = np.random.default_rng(11 + interval + int(paged) + T0)
     L, Hk, D, W, steps = 1, 3, 64, 8, 40
     C = 1024 if T0 < 1000 else 4096
@@ -405,11 +409,16 @@ def test_row_index_expiry_keeps_logical_contents(dev, paged, interval, T0):
         n = int(o_live[0, h])
         o_k[o_base[0, h]:o_base[0, h] + n] = logical_rows(ck, h, n)
         o_v[o_base[0, h]:o_base[0, h] + n] = logical_rows(cv, h, n)
+    exact = m.layer_major_exact_through[:, st.active_slot]
+    assert (exact == -1).all(), "a pack leaves the record unknown"
     for s in range(steps):
         cur = T0 + s
+        if not steady:
+            m.layer_major_exact_through.fill_(-1)
         m.apply_dms_evictions([seq], [cur], window_size=W, sync_stats=False)
         if interval == 1 or s == 0 or cur % interval == 0:
             O.expire_layer(o_pos[0][None], o_ev[0][None], o_live[0][None], o_base[0][None], o_k, o_v, [cur], W)
+            assert (exact == cur).all(), "an all-slots call records the position it made the span exact for"
         assert np.array_equal(st.live_counts.cpu().numpy(), o_live), f"compact lengths differ at step {s}"
         _, _, slot, _ = m.prepare_decode_metadata([seq])
         _, _, o_slot = O.prepare_decode_metadata(o_base[None], o_live[None])
