@@ -641,7 +641,7 @@ def test_peer_allreduce_kernel_with_a_staged_peer_and_with_a_silent_one(dev):
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
 @pytest.mark.parametrize("rows,n,k,bias", [(8, 3072, 2048, True), (8, 2048, 2048, False), (8, 16384, 2048, False),
                                            (8, 2048, 8192, False), (1, 128256, 2048, False), (5, 6144, 4096, True),
-                                           (3, 48, 2048, True)])
+                                           (3, 48, 2048, True), (8, 4096, 12288, True), (2, 1024, 8192, True), (8, 16, 4096, False)])
 def test_decode_linear_kernel_matches_float32_reference(dev, dtype, rows, n, k, bias):
     """Weight-streaming linear layer for <= 8 rows against x @ W^T (+ b) in float32 (the reference
     calls F.linear, layers/linear.py:1044-1048): one rounding of the 16-bit output type."""
