@@ -179,7 +179,7 @@ def main() -> None:
     ap.add_argument("--seed", type=int, default=0)
     out = run(ap.parse_args())
     if int(os.environ.get("RANK", "0")) == 0:
-        print(json.dumps(out))
+        print(json.dumps(out), flush=True)
     import torch.distributed as dist
     if dist.is_initialized():
         torch.cuda.synchronize()
