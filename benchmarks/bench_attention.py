@@ -14,8 +14,9 @@ its `benchmarks/bench_compact_decode.py:81-92,141-154` does (eager calls between
 `max_live_count` passed so that the call does not synchronise) and also as a CUDA graph of the
 same launches.  The reference has contiguous spans and no per-head scale, so its rows use that
 layout with the same span lengths and distinct pools per layer.  It is imported from an unmodified
-install of the reference under `baseline/_ref` (see DESIGN.md for the install command) and is a
-comparison row only: nothing else in this repository imports it."""
+install of the reference under `baseline/_ref` (`python -m pip install --no-index --no-build-isolation --no-deps
+--target baseline/_ref <a copy of the reference tree>`) and is a comparison row only: nothing else in this
+repository imports it."""
 from __future__ import annotations
 
 import argparse
