@@ -295,7 +295,11 @@ __global__ void __launch_bounds__(kIdxThreads, 7) expire_indexed_kernel(ExpiryPa
     // is inspected instead of the whole span; anything that does not match these expectations takes the general
     // path below. ----
     bool handled = false;
-    if (active && p.exact && p.mode == 0 && p.exact[moff] == cur - 1) {
+    // every thread reads the record before thread 0 rewrites it at the end of the kernel (all threads of the CTA must
+    // take the same path below)
+    const long long through = (active && p.exact) ? p.exact[moff] : -2;
+    __syncthreads();
+    if (active && p.exact && p.mode == 0 && through == cur - 1) {
         int idx = live - p.window - 1;
         if (idx >= 1 && (long long)pos[idx] != cur - p.window - 1) --idx;
         if (idx >= 0 && (long long)pos[idx] == cur - p.window - 1 && ri[live - 1] == live - 1) {
