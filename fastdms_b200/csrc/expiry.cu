@@ -268,6 +268,7 @@ __global__ void __launch_bounds__(kIdxThreads, 7) expire_indexed_kernel(ExpiryPa
     const int l = item / (p.hk * p.seqs);
     const int srow = p.seq_slots ? p.seq_slots[sidx] : sidx;
     const int tid = threadIdx.x, lane = tid & 31;
+    pdl_trigger();                      // a dependent launch (the decode metadata) may become resident; it waits for this kernel
 
     const int64_t moff = (int64_t)l * p.meta_sl + (int64_t)srow * p.meta_ss + h;
     const int old_live = p.live[moff];

@@ -46,6 +46,8 @@ __global__ void __launch_bounds__(kMetaThreads) build_decode_metadata_kernel(Met
     const int items = p.batch * p.hk;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     if (tid == 0) s_carry = 0;
+    pdl_trigger();                      // the next launch of the stream may become resident
+    pdl_wait();                         // live counts and block tables come from the preceding kernel (expiry)
     __syncthreads();
     for (int i0 = 0; i0 < items; i0 += kMetaThreads) {
         const int i = i0 + tid;
@@ -116,6 +118,8 @@ __global__ void record_decisions_kernel(
     int total, int batch, int hk, int capacity, unsigned long long* true_count, int advance) {
   // With `advance` the launch is a single CTA that strides over all spans and, once every read of
   // positions[] is done, adds one to each of them (the step's last use of the positions).
+  pdl_trigger();
+  pdl_wait();                           // the decisions come from the preceding kernels
   for (int i0 = blockIdx.x * blockDim.x; i0 < total; i0 += gridDim.x * blockDim.x) {     // uniform per CTA
     const int i = i0 + threadIdx.x;
     bool e = false;
@@ -240,7 +244,8 @@ extern "C" int32_t fdms_build_decode_metadata(
     p.seq_slots = seq_slots;
     p.base_out = base_out; p.live_out = live_out; p.slot_out = slot_out; p.cu_live_out = cu_live_out;
     p.layers = num_layers; p.batch = batch; p.hk = num_kv_heads; p.dev_status = dev_status;
-    build_decode_metadata_kernel<<<num_layers, kMetaThreads, 0, (cudaStream_t)stream>>>(p);
+    FDMS_CUDA_OK(launch_chained(build_decode_metadata_kernel, dim3((unsigned)num_layers), dim3(kMetaThreads), (cudaStream_t)stream,
+                                chain_launches(), p));
     FDMS_CHECK_LAUNCH("build_decode_metadata_kernel");
     return FDMS_OK;
 }
@@ -263,10 +268,11 @@ extern "C" int32_t fdms_record_decisions(
     FDMS_REQUIRE(total < (1ll << 31), FDMS_E_CAPACITY, "fdms_record_decisions: too many spans");
     const int threads = advance_positions ? 1024 : 256;
     const unsigned blocks = advance_positions ? 1u : (unsigned)((total + threads - 1) / threads);
-    record_decisions_kernel<<<blocks, threads, 0, (cudaStream_t)stream>>>(
+    FDMS_CUDA_OK(launch_chained(
+        record_decisions_kernel, dim3(blocks), dim3((unsigned)threads), (cudaStream_t)stream, chain_launches(),
         token_positions, pos_stride_l, pos_stride_s, pos_stride_h, evict_mask, ev_stride_l, ev_stride_s,
         ev_stride_h, live_counts, meta_stride_l, meta_stride_s, evict_all, ea_stride_l, ea_stride_b, positions,
-        seq_slots, (int)total, batch, num_kv_heads, capacity, (unsigned long long*)true_count, advance_positions ? 1 : 0);
+        seq_slots, (int)total, batch, num_kv_heads, capacity, (unsigned long long*)true_count, advance_positions ? 1 : 0));
     FDMS_CHECK_LAUNCH("record_decisions_kernel");
     return FDMS_OK;
 }
