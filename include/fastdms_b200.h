@@ -430,13 +430,15 @@ int32_t fdms_argmax_rows(const void* x, int64_t row_stride, int32_t dtype, int64
 /* ---------------------------------------------------------------------------------------------
  * (e) tensor parallel by KV head: the all-reduce after o_proj and down_proj
  * (fastdms/layers/linear.py:1044-1048 calls NCCL's all_reduce).  One-shot all-reduce over NVLink peer
- * memory for tensors of at most max_bytes: every rank publishes its input in a peer-readable region,
- * raises a flag in each peer's region, waits (bounded) for the peers' flags and sums all inputs in rank
- * order, so every rank gets the same bits.  peer_regions[r] is rank r's region of
+ * memory for tensors of at most max_bytes: every rank pushes its input into a slot of every peer's region,
+ * each 32-bit word next to the call's epoch (so a word carries its own "ready" mark: no fence, no flag), reads
+ * the slots the peers pushed into its own region, waiting (bounded) for words of an older epoch, and sums all
+ * inputs in rank order, so every rank gets the same bits.  peer_regions[r] is rank r's region of
  * fdms_allreduce_region_bytes(world, max_bytes) bytes, zero-filled once before the first call and
  * mapped into this process with fdms_ipc_region_open; the same call sequence must run on every rank.  in/out: n
  * elements of dtype (FDMS_F32 / FDMS_BF16 / FDMS_F16), 16-byte aligned, n * size a multiple of 16.
- * A peer that does not answer within about a second raises FDMS_DEV_WAIT_TIMEOUT and is left out.
+ * A peer that does not answer within about a second raises FDMS_DEV_WAIT_TIMEOUT and is left out; after that
+ * the region must not be used again (the ranks' call counters may disagree): re-create it collectively.
  * --------------------------------------------------------------------------------------------- */
 int64_t fdms_allreduce_region_bytes(int32_t world, int64_t max_bytes);
 /* Peer regions (the one place this library allocates: the caller owns the result and destroys it).
@@ -469,9 +471,9 @@ int32_t fdms_linear_decode_fp8(const void* x, int64_t x_row_stride, const void* 
 /* Row-parallel linear layer fused with its all-reduce, for decode-sized inputs (rows <= 8):
  *   y = sum over ranks of x_r W_r^T (+ bias), one kernel per rank instead of F.linear + NCCL all_reduce
  * (fastdms/layers/linear.py:1044-1048, the o_proj / down_proj call sites).  Every CTA pushes its float32
- * partial tile into a slot of each rank's peer-mapped region (plain peer stores), raises a flag in each
- * peer, waits (bounded) for the peers' flags and sums the ranks' slots from its own memory in rank
- * order: identical bits on every rank, one rounding.  x [rows, in_features] and weight
+ * partial tile into a slot of each peer's mapped region (plain peer stores of {value, epoch} pairs: a value
+ * carries its own "ready" mark, so there is no fence and no flag), waits (bounded) for the peers' values of this
+ * call in its own region and sums the ranks' partials in rank order: identical bits on every rank, one rounding.  x [rows, in_features] and weight
  * [out_features, in_features] are this rank's shards (bf16 or f16, rows 16-byte aligned,
  * in_features % 256 == 0, out_features % 16 == 0, at most 512 CTAs: out_features <= 8192 for
  * in_features >= 2048); bias (may be null) is added once, pass the same vector on every rank.
