@@ -10,6 +10,8 @@
 // k-index of the MMA is a fixed permutation of the memory order (a lane's four MMA k-pairs are the
 // four element pairs of its 16-byte vector, for A and B alike), so no shuffle or shared-memory
 // staging is needed.  f32 accumulation, one rounding to the activation dtype at the end.
+#include <stdlib.h>
+
 #include "common.cuh"
 
 namespace fdms {
@@ -326,7 +328,9 @@ extern "C" int32_t fdms_linear_decode_norm(
 // ------------------------------------------------------------------------------------------------
 namespace fdms {
 
-constexpr int kSg8Vecs = 4;            // 16-byte weight vectors per lane, row and step: 256 k elements per warp and step
+// VECS = 16-byte weight vectors per lane, row and step: 64 * VECS k elements per warp and step.  With 4 a warp has
+// 4 KB of weights in flight, half of what the 16-bit kernel keeps; layers with few tiles and a long K (down_proj)
+// take 8, so that the halved bytes also halve the number of dependent round trips.
 
 __device__ __forceinline__ void sg8_cvt(uint32_t w, uint32_t& lo, uint32_t& hi) {       // 4 e4m3 bytes -> 2 f16x2
     asm("{\n\t.reg .b16 a, b;\n\tmov.b32 {a, b}, %2;\n\tcvt.rn.f16x2.e4m3x2 %0, a;\n\tcvt.rn.f16x2.e4m3x2 %1, b;\n\t}"
@@ -351,7 +355,7 @@ __device__ __forceinline__ void sg8_x_to_f16(const uint4& v, uint32_t (&o)[4]) {
     }
 }
 
-template <bool BF16, int NT>
+template <bool BF16, int NT, int VECS>
 __global__ void __launch_bounds__(kSgWarps * 32) skinny_gemm_fp8_kernel(
     const uint16_t* __restrict__ x, int64_t x_stride, const uint8_t* __restrict__ w, int64_t w_stride,
     const float* __restrict__ scale, const uint16_t* __restrict__ bias, uint16_t* __restrict__ y, int64_t y_stride,
@@ -365,22 +369,22 @@ __global__ void __launch_bounds__(kSgWarps * 32) skinny_gemm_fp8_kernel(
     for (int nt = 0; nt < NT; ++nt) { acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.0f; }
     pdl_trigger();
     // first tile's weight vectors before the dependency is resolved (weights are written by nobody)
-    uint4 wa[kSg8Vecs], wb[kSg8Vecs];
+    uint4 wa[VECS], wb[VECS];
     {
         const uint8_t* w0 = w + (int64_t)(n0 + g) * w_stride + k_begin + 16 * t;
         const uint8_t* w1 = w0 + 8 * w_stride;
 #pragma unroll
-        for (int j = 0; j < kSg8Vecs; ++j) {
+        for (int j = 0; j < VECS; ++j) {
             wa[j] = __ldcs((const uint4*)(w0 + 64 * j));
             wb[j] = __ldcs((const uint4*)(w1 + 64 * j));
         }
     }
     pdl_wait();
     const uint16_t* xr = x + (int64_t)g * x_stride + k_begin + 16 * t;
-    for (int ks = 0; ks < kslice; ks += kSgStep) {
-        uint32_t xb[kSg8Vecs][8];
+    for (int ks = 0; ks < kslice; ks += 64 * VECS) {
+        uint32_t xb[VECS][8];
 #pragma unroll
-        for (int j = 0; j < kSg8Vecs; ++j) {
+        for (int j = 0; j < VECS; ++j) {
             if (g >= M) {
 #pragma unroll
                 for (int i = 0; i < 8; ++i) xb[j][i] = 0u;
@@ -399,13 +403,13 @@ __global__ void __launch_bounds__(kSgWarps * 32) skinny_gemm_fp8_kernel(
             const uint8_t* w1 = w0 + 8 * w_stride;
             if (ks != 0 || nt != 0) {
 #pragma unroll
-                for (int j = 0; j < kSg8Vecs; ++j) {
+                for (int j = 0; j < VECS; ++j) {
                     wa[j] = __ldcs((const uint4*)(w0 + 64 * j));
                     wb[j] = __ldcs((const uint4*)(w1 + 64 * j));
                 }
             }
 #pragma unroll
-            for (int j = 0; j < kSg8Vecs; ++j) {
+            for (int j = 0; j < VECS; ++j) {
                 const uint32_t aw[4] = {wa[j].x, wa[j].y, wa[j].z, wa[j].w}, bw[4] = {wb[j].x, wb[j].y, wb[j].z, wb[j].w};
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
@@ -460,14 +464,22 @@ extern "C" int32_t fdms_linear_decode_fp8(const void* x, int64_t x_row_stride, c
     const unsigned grid = (unsigned)((tiles + nt - 1) / nt);
     const bool bf = dtype == FDMS_BF16;
     cudaStream_t st = (cudaStream_t)stream;
-#define FDMS_SG8_LAUNCH(B, T)                                                                                    \
-    FDMS_CUDA_OK(launch_chained(skinny_gemm_fp8_kernel<B, T>, dim3(grid), dim3(kSgWarps * 32), st, chain_launches(), \
-                                (const uint16_t*)x, x_row_stride, (const uint8_t*)weight_e4m3, w_row_stride, scale,   \
-                                (const uint16_t*)bias, (uint16_t*)y, y_row_stride, (int)rows, (int)out_features,      \
+    // 8 vectors per step (8 KB of weights per warp in flight, about 150 registers: one CTA per SM) where a warp's K
+    // range allows it and the layer has no more CTAs than that anyway: down_proj of the 1B shape 10.1 -> 8.4 us; with
+    // 256 CTAs (the 8B shape's 4096-wide layers) the lost occupancy costs more, 16.3 -> 24.2 us.  FDMS_FP8_VECS=4 / 8
+    // overrides.
+    static const int vecs_env = [] { const char* e = getenv("FDMS_FP8_VECS"); return e ? atoi(e) : 0; }();
+    const bool can8 = nt == 1 && in_features % (kSgWarps * 512) == 0;
+    const bool vecs8 = can8 && (vecs_env == 8 || (vecs_env != 4 && grid <= 148));
+#define FDMS_SG8_LAUNCH(B, T, V)                                                                                    \
+    FDMS_CUDA_OK(launch_chained(skinny_gemm_fp8_kernel<B, T, V>, dim3(grid), dim3(kSgWarps * 32), st, chain_launches(), \
+                                (const uint16_t*)x, x_row_stride, (const uint8_t*)weight_e4m3, w_row_stride, scale,      \
+                                (const uint16_t*)bias, (uint16_t*)y, y_row_stride, (int)rows, (int)out_features,         \
                                 (int)in_features))
-#define FDMS_SG8_PICK(B)                                                                         \
-    do {                                                                                         \
-        if (nt == 4) FDMS_SG8_LAUNCH(B, 4); else if (nt == 2) FDMS_SG8_LAUNCH(B, 2); else FDMS_SG8_LAUNCH(B, 1); \
+#define FDMS_SG8_PICK(B)                                                                                  \
+    do {                                                                                                  \
+        if (vecs8) FDMS_SG8_LAUNCH(B, 1, 8);                                                              \
+        else if (nt == 4) FDMS_SG8_LAUNCH(B, 4, 4); else if (nt == 2) FDMS_SG8_LAUNCH(B, 2, 4); else FDMS_SG8_LAUNCH(B, 1, 4); \
     } while (0)
     if (bf) FDMS_SG8_PICK(true); else FDMS_SG8_PICK(false);
 #undef FDMS_SG8_PICK
