@@ -70,7 +70,10 @@ struct SgNorm {
 // gate columns n0 .. n0 + 15 and the up columns N/2 + n0 .. of W[N, K], and it writes
 //   y[m, n0 + j] = round(round(silu(gate)) * up),  gate and up rounded to the activation dtype first,
 // the arithmetic of the projection followed by silu_mul_kernel (fastdms/layers/activation.py: SiluAndMul), [M, N/2].
-template <bool BF16, int NT, bool NORM, bool GATED = false>
+// WV = 16-byte weight vectors per lane, row and step (8: 256 k elements per warp and step, 8 KB of weights per warp in
+// flight; 16: twice that, about 200 registers, for layers with at most one CTA per SM and a long K, where the number
+// of dependent round trips is what the launch costs).
+template <bool BF16, int NT, bool NORM, bool GATED = false, int WV = 8>
 __global__ void __launch_bounds__(kSgWarps * 32) skinny_gemm_kernel(
     const uint16_t* __restrict__ x, int64_t x_stride, const uint16_t* __restrict__ w, int64_t w_stride,
     const uint16_t* __restrict__ bias, uint16_t* __restrict__ y, int64_t y_stride, int M, int N, int K, SgNorm nrm) {
@@ -87,12 +90,13 @@ __global__ void __launch_bounds__(kSgWarps * 32) skinny_gemm_kernel(
     // The weights do not depend on the preceding kernel: the first tile's vectors are requested before
     // the dependency is resolved, so a chained launch streams them while that kernel still runs.
     pdl_trigger();
-    uint4 wa[8], wb[8];
+    static_assert(WV == 8 || (NT == 1 && !NORM && !GATED), "the wide step is for plain single-tile CTAs");
+    uint4 wa[WV], wb[WV];
     {
         const uint16_t* w0 = w + (int64_t)(n0 + g) * w_stride + k_begin + 8 * t;
         const uint16_t* w1 = w0 + 8 * w_stride;
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
+        for (int j = 0; j < WV; ++j) {
             wa[j] = __ldcs((const uint4*)(w0 + 32 * j));
             wb[j] = __ldcs((const uint4*)(w1 + 32 * j));
         }
@@ -132,10 +136,10 @@ __global__ void __launch_bounds__(kSgWarps * 32) skinny_gemm_kernel(
         for (int wv = 0; wv < kSgWarps; ++wv) tot += s_ss[wv][g];
         inv = rsqrtf(tot / (float)K + nrm.eps);
     }
-    for (int ks = 0; ks < kslice; ks += kSgStep) {
-        uint4 xb[8];
+    for (int ks = 0; ks < kslice; ks += 32 * WV) {
+        uint4 xb[WV];
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
+        for (int j = 0; j < WV; ++j) {
             if (g >= M) { xb[j] = make_uint4(0u, 0u, 0u, 0u); continue; }
             if (!NORM) { xb[j] = __ldg((const uint4*)(xr + ks + 32 * j)); continue; }
             float f[8], nw[8];
@@ -159,13 +163,13 @@ __global__ void __launch_bounds__(kSgWarps * 32) skinny_gemm_kernel(
             const uint16_t* w1 = w0 + 8 * w_stride;
             if (ks != 0 || nt != 0) {
 #pragma unroll
-                for (int j = 0; j < 8; ++j) {
+                for (int j = 0; j < WV; ++j) {
                     wa[j] = __ldcs((const uint4*)(w0 + 32 * j));
                     wb[j] = __ldcs((const uint4*)(w1 + 32 * j));
                 }
             }
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
+            for (int j = 0; j < WV; ++j) {
                 sg_mma<BF16>(acc[nt], wa[j].x, wb[j].x, wa[j].y, wb[j].y, xb[j].x, xb[j].y);
                 sg_mma<BF16>(acc[nt], wa[j].z, wb[j].z, wa[j].w, wb[j].w, xb[j].z, xb[j].w);
             }
@@ -246,6 +250,21 @@ static int32_t linear_decode_launch(const void* x, int64_t x_row_stride, const v
     const bool bf = dtype == FDMS_BF16;
     cudaStream_t st = (cudaStream_t)stream;
     const SgNorm nrm = norm ? *norm : SgNorm{nullptr, 0, nullptr, 0.0f, nullptr, 0};
+    // Few CTAs (at most one per SM) and a long K: twice the weights per warp and step in flight (down_proj of the 1B
+    // shape: four dependent round trips become two).  FDMS_LINEAR_WIDE=0 turns it off.
+    static const bool wide_on = [] { const char* e = getenv("FDMS_LINEAR_WIDE"); return !(e && e[0] == '0'); }();
+    if (!norm && nt == 1 && wide_on && grid <= 148 && in_features % (kSgWarps * 512) == 0) {
+        if (bf)
+            FDMS_CUDA_OK(launch_chained(skinny_gemm_kernel<true, 1, false, false, 16>, dim3(grid), dim3(kSgWarps * 32), st, chain_launches(),
+                                        (const uint16_t*)x, x_row_stride, (const uint16_t*)weight, w_row_stride, (const uint16_t*)bias,
+                                        (uint16_t*)y, y_row_stride, (int)rows, (int)out_features, (int)in_features, nrm));
+        else
+            FDMS_CUDA_OK(launch_chained(skinny_gemm_kernel<false, 1, false, false, 16>, dim3(grid), dim3(kSgWarps * 32), st, chain_launches(),
+                                        (const uint16_t*)x, x_row_stride, (const uint16_t*)weight, w_row_stride, (const uint16_t*)bias,
+                                        (uint16_t*)y, y_row_stride, (int)rows, (int)out_features, (int)in_features, nrm));
+        FDMS_CHECK_LAUNCH("skinny_gemm_kernel (wide step)");
+        return FDMS_OK;
+    }
 #define FDMS_SG_LAUNCH(B, T, NM)                                                                                \
     FDMS_CUDA_OK(launch_chained(skinny_gemm_kernel<B, T, NM>, dim3(grid), dim3(kSgWarps * 32), st, chain_launches(), \
                                 (const uint16_t*)x, x_row_stride, (const uint16_t*)weight, w_row_stride,         \
