@@ -64,7 +64,8 @@ def run(args) -> dict:
         max_num_batched_tokens=max(4 * args.prefill_chunk, 8192) if args.prefill_chunk else max(2 * args.max_prompt, 16384),
         kv_cache_dtype="float8_e4m3fn", compact_kv_paged=args.paged, compact_kv_budget_bytes=budget,
         dms_window_size=args.window, compact_kv_admission=args.admission,
-        compact_kv_admission_keep_estimate=args.keep_estimate, prefill_chunk_size=args.prefill_chunk or None)
+        compact_kv_admission_keep_estimate=args.keep_estimate, prefill_chunk_size=args.prefill_chunk or None,
+        decode_run_ahead=args.run_ahead)
     mgr = engine.model_runner.compact_kv_manager
     vocab = hf["vocab_size"]
     g = torch.Generator().manual_seed(args.seed + rank)
@@ -152,7 +153,7 @@ def run(args) -> dict:
         "decode_steps": len(decode_ms), "decode_ms_per_step": {"p50": float(np.median(dm)), "p90": float(np.quantile(dm, 0.9))},
         "mean_decode_batch": float(np.mean(decode_batch)) if decode_batch else 0.0,
         "pool_rows_per_layer": mgr.capacity_tokens, "pool_gib": mgr.capacity_tokens * elem_rows / (1 << 30),
-        "peak_live_rows_layer0_sampled": peak_live, "admission": args.admission, "prefill_chunk": args.prefill_chunk,
+        "peak_live_rows_layer0_sampled": peak_live, "admission": args.admission, "prefill_chunk": args.prefill_chunk, "run_ahead": bool(args.run_ahead),
         "admission_denied": denied, "prefill_retries": retries, "preemptions": preempt,
         "pool_returned_clean": bool(pool_clean), "layout": "paged" if mgr.paged else "spans",
         "device_status": status,
@@ -176,6 +177,8 @@ def main() -> None:
     ap.add_argument("--admission", choices=["reserve", "optimistic"], default="reserve")
     ap.add_argument("--keep-estimate", type=float, default=0.2)
     ap.add_argument("--prefill-chunk", type=int, default=2048, help="prefill prompts in chunks of this many tokens (0: one pass)")
+    ap.add_argument("--run-ahead", action="store_true",
+                    help="launch the next decode step from device-resident tokens before this step's are read")
     ap.add_argument("--seed", type=int, default=0)
     out = run(ap.parse_args())
     if int(os.environ.get("RANK", "0")) == 0:
