@@ -699,9 +699,10 @@ __device__ __forceinline__ void fold_and_write(const AttnParams& p, float* s_m, 
 // the slot and lane s refills it with the warp's page R further on.  There is no producer warp and no
 // CTA-wide barrier in the page loop: eight issuers per CTA run in parallel, the prefetch depth costs
 // no registers, and a CTA whose range fits its rings (R pages per warp) has ALL of its K/V in flight
-// before the dependency on the preceding kernel is resolved.  With one CTA per SM and at most half an
-// SM's shared memory per CTA, the CTAs of the next launch of the stream are resident next to this
-// launch's, so their copies run under this launch's math and merge.
+// before the dependency on the preceding kernel is resolved.  With the default ring of 3 slots a CTA of head_dim 64
+// takes 69 KB of shared memory and about 80 registers per thread, so three CTAs fit on an SM (the host sizes the
+// grid for that; FDMS_ATTN_WAVE=1 launches one CTA per SM instead, which leaves room for the next launch of the
+// stream to be resident beside this one).
 // Every mbarrier wait is bounded; when one runs out the warp raises FDMS_DEV_WAIT_TIMEOUT, stops
 // issuing, gives its copies in flight a short time to land and goes on to the merge.
 // ------------------------------------------------------------------------------------------------
