@@ -1489,9 +1489,8 @@ static int32_t attn_decode_common(
         const char* loader = getenv("FDMS_ATTN_LOADER");
         const bool direct = !(loader && loader[0] == 's');
         const int ctas_per_sm = head_dim == 64 ? (direct ? 2 : 3) : 1;
-        // The staged kernel aims at ONE CTA per SM and at most half of an SM's shared memory per CTA
-        // (head_dim 64), so that the next launch of the stream is resident beside this one and its
-        // copies run under this launch's math; FDMS_ATTN_WAVE=2 fills both CTA slots with one launch.
+        // CTAs per SM the grid is sized for: what the kernel's registers and shared memory allow (two for the
+        // direct loader, three for the staged one at head_dim 64); FDMS_ATTN_WAVE=n sizes it for fewer.
         int wave = env_int("FDMS_ATTN_WAVE", 0);
         if (wave < 1) wave = ctas_per_sm;
         if (wave > ctas_per_sm) wave = ctas_per_sm;
