@@ -5,8 +5,11 @@ it off).
 Same class names, parameter layout and `weight_loader` protocol as the reference's
 `fastdms/layers/linear.py` (:946-1048), so checkpoints load the same way: QKV and gate/up are
 packed column-parallel weights, o_proj/down_proj are row-parallel and all-reduce their output over
-the tensor-parallel group (NCCL).  The reference's opt-in FP8/int4 weight paths are not part of the
-compact-DMS decode path and are not provided.
+the tensor-parallel group: at decode sizes in one launch with the projection (`fdms_linear_decode_allreduce`,
+see `layers/peer_allreduce.py`), otherwise with NCCL.  Other decode-size forms: the gate_up projection with its
+activation (`gated_linear`), weight-only FP8 (`LinearBase.quantize_fp8`, `Config.fp8_weights`).  The reference's
+activation-quantised FP8 and its int4 weight paths are not part of the compact-DMS decode path and are not
+provided.
 """
 from __future__ import annotations
 
