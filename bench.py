@@ -256,7 +256,7 @@ def run_reference(args) -> None:
                                    f"on {cores} host cores"},
         "e2e": {"value": value, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
-    print(json.dumps(line))
+    emit(line)
 
 
 # ------------------------------------------------------------------------------------------------
@@ -533,7 +533,7 @@ def run_ours(args) -> None:
                 "sample": f"{sample_steps} full decode steps (16 layers x 8 sequences x 8 KV heads) of the numpy oracle "
                           f"port of the reference's CPU path (contiguous-span layout), {procs} single-threaded worker "
                           f"processes on {os.cpu_count()} host cores"}
-        print(json.dumps(line))
+        emit(line)
     if world > 1:
         dist.destroy_process_group()
 
@@ -548,10 +548,30 @@ def main() -> None:
     ap.add_argument("--no-model", action="store_true", help="skip the whole-model block")
     ap.add_argument("--model-steps", type=int, default=64, help="decode steps of the whole-model block")
     args = ap.parse_args()
+    # The one JSON line is the only thing on standard output: libraries that print there from native code (NCCL's
+    # version banner under NCCL_DEBUG=WARN, for one) are sent to standard error for the length of the run.
+    global _RESULT_FD
+    sys.stdout.flush()
+    _RESULT_FD = os.dup(1)
+    os.dup2(2, 1)
     if args.impl == "reference":
         run_reference(args)
     else:
         run_ours(args)
+    sys.stdout.flush()
+
+
+_RESULT_FD = None
+
+
+def emit(line: dict) -> None:
+    """Writes the result line to the process's original standard output."""
+    data = (json.dumps(line) + "\n").encode()
+    if _RESULT_FD is None:
+        sys.stdout.write(data.decode())
+        sys.stdout.flush()
+    else:
+        os.write(_RESULT_FD, data)
 
 
 if __name__ == "__main__":
