@@ -127,7 +127,61 @@ __device__ __forceinline__ void pfx_stage_tile(const PrefixParams& p, int base, 
     }
 }
 
-// FP8 pools, software-pipelined: the bytes of the NEXT tile are fetched into registers (one 16-byte K
+// FP8 pools, software-pipelined: the bytes of the NEXT tile travel with asynchronous 16-byte copies into a raw
+// staging area in shared memory (no registers held across the math) while the warps compute on the current tile.
+// A thread converts exactly the vectors it copied itself, so waiting for its own copy group is enough.
+__device__ __forceinline__ void pfx_cp_async16(void* smem_dst, const void* gsrc) {
+    const uint32_t d = (uint32_t)__cvta_generic_to_shared(smem_dst);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d), "l"(gsrc) : "memory");
+}
+
+template <int D>
+__device__ __forceinline__ void pfx_fetch_tile(const PrefixParams& p, int base, const int32_t* bt, int live, int i0,
+                                               uint8_t* Kraw, uint8_t* Vraw, int tid, int nthreads) {
+    constexpr int VPR = D / 16;
+    for (int x = tid; x < kPfxTile * VPR; x += nthreads) {
+        const int r = x / VPR, c = x - r * VPR;
+        bool have = false;
+        if (i0 + r < live) {
+            const int64_t row = span_row(base, bt, i0 + r);
+            if (row >= 0 && row < p.pool_rows) {
+                pfx_cp_async16(Kraw + 16 * x, (const uint8_t*)p.k_pool + row * D + 16 * c);
+                pfx_cp_async16(Vraw + 16 * x, (const uint8_t*)p.v_pool + row * D + 16 * c);
+                have = true;
+            } else if (p.dev_status) {
+                atomicOr(p.dev_status, FDMS_DEV_BAD_INDEX);
+            }
+        }
+        if (!have) {
+            *(uint4*)(Kraw + 16 * x) = make_uint4(0u, 0u, 0u, 0u);
+            *(uint4*)(Vraw + 16 * x) = make_uint4(0u, 0u, 0u, 0u);
+        }
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+}
+
+template <int D>
+__device__ __forceinline__ void pfx_commit_tile(const uint8_t* Kraw, const uint8_t* Vraw, __half* Ks, __half* Vs, int tid,
+                                                int nthreads) {
+    constexpr int LD = D + 8, VPR = D / 16;
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    for (int x = tid; x < kPfxTile * VPR; x += nthreads) {
+        const int r = x / VPR, c = x - r * VPR;
+        const uint4 kb = *(const uint4*)(Kraw + 16 * x), vb = *(const uint4*)(Vraw + 16 * x);
+        uint4 lo, hi;
+        pfx_e4m3x4_to_f16x2x2(kb.x, lo.x, lo.y); pfx_e4m3x4_to_f16x2x2(kb.y, lo.z, lo.w);
+        pfx_e4m3x4_to_f16x2x2(kb.z, hi.x, hi.y); pfx_e4m3x4_to_f16x2x2(kb.w, hi.z, hi.w);
+        *(uint4*)(Ks + r * LD + 16 * c) = lo;
+        *(uint4*)(Ks + r * LD + 16 * c + 8) = hi;
+        pfx_e4m3x4_to_f16x2x2(vb.x, lo.x, lo.y); pfx_e4m3x4_to_f16x2x2(vb.y, lo.z, lo.w);
+        pfx_e4m3x4_to_f16x2x2(vb.z, hi.x, hi.y); pfx_e4m3x4_to_f16x2x2(vb.w, hi.z, hi.w);
+        *(uint4*)(Vs + r * LD + 16 * c) = lo;
+        *(uint4*)(Vs + r * LD + 16 * c + 8) = hi;
+    }
+}
+
+// The same look-ahead held in registers (head_dim 128, where the raw staging area would not fit the static
+// shared-memory limit and the kernel has registers to spare): the bytes of the NEXT tile are fetched into registers (one 16-byte K
 // and V vector per thread and pass) while the warps compute on the tile in shared memory.
 template <int D>
 struct PfxFetch {
@@ -136,7 +190,7 @@ struct PfxFetch {
 };
 
 template <int D>
-__device__ __forceinline__ void pfx_fetch_tile(const PrefixParams& p, int base, const int32_t* bt, int live, int i0,
+__device__ __forceinline__ void pfx_fetch_tile_regs(const PrefixParams& p, int base, const int32_t* bt, int live, int i0,
                                                PfxFetch<D>& f, int tid, int nthreads) {
     constexpr int VPR = D / 16;
 #pragma unroll
@@ -158,7 +212,7 @@ __device__ __forceinline__ void pfx_fetch_tile(const PrefixParams& p, int base, 
 }
 
 template <int D>
-__device__ __forceinline__ void pfx_commit_tile(const PfxFetch<D>& f, __half* Ks, __half* Vs, int tid, int nthreads) {
+__device__ __forceinline__ void pfx_commit_tile_regs(const PfxFetch<D>& f, __half* Ks, __half* Vs, int tid, int nthreads) {
     constexpr int LD = D + 8, VPR = D / 16;
 #pragma unroll
     for (int j = 0; j < PfxFetch<D>::kPasses; ++j) {
@@ -182,6 +236,9 @@ __global__ void __launch_bounds__(kPfxMaxWarps * 32, D == 64 ? 2 : 1) prefix_att
     constexpr int LD = D + 8, KS = D / 16, NT = D / 8;
     __shared__ __align__(16) __half Ks[kPfxTile * LD];
     __shared__ __align__(16) __half Vs[kPfxTile * LD];
+    constexpr bool kRawStage = D == 64;                         // next tile through shared memory (else registers)
+    __shared__ __align__(16) uint8_t Kraw[kRawStage ? kPfxTile * D : 16];        // the next tile's FP8 bytes
+    __shared__ __align__(16) uint8_t Vraw[kRawStage ? kPfxTile * D : 16];
     const int s = blockIdx.z, h = blockIdx.y;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
     const int nthreads = blockDim.x;
@@ -221,13 +278,23 @@ __global__ void __launch_bounds__(kPfxMaxWarps * 32, D == 64 ? 2 : 1) prefix_att
 
     const bool fp8 = p.kv_dtype == FDMS_E4M3;
     PfxFetch<D> nxt;
-    if (fp8) pfx_fetch_tile<D>(p, base, bt, live, 0, nxt, tid, nthreads);
+    if (fp8) {
+        if constexpr (kRawStage) pfx_fetch_tile<D>(p, base, bt, live, 0, Kraw, Vraw, tid, nthreads);
+        else pfx_fetch_tile_regs<D>(p, base, bt, live, 0, nxt, tid, nthreads);
+    }
     for (int i0 = 0; i0 < live; i0 += kPfxTile) {
         __syncthreads();                                  // the previous tile has been consumed
-        if (fp8) pfx_commit_tile<D>(nxt, Ks, Vs, tid, nthreads);
-        else pfx_stage_tile<D>(p, base, bt, live, i0, Ks, Vs, tid, nthreads);
+        if (fp8) {
+            if constexpr (kRawStage) pfx_commit_tile<D>(Kraw, Vraw, Ks, Vs, tid, nthreads);
+            else pfx_commit_tile_regs<D>(nxt, Ks, Vs, tid, nthreads);
+        } else {
+            pfx_stage_tile<D>(p, base, bt, live, i0, Ks, Vs, tid, nthreads);
+        }
         __syncthreads();
-        if (fp8 && i0 + kPfxTile < live) pfx_fetch_tile<D>(p, base, bt, live, i0 + kPfxTile, nxt, tid, nthreads);
+        if (fp8 && i0 + kPfxTile < live) {
+            if constexpr (kRawStage) pfx_fetch_tile<D>(p, base, bt, live, i0 + kPfxTile, Kraw, Vraw, tid, nthreads);
+            else pfx_fetch_tile_regs<D>(p, base, bt, live, i0 + kPfxTile, nxt, tid, nthreads);
+        }
         if (!active) continue;
         // ---- S = Q K^T for 64 span rows ----
         float sc[8][4];
