@@ -39,3 +39,22 @@ def test_cached_scratch_is_not_an_inference_tensor():
     finally:
         _lib._status_words.clear()
         _lib._status_words.update(saved)
+
+
+def test_reference_arm_prints_one_line_with_the_shared_config():
+    """`bench.py --impl reference` (the CPU arm) writes exactly one JSON line to standard output and names the
+    workload with the same `config` object as the GPU arm."""
+    import json
+    import subprocess
+    out = subprocess.run([sys.executable, str(ROOT / "bench.py"), "--impl", "reference", "--steps", "1", "--warmup", "0"],
+                         capture_output=True, text=True, timeout=600, cwd=str(ROOT))
+    assert out.returncode == 0, out.stderr[-400:]
+    lines = [l for l in out.stdout.splitlines() if l.strip()]
+    assert len(lines) == 1
+    d = json.loads(lines[0])
+    import bench
+    assert d["impl"] == "reference" and d["config"] == bench.workload_config(1)
+    assert d["unit"] == "tok/s" and d["higher_is_better"] is True and d["value"] > 0
+    assert d["e2e"]["h2d_bytes_per_step"] == 0 and d["cpu_baseline"]["kind"] == "port"
+    src = (ROOT / "bench.py").read_text()
+    assert src.count('"config": workload_config(') == 2          # both arms
